@@ -1,0 +1,165 @@
+// Shared device/host helpers of libmhlo_cuda.so: status plumbing, dtype traits, 128-bit streaming
+// loads/stores and warp/CTA reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/mhlo_cuda.h"
+
+namespace mhlo {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+// Records a printf-style message for mhlo_cuda_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+// Turns a CUDA runtime error into a status code with the failing call recorded.
+#define MHLO_CUDA_TRY(expr, code)                                                                \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess)                                                                   \
+            return ::mhlo::fail((code), "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),  \
+                                __FILE__, __LINE__);                                             \
+    } while (0)
+
+// Checks the launch that was just enqueued. A missing device or a wrong-arch build shows up here.
+#define MHLO_CUDA_CHECK_LAUNCH(what)                                                             \
+    do {                                                                                         \
+        cudaError_t _e = cudaGetLastError();                                                     \
+        if (_e != cudaSuccess) {                                                                 \
+            int _c = (_e == cudaErrorNoDevice || _e == cudaErrorInsufficientDriver)              \
+                         ? MHLO_CUDA_NO_DEVICE                                                   \
+                         : MHLO_CUDA_EXECUTION_FAILED;                                           \
+            return ::mhlo::fail(_c, "launch of %s failed: %s", (what), cudaGetErrorString(_e));  \
+        }                                                                                        \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- 16-byte vectors of T <-> fp32 ------------------------------------------------------------------
+
+template <typename T>
+struct VecTraits;
+
+template <>
+struct VecTraits<float> {
+    static constexpr int kElems = 4;
+    __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+        f[0] = __uint_as_float(v.x);
+        f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z);
+        f[3] = __uint_as_float(v.w);
+    }
+    __device__ __forceinline__ static uint4 pack(const float* f) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                          __float_as_uint(f[3]));
+    }
+    __device__ __forceinline__ static float to_float(float x) { return x; }
+    __device__ __forceinline__ static float from_float(float x) { return x; }
+};
+
+template <>
+struct VecTraits<__nv_bfloat16> {
+    static constexpr int kElems = 8;
+    __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ __forceinline__ static uint4 pack(const float* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ static float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+    __device__ __forceinline__ static __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+
+template <>
+struct VecTraits<__half> {
+    static constexpr int kElems = 8;
+    __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = p.x;
+            f[2 * i + 1] = p.y;
+        }
+    }
+    __device__ __forceinline__ static uint4 pack(const float* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 p = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ static float to_float(__half x) { return __half2float(x); }
+    __device__ __forceinline__ static __half from_float(float x) { return __float2half_rn(x); }
+};
+
+// Streaming 128-bit global access: the row kernels touch every byte once, so they bypass L1 on the way
+// in and mark stores evict-first on the way out.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+// ---- reductions --------------------------------------------------------------------------------------
+
+struct SumOp {
+    __device__ __forceinline__ static float apply(float a, float b) { return a + b; }
+    __device__ __forceinline__ static float identity() { return 0.f; }
+};
+struct MaxOp {
+    __device__ __forceinline__ static float apply(float a, float b) { return fmaxf(a, b); }
+    __device__ __forceinline__ static float identity() { return -INFINITY; }
+};
+
+template <typename Op>
+__device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// All-reduce over the CTA. `scratch` is 32 floats of shared memory that the caller alternates between
+// consecutive reductions, so one __syncthreads() per reduction is enough. With a single warp no shared
+// memory is touched.
+template <typename Op>
+__device__ __forceinline__ float cta_reduce(float v, float* scratch) {
+    v = warp_reduce<Op>(v);
+    const int nwarps = blockDim.x >> 5;
+    if (nwarps == 1) return v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = lane < nwarps ? scratch[lane] : Op::identity();
+    return warp_reduce<Op>(r);
+}
+
+}  // namespace mhlo

@@ -1,0 +1,177 @@
+// Device, memory, stream and event entry points of libmhlo_cuda.so plus the thread-local error slot.
+// They stand where IntegratedExecutor uses MTLDevice/MTLBuffer/MTLCommandBuffer
+// (Sources/MetalHLOCore/Runtime/IntegratedExecutor.swift:106-141,182-190,232-252).
+#include <cstring>
+
+#include "common.cuh"
+
+namespace mhlo {
+
+static thread_local char g_error[1024] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+void clear_error() { g_error[0] = '\0'; }
+
+}  // namespace mhlo
+
+using mhlo::fail;
+
+extern "C" {
+
+const char* mhlo_cuda_version(void) { return "mhlo-cuda 0.1.0 sm_100a"; }
+
+const char* mhlo_cuda_last_error(void) { return mhlo::g_error; }
+
+size_t mhlo_cuda_dtype_size(int dtype) {
+    switch (dtype) {
+        case MHLO_DT_F16: case MHLO_DT_BF16: case MHLO_DT_I16: case MHLO_DT_UI16: return 2;
+        case MHLO_DT_F32: case MHLO_DT_I32: case MHLO_DT_UI32: return 4;
+        case MHLO_DT_F64: case MHLO_DT_I64: case MHLO_DT_UI64: return 8;
+        case MHLO_DT_I1: case MHLO_DT_I8: case MHLO_DT_UI8: return 1;
+        default: return 0;
+    }
+}
+
+int mhlo_cuda_device_count(int* out_count) {
+    if (!out_count) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_count: null output");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        *out_count = 0;
+        return fail(MHLO_CUDA_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    }
+    *out_count = n;
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_device_set(int ordinal) {
+    MHLO_CUDA_TRY(cudaSetDevice(ordinal), MHLO_CUDA_NO_DEVICE);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_device_name(int ordinal, char* out_name, size_t cap) {
+    if (!out_name || cap == 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_name: no output buffer");
+    cudaDeviceProp prop;
+    MHLO_CUDA_TRY(cudaGetDeviceProperties(&prop, ordinal), MHLO_CUDA_NO_DEVICE);
+    snprintf(out_name, cap, "%s", prop.name);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_stream_create(mhlo_cuda_stream_t* out_stream) {
+    if (!out_stream) return fail(MHLO_CUDA_INVALID_ARGUMENT, "stream_create: null output");
+    cudaStream_t s;
+    MHLO_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), MHLO_CUDA_NO_DEVICE);
+    *out_stream = s;
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_stream_destroy(mhlo_cuda_stream_t stream) {
+    MHLO_CUDA_TRY(cudaStreamDestroy(static_cast<cudaStream_t>(stream)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_stream_sync(mhlo_cuda_stream_t stream) {
+    MHLO_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_alloc(size_t bytes, void** out_dev) {
+    if (!out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "alloc: null output");
+    *out_dev = nullptr;
+    if (bytes == 0) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaMalloc(out_dev, bytes), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_free(void* dev) {
+    if (!dev) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaFree(dev), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_host_alloc(size_t bytes, void** out_host) {
+    if (!out_host) return fail(MHLO_CUDA_INVALID_ARGUMENT, "host_alloc: null output");
+    *out_host = nullptr;
+    if (bytes == 0) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaMallocHost(out_host, bytes), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_host_free(void* host) {
+    if (!host) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaFreeHost(host), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_upload(void* dst_dev, const void* src_host, size_t bytes, mhlo_cuda_stream_t stream) {
+    if (bytes == 0) return MHLO_CUDA_OK;
+    if (!dst_dev || !src_host) return fail(MHLO_CUDA_INVALID_ARGUMENT, "upload: null pointer");
+    MHLO_CUDA_TRY(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice,
+                                  static_cast<cudaStream_t>(stream)),
+                  MHLO_CUDA_TRANSFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_download(void* dst_host, const void* src_dev, size_t bytes, mhlo_cuda_stream_t stream) {
+    if (bytes == 0) return MHLO_CUDA_OK;
+    if (!dst_host || !src_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "download: null pointer");
+    MHLO_CUDA_TRY(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream)),
+                  MHLO_CUDA_TRANSFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_copy(void* dst_dev, const void* src_dev, size_t bytes, mhlo_cuda_stream_t stream) {
+    if (bytes == 0) return MHLO_CUDA_OK;
+    if (!dst_dev || !src_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "copy: null pointer");
+    MHLO_CUDA_TRY(cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice,
+                                  static_cast<cudaStream_t>(stream)),
+                  MHLO_CUDA_TRANSFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_memset(void* dst_dev, int byte_value, size_t bytes, mhlo_cuda_stream_t stream) {
+    if (bytes == 0) return MHLO_CUDA_OK;
+    if (!dst_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "memset: null pointer");
+    MHLO_CUDA_TRY(cudaMemsetAsync(dst_dev, byte_value, bytes, static_cast<cudaStream_t>(stream)),
+                  MHLO_CUDA_TRANSFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_event_create(void** out_event) {
+    if (!out_event) return fail(MHLO_CUDA_INVALID_ARGUMENT, "event_create: null output");
+    cudaEvent_t e;
+    MHLO_CUDA_TRY(cudaEventCreate(&e), MHLO_CUDA_NO_DEVICE);
+    *out_event = e;
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_event_destroy(void* event) {
+    if (!event) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaEventDestroy(static_cast<cudaEvent_t>(event)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_event_record(void* event, mhlo_cuda_stream_t stream) {
+    MHLO_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)),
+                  MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_event_elapsed_ms(void* start, void* stop, float* out_ms) {
+    if (!out_ms) return fail(MHLO_CUDA_INVALID_ARGUMENT, "event_elapsed_ms: null output");
+    MHLO_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)), MHLO_CUDA_EXECUTION_FAILED);
+    MHLO_CUDA_TRY(cudaEventElapsedTime(out_ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)),
+                  MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+}  // extern "C"
