@@ -216,6 +216,12 @@ def run_ours(args):
                      for i, n in enumerate(names)}
     clocks = sampler.stop() if rank == 0 else None
 
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"kernels_only": True, "rows": ROWS, "per_kernel_gbs":
+                              {n: KERNEL_BYTES / (per_kernel_ms[n] * 1e-3) / 1e9 for n in names}}))
+        return
+
     # ---- end to end through the C ABI with host buffers: upload, three kernels, download of every result ----
     y_host = [torch.empty_like(x_host) for _ in range(3)]
     nbytes = x_host.numel() * 2
@@ -294,15 +300,22 @@ TRAFFIC_BYTES: dict = {}
 
 
 def main():
+    global ROWS, KERNEL_BYTES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="norms")
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="rows of the norm sweep (default: the benchmark configuration; smaller for profiler captures)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "ours":
+    if args.warmup < 3 and args.impl == "ours" and not args.kernels_only:
         args.warmup = 3
+    ROWS = args.rows
+    KERNEL_BYTES = ROWS * HIDDEN * 2 * 2
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -97,7 +97,7 @@ int mhlo_cuda_event_elapsed_ms(void* start, void* stop, float* out_ms);
  * Sources/MetalHLOCore/Compiler/KernelTypes.swift:212-257). Zero in a field = let the library choose.
  *   threads        threads per CTA (multiple of 32, <= 1024); one CTA works on one row at a time
  *   vecs_per_thread  16-byte vectors each thread keeps in registers (1, 2, 4 or 8)
- *   ctas_per_sm    grid = min(rows, 148 * ctas_per_sm) CTAs walking rows with a grid stride
+ *   ctas_per_sm    CTAs per SM of the persistent grid; 0 = as many as fit (occupancy query), -1 = one CTA per row
  */
 typedef struct {
     int32_t threads;

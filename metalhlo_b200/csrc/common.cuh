@@ -61,6 +61,14 @@ struct VecTraits<float> {
         return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
                           __float_as_uint(f[3]));
     }
+    __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+        f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+        f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2* f) {
+        return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x),
+                          __float_as_uint(f[1].y));
+    }
     __device__ __forceinline__ static float to_float(float x) { return x; }
     __device__ __forceinline__ static float from_float(float x) { return x; }
 };
@@ -81,6 +89,21 @@ struct VecTraits<__nv_bfloat16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 p = __float22bfloat162_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&p);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
@@ -106,6 +129,20 @@ struct VecTraits<__half> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             __half2 p = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 p = __float22half2_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&p);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);

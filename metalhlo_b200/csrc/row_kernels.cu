@@ -35,106 +35,227 @@ constexpr int row_vec_max_threads() {
     return vals > 32 ? 256 : (vals > 16 ? 512 : 1024);
 }
 
-template <typename T, int VPT, int OP>
-__global__ void __launch_bounds__((row_vec_max_threads<T, VPT>())) row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
-                                                       const T* __restrict__ beta, T* __restrict__ y,
-                                                       int64_t rows, int hidden, float eps) {
+// Packed fp32x2 arithmetic (one issue slot for two lanes of math on sm_100). The row kernels are bound by
+// instruction issue before they are bound by HBM, so every per-element operation is done two at a time.
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// CTA all-reduce with one barrier. `scratch` is 32 floats whose slots at and above the warp count hold the
+// identity (written once at kernel start); the caller never reuses a scratch array for two consecutive
+// reductions, which is what makes a single __syncthreads() per reduction safe.
+template <typename Op>
+__device__ __forceinline__ float cta_reduce1(float v, float* scratch, int nwarps) {
+    v = warp_reduce<Op>(v);
+    if (nwarps == 1) return v;
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (nwarps <= 4) {
+        const float4 r = *reinterpret_cast<const float4*>(scratch);
+        return Op::apply(Op::apply(r.x, r.y), Op::apply(r.z, r.w));
+    }
+    return warp_reduce<Op>(scratch[threadIdx.x & 31]);
+}
+
+// One CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... Each thread owns VPT 16-byte vectors of the row
+// (vector index tid + i*blockDim.x), keeps them as fp32 pairs in registers and has the next row's vectors in
+// flight while it works on the current one. gamma/beta are widened to fp32 once per CTA into shared memory,
+// laid out in float4 planes so that a warp's reads are contiguous. FULL = every thread slot maps to a real
+// vector (no predicates in the loop).
+constexpr int kDepth = 2;
+
+template <typename T, int VPT, int OP, bool FULL>
+__global__ void __launch_bounds__((row_vec_max_threads<T, VPT>()))
+row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+               T* __restrict__ y, int64_t rows, int hidden, float eps) {
     using VT = VecTraits<T>;
     constexpr int E = VT::kElems;
-    __shared__ float red[2][32];
-    const int nvec = hidden / E;
-    const float inv_n = 1.0f / static_cast<float>(hidden);
-    int ph = 0;  // which half of red[] the next reduction uses; alternating makes one barrier per reduction safe
+    constexpr int H = E / 2;  // float2 per vector
+    constexpr int P = E / 4;  // float4 planes per vector
+    extern __shared__ __align__(16) float params[];
+    __shared__ __align__(16) float red[2][32];
 
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const uint4* xr = reinterpret_cast<const uint4*>(x + row * hidden);
-        uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
-        float v[VPT][E];
-        bool live[VPT];
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    const int nwarps = nthreads >> 5;
+    const int nvec = hidden / E;
+    const int nslots = nthreads * VPT;
+    const float inv_n = 1.0f / static_cast<float>(hidden);
+    float4* const gsm = reinterpret_cast<float4*>(params);
+    float4* const bsm = gsm + P * nslots;
+
+    bool live[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) live[i] = FULL || (tid + i * nthreads < nvec);
+
+    if (tid < 32) {
+        red[0][tid] = (OP == kSoftmax) ? -INFINITY : 0.f;
+        red[1][tid] = 0.f;
+    }
+    if constexpr (OP != kSoftmax) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int idx = threadIdx.x + i * blockDim.x;
-            live[i] = idx < nvec;
-            if (live[i]) {
-                VT::unpack(ld_stream16(xr + idx), v[i]);
+            const int idx = tid + i * nthreads;
+            if (!live[i]) continue;
+            float2 g[H], b[H];
+            if (gamma != nullptr) {
+                VT::unpack2(__ldg(reinterpret_cast<const uint4*>(gamma) + idx), g);
             } else {
 #pragma unroll
-                for (int e = 0; e < E; ++e) v[i][e] = (OP == kSoftmax) ? -INFINITY : 0.f;
+                for (int h = 0; h < H; ++h) g[h] = splat2(1.f);
+            }
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                gsm[p * nslots + idx] = make_float4(g[2 * p].x, g[2 * p].y, g[2 * p + 1].x, g[2 * p + 1].y);
+            if constexpr (OP == kLayerNorm) {
+                if (beta != nullptr) {
+                    VT::unpack2(__ldg(reinterpret_cast<const uint4*>(beta) + idx), b);
+                } else {
+#pragma unroll
+                    for (int h = 0; h < H; ++h) b[h] = splat2(0.f);
+                }
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+                    bsm[p * nslots + idx] = make_float4(b[2 * p].x, b[2 * p].y, b[2 * p + 1].x, b[2 * p + 1].y);
             }
         }
+    }
+    __syncthreads();
+
+    // Register ring of kDepth rows: row r + kDepth*gridDim.x is requested as soon as row r has been unpacked,
+    // so kDepth rows per CTA are in flight while one is being worked on.
+    uint4 raw[kDepth][VPT];
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) {
+        const int64_t r = blockIdx.x + static_cast<int64_t>(d) * gridDim.x;
+        if (r < rows) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + r * hidden);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+                if (live[i]) raw[d][i] = ld_stream16(xr + tid + i * nthreads);
+        }
+    }
+    int ph = 0;
+    for (int64_t row0 = blockIdx.x; row0 < rows; row0 += static_cast<int64_t>(kDepth) * gridDim.x) {
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        const int64_t row = row0 + static_cast<int64_t>(d) * gridDim.x;
+        if (row >= rows) break;
+        float2 v[VPT][H];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            if (live[i]) {
+                VT::unpack2(raw[d][i], v[i]);
+            } else {
+#pragma unroll
+                for (int h = 0; h < H; ++h) v[i][h] = splat2((OP == kSoftmax) ? -INFINITY : 0.f);
+            }
+        }
+        const int64_t next = row + static_cast<int64_t>(kDepth) * gridDim.x;
+        if (next < rows) {
+            const uint4* xn = reinterpret_cast<const uint4*>(x + next * hidden);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+                if (live[i]) raw[d][i] = ld_stream16(xn + tid + i * nthreads);
+        }
+        uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
 
         if constexpr (OP == kSoftmax) {
             float m = -INFINITY;
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                for (int e = 0; e < E; ++e) m = fmaxf(m, v[i][e]);
-            m = cta_reduce<MaxOp>(m, red[ph]);
-            ph ^= 1;
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i)
-#pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    v[i][e] = row_exp<T>(v[i][e] - m);  // exp(-inf) = 0 for the padding lanes
-                    s += v[i][e];
-                }
-            s = cta_reduce<SumOp>(s, red[ph]);
-            ph ^= 1;
-            const float inv = 1.0f / s;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                if (!live[i]) continue;
-#pragma unroll
-                for (int e = 0; e < E; ++e) v[i][e] *= inv;
-                st_stream16(yr + threadIdx.x + i * blockDim.x, VT::pack(v[i]));
-            }
-        } else {
-            float mean = 0.f;
-            if constexpr (OP == kLayerNorm) {
-                float s = 0.f;
+                for (int h = 0; h < H; ++h) m = fmaxf(m, fmaxf(v[i][h].x, v[i][h].y));
+            m = cta_reduce1<MaxOp>(m, red[0], nwarps);
+            float2 s2 = splat2(0.f);
+            if constexpr (sizeof(T) == 2) {
+                // exp(x - m) = 2^(x*log2(e) - m*log2(e)): one packed FMA and one ex2 per element
+                const float2 l2 = splat2(1.4426950408889634f);
+                const float2 nb = splat2(-m * 1.4426950408889634f);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                    for (int e = 0; e < E; ++e) s += v[i][e];
-                mean = cta_reduce<SumOp>(s, red[ph]) * inv_n;
+                    for (int h = 0; h < H; ++h) {
+                        const float2 t = fma2(v[i][h], l2, nb);
+                        v[i][h] = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+                        s2 = add2(s2, v[i][h]);
+                    }
+            } else {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+                        v[i][h] = make_float2(expf(v[i][h].x - m), expf(v[i][h].y - m));
+                        s2 = add2(s2, v[i][h]);
+                    }
+            }
+            const float s = cta_reduce1<SumOp>(s2.x + s2.y, red[1], nwarps);
+            const float2 inv = splat2(__frcp_rn(s));
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                if (!live[i]) continue;
+#pragma unroll
+                for (int h = 0; h < H; ++h) v[i][h] = mul2(v[i][h], inv);
+                st_stream16(yr + tid + i * nthreads, VT::pack2(v[i]));
+            }
+        } else {
+            float rstd;
+            if constexpr (OP == kLayerNorm) {
+                float2 s2 = splat2(0.f);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                    for (int h = 0; h < H; ++h) s2 = add2(s2, v[i][h]);
+                const float mean = cta_reduce1<SumOp>(s2.x + s2.y, red[0], nwarps) * inv_n;
+                const float2 nm = splat2(-mean);
+                float2 q2 = splat2(0.f);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    if (!live[i]) continue;
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+                        v[i][h] = add2(v[i][h], nm);
+                        q2 = fma2(v[i][h], v[i][h], q2);
+                    }
+                }
+                rstd = rsqrtf(cta_reduce1<SumOp>(q2.x + q2.y, red[1], nwarps) * inv_n + eps);
+            } else {
+                float2 q2 = splat2(0.f);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                    for (int h = 0; h < H; ++h) q2 = fma2(v[i][h], v[i][h], q2);
+                rstd = rsqrtf(cta_reduce1<SumOp>(q2.x + q2.y, red[ph], nwarps) * inv_n + eps);
                 ph ^= 1;
             }
-            float q = 0.f;
+            const float2 r2 = splat2(rstd);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 if (!live[i]) continue;
+                const int idx = tid + i * nthreads;
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    const float d = v[i][e] - mean;
-                    q += d * d;
+                for (int p = 0; p < P; ++p) {
+                    const float4 g4 = gsm[p * nslots + idx];
+                    if constexpr (OP == kLayerNorm) {
+                        const float4 b4 = bsm[p * nslots + idx];
+                        v[i][2 * p] = fma2(mul2(v[i][2 * p], r2), make_float2(g4.x, g4.y), make_float2(b4.x, b4.y));
+                        v[i][2 * p + 1] =
+                            fma2(mul2(v[i][2 * p + 1], r2), make_float2(g4.z, g4.w), make_float2(b4.z, b4.w));
+                    } else {
+                        v[i][2 * p] = mul2(mul2(v[i][2 * p], r2), make_float2(g4.x, g4.y));
+                        v[i][2 * p + 1] = mul2(mul2(v[i][2 * p + 1], r2), make_float2(g4.z, g4.w));
+                    }
                 }
-            }
-            q = cta_reduce<SumOp>(q, red[ph]);
-            ph ^= 1;
-            const float rstd = 1.0f / sqrtf(q * inv_n + eps);
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                if (!live[i]) continue;
-                const int idx = threadIdx.x + i * blockDim.x;
-                float g[E], b[E];
-                if (gamma != nullptr) {
-                    VT::unpack(__ldg(reinterpret_cast<const uint4*>(gamma) + idx), g);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < E; ++e) g[e] = 1.f;
-                }
-                if (OP == kLayerNorm && beta != nullptr) {
-                    VT::unpack(__ldg(reinterpret_cast<const uint4*>(beta) + idx), b);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < E; ++e) b[e] = 0.f;
-                }
-#pragma unroll
-                for (int e = 0; e < E; ++e) v[i][e] = (v[i][e] - mean) * rstd * g[e] + b[e];
-                st_stream16(yr + idx, VT::pack(v[i]));
+                st_stream16(yr + idx, VT::pack2(v[i]));
             }
         }
+      }
     }
 }
 
@@ -199,7 +320,10 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
     T* yp = static_cast<T*>(y);
 
     const int64_t nvec = len / E;
-    const bool vec_ok = inner == 1 && len % E == 0 && nvec <= 8 * 1024 && aligned16(x) && aligned16(y) &&
+    // Largest row the register-resident kernel covers: 8 vectors per thread at the CTA size that leaves
+    // room for 8*E fp32 values per thread.
+    const int64_t max_vecs = 8 * (8 * E > 32 ? 256 : 512);
+    const bool vec_ok = inner == 1 && len % E == 0 && nvec <= max_vecs && aligned16(x) && aligned16(y) &&
                         aligned16(gamma) && aligned16(beta);
     if (!vec_ok) {
         const int grid = static_cast<int>(rows < 148LL * 64 ? rows : 148LL * 64);
@@ -210,18 +334,16 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
 
     int vpt = tuning ? tuning->vecs_per_thread : 0;
     int threads = tuning ? tuning->threads : 0;
-    int ctas_per_sm = tuning ? tuning->ctas_per_sm : 0;
+    const int ctas_per_sm = tuning ? tuning->ctas_per_sm : 0;
     if (vpt == 0) {
-        vpt = 1;
-        while (vpt < 8 && nvec > 128LL * vpt) vpt *= 2;
-        if (sizeof(T) == 2 && vpt > 4 && nvec <= 1024 * 4) vpt = 4;  // keep 16-bit rows at <= 32 fp32 regs
+        // 32 fp32 values per thread measured best on B200 (128 threads for a 4096-wide bf16 row); short rows
+        // shrink the share so that a CTA still has at least one full warp.
+        vpt = 32 / E;
+        while (vpt > 1 && nvec < 32LL * vpt) vpt /= 2;
+        while (vpt < 8 && (nvec + vpt - 1) / vpt > (vpt * E > 32 ? 256 : (vpt * E > 16 ? 512 : 1024))) vpt *= 2;
     }
     if (vpt != 1 && vpt != 2 && vpt != 4 && vpt != 8)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: vecs_per_thread must be 1, 2, 4 or 8 (got %d)", what, vpt);
-    if (threads == 0 && !(tuning && tuning->vecs_per_thread)) {
-        // grow the per-thread share until the CTA fits its register-derived thread limit
-        while (vpt < 8 && (nvec + vpt - 1) / vpt > (vpt * E > 32 ? 256 : (vpt * E > 16 ? 512 : 1024))) vpt *= 2;
-    }
     if (threads == 0) threads = static_cast<int>(((nvec + vpt - 1) / vpt + 31) / 32 * 32);
     if (threads % 32 != 0 || threads < 32 || threads > 1024)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: threads must be a multiple of 32 in [32,1024] (got %d)",
@@ -233,18 +355,44 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
     if (static_cast<int64_t>(threads) * vpt < nvec)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: threads*vecs_per_thread=%d does not cover %lld vectors",
                     what, threads * vpt, static_cast<long long>(nvec));
-    int64_t grid = rows;
-    if (ctas_per_sm > 0 && grid > static_cast<int64_t>(kNumSMs) * ctas_per_sm)
-        grid = static_cast<int64_t>(kNumSMs) * ctas_per_sm;
-    if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
-    const int h = static_cast<int>(len);
-    const int g = static_cast<int>(grid);
+    const bool full = static_cast<int64_t>(threads) * vpt == nvec;
+    const size_t smem = (OP == kLayerNorm ? 2 : (OP == kRmsNorm ? 1 : 0)) * sizeof(float) * E * threads * vpt;
+    if (smem > 200 * 1024)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: %d threads x %d vectors need %zu bytes of shared memory",
+                    what, threads, vpt, smem);
+
+    using Kernel = void (*)(const T*, const T*, const T*, T*, int64_t, int, float);
+    Kernel kernel = nullptr;
+#define MHLO_ROW_PICK(V)                                                                      \
+    case V:                                                                                   \
+        kernel = full ? row_vec_kernel<T, V, OP, true> : row_vec_kernel<T, V, OP, false>;     \
+        break;
     switch (vpt) {
-        case 1: row_vec_kernel<T, 1, OP><<<g, threads, 0, stream>>>(xp, gp, bp, yp, rows, h, eps); break;
-        case 2: row_vec_kernel<T, 2, OP><<<g, threads, 0, stream>>>(xp, gp, bp, yp, rows, h, eps); break;
-        case 4: row_vec_kernel<T, 4, OP><<<g, threads, 0, stream>>>(xp, gp, bp, yp, rows, h, eps); break;
-        default: row_vec_kernel<T, 8, OP><<<g, threads, 0, stream>>>(xp, gp, bp, yp, rows, h, eps); break;
+        MHLO_ROW_PICK(1)
+        MHLO_ROW_PICK(2)
+        MHLO_ROW_PICK(4)
+        MHLO_ROW_PICK(8)
     }
+#undef MHLO_ROW_PICK
+    if (smem + 1024 > 48 * 1024)
+        MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                      MHLO_CUDA_EXECUTION_FAILED);
+    int64_t grid = rows;
+    if (ctas_per_sm >= 0) {
+        int per_sm = ctas_per_sm;
+        if (per_sm == 0) {
+            MHLO_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem),
+                          MHLO_CUDA_NO_DEVICE);
+            // more than ~16 resident warps per SM measured slower (the rows in flight stop fitting the DRAM pages
+            // the SM has open), so the occupancy bound is capped
+            const int cap = 512 / threads > 4 ? 512 / threads : 4;
+            if (per_sm > cap) per_sm = cap;
+            if (per_sm < 1) per_sm = 1;
+        }
+        if (grid > static_cast<int64_t>(kNumSMs) * per_sm) grid = static_cast<int64_t>(kNumSMs) * per_sm;
+    }
+    if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
+    kernel<<<static_cast<int>(grid), threads, smem, stream>>>(xp, gp, bp, yp, rows, static_cast<int>(len), eps);
     MHLO_CUDA_CHECK_LAUNCH(what);
     return MHLO_CUDA_OK;
 }
