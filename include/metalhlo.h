@@ -1,0 +1,171 @@
+/*
+ * metalhlo.h — the MetalHLO C API as served by the B200 backend (libCMetalHLO.so).
+ *
+ * Every name, enum value, struct layout and calling convention below is that of the reference's C API
+ * (Sources/CMetalHLO/include/metalhlo.h:23-397, implemented in Sources/CMetalHLO/CInterface.swift:202-1010),
+ * so a C or C++ host written against MetalHLO links against this library unchanged. What differs is what runs
+ * underneath: StableHLO text is compiled by the C++ compiler core and executed by hand-written sm_100a CUDA
+ * kernels. There is no CPU fallback; without a CUDA device mhlo_client_create returns MHLO_ERROR_NO_DEVICE.
+ *
+ * Ownership: handles are opaque pointers. Whoever receives a handle from *_create, mhlo_compile* or
+ * mhlo_execute* destroys it with the matching *_destroy. Strings from mhlo_client_device_name are heap copies
+ * released with mhlo_free_string; mhlo_version and mhlo_get_last_error return library-owned storage.
+ * Errors: functions return an MHLOStatusCode; the message of the most recent failure (process-global, as in the
+ * reference, CInterface.swift:116-126) is read with mhlo_get_last_error. Calls are synchronous. A handle must
+ * not be used from two threads at once.
+ */
+#ifndef METALHLO_H
+#define METALHLO_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* MHLOClientRef;
+typedef void* MHLOExecutableRef;
+typedef void* MHLOBufferRef;
+
+/* reference: metalhlo.h:37-49 */
+typedef enum {
+    MHLO_OK = 0,
+    MHLO_ERROR_NO_DEVICE = 1,
+    MHLO_ERROR_UNSUPPORTED_DEVICE = 2,
+    MHLO_ERROR_PARSE_FAILED = 3,
+    MHLO_ERROR_UNSUPPORTED_OP = 4,
+    MHLO_ERROR_COMPILATION_FAILED = 5,
+    MHLO_ERROR_BUFFER_FAILED = 6,
+    MHLO_ERROR_INPUT_MISMATCH = 7,
+    MHLO_ERROR_EXECUTION_FAILED = 8,
+    MHLO_ERROR_TRANSFER_FAILED = 9,
+    MHLO_ERROR_INVALID_ARGUMENT = 10,
+} MHLOStatusCode;
+
+/* reference: metalhlo.h:61-75 */
+typedef enum {
+    MHLO_F16 = 0, MHLO_F32 = 1, MHLO_F64 = 2, MHLO_BF16 = 3, MHLO_I1 = 4, MHLO_I8 = 5, MHLO_I16 = 6,
+    MHLO_I32 = 7, MHLO_I64 = 8, MHLO_UI8 = 9, MHLO_UI16 = 10, MHLO_UI32 = 11, MHLO_UI64 = 12,
+} MHLOElementType;
+
+/* reference: metalhlo.h:102-107 */
+typedef enum { MHLO_OPT_O0 = 0, MHLO_OPT_O1 = 1, MHLO_OPT_O2 = 2, MHLO_OPT_O3 = 3 } MHLOOptimizationLevel;
+
+/* reference: metalhlo.h:110-116. Accepted for compatibility; every policy runs on the CUDA device. */
+typedef enum {
+    MHLO_DEVICE_GPU_ONLY = 0, MHLO_DEVICE_ANE_ONLY = 1, MHLO_DEVICE_AUTO = 2, MHLO_DEVICE_PREFER_ANE = 3,
+    MHLO_DEVICE_PREFER_GPU = 4,
+} MHLODevicePolicy;
+
+/* reference: metalhlo.h:119-128 */
+typedef struct {
+    MHLOOptimizationLevel optimization_level; /* default MHLO_OPT_O2 */
+    bool enable_caching;                      /* default true: identical text + config reuses the compiled program */
+    bool enable_debug_info;                   /* default false */
+    MHLODevicePolicy device_policy;           /* default MHLO_DEVICE_GPU_ONLY */
+} MHLOCompileConfig;
+
+/* reference: metalhlo.h:221-230 */
+typedef struct {
+    int64_t execution_count;
+    double total_execution_time_ms;
+    double last_execution_time_ms;
+    double average_execution_time_ms;
+} MHLOExecutionStats;
+
+/* reference: metalhlo.h:351-368. The ANE fields are always zero / false here. */
+typedef struct {
+    int32_t partition_count;
+    int32_t gpu_partition_count;
+    int32_t ane_partition_count;
+    double gpu_time_ms;
+    double ane_time_ms;
+    double transfer_time_ms;
+    double total_time_ms;
+    bool used_ane;
+} MHLOExecutionProfile;
+
+/* ---- library (reference: metalhlo.h:23, 53-56, 78, 397) ---- */
+const char* mhlo_version(void);
+const char* mhlo_get_last_error(void);
+void mhlo_clear_error(void);
+size_t mhlo_element_type_size(MHLOElementType type); /* 0 for I1, as in the reference */
+void mhlo_free_string(const char* str);
+
+/* ---- client (reference: metalhlo.h:87-95) ---- */
+MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client);
+void mhlo_client_destroy(MHLOClientRef client);
+char* mhlo_client_device_name(MHLOClientRef client);
+
+/* ---- compilation (reference: metalhlo.h:132-177) ---- */
+void mhlo_compile_config_init(MHLOCompileConfig* out_config);
+bool mhlo_ane_available(void); /* always false on this backend */
+MHLOStatusCode mhlo_compile(MHLOClientRef client, const char* mlir_text, MHLOExecutableRef* out_executable);
+MHLOStatusCode mhlo_compile_n(MHLOClientRef client, const char* mlir_text, size_t mlir_length,
+                              MHLOExecutableRef* out_executable);
+MHLOStatusCode mhlo_compile_with_config(MHLOClientRef client, const char* mlir_text,
+                                        const MHLOCompileConfig* config, MHLOExecutableRef* out_executable);
+
+/* ---- executable (reference: metalhlo.h:180-243) ---- */
+void mhlo_executable_destroy(MHLOExecutableRef executable);
+int32_t mhlo_executable_input_count(MHLOExecutableRef executable);
+int32_t mhlo_executable_output_count(MHLOExecutableRef executable);
+/* out_shape (room for the rank), out_rank and out_element_type may each be NULL. */
+MHLOStatusCode mhlo_executable_input_type(MHLOExecutableRef executable, int32_t index, int64_t* out_shape,
+                                          int32_t* out_rank, MHLOElementType* out_element_type);
+MHLOStatusCode mhlo_executable_output_type(MHLOExecutableRef executable, int32_t index, int64_t* out_shape,
+                                           int32_t* out_rank, MHLOElementType* out_element_type);
+MHLOStatusCode mhlo_executable_get_stats(MHLOExecutableRef executable, MHLOExecutionStats* out_stats);
+void mhlo_executable_reset_stats(MHLOExecutableRef executable);
+
+/* ---- buffers (reference: metalhlo.h:260-310) ---- */
+MHLOStatusCode mhlo_buffer_create(MHLOClientRef client, const void* data, size_t data_size, const int64_t* shape,
+                                  int32_t rank, MHLOElementType element_type, MHLOBufferRef* out_buffer);
+MHLOStatusCode mhlo_buffer_create_uninitialized(MHLOClientRef client, const int64_t* shape, int32_t rank,
+                                                MHLOElementType element_type, MHLOBufferRef* out_buffer);
+void mhlo_buffer_destroy(MHLOBufferRef buffer);
+void mhlo_buffer_shape(MHLOBufferRef buffer, int64_t* out_shape, int32_t* out_rank);
+int32_t mhlo_buffer_rank(MHLOBufferRef buffer);
+MHLOElementType mhlo_buffer_element_type(MHLOBufferRef buffer);
+size_t mhlo_buffer_byte_count(MHLOBufferRef buffer);
+MHLOStatusCode mhlo_buffer_to_host(MHLOBufferRef buffer, void* out_data, size_t data_size);
+
+/* ---- execution (reference: metalhlo.h:325-388) ----
+ * out_outputs must have room for mhlo_executable_output_count handles; each is a new buffer owned by the caller.
+ * The *_with_timing variant reports seconds: encode = host time spent enqueueing, gpu = device time between CUDA
+ * events around the program, total = wall clock of the call. */
+MHLOStatusCode mhlo_execute(MHLOExecutableRef executable, const MHLOBufferRef* inputs, int32_t num_inputs,
+                            MHLOBufferRef* out_outputs, int32_t* out_num_outputs);
+MHLOStatusCode mhlo_execute_with_timing(MHLOExecutableRef executable, const MHLOBufferRef* inputs,
+                                        int32_t num_inputs, MHLOBufferRef* out_outputs, int32_t* out_num_outputs,
+                                        double* out_encode_time, double* out_gpu_time, double* out_total_time);
+MHLOStatusCode mhlo_execute_with_profile(MHLOExecutableRef executable, const MHLOBufferRef* inputs,
+                                         int32_t num_inputs, MHLOBufferRef* out_outputs, int32_t* out_num_outputs,
+                                         MHLOExecutionProfile* out_profile);
+
+/* ---- additions of this backend (no counterpart in the reference's header) ----
+ * Introspection for tests and benchmarks, and execution on device memory the caller already owns. */
+/* Host-only (no CUDA device needed): parse, run the pass pipeline of the given level, return the module text
+ * (free with mhlo_free_string). */
+MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimization_level, char** out_text);
+/* StableHLO text after the pass pipeline; free with mhlo_free_string. */
+char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable);
+/* Kernel launches one execution enqueues. */
+int32_t mhlo_b200_executable_launch_count(MHLOExecutableRef executable);
+/* Bytes of the statically planned arena that holds every intermediate. */
+int64_t mhlo_b200_executable_arena_bytes(MHLOExecutableRef executable);
+/* Newline-separated labels of the launch list; free with mhlo_free_string. */
+char* mhlo_b200_executable_steps(MHLOExecutableRef executable);
+/* Device address of a buffer's storage (dense row-major). */
+void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer);
+/* Enqueues the program on `stream` (a cudaStream_t) reading/writing caller-owned dense device tensors of the
+ * executable's declared types. Allocates nothing and does not synchronise. */
+MHLOStatusCode mhlo_b200_execute_on_device(MHLOExecutableRef executable, const void* const* input_ptrs,
+                                           void* const* output_ptrs, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* METALHLO_H */

@@ -135,6 +135,178 @@ int mhlo_cuda_rms_norm(int dtype, const void* x_dev, const void* gamma_dev, void
 int mhlo_cuda_softmax(int dtype, const void* x_dev, void* y_dev, int64_t outer, int64_t axis_len,
                       int64_t inner, const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
 
+
+/* ---- generic tensor kernels (strided views) --------------------------------------------------------- */
+
+#define MHLO_CUDA_MAX_RANK 8
+#define MHLO_CUDA_EW_MAX_INPUTS 8
+#define MHLO_CUDA_EW_MAX_INSTS 32
+
+/*
+ * A strided view of device memory: element (i0..i{rank-1}) lives at base + sum(i_d * stride[d]) elements.
+ * stride 0 broadcasts a dimension, a negative stride reverses it. This is what a reshape / transpose /
+ * broadcast_in_dim / slice / reverse result is until a kernel needs it contiguous - the counterpart of
+ * StridedTensorView (Sources/MetalHLOCore/Runtime/StridedTensorView.swift) and of the zero-copy reshape
+ * views in CodeGenerator.swift:183-245.
+ */
+typedef struct {
+    const void* base;
+    int32_t dtype;
+    int32_t rank;
+    int64_t shape[MHLO_CUDA_MAX_RANK];
+    int64_t stride[MHLO_CUDA_MAX_RANK];
+} mhlo_cuda_view;
+
+/* Opcodes of the elementwise program (one StableHLO elementwise op each, plus the fused activations). */
+enum {
+    MHLO_EW_COPY = 0,  /* r = a (also convert: the store rounds to the output dtype) */
+    MHLO_EW_IMM,       /* r = imm */
+    MHLO_EW_IOTA,      /* r = index along output dimension (int)imm */
+    MHLO_EW_ADD, MHLO_EW_SUB, MHLO_EW_MUL, MHLO_EW_DIV, MHLO_EW_REM, MHLO_EW_MAX, MHLO_EW_MIN, MHLO_EW_POW,
+    MHLO_EW_ATAN2, MHLO_EW_AND, MHLO_EW_OR, MHLO_EW_XOR, MHLO_EW_SHL, MHLO_EW_SHR_A, MHLO_EW_SHR_L,
+    MHLO_EW_NEG, MHLO_EW_ABS, MHLO_EW_EXP, MHLO_EW_EXPM1, MHLO_EW_LOG, MHLO_EW_LOG1P, MHLO_EW_SQRT,
+    MHLO_EW_RSQRT, MHLO_EW_CBRT, MHLO_EW_TANH, MHLO_EW_LOGISTIC, MHLO_EW_SIN, MHLO_EW_COS, MHLO_EW_TAN,
+    MHLO_EW_FLOOR, MHLO_EW_CEIL, MHLO_EW_ROUND_AFZ, MHLO_EW_ROUND_EVEN, MHLO_EW_SIGN, MHLO_EW_NOT,
+    MHLO_EW_IS_FINITE, MHLO_EW_POPCNT, MHLO_EW_CLZ,
+    MHLO_EW_CMP_EQ, MHLO_EW_CMP_NE, MHLO_EW_CMP_LT, MHLO_EW_CMP_LE, MHLO_EW_CMP_GT, MHLO_EW_CMP_GE,
+    MHLO_EW_SELECT,    /* r = a ? b : c */
+    MHLO_EW_CLAMP,     /* r = min(max(b, a), c) with a = lower bound, c = upper bound */
+    MHLO_EW_GELU_TANH, MHLO_EW_GELU_ERF, MHLO_EW_SILU, MHLO_EW_RELU,
+    MHLO_EW_ROUND_TO,  /* r = a rounded to the float dtype (int)imm and widened again: keeps the unfused rounding
+                          points of a fused chain */
+    MHLO_EW_OP_COUNT
+};
+
+/* One instruction: register a/b/c are indices into [inputs..., results of earlier instructions...]. */
+typedef struct {
+    int32_t op;
+    int32_t a, b, c;
+    double imm;
+} mhlo_cuda_ew_inst;
+
+/*
+ * Runs `prog` once per output element. Registers 0..n_inputs-1 hold the element of each input view (all views
+ * have the output's rank and shape; use stride 0 to broadcast); instruction k writes register n_inputs+k; the
+ * last instruction's result is stored to out (contiguous, row-major) rounded/wrapped to out_dtype.
+ * Arithmetic runs in fp64 when any operand or the output is f64, else in fp32 when any is a float type, else
+ * in 64-bit integers (ui64 operands select unsigned division/shift/compare). Replaces the generated unary /
+ * binary / compare / select / clamp / convert / iota / broadcast / transpose / slice / reverse kernels
+ * (Sources/MetalHLOCore/Compiler/CodeGenerator.swift:851-1122,1558-2048,2840-3151) and kernel_elementwise_chain,
+ * kernel_gelu, kernel_silu (:4853-4981).
+ */
+int mhlo_cuda_elementwise(const mhlo_cuda_view* inputs, int32_t n_inputs, const mhlo_cuda_ew_inst* prog,
+                          int32_t n_insts, void* out_dev, int32_t out_dtype, const int64_t* out_shape,
+                          int32_t out_rank, mhlo_cuda_stream_t stream);
+
+/*
+ * Same as mhlo_cuda_elementwise, but the result is written through a strided destination view (`out`, whose
+ * dtype/rank/shape define the iteration space). With a one-instruction COPY program this is the strided copy
+ * that materialises transposes, concatenate operands and pad interiors.
+ */
+int mhlo_cuda_elementwise_to_view(const mhlo_cuda_view* inputs, int32_t n_inputs, const mhlo_cuda_ew_inst* prog,
+                                  int32_t n_insts, const mhlo_cuda_view* out, mhlo_cuda_stream_t stream);
+
+enum {
+    MHLO_REDUCE_SUM = 0, MHLO_REDUCE_MAX, MHLO_REDUCE_MIN, MHLO_REDUCE_PROD, MHLO_REDUCE_AND, MHLO_REDUCE_OR,
+    MHLO_REDUCE_XOR, MHLO_REDUCE_ARGMAX, MHLO_REDUCE_ARGMIN
+};
+
+/*
+ * Reduces the trailing (rank - n_kept) dimensions of `in` (the caller permutes the view so the kept dimensions
+ * come first). out_dev is contiguous over the kept dimensions in the input dtype. init_dev (device scalar of the
+ * input dtype, may be NULL) is folded in as one more element. Float types accumulate in fp32 (f64 in fp64),
+ * integers in int64. ARGMAX/ARGMIN additionally need index_out_dev (dtype index_dtype, I32 or I64): the
+ * flattened position of the first extremum along the reduced dimensions; NaN counts as the extremum.
+ * Replaces kernel_reduce (CodeGenerator.swift:4071-4496) and MPSGraphCompiler.compileReduce
+ * (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift:1070-1144).
+ */
+int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const void* init_dev, void* out_dev,
+                     void* index_out_dev, int32_t index_dtype, mhlo_cuda_stream_t stream);
+
+/* Dimension numbers of stablehlo.gather; counts say how many entries of each array are used. */
+typedef struct {
+    int32_t n_offset_dims, n_collapsed, n_operand_batching, n_start_index_map;
+    int32_t offset_dims[MHLO_CUDA_MAX_RANK];
+    int32_t collapsed_slice_dims[MHLO_CUDA_MAX_RANK];
+    int32_t operand_batching_dims[MHLO_CUDA_MAX_RANK];
+    int32_t start_indices_batching_dims[MHLO_CUDA_MAX_RANK];
+    int32_t start_index_map[MHLO_CUDA_MAX_RANK];
+    int32_t index_vector_dim;
+    int64_t slice_sizes[MHLO_CUDA_MAX_RANK];
+} mhlo_cuda_gather_dims;
+
+/*
+ * stablehlo.gather with the full dimension-number semantics; start indices are clamped so that every slice
+ * stays inside the operand (CodeGenerator.swift:1133-1292, clamp at :1252-1254). operand and indices are
+ * contiguous; elem_size is the operand's bytes per element (values are moved, never interpreted).
+ */
+int mhlo_cuda_gather(const void* operand_dev, int32_t elem_size, const int64_t* operand_shape, int32_t operand_rank,
+                     const void* indices_dev, int32_t index_dtype, const int64_t* indices_shape,
+                     int32_t indices_rank, const mhlo_cuda_gather_dims* dims, void* out_dev,
+                     const int64_t* out_shape, int32_t out_rank, mhlo_cuda_stream_t stream);
+
+/*
+ * dynamic_slice / dynamic_update_slice: start indices are read on the device from n_idx scalar tensors
+ * (index_dtype I32 or I64) and clamped to keep the window inside `operand`
+ * (CodeGenerator.swift:1640-1790). For the update form, out must already hold the operand.
+ */
+int mhlo_cuda_dynamic_slice(const void* operand_dev, int32_t elem_size, const int64_t* operand_shape, int32_t rank,
+                            const void* const* index_devs, int32_t index_dtype, const int64_t* slice_sizes,
+                            void* out_dev, mhlo_cuda_stream_t stream);
+int mhlo_cuda_dynamic_update_slice(void* operand_inout_dev, int32_t elem_size, const int64_t* operand_shape,
+                                   int32_t rank, const void* update_dev, const int64_t* update_shape,
+                                   const void* const* index_devs, int32_t index_dtype, mhlo_cuda_stream_t stream);
+
+/*
+ * C[b0,b1,m,n] = sum_k A(b0,b1,m,k) * B(b0,b1,k,n) for arbitrary element strides (a_strides / b_strides =
+ * {batch0, batch1, row, col} strides in elements; C is contiguous). Any dtype: floats accumulate in fp32
+ * (f64 in fp64), integers in int64. This is the general-layout path of dot_general - strict fp32 as the
+ * reference defaults to (Sources/MetalHLOCore/Compiler/TF32Transform.swift:20 is opt-in) - and the fallback
+ * for shapes the tensor-core kernels do not take. Replaces kernel_matmul basic/tiled and kernel_gemv
+ * (CodeGenerator.swift:3344-3454,3891-4068).
+ */
+int mhlo_cuda_dot_strided(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                          const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0,
+                          int64_t batch1, int64_t m, int64_t n, int64_t k, mhlo_cuda_stream_t stream);
+
+/* ---- contractions ------------------------------------------------------------------------------------ */
+
+enum {
+    MHLO_EPILOGUE_NONE = 0, MHLO_EPILOGUE_RELU, MHLO_EPILOGUE_GELU_TANH, MHLO_EPILOGUE_GELU_ERF,
+    MHLO_EPILOGUE_SILU, MHLO_EPILOGUE_TANH, MHLO_EPILOGUE_SIGMOID
+};
+
+/*
+ * dot_general in canonical form with a fused epilogue:
+ *   C[b0,b1,m,n] = act( sum_k A(b0,b1,m,k) * B(b0,b1,k,n) + bias[n] ),  C dense row-major, fp32 accumulation.
+ * a_strides / b_strides = {batch0, batch1, row, col} element strides, so transposed and batch-interleaved
+ * operands need no copy. bias_dev ([n], dtype = out_dtype) may be NULL. BF16/F16 operands whose rows or columns
+ * are contiguous and 16-byte aligned run on the tcgen05 tensor-core kernel (TMA-fed, TMEM accumulators);
+ * everything else takes the general-layout kernel behind mhlo_cuda_dot_strided. Replaces kernel_matmul (MPP and
+ * simdgroup variants, Sources/MetalHLOCore/Compiler/CodeGenerator.swift:3463-3886), kernel_matmul_bias_act
+ * (:4797-4850) and the semantics of FusedMatMulBiasActivationHandler
+ * (Sources/MetalHLOCore/Compiler/CustomCallHandlers.swift:927-1073).
+ */
+int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                   const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
+                   int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
+                   mhlo_cuda_stream_t stream);
+
+/*
+ * Fused scaled dot-product attention, O = softmax(scale * Q K^T [+ mask] [causal]) V with fp32 softmax and
+ * accumulation. Q [B,H,Sq,D], K/V [B,H,Sk,D], O [B,H,Sq,D] logically; *_strides = {batch, head, sequence}
+ * element strides (the head dimension D is contiguous), so [B,S,H,D] tensors are read and written in place.
+ * causal: key j is visible to query i iff j <= i + (Sk - Sq). mask_dev: optional additive [Sq,Sk] mask of the
+ * operand dtype shared by every batch and head. Replaces kernel_attention (CodeGenerator.swift:4527-4595) and
+ * flash_attention_tiled_kernel (Sources/MetalHLOCore/Metal/Kernels/FlashAttentionKernel.swift:469-670) with the
+ * semantics of FusedScaledDotProductAttentionHandler (CustomCallHandlers.swift:179-278).
+ */
+int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_strides[3], const void* k_dev,
+                        const int64_t k_strides[3], const void* v_dev, const int64_t v_strides[3],
+                        const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,
+                        int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
+                        int32_t causal, mhlo_cuda_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,157 @@
+// Entry points of the contractions: mhlo_cuda_gemm and mhlo_cuda_attention choose between the tcgen05
+// tensor-core kernels and the general-layout kernels, and hold the general-layout attention kernel.
+#include "common.cuh"
+#include "contraction.cuh"
+
+namespace mhlo {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p) { return VecTraits<T>::to_float(*p); }
+
+// General-layout attention: one warp per query row. Keys are taken 32 at a time - lane j scores key j against
+// the query held in shared memory, the warp does the online-softmax update with shuffles, then every lane
+// accumulates its slice of the head dimension over the 32 weighted value rows. Any dtype, D <= 256, any strides.
+template <typename T>
+__global__ void __launch_bounds__(128) attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                             const T* __restrict__ v, const T* __restrict__ mask,
+                                                             T* __restrict__ o, AttnShape s) {
+    constexpr int kMaxPerLane = 8;
+    __shared__ float qs[4][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+    const int64_t total = s.batch * s.heads * s.seq_q;
+    if (row >= total) return;
+    const int64_t i = row % s.seq_q, h = (row / s.seq_q) % s.heads, b = row / (s.seq_q * s.heads);
+    const T* qp = q + b * s.qs[0] + h * s.qs[1] + i * s.qs[2];
+    const T* kp = k + b * s.ks[0] + h * s.ks[1];
+    const T* vp = v + b * s.vs[0] + h * s.vs[1];
+    T* op = o + b * s.os[0] + h * s.os[1] + i * s.os[2];
+    const int D = static_cast<int>(s.head_dim);
+    for (int d = lane; d < D; d += 32) qs[warp][d] = ldf(qp + d) * s.scale;
+    __syncwarp();
+    float acc[kMaxPerLane];
+#pragma unroll
+    for (int t = 0; t < kMaxPerLane; ++t) acc[t] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    int64_t lim = s.causal ? i + (s.seq_k - s.seq_q) + 1 : s.seq_k;
+    if (lim > s.seq_k) lim = s.seq_k;
+    for (int64_t j0 = 0; j0 < lim; j0 += 32) {
+        const int64_t j = j0 + lane;
+        float sc = -INFINITY;
+        if (j < lim) {
+            const T* kr = kp + j * s.ks[2];
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot += qs[warp][d] * ldf(kr + d);
+            sc = dot;
+            if (mask != nullptr) sc += ldf(mask + i * s.seq_k + j);
+        }
+        float cm = sc;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, x));
+        const float mn = fmaxf(m, cm);
+        const float corr = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        const float p = (sc == -INFINITY || mn == -INFINITY) ? 0.f : __expf(sc - mn);
+        float ps = p;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
+        l = l * corr + ps;
+        m = mn;
+#pragma unroll
+        for (int t = 0; t < kMaxPerLane; ++t) acc[t] *= corr;
+        const int cnt = static_cast<int>(lim - j0 < 32 ? lim - j0 : 32);
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const T* vr = vp + (j0 + jj) * s.vs[2];
+#pragma unroll
+            for (int t = 0; t < kMaxPerLane; ++t) {
+                const int d = lane + 32 * t;
+                if (d < D) acc[t] += pj * ldf(vr + d);
+            }
+        }
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int t = 0; t < kMaxPerLane; ++t) {
+        const int d = lane + 32 * t;
+        if (d < D) op[d] = VecTraits<T>::from_float(acc[t] * inv);
+    }
+}
+
+template <typename T>
+int launch_attention_rows(const void* q, const void* k, const void* v, const void* mask, void* o, const AttnShape& s,
+                          cudaStream_t stream) {
+    const int64_t rows = s.batch * s.heads * s.seq_q;
+    const int64_t grid = (rows + 3) / 4;
+    if (grid > 0x7fffffffLL) return fail(MHLO_CUDA_UNSUPPORTED, "attention: too many query rows");
+    attention_rows_kernel<T><<<static_cast<int>(grid), 128, 0, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(mask),
+        static_cast<T*>(o), s);
+    MHLO_CUDA_CHECK_LAUNCH("attention");
+    return MHLO_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace mhlo
+
+using namespace mhlo;
+
+extern "C" {
+
+int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                   const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
+                   int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
+                   mhlo_cuda_stream_t stream) {
+    if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epilogue);
+    if (!a_strides || !b_strides) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm: null strides");
+    GemmProblem p;
+    p.a = a_dev; p.b = b_dev; p.c = c_dev; p.bias = bias_dev;
+    for (int i = 0; i < 4; ++i) { p.as[i] = a_strides[i]; p.bs[i] = b_strides[i]; }
+    p.batch0 = batch0; p.batch1 = batch1; p.m = m; p.n = n; p.k = k;
+    p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
+    if (gemm_tc_supported(p)) return gemm_tc_launch(p, static_cast<cudaStream_t>(stream));
+    int st = mhlo_cuda_dot_strided(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_dev, batch0, batch1, m, n, k, stream);
+    if (st != MHLO_CUDA_OK || (bias_dev == nullptr && epilogue == MHLO_EPILOGUE_NONE)) return st;
+    // bias / activation as an in-place elementwise pass over C
+    mhlo_cuda_view in[2];
+    memset(in, 0, sizeof in);
+    const int64_t rows = batch0 * batch1 * m;
+    in[0].base = c_dev; in[0].dtype = out_dtype; in[0].rank = 2;
+    in[0].shape[0] = rows; in[0].shape[1] = n; in[0].stride[0] = n; in[0].stride[1] = 1;
+    in[1] = in[0];
+    in[1].base = bias_dev; in[1].stride[0] = 0;
+    mhlo_cuda_ew_inst prog[2];
+    int ni = 0, n_in = 1, cur = 0;
+    if (bias_dev != nullptr) { n_in = 2; prog[ni++] = {MHLO_EW_ADD, 0, 1, 0, 0.0}; cur = n_in; }
+    static const int act_op[] = {MHLO_EW_COPY, MHLO_EW_RELU, MHLO_EW_GELU_TANH, MHLO_EW_GELU_ERF, MHLO_EW_SILU, MHLO_EW_TANH, MHLO_EW_LOGISTIC};
+    if (epilogue != MHLO_EPILOGUE_NONE) { prog[ni] = {act_op[epilogue], cur, cur, cur, 0.0}; ++ni; }
+    const int64_t shape[2] = {rows, n};
+    return mhlo_cuda_elementwise(in, n_in, prog, ni, c_dev, out_dtype, shape, 2, stream);
+}
+
+int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_strides[3], const void* k_dev,
+                        const int64_t k_strides[3], const void* v_dev, const int64_t v_strides[3],
+                        const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,
+                        int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
+                        int32_t causal, mhlo_cuda_stream_t stream) {
+    if (batch < 0 || heads < 0 || seq_q < 0 || seq_k < 0 || head_dim < 0)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: negative extent");
+    if (!q_strides || !k_strides || !v_strides || !o_strides) return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: null strides");
+    if (batch * heads * seq_q * head_dim == 0) return MHLO_CUDA_OK;
+    if (!q_dev || !o_dev || (seq_k > 0 && (!k_dev || !v_dev))) return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: null pointer");
+    AttnShape s;
+    for (int i = 0; i < 3; ++i) { s.qs[i] = q_strides[i]; s.ks[i] = k_strides[i]; s.vs[i] = v_strides[i]; s.os[i] = o_strides[i]; }
+    s.batch = batch; s.heads = heads; s.seq_q = seq_q; s.seq_k = seq_k; s.head_dim = head_dim; s.scale = scale; s.causal = causal;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (attention_tc_supported(dtype, s, mask_dev)) return attention_tc_launch(dtype, q_dev, k_dev, v_dev, o_dev, s, st);
+    if (head_dim > 256) return fail(MHLO_CUDA_UNSUPPORTED, "attention: head_dim %lld above 256", (long long)head_dim);
+    switch (dtype) {
+        case MHLO_DT_F32: return launch_attention_rows<float>(q_dev, k_dev, v_dev, mask_dev, o_dev, s, st);
+        case MHLO_DT_F16: return launch_attention_rows<__half>(q_dev, k_dev, v_dev, mask_dev, o_dev, s, st);
+        case MHLO_DT_BF16: return launch_attention_rows<__nv_bfloat16>(q_dev, k_dev, v_dev, mask_dev, o_dev, s, st);
+        default: return fail(MHLO_CUDA_UNSUPPORTED, "attention: dtype %d", dtype);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,502 @@
+// The mhlo_* C API (include/metalhlo.h) over the C++ compiler core and libmhlo_cuda.so. Behaviour follows
+// Sources/CMetalHLO/CInterface.swift:202-1010: opaque retained handles, MHLOStatusCode returns, a process-global
+// last-error string that is NULL when clear, synchronous execution with new output buffers per call, and
+// per-executable execution statistics.
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../../include/metalhlo.h"
+#include "../../../include/mhlo_cuda.h"
+#include "compiler.h"
+
+using namespace mhlo;
+
+namespace {
+
+std::mutex g_error_mu;
+std::string g_error;
+bool g_has_error = false;
+
+int set_error(int code, const std::string& msg) {
+    std::lock_guard<std::mutex> lock(g_error_mu);
+    g_error = msg;
+    g_has_error = true;
+    return code;
+}
+
+struct Client {
+    int device = 0;
+    void* stream = nullptr;
+    std::mutex mu;
+    // in-process executable cache keyed by (text, level): MetalHLOCompiler.swift:730-782 keeps the same
+    std::map<std::string, std::shared_ptr<Executable>> cache;
+    int64_t cache_hits = 0, cache_misses = 0;
+};
+
+struct ExecutableHandle {
+    Client* client;
+    std::shared_ptr<Executable> exe;
+    ExecutionStats stats;
+};
+
+struct Buffer {
+    Client* client;
+    void* dev = nullptr;
+    TensorType type;
+    size_t bytes = 0;
+};
+
+// I1 tensors occupy one byte per element on the device (mhlo_element_type_size reports 0 for I1, as the
+// reference does, so callers size bool buffers themselves).
+size_t buffer_bytes(const TensorType& t) { return static_cast<size_t>(t.bytes()); }
+
+MHLOStatusCode make_buffer(Client* c, const TensorType& t, Buffer** out) {
+    std::unique_ptr<Buffer> b(new Buffer());
+    b->client = c;
+    b->type = t;
+    b->bytes = buffer_bytes(t);
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    if (b->bytes > 0 && mhlo_cuda_alloc(b->bytes, &b->dev) != 0)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_BUFFER_FAILED, mhlo_cuda_last_error()));
+    *out = b.release();
+    return MHLO_OK;
+}
+
+bool valid_dtype(int t) { return t >= 0 && t <= 12; }
+
+MHLOStatusCode run(ExecutableHandle* h, const MHLOBufferRef* inputs, int32_t num_inputs, MHLOBufferRef* out_outputs,
+                   int32_t* out_num_outputs, double* encode_s, double* gpu_s, double* total_s) {
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    if (!out_outputs) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_outputs is null"));
+    if (!out_num_outputs) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_num_outputs is null"));
+    Executable& exe = *h->exe;
+    Client* c = h->client;
+    if (num_inputs != exe.num_inputs())
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INPUT_MISMATCH, "Input count mismatch: expected " +
+                                                     std::to_string(exe.num_inputs()) + ", got " + std::to_string(num_inputs)));
+    std::vector<const void*> in_ptrs(static_cast<size_t>(num_inputs));
+    for (int i = 0; i < num_inputs; ++i) {
+        if (!inputs || !inputs[i]) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "Input " + std::to_string(i) + " is null"));
+        const Buffer* b = static_cast<const Buffer*>(inputs[i]);
+        if (b->type != exe.input_type(i))
+            return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INPUT_MISMATCH, "Input " + std::to_string(i) + " is " + b->type.str() +
+                                                         ", executable expects " + exe.input_type(i).str()));
+        in_ptrs[static_cast<size_t>(i)] = b->dev;
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_error_mu);
+        g_has_error = false;
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    std::vector<Buffer*> outs;
+    std::vector<void*> out_ptrs;
+    auto cleanup = [&]() { for (Buffer* b : outs) { mhlo_cuda_free(b->dev); delete b; } };
+    for (int i = 0; i < exe.num_outputs(); ++i) {
+        Buffer* b = nullptr;
+        MHLOStatusCode st = make_buffer(c, exe.output_type(i), &b);
+        if (st != MHLO_OK) { cleanup(); return st; }
+        outs.push_back(b);
+        out_ptrs.push_back(b->dev);
+    }
+    void *ev0 = nullptr, *ev1 = nullptr;
+    const bool timed = gpu_s != nullptr;
+    if (timed) { mhlo_cuda_event_create(&ev0); mhlo_cuda_event_create(&ev1); mhlo_cuda_event_record(ev0, c->stream); }
+    int st;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);  // one program at a time per client stream and arena
+        st = exe.execute(in_ptrs.data(), out_ptrs.data(), c->stream);
+    }
+    const auto t1 = std::chrono::steady_clock::now();
+    if (timed) mhlo_cuda_event_record(ev1, c->stream);
+    if (st == 0 && mhlo_cuda_stream_sync(c->stream) != 0) { st = MHLO_ERROR_EXECUTION_FAILED; set_error(st, mhlo_cuda_last_error()); }
+    else if (st != 0) set_error(st, exe.last_error());
+    if (timed) {
+        float ms = 0;
+        if (st == 0) mhlo_cuda_event_elapsed_ms(ev0, ev1, &ms);
+        *gpu_s = ms * 1e-3;
+        mhlo_cuda_event_destroy(ev0);
+        mhlo_cuda_event_destroy(ev1);
+    }
+    if (st != 0) { cleanup(); return static_cast<MHLOStatusCode>(st); }
+    const auto t2 = std::chrono::steady_clock::now();
+    const double total = std::chrono::duration<double>(t2 - t0).count();
+    if (encode_s) *encode_s = std::chrono::duration<double>(t1 - t0).count();
+    if (total_s) *total_s = total;
+    h->stats.count += 1;
+    h->stats.last_ms = total * 1e3;
+    h->stats.total_ms += total * 1e3;
+    *out_num_outputs = static_cast<int32_t>(outs.size());
+    for (size_t i = 0; i < outs.size(); ++i) out_outputs[i] = outs[i];
+    return MHLO_OK;
+}
+
+MHLOStatusCode compile_impl(Client* c, const std::string& text, const MHLOCompileConfig* config, MHLOExecutableRef* out) {
+    if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "client is null"));
+    if (!out) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_executable is null"));
+    *out = nullptr;
+    CompileOptions opt;
+    if (config) {
+        if (config->optimization_level < 0 || config->optimization_level > 3)
+            return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "optimization_level out of range"));
+        opt.opt_level = config->optimization_level;
+        opt.enable_caching = config->enable_caching;
+        opt.enable_debug_info = config->enable_debug_info;
+    }
+    if (const char* env = std::getenv("METALHLO_OPT_LEVEL"))
+        if (!config && env[0] >= '0' && env[0] <= '3') opt.opt_level = env[0] - '0';
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    const std::string key = std::to_string(opt.opt_level) + "|" + text;
+    std::shared_ptr<Executable> exe;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        if (opt.enable_caching) {
+            auto it = c->cache.find(key);
+            if (it != c->cache.end()) { exe = it->second; ++c->cache_hits; }
+        }
+    }
+    if (!exe) {
+        try {
+            exe = std::shared_ptr<Executable>(Executable::compile(text, opt).release());
+        } catch (const CompileError& e) {
+            return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));
+        } catch (const std::exception& e) {
+            return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
+        }
+        std::lock_guard<std::mutex> lock(c->mu);
+        ++c->cache_misses;
+        if (opt.enable_caching) c->cache[key] = exe;
+    }
+    ExecutableHandle* h = new ExecutableHandle();
+    h->client = c;
+    h->exe = exe;
+    *out = h;
+    return MHLO_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mhlo_version(void) { return "0.2.0"; }
+
+const char* mhlo_get_last_error(void) {
+    std::lock_guard<std::mutex> lock(g_error_mu);
+    return g_has_error ? g_error.c_str() : nullptr;
+}
+
+void mhlo_clear_error(void) {
+    std::lock_guard<std::mutex> lock(g_error_mu);
+    g_has_error = false;
+    g_error.clear();
+}
+
+size_t mhlo_element_type_size(MHLOElementType type) {
+    if (type == MHLO_I1) return 0;
+    return valid_dtype(type) ? dtype_size(static_cast<DType>(type)) : 0;
+}
+
+void mhlo_free_string(const char* str) { std::free(const_cast<char*>(str)); }
+
+MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) {
+    if (!out_client) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_client is null"));
+    *out_client = nullptr;
+    int n = 0;
+    if (mhlo_cuda_device_count(&n) != 0 || n == 0)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, std::string("No CUDA device available: ") + mhlo_cuda_last_error()));
+    std::unique_ptr<Client> c(new Client());
+    // one process drives one GPU: LOCAL_RANK picks it when several ranks share a box
+    if (const char* lr = std::getenv("METALHLO_DEVICE")) c->device = std::atoi(lr);
+    else if (const char* lr2 = std::getenv("LOCAL_RANK")) c->device = std::atoi(lr2) % n;
+    if (c->device < 0 || c->device >= n) c->device = 0;
+    if (mhlo_cuda_device_set(c->device) != 0 || mhlo_cuda_stream_create(&c->stream) != 0)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    *out_client = c.release();
+    return MHLO_OK;
+}
+
+void mhlo_client_destroy(MHLOClientRef client) {
+    Client* c = static_cast<Client*>(client);
+    if (!c) return;
+    mhlo_cuda_device_set(c->device);
+    c->cache.clear();
+    if (c->stream) mhlo_cuda_stream_destroy(c->stream);
+    delete c;
+}
+
+char* mhlo_client_device_name(MHLOClientRef client) {
+    Client* c = static_cast<Client*>(client);
+    if (!c) return nullptr;
+    char name[256];
+    if (mhlo_cuda_device_name(c->device, name, sizeof name) != 0) return nullptr;
+    return strdup(name);
+}
+
+void mhlo_compile_config_init(MHLOCompileConfig* out_config) {
+    if (!out_config) return;
+    out_config->optimization_level = MHLO_OPT_O2;
+    out_config->enable_caching = true;
+    out_config->enable_debug_info = false;
+    out_config->device_policy = MHLO_DEVICE_GPU_ONLY;
+}
+
+bool mhlo_ane_available(void) { return false; }
+
+MHLOStatusCode mhlo_compile(MHLOClientRef client, const char* mlir_text, MHLOExecutableRef* out_executable) {
+    if (!mlir_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "mlir_text is null"));
+    return compile_impl(static_cast<Client*>(client), mlir_text, nullptr, out_executable);
+}
+
+MHLOStatusCode mhlo_compile_n(MHLOClientRef client, const char* mlir_text, size_t mlir_length, MHLOExecutableRef* out_executable) {
+    if (!mlir_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "mlir_text is null"));
+    return compile_impl(static_cast<Client*>(client), std::string(mlir_text, mlir_length), nullptr, out_executable);
+}
+
+MHLOStatusCode mhlo_compile_with_config(MHLOClientRef client, const char* mlir_text, const MHLOCompileConfig* config,
+                                        MHLOExecutableRef* out_executable) {
+    if (!mlir_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "mlir_text is null"));
+    return compile_impl(static_cast<Client*>(client), mlir_text, config, out_executable);
+}
+
+void mhlo_executable_destroy(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return;
+    mhlo_cuda_device_set(h->client->device);
+    delete h;
+}
+
+int32_t mhlo_executable_input_count(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? h->exe->num_inputs() : 0;
+}
+
+int32_t mhlo_executable_output_count(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? h->exe->num_outputs() : 0;
+}
+
+static MHLOStatusCode describe(const TensorType& t, int64_t* out_shape, int32_t* out_rank, MHLOElementType* out_type) {
+    if (out_shape) for (int d = 0; d < t.rank(); ++d) out_shape[d] = t.shape[d];
+    if (out_rank) *out_rank = t.rank();
+    if (out_type) *out_type = static_cast<MHLOElementType>(t.dtype);
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_executable_input_type(MHLOExecutableRef executable, int32_t index, int64_t* out_shape, int32_t* out_rank,
+                                          MHLOElementType* out_element_type) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    if (index < 0 || index >= h->exe->num_inputs()) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "Input index out of range"));
+    return describe(h->exe->input_type(index), out_shape, out_rank, out_element_type);
+}
+
+MHLOStatusCode mhlo_executable_output_type(MHLOExecutableRef executable, int32_t index, int64_t* out_shape, int32_t* out_rank,
+                                           MHLOElementType* out_element_type) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    if (index < 0 || index >= h->exe->num_outputs()) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "Output index out of range"));
+    return describe(h->exe->output_type(index), out_shape, out_rank, out_element_type);
+}
+
+MHLOStatusCode mhlo_executable_get_stats(MHLOExecutableRef executable, MHLOExecutionStats* out_stats) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    if (!out_stats) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_stats is null"));
+    out_stats->execution_count = h->stats.count;
+    out_stats->total_execution_time_ms = h->stats.total_ms;
+    out_stats->last_execution_time_ms = h->stats.last_ms;
+    out_stats->average_execution_time_ms = h->stats.count ? h->stats.total_ms / static_cast<double>(h->stats.count) : 0.0;
+    return MHLO_OK;
+}
+
+void mhlo_executable_reset_stats(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (h) h->stats = ExecutionStats();
+}
+
+MHLOStatusCode mhlo_buffer_create(MHLOClientRef client, const void* data, size_t data_size, const int64_t* shape, int32_t rank,
+                                  MHLOElementType element_type, MHLOBufferRef* out_buffer) {
+    Client* c = static_cast<Client*>(client);
+    if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "client is null"));
+    if (!out_buffer) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_buffer is null"));
+    *out_buffer = nullptr;
+    if (rank < 0 || rank > MHLO_CUDA_MAX_RANK || (rank > 0 && !shape)) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "bad shape or rank"));
+    if (!valid_dtype(element_type)) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "unknown element type"));
+    TensorType t;
+    t.dtype = static_cast<DType>(element_type);
+    for (int d = 0; d < rank; ++d) {
+        if (shape[d] < 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "negative dimension"));
+        t.shape.push_back(shape[d]);
+    }
+    const size_t need = buffer_bytes(t);
+    if (data_size != need)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_BUFFER_FAILED, "Data size mismatch: expected " + std::to_string(need) +
+                                                     " bytes for " + t.str() + ", got " + std::to_string(data_size)));
+    if (need > 0 && !data) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "data is null"));
+    Buffer* b = nullptr;
+    MHLOStatusCode st = make_buffer(c, t, &b);
+    if (st != MHLO_OK) return st;
+    if (need > 0 && (mhlo_cuda_upload(b->dev, data, need, c->stream) != 0 || mhlo_cuda_stream_sync(c->stream) != 0)) {
+        set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error());
+        mhlo_cuda_free(b->dev);
+        delete b;
+        return MHLO_ERROR_TRANSFER_FAILED;
+    }
+    *out_buffer = b;
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_buffer_create_uninitialized(MHLOClientRef client, const int64_t* shape, int32_t rank, MHLOElementType element_type,
+                                                MHLOBufferRef* out_buffer) {
+    Client* c = static_cast<Client*>(client);
+    if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "client is null"));
+    if (!out_buffer) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_buffer is null"));
+    *out_buffer = nullptr;
+    if (rank < 0 || rank > MHLO_CUDA_MAX_RANK || (rank > 0 && !shape) || !valid_dtype(element_type))
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "bad shape, rank or element type"));
+    TensorType t;
+    t.dtype = static_cast<DType>(element_type);
+    for (int d = 0; d < rank; ++d) {
+        if (shape[d] < 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "negative dimension"));
+        t.shape.push_back(shape[d]);
+    }
+    Buffer* b = nullptr;
+    MHLOStatusCode st = make_buffer(c, t, &b);
+    if (st != MHLO_OK) return st;
+    if (b->bytes) mhlo_cuda_memset(b->dev, 0, b->bytes, c->stream);  // the reference's fresh MTLBuffers read as zero
+    *out_buffer = b;
+    return MHLO_OK;
+}
+
+void mhlo_buffer_destroy(MHLOBufferRef buffer) {
+    Buffer* b = static_cast<Buffer*>(buffer);
+    if (!b) return;
+    mhlo_cuda_device_set(b->client->device);
+    mhlo_cuda_stream_sync(b->client->stream);
+    mhlo_cuda_free(b->dev);
+    delete b;
+}
+
+void mhlo_buffer_shape(MHLOBufferRef buffer, int64_t* out_shape, int32_t* out_rank) {
+    Buffer* b = static_cast<Buffer*>(buffer);
+    if (!b) return;
+    if (out_shape) for (int d = 0; d < b->type.rank(); ++d) out_shape[d] = b->type.shape[d];
+    if (out_rank) *out_rank = b->type.rank();
+}
+
+int32_t mhlo_buffer_rank(MHLOBufferRef buffer) { return buffer ? static_cast<Buffer*>(buffer)->type.rank() : 0; }
+
+MHLOElementType mhlo_buffer_element_type(MHLOBufferRef buffer) {
+    return buffer ? static_cast<MHLOElementType>(static_cast<Buffer*>(buffer)->type.dtype) : MHLO_F32;
+}
+
+size_t mhlo_buffer_byte_count(MHLOBufferRef buffer) { return buffer ? static_cast<Buffer*>(buffer)->bytes : 0; }
+
+MHLOStatusCode mhlo_buffer_to_host(MHLOBufferRef buffer, void* out_data, size_t data_size) {
+    Buffer* b = static_cast<Buffer*>(buffer);
+    if (!b) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "buffer is null"));
+    if (!out_data) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_data is null"));
+    if (b->bytes > data_size)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, "Output buffer too small: need " + std::to_string(b->bytes) +
+                                                     ", got " + std::to_string(data_size)));
+    if (b->bytes == 0) return MHLO_OK;
+    if (mhlo_cuda_device_set(b->client->device) != 0 || mhlo_cuda_download(out_data, b->dev, b->bytes, b->client->stream) != 0 ||
+        mhlo_cuda_stream_sync(b->client->stream) != 0)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error()));
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_execute(MHLOExecutableRef executable, const MHLOBufferRef* inputs, int32_t num_inputs, MHLOBufferRef* out_outputs,
+                            int32_t* out_num_outputs) {
+    return run(static_cast<ExecutableHandle*>(executable), inputs, num_inputs, out_outputs, out_num_outputs, nullptr, nullptr, nullptr);
+}
+
+MHLOStatusCode mhlo_execute_with_timing(MHLOExecutableRef executable, const MHLOBufferRef* inputs, int32_t num_inputs,
+                                        MHLOBufferRef* out_outputs, int32_t* out_num_outputs, double* out_encode_time,
+                                        double* out_gpu_time, double* out_total_time) {
+    double enc = 0, gpu = 0, tot = 0;
+    MHLOStatusCode st = run(static_cast<ExecutableHandle*>(executable), inputs, num_inputs, out_outputs, out_num_outputs, &enc, &gpu, &tot);
+    if (out_encode_time) *out_encode_time = enc;
+    if (out_gpu_time) *out_gpu_time = gpu;
+    if (out_total_time) *out_total_time = tot;
+    return st;
+}
+
+MHLOStatusCode mhlo_execute_with_profile(MHLOExecutableRef executable, const MHLOBufferRef* inputs, int32_t num_inputs,
+                                         MHLOBufferRef* out_outputs, int32_t* out_num_outputs, MHLOExecutionProfile* out_profile) {
+    double enc = 0, gpu = 0, tot = 0;
+    MHLOStatusCode st = run(static_cast<ExecutableHandle*>(executable), inputs, num_inputs, out_outputs, out_num_outputs, &enc, &gpu, &tot);
+    if (out_profile) {
+        std::memset(out_profile, 0, sizeof *out_profile);
+        out_profile->partition_count = 1;
+        out_profile->gpu_partition_count = 1;
+        out_profile->gpu_time_ms = gpu * 1e3;
+        out_profile->total_time_ms = tot * 1e3;
+    }
+    return st;
+}
+
+// ---- introspection used by the tests and the benchmark (not part of the reference's header) --------------------------
+
+// Writes the optimised module (StableHLO text after the pass pipeline) into a malloc'd string; free with mhlo_free_string.
+char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? strdup(h->exe->optimized_text().c_str()) : nullptr;
+}
+
+// Host-only: parses `mlir_text`, runs the pass pipeline of `optimization_level` and returns the resulting module as
+// text (malloc'd; free with mhlo_free_string). Needs no CUDA device, so the compiler core can be tested anywhere.
+MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimization_level, char** out_text) {
+    if (!mlir_text || !out_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    *out_text = nullptr;
+    try {
+        Module m = parse_module(mlir_text);
+        Function f = m.main();
+        CompileOptions opt;
+        opt.opt_level = optimization_level;
+        run_pass_pipeline(f, opt);
+        *out_text = strdup(print_function(f).c_str());
+        return MHLO_OK;
+    } catch (const CompileError& e) {
+        return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));
+    } catch (const std::exception& e) {
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
+    }
+}
+
+// Kernel launches one execution enqueues, the arena size and a newline-separated list of step labels.
+int32_t mhlo_b200_executable_launch_count(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? h->exe->num_kernel_launches() : 0;
+}
+int64_t mhlo_b200_executable_arena_bytes(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? h->exe->arena_bytes() : 0;
+}
+char* mhlo_b200_executable_steps(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return nullptr;
+    std::string s;
+    for (const std::string& l : h->exe->step_labels()) s += l + "\n";
+    return strdup(s.c_str());
+}
+// Device pointer of a buffer, so that a caller holding device memory (torch, another library) can run kernels on
+// it or time device-resident execution.
+void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer) { return buffer ? static_cast<Buffer*>(buffer)->dev : nullptr; }
+// Runs the executable on caller-provided device pointers and stream (no allocation, no synchronisation).
+MHLOStatusCode mhlo_b200_execute_on_device(MHLOExecutableRef executable, const void* const* input_ptrs, void* const* output_ptrs,
+                                           void* stream) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    const int st = h->exe->execute(input_ptrs, output_ptrs, stream);
+    if (st != 0) set_error(st, h->exe->last_error());
+    return static_cast<MHLOStatusCode>(st);
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// Compiler-core interfaces: pass pipeline, static memory plan and the compiled executable.
+// The reference counterparts are MetalHLOCompiler (Sources/MetalHLOCore/Compiler/MetalHLOCompiler.swift:154-252),
+// PassManager (Compiler/PassManager.swift), StaticMemoryPlanner (Memory/StaticMemoryPlanner.swift) and
+// IntegratedExecutor (Runtime/IntegratedExecutor.swift).
+#pragma once
+
+#include <functional>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "ir.h"
+
+namespace mhlo {
+
+struct CompileOptions {
+    int opt_level = 2;           // 0..3, same meaning as MHLOOptimizationLevel
+    bool enable_caching = true;
+    bool enable_debug_info = false;
+    bool has_enabled_set = false;
+    std::set<std::string> enabled_passes;   // when has_enabled_set: only these run
+    std::set<std::string> disabled_passes;  // never run (METALHLO_DISABLED_PASSES)
+};
+
+struct PassRecord {
+    std::string name;
+    bool ran = false;
+    bool changed = false;
+    int ops_before = 0, ops_after = 0;
+};
+
+// Names of every registered pass in pipeline order (Compiler/PassManager.swift:121-237).
+const std::vector<std::string>& all_pass_names();
+// The pass set an optimisation level enables (Sources/MetalHLO/CompilationConfig.swift:232-263).
+std::set<std::string> passes_for_level(int opt_level);
+// Runs the pipeline once over f (single sweep, as the reference does). Returns one record per registered pass.
+std::vector<PassRecord> run_pass_pipeline(Function& f, const CompileOptions& options);
+
+// ---- memory plan -----------------------------------------------------------------------------------------------
+
+struct PlanInterval {
+    int64_t bytes = 0;
+    int first = 0, last = 0;  // inclusive step range in which the buffer is live
+    int64_t offset = -1;      // assigned by plan_memory
+};
+// Lifetime-interval offset assignment into one arena: largest buffers first, each at the lowest 256-byte
+// aligned offset that does not overlap a buffer whose lifetime intersects; total rounded up to 4096
+// (Memory/StaticMemoryPlanner.swift:175-253,486-554). Returns the arena size.
+int64_t plan_memory(std::vector<PlanInterval>* buffers);
+
+// ---- executable ------------------------------------------------------------------------------------------------
+
+struct ExecutionStats {
+    int64_t count = 0;
+    double total_ms = 0, last_ms = 0;
+};
+
+class Executable {
+  public:
+    ~Executable();
+    // Parses, optimises, lowers and plans `mlir`; uploads constants and allocates the arena on the current CUDA
+    // device. Throws CompileError.
+    static std::unique_ptr<Executable> compile(const std::string& mlir, const CompileOptions& options);
+
+    int num_inputs() const { return static_cast<int>(input_types_.size()); }
+    int num_outputs() const { return static_cast<int>(output_types_.size()); }
+    const TensorType& input_type(int i) const { return input_types_[i]; }
+    const TensorType& output_type(int i) const { return output_types_[i]; }
+
+    // Enqueues the whole program on `stream`. inputs/outputs are device pointers to dense row-major tensors of the
+    // declared types. Returns 0 or an MHLO status code (message via last_error()).
+    int execute(const void* const* inputs, void* const* outputs, void* stream);
+    const std::string& last_error() const { return error_; }
+
+    int num_steps() const { return static_cast<int>(steps_.size()); }
+    int num_kernel_launches() const { return launches_per_run_; }
+    int64_t arena_bytes() const { return arena_bytes_; }
+    int64_t constant_bytes() const { return static_cast<int64_t>(const_pool_.size()); }
+    const std::vector<PassRecord>& pass_log() const { return pass_log_; }
+    const std::string& optimized_text() const { return optimized_text_; }
+    std::vector<std::string> step_labels() const;
+    ExecutionStats stats;
+
+  private:
+    friend class Lowering;
+    struct Ctx {
+        const void* const* inputs;
+        void* const* outputs;
+        char* arena;
+        char* consts;
+        void* stream;
+    };
+    struct Step {
+        std::string label;
+        int launches = 1;
+        std::function<int(const Ctx&)> run;  // returns an mhlo_cuda status
+    };
+    std::vector<TensorType> input_types_, output_types_;
+    std::vector<Step> steps_;
+    std::vector<uint8_t> const_pool_;
+    char* const_dev_ = nullptr;
+    char* arena_dev_ = nullptr;
+    int64_t arena_bytes_ = 0;
+    int launches_per_run_ = 0;
+    std::vector<PassRecord> pass_log_;
+    std::string optimized_text_;
+    std::string error_;
+};
+
+// Small helpers over backend_config JSON strings of fused custom calls.
+double json_number(const std::string& json, const std::string& key, double dflt);
+bool json_bool(const std::string& json, const std::string& key, bool dflt);
+std::string json_string(const std::string& json, const std::string& key, const std::string& dflt);
+std::vector<int64_t> json_int_array(const std::string& json, const std::string& key);
+
+}  // namespace mhlo

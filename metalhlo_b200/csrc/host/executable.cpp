@@ -1,0 +1,1040 @@
+// Lowers an optimised function to a list of device launches over a statically planned arena and runs it.
+//
+// Role in the reference: CodeGenerator.generateWithViews + buildBindings + calculateDispatch
+// (Sources/MetalHLOCore/Compiler/CodeGenerator.swift:103-166,5380-5879) decide, per op, which kernel runs on
+// which buffers; StaticMemoryPlanner places intermediates; IntegratedExecutor.execute
+// (Sources/MetalHLOCore/Runtime/IntegratedExecutor.swift:150-270) walks the list. Here the kernels are the AOT
+// sm_100a entry points of libmhlo_cuda.so, and reshape / transpose / broadcast_in_dim / slice / reverse never
+// launch anything: they become strided views that the consuming kernel reads directly.
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <numeric>
+
+#include "../../../include/mhlo_cuda.h"
+#include "compiler.h"
+#include "numeric.h"
+
+namespace mhlo {
+
+// ---- tiny JSON field readers (backend_config of fused custom calls) -------------------------------------------------
+
+static size_t json_find(const std::string& j, const std::string& key) {
+    const std::string pat = "\"" + key + "\"";
+    size_t p = j.find(pat);
+    if (p == std::string::npos) return p;
+    p = j.find(':', p + pat.size());
+    if (p == std::string::npos) return p;
+    ++p;
+    while (p < j.size() && std::isspace(static_cast<unsigned char>(j[p]))) ++p;
+    return p;
+}
+double json_number(const std::string& j, const std::string& key, double dflt) {
+    size_t p = json_find(j, key);
+    if (p == std::string::npos) return dflt;
+    char* end = nullptr;
+    double v = std::strtod(j.c_str() + p, &end);
+    return end == j.c_str() + p ? dflt : v;
+}
+bool json_bool(const std::string& j, const std::string& key, bool dflt) {
+    size_t p = json_find(j, key);
+    if (p == std::string::npos) return dflt;
+    if (j.compare(p, 4, "true") == 0) return true;
+    if (j.compare(p, 5, "false") == 0) return false;
+    return json_number(j, key, dflt ? 1 : 0) != 0;
+}
+std::string json_string(const std::string& j, const std::string& key, const std::string& dflt) {
+    size_t p = json_find(j, key);
+    if (p == std::string::npos || j[p] != '"') return dflt;
+    size_t e = j.find('"', p + 1);
+    return e == std::string::npos ? dflt : j.substr(p + 1, e - p - 1);
+}
+std::vector<int64_t> json_int_array(const std::string& j, const std::string& key) {
+    std::vector<int64_t> out;
+    size_t p = json_find(j, key);
+    if (p == std::string::npos || j[p] != '[') return out;
+    ++p;
+    while (p < j.size() && j[p] != ']') {
+        char* end = nullptr;
+        long long v = std::strtoll(j.c_str() + p, &end, 10);
+        if (end == j.c_str() + p) { ++p; continue; }
+        out.push_back(v);
+        p = static_cast<size_t>(end - j.c_str());
+    }
+    return out;
+}
+
+// ---- memory planner ---------------------------------------------------------------------------------------------------
+
+int64_t plan_memory(std::vector<PlanInterval>* buffers) {
+    std::vector<int> order(buffers->size());
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(),
+                     [&](int a, int b) { return (*buffers)[a].bytes > (*buffers)[b].bytes; });
+    auto align = [](int64_t v) { return (v + 255) / 256 * 256; };
+    std::vector<int> placed;
+    int64_t total = 0;
+    for (int id : order) {
+        PlanInterval& b = (*buffers)[id];
+        if (b.bytes == 0) { b.offset = 0; continue; }
+        // candidate offsets: 0 and the end of every placed buffer that is live at the same time
+        std::vector<std::pair<int64_t, int64_t>> busy;
+        for (int o : placed) {
+            const PlanInterval& q = (*buffers)[o];
+            if (q.last < b.first || b.last < q.first) continue;
+            busy.emplace_back(q.offset, q.offset + align(q.bytes));
+        }
+        std::sort(busy.begin(), busy.end());
+        int64_t best = -1, best_gap = INT64_MAX, cursor = 0;
+        const int64_t need = align(b.bytes);
+        for (const auto& iv : busy) {
+            if (iv.first - cursor >= need && iv.first - cursor < best_gap) { best = cursor; best_gap = iv.first - cursor; }
+            cursor = std::max(cursor, iv.second);
+        }
+        if (best < 0) best = cursor;  // no gap fits: append after the last conflicting buffer
+        b.offset = best;
+        total = std::max(total, best + need);
+        placed.push_back(id);
+    }
+    return (total + 4095) / 4096 * 4096;
+}
+
+// ---- lowering -----------------------------------------------------------------------------------------------------------
+
+namespace {
+
+struct View {
+    int buf = -1;
+    int64_t offset = 0;  // elements
+    std::vector<int64_t> strides;
+    TensorType type;
+};
+
+struct Buffer {
+    enum Kind { Input, Const, Arena, Output } kind = Arena;
+    int index = 0;  // input / output ordinal
+    int64_t bytes = 0;
+    int64_t offset = 0;  // byte offset inside the const pool / arena
+    int first = -1, last = -1;
+};
+
+std::vector<int64_t> dense_strides(const std::vector<int64_t>& shape) {
+    std::vector<int64_t> s(shape.size());
+    int64_t m = 1;
+    for (int d = static_cast<int>(shape.size()) - 1; d >= 0; --d) { s[d] = m; m *= shape[d]; }
+    return s;
+}
+
+bool is_dense(const View& v) {
+    int64_t expect = 1;
+    for (int d = v.type.rank() - 1; d >= 0; --d) {
+        if (v.type.shape[d] == 1) continue;
+        if (v.strides[d] != expect) return false;
+        expect *= v.type.shape[d];
+    }
+    return true;
+}
+
+// numpy's no-copy reshape: can `v` be viewed with `shape` without moving data?
+bool reshape_view(const View& v, const std::vector<int64_t>& shape, View* out) {
+    std::vector<int64_t> os, ost;  // old dims without extent 1
+    for (int d = 0; d < v.type.rank(); ++d)
+        if (v.type.shape[d] != 1) { os.push_back(v.type.shape[d]); ost.push_back(v.strides[d]); }
+    std::vector<int64_t> ns(shape.size(), 0);
+    size_t oi = 0, ni = 0;
+    const size_t on = os.size(), nn = shape.size();
+    int64_t count = 1;
+    for (int64_t d : shape) count *= d;
+    if (count == 0) { out->strides = dense_strides(shape); return true; }
+    while (ni < nn && oi < on) {
+        if (shape[ni] == 1) { ns[ni++] = 0; continue; }
+        int64_t np = shape[ni], op = os[oi];
+        size_t oj = oi + 1, nj = ni + 1;
+        while (np != op) {
+            if (np < op) { if (nj >= nn) return false; np *= shape[nj++]; }
+            else { if (oj >= on) return false; op *= os[oj++]; }
+        }
+        for (size_t k = oi; k + 1 < oj; ++k)
+            if (ost[k] != ost[k + 1] * os[k + 1]) return false;  // old dims of this group are not mergeable
+        int64_t st = ost[oj - 1];
+        for (size_t k = nj; k-- > ni;) {
+            ns[k] = st;
+            st *= shape[k];
+        }
+        oi = oj;
+        ni = nj;
+    }
+    for (; ni < nn; ++ni) { if (shape[ni] != 1) return false; ns[ni] = 0; }
+    if (oi < on) return false;
+    out->strides = ns;
+    return true;
+}
+
+int ew_opcode(const std::string& n) {
+    static const std::map<std::string, int> table = {
+        {"add", MHLO_EW_ADD}, {"subtract", MHLO_EW_SUB}, {"multiply", MHLO_EW_MUL}, {"divide", MHLO_EW_DIV},
+        {"remainder", MHLO_EW_REM}, {"maximum", MHLO_EW_MAX}, {"minimum", MHLO_EW_MIN}, {"power", MHLO_EW_POW},
+        {"atan2", MHLO_EW_ATAN2}, {"and", MHLO_EW_AND}, {"or", MHLO_EW_OR}, {"xor", MHLO_EW_XOR},
+        {"shift_left", MHLO_EW_SHL}, {"shift_right_arithmetic", MHLO_EW_SHR_A}, {"shift_right_logical", MHLO_EW_SHR_L},
+        {"negate", MHLO_EW_NEG}, {"abs", MHLO_EW_ABS}, {"exponential", MHLO_EW_EXP}, {"exponential_minus_one", MHLO_EW_EXPM1},
+        {"log", MHLO_EW_LOG}, {"log_plus_one", MHLO_EW_LOG1P}, {"sqrt", MHLO_EW_SQRT}, {"rsqrt", MHLO_EW_RSQRT},
+        {"cbrt", MHLO_EW_CBRT}, {"tanh", MHLO_EW_TANH}, {"logistic", MHLO_EW_LOGISTIC}, {"sine", MHLO_EW_SIN},
+        {"cosine", MHLO_EW_COS}, {"tan", MHLO_EW_TAN}, {"floor", MHLO_EW_FLOOR}, {"ceil", MHLO_EW_CEIL},
+        {"round_nearest_afz", MHLO_EW_ROUND_AFZ}, {"round_nearest_even", MHLO_EW_ROUND_EVEN}, {"sign", MHLO_EW_SIGN},
+        {"not", MHLO_EW_NOT}, {"is_finite", MHLO_EW_IS_FINITE}, {"popcnt", MHLO_EW_POPCNT},
+        {"count_leading_zeros", MHLO_EW_CLZ}, {"convert", MHLO_EW_COPY}, {"select", MHLO_EW_SELECT},
+        {"clamp", MHLO_EW_CLAMP}, {"copy", MHLO_EW_COPY}, {"optimization_barrier", MHLO_EW_COPY},
+        {"gelu_tanh", MHLO_EW_GELU_TANH}, {"gelu_erf", MHLO_EW_GELU_ERF}, {"silu", MHLO_EW_SILU}, {"relu", MHLO_EW_RELU},
+    };
+    auto it = table.find(n);
+    return it == table.end() ? -1 : it->second;
+}
+
+}  // namespace
+
+int elementwise_opcode(const std::string& name) { return ew_opcode(name); }
+
+class Lowering {
+  public:
+    Lowering(const Function& f, Executable* exe) : f_(f), exe_(exe), views_(f.values.size()), have_(f.values.size(), false) {}
+
+    void run() {
+        for (size_t i = 0; i < f_.args.size(); ++i) {
+            Buffer b;
+            b.kind = Buffer::Input;
+            b.index = static_cast<int>(i);
+            b.bytes = f_.type_of(f_.args[i]).bytes();
+            set(f_.args[i], dense_view(add_buffer(b), f_.type_of(f_.args[i])));
+            exe_->input_types_.push_back(f_.type_of(f_.args[i]));
+        }
+        for (const Op& op : f_.ops) {
+            if (op.dead) continue;
+            if (op.name == "return") { lower_return(op); break; }
+            lower(op);
+        }
+        plan();
+    }
+
+  private:
+    const Function& f_;
+    Executable* exe_;
+    std::vector<View> views_;
+    std::vector<bool> have_;
+    std::vector<Buffer> buffers_;
+
+    using Ctx = Executable::Ctx;
+
+    // ---- buffers and views ----------------------------------------------------------------------------------------
+    int add_buffer(const Buffer& b) { buffers_.push_back(b); return static_cast<int>(buffers_.size()) - 1; }
+    int new_arena(int64_t bytes) { Buffer b; b.kind = Buffer::Arena; b.bytes = bytes; return add_buffer(b); }
+    static View dense_view(int buf, const TensorType& t) { View v; v.buf = buf; v.type = t; v.strides = dense_strides(t.shape); return v; }
+    void set(int value, const View& v) { views_[value] = v; have_[value] = true; }
+    const View& get(int value) const {
+        if (!have_[value]) fail_compile("internal: value " + f_.values[value].name + " used before it is lowered");
+        return views_[value];
+    }
+    int step_index() const { return static_cast<int>(exe_->steps_.size()); }
+    void touch(int buf) {
+        Buffer& b = buffers_[buf];
+        const int s = step_index();
+        if (b.first < 0) b.first = s;
+        b.last = std::max(b.last, s);
+    }
+    void keep_alive(const View& v) { touch(v.buf); }
+
+    // Resolved at run time: base pointer of a buffer.
+    std::function<char*(const Ctx&)> resolver(int buf) {
+        // The buffer table is final only after plan(); capture the index and look it up through a shared copy.
+        auto table = table_;
+        return [table, buf](const Ctx& c) -> char* {
+            const Buffer& b = (*table)[buf];
+            switch (b.kind) {
+                case Buffer::Input: return static_cast<char*>(const_cast<void*>(c.inputs[b.index]));
+                case Buffer::Output: return static_cast<char*>(c.outputs[b.index]);
+                case Buffer::Const: return c.consts + b.offset;
+                default: return c.arena + b.offset;
+            }
+        };
+    }
+    std::shared_ptr<std::vector<Buffer>> table_ = std::make_shared<std::vector<Buffer>>();
+
+    struct DevView {  // a View whose pointer is resolved per call
+        std::function<char*(const Ctx&)> base;
+        mhlo_cuda_view v;
+        int64_t byte_offset;
+    };
+    DevView dev(const View& v) {
+        if (v.type.rank() > MHLO_CUDA_MAX_RANK) fail_unsupported("tensor rank above 8: " + v.type.str());
+        DevView d;
+        d.base = resolver(v.buf);
+        std::memset(&d.v, 0, sizeof d.v);
+        d.v.dtype = static_cast<int>(v.type.dtype);
+        d.v.rank = v.type.rank();
+        for (int i = 0; i < v.type.rank(); ++i) { d.v.shape[i] = v.type.shape[i]; d.v.stride[i] = v.strides[i]; }
+        d.byte_offset = v.offset * static_cast<int64_t>(dtype_size(v.type.dtype));
+        return d;
+    }
+    static mhlo_cuda_view bind(const DevView& d, const Ctx& c) {
+        mhlo_cuda_view v = d.v;
+        v.base = d.base(c) + d.byte_offset;
+        return v;
+    }
+
+    void add_step(const std::string& label, std::function<int(const Ctx&)> run, int launches = 1) {
+        Executable::Step s;
+        s.label = label;
+        s.run = std::move(run);
+        s.launches = launches;
+        exe_->steps_.push_back(std::move(s));
+        exe_->launches_per_run_ += launches;
+    }
+
+    // Copies a view into a fresh dense arena buffer (the only place a transpose / broadcast / slice costs a launch).
+    View materialize(const View& v, const std::string& why) {
+        if (is_dense(v)) return v;
+        View out = dense_view(new_arena(v.type.bytes()), v.type);
+        copy_view(v, out, "copy(" + why + ")");
+        return out;
+    }
+    // A dense view whose element 0 is at the buffer start (needed when a raw pointer is handed to a kernel that
+    // takes an offset-free base is NOT required: pointers carry the offset). Kept for clarity.
+    void copy_view(const View& src, const View& dst, const std::string& label) {
+        DevView s = dev(src), d = dev(dst);
+        keep_alive(src);
+        keep_alive(dst);
+        add_step(label, [s, d](const Ctx& c) {
+            mhlo_cuda_view sv = bind(s, c), dv = bind(d, c);
+            mhlo_cuda_ew_inst inst = {MHLO_EW_COPY, 0, 0, 0, 0.0};
+            return mhlo_cuda_elementwise_to_view(&sv, 1, &inst, 1, &dv, c.stream);
+        });
+    }
+
+    // Broadcasts a view to `shape` (numpy-style trailing alignment is NOT used: StableHLO operands already have
+    // the result rank except for scalars, which broadcast everywhere).
+    static View expand_to(const View& v, const std::vector<int64_t>& shape) {
+        if (v.type.shape == shape) return v;
+        View o = v;
+        o.type.shape = shape;
+        o.strides.assign(shape.size(), 0);
+        if (v.type.rank() == static_cast<int>(shape.size()))
+            for (size_t d = 0; d < shape.size(); ++d) o.strides[d] = v.type.shape[d] == shape[d] ? v.strides[d] : 0;
+        return o;
+    }
+
+    // Elementwise program over `ins` (each already of the output shape) into a new dense buffer.
+    View emit_elementwise(const std::vector<View>& ins, const std::vector<mhlo_cuda_ew_inst>& prog, const TensorType& out_t,
+                          const std::string& label) {
+        View out = dense_view(new_arena(out_t.bytes()), out_t);
+        std::vector<DevView> dv;
+        for (const View& v : ins) { dv.push_back(dev(expand_to(v, out_t.shape))); keep_alive(v); }
+        keep_alive(out);
+        DevView dout = dev(out);
+        add_step(label, [dv, dout, prog, out_t](const Ctx& c) {
+            mhlo_cuda_view in[MHLO_CUDA_EW_MAX_INPUTS];
+            for (size_t i = 0; i < dv.size(); ++i) in[i] = bind(dv[i], c);
+            mhlo_cuda_view o = bind(dout, c);
+            return mhlo_cuda_elementwise(in, static_cast<int>(dv.size()), prog.data(), static_cast<int>(prog.size()),
+                                         const_cast<void*>(o.base), static_cast<int>(out_t.dtype), out_t.shape.data(),
+                                         out_t.rank(), c.stream);
+        });
+        return out;
+    }
+
+    // ---- per-op lowering --------------------------------------------------------------------------------------------
+    void lower(const Op& op) {
+        const std::string& n = op.name;
+        if (op.results.empty()) return;  // ops without results have no effect here
+        const TensorType& rt = op.result_types[0];
+        if (n == "constant") return lower_constant(op);
+        if (n == "reshape" || n == "bitcast") return lower_reshape(op);
+        if (n == "transpose") {
+            const View& x = get(op.operands[0]);
+            std::vector<int64_t> perm = op.int_list("permutation");
+            if (static_cast<int>(perm.size()) != x.type.rank()) fail_compile("transpose: permutation rank mismatch");
+            View o = x;
+            o.type = rt;
+            for (size_t d = 0; d < perm.size(); ++d) o.strides[d] = x.strides[perm[d]];
+            return set(op.results[0], o);
+        }
+        if (n == "broadcast_in_dim") {
+            const View& x = get(op.operands[0]);
+            std::vector<int64_t> dims = op.int_list("broadcast_dimensions");
+            if (static_cast<int>(dims.size()) != x.type.rank()) fail_compile("broadcast_in_dim: dims rank mismatch");
+            View o = x;
+            o.type = rt;
+            o.strides.assign(rt.shape.size(), 0);
+            for (size_t d = 0; d < dims.size(); ++d)
+                o.strides[dims[d]] = (x.type.shape[d] == 1 && rt.shape[dims[d]] != 1) ? 0 : x.strides[d];
+            return set(op.results[0], o);
+        }
+        if (n == "broadcast") {  // leading broadcast_sizes
+            const View& x = get(op.operands[0]);
+            View o = x;
+            o.type = rt;
+            const size_t lead = rt.shape.size() - x.type.shape.size();
+            o.strides.assign(rt.shape.size(), 0);
+            for (size_t d = 0; d < x.strides.size(); ++d) o.strides[lead + d] = x.strides[d];
+            return set(op.results[0], o);
+        }
+        if (n == "slice") {
+            const View& x = get(op.operands[0]);
+            std::vector<int64_t> st = op.int_list("start_indices"), sd = op.int_list("strides");
+            if (sd.empty()) sd.assign(st.size(), 1);
+            View o = x;
+            o.type = rt;
+            for (size_t d = 0; d < st.size(); ++d) { o.offset += st[d] * x.strides[d]; o.strides[d] = x.strides[d] * sd[d]; }
+            return set(op.results[0], o);
+        }
+        if (n == "reverse") {
+            const View& x = get(op.operands[0]);
+            View o = x;
+            for (int64_t d : op.int_list("dimensions")) {
+                o.offset += (x.type.shape[d] - 1) * x.strides[d];
+                o.strides[d] = -x.strides[d];
+            }
+            return set(op.results[0], o);
+        }
+        if (n == "iota") {
+            std::vector<mhlo_cuda_ew_inst> prog = {{MHLO_EW_IOTA, 0, 0, 0, static_cast<double>(op.int_attr("iota_dimension", 0))}};
+            return set(op.results[0], emit_elementwise({}, prog, rt, "iota"));
+        }
+        if (n == "compare") {
+            static const std::map<std::string, int> dir = {{"EQ", MHLO_EW_CMP_EQ}, {"NE", MHLO_EW_CMP_NE}, {"LT", MHLO_EW_CMP_LT},
+                                                           {"LE", MHLO_EW_CMP_LE}, {"GT", MHLO_EW_CMP_GT}, {"GE", MHLO_EW_CMP_GE}};
+            auto it = dir.find(op.str_attr("comparison_direction"));
+            if (it == dir.end()) fail_compile("compare without a comparison_direction");
+            std::vector<mhlo_cuda_ew_inst> prog = {{it->second, 0, 1, 0, 0.0}};
+            return set(op.results[0], emit_elementwise({get(op.operands[0]), get(op.operands[1])}, prog, rt, "compare"));
+        }
+        if (n == "concatenate") return lower_concatenate(op);
+        if (n == "pad") return lower_pad(op);
+        if (n == "reduce") return lower_reduce(op);
+        if (n == "dot_general" || n == "dot") return lower_dot(op);
+        if (n == "gather") return lower_gather(op);
+        if (n == "dynamic_slice") return lower_dynamic_slice(op);
+        if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
+        if (n == "custom_call") return lower_custom_call(op);
+        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "sort" ||
+            n == "convolution" || n == "fft" || n == "scatter" || n == "reduce_window" || n == "select_and_scatter" ||
+            n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
+            fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
+        const int code = ew_opcode(n);
+        if (code >= 0) {
+            std::vector<View> ins;
+            for (int v : op.operands) ins.push_back(get(v));
+            if (ins.empty() || ins.size() > 3) fail_compile("elementwise op " + n + " with " + std::to_string(ins.size()) + " operands");
+            mhlo_cuda_ew_inst inst = {code, 0, ins.size() > 1 ? 1 : 0, ins.size() > 2 ? 2 : 0, 0.0};
+            return set(op.results[0], emit_elementwise(ins, {inst}, rt, n));
+        }
+        fail_unsupported("unsupported operation: " + (op.dialect.empty() ? "" : op.dialect + ".") + n);
+    }
+
+    void lower_constant(const Op& op) {
+        const Attr* val = op.attr("value");
+        const TensorType& rt = op.result_types[0];
+        if (!val || val->kind != Attr::Dense) fail_compile("constant without a dense value");
+        Buffer b;
+        b.kind = Buffer::Const;
+        const size_t es = dtype_size(rt.dtype);
+        std::vector<uint8_t> bytes = val->dense;
+        const bool splat = val->splat || (bytes.size() == es && rt.count() != 1);
+        if (!splat && static_cast<int64_t>(bytes.size()) != rt.bytes())
+            fail_compile("constant payload of " + std::to_string(bytes.size()) + " bytes does not match " + rt.str());
+        // 256-byte aligned slot in the pool
+        size_t off = (exe_->const_pool_.size() + 255) / 256 * 256;
+        exe_->const_pool_.resize(off + std::max<size_t>(bytes.size(), 1), 0);
+        if (!bytes.empty()) std::memcpy(exe_->const_pool_.data() + off, bytes.data(), bytes.size());
+        b.offset = static_cast<int64_t>(off);
+        b.bytes = static_cast<int64_t>(bytes.size());
+        View v = dense_view(add_buffer(b), rt);
+        if (splat) v.strides.assign(rt.shape.size(), 0);
+        set(op.results[0], v);
+    }
+
+    void lower_reshape(const Op& op) {
+        const View& x = get(op.operands[0]);
+        const TensorType& rt = op.result_types[0];
+        View o = x;
+        o.type = rt;
+        if (x.type.dtype != rt.dtype) {
+            if (dtype_size(x.type.dtype) != dtype_size(rt.dtype) || !is_dense(x)) fail_unsupported("bitcast between element sizes");
+        }
+        if (reshape_view(x, rt.shape, &o)) return set(op.results[0], o);
+        View m = materialize(x, "reshape");
+        o = m;
+        o.type = rt;
+        o.strides = dense_strides(rt.shape);
+        set(op.results[0], o);
+    }
+
+    void lower_concatenate(const Op& op) {
+        const TensorType& rt = op.result_types[0];
+        const int64_t dim = op.int_attr("dimension", 0);
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        int64_t at = 0;
+        for (int v : op.operands) {
+            const View& x = get(v);
+            View dst = out;
+            dst.type.shape = x.type.shape;
+            dst.offset = at * out.strides[dim];
+            copy_view(x, dst, "concatenate");
+            at += x.type.shape[dim];
+        }
+        set(op.results[0], out);
+    }
+
+    void lower_pad(const Op& op) {
+        const TensorType& rt = op.result_types[0];
+        View x = get(op.operands[0]);
+        const View& pv = get(op.operands[1]);
+        std::vector<int64_t> lo = op.int_list("edge_padding_low"), hi = op.int_list("edge_padding_high"),
+                             in = op.int_list("interior_padding");
+        if (in.empty()) in.assign(lo.size(), 0);
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        copy_view(expand_to(pv, rt.shape), out, "pad.fill");
+        // negative edge padding trims the operand first
+        View dst = out;
+        for (size_t d = 0; d < lo.size(); ++d) {
+            const int64_t step = in[d] + 1;
+            int64_t first = 0, count = x.type.shape[d];
+            // operand element j lands at lo + j*step; keep those inside [0, out extent)
+            while (count > 0 && lo[d] + first * step < 0) { ++first; --count; }
+            while (count > 0 && lo[d] + (first + count - 1) * step >= rt.shape[d]) --count;
+            x.offset += first * x.strides[d];
+            x.type.shape[d] = count;
+            dst.offset += (lo[d] + first * step) * out.strides[d];
+            dst.strides[d] = out.strides[d] * step;
+            dst.type.shape[d] = count;
+        }
+        if (x.type.count() > 0) copy_view(x, dst, "pad.interior");
+        set(op.results[0], out);
+    }
+
+    void lower_reduce(const Op& op) {
+        const size_t n_in = op.operands.size() / 2;
+        std::string red = op.str_attr("reducer");
+        static const std::map<std::string, int> kinds = {
+            {"add", MHLO_REDUCE_SUM}, {"maximum", MHLO_REDUCE_MAX}, {"minimum", MHLO_REDUCE_MIN}, {"multiply", MHLO_REDUCE_PROD},
+            {"and", MHLO_REDUCE_AND}, {"or", MHLO_REDUCE_OR}, {"xor", MHLO_REDUCE_XOR}, {"argmax", MHLO_REDUCE_ARGMAX},
+            {"argmin", MHLO_REDUCE_ARGMIN}};
+        auto it = kinds.find(red);
+        if (it == kinds.end()) fail_unsupported("reduce with a reducer body this backend does not recognise (" + red + ")");
+        int kind = it->second;
+        const bool arg = kind == MHLO_REDUCE_ARGMAX || kind == MHLO_REDUCE_ARGMIN;
+        if ((arg && n_in != 2) || (!arg && n_in != 1)) fail_unsupported("variadic reduce other than the argmax/argmin form");
+        const View& x = get(op.operands[0]);
+        std::vector<int64_t> dims = op.int_list("dimensions");
+        std::vector<bool> reduced(x.type.rank(), false);
+        for (int64_t d : dims) reduced[d] = true;
+        View p = x;
+        p.type.shape.clear();
+        p.strides.clear();
+        int kept = 0;
+        for (int d = 0; d < x.type.rank(); ++d)
+            if (!reduced[d]) { p.type.shape.push_back(x.type.shape[d]); p.strides.push_back(x.strides[d]); ++kept; }
+        for (int d = 0; d < x.type.rank(); ++d)
+            if (reduced[d]) { p.type.shape.push_back(x.type.shape[d]); p.strides.push_back(x.strides[d]); }
+        if (arg && dims.size() != 1) fail_unsupported("argmax/argmin over more than one dimension");
+        const TensorType& rt = op.result_types[0];
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        View iout;
+        DevView dio;
+        bool has_index = false;
+        if (arg) {
+            const TensorType& it2 = op.result_types[1];
+            if (it2.dtype != DType::I32 && it2.dtype != DType::I64) fail_unsupported("argmax index type " + it2.str());
+            iout = dense_view(new_arena(it2.bytes()), it2);
+            dio = dev(iout);
+            has_index = true;
+        }
+        View init = materialize(get(op.operands[n_in]), "reduce.init");
+        DevView dp = dev(p), dout = dev(out), dinit = dev(init);
+        keep_alive(x); keep_alive(out); keep_alive(init);
+        if (has_index) keep_alive(iout);
+        const int index_dtype = has_index ? static_cast<int>(op.result_types[1].dtype) : MHLO_DT_I32;
+        add_step("reduce." + red, [dp, dout, dinit, dio, has_index, kept, kind, index_dtype](const Ctx& c) {
+            mhlo_cuda_view in = bind(dp, c);
+            return mhlo_cuda_reduce(&in, kept, kind, bind(dinit, c).base, const_cast<void*>(bind(dout, c).base),
+                                    has_index ? const_cast<void*>(bind(dio, c).base) : nullptr, index_dtype, c.stream);
+        });
+        set(op.results[0], out);
+        if (arg) set(op.results[1], iout);
+    }
+
+    // Merges a group of (extent, stride) pairs into as few dims as their strides allow.
+    static void merge_group(std::vector<int64_t>* shape, std::vector<int64_t>* stride) {
+        std::vector<int64_t> s, t;
+        for (size_t i = 0; i < shape->size(); ++i) {
+            if ((*shape)[i] == 1) continue;
+            if (!s.empty() && t.back() == (*stride)[i] * (*shape)[i]) { s.back() *= (*shape)[i]; t.back() = (*stride)[i]; }
+            else { s.push_back((*shape)[i]); t.push_back((*stride)[i]); }
+        }
+        *shape = s;
+        *stride = t;
+    }
+
+    void lower_dot(const Op& op) {
+        View a = get(op.operands[0]), b = get(op.operands[1]);
+        const TensorType& rt = op.result_types[0];
+        std::vector<int64_t> lb, rb, lc, rc;
+        if (op.name == "dot") {
+            lc = {a.type.rank() - 1};
+            rc = {0};
+        } else {
+            lb = op.int_list("lhs_batching_dimensions"); rb = op.int_list("rhs_batching_dimensions");
+            lc = op.int_list("lhs_contracting_dimensions"); rc = op.int_list("rhs_contracting_dimensions");
+        }
+        auto rest = [](int rank, const std::vector<int64_t>& x, const std::vector<int64_t>& y) {
+            std::vector<int64_t> r;
+            for (int d = 0; d < rank; ++d)
+                if (std::find(x.begin(), x.end(), d) == x.end() && std::find(y.begin(), y.end(), d) == y.end()) r.push_back(d);
+            return r;
+        };
+        std::vector<int64_t> lf = rest(a.type.rank(), lb, lc), rf = rest(b.type.rank(), rb, rc);
+        struct Grp { std::vector<int64_t> shape, stride; };
+        auto group = [](const View& v, const std::vector<int64_t>& dims) {
+            Grp g;
+            for (int64_t d : dims) { g.shape.push_back(v.type.shape[d]); g.stride.push_back(v.strides[d]); }
+            return g;
+        };
+        auto extent = [](const Grp& g) { int64_t n = 1; for (int64_t d : g.shape) n *= d; return n; };
+        // try the views as they are; if a group does not merge far enough, copy that operand into the canonical
+        // [batch.., free.., contracting..] (lhs) / [batch.., contracting.., free..] (rhs) order and retry once
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            Grp am = group(a, lf), ak = group(a, lc), bk = group(b, rc), bn = group(b, rf);
+            Grp ab = group(a, lb), bb = group(b, rb);
+            const int64_t M = extent(am), N = extent(bn), K = extent(ak), B = extent(ab);
+            merge_group(&am.shape, &am.stride);
+            merge_group(&bn.shape, &bn.stride);
+            // contracting dims must merge identically on both sides
+            {
+                std::vector<int64_t> s, ta, tb;
+                for (size_t i = 0; i < ak.shape.size(); ++i) {
+                    if (ak.shape[i] == 1) continue;
+                    if (!s.empty() && ta.back() == ak.stride[i] * ak.shape[i] && tb.back() == bk.stride[i] * bk.shape[i]) {
+                        s.back() *= ak.shape[i]; ta.back() = ak.stride[i]; tb.back() = bk.stride[i];
+                    } else { s.push_back(ak.shape[i]); ta.push_back(ak.stride[i]); tb.push_back(bk.stride[i]); }
+                }
+                ak.shape = s; ak.stride = ta; bk.shape = s; bk.stride = tb;
+            }
+            {
+                std::vector<int64_t> s, ta, tb;
+                for (size_t i = 0; i < ab.shape.size(); ++i) {
+                    if (ab.shape[i] == 1) continue;
+                    if (!s.empty() && ta.back() == ab.stride[i] * ab.shape[i] && tb.back() == bb.stride[i] * bb.shape[i]) {
+                        s.back() *= ab.shape[i]; ta.back() = ab.stride[i]; tb.back() = bb.stride[i];
+                    } else { s.push_back(ab.shape[i]); ta.push_back(ab.stride[i]); tb.push_back(bb.stride[i]); }
+                }
+                ab.shape = s; ab.stride = ta; bb.shape = s; bb.stride = tb;
+            }
+            const bool a_ok = am.shape.size() <= 1 && ak.shape.size() <= 1 && ab.shape.size() <= 2;
+            const bool b_ok = bn.shape.size() <= 1 && bk.shape.size() <= 1 && bb.shape.size() <= 2;
+            if (a_ok && b_ok) {
+                int64_t as[4] = {0, 0, 0, 0}, bs[4] = {0, 0, 0, 0};
+                int64_t b0 = 1, b1 = 1;
+                if (ab.shape.size() == 2) { b0 = ab.shape[0]; b1 = ab.shape[1]; as[0] = ab.stride[0]; as[1] = ab.stride[1]; bs[0] = bb.stride[0]; bs[1] = bb.stride[1]; }
+                else if (ab.shape.size() == 1) { b1 = ab.shape[0]; as[1] = ab.stride[0]; bs[1] = bb.stride[0]; }
+                as[2] = am.shape.empty() ? 0 : am.stride[0];
+                as[3] = ak.shape.empty() ? 0 : ak.stride[0];
+                bs[2] = bk.shape.empty() ? 0 : bk.stride[0];
+                bs[3] = bn.shape.empty() ? 0 : bn.stride[0];
+                (void)B;
+                View out = dense_view(new_arena(rt.bytes()), rt);
+                DevView da = dev(a), db = dev(b), dc = dev(out);
+                keep_alive(a); keep_alive(b); keep_alive(out);
+                const int in_dt = static_cast<int>(a.type.dtype), out_dt = static_cast<int>(rt.dtype);
+                std::array<int64_t, 4> asv = {as[0], as[1], as[2], as[3]}, bsv = {bs[0], bs[1], bs[2], bs[3]};
+                add_step("dot_general", [=](const Ctx& c) {
+                    return mhlo_cuda_gemm(in_dt, out_dt, bind(da, c).base, asv.data(), bind(db, c).base, bsv.data(),
+                                          const_cast<void*>(bind(dc, c).base), b0, b1, M, N, K, nullptr, MHLO_EPILOGUE_NONE,
+                                          c.stream);
+                });
+                return set(op.results[0], out);
+            }
+            if (attempt == 1) fail_compile("internal: dot_general operands did not canonicalise");
+            if (!a_ok) {
+                std::vector<int64_t> perm = lb;
+                perm.insert(perm.end(), lf.begin(), lf.end());
+                perm.insert(perm.end(), lc.begin(), lc.end());
+                a = permuted_copy(a, perm, "dot.lhs");
+                const int nb = static_cast<int>(lb.size()), nf = static_cast<int>(lf.size()), nc = static_cast<int>(lc.size());
+                lb.clear(); lf.clear(); lc.clear();
+                for (int i = 0; i < nb; ++i) lb.push_back(i);
+                for (int i = 0; i < nf; ++i) lf.push_back(nb + i);
+                for (int i = 0; i < nc; ++i) lc.push_back(nb + nf + i);
+            }
+            if (!b_ok) {
+                std::vector<int64_t> perm = rb;
+                perm.insert(perm.end(), rc.begin(), rc.end());
+                perm.insert(perm.end(), rf.begin(), rf.end());
+                b = permuted_copy(b, perm, "dot.rhs");
+                const int nb = static_cast<int>(rb.size()), nc = static_cast<int>(rc.size()), nf = static_cast<int>(rf.size());
+                rb.clear(); rc.clear(); rf.clear();
+                for (int i = 0; i < nb; ++i) rb.push_back(i);
+                for (int i = 0; i < nc; ++i) rc.push_back(nb + i);
+                for (int i = 0; i < nf; ++i) rf.push_back(nb + nc + i);
+            }
+        }
+    }
+
+    View permuted_copy(const View& v, const std::vector<int64_t>& perm, const std::string& why) {
+        View p = v;
+        p.type.shape.clear();
+        p.strides.clear();
+        for (int64_t d : perm) { p.type.shape.push_back(v.type.shape[d]); p.strides.push_back(v.strides[d]); }
+        View out = dense_view(new_arena(p.type.bytes()), p.type);
+        copy_view(p, out, "copy(" + why + ")");
+        return out;
+    }
+
+    void lower_gather(const Op& op) {
+        View operand = materialize(get(op.operands[0]), "gather.operand");
+        View indices = materialize(get(op.operands[1]), "gather.indices");
+        const TensorType& rt = op.result_types[0];
+        mhlo_cuda_gather_dims g;
+        std::memset(&g, 0, sizeof g);
+        auto fill = [&](const char* key, int32_t* dst, int32_t* count) {
+            std::vector<int64_t> v = op.int_list(key);
+            if (v.size() > MHLO_CUDA_MAX_RANK) fail_unsupported(std::string("gather: ") + key + " longer than 8");
+            for (size_t i = 0; i < v.size(); ++i) dst[i] = static_cast<int32_t>(v[i]);
+            if (count) *count = static_cast<int32_t>(v.size());
+        };
+        fill("offset_dims", g.offset_dims, &g.n_offset_dims);
+        fill("collapsed_slice_dims", g.collapsed_slice_dims, &g.n_collapsed);
+        fill("operand_batching_dims", g.operand_batching_dims, &g.n_operand_batching);
+        fill("start_indices_batching_dims", g.start_indices_batching_dims, nullptr);
+        fill("start_index_map", g.start_index_map, &g.n_start_index_map);
+        g.index_vector_dim = static_cast<int32_t>(op.int_attr("index_vector_dim", indices.type.rank()));
+        std::vector<int64_t> ss = op.int_list("slice_sizes");
+        if (static_cast<int>(ss.size()) != operand.type.rank()) fail_compile("gather: slice_sizes rank mismatch");
+        for (size_t i = 0; i < ss.size(); ++i) g.slice_sizes[i] = ss[i];
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dop = dev(operand), din = dev(indices), dout = dev(out);
+        keep_alive(operand); keep_alive(indices); keep_alive(out);
+        const TensorType ot = operand.type, it = indices.type, rtt = rt;
+        add_step("gather", [=](const Ctx& c) {
+            return mhlo_cuda_gather(bind(dop, c).base, static_cast<int>(dtype_size(ot.dtype)), ot.shape.data(), ot.rank(),
+                                    bind(din, c).base, static_cast<int>(it.dtype), it.shape.data(), it.rank(), &g,
+                                    const_cast<void*>(bind(dout, c).base), rtt.shape.data(), rtt.rank(), c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    void lower_dynamic_slice(const Op& op) {
+        View operand = materialize(get(op.operands[0]), "dynamic_slice.operand");
+        const TensorType& rt = op.result_types[0];
+        std::vector<DevView> idx;
+        DType idt = DType::I32;
+        for (size_t i = 1; i < op.operands.size(); ++i) {
+            View iv = materialize(get(op.operands[i]), "dynamic_slice.index");
+            idt = iv.type.dtype;
+            idx.push_back(dev(iv));
+            keep_alive(iv);
+        }
+        if (static_cast<int>(idx.size()) != operand.type.rank()) fail_compile("dynamic_slice: one start index per dimension expected");
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dop = dev(operand), dout = dev(out);
+        keep_alive(operand); keep_alive(out);
+        const TensorType ot = operand.type, rtt = rt;
+        const int index_dtype = static_cast<int>(idt);
+        add_step("dynamic_slice", [=](const Ctx& c) {
+            const void* ptrs[MHLO_CUDA_MAX_RANK];
+            for (size_t i = 0; i < idx.size(); ++i) ptrs[i] = bind(idx[i], c).base;
+            return mhlo_cuda_dynamic_slice(bind(dop, c).base, static_cast<int>(dtype_size(ot.dtype)), ot.shape.data(), ot.rank(),
+                                           ptrs, index_dtype, rtt.shape.data(), const_cast<void*>(bind(dout, c).base), c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    void lower_dynamic_update_slice(const Op& op) {
+        const View& operand = get(op.operands[0]);
+        View update = materialize(get(op.operands[1]), "dynamic_update_slice.update");
+        const TensorType& rt = op.result_types[0];
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        copy_view(operand, out, "dynamic_update_slice.copy");
+        std::vector<DevView> idx;
+        DType idt = DType::I32;
+        for (size_t i = 2; i < op.operands.size(); ++i) {
+            View iv = materialize(get(op.operands[i]), "dynamic_update_slice.index");
+            idt = iv.type.dtype;
+            idx.push_back(dev(iv));
+            keep_alive(iv);
+        }
+        DevView dup = dev(update), dout = dev(out);
+        keep_alive(update); keep_alive(out);
+        const TensorType ut = update.type, rtt = rt;
+        const int index_dtype = static_cast<int>(idt);
+        add_step("dynamic_update_slice", [=](const Ctx& c) {
+            const void* ptrs[MHLO_CUDA_MAX_RANK];
+            for (size_t i = 0; i < idx.size(); ++i) ptrs[i] = bind(idx[i], c).base;
+            return mhlo_cuda_dynamic_update_slice(const_cast<void*>(bind(dout, c).base), static_cast<int>(dtype_size(rtt.dtype)),
+                                                  rtt.shape.data(), rtt.rank(), bind(dup, c).base, ut.shape.data(), ptrs,
+                                                  index_dtype, c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    void lower_custom_call(const Op& op);
+    void lower_return(const Op& op);
+    void plan();
+};
+
+// ---- fused custom calls ------------------------------------------------------------------------------------------------
+
+void Lowering::lower_custom_call(const Op& op) {
+    const std::string target = op.str_attr("call_target_name");
+    const std::string cfg = op.str_attr("backend_config");
+    const TensorType& rt = op.result_types[0];
+    auto operand = [&](size_t i) -> const View& {
+        if (i >= op.operands.size()) fail_compile("custom_call @" + target + " needs at least " + std::to_string(i + 1) + " operands");
+        return get(op.operands[i]);
+    };
+    auto last_axis_only = [&](const std::vector<int64_t>& axes, int rank) {
+        return axes.empty() || (axes.size() == 1 && (axes[0] == -1 || axes[0] == rank - 1));
+    };
+    if (target == "fused_layer_norm" || target == "fused_rms_norm") {
+        const bool ln = target == "fused_layer_norm";
+        View x = materialize(operand(0), target);
+        if (!last_axis_only(json_int_array(cfg, "axes"), x.type.rank())) fail_unsupported(target + " over an axis other than the last");
+        const int64_t hidden = x.type.rank() ? x.type.shape.back() : 1;
+        const int64_t rows = hidden ? x.type.count() / hidden : 0;
+        bool has_g = op.operands.size() > 1, has_b = ln && op.operands.size() > 2;
+        View g, b;
+        if (has_g) g = materialize(expand_to(operand(1), {hidden}), target + ".gamma");
+        if (has_b) b = materialize(expand_to(operand(2), {hidden}), target + ".beta");
+        if (has_g && !is_dense(g)) g = materialize(g, "gamma");
+        const float eps = static_cast<float>(json_number(cfg, "eps", json_number(cfg, "epsilon", 1e-5)));
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dx = dev(x), dg, db, dout = dev(out);
+        keep_alive(x); keep_alive(out);
+        if (has_g) { dg = dev(g); keep_alive(g); }
+        if (has_b) { db = dev(b); keep_alive(b); }
+        const int dt = static_cast<int>(x.type.dtype);
+        add_step(target, [=](const Ctx& c) {
+            const void* gp = has_g ? bind(dg, c).base : nullptr;
+            const void* bp = has_b ? bind(db, c).base : nullptr;
+            if (ln) return mhlo_cuda_layer_norm(dt, bind(dx, c).base, gp, bp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, nullptr, c.stream);
+            return mhlo_cuda_rms_norm(dt, bind(dx, c).base, gp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, nullptr, c.stream);
+        });
+        return set(op.results[0], out);
+    }
+    if (target == "fused_softmax") {
+        View x = materialize(operand(0), target);
+        int64_t axis = static_cast<int64_t>(json_number(cfg, "axis", -1));
+        if (axis < 0) axis += x.type.rank();
+        if (axis < 0 || axis >= std::max(1, x.type.rank())) fail_compile("fused_softmax: axis out of range");
+        int64_t outer = 1, inner = 1;
+        for (int d = 0; d < axis; ++d) outer *= x.type.shape[d];
+        for (int d = static_cast<int>(axis) + 1; d < x.type.rank(); ++d) inner *= x.type.shape[d];
+        const int64_t len = x.type.rank() ? x.type.shape[axis] : 1;
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dx = dev(x), dout = dev(out);
+        keep_alive(x); keep_alive(out);
+        const int dt = static_cast<int>(x.type.dtype);
+        add_step(target, [=](const Ctx& c) {
+            return mhlo_cuda_softmax(dt, bind(dx, c).base, const_cast<void*>(bind(dout, c).base), outer, len, inner, nullptr, c.stream);
+        });
+        return set(op.results[0], out);
+    }
+    if (target == "fused_gelu" || target == "fused_silu" || target == "fused_relu") {
+        int code = MHLO_EW_RELU;
+        if (target == "fused_gelu") code = json_bool(cfg, "approximate", true) ? MHLO_EW_GELU_TANH : MHLO_EW_GELU_ERF;
+        if (target == "fused_silu") code = MHLO_EW_SILU;
+        mhlo_cuda_ew_inst inst = {code, 0, 0, 0, 0.0};
+        return set(op.results[0], emit_elementwise({operand(0)}, {inst}, rt, target));
+    }
+    if (target == "fused_elementwise") {
+        // program: attribute "_program" = array of [opcode, a, b, c, imm] built by producer-consumer fusion
+        const Attr* pa = op.attr("_program");
+        if (!pa || pa->kind != Attr::Array) fail_unsupported("fused_elementwise without a program attribute");
+        std::vector<mhlo_cuda_ew_inst> prog;
+        for (const Attr& e : pa->elems) {
+            if (e.elems.size() != 5) fail_compile("fused_elementwise: malformed instruction");
+            mhlo_cuda_ew_inst inst;
+            inst.op = static_cast<int>(e.elems[0].i);
+            inst.a = static_cast<int>(e.elems[1].i);
+            inst.b = static_cast<int>(e.elems[2].i);
+            inst.c = static_cast<int>(e.elems[3].i);
+            inst.imm = e.elems[4].as_float();
+            prog.push_back(inst);
+        }
+        std::vector<View> ins;
+        for (int v : op.operands) ins.push_back(get(v));
+        return set(op.results[0], emit_elementwise(ins, prog, rt, target));
+    }
+    if (target == "fused_matmul_bias_activation") {
+        // act(x . w + bias): x [.., M, K] (leading dims flattened), w [K, N], bias [N] (optional)
+        View x = materialize(operand(0), target + ".x"), w = operand(1);
+        if (w.type.rank() != 2) fail_unsupported(target + ": weight must be rank 2");
+        const int64_t K = w.type.shape[0], N = w.type.shape[1];
+        const int64_t M = K ? x.type.count() / K : 0;
+        const bool has_bias = op.operands.size() > 2;
+        View bias;
+        if (has_bias) bias = materialize(expand_to(operand(2), {N}), target + ".bias");
+        const std::string act = json_string(cfg, "activation", "none");
+        int epi = MHLO_EPILOGUE_NONE;
+        if (act == "gelu" || act == "gelu_tanh") epi = MHLO_EPILOGUE_GELU_TANH;
+        else if (act == "gelu_erf") epi = MHLO_EPILOGUE_GELU_ERF;
+        else if (act == "relu") epi = MHLO_EPILOGUE_RELU;
+        else if (act == "silu") epi = MHLO_EPILOGUE_SILU;
+        else if (act == "tanh") epi = MHLO_EPILOGUE_TANH;
+        else if (act == "sigmoid" || act == "logistic") epi = MHLO_EPILOGUE_SIGMOID;
+        else if (act != "none") fail_unsupported(target + ": activation '" + act + "'");
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dx = dev(x), dw = dev(w), dbias, dout = dev(out);
+        keep_alive(x); keep_alive(w); keep_alive(out);
+        if (has_bias) { dbias = dev(bias); keep_alive(bias); }
+        const int in_dt = static_cast<int>(x.type.dtype), out_dt = static_cast<int>(rt.dtype);
+        std::array<int64_t, 4> as = {0, 0, K, 1}, bs = {0, 0, w.strides[0], w.strides[1]};
+        add_step(target, [=](const Ctx& c) {
+            return mhlo_cuda_gemm(in_dt, out_dt, bind(dx, c).base, as.data(), bind(dw, c).base, bs.data(),
+                                  const_cast<void*>(bind(dout, c).base), 1, 1, M, N, K, has_bias ? bind(dbias, c).base : nullptr,
+                                  epi, c.stream);
+        });
+        return set(op.results[0], out);
+    }
+    if (target == "fused_scaled_dot_product_attention") {
+        // q [B,H,Sq,D], k/v [B,H,Sk,D] in logical order; the views may be permutations of other layouts as long as D
+        // is contiguous. Output dense [B,H,Sq,D] unless "output_layout":"BSHD" asks for [B,Sq,H,D].
+        View q = operand(0), k = operand(1), v = operand(2);
+        if (q.type.rank() == 3) {  // [BH,S,D] -> [1,BH,S,D]
+            for (View* t : {&q, &k, &v}) { t->type.shape.insert(t->type.shape.begin(), 1); t->strides.insert(t->strides.begin(), 0); }
+        }
+        if (q.type.rank() != 4) fail_unsupported(target + ": rank-3 or rank-4 operands expected, got " + q.type.str());
+        for (View* t : {&q, &k, &v})
+            if (t->strides[3] != 1 && t->type.shape[3] != 1) *t = materialize(*t, target + ".operand");
+        const bool has_mask = json_bool(cfg, "has_mask", false) && op.operands.size() > 3;
+        View mask;
+        if (has_mask) {
+            const int64_t sq = q.type.shape[2], sk = k.type.shape[2];
+            mask = operand(3);
+            if (mask.type.count() != sq * sk) fail_unsupported(target + ": only a [Sq,Sk] additive mask shared by all heads is supported");
+            View m2 = mask;
+            if (!reshape_view(mask, {sq, sk}, &m2)) { m2 = materialize(mask, "mask"); m2.strides = {sk, 1}; }
+            m2.type.shape = {sq, sk};
+            mask = materialize(m2, target + ".mask");
+        }
+        const float scale = static_cast<float>(json_number(cfg, "scale", 1.0));
+        const bool causal = json_bool(cfg, "is_causal", false);
+        const bool bshd_out = json_string(cfg, "output_layout", "BHSD") == "BSHD";
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dq = dev(q), dk = dev(k), dv = dev(v), dm, dout = dev(out);
+        keep_alive(q); keep_alive(k); keep_alive(v); keep_alive(out);
+        if (has_mask) { dm = dev(mask); keep_alive(mask); }
+        const int dt = static_cast<int>(q.type.dtype);
+        const int64_t B = q.type.shape[0], H = q.type.shape[1], Sq = q.type.shape[2], D = q.type.shape[3], Sk = k.type.shape[2];
+        std::array<int64_t, 3> qs = {q.strides[0], q.strides[1], q.strides[2]}, ks = {k.strides[0], k.strides[1], k.strides[2]},
+                               vs = {v.strides[0], v.strides[1], v.strides[2]};
+        std::array<int64_t, 3> os = bshd_out ? std::array<int64_t, 3>{Sq * H * D, D, H * D} : std::array<int64_t, 3>{H * Sq * D, Sq * D, D};
+        add_step(target, [=](const Ctx& c) {
+            return mhlo_cuda_attention(dt, bind(dq, c).base, qs.data(), bind(dk, c).base, ks.data(), bind(dv, c).base, vs.data(),
+                                       has_mask ? bind(dm, c).base : nullptr, const_cast<void*>(bind(dout, c).base), os.data(), B, H, Sq,
+                                       Sk, D, scale, causal ? 1 : 0, c.stream);
+        });
+        return set(op.results[0], out);
+    }
+    fail_unsupported("custom_call target @" + target + " is not provided by this backend");
+}
+
+void Lowering::lower_return(const Op& op) {
+    std::set<int> claimed;
+    for (size_t i = 0; i < op.operands.size(); ++i) {
+        const View& v = get(op.operands[i]);
+        exe_->output_types_.push_back(v.type);
+        Buffer& b = buffers_[v.buf];
+        const bool whole = b.kind == Buffer::Arena && v.offset == 0 && is_dense(v) && b.bytes == v.type.bytes() &&
+                           !claimed.count(v.buf) && v.type.count() > 0;
+        bool zero_stride = false;
+        for (size_t d = 0; d < v.strides.size(); ++d) zero_stride |= v.strides[d] == 0 && v.type.shape[d] > 1;
+        if (whole && !zero_stride) {
+            // the producing kernel writes straight into the caller's output buffer
+            b.kind = Buffer::Output;
+            b.index = static_cast<int>(i);
+            claimed.insert(v.buf);
+            continue;
+        }
+        Buffer ob;
+        ob.kind = Buffer::Output;
+        ob.index = static_cast<int>(i);
+        ob.bytes = v.type.bytes();
+        View dst = dense_view(add_buffer(ob), v.type);
+        if (v.type.count() > 0) copy_view(v, dst, "copy(output)");
+    }
+}
+
+void Lowering::plan() {
+    std::vector<PlanInterval> ivs;
+    std::vector<int> ids;
+    for (size_t i = 0; i < buffers_.size(); ++i) {
+        if (buffers_[i].kind != Buffer::Arena) continue;
+        PlanInterval p;
+        p.bytes = buffers_[i].bytes;
+        p.first = std::max(0, buffers_[i].first);
+        p.last = std::max(p.first, buffers_[i].last);
+        ivs.push_back(p);
+        ids.push_back(static_cast<int>(i));
+    }
+    const bool no_reuse = std::getenv("METALHLO_NO_REUSE") || std::getenv("METALHLO_DEBUG_NO_BUFFER_REUSE");
+    if (no_reuse)
+        for (PlanInterval& p : ivs) { p.first = 0; p.last = step_index(); }
+    exe_->arena_bytes_ = plan_memory(&ivs);
+    for (size_t k = 0; k < ids.size(); ++k) buffers_[ids[k]].offset = ivs[k].offset;
+    *table_ = buffers_;
+}
+
+// ---- Executable --------------------------------------------------------------------------------------------------------
+
+Executable::~Executable() {
+    if (const_dev_) mhlo_cuda_free(const_dev_);
+    if (arena_dev_) mhlo_cuda_free(arena_dev_);
+}
+
+std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const CompileOptions& options) {
+    Module m = parse_module(mlir);
+    Function f = m.main();
+    if (std::getenv("METALHLO_DUMP_MLIR")) fprintf(stderr, "[metalhlo] parsed module:\n%s\n", print_function(f).c_str());
+    std::unique_ptr<Executable> exe(new Executable());
+    exe->pass_log_ = run_pass_pipeline(f, options);
+    exe->optimized_text_ = print_function(f);
+    if (std::getenv("METALHLO_DUMP_OPTIMIZED")) fprintf(stderr, "[metalhlo] optimized module:\n%s\n", exe->optimized_text_.c_str());
+    Lowering lower(f, exe.get());
+    lower.run();
+    if (!exe->const_pool_.empty()) {
+        void* p = nullptr;
+        if (mhlo_cuda_alloc(exe->const_pool_.size(), &p) != 0) throw CompileError(6, std::string("constant pool: ") + mhlo_cuda_last_error());
+        exe->const_dev_ = static_cast<char*>(p);
+        if (mhlo_cuda_upload(p, exe->const_pool_.data(), exe->const_pool_.size(), nullptr) != 0 || mhlo_cuda_stream_sync(nullptr) != 0)
+            throw CompileError(9, std::string("constant upload: ") + mhlo_cuda_last_error());
+    }
+    if (exe->arena_bytes_ > 0) {
+        void* p = nullptr;
+        if (mhlo_cuda_alloc(static_cast<size_t>(exe->arena_bytes_), &p) != 0)
+            throw CompileError(6, std::string("arena of ") + std::to_string(exe->arena_bytes_) + " bytes: " + mhlo_cuda_last_error());
+        exe->arena_dev_ = static_cast<char*>(p);
+    }
+    return exe;
+}
+
+int Executable::execute(const void* const* inputs, void* const* outputs, void* stream) {
+    Ctx c{inputs, outputs, arena_dev_, const_dev_, stream};
+    const bool debug = std::getenv("METALHLO_DEBUG_DISPATCH") != nullptr;
+    for (size_t i = 0; i < steps_.size(); ++i) {
+        if (debug) fprintf(stderr, "[metalhlo] step %zu: %s\n", i, steps_[i].label.c_str());
+        const int st = steps_[i].run(c);
+        if (st != 0) {
+            error_ = "step " + std::to_string(i) + " (" + steps_[i].label + "): " + mhlo_cuda_last_error();
+            return st;
+        }
+    }
+    return 0;
+}
+
+std::vector<std::string> Executable::step_labels() const {
+    std::vector<std::string> l;
+    for (const Step& s : steps_) l.push_back(s.label);
+    return l;
+}
+
+}  // namespace mhlo
