@@ -522,18 +522,16 @@ class Parser {
         }
         error("unsupported attribute syntax");
     }
-    void maybe_type_suffix() {  // "1 : i64", "1.0 : f32"
+    void maybe_type_suffix() {  // "1 : i64", "1.0 : f32", "0 : index"; a tensor type after ':' belongs to the op
         size_t save = p_;
         skip();
         if (cur() == ':') {
             ++p_;
             skip();
             if (ident_char(cur())) {
-                size_t q = p_;
                 std::string w = ident();
                 DType d;
                 if (dtype_from_name(w, &d) || w == "index") return;
-                if (w == "tensor") { p_ = q; type(); return; }
             }
         }
         p_ = save;
@@ -975,6 +973,38 @@ class Parser {
         if (cur() == ':') {
             ++p_;
             signature(in_types, &op->result_types);
+        }
+        skip();
+        if (op->name == "reduce" && peek_word("reducer")) {
+            // jax prints the body after the type: reducer(%a: t, %b: t) (%c: t, %d: t) { ... }
+            word();
+            std::vector<int> args;
+            skip();
+            while (cur() == '(') {
+                ++p_;
+                skip();
+                while (cur() != ')') {
+                    std::string n = value_name();
+                    expect(':');
+                    TensorType t = type();
+                    skip();
+                    if (peek_word("loc")) { word(); skip_balanced('(', ')'); }
+                    int v = fn_->new_value(t, n);
+                    names_[n] = v;
+                    args.push_back(v);
+                    if (!accept(',')) break;
+                    skip();
+                }
+                expect(')');
+                skip();
+            }
+            auto r = region();
+            // the printed order is (lhs0, rhs0) (lhs1, rhs1): block arguments are lhs0, lhs1, rhs0, rhs1
+            std::vector<int> ordered;
+            for (size_t k = 0; k < args.size(); k += 2) ordered.push_back(args[k]);
+            for (size_t k = 1; k < args.size(); k += 2) ordered.push_back(args[k]);
+            r->args = ordered;
+            op->regions.push_back(r);
         }
         if (have_dense) {
             if (op->result_types.empty()) fail_parse("constant without a type");

@@ -752,7 +752,7 @@ bool fuse_attention(Function& f) {
                 if (!single_use_or_softmax_input(s)) { ok = false; break; }
                 double c;
                 if (o->name == "select" && is_causal_predicate(g, o->operands[0], pt.rank()) && scalar_constant(g, o->operands[2], &c) &&
-                    (c <= -1e9 || std::isinf(c))) { causal = true; s = o->operands[1]; continue; }
+                    (c <= -1e4 || std::isinf(c))) { causal = true; s = o->operands[1]; continue; }
                 if (o->name == "multiply" && scalar_constant(g, o->operands[1], &c)) { scale *= c; s = o->operands[0]; continue; }
                 if (o->name == "multiply" && scalar_constant(g, o->operands[0], &c)) { scale *= c; s = o->operands[1]; continue; }
                 if (o->name == "divide" && scalar_constant(g, o->operands[1], &c)) { scale /= c; s = o->operands[0]; continue; }

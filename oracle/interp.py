@@ -1,0 +1,1077 @@
+"""numpy interpreter for StableHLO text — TEST INFRASTRUCTURE ONLY (the module-level parity oracle).
+
+It evaluates a module the way the reference lowers it, op by op (unfused semantics; the reference requires every
+optimisation level to agree with that, Tests/MetalHLOTests/Conformance/OptimizationCorrectnessTests.swift:19-24):
+floating-point values are carried in float64 whatever their declared element type, integers in their own numpy
+dtype so that wrap-around and truncation are exact. Semantics follow
+Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift:814-1144 (dot_general, broadcast_in_dim, reduce/argmax),
+Sources/MetalHLOCore/Compiler/CodeGenerator.swift:1012-1075 (convert = C cast), :1133-1292 (gather with clamped start
+indices), :1977-2005 (iota) and the fused custom-call handlers in Compiler/CustomCallHandlers.swift.
+
+The parser here is independent of the product's C++ parser on purpose: both read the same dialect
+(Sources/MetalHLOCore/Parser/Parser.swift) and the tests compare their results.
+
+Pinned against the reference's vendored StableHLO interpreter suite
+(Tests/MetalHLOTests/Conformance/StableHLO/interpret/*.mlir, `check.expect_*` goldens) by tests/test_interp_suite.py.
+"""
+from __future__ import annotations
+
+import json
+import math
+import re
+
+import numpy as np
+
+try:
+    import ml_dtypes
+
+    _BF16 = np.dtype(ml_dtypes.bfloat16)
+except Exception:  # pragma: no cover
+    _BF16 = None
+
+INT_DTYPES = {"i1": np.bool_, "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "ui8": np.uint8,
+              "ui16": np.uint16, "ui32": np.uint32, "ui64": np.uint64, "si8": np.int8, "si16": np.int16,
+              "si32": np.int32, "si64": np.int64}
+FLOAT_DTYPES = ("f16", "f32", "f64", "bf16")
+
+
+class Unsupported(Exception):
+    pass
+
+
+class TType:
+    def __init__(self, shape, dtype):
+        self.shape, self.dtype = tuple(shape), dtype
+
+    @property
+    def is_float(self):
+        return self.dtype in FLOAT_DTYPES
+
+    def np_dtype(self):
+        return np.float64 if self.is_float else INT_DTYPES[self.dtype]
+
+    def __repr__(self):
+        return "tensor<" + "x".join([str(d) for d in self.shape] + [self.dtype]) + ">"
+
+
+def round_to(arr, dtype):
+    """Rounds float64 values to the precision of a storage dtype (used when a convert asks for it)."""
+    if dtype == "f32":
+        return arr.astype(np.float32).astype(np.float64)
+    if dtype == "f16":
+        with np.errstate(over="ignore"):
+            return arr.astype(np.float16).astype(np.float64)
+    if dtype == "bf16" and _BF16 is not None:
+        return arr.astype(np.float32).astype(_BF16).astype(np.float64)
+    return arr
+
+
+class Scanner:
+    def __init__(self, text):
+        self.s, self.p = text, 0
+
+    def ws(self):
+        s = self.s
+        while self.p < len(s):
+            if s[self.p].isspace():
+                self.p += 1
+            elif s.startswith("//", self.p):
+                e = s.find("\n", self.p)
+                self.p = len(s) if e < 0 else e
+            else:
+                break
+
+    def peek(self, n=1):
+        self.ws()
+        return self.s[self.p:self.p + n]
+
+    def accept(self, tok):
+        self.ws()
+        if self.s.startswith(tok, self.p):
+            self.p += len(tok)
+            return True
+        return False
+
+    def expect(self, tok):
+        if not self.accept(tok):
+            raise SyntaxError(f"expected {tok!r} at {self.s[self.p:self.p + 40]!r}")
+
+    _ident = re.compile(r"[A-Za-z_][A-Za-z0-9_.$]*")
+    _value = re.compile(r"%[A-Za-z0-9_.$\-]+(#\d+)?")
+    _number = re.compile(r"[-+]?(0x[0-9a-fA-F]+|inf|nan|NaN|(\d+\.?\d*([eE][-+]?\d+)?|\.\d+([eE][-+]?\d+)?))")
+
+    def ident(self):
+        self.ws()
+        m = self._ident.match(self.s, self.p)
+        if not m:
+            raise SyntaxError(f"expected identifier at {self.s[self.p:self.p + 40]!r}")
+        self.p = m.end()
+        return m.group()
+
+    def value(self):
+        self.ws()
+        m = self._value.match(self.s, self.p)
+        if not m:
+            raise SyntaxError(f"expected SSA value at {self.s[self.p:self.p + 40]!r}")
+        self.p = m.end()
+        return m.group()
+
+    def number_token(self):
+        self.ws()
+        for kw in ("true", "false"):
+            if self.s.startswith(kw, self.p):
+                self.p += len(kw)
+                return kw
+        m = self._number.match(self.s, self.p)
+        if not m:
+            raise SyntaxError(f"expected number at {self.s[self.p:self.p + 40]!r}")
+        self.p = m.end()
+        return m.group()
+
+    def string(self):
+        self.ws()
+        assert self.s[self.p] == '"'
+        out, p = [], self.p + 1
+        while self.s[p] != '"':
+            if self.s[p] == "\\":
+                nxt = self.s[p + 1]
+                if nxt in "\"\\":
+                    out.append(nxt); p += 2
+                elif nxt == "n":
+                    out.append("\n"); p += 2
+                elif nxt == "t":
+                    out.append("\t"); p += 2
+                else:
+                    out.append(chr(int(self.s[p + 1:p + 3], 16))); p += 3
+            else:
+                out.append(self.s[p]); p += 1
+        self.p = p + 1
+        return "".join(out)
+
+    def balanced(self, open_c, close_c):
+        self.ws()
+        assert self.s[self.p] == open_c, self.s[self.p:self.p + 30]
+        depth, p = 0, self.p
+        while True:
+            c = self.s[p]
+            if c == '"':
+                q = p + 1
+                while self.s[q] != '"':
+                    q += 2 if self.s[q] == "\\" else 1
+                p = q
+            elif c == open_c:
+                depth += 1
+            elif c == close_c:
+                depth -= 1
+                if depth == 0:
+                    body = self.s[self.p + 1:p]
+                    self.p = p + 1
+                    return body
+            p += 1
+
+    def type(self):
+        self.ws()
+        if self.peek() == "!":
+            self.ident_bang()
+            return TType((), "i1")
+        w = self.ident()
+        if w == "tuple":
+            body = self.balanced("<", ">")
+            return Scanner(body).type() if body.strip() else TType((), "i1")
+        if w != "tensor":
+            if w in INT_DTYPES or w in FLOAT_DTYPES:
+                return TType((), w)
+            raise Unsupported(f"type {w}")
+        body = self.balanced("<", ">").split(",")[0].strip()
+        parts = body.split("x")
+        if any(p in ("?", "*") for p in parts):
+            raise Unsupported("dynamic shape")
+        dt = parts[-1]
+        if dt.startswith("complex") or (dt not in INT_DTYPES and dt not in FLOAT_DTYPES):
+            raise Unsupported(f"element type {dt}")
+        return TType([int(p) for p in parts[:-1]], dt)
+
+    def ident_bang(self):
+        self.p += 1
+        self.ident()
+        if self.peek() == "<":
+            self.balanced("<", ">")
+
+
+def parse_number(tok, ttype):
+    if tok == "true":
+        return True
+    if tok == "false":
+        return False
+    neg = tok.startswith("-")
+    body = tok.lstrip("+-")
+    if body.startswith("0x"):
+        bits = int(body, 16)
+        if ttype.is_float:
+            width = {"f16": 2, "bf16": 2, "f32": 4, "f64": 8}[ttype.dtype]
+            raw = bits.to_bytes(width, "little")
+            if ttype.dtype == "bf16":
+                return float(np.frombuffer(raw + b"", dtype=np.uint16).astype(np.uint32).__lshift__(16).view(np.float32)[0])
+            return float(np.frombuffer(raw, dtype={"f16": np.float16, "f32": np.float32, "f64": np.float64}[ttype.dtype])[0])
+        return -bits if neg else bits
+    if body in ("inf",):
+        return -math.inf if neg else math.inf
+    if body.lower() == "nan":
+        return math.nan
+    if ttype.is_float:
+        return float(tok)
+    return int(float(tok)) if ("." in tok or "e" in tok.lower()) else int(tok)
+
+
+def dense_value(body, ttype):
+    """Array of a dense<...> body for a tensor type (floats as float64, ints in their dtype)."""
+    body = body.strip()
+    npdt = ttype.np_dtype()
+    n = int(np.prod(ttype.shape, dtype=np.int64)) if ttype.shape else 1
+    if body == "":
+        return np.zeros(ttype.shape, dtype=npdt)
+    if body.startswith('"'):
+        raw = bytes.fromhex(Scanner(body).string()[2:])
+        store = {"f16": np.float16, "f32": np.float32, "f64": np.float64}.get(ttype.dtype, INT_DTYPES.get(ttype.dtype))
+        if ttype.dtype == "bf16":
+            arr = (np.frombuffer(raw, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        elif ttype.dtype == "i1":
+            arr = np.frombuffer(raw, dtype=np.uint8) != 0
+        else:
+            arr = np.frombuffer(raw, dtype=store)
+        if arr.size == 1 and n != 1:
+            arr = np.full(ttype.shape, arr[0])
+        return arr.reshape(ttype.shape).astype(npdt)
+    if "(" in body:
+        raise Unsupported("complex constant")
+    toks = re.findall(r"true|false|[-+]?(?:0x[0-9a-fA-F]+|inf|nan|NaN|\d+\.?\d*(?:[eE][-+]?\d+)?|\.\d+(?:[eE][-+]?\d+)?)", body)
+    vals = [parse_number(t, ttype) for t in toks]
+    if not ttype.is_float and ttype.dtype != "i1":
+        info = np.iinfo(npdt)
+        vals = [((v - info.min) % (info.max - info.min + 1)) + info.min if not info.min <= v <= info.max else v for v in vals]
+    if len(vals) == 1 and (n != 1 or "[" not in body):
+        return np.full(ttype.shape, vals[0], dtype=npdt)
+    return np.array(vals, dtype=npdt).reshape(ttype.shape)
+
+
+class Op:
+    __slots__ = ("name", "operands", "results", "types", "attrs", "regions", "in_types")
+
+    def __init__(self):
+        self.name, self.operands, self.results, self.types, self.attrs, self.regions, self.in_types = "", [], [], [], {}, [], []
+
+
+class Region:
+    def __init__(self):
+        self.args, self.ops = [], []
+
+
+class Func:
+    def __init__(self):
+        self.name, self.args, self.arg_types, self.ops, self.result_types = "", [], [], [], []
+
+
+class ModuleParser(Scanner):
+    def parse(self):
+        funcs = []
+        self.ws()
+        if self.accept("module"):
+            self.ws()
+            if self.peek() == "@":
+                self.p += 1
+                self.ident()
+            elif self.peek() == '"':
+                self.string()
+            if self.accept("attributes"):
+                self.balanced("{", "}")
+            self.expect("{")
+        while True:
+            self.ws()
+            if self.p >= len(self.s) or self.peek() == "}":
+                break
+            if self.s.startswith("func.func", self.p):
+                funcs.append(self.func())
+            else:
+                e = self.s.find("\n", self.p)
+                self.p = len(self.s) if e < 0 else e
+        return funcs
+
+    def func(self):
+        self.expect("func.func")
+        for vis in ("private", "public"):
+            self.accept(vis)
+        self.expect("@")
+        f = Func()
+        f.name = self.ident()
+        self.expect("(")
+        while self.peek() != ")":
+            f.args.append(self.value())
+            self.expect(":")
+            f.arg_types.append(self.type())
+            if self.peek() == "{":
+                self.balanced("{", "}")
+            if self.peek(3) == "loc":
+                self.ident(); self.balanced("(", ")")
+            if not self.accept(","):
+                break
+        self.expect(")")
+        if self.accept("->"):
+            if self.peek() == "(":
+                self.p += 1
+                while self.peek() != ")":
+                    f.result_types.append(self.type())
+                    if self.peek() == "{":
+                        self.balanced("{", "}")
+                    if not self.accept(","):
+                        break
+                self.expect(")")
+            else:
+                f.result_types.append(self.type())
+                if self.peek() == "{":
+                    save = self.p
+                    body = self.balanced("{", "}")
+                    if re.match(r"\s*(%|return|func\.return|stablehlo\.|check\.|chlo\.|\^)", body) or body.strip() == "":
+                        self.p = save
+        if self.accept("attributes"):
+            self.balanced("{", "}")
+        self.expect("{")
+        f.ops = self.block()[1]
+        self.expect("}")
+        return f
+
+    def block(self):
+        args, ops = [], []
+        while True:
+            self.ws()
+            if self.peek() == "}":
+                return args, ops
+            if self.peek() == "^":
+                self.p += 1
+                self.ident()
+                if self.accept("("):
+                    while self.peek() != ")":
+                        name = self.value()
+                        self.expect(":")
+                        t = self.type()
+                        if self.peek(3) == "loc":
+                            self.ident(); self.balanced("(", ")")
+                        args.append((name, t))
+                        if not self.accept(","):
+                            break
+                    self.expect(")")
+                self.expect(":")
+                continue
+            ops.append(self.operation())
+
+    def region(self):
+        self.expect("{")
+        r = Region()
+        r.args, r.ops = self.block()
+        self.expect("}")
+        return r
+
+    def operation(self):
+        op = Op()
+        names, declared = [], None
+        if self.peek() == "%":
+            while True:
+                n = self.value()
+                m = re.match(r":(\d+)", self.s[self.p:])
+                if m:
+                    declared = int(m.group(1))
+                    self.p += m.end()
+                names.append(n)
+                if not self.accept(","):
+                    break
+            self.expect("=")
+        self.ws()
+        if self.peek() == '"':
+            op.name = self.string()
+            self.generic(op)
+        else:
+            op.name = self.ident()
+            self.pretty(op)
+        if self.peek(3) == "loc":
+            self.ident(); self.balanced("(", ")")
+        for k in ("stablehlo.", "chlo.", "func.", "mhlo."):
+            if op.name.startswith(k):
+                op.name = op.name[len(k):]
+        if declared:
+            op.results = [f"{names[0]}#{i}" for i in range(declared)]
+        else:
+            op.results = names
+        return op
+
+    def operands(self, op, close):
+        while self.peek() != close:
+            op.operands.append(self.value())
+            if not self.accept(","):
+                break
+        self.expect(close)
+
+    def signature(self, op):
+        ins, outs = [], []
+        if self.peek() == "(":
+            self.p += 1
+            while self.peek() != ")":
+                ins.append(self.type())
+                if not self.accept(","):
+                    break
+            self.expect(")")
+            self.expect("->")
+            if self.peek() == "(":
+                self.p += 1
+                while self.peek() != ")":
+                    outs.append(self.type())
+                    if not self.accept(","):
+                        break
+                self.expect(")")
+            else:
+                outs.append(self.type())
+        else:
+            ts = [self.type()]
+            while self.accept(","):
+                ts.append(self.type())
+            if self.accept("->"):
+                ins = ts
+                outs = [self.type()]
+            else:
+                ins, outs = ts, [ts[-1]]
+        op.in_types, op.types = ins, outs
+
+    def attr(self):
+        self.ws()
+        c = self.peek()
+        if c == '"':
+            v = self.string()
+            self.type_suffix()
+            return v
+        if c == "[":
+            self.p += 1
+            out = []
+            while self.peek() != "]":
+                out.append(self.attr())
+                if not self.accept(","):
+                    break
+            self.expect("]")
+            return out
+        if c == "{":
+            return self.attr_dict("{", "}")
+        if c == "#":
+            self.p += 1
+            tag = self.ident()
+            if self.peek() != "<":
+                return tag
+            save = self.p
+            body = self.balanced("<", ">")
+            if "=" not in body:
+                return body.split()[-1] if body.split() else tag
+            self.p = save
+            return self.attr_dict("<", ">")
+        if self.s.startswith("dense", self.p):
+            self.p += 5
+            body = self.balanced("<", ">")
+            self.expect(":")
+            t = self.type()
+            return ("dense", body, t)
+        if self.s.startswith("array", self.p):
+            self.p += 5
+            body = self.balanced("<", ">")
+            vals = body.split(":", 1)[1] if ":" in body else ""
+            return [int(x) for x in vals.replace(" ", "").split(",") if x]
+        if c == "@":
+            self.p += 1
+            return self.ident()
+        m = re.match(r"true|false|unit", self.s[self.p:])
+        if m and not (self.s[self.p + m.end()].isalnum() or self.s[self.p + m.end()] == "_"):
+            self.p += m.end()
+            return m.group() != "false"
+        if c.isdigit() or c in "-+":
+            tok = self.number_token()
+            self.type_suffix()
+            if tok.lower().lstrip("+-").startswith("0x"):
+                return int(tok, 16)
+            return float(tok) if ("." in tok or "e" in tok.lower() or "inf" in tok or "nan" in tok.lower()) else int(tok)
+        w = self.ident()
+        if w in ("tensor", "tuple"):
+            self.balanced("<", ">")
+            return w
+        if self.peek() == "<":
+            self.balanced("<", ">")
+        return w
+
+    def type_suffix(self):
+        # "1 : i64" / "1.0 : f32" / "0 : index"; a tensor type after ':' belongs to the operation, not the number
+        m = re.match(r"\s*:\s*(index|[su]?i\d+|bf16|f\d+)\b", self.s[self.p:])
+        if m:
+            self.p += m.end()
+
+    def attr_dict(self, o, c):
+        self.expect(o)
+        d = {}
+        while self.peek() != c:
+            key = self.string() if self.peek() == '"' else self.ident()
+            if self.accept("="):
+                d[key] = self.attr()
+            else:
+                d[key] = True
+            if not self.accept(","):
+                break
+        self.expect(c)
+        return d
+
+    def generic(self, op):
+        self.expect("(")
+        self.operands(op, ")")
+        if self.peek(2) == "<{":
+            self.p += 1
+            op.attrs.update(self.attr_dict("{", "}"))
+            self.expect(">")
+        if self.peek() == "(":
+            save = self.p
+            self.p += 1
+            if self.peek() == "{":
+                while True:
+                    op.regions.append(self.region())
+                    if not self.accept(","):
+                        break
+                self.expect(")")
+            else:
+                self.p = save
+        if self.peek() == "{":
+            op.attrs.update(self.attr_dict("{", "}"))
+        self.expect(":")
+        self.signature(op)
+
+    def pretty(self, op):
+        kw = []
+        name = op.name.split(".")[-1]
+        if name == "reduce" and self.accept("("):
+            ins, inits = [], []
+            while True:
+                ins.append(self.value())
+                self.expect("init")
+                self.expect(":")
+                inits.append(self.value())
+                self.expect(")")
+                if self.accept(","):
+                    self.expect("(")
+                    continue
+                break
+            op.operands = ins + inits
+        while True:
+            self.ws()
+            c = self.peek()
+            if c in (":", "{", "}", ""):
+                break
+            if c == ",":
+                self.p += 1
+            elif c == "%":
+                op.operands.append(self.value())
+            elif c == "@":
+                self.p += 1
+                op.attrs["call_target_name"] = self.ident()
+                if self.accept("("):
+                    self.operands(op, ")")
+            elif c == "[":
+                body = self.balanced("[", "]")
+                if ":" in body:
+                    st, li, sd = [], [], []
+                    for part in body.split(","):
+                        f = [int(x) for x in part.strip().split(":")]
+                        st.append(f[0]); li.append(f[1]); sd.append(f[2] if len(f) > 2 else 1)
+                    op.attrs.update(start_indices=st, limit_indices=li, strides=sd)
+                else:
+                    op.attrs["indices"] = [int(x) for x in body.split(",") if x.strip()]
+            elif c == "(":
+                self.balanced("(", ")")
+            elif self.peek(2) == "<{":
+                self.p += 1
+                op.attrs.update(self.attr_dict("{", "}"))
+                self.expect(">")
+            elif self.s.startswith("dense", self.p):
+                self.p += 5
+                op.attrs["_dense"] = self.balanced("<", ">")
+            elif c == "#":
+                v = self.attr()
+                if isinstance(v, dict):
+                    op.attrs.update(v)
+            elif c == '"':
+                kw.append(self.string())
+            else:
+                w = self.ident()
+                if w == "applies":
+                    op.attrs["reducer"] = self.ident().split(".")[-1]
+                elif w == "across":
+                    pass
+                elif w in ("reducer", "cond", "do"):
+                    while self.peek() == "(":
+                        self.balanced("(", ")")
+                    if self.peek() == "{":
+                        op.regions.append(self.region())
+                elif self.accept("="):
+                    v = self.attr()
+                    self.ws()
+                    if self.s.startswith("x", self.p) and not (self.s[self.p + 1].isalnum() or self.s[self.p + 1] == "_"):
+                        self.p += 1
+                        op.attrs[w + ".lhs"], op.attrs[w + ".rhs"] = v, self.attr()
+                    else:
+                        op.attrs[w] = v
+                else:
+                    kw.append(w)
+        if self.peek() == "{":
+            save = self.p
+            body = self.balanced("{", "}")
+            self.p = save
+            if re.match(r"\s*(\^|%|stablehlo\.|return|func\.return)", body):
+                op.regions.append(self.region())
+            else:
+                op.attrs.update(self.attr_dict("{", "}"))
+        if name in ("return",) or op.name in ("return", "func.return", "stablehlo.return"):
+            if self.accept(":"):
+                self.signature(op)
+            return
+        if self.accept(":"):
+            self.signature(op)
+        self.ws()
+        if name == "reduce" and self.s.startswith("reducer", self.p):
+            self.ident()
+            r_args = []
+            while self.peek() == "(":
+                self.p += 1
+                while self.peek() != ")":
+                    an = self.value()
+                    self.expect(":")
+                    r_args.append((an, self.type()))
+                    if not self.accept(","):
+                        break
+                self.expect(")")
+            r = self.region()
+            r.args = r_args[0::2] + r_args[1::2]
+            op.regions.append(r)
+        op.attrs["_kw"] = kw
+
+
+def parse(text):
+    return ModuleParser(text).parse()
+
+
+# ---- evaluation ------------------------------------------------------------------------------------------------------
+
+_DIRS = {"EQ": np.equal, "NE": np.not_equal, "LT": np.less, "LE": np.less_equal, "GT": np.greater, "GE": np.greater_equal}
+
+
+def _ints(v):
+    if v is None:
+        return []
+    if isinstance(v, (int, np.integer)):
+        return [int(v)]
+    return [int(x) for x in v]
+
+
+def _wrap(arr, ttype):
+    """Brings a numpy result to the carrier dtype of its declared type."""
+    if ttype.is_float:
+        return np.asarray(arr, dtype=np.float64)
+    return np.asarray(arr).astype(ttype.np_dtype())
+
+
+def _float_to_int(arr, ttype):
+    # C cast: toward zero; out-of-range and NaN follow the device conversion (saturate, NaN -> 0)
+    dt = ttype.np_dtype()
+    if dt == np.bool_:
+        return arr != 0
+    info = np.iinfo(dt)
+    a = np.nan_to_num(np.trunc(arr), nan=0.0, posinf=float(info.max), neginf=float(info.min))
+    return np.clip(a, float(info.min), float(info.max)).astype(dt)
+
+
+class Interpreter:
+    def __init__(self, round_floats: bool = False):
+        self.round_floats = round_floats
+
+    def run(self, func, inputs):
+        env = {}
+        for name, t, x in zip(func.args, func.arg_types, inputs):
+            env[name] = self._input(x, t)
+        return self._run_ops(func.ops, env)
+
+    def _input(self, x, t):
+        if hasattr(x, "detach"):
+            x = x.detach().cpu()
+            x = x.double().numpy() if x.is_floating_point() else x.numpy()
+        a = np.asarray(x)
+        a = a.astype(np.float64) if t.is_float else a.astype(t.np_dtype())
+        assert a.shape == t.shape, (a.shape, t)
+        return a
+
+    def _run_ops(self, ops, env):
+        for op in ops:
+            if op.name in ("return", "func.return", "stablehlo.return"):
+                return [env[v] for v in op.operands]
+            if op.name.startswith("check."):
+                continue
+            outs = self.eval(op, [env[v] if v in env else env[v + "#0"] for v in op.operands], env)
+            if not isinstance(outs, (list, tuple)):
+                outs = [outs]
+            for name, t, v in zip(op.results, op.types, outs):
+                v = _wrap(v, t)
+                if self.round_floats and t.is_float:
+                    v = round_to(v, t.dtype)
+                env[name] = v.reshape(t.shape)
+        return []
+
+    def eval(self, op, a, env):
+        n, t = op.name, (op.types[0] if op.types else None)
+        A = op.attrs
+        it = op.in_types
+        f = getattr(self, "op_" + n, None)
+        if f is not None:
+            return f(op, a, t)
+        un = {"negate": np.negative, "abs": np.abs, "exponential": np.exp, "exponential_minus_one": np.expm1, "log": np.log,
+              "log_plus_one": np.log1p, "sqrt": np.sqrt, "rsqrt": lambda x: 1.0 / np.sqrt(x), "cbrt": np.cbrt, "tanh": np.tanh,
+              "logistic": lambda x: 1.0 / (1.0 + np.exp(-x)), "sine": np.sin, "cosine": np.cos, "tan": np.tan, "floor": np.floor,
+              "ceil": np.ceil, "round_nearest_even": np.rint, "sign": np.sign, "is_finite": np.isfinite,
+              "round_nearest_afz": lambda x: np.sign(x) * np.floor(np.abs(x) + 0.5)}
+        if n in un:
+            with np.errstate(all="ignore"):
+                return un[n](a[0])
+        if n == "not":
+            return np.logical_not(a[0]) if a[0].dtype == np.bool_ else np.invert(a[0])
+        if n == "popcnt":
+            bits = a[0].dtype.itemsize * 8
+            u = a[0].astype(f"uint{bits}")
+            return sum(((u >> i) & 1) for i in range(bits)).astype(a[0].dtype)
+        if n == "count_leading_zeros":
+            bits = a[0].dtype.itemsize * 8
+            u = a[0].astype(f"uint{bits}").astype(np.uint64)
+            out = np.full(u.shape, bits, dtype=np.int64)
+            for i in range(bits):
+                out = np.where((u >> np.uint64(i)) != 0, bits - 1 - i, out)
+            return out
+        with np.errstate(all="ignore"):
+            if n == "add":
+                return np.logical_or(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] + a[1]
+            if n == "subtract":
+                return a[0] - a[1]
+            if n == "multiply":
+                return np.logical_and(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] * a[1]
+            if n == "divide":
+                if t.is_float:
+                    return a[0] / a[1]
+                q = np.where(a[1] == 0, 1, a[1])
+                r = np.trunc(a[0].astype(np.float64) / q.astype(np.float64)) if a[0].dtype.itemsize < 8 else (np.abs(a[0]) // np.abs(q)) * np.sign(a[0]) * np.sign(q)
+                return np.where(a[1] == 0, -1, r)
+            if n == "remainder":
+                if t.is_float:
+                    return np.fmod(a[0], a[1])
+                q = np.where(a[1] == 0, 1, a[1])
+                return np.where(a[1] == 0, a[0], np.fmod(a[0], q))
+            if n == "maximum":
+                return np.maximum(a[0], a[1])
+            if n == "minimum":
+                return np.minimum(a[0], a[1])
+            if n == "power":
+                if t.is_float:
+                    return np.power(a[0], a[1])
+                base, e = a[0].astype(object), a[1].astype(object)
+                info = np.iinfo(t.np_dtype())
+                out = np.empty(base.shape, dtype=object)
+                for idx in np.ndindex(base.shape):
+                    b_, e_ = int(base[idx]), int(e[idx])
+                    if e_ < 0:
+                        v = 1 if b_ == 1 else ((-1 if e_ % 2 else 1) if b_ == -1 else 0)
+                    else:
+                        v = pow(b_, e_, 1 << 64)
+                    v &= (1 << (8 * np.dtype(t.np_dtype()).itemsize)) - 1
+                    if info.min < 0 and v > info.max:
+                        v -= 1 << (8 * np.dtype(t.np_dtype()).itemsize)
+                    out[idx] = v
+                return out.astype(t.np_dtype())
+            if n == "atan2":
+                return np.arctan2(a[0], a[1])
+            if n == "and":
+                return np.logical_and(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] & a[1]
+            if n == "or":
+                return np.logical_or(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] | a[1]
+            if n == "xor":
+                return np.logical_xor(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] ^ a[1]
+            if n in ("shift_left", "shift_right_arithmetic", "shift_right_logical"):
+                bits = a[0].dtype.itemsize * 8
+                sh = a[1].astype(np.int64)
+                big = (sh >= bits) | (sh < 0)
+                s = np.where(big, 0, sh).astype(a[0].dtype)
+                if n == "shift_left":
+                    return np.where(big, 0, a[0] << s)
+                if n == "shift_right_arithmetic":
+                    return np.where(big, np.where(a[0] < 0, -1, 0), a[0] >> s).astype(a[0].dtype)
+                u = a[0].astype(f"uint{bits}")
+                return np.where(big, 0, u >> s.astype(f"uint{bits}")).astype(a[0].dtype)
+        raise Unsupported(f"op {n}")
+
+    # -- structural ops
+    def op_constant(self, op, a, t):
+        v = op.attrs.get("value")
+        if v is not None:
+            return dense_value(v[1], t)
+        return dense_value(op.attrs["_dense"], t)
+
+    def op_iota(self, op, a, t):
+        d = int(op.attrs.get("dim", op.attrs.get("iota_dimension", 0)))
+        shape = [1] * len(t.shape)
+        shape[d] = t.shape[d]
+        return np.broadcast_to(np.arange(t.shape[d]).reshape(shape), t.shape)
+
+    def op_convert(self, op, a, t):
+        src = op.in_types[0] if op.in_types else None
+        x = a[0]
+        if t.is_float:
+            return round_to(x.astype(np.float64), t.dtype)  # a convert is a real rounding point
+        if x.dtype == np.float64:
+            return _float_to_int(x, t)
+        if t.dtype == "i1":
+            return x != 0
+        return x.astype(t.np_dtype())
+
+    def op_compare(self, op, a, t):
+        d = op.attrs.get("comparison_direction")
+        if d is None:
+            d = [k for k in op.attrs.get("_kw", []) if k in _DIRS][0]
+        return _DIRS[d](a[0], a[1])
+
+    def op_select(self, op, a, t):
+        return np.where(a[0], a[1], a[2])
+
+    def op_clamp(self, op, a, t):
+        return np.minimum(np.maximum(a[1], a[0]), a[2])
+
+    def op_broadcast_in_dim(self, op, a, t):
+        dims = _ints(op.attrs.get("dims", op.attrs.get("broadcast_dimensions")))
+        shape = [1] * len(t.shape)
+        for i, d in enumerate(dims):
+            shape[d] = a[0].shape[i]
+        return np.broadcast_to(a[0].reshape(shape), t.shape)
+
+    def op_reshape(self, op, a, t):
+        return a[0].reshape(t.shape)
+
+    def op_transpose(self, op, a, t):
+        return np.transpose(a[0], _ints(op.attrs.get("dims", op.attrs.get("permutation"))))
+
+    def op_reverse(self, op, a, t):
+        return np.flip(a[0], axis=tuple(_ints(op.attrs.get("dims", op.attrs.get("dimensions")))))
+
+    def op_slice(self, op, a, t):
+        st, li = _ints(op.attrs["start_indices"]), _ints(op.attrs["limit_indices"])
+        sd = _ints(op.attrs.get("strides")) or [1] * len(st)
+        return a[0][tuple(slice(s, l, k) for s, l, k in zip(st, li, sd))]
+
+    def op_concatenate(self, op, a, t):
+        return np.concatenate(a, axis=int(op.attrs.get("dim", op.attrs.get("dimension", 0))))
+
+    def op_pad(self, op, a, t):
+        lo = _ints(op.attrs.get("low", op.attrs.get("edge_padding_low")))
+        hi = _ints(op.attrs.get("high", op.attrs.get("edge_padding_high")))
+        inter = _ints(op.attrs.get("interior", op.attrs.get("interior_padding"))) or [0] * len(lo)
+        out = np.full(t.shape, a[1].reshape(()), dtype=a[0].dtype)
+        x = a[0]
+        src, dst = [], []
+        for d in range(x.ndim):
+            step = inter[d] + 1
+            first, count = 0, x.shape[d]
+            while count > 0 and lo[d] + first * step < 0:
+                first += 1; count -= 1
+            while count > 0 and lo[d] + (first + count - 1) * step >= t.shape[d]:
+                count -= 1
+            src.append(slice(first, first + count))
+            start = lo[d] + first * step
+            dst.append(slice(start, start + (count - 1) * step + 1 if count > 0 else start, step))
+        out[tuple(dst)] = x[tuple(src)]
+        return out
+
+    def op_dot(self, op, a, t):
+        return self._dot(a[0], a[1], [], [], [a[0].ndim - 1], [0], t)
+
+    def op_dot_general(self, op, a, t):
+        A = op.attrs
+        d = A.get("dot_dimension_numbers", A)
+        lb = _ints(d.get("lhs_batching_dimensions", A.get("batching_dims.lhs")))
+        rb = _ints(d.get("rhs_batching_dimensions", A.get("batching_dims.rhs")))
+        lc = _ints(d.get("lhs_contracting_dimensions", A.get("contracting_dims.lhs")))
+        rc = _ints(d.get("rhs_contracting_dimensions", A.get("contracting_dims.rhs")))
+        return self._dot(a[0], a[1], lb, rb, lc, rc, t)
+
+    def _dot(self, x, y, lb, rb, lc, rc, t):
+        lf = [d for d in range(x.ndim) if d not in lb and d not in lc]
+        rf = [d for d in range(y.ndim) if d not in rb and d not in rc]
+        xs = np.transpose(x, lb + lf + lc)
+        ys = np.transpose(y, rb + rc + rf)
+        B = int(np.prod([x.shape[d] for d in lb], dtype=np.int64))
+        M = int(np.prod([x.shape[d] for d in lf], dtype=np.int64))
+        K = int(np.prod([x.shape[d] for d in lc], dtype=np.int64))
+        N = int(np.prod([y.shape[d] for d in rf], dtype=np.int64))
+        if t.is_float:
+            out = np.matmul(xs.reshape(B, M, K).astype(np.float64), ys.reshape(B, K, N).astype(np.float64))
+        elif t.dtype == "i1":
+            out = np.matmul(xs.reshape(B, M, K).astype(np.int64), ys.reshape(B, K, N).astype(np.int64)) != 0
+        else:
+            out = np.matmul(xs.reshape(B, M, K).astype(np.int64), ys.reshape(B, K, N).astype(np.int64))
+        return out.reshape(t.shape)
+
+    def op_reduce(self, op, a, t):
+        n_in = len(a) // 2
+        dims = tuple(_ints(op.attrs.get("dimensions", op.attrs.get("dims"))))
+        red = op.attrs.get("reducer")
+        if red is None and op.regions:
+            red = self._classify(op.regions[0])
+        x, init = a[0], a[n_in]
+        if red in ("argmax", "argmin"):
+            assert n_in == 2 and len(dims) == 1
+            axis = dims[0]
+            xv = np.where(np.isnan(x), np.inf if red == "argmax" else -np.inf, x) if x.dtype == np.float64 else x
+            idx = (np.argmax if red == "argmax" else np.argmin)(xv, axis=axis)
+            val = np.take_along_axis(x, np.expand_dims(idx, axis), axis=axis).squeeze(axis)
+            return [val, idx]
+        fns = {"add": np.add, "maximum": np.maximum, "minimum": np.minimum, "multiply": np.multiply,
+               "and": np.logical_and if x.dtype == np.bool_ else np.bitwise_and,
+               "or": np.logical_or if x.dtype == np.bool_ else np.bitwise_or,
+               "xor": np.logical_xor if x.dtype == np.bool_ else np.bitwise_xor}
+        if red not in fns:
+            raise Unsupported(f"reducer {red}")
+        fn = fns[red]
+        if x.dtype == np.bool_ and red in ("add", "multiply"):
+            fn = np.logical_or if red == "add" else np.logical_and
+        with np.errstate(all="ignore"):
+            out = fn.reduce(x, axis=dims) if x.size or True else None
+            out = fn(out, init.reshape(()).astype(out.dtype) if hasattr(out, "dtype") else init)
+        return out
+
+    @staticmethod
+    def _classify(region):
+        names = [o.name.split(".")[-1] for o in region.ops]
+        if "select" in names and "compare" in names:
+            cmp = [o for o in region.ops if o.name.endswith("compare")][0]
+            d = cmp.attrs.get("comparison_direction") or [k for k in cmp.attrs.get("_kw", []) if k in _DIRS][0]
+            return "argmax" if d in ("GT", "GE") else "argmin"
+        for n in names:
+            if n in ("add", "maximum", "minimum", "multiply", "and", "or", "xor"):
+                return n
+        return "unknown"
+
+    def op_gather(self, op, a, t):
+        A = op.attrs
+        d = A.get("dimension_numbers", A)
+        offset_dims = _ints(d.get("offset_dims"))
+        collapsed = _ints(d.get("collapsed_slice_dims"))
+        ob = _ints(d.get("operand_batching_dims"))
+        sb = _ints(d.get("start_indices_batching_dims"))
+        sim = _ints(d.get("start_index_map"))
+        ivd = int(d.get("index_vector_dim"))
+        ss = _ints(A.get("slice_sizes"))
+        operand, idx = a[0], a[1].astype(np.int64)
+        if ivd == idx.ndim:
+            idx = idx[..., None]
+        idx = np.moveaxis(idx, ivd, -1)  # [...batch, len(sim)]
+        batch_shape = idx.shape[:-1]
+        out = np.empty(t.shape, dtype=operand.dtype)
+        batch_dims_out = [d_ for d_ in range(len(t.shape)) if d_ not in offset_dims]
+        kept = [d_ for d_ in range(operand.ndim) if d_ not in collapsed and d_ not in ob]
+        # position of each batching dim inside the batch coordinates (index_vector_dim removed)
+        sb_pos = [b - (1 if b > ivd else 0) for b in sb]
+        for bidx in np.ndindex(*batch_shape):
+            start = [0] * operand.ndim
+            for k, od in enumerate(sim):
+                v = int(idx[bidx + (k,)])
+                start[od] = min(max(v, 0), operand.shape[od] - ss[od])
+            for k, od in enumerate(ob):
+                start[od] = bidx[sb_pos[k]]
+            sl = tuple(slice(start[d_], start[d_] + ss[d_]) for d_ in range(operand.ndim))
+            piece = operand[sl]
+            piece = piece.reshape([ss[d_] for d_ in kept])
+            sel = [None] * len(t.shape)
+            for k, od in enumerate(batch_dims_out):
+                sel[od] = bidx[k]
+            for od in offset_dims:
+                sel[od] = slice(None)
+            out[tuple(sel)] = piece
+        return out
+
+    def op_dynamic_slice(self, op, a, t):
+        sizes = _ints(op.attrs.get("sizes", op.attrs.get("slice_sizes")))
+        x = a[0]
+        st = [min(max(int(a[1 + d].reshape(())), 0), x.shape[d] - sizes[d]) for d in range(x.ndim)]
+        return x[tuple(slice(s, s + n) for s, n in zip(st, sizes))]
+
+    def op_dynamic_update_slice(self, op, a, t):
+        x, u = a[0].copy(), a[1]
+        st = [min(max(int(a[2 + d].reshape(())), 0), x.shape[d] - u.shape[d]) for d in range(x.ndim)]
+        x[tuple(slice(s, s + n) for s, n in zip(st, u.shape))] = u
+        return x
+
+    def op_optimization_barrier(self, op, a, t):
+        return a
+
+    def op_custom_call(self, op, a, t):
+        target = op.attrs.get("call_target_name")
+        cfg = op.attrs.get("backend_config", "{}")
+        cfg = json.loads(cfg) if isinstance(cfg, str) and cfg.strip().startswith("{") else (cfg if isinstance(cfg, dict) else {})
+        x = a[0]
+        if target == "fused_layer_norm":
+            eps = float(cfg.get("eps", 1e-5))
+            mean = x.mean(-1, keepdims=True)
+            var = ((x - mean) ** 2).mean(-1, keepdims=True)
+            y = (x - mean) / np.sqrt(var + eps)
+            if len(a) > 1:
+                y = y * a[1]
+            if len(a) > 2:
+                y = y + a[2]
+            return y
+        if target == "fused_rms_norm":
+            eps = float(cfg.get("eps", 1e-5))
+            y = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+            return y * a[1] if len(a) > 1 else y
+        if target == "fused_softmax":
+            ax = int(cfg.get("axis", -1))
+            e = np.exp(x - x.max(ax, keepdims=True))
+            return e / e.sum(ax, keepdims=True)
+        if target == "fused_gelu":
+            if cfg.get("approximate", True):
+                return 0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+            return 0.5 * x * (1 + np.vectorize(math.erf)(x / math.sqrt(2)))
+        if target == "fused_silu":
+            return x / (1 + np.exp(-x))
+        if target == "fused_scaled_dot_product_attention":
+            q, k, v = a[0], a[1], a[2]
+            s = np.einsum("...qd,...kd->...qk", q, k) * float(cfg.get("scale", 1.0))
+            if cfg.get("has_mask") and len(a) > 3:
+                s = s + a[3]
+            if cfg.get("is_causal"):
+                sq, sk = s.shape[-2:]
+                s = np.where(np.arange(sk)[None, :] <= np.arange(sq)[:, None] + (sk - sq), s, -np.inf)
+            p = np.exp(s - s.max(-1, keepdims=True))
+            p = p / p.sum(-1, keepdims=True)
+            return np.einsum("...qk,...kd->...qd", p, v)
+        if target == "fused_matmul_bias_activation":
+            y = x @ a[1]
+            if len(a) > 2:
+                y = y + a[2]
+            act = cfg.get("activation", "none")
+            if act in ("gelu", "gelu_tanh"):
+                y = 0.5 * y * (1 + np.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+            elif act == "relu":
+                y = np.maximum(y, 0)
+            elif act == "silu":
+                y = y / (1 + np.exp(-y))
+            elif act == "tanh":
+                y = np.tanh(y)
+            elif act in ("sigmoid", "logistic"):
+                y = 1 / (1 + np.exp(-y))
+            return y
+        raise Unsupported(f"custom_call @{target}")
+
+
+def evaluate(text, inputs, function: str | None = None, round_floats: bool = False):
+    """Runs @main (or `function`) of a StableHLO module on numpy inputs; returns a list of arrays (floats in fp64)."""
+    funcs = parse(text)
+    f = next((g for g in funcs if g.name == (function or "main")), funcs[0])
+    return Interpreter(round_floats).run(f, inputs)
