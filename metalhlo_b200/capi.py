@@ -293,7 +293,8 @@ class Client:
             shape, ptr, nbytes = tuple(t.shape), t.data_ptr(), t.numel() * t.element_size()
             keep = t
         else:
-            a = np.ascontiguousarray(array)
+            a = np.asarray(array)
+            a = a if a.flags['C_CONTIGUOUS'] else np.ascontiguousarray(a)  # keeps 0-d arrays 0-d
             code = dtype_code(a.dtype) if element_type is None else element_type
             shape, ptr, nbytes = a.shape, a.ctypes.data, a.nbytes
             keep = a

@@ -26,6 +26,22 @@ class RowTuning(C.Structure):
     _fields_ = [("threads", C.c_int32), ("vecs_per_thread", C.c_int32), ("ctas_per_sm", C.c_int32)]
 
 
+class View(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_int64 * 8),
+                ("stride", C.c_int64 * 8)]
+
+
+class EwInst(C.Structure):
+    _fields_ = [("op", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("c", C.c_int32), ("imm", C.c_double)]
+
+
+class GatherDims(C.Structure):
+    _fields_ = [("n_offset_dims", C.c_int32), ("n_collapsed", C.c_int32), ("n_operand_batching", C.c_int32),
+                ("n_start_index_map", C.c_int32), ("offset_dims", C.c_int32 * 8), ("collapsed_slice_dims", C.c_int32 * 8),
+                ("operand_batching_dims", C.c_int32 * 8), ("start_indices_batching_dims", C.c_int32 * 8),
+                ("start_index_map", C.c_int32 * 8), ("index_vector_dim", C.c_int32), ("slice_sizes", C.c_int64 * 8)]
+
+
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: build it with `make -C metalhlo_b200/csrc` "
@@ -60,6 +76,18 @@ _PROTOTYPES = {
     "mhlo_cuda_layer_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _i64, _i64, _f32, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_rms_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _i64, _i64, _f32, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_softmax": (C.c_int, [C.c_int, _vp, _vp, _i64, _i64, _i64, C.POINTER(RowTuning), _vp]),
+    "mhlo_cuda_elementwise": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp]),
+    "mhlo_cuda_elementwise_to_view": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, C.POINTER(View), _vp]),
+    "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
+                                   _vp, C.POINTER(_i64), _i32, _vp]),
+    "mhlo_cuda_dynamic_slice": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, C.POINTER(_vp), _i32, C.POINTER(_i64), _vp, _vp]),
+    "mhlo_cuda_dynamic_update_slice": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, C.POINTER(_i64), C.POINTER(_vp), _i32, _vp]),
+    "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
+                                 _i32, _vp]),
+    "mhlo_cuda_attention": (C.c_int, [_i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _vp,
+                                      C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
 }
 for _name, (_res, _args) in _PROTOTYPES.items():
     _fn = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
@@ -130,6 +158,59 @@ def rms_norm(x, gamma, eps: float = 1e-5, out=None, tuning=None, stream=None):
     rows = x.numel() // hidden if hidden else 0
     check(lib.mhlo_cuda_rms_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(gamma), _ptr(out), rows, hidden, eps,
                                  _tuning(tuning), _stream(stream)))
+    return out
+
+
+EPILOGUES = {"none": 0, "relu": 1, "gelu_tanh": 2, "gelu_erf": 3, "silu": 4, "tanh": 5, "sigmoid": 6}
+
+
+def _i64s(vals):
+    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool = False, trans_b: bool = False,
+         out=None, stream=None):
+    """C[..., M, N] = act(A . B + bias) through ``mhlo_cuda_gemm``.
+
+    a: [batch..., M, K] (or [batch..., K, M] with trans_a), b: [batch..., K, N] (or [batch..., N, K] with trans_b);
+    up to two leading batch dimensions, both operands dense CUDA tensors of the same dtype.
+    """
+    import torch
+
+    assert a.is_cuda and b.is_cuda and a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype
+    batch = list(a.shape[:-2])
+    assert len(batch) <= 2 and list(b.shape[:-2]) == batch
+    b0, b1 = ([1, 1] + batch)[-2:]
+    m, k = (a.shape[-1], a.shape[-2]) if trans_a else (a.shape[-2], a.shape[-1])
+    n = b.shape[-2] if trans_b else b.shape[-1]
+    a_mat, b_mat = a.shape[-2] * a.shape[-1], b.shape[-2] * b.shape[-1]
+    a_str = [b1 * a_mat, a_mat] + ([1, m] if trans_a else [k, 1])
+    b_str = [b1 * b_mat, b_mat] + ([1, k] if trans_b else [n, 1])
+    out_dtype = a.dtype if out_dtype is None else out_dtype
+    if out is None:
+        out = torch.empty(batch + [m, n], dtype=out_dtype, device=a.device)
+    check(lib.mhlo_cuda_gemm(torch_dtype_code(a.dtype), torch_dtype_code(out_dtype), _ptr(a), _i64s(a_str), _ptr(b),
+                             _i64s(b_str), _ptr(out), b0, b1, m, n, k, _ptr(bias), EPILOGUES[epilogue], _stream(stream)))
+    return out
+
+
+def attention(q, k, v, scale: float, causal: bool = False, mask=None, layout: str = "BHSD", out=None, stream=None):
+    """Fused attention through ``mhlo_cuda_attention``. q/k/v are dense [B,H,S,D] (layout "BHSD") or [B,S,H,D] ("BSHD")."""
+    import torch
+
+    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    if layout == "BHSD":
+        B, H, Sq, D = q.shape
+        Sk = k.shape[2]
+        strides = lambda S: [H * S * D, S * D, D]
+    else:
+        B, Sq, H, D = q.shape
+        Sk = k.shape[1]
+        strides = lambda S: [S * H * D, D, H * D]
+    out = torch.empty_like(q) if out is None else out
+    check(lib.mhlo_cuda_attention(torch_dtype_code(q.dtype), _ptr(q), _i64s(strides(Sq)), _ptr(k), _i64s(strides(Sk)), _ptr(v),
+                                  _i64s(strides(Sk)), _ptr(mask), _ptr(out), _i64s(strides(Sq)), B, H, Sq, Sk, D, scale,
+                                  1 if causal else 0, _stream(stream)))
     return out
 
 
