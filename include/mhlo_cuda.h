@@ -293,6 +293,13 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
                    mhlo_cuda_stream_t stream);
 
 /*
+ * Every wait inside the tensor-core kernels (mbarrier phases fed by TMA and tcgen05.commit) is bounded; a kernel
+ * whose wait expires records a non-zero word and drains instead of spinning. This call synchronises the device,
+ * reads and clears that word: *out_code = 0 when no kernel gave up since the last call.
+ */
+int mhlo_cuda_device_error(int32_t* out_code);
+
+/*
  * Fused scaled dot-product attention, O = softmax(scale * Q K^T [+ mask] [causal]) V with fp32 softmax and
  * accumulation. Q [B,H,Sq,D], K/V [B,H,Sk,D], O [B,H,Sq,D] logically; *_strides = {batch, head, sequence}
  * element strides (the head dimension D is contiguous), so [B,S,H,D] tensors are read and written in place.

@@ -25,6 +25,8 @@ struct AttnShape {
 // Tensor-core (tcgen05 + TMA + TMEM) paths; *_supported() says whether the problem meets their layout rules.
 bool gemm_tc_supported(const GemmProblem& p);
 int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream);
+int gemm_device_error();       // synchronises; returns and clears the GEMM kernel's error word (-1: CUDA error)
+int attention_device_error();  // same for the attention kernel
 bool attention_tc_supported(int dtype, const AttnShape& s, const void* mask);
 int attention_tc_launch(int dtype, const void* q, const void* k, const void* v, void* o, const AttnShape& s,
                         cudaStream_t stream);

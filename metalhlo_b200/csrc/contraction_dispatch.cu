@@ -98,6 +98,15 @@ using namespace mhlo;
 
 extern "C" {
 
+int mhlo_cuda_device_error(int32_t* out_code) {
+    if (!out_code) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_error: null output");
+    const int g = gemm_device_error(), a = attention_device_error();
+    if (g < 0 || a < 0) return fail(MHLO_CUDA_EXECUTION_FAILED, "device_error: %s", cudaGetErrorString(cudaGetLastError()));
+    *out_code = g != 0 ? g : (a != 0 ? 100 + a : 0);
+    if (*out_code != 0) return fail(MHLO_CUDA_EXECUTION_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d)", *out_code);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
                    const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
                    int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,

@@ -1,12 +1,495 @@
-// tcgen05 GEMM (placeholder until the kernel lands: reports "not supported" so the dispatcher uses the
-// general-layout path).
+// dot_general on the 5th-generation tensor cores: a persistent, warp-specialised tcgen05 GEMM.
+//
+//   C[b, m, n] = act( sum_k A[b, m, k] * B[b, k, n] + bias[n] ),  A/B bf16 or f16, fp32 accumulation in TMEM.
+//
+// One CTA per SM walks output tiles of 128 x BN (BN = 256 or 128). Per tile the K loop advances in 64-element
+// panels through a ring of shared-memory stages:
+//   warp 0 (one lane)  producer: TMA (cp.async.bulk.tensor, 128-byte swizzle, zero fill out of bounds) of the
+//                      A and B panels into the next free stage, completion on the stage's "full" mbarrier
+//   warp 1 (one lane)  MMA issuer: four tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) per stage from
+//                      shared-memory descriptors into one of two TMEM accumulator buffers; tcgen05.commit hands
+//                      the stage back to the producer and, after the last panel, the accumulator to the epilogue
+//   warps 2-5          epilogue: tcgen05.ld of the accumulator (each warp its own 32 TMEM lanes = 32 rows),
+//                      bias + activation in fp32, conversion, 16-byte stores; the other accumulator buffer is
+//                      being filled by the MMA warp meanwhile
+// Operand layouts: A may be K-major ([m][k], k contiguous) or M-major ([k][m]); B K-major ([n][k]) or N-major
+// ([k][n]) - the instruction descriptor carries the majors, so transposed operands are read in place. Up to two
+// batch dimensions ride along as TMA coordinates. Every mbarrier wait is bounded: on expiry the kernel records an
+// error word and drains, it never spins forever.
+//
+// HBM traffic per tile pass: A and B panels are re-read from L2 across tiles; the tile order walks 16 row-tiles
+// per column band so that the 148 concurrently resident tiles share operands in L2. Algorithmic bytes:
+// (M*K + K*N) * 2 read + M*N * sizeof(out) written per batch entry.
+#include <cuda.h>
+
+#include <algorithm>
+#include <string>
+
 #include "contraction.cuh"
 
 namespace mhlo {
-bool gemm_tc_supported(const GemmProblem&) { return false; }
-int gemm_tc_launch(const GemmProblem&, cudaStream_t) { return fail(MHLO_CUDA_UNSUPPORTED, "tensor-core GEMM not built"); }
-bool attention_tc_supported(int, const AttnShape&, const void*) { return false; }
-int attention_tc_launch(int, const void*, const void*, const void*, void*, const AttnShape&, cudaStream_t) {
-    return fail(MHLO_CUDA_UNSUPPORTED, "tensor-core attention not built");
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // one 128-byte swizzle row of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+__device__ int g_gemm_error = 0;
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false when the phase did not complete within kSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand panel (start address, leading / stride byte
+// offsets in 16-byte units, descriptor version 1, layout type 2 = SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fff);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+__device__ __forceinline__ float epilogue_act(float v, int act) {
+    switch (act) {
+        case MHLO_EPILOGUE_RELU: return fmaxf(v, 0.f);
+        case MHLO_EPILOGUE_GELU_TANH: {
+            const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+            return 0.5f * v * (1.0f + tanhf(inner));
+        }
+        case MHLO_EPILOGUE_GELU_ERF: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+        case MHLO_EPILOGUE_SILU: return v / (1.0f + __expf(-v));
+        case MHLO_EPILOGUE_TANH: return tanhf(v);
+        case MHLO_EPILOGUE_SIGMOID: return 1.0f / (1.0f + __expf(-v));
+        default: return v;
+    }
+}
+
+struct GemmParams {
+    void* c;
+    const void* bias;
+    int64_t m, n, k;
+    int64_t batch0, batch1;
+    int32_t tiles_m, tiles_n;
+    int64_t num_tiles;
+    int32_t a_mn_major, b_mn_major;  // 0 = K-major, 1 = M/N-major
+    int32_t in_bf16;                 // operand format: 1 = bf16, 0 = f16
+    int32_t out_dtype;               // MHLO_DT_BF16 / F16 / F32
+    int32_t epilogue;
+    int32_t c_vec_ok;                // rows of C start 16-byte aligned: vector stores allowed
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + slack for 1024-byte alignment
+};
+
+// Tile order: bands of 16 row-tiles; inside a band the column index is the slow one.
+__device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int* bz, int* tm, int* tn) {
+    const int64_t per_batch = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    *bz = static_cast<int>(tile / per_batch);
+    int64_t t = tile % per_batch;
+    constexpr int kBand = 16;
+    const int64_t band_tiles = static_cast<int64_t>(kBand) * p.tiles_n;
+    const int band = static_cast<int>(t / band_tiles);
+    const int rows_in_band = min(kBand, p.tiles_m - band * kBand);
+    t -= band * band_tiles;
+    *tm = band * kBand + static_cast<int>(t % rows_in_band);
+    *tn = static_cast<int>(t / rows_in_band);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStageBytes);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full = empty_bar + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = static_cast<int>((p.k + BK - 1) / BK);
+    constexpr uint32_t kTmemCols = 2 * BN;
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_a);
+        prefetch_tmap(&map_b);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                int bz, tm, tn;
+                tile_coords(tile, p, &bz, &tm, &tn);
+                const int b0 = bz / static_cast<int>(p.batch1), b1 = bz % static_cast<int>(p.batch1);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; atomicExch(&g_gemm_error, 1); break; }
+                    uint8_t* sa = smem + stage * L::kStageBytes;
+                    uint8_t* sb = sa + L::kABytes;
+                    mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+                    if (!p.a_mn_major) {
+                        tma_load_4d(sa, &map_a, &full_bar[stage], kb * BK, tm * BM, b1, b0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_4d(sa + j * 64 * BK * 2, &map_a, &full_bar[stage], tm * BM + j * 64, kb * BK, b1, b0);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_4d(sb, &map_b, &full_bar[stage], kb * BK, tn * BN, b1, b0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_4d(sb + j * 64 * BK * 2, &map_b, &full_bar[stage], tn * BN + j * 64, kb * BK, b1, b0);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
+            const uint32_t fmt = p.in_bf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) |
+                                   (static_cast<uint32_t>(p.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(BM >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { atomicExch(&g_gemm_error, 2); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase)) { ok = false; atomicExch(&g_gemm_error, 3); break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+                    const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B along the swizzled row.
+                        // M/N-major: 64-element blocks are one 8 KiB box apart (LBO), 8-row K groups 1024 B (SBO), a K
+                        // step is 16 rows = 2048 B.
+                        const uint64_t da = p.a_mn_major ? make_smem_desc(sa + k * UMMA_K * 128, 64 * BK * 2, 1024)
+                                                         : make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+                        const uint64_t db = p.b_mn_major ? make_smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
+                                                         : make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                umma_commit(&tmem_full[acc]);  // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const size_t out_es = p.out_dtype == MHLO_DT_F32 ? 4 : 2;
+        for (int64_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            int bz, tm, tn;
+            tile_coords(tile, p, &bz, &tm, &tn);
+            if (!mbar_wait(&tmem_full[acc], acc_phase)) { atomicExch(&g_gemm_error, 4); break; }
+            tc_fence_after();
+            const int64_t row = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            uint8_t* crow = static_cast<uint8_t*>(p.c) + (static_cast<int64_t>(bz) * p.m + row) * p.n * out_es;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0);
+                tmem_ld32(taddr, r);
+                tmem_ld_wait();
+                const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
+                if (!row_ok || col0 >= p.n) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int64_t col = col0 + j;
+                        float b = 0.f;
+                        if (col < p.n) {
+                            if (p.out_dtype == MHLO_DT_F32) b = static_cast<const float*>(p.bias)[col];
+                            else if (p.out_dtype == MHLO_DT_BF16) b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+                            else b = __half2float(static_cast<const __half*>(p.bias)[col]);
+                        }
+                        v[j] += b;
+                    }
+                }
+                if (p.epilogue != MHLO_EPILOGUE_NONE) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = epilogue_act(v[j], p.epilogue);
+                }
+                const bool full = col0 + 32 <= p.n;
+                if (p.out_dtype == MHLO_DT_F32) {
+                    float* dst = reinterpret_cast<float*>(crow) + col0;
+                    if (full && p.c_vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = v[j];
+                    }
+                } else {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (p.out_dtype == MHLO_DT_BF16) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    uint16_t* dst = reinterpret_cast<uint16_t*>(crow) + col0;
+                    if (full && p.c_vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.n; ++j)
+                            dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------------
+
+bool encode_map(CUtensorMap* map, const void* base, const int64_t dims[4], const int64_t strides_bytes[3], const uint32_t box[4],
+                std::string* why) {
+    cuuint64_t gdim[4];
+    cuuint64_t gstr[3];
+    cuuint32_t bx[4], es[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 4; ++i) { gdim[i] = static_cast<cuuint64_t>(dims[i]); bx[i] = box[i]; }
+    for (int i = 0; i < 3; ++i) gstr[i] = static_cast<cuuint64_t>(strides_bytes[i]);
+    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, bx, es,
+                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        const char* msg = nullptr;
+        cuGetErrorString(r, &msg);
+        *why = msg ? msg : "cuTensorMapEncodeTiled failed";
+        return false;
+    }
+    return true;
+}
+
+// Operand as a 4-D tensor map {inner, outer, batch1, batch0}. `inner_is_k`: the contiguous dimension is K.
+bool operand_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t outer_stride, int64_t b1, int64_t b1_stride,
+                 int64_t b0, int64_t b0_stride, uint32_t box_inner, uint32_t box_outer, std::string* why) {
+    const int64_t dims[4] = {inner, outer, b1, b0};
+    // a dimension of extent 1 still needs a legal stride (non-zero multiple of 16)
+    const int64_t span = std::max<int64_t>(16, ((outer > 1 ? outer_stride * outer : inner) * 2 + 15) / 16 * 16);
+    int64_t s1 = outer_stride * 2, s2 = b1_stride * 2, s3 = b0_stride * 2;
+    if (outer == 1 || s1 == 0) s1 = span;
+    if (b1 == 1 || s2 == 0) s2 = span;
+    if (b0 == 1 || s3 == 0) s3 = span;
+    const int64_t strides[3] = {s1, s2, s3};
+    const uint32_t box[4] = {box_inner, box_outer, 1, 1};
+    return encode_map(map, base, dims, strides, box, why);
+}
+
+bool stride_ok(int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0; }
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmProblem& p) {
+    const bool f16 = p.in_dtype == MHLO_DT_F16, bf16 = p.in_dtype == MHLO_DT_BF16;
+    if (!f16 && !bf16) return false;
+    if (p.out_dtype != p.in_dtype && p.out_dtype != MHLO_DT_F32) return false;
+    if (p.m <= 0 || p.n <= 0 || p.k <= 0 || p.batch0 <= 0 || p.batch1 <= 0) return false;
+    if (p.m * p.n < 64 * 64) return false;  // tiny products: the general kernel has less fixed cost
+    if (!aligned16(p.a) || !aligned16(p.b)) return false;
+    // one of (row, col) strides must be 1; the other, and the batch strides, 16-byte multiples
+    const bool a_k = p.as[3] == 1 || p.k == 1, a_m = p.as[2] == 1 || p.m == 1;
+    const bool b_n = p.bs[3] == 1 || p.n == 1, b_k = p.bs[2] == 1 || p.k == 1;
+    if (!(a_k || a_m) || !(b_n || b_k)) return false;
+    auto batch_ok = [&](const int64_t* s) {
+        return (p.batch0 == 1 || stride_ok(s[0])) && (p.batch1 == 1 || stride_ok(s[1]));
+    };
+    if (!batch_ok(p.as) || !batch_ok(p.bs)) return false;
+    if (a_k ? !(p.m == 1 || stride_ok(p.as[2])) : !(p.k == 1 || stride_ok(p.as[3]))) return false;
+    if (b_k ? !(p.n == 1 || stride_ok(p.bs[3])) : !(p.k == 1 || stride_ok(p.bs[2]))) return false;
+    if (p.batch0 * p.batch1 > 0x7fffffffLL || p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL) return false;
+    return true;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const GemmProblem& pr, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    const bool a_k = pr.as[3] == 1 || pr.k == 1;
+    const bool b_k = pr.bs[2] == 1 || pr.k == 1;  // K-major B = [n][k] with k contiguous
+    CUtensorMap map_a, map_b;
+    std::string why;
+    bool ok;
+    if (a_k) ok = operand_map(&map_a, pr.a, pr.k, pr.m, pr.as[2], pr.batch1, pr.as[1], pr.batch0, pr.as[0], BK, BM, &why);
+    else ok = operand_map(&map_a, pr.a, pr.m, pr.k, pr.as[3], pr.batch1, pr.as[1], pr.batch0, pr.as[0], 64, BK, &why);
+    if (!ok) return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for A: %s", why.c_str());
+    if (b_k) ok = operand_map(&map_b, pr.b, pr.k, pr.n, pr.bs[3], pr.batch1, pr.bs[1], pr.batch0, pr.bs[0], BK, BN, &why);
+    else ok = operand_map(&map_b, pr.b, pr.n, pr.k, pr.bs[2], pr.batch1, pr.bs[1], pr.batch0, pr.bs[0], 64, BK, &why);
+    if (!ok) return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for B: %s", why.c_str());
+
+    GemmParams p;
+    p.c = pr.c;
+    p.bias = pr.bias;
+    p.m = pr.m; p.n = pr.n; p.k = pr.k;
+    p.batch0 = pr.batch0; p.batch1 = pr.batch1;
+    p.tiles_m = static_cast<int>((pr.m + BM - 1) / BM);
+    p.tiles_n = static_cast<int>((pr.n + BN - 1) / BN);
+    p.num_tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n * pr.batch0 * pr.batch1;
+    p.a_mn_major = a_k ? 0 : 1;
+    p.b_mn_major = b_k ? 0 : 1;
+    p.in_bf16 = pr.in_dtype == MHLO_DT_BF16;
+    p.out_dtype = pr.out_dtype;
+    p.epilogue = pr.epilogue;
+    const size_t out_es = pr.out_dtype == MHLO_DT_F32 ? 4 : 2;
+    p.c_vec_ok = aligned16(pr.c) && (pr.n * out_es) % 16 == 0;
+
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
+        attr_set = true;
+    }
+    const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
+    kernel<<<grid, 192, L::kTotal, stream>>>(map_a, map_b, p);
+    MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
+    return MHLO_CUDA_OK;
+}
+
+int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
+    // wide tiles when there are enough of them to fill the machine, otherwise 128 x 128
+    const int64_t tiles_256 = ((p.m + BM - 1) / BM) * ((p.n + 255) / 256) * p.batch0 * p.batch1;
+    if (p.n > 128 && tiles_256 >= kNumSMs) return launch_gemm<256, 4>(p, stream);
+    return launch_gemm<128, 6>(p, stream);
+}
+
+int gemm_device_error() {
+    int v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof v) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero);
+    return v;
+}
+
 }  // namespace mhlo

@@ -86,6 +86,7 @@ _PROTOTYPES = {
     "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                  _i32, _vp]),
+    "mhlo_cuda_device_error": (C.c_int, [C.POINTER(_i32)]),
     "mhlo_cuda_attention": (C.c_int, [_i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _vp,
                                       C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
 }
@@ -159,6 +160,13 @@ def rms_norm(x, gamma, eps: float = 1e-5, out=None, tuning=None, stream=None):
     check(lib.mhlo_cuda_rms_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(gamma), _ptr(out), rows, hidden, eps,
                                  _tuning(tuning), _stream(stream)))
     return out
+
+
+def device_error() -> int:
+    """Synchronises and returns the tensor-core kernels' error word (0 = no bounded wait expired)."""
+    code = C.c_int32(0)
+    lib.mhlo_cuda_device_error(C.byref(code))
+    return code.value
 
 
 EPILOGUES = {"none": 0, "relu": 1, "gelu_tanh": 2, "gelu_erf": 3, "silu": 4, "tanh": 5, "sigmoid": 6}
