@@ -9,7 +9,7 @@
 //   warp 1 (one lane)  MMA issuer: four tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) per stage from
 //                      shared-memory descriptors into one of two TMEM accumulator buffers; tcgen05.commit hands
 //                      the stage back to the producer and, after the last panel, the accumulator to the epilogue
-//   warps 2-5          epilogue: tcgen05.ld of the accumulator (each warp its own 32 TMEM lanes = 32 rows),
+//   warps 2-9          epilogue: tcgen05.ld of the accumulator (each warp 32 TMEM lanes = 32 rows, half the columns),
 //                      bias + activation in fp32, conversion, 16-byte stores; the other accumulator buffer is
 //                      being filled by the MMA warp meanwhile
 // Operand layouts: A may be K-major ([m][k], k contiguous) or M-major ([k][m]); B K-major ([n][k]) or N-major
@@ -34,6 +34,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // one 128-byte swizzle row of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, each taking half of the tile's columns
+constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
 __device__ int g_gemm_error = 0;
 
@@ -179,7 +181,7 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ GemmParams p) {
     using L = SmemLayout<BN, STAGES>;
@@ -199,7 +201,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         prefetch_tmap(&map_a);
         prefetch_tmap(&map_b);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -285,8 +287,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
+        // ---------------- epilogue (warps 2..9) ----------------
         const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+        const int col_begin = ((warp - 2) >> 2) * (BN / 2), col_end = col_begin + BN / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
         const size_t out_es = p.out_dtype == MHLO_DT_F32 ? 4 : 2;
@@ -299,7 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool row_ok = row < p.m;
             uint8_t* crow = static_cast<uint8_t*>(p.c) + (static_cast<int64_t>(bz) * p.m + row) * p.n * out_es;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0);
                 tmem_ld32(taddr, r);
@@ -472,7 +475,7 @@ static int launch_gemm(const GemmProblem& pr, cudaStream_t stream) {
         attr_set = true;
     }
     const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
-    kernel<<<grid, 192, L::kTotal, stream>>>(map_a, map_b, p);
+    kernel<<<grid, kGemmThreads, L::kTotal, stream>>>(map_a, map_b, p);
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
 }
