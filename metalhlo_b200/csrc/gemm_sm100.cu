@@ -385,13 +385,26 @@ bool encode_map(CUtensorMap* map, const void* base, const int64_t dims[4], const
     cuuint32_t bx[4], es[4] = {1, 1, 1, 1};
     for (int i = 0; i < 4; ++i) { gdim[i] = static_cast<cuuint64_t>(dims[i]); bx[i] = box[i]; }
     for (int i = 0; i < 3; ++i) gstr[i] = static_cast<cuuint64_t>(strides_bytes[i]);
-    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, bx, es,
-                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // The driver entry point is looked up at run time so that the library loads on machines without libcuda
+    // (the host-side compiler and the ABI tests run there).
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+            *why = "cuTensorMapEncodeTiled is not available from this driver";
+            return false;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, bx, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        const char* msg = nullptr;
-        cuGetErrorString(r, &msg);
-        *why = msg ? msg : "cuTensorMapEncodeTiled failed";
+        *why = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r));
         return false;
     }
     return true;
