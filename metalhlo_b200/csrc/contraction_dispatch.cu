@@ -153,7 +153,8 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
     for (int i = 0; i < 3; ++i) { s.qs[i] = q_strides[i]; s.ks[i] = k_strides[i]; s.vs[i] = v_strides[i]; s.os[i] = o_strides[i]; }
     s.batch = batch; s.heads = heads; s.seq_q = seq_q; s.seq_k = seq_k; s.head_dim = head_dim; s.scale = scale; s.causal = causal;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (attention_tc_supported(dtype, s, mask_dev)) return attention_tc_launch(dtype, q_dev, k_dev, v_dev, o_dev, s, st);
+    if (attention_tc_supported(dtype, s, mask_dev) && aligned16(q_dev) && aligned16(k_dev) && aligned16(v_dev) && aligned16(o_dev))
+        return attention_tc_launch(dtype, q_dev, k_dev, v_dev, o_dev, s, st);
     if (head_dim > 256) return fail(MHLO_CUDA_UNSUPPORTED, "attention: head_dim %lld above 256", (long long)head_dim);
     switch (dtype) {
         case MHLO_DT_F32: return launch_attention_rows<float>(q_dev, k_dev, v_dev, mask_dev, o_dev, s, st);
