@@ -43,6 +43,7 @@ struct AttnParams {
     float scale_log2;  // scale * log2(e)
     int32_t causal;
     int32_t is_bf16;
+    int32_t debug;
 };
 
 template <int D>
@@ -55,7 +56,7 @@ struct AttnSmem {
     static constexpr int kKOff = kQOff + kQBytes;
     static constexpr int kVOff = kKOff + kKvStages * kKBytes;
     static constexpr int kPOff = kVOff + kKvStages * kVBytes;
-    static constexpr int kBarOff = kPOff + kHalves * kPBytes;
+    static constexpr int kBarOff = kPOff + 2 * kHalves * kPBytes;  // two P buffers per half
     static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
@@ -81,8 +82,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
     using L = AttnSmem<D>;
     constexpr int kPanels = D / 64;            // 64-element (128-byte) panels along the head dimension
-    constexpr uint32_t kTmemCols = 512;        // S: 2 x 64 columns, O: 2 x D columns
-    constexpr uint32_t kSCol = 0, kOCol = 2 * kBlockN;
+    constexpr uint32_t kTmemCols = 512;        // S: 4 x 64 columns (two buffers per half), O: 2 x D columns
+    constexpr uint32_t kSCol = 0, kOCol = 4 * kBlockN;  // S: [half][2 buffers] x 64 columns, then O: [half] x D
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -91,10 +92,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* k_empty = k_full + kKvStages;
     uint64_t* v_full = k_empty + kKvStages;
     uint64_t* v_empty = v_full + kKvStages;
-    uint64_t* s_full = v_empty + kKvStages;        // per half
-    uint64_t* p_full = s_full + kHalves;
-    uint64_t* pv_done = p_full + kHalves;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kHalves);
+    uint64_t* s_full = v_empty + kKvStages;        // [half][buffer]
+    uint64_t* p_full = s_full + 2 * kHalves;       // [half][buffer]
+    uint64_t* pv_done = p_full + 2 * kHalves;      // [half][buffer]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2 * kHalves);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mblk = gridDim.x - 1 - blockIdx.x;  // heavy (late, for causal) query blocks first
@@ -112,7 +113,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         prefetch_tmap(&map_v);
         mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int h = 0; h < kHalves; ++h) { mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1); }
+        for (int h = 0; h < kHalves; ++h) { mbar_init(&s_full[2 * h], 1); mbar_init(&s_full[2 * h + 1], 1);
+            for (int b = 0; b < 2; ++b) { mbar_init(&p_full[2 * h + b], 4); mbar_init(&pv_done[2 * h + b], 1); } }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -146,8 +148,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0 && nblk > 0) {
+        // ---------------- MMA issuer: the whole warp walks the schedule (uniform control flow keeps descriptors in
+        // uniform registers); one elected lane issues the tcgen05 instructions ----------------
+        if (nblk > 0) {
             const uint32_t fmt = p.is_bf16 ? 1u : 0u;
             // S = Q K^T: both operands K-major, N = 64. O += P V: P K-major, V N-major (head dim contiguous), N = D.
             const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
@@ -156,56 +159,53 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                            p_addr = smem_u32(smem + L::kPOff);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(&g_attn_error, 3);
-            auto issue_s = [&](int h, int stage) {
+            auto issue_s = [&](int h, int stage, int buf) {
                 const uint32_t qa = q_addr + h * kPanels * kBlockM * 128, ka = k_addr + stage * L::kKBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = make_smem_desc(qa + (kk / 4) * kBlockM * 128 + (kk % 4) * 32, 16, 1024);
                     const uint64_t db = make_smem_desc(ka + (kk / 4) * kBlockN * 128 + (kk % 4) * 32, 16, 1024);
-                    umma_f16(tmem_base + kSCol + h * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
+                    if (elect_one()) umma_f16(tmem_base + kSCol + (2 * h + buf) * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[h]);
+                if (elect_one()) umma_commit(&s_full[2 * h + buf]);
+                __syncwarp();
             };
-            auto issue_pv = [&](int h, int stage, bool accumulate) {
-                const uint32_t pa = p_addr + h * L::kPBytes, va = v_addr + stage * L::kVBytes;
+            auto issue_pv = [&](int h, int stage, int buf, bool accumulate) {
+                const uint32_t pa = p_addr + (2 * h + buf) * L::kPBytes, va = v_addr + stage * L::kVBytes;
 #pragma unroll
                 for (int kk = 0; kk < kBlockN / 16; ++kk) {
                     const uint64_t da = make_smem_desc(pa + kk * 32, 16, 1024);
                     const uint64_t db = make_smem_desc(va + kk * 16 * 128, kBlockN * 128, 1024);
-                    umma_f16(tmem_base + kOCol + h * D, da, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+                    if (elect_one()) umma_f16(tmem_base + kOCol + h * D, da, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
                 }
-                umma_commit(&pv_done[h]);
+                if (elect_one()) umma_commit(&pv_done[2 * h + buf]);
+                __syncwarp();
             };
-            int stage = 0;      // stage of block j (V) ; block j+1's K is in the next stage
-            uint32_t phase = 0;
-            if (ok) {
-                ok = mbar_wait(&k_full[0], 0);
-                if (ok) {
-                    tc_fence_after();
-                    issue_s(0, 0);
-                    issue_s(1, 0);
-                    umma_commit(&k_empty[0]);
-                } else atomicExch(&g_attn_error, 4);
+            // Scores run two key blocks ahead of the softmax (two S buffers per half): S_h(j+2) is issued as soon as the
+            // softmax has consumed S_h(j), so a warpgroup never waits for the tensor pipe.
+            auto kstage = [](int j) { return j % kKvStages; };
+            auto kphase = [](int j) { return static_cast<uint32_t>((j / kKvStages) & 1); };
+            for (int j = 0; j < 2 && j < nblk && ok; ++j) {
+                if (!mbar_wait(&k_full[kstage(j)], kphase(j))) { ok = false; atomicExch(&g_attn_error, 4); break; }
+                tc_fence_after();
+                issue_s(0, kstage(j), j & 1);
+                issue_s(1, kstage(j), j & 1);
+                { if (elect_one()) umma_commit(&k_empty[kstage(j)]); __syncwarp(); }
             }
             for (int j = 0; j < nblk && ok; ++j) {
-                const int nstage = stage + 1 == kKvStages ? 0 : stage + 1;
-                const uint32_t nphase = stage + 1 == kKvStages ? phase ^ 1 : phase;
                 for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!mbar_wait(&p_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                    if (!mbar_wait(&p_full[2 * h + (j & 1)], (j >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                    if (h == 0 && !mbar_wait(&v_full[kstage(j)], kphase(j))) { ok = false; atomicExch(&g_attn_error, 7); break; }
                     tc_fence_after();
-                    if (j + 1 < nblk) {
-                        if (h == 0 && !mbar_wait(&k_full[nstage], nphase)) { ok = false; atomicExch(&g_attn_error, 6); break; }
+                    issue_pv(h, kstage(j), j & 1, j > 0);
+                    if (h == kHalves - 1) { if (elect_one()) umma_commit(&v_empty[kstage(j)]); __syncwarp(); }
+                    if (j + 2 < nblk) {
+                        if (h == 0 && !mbar_wait(&k_full[kstage(j + 2)], kphase(j + 2))) { ok = false; atomicExch(&g_attn_error, 6); break; }
                         tc_fence_after();
-                        issue_s(h, nstage);
-                        if (h == kHalves - 1) umma_commit(&k_empty[nstage]);
+                        issue_s(h, kstage(j + 2), j & 1);
+                        if (h == kHalves - 1) { if (elect_one()) umma_commit(&k_empty[kstage(j + 2)]); __syncwarp(); }
                     }
-                    if (h == 0 && !mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
-                    tc_fence_after();
-                    issue_pv(h, stage, j > 0);
-                    if (h == kHalves - 1) umma_commit(&v_empty[stage]);
                 }
-                stage = nstage;
-                phase = nphase;
             }
         }
     } else {
@@ -215,18 +215,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = quarter * 32 + lane;   // row inside the half
         const int qi = m0 + h * kBlockM + r; // query index
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t s_taddr = tmem_base + lane_base + kSCol + h * kBlockN;
+        const uint32_t s_taddr0 = tmem_base + lane_base + kSCol + 2 * h * kBlockN;
         const uint32_t o_taddr = tmem_base + lane_base + kOCol + h * D;
-        uint8_t* p_row = smem + L::kPOff + h * L::kPBytes + r * 128;
+        uint8_t* p_row0 = smem + L::kPOff + 2 * h * L::kPBytes + r * 128;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
-            if (!mbar_wait(&s_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
+            if (!mbar_wait(&s_full[2 * h + (j & 1)], (j >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
+            const uint32_t s_taddr = s_taddr0 + (j & 1) * kBlockN;
             tc_fence_after();
             uint32_t sr[kBlockN];
+            if (p.debug != 2) {
             tmem_ld32(s_taddr, sr);
             tmem_ld32(s_taddr + 32, sr + 32);
             tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBlockN; ++c) sr[c] = 0;
+            }
             const int key0 = j * kBlockN;
             const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
             if (key0 + kBlockN - 1 > last_visible) {  // diagonal or ragged block: mask the invisible keys
@@ -258,28 +264,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int c = 0; c < kBlockN; c += 2) {
                 const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
-                const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                const float2 e = p.debug == 1 ? x : make_float2(fast_exp2(x.x), fast_exp2(x.y));
                 rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
                 packed[c / 2] = pack16(e.x, e.y, p.is_bf16 != 0);
             }
             l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
-            // P's buffer and O are free once the previous PV product has completed
-            if (j > 0) {
-                if (!mbar_wait(&pv_done[h], (j - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 9); break; }
+            // The accumulator may only be rescaled once every PV product issued so far has completed (rare path).
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                if (!mbar_wait(&pv_done[2 * h + ((j - 1) & 1)], ((j - 1) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 9); break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t orow[32];
-                        tmem_ld32(o_taddr + c0, orow);
-                        tmem_ld_wait();
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t orow[32];
+                    tmem_ld32(o_taddr + c0, orow);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                        tmem_st32(o_taddr + c0, orow);
-                    }
-                    tmem_st_wait();
+                    for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                    tmem_st32(o_taddr + c0, orow);
                 }
+                tmem_st_wait();
             }
+            // P buffer (j & 1) is free once the PV product of block j-2 has read it
+            if (j >= 2) {
+                if (!mbar_wait(&pv_done[2 * h + (j & 1)], ((j - 2) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 11); break; }
+            }
+            uint8_t* p_row = p_row0 + (j & 1) * L::kPBytes;
             // row r of the K-major, 128-byte-swizzled P tile: 16-byte chunk c lands at chunk (c ^ (r & 7))
 #pragma unroll
             for (int c = 0; c < 8; ++c)
@@ -288,11 +297,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[h]);
+            if (lane == 0) mbar_arrive(&p_full[2 * h + (j & 1)]);
         }
         // ---- write O / l ----
         if (ok && nblk > 0) {
-            if (!mbar_wait(&pv_done[h], (nblk - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); }
+            if (!mbar_wait(&pv_done[2 * h + ((nblk - 1) & 1)], ((nblk - 1) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); }
             tc_fence_after();
         }
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -384,6 +393,7 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
     p.scale_log2 = s.scale * kLog2e;
     p.causal = s.causal;
     p.is_bf16 = dtype == MHLO_DT_BF16;
+    p.debug = getenv("MHLO_ATTN_DEBUG") ? atoi(getenv("MHLO_ATTN_DEBUG")) : 0;
     auto kernel = attention_tcgen05_kernel<D>;
     static bool attr_set = false;
     if (!attr_set) {
