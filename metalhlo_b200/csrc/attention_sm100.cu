@@ -1,17 +1,19 @@
 // Fused flash attention on tcgen05: O = softmax(scale * Q K^T [causal]) V for bf16 / f16, head_dim 64 or 128, fp32
 // softmax statistics and fp32 accumulation in TMEM. The S^2 score matrix never reaches HBM.
 //
-// One CTA owns 256 query rows of one (batch, head) as two halves of 128 rows and walks the keys in blocks of 64:
-//   warp 0 (one lane)   TMA producer: Q once (both halves), then K_j and V_j tiles through 3-stage rings
-//   warp 1 (one lane)   MMA issuer, software-pipelined over the two halves:
-//                         S_h(j+1) = Q_h K_{j+1}^T   (tcgen05.mma M128 N64, K-major operands, into TMEM columns S_h)
-//                         O_h     += P_h(j) V_j      (M128 N=D, P from shared memory, V N-major, accumulates in TMEM)
+// One CTA owns 256 query rows of one (batch, head) as two halves of 128 rows and walks the keys in blocks of 128:
+//   warp 0 (one lane)   TMA producer: Q once (both halves), then K_j and V_j tiles through 2-stage rings
+//   warp 1              MMA issuer (warp-uniform loop, one elected lane issues), ping-ponging the two halves:
+//                         S_h(j+1) = Q_h K_{j+1}^T   (tcgen05.mma M128 N128, both operands K-major in shared memory)
+//                         O_h     += P_h(j) V_j      (P read from tensor memory, V N-major in shared memory, N = D)
 //                       so the tensor pipe works on one half while the other half's softmax runs
-//   warps 2-5 / 6-9     softmax warpgroups for half 0 / 1; a thread owns one query row: tcgen05.ld of its 64 scores,
-//                       running maximum, exp2, row sum, P packed to 16 bit and written to shared memory in the
-//                       128-byte-swizzled K-major layout the PV MMA reads. The maximum used in the exponent is only
-//                       advanced when it grew by more than 2^8 ("lazy rescale"): only then is O rescaled in TMEM
-//                       (tcgen05.ld, multiply, tcgen05.st).
+//   warps 2-5 / 6-9     softmax warpgroups for half 0 / 1; a thread owns one query row: two passes of tcgen05.ld over
+//                       its 128 scores (row maximum, then exp2 and row sum), probabilities packed to 16 bit and
+//                       written with tcgen05.st over the score columns they came from - P never touches shared
+//                       memory. The maximum used in the exponent only advances when it grew by more than 2^8
+//                       ("lazy rescale"); only then is O rescaled in TMEM (tcgen05.ld, multiply, tcgen05.st).
+// TMEM: S_h/P_h 2 x 128 columns, O_h 2 x D columns (all 512 at D = 128). Shared memory at D = 128: Q 64 KiB,
+// K 2 x 32 KiB, V 2 x 32 KiB.
 // Causal masking skips key blocks right of the diagonal and masks inside diagonal blocks; ragged sequence ends are
 // zero-filled by TMA and masked to -inf. Every mbarrier wait is bounded.
 //
@@ -28,8 +30,8 @@ namespace {
 
 constexpr int kBlockM = 128;     // query rows per half
 constexpr int kHalves = 2;
-constexpr int kBlockN = 64;      // keys per step
-constexpr int kKvStages = 3;
+constexpr int kBlockN = 128;     // keys per step
+constexpr int kKvStages = 2;
 constexpr int kAttnThreads = 32 * (2 + 4 * kHalves);
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units: exponentials stay below 2^8 between rescales
@@ -43,7 +45,6 @@ struct AttnParams {
     float scale_log2;  // scale * log2(e)
     int32_t causal;
     int32_t is_bf16;
-    int32_t debug;
 };
 
 template <int D>
@@ -51,12 +52,10 @@ struct AttnSmem {
     static constexpr int kQBytes = kHalves * kBlockM * D * 2;
     static constexpr int kKBytes = kBlockN * D * 2;  // one stage
     static constexpr int kVBytes = kBlockN * D * 2;
-    static constexpr int kPBytes = kBlockM * kBlockN * 2;  // per half
     static constexpr int kQOff = 0;
     static constexpr int kKOff = kQOff + kQBytes;
     static constexpr int kVOff = kKOff + kKvStages * kKBytes;
-    static constexpr int kPOff = kVOff + kKvStages * kVBytes;
-    static constexpr int kBarOff = kPOff + 2 * kHalves * kPBytes;  // two P buffers per half
+    static constexpr int kBarOff = kVOff + kKvStages * kVBytes;
     static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
@@ -75,35 +74,43 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (the probabilities) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
     using L = AttnSmem<D>;
-    constexpr int kPanels = D / 64;            // 64-element (128-byte) panels along the head dimension
-    constexpr uint32_t kTmemCols = 512;        // S: 4 x 64 columns (two buffers per half), O: 2 x D columns
-    constexpr uint32_t kSCol = 0, kOCol = 4 * kBlockN;  // S: [half][2 buffers] x 64 columns, then O: [half] x D
+    constexpr int kPanels = D / 64;       // 64-element (128-byte) panels along the head dimension
+    constexpr uint32_t kTmemCols = 512;   // S_h: 128 columns per half (P overwrites them in place), O_h: D columns per half
+    constexpr uint32_t kSCol = 0, kOCol = kHalves * kBlockN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-    uint64_t* q_full = bars;                       // 1
-    uint64_t* k_full = q_full + 1;                 // kKvStages
+    uint64_t* q_full = bars;
+    uint64_t* k_full = q_full + 1;
     uint64_t* k_empty = k_full + kKvStages;
     uint64_t* v_full = k_empty + kKvStages;
     uint64_t* v_empty = v_full + kKvStages;
-    uint64_t* s_full = v_empty + kKvStages;        // [half][buffer]
-    uint64_t* p_full = s_full + 2 * kHalves;       // [half][buffer]
-    uint64_t* pv_done = p_full + 2 * kHalves;      // [half][buffer]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2 * kHalves);
+    uint64_t* s_full = v_empty + kKvStages;  // per half: scores of the current key block are in TMEM
+    uint64_t* p_full = s_full + kHalves;     // per half: probabilities written (and O rescaled if needed)
+    uint64_t* pv_done = p_full + kHalves;    // per half: every PV product issued so far has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kHalves);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mblk = gridDim.x - 1 - blockIdx.x;  // heavy (late, for causal) query blocks first
     const int head = blockIdx.y, bat = blockIdx.z;
     const int m0 = mblk * kHalves * kBlockM;
     const int causal_off = p.seq_k - p.seq_q;
-    // keys this CTA visits: all, or up to the last key its last query row may see
-    int kv_len = p.seq_k;
+    int kv_len = p.seq_k;  // keys this CTA visits: all, or up to the last key its last query row may see
     if (p.causal) kv_len = min(p.seq_k, max(0, min(m0 + kHalves * kBlockM, p.seq_q) + causal_off));
     const int nblk = (kv_len + kBlockN - 1) / kBlockN;
 
@@ -113,8 +120,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         prefetch_tmap(&map_v);
         mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int h = 0; h < kHalves; ++h) { mbar_init(&s_full[2 * h], 1); mbar_init(&s_full[2 * h + 1], 1);
-            for (int b = 0; b < 2; ++b) { mbar_init(&p_full[2 * h + b], 4); mbar_init(&pv_done[2 * h + b], 1); } }
+        for (int h = 0; h < kHalves; ++h) { mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1); }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -152,100 +158,103 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // uniform registers); one elected lane issues the tcgen05 instructions ----------------
         if (nblk > 0) {
             const uint32_t fmt = p.is_bf16 ? 1u : 0u;
-            // S = Q K^T: both operands K-major, N = 64. O += P V: P K-major, V N-major (head dim contiguous), N = D.
+            // S = Q K^T: both operands K-major from shared memory, N = 128 keys.
+            // O += P V: P from tensor memory (K-major), V from shared memory N-major (head dim contiguous), N = D.
             const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(smem + L::kQOff), k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff),
-                           p_addr = smem_u32(smem + L::kPOff);
+            const uint32_t q_addr = smem_u32(smem + L::kQOff), k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(&g_attn_error, 3);
-            auto issue_s = [&](int h, int stage, int buf) {
+            auto issue_s = [&](int h, int stage) {
                 const uint32_t qa = q_addr + h * kPanels * kBlockM * 128, ka = k_addr + stage * L::kKBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = make_smem_desc(qa + (kk / 4) * kBlockM * 128 + (kk % 4) * 32, 16, 1024);
                     const uint64_t db = make_smem_desc(ka + (kk / 4) * kBlockN * 128 + (kk % 4) * 32, 16, 1024);
-                    if (elect_one()) umma_f16(tmem_base + kSCol + (2 * h + buf) * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
+                    if (elect_one()) umma_f16(tmem_base + kSCol + h * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
                 }
-                if (elect_one()) umma_commit(&s_full[2 * h + buf]);
+                if (elect_one()) umma_commit(&s_full[h]);
                 __syncwarp();
             };
-            auto issue_pv = [&](int h, int stage, int buf, bool accumulate) {
-                const uint32_t pa = p_addr + (2 * h + buf) * L::kPBytes, va = v_addr + stage * L::kVBytes;
+            auto issue_pv = [&](int h, int stage, bool accumulate) {
+                const uint32_t va = v_addr + stage * L::kVBytes;
 #pragma unroll
                 for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    const uint64_t da = make_smem_desc(pa + kk * 32, 16, 1024);
+                    // 16 keys of P = 8 packed 32-bit columns; 16 keys of V = 16 rows of 128 bytes in every head-dim panel
                     const uint64_t db = make_smem_desc(va + kk * 16 * 128, kBlockN * 128, 1024);
-                    if (elect_one()) umma_f16(tmem_base + kOCol + h * D, da, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+                    if (elect_one()) umma_f16_ts(tmem_base + kOCol + h * D, tmem_base + kSCol + h * kBlockN + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
                 }
-                if (elect_one()) umma_commit(&pv_done[2 * h + buf]);
+                if (elect_one()) umma_commit(&pv_done[h]);
                 __syncwarp();
             };
-            // Scores run two key blocks ahead of the softmax (two S buffers per half): S_h(j+2) is issued as soon as the
-            // softmax has consumed S_h(j), so a warpgroup never waits for the tensor pipe.
-            auto kstage = [](int j) { return j % kKvStages; };
-            auto kphase = [](int j) { return static_cast<uint32_t>((j / kKvStages) & 1); };
-            for (int j = 0; j < 2 && j < nblk && ok; ++j) {
-                if (!mbar_wait(&k_full[kstage(j)], kphase(j))) { ok = false; atomicExch(&g_attn_error, 4); break; }
-                tc_fence_after();
-                issue_s(0, kstage(j), j & 1);
-                issue_s(1, kstage(j), j & 1);
-                { if (elect_one()) umma_commit(&k_empty[kstage(j)]); __syncwarp(); }
-            }
-            for (int j = 0; j < nblk && ok; ++j) {
-                for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!mbar_wait(&p_full[2 * h + (j & 1)], (j >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
-                    if (h == 0 && !mbar_wait(&v_full[kstage(j)], kphase(j))) { ok = false; atomicExch(&g_attn_error, 7); break; }
+            int stage = 0;
+            uint32_t phase = 0;
+            if (ok) {
+                ok = mbar_wait(&k_full[0], 0);
+                if (ok) {
                     tc_fence_after();
-                    issue_pv(h, kstage(j), j & 1, j > 0);
-                    if (h == kHalves - 1) { if (elect_one()) umma_commit(&v_empty[kstage(j)]); __syncwarp(); }
-                    if (j + 2 < nblk) {
-                        if (h == 0 && !mbar_wait(&k_full[kstage(j + 2)], kphase(j + 2))) { ok = false; atomicExch(&g_attn_error, 6); break; }
+                    issue_s(0, 0);
+                    issue_s(1, 0);
+                    if (elect_one()) umma_commit(&k_empty[0]);
+                    __syncwarp();
+                } else atomicExch(&g_attn_error, 4);
+            }
+            // Tensor-pipe order per key block j: PV_0(j), S_0(j+1), PV_1(j), S_1(j+1). The pipe executes one thread's MMAs in
+            // order, so S_h(j+1) overwrites the S/P columns only after PV_h(j) has read the probabilities from them.
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int nstage = stage + 1 == kKvStages ? 0 : stage + 1;
+                const uint32_t nphase = stage + 1 == kKvStages ? phase ^ 1 : phase;
+                for (int h = 0; h < kHalves && ok; ++h) {
+                    if (!mbar_wait(&p_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                    if (h == 0 && !mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
+                    tc_fence_after();
+                    issue_pv(h, stage, j > 0);
+                    if (h == kHalves - 1) { if (elect_one()) umma_commit(&v_empty[stage]); __syncwarp(); }
+                    if (j + 1 < nblk) {
+                        if (h == 0 && !mbar_wait(&k_full[nstage], nphase)) { ok = false; atomicExch(&g_attn_error, 6); break; }
                         tc_fence_after();
-                        issue_s(h, kstage(j + 2), j & 1);
-                        if (h == kHalves - 1) { if (elect_one()) umma_commit(&k_empty[kstage(j + 2)]); __syncwarp(); }
+                        issue_s(h, nstage);
+                        if (h == kHalves - 1) { if (elect_one()) umma_commit(&k_empty[nstage]); __syncwarp(); }
                     }
                 }
+                stage = nstage;
+                phase = nphase;
             }
         }
     } else {
-// ---------------- softmax warpgroups ----------------
+        // ---------------- softmax warpgroups ----------------
         const int h = (warp - 2) >> 2;       // which half of the query block
         const int quarter = warp & 3;        // TMEM lanes this warp may touch
         const int r = quarter * 32 + lane;   // row inside the half
         const int qi = m0 + h * kBlockM + r; // query index
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t s_taddr0 = tmem_base + lane_base + kSCol + 2 * h * kBlockN;
+        const uint32_t s_taddr = tmem_base + lane_base + kSCol + h * kBlockN;
         const uint32_t o_taddr = tmem_base + lane_base + kOCol + h * D;
-        uint8_t* p_row0 = smem + L::kPOff + 2 * h * L::kPBytes + r * 128;
+        const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
-            if (!mbar_wait(&s_full[2 * h + (j & 1)], (j >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
-            const uint32_t s_taddr = s_taddr0 + (j & 1) * kBlockN;
+            if (!mbar_wait(&s_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
             tc_fence_after();
-            uint32_t sr[kBlockN];
-            if (p.debug != 2) {
-            tmem_ld32(s_taddr, sr);
-            tmem_ld32(s_taddr + 32, sr + 32);
-            tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int c = 0; c < kBlockN; ++c) sr[c] = 0;
-            }
             const int key0 = j * kBlockN;
-            const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
-            if (key0 + kBlockN - 1 > last_visible) {  // diagonal or ragged block: mask the invisible keys
-#pragma unroll
-                for (int c = 0; c < kBlockN; ++c)
-                    if (key0 + c > last_visible) sr[c] = 0xff800000u;  // -inf
-            }
-            // row maximum of the raw scores with four independent chains (scale > 0, so it commutes with max)
+            const bool need_mask = key0 + kBlockN - 1 > last_visible;  // diagonal or ragged block
+            // ---- pass 1: row maximum of the raw scores (scale > 0, so scaling commutes with max) ----
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < kBlockN; c += 4) {
+            for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+                uint32_t sr[64];
+                tmem_ld32(s_taddr + c0, sr);
+                tmem_ld32(s_taddr + c0 + 32, sr + 32);
+                tmem_ld_wait();
+                if (need_mask) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(sr[c + u]));
+                    for (int c = 0; c < 64; ++c)
+                        if (key0 + c0 + c > last_visible) sr[c] = 0xff800000u;  // -inf
+                }
+#pragma unroll
+                for (int c = 0; c < 64; c += 4)
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(sr[c + u]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             // advance the reference maximum only when it would otherwise let exponentials exceed 2^threshold
@@ -256,23 +265,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 m_ref = mx;
                 l *= alpha;
             }
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // p = 2^(s * scale*log2e - m): one packed FMA per two scores, then ex2
-            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
-            uint32_t packed[kBlockN / 2];
-            float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-            for (int c = 0; c < kBlockN; c += 2) {
-                const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
-                const float2 e = p.debug == 1 ? x : make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
-                packed[c / 2] = pack16(e.x, e.y, p.is_bf16 != 0);
-            }
-            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
-            // The accumulator may only be rescaled once every PV product issued so far has completed (rare path).
+            // every PV product issued so far completed before these scores were signalled, so O may be rescaled here
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                if (!mbar_wait(&pv_done[2 * h + ((j - 1) & 1)], ((j - 1) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 9); break; }
-                tc_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t orow[32];
@@ -282,26 +276,42 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
                     tmem_st32(o_taddr + c0, orow);
                 }
-                tmem_st_wait();
             }
-            // P buffer (j & 1) is free once the PV product of block j-2 has read it
-            if (j >= 2) {
-                if (!mbar_wait(&pv_done[2 * h + (j & 1)], ((j - 2) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 11); break; }
-            }
-            uint8_t* p_row = p_row0 + (j & 1) * L::kPBytes;
-            // row r of the K-major, 128-byte-swizzled P tile: 16-byte chunk c lands at chunk (c ^ (r & 7))
+            // ---- pass 2: p = 2^(s * scale*log2e - m), packed to 16 bit and written over the scores ----
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
+            float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            fence_proxy_async();
+            for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+                uint32_t sr[64];
+                tmem_ld32(s_taddr + c0, sr);
+                tmem_ld32(s_taddr + c0 + 32, sr + 32);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        if (key0 + c0 + c > last_visible) sr[c] = 0xff800000u;
+                }
+                uint32_t packed[32];
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) {
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
+                    const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
+                    packed[c / 2] = pack16(e.x, e.y, p.is_bf16 != 0);
+                }
+                // keys [c0, c0+64) as 32 packed columns at column c0/2: those score columns have been consumed already
+                tmem_st32(s_taddr + c0 / 2, packed);
+            }
+            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[2 * h + (j & 1)]);
+            if (lane == 0) mbar_arrive(&p_full[h]);
         }
         // ---- write O / l ----
         if (ok && nblk > 0) {
-            if (!mbar_wait(&pv_done[2 * h + ((nblk - 1) & 1)], ((nblk - 1) >> 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); }
+            if (!mbar_wait(&pv_done[h], (nblk - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); }
             tc_fence_after();
         }
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -338,7 +348,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tmem_dealloc(tmem_base, kTmemCols);
     }
 }
-
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -393,7 +402,6 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
     p.scale_log2 = s.scale * kLog2e;
     p.causal = s.causal;
     p.is_bf16 = dtype == MHLO_DT_BF16;
-    p.debug = getenv("MHLO_ATTN_DEBUG") ? atoi(getenv("MHLO_ATTN_DEBUG")) : 0;
     auto kernel = attention_tcgen05_kernel<D>;
     static bool attr_set = false;
     if (!attr_set) {

@@ -158,8 +158,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // ---------------- MMA issuer: the whole warp runs the loop so that descriptors stay in uniform registers;
+        // one elected lane issues the tcgen05 instructions ----------------
+        {
             // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
             const uint32_t fmt = p.in_bf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) |
@@ -188,12 +189,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                          : make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
                         const uint64_t db = p.b_mn_major ? make_smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
                                                          : make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
-                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (elect_one()) umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    if (elect_one()) umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                umma_commit(&tmem_full[acc]);  // accumulator complete
+                if (elect_one()) umma_commit(&tmem_full[acc]);  // accumulator complete
+                __syncwarp();
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }

@@ -140,3 +140,119 @@ def mlp_softmax_module(m: int = 512, k: int = 1024, n: int = 1024, dt: str = "f3
     g, gres = gelu_text("%2", (m, n), dt)
     sm, res = softmax_text(gres, (m, n), dt, 1)
     return func([tx, tw, tb], [to], (body + g + sm).rstrip("\n"), res)
+
+
+def gpt2_module(batch: int = 32, seq: int = 1024, layers: int = 12, d_model: int = 768, heads: int = 12, vocab: int = 50257,
+                dt: str = "f16", eps: float = 1e-5):
+    """GPT-2 forward pass (pre-LN blocks, tanh-GELU MLP, causal attention, tied output embedding) in the op forms
+    `jax.jit` prints. Parameters arrive as fp32 and are converted to `dt` inside the module; token ids are i32.
+
+    Returns (text, parameter list) where the parameter list is [(name, shape, dtype)] in argument order:
+    ids, wte, wpe, then per layer ln1_g, ln1_b, w_qkv, b_qkv, w_o, b_o, ln2_g, ln2_b, w_fc, b_fc, w_proj, b_proj,
+    then lnf_g, lnf_b. The result is the logits tensor [batch, seq, vocab] in `dt`.
+    """
+    dh = d_model // heads
+    params = [("ids", (batch, seq), "i32"), ("wte", (vocab, d_model), "f32"), ("wpe", (seq, d_model), "f32")]
+    for i in range(layers):
+        params += [(f"l{i}.ln1_g", (d_model,), "f32"), (f"l{i}.ln1_b", (d_model,), "f32"),
+                   (f"l{i}.w_qkv", (d_model, 3 * d_model), "f32"), (f"l{i}.b_qkv", (3 * d_model,), "f32"),
+                   (f"l{i}.w_o", (d_model, d_model), "f32"), (f"l{i}.b_o", (d_model,), "f32"),
+                   (f"l{i}.ln2_g", (d_model,), "f32"), (f"l{i}.ln2_b", (d_model,), "f32"),
+                   (f"l{i}.w_fc", (d_model, 4 * d_model), "f32"), (f"l{i}.b_fc", (4 * d_model,), "f32"),
+                   (f"l{i}.w_proj", (4 * d_model, d_model), "f32"), (f"l{i}.b_proj", (d_model,), "f32")]
+    params += [("lnf_g", (d_model,), "f32"), ("lnf_b", (d_model,), "f32")]
+    arg = {name: f"%arg{i}" for i, (name, _, _) in enumerate(params)}
+    lines = []
+    counter = [0]
+
+    def fresh(tag="t"):
+        counter[0] += 1
+        return f"%{tag}{counter[0]}"
+
+    def emit(line):
+        lines.append("    " + line)
+
+    def cvt(name, shape):
+        v = fresh("p")
+        emit(f"{v} = stablehlo.convert {arg[name]} : ({tt(shape, 'f32')}) -> {tt(shape, dt)}")
+        return v
+
+    act = (batch, seq, d_model)
+    t_act = tt(act, dt)
+
+    def dense(x, xshape, w, wshape, b):
+        oshape = xshape[:-1] + (wshape[1],)
+        y, bb, o = fresh(), fresh(), fresh()
+        emit(f"{y} = stablehlo.dot_general {x}, {w}, contracting_dims = [{len(xshape) - 1}] x [0] : ({tt(xshape, dt)}, {tt(wshape, dt)}) -> {tt(oshape, dt)}")
+        emit(f"{bb} = stablehlo.broadcast_in_dim {b}, dims = [{len(oshape) - 1}] : ({tt((wshape[1],), dt)}) -> {tt(oshape, dt)}")
+        emit(f"{o} = stablehlo.add {y}, {bb} : {tt(oshape, dt)}")
+        return o, oshape
+
+    def layer_norm(x, g, b, prefix):
+        body, res = layer_norm_text(x, act, dt, g, b, eps=eps, prefix=prefix)
+        lines.extend(body.rstrip("\n").split("\n"))
+        return res
+
+    # embeddings
+    wte = cvt("wte", (vocab, d_model))
+    wpe = cvt("wpe", (seq, d_model))
+    idx, tok, pos, x = fresh(), fresh(), fresh(), fresh()
+    emit(f"{idx} = stablehlo.reshape {arg['ids']} : ({tt((batch, seq), 'i32')}) -> {tt((batch, seq, 1), 'i32')}")
+    emit(f"{tok} = \"stablehlo.gather\"({wte}, {idx}) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], collapsed_slice_dims = [0], "
+         f"start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1, {d_model}>}}> : "
+         f"({tt((vocab, d_model), dt)}, {tt((batch, seq, 1), 'i32')}) -> {t_act}")
+    emit(f"{pos} = stablehlo.broadcast_in_dim {wpe}, dims = [1, 2] : ({tt((seq, d_model), dt)}) -> {t_act}")
+    emit(f"{x} = stablehlo.add {tok}, {pos} : {t_act}")
+    # causal predicate shared by all layers
+    ti, tb = tt((seq, seq), "i32"), tt((seq, seq), "i1")
+    ts = tt((batch, heads, seq, seq), dt)
+    emit(f"%iq = stablehlo.iota dim = 0 : {ti}")
+    emit(f"%ik = stablehlo.iota dim = 1 : {ti}")
+    emit(f"%causal = stablehlo.compare  GE, %iq, %ik,  SIGNED : ({ti}, {ti}) -> {tb}")
+    emit(f"%causalb = stablehlo.broadcast_in_dim %causal, dims = [2, 3] : ({tb}) -> {tt((batch, heads, seq, seq), 'i1')}")
+    neg = "-6.000000e+04" if dt == "f16" else "-1.000000e+09"
+    emit(f"%neg = stablehlo.constant dense<{neg}> : {ts}")
+    emit(f"%scale = stablehlo.constant dense<{1.0 / math.sqrt(dh):e}> : {ts}")
+    t_heads = tt((batch, seq, heads, dh), dt)
+    for i in range(layers):
+        p = {k: cvt(f"l{i}.{k}", s) for k, s in [("ln1_g", (d_model,)), ("ln1_b", (d_model,)), ("w_qkv", (d_model, 3 * d_model)),
+                                                   ("b_qkv", (3 * d_model,)), ("w_o", (d_model, d_model)), ("b_o", (d_model,)),
+                                                   ("ln2_g", (d_model,)), ("ln2_b", (d_model,)), ("w_fc", (d_model, 4 * d_model)),
+                                                   ("b_fc", (4 * d_model,)), ("w_proj", (4 * d_model, d_model)), ("b_proj", (d_model,))]}
+        hn = layer_norm(x, p["ln1_g"], p["ln1_b"], f"a{i}n")
+        qkv, qkv_shape = dense(hn, act, p["w_qkv"], (d_model, 3 * d_model), p["b_qkv"])
+        parts = []
+        for k in range(3):
+            sl, rs = fresh(), fresh()
+            emit(f"{sl} = stablehlo.slice {qkv} [0:{batch}, 0:{seq}, {k * d_model}:{(k + 1) * d_model}] : ({tt(qkv_shape, dt)}) -> {t_act}")
+            emit(f"{rs} = stablehlo.reshape {sl} : ({t_act}) -> {t_heads}")
+            parts.append(rs)
+        q, k_, v = parts
+        s0, s1, s2 = fresh(), fresh(), fresh()
+        emit(f"{s0} = stablehlo.dot_general {q}, {k_}, batching_dims = [0, 2] x [0, 2], contracting_dims = [3] x [3] : ({t_heads}, {t_heads}) -> {ts}")
+        emit(f"{s1} = stablehlo.multiply {s0}, %scale : {ts}")
+        emit(f"{s2} = stablehlo.select %causalb, {s1}, %neg : {tt((batch, heads, seq, seq), 'i1')}, {ts}")
+        sm, pr = softmax_text(s2, (batch, heads, seq, seq), dt, 3, prefix=f"a{i}s")
+        lines.extend(sm.rstrip("\n").split("\n"))
+        o0, o1, o2 = fresh(), fresh(), fresh()
+        emit(f"{o0} = stablehlo.dot_general {pr}, {v}, batching_dims = [0, 1] x [0, 2], contracting_dims = [3] x [1] : ({ts}, {t_heads}) -> {tt((batch, heads, seq, dh), dt)}")
+        emit(f"{o1} = stablehlo.transpose {o0}, dims = [0, 2, 1, 3] : ({tt((batch, heads, seq, dh), dt)}) -> {t_heads}")
+        emit(f"{o2} = stablehlo.reshape {o1} : ({t_heads}) -> {t_act}")
+        ao, _ = dense(o2, act, p["w_o"], (d_model, d_model), p["b_o"])
+        x1 = fresh()
+        emit(f"{x1} = stablehlo.add {x}, {ao} : {t_act}")
+        hn2 = layer_norm(x1, p["ln2_g"], p["ln2_b"], f"m{i}n")
+        fc, fc_shape = dense(hn2, act, p["w_fc"], (d_model, 4 * d_model), p["b_fc"])
+        gl, gres = gelu_text(fc, fc_shape, dt, prefix=f"m{i}g")
+        lines.extend(gl.rstrip("\n").split("\n"))
+        pj, _ = dense(gres, fc_shape, p["w_proj"], (4 * d_model, d_model), p["b_proj"])
+        x2 = fresh()
+        emit(f"{x2} = stablehlo.add {x1}, {pj} : {t_act}")
+        x = x2
+    g, b = cvt("lnf_g", (d_model,)), cvt("lnf_b", (d_model,))
+    xf = layer_norm(x, g, b, "fn")
+    logits = fresh("logits")
+    t_logits = tt((batch, seq, vocab), dt)
+    emit(f"{logits} = stablehlo.dot_general {xf}, {wte}, contracting_dims = [2] x [1] : ({t_act}, {tt((vocab, d_model), dt)}) -> {t_logits}")
+    text = func([tt(s, d) for _, s, d in params], [t_logits], "\n".join(lines), logits)
+    return text, params
