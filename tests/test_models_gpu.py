@@ -1,0 +1,74 @@
+"""Whole-module parity through the C API: the reference-runnable fp32 MLP+softmax configuration and a reduced GPT-2
+forward pass (same graph as the full model, smaller extents) at every optimisation level against the numpy oracle."""
+import numpy as np
+import pytest
+
+from metalhlo_b200 import modules
+from oracle import interp
+from parity import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def client():
+    from metalhlo_b200 import capi
+
+    return capi.Client()
+
+
+@pytest.mark.parametrize("level", [0, 1, 2, 3])
+def test_mlp_softmax_fp32_configuration(level):
+    # X [512,1024] ~ N(0,1), W [1024,1024] ~ N(0,0.02), b zeros: dot_general + bias -> tanh GELU -> softmax
+    rng = np.random.default_rng(42)
+    x = rng.standard_normal((512, 1024)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((1024, 1024))).astype(np.float32)
+    b = np.zeros(1024, np.float32)
+    text = modules.mlp_softmax_module()
+    want = interp.evaluate(text, [x, w, b])[0]
+    c = client()
+    exe = c.compile(text, level)
+    got = exe.execute([c.buffer(x), c.buffer(w), c.buffer(b)])[0].to_numpy()
+    assert_close(got.astype(np.float64), want, 1e-5, f"O{level}")
+    np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=1e-5)
+    if level == 3:
+        assert exe.steps == ["fused_matmul_bias_activation", "fused_softmax"]
+
+
+def gpt2_inputs(params, vocab, seed=0):
+    rng = np.random.default_rng(seed)
+    out = []
+    for name, shape, dt in params:
+        if dt == "i32":
+            out.append(rng.integers(0, vocab, size=shape).astype(np.int32))
+        elif name.endswith("_g"):
+            out.append(np.ones(shape, np.float32))
+        elif name.endswith(("ln1_b", "ln2_b", "lnf_b")):
+            out.append(np.zeros(shape, np.float32))
+        else:
+            out.append((0.02 * rng.standard_normal(shape)).astype(np.float32))
+    return out
+
+
+@pytest.mark.parametrize("level", [0, 2, 3])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_reduced_gpt2_forward(level, dt):
+    vocab = 1031  # not a multiple of 8: ragged logits rows like the real vocabulary
+    text, params = modules.gpt2_module(batch=2, seq=128, layers=2, d_model=256, heads=4, vocab=vocab, dt=dt)
+    ins = gpt2_inputs(params, vocab)
+    want = interp.evaluate(text, ins)[0]
+    c = client()
+    exe = c.compile(text, level)
+    got = exe.execute([c.buffer(a) for a in ins])[0].to_numpy().astype(np.float64)
+    # ~150 chained 16-bit ops: the per-op bound of tests/parity.py does not compose, so the whole-model check is normwise
+    # (relative L2 error within the 16-bit tolerance, worst element within 5 % of the logit range)
+    rel_l2 = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert rel_l2 < 2e-2, f"gpt2 {dt} O{level}: relative L2 error {rel_l2:.3e}"
+    assert np.abs(got - want).max() < 5e-2 * np.abs(want).max(), f"gpt2 {dt} O{level}"
+    if level == 3:
+        fused = [s for s in exe.steps if s.startswith("fused")]
+        assert fused.count("fused_scaled_dot_product_attention") == 2
+        assert fused.count("fused_layer_norm") == 5 and fused.count("fused_matmul_bias_activation") == 8
+    # greedy next-token ids agree wherever the oracle's top-2 margin exceeds the 16-bit resolution
+    top2 = np.sort(want, axis=-1)[..., -2:]
+    clear = (top2[..., 1] - top2[..., 0]) > 0.05 * np.abs(top2[..., 1]) + 1e-3
+    assert np.array_equal(got.argmax(-1)[clear], want.argmax(-1)[clear])
