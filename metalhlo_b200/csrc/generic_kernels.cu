@@ -236,6 +236,80 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ EwParam
     }
 }
 
+// Fast path of the elementwise program: one instruction, float tensors, every input either dense over the output or
+// a single broadcast element. Eight elements per thread through 16-byte accesses; the opcode switch is uniform and
+// works on registers, so residual adds, bias-free activations, converts and dense copies run at memory speed.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* f) {
+    if constexpr (sizeof(T) == 4) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        VecTraits<T>::unpack(v, f);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* f) {
+    if constexpr (sizeof(T) == 4) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+    } else {
+        *reinterpret_cast<uint4*>(p) = VecTraits<T>::pack(f);
+    }
+}
+
+struct EwVecParams {
+    const void* in[3];
+    void* out;
+    int64_t n;
+    int32_t scalar_mask;  // bit k: input k is one broadcast element
+    int32_t n_inputs, op;
+    double imm;
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) ew_vec_kernel(const EwVecParams p) {
+    const int64_t nvec = p.n / 8;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    float sc[3] = {0.f, 0.f, 0.f};
+    for (int k = 0; k < p.n_inputs; ++k)
+        if ((p.scalar_mask >> k) & 1) sc[k] = VecTraits<TI>::to_float(static_cast<const TI*>(p.in[k])[0]);
+    for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += step) {
+        float x[3][8], r[8];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            if (k < p.n_inputs && !((p.scalar_mask >> k) & 1)) {
+                load8(static_cast<const TI*>(p.in[k]) + v * 8, x[k]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[k][e] = sc[k];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[e] = ew_float_op<float>(p.op, x[0][e], x[1][e], x[2][e], p.imm);
+        store8(static_cast<TO*>(p.out) + v * 8, r);
+    }
+    // ragged tail
+    if (blockIdx.x == 0 && threadIdx.x < p.n % 8) {
+        const int64_t i = nvec * 8 + threadIdx.x;
+        float x[3];
+        for (int k = 0; k < 3; ++k)
+            x[k] = k < p.n_inputs ? (((p.scalar_mask >> k) & 1) ? sc[k] : VecTraits<TI>::to_float(static_cast<const TI*>(p.in[k])[i])) : 0.f;
+        static_cast<TO*>(p.out)[i] = VecTraits<TO>::from_float(ew_float_op<float>(p.op, x[0], x[1], x[2], p.imm));
+    }
+}
+
+template <typename TI>
+bool launch_ew_vec_out(int out_dtype, const EwVecParams& p, int grid, cudaStream_t s) {
+    switch (out_dtype) {
+        case MHLO_DT_F32: ew_vec_kernel<TI, float><<<grid, 256, 0, s>>>(p); return true;
+        case MHLO_DT_F16: ew_vec_kernel<TI, __half><<<grid, 256, 0, s>>>(p); return true;
+        case MHLO_DT_BF16: ew_vec_kernel<TI, __nv_bfloat16><<<grid, 256, 0, s>>>(p); return true;
+        default: return false;
+    }
+}
+
 // Collapses adjacent dimensions that are mergeable in the output and in every input, drops extent-1 dims.
 void collapse_dims(EwParams* p) {
     int64_t shape[MHLO_CUDA_MAX_RANK];
@@ -685,8 +759,38 @@ static int elementwise_impl(const mhlo_cuda_view* inputs, int32_t n_inputs, cons
             }
             if (dense) p.contiguous_mask |= 1 << k;
         }
-    const int grid = grid_for(p.n, 256);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // fast path: one non-iota instruction over dense / scalar float inputs of one dtype
+    if (n_insts == 1 && !uses_iota && out_strides == nullptr && !any_f64 && n_inputs >= 1 && n_inputs <= 3 &&
+        (out_dtype == MHLO_DT_F32 || out_dtype == MHLO_DT_F16 || out_dtype == MHLO_DT_BF16) && aligned16(out_dev)) {
+        const int in_dt = inputs[0].dtype;
+        bool ok = in_dt == MHLO_DT_F32 || in_dt == MHLO_DT_F16 || in_dt == MHLO_DT_BF16;
+        EwVecParams vp;
+        memset(&vp, 0, sizeof vp);
+        for (int k = 0; k < n_inputs && ok; ++k) {
+            bool scalar = true;
+            for (int d = 0; d < p.rank; ++d) scalar &= p.in[k].stride[d] == 0;
+            const bool dense = (p.contiguous_mask >> k) & 1;
+            ok = p.in[k].dtype == in_dt && (scalar || (dense && aligned16(p.in[k].base)));
+            if (scalar && !(dense && p.n == 1)) vp.scalar_mask |= 1 << k;
+            vp.in[k] = p.in[k].base;
+        }
+        // instruction operands must name the inputs in order (a = 0, b = 1, c = 2), which is how single ops are built
+        ok = ok && prog[0].a == 0 && (n_inputs < 2 || prog[0].b == 1) && (n_inputs < 3 || prog[0].c == 2);
+        if (ok) {
+            vp.out = out_dev; vp.n = p.n; vp.n_inputs = n_inputs; vp.op = prog[0].op; vp.imm = prog[0].imm;
+            const int vgrid = grid_for((p.n + 7) / 8, 256);
+            bool launched = false;
+            if (in_dt == MHLO_DT_F32) launched = launch_ew_vec_out<float>(out_dtype, vp, vgrid, s);
+            else if (in_dt == MHLO_DT_F16) launched = launch_ew_vec_out<__half>(out_dtype, vp, vgrid, s);
+            else launched = launch_ew_vec_out<__nv_bfloat16>(out_dtype, vp, vgrid, s);
+            if (launched) {
+                MHLO_CUDA_CHECK_LAUNCH("elementwise_vec");
+                return MHLO_CUDA_OK;
+            }
+        }
+    }
+    const int grid = grid_for(p.n, 256);
     if (any_f64) ew_kernel<double><<<grid, 256, 0, s>>>(p);
     else if (any_float) ew_kernel<float><<<grid, 256, 0, s>>>(p);
     else ew_kernel<int64_t><<<grid, 256, 0, s>>>(p);

@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <numeric>
 
 #include "../../../include/mhlo_cuda.h"
@@ -1020,13 +1021,33 @@ std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const C
 int Executable::execute(const void* const* inputs, void* const* outputs, void* stream) {
     Ctx c{inputs, outputs, arena_dev_, const_dev_, stream};
     const bool debug = std::getenv("METALHLO_DEBUG_DISPATCH") != nullptr;
+    // METALHLO_PROFILE_GPU: per-step device times from CUDA events (synchronises after every step)
+    const bool profile = std::getenv("METALHLO_PROFILE_GPU") != nullptr;
+    void *e0 = nullptr, *e1 = nullptr;
+    if (profile) { mhlo_cuda_event_create(&e0); mhlo_cuda_event_create(&e1); }
+    std::map<std::string, std::pair<int, double>> by_label;
     for (size_t i = 0; i < steps_.size(); ++i) {
         if (debug) fprintf(stderr, "[metalhlo] step %zu: %s\n", i, steps_[i].label.c_str());
+        if (profile) mhlo_cuda_event_record(e0, stream);
         const int st = steps_[i].run(c);
         if (st != 0) {
             error_ = "step " + std::to_string(i) + " (" + steps_[i].label + "): " + mhlo_cuda_last_error();
             return st;
         }
+        if (profile) {
+            float ms = 0;
+            mhlo_cuda_event_record(e1, stream);
+            mhlo_cuda_event_elapsed_ms(e0, e1, &ms);
+            auto& slot = by_label[steps_[i].label];
+            slot.first += 1;
+            slot.second += ms;
+            if (ms > 0.5f) fprintf(stderr, "[metalhlo] step %zu %-40s %.3f ms\n", i, steps_[i].label.c_str(), ms);
+        }
+    }
+    if (profile) {
+        for (const auto& kv : by_label) fprintf(stderr, "[metalhlo] %-44s x%-4d %.3f ms\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        mhlo_cuda_event_destroy(e0);
+        mhlo_cuda_event_destroy(e1);
     }
     return 0;
 }

@@ -817,7 +817,22 @@ bool fuse_attention(Function& f) {
                 if (!cand.dead && cand.results.size() == 1 && cand.results[0] == root_result) root = &cand;
             std::string cfg = "{\"scale\":" + fmt_double(scale) + ",\"is_causal\":" + (causal ? "true" : "false") +
                               ",\"has_mask\":false,\"num_heads\":" + std::to_string(H) + ",\"head_dim\":" + std::to_string(D) + "}";
-            make_custom_call(*root, "fused_scaled_dot_product_attention", {q4, k4, v4}, cfg);
+            // When the only consumer transposes [B,H,S,D] to [B,S,H,D] (the layout the following reshape + dense layer
+            // wants), let the kernel write that layout directly instead of materialising a transposed copy.
+            Op* only_user = nullptr;
+            int n_users = 0;
+            for (Op& cand : f.ops) {
+                if (cand.dead) continue;
+                for (int v : cand.operands)
+                    if (v == root_result) { ++n_users; only_user = &cand; }
+            }
+            if (n_users == 1 && only_user->name == "transpose" && only_user->int_list("permutation") == std::vector<int64_t>{0, 2, 1, 3}) {
+                cfg.insert(cfg.size() - 1, ",\"output_layout\":\"BSHD\"");
+                make_custom_call(*only_user, "fused_scaled_dot_product_attention", {q4, k4, v4}, cfg);
+                root->dead = true;
+            } else {
+                make_custom_call(*root, "fused_scaled_dot_product_attention", {q4, k4, v4}, cfg);
+            }
             changed = true;
         }
         if (!changed) break;
