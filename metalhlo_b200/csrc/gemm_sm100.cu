@@ -39,19 +39,21 @@ constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
 __device__ int g_gemm_error = 0;
 
-__device__ __forceinline__ float epilogue_act(float v, int act) {
-    switch (act) {
-        case MHLO_EPILOGUE_RELU: return fmaxf(v, 0.f);
-        case MHLO_EPILOGUE_GELU_TANH: {
-            const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            return 0.5f * v * (1.0f + tanhf(inner));
-        }
-        case MHLO_EPILOGUE_GELU_ERF: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-        case MHLO_EPILOGUE_SILU: return v / (1.0f + __expf(-v));
-        case MHLO_EPILOGUE_TANH: return tanhf(v);
-        case MHLO_EPILOGUE_SIGMOID: return 1.0f / (1.0f + __expf(-v));
-        default: return v;
+template <int ACT>
+__device__ __forceinline__ float epilogue_act(float v) {
+    if constexpr (ACT == MHLO_EPILOGUE_RELU) return fmaxf(v, 0.f);
+    if constexpr (ACT == MHLO_EPILOGUE_GELU_TANH) {
+        const float inner = 0.7978845608028654f * v * fmaf(0.044715f * v, v, 1.0f);
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));  // 2^-11 relative error: below the 16-bit output resolution
+        const float hv = 0.5f * v;
+        return fmaf(hv, t, hv);
     }
+    if constexpr (ACT == MHLO_EPILOGUE_GELU_ERF) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    if constexpr (ACT == MHLO_EPILOGUE_SILU) return v / (1.0f + __expf(-v));
+    if constexpr (ACT == MHLO_EPILOGUE_TANH) return tanhf(v);
+    if constexpr (ACT == MHLO_EPILOGUE_SIGMOID) return 1.0f / (1.0f + __expf(-v));
+    return v;
 }
 
 struct GemmParams {
@@ -74,7 +76,10 @@ struct SmemLayout {
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + slack for 1024-byte alignment
+    static constexpr int kStagingBytes = kEpilogueWarps * 4096;  // one 32-row x 128-byte tile per epilogue warp
+    static constexpr int kStagingOff = STAGES * kStageBytes;
+    static constexpr int kBarrierOff = kStagingOff + kStagingBytes;
+    static constexpr int kTotal = kBarrierOff + kBarrierBytes + 1024;  // + slack for 1024-byte alignment
 };
 
 // Tile order: bands of 16 row-tiles; inside a band the column index is the slow one.
@@ -91,14 +96,14 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
     *tn = static_cast<int>(t / rows_in_band);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int ACT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ GemmParams p) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStageBytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarrierOff);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full = empty_bar + STAGES;
     uint64_t* tmem_empty = tmem_full + 2;
@@ -212,66 +217,112 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tile_coords(tile, p, &bz, &tm, &tn);
             if (!mbar_wait(&tmem_full[acc], acc_phase)) { atomicExch(&g_gemm_error, 4); break; }
             tc_fence_after();
-            const int64_t row = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
-            const bool row_ok = row < p.m;
-            uint8_t* crow = static_cast<uint8_t*>(p.c) + (static_cast<int64_t>(bz) * p.m + row) * p.n * out_es;
+            // Each warp turns its 32 rows x (BN/2) columns into output in chunks of 128 bytes per row: the thread that owns
+            // a row (TMEM lane) writes its 128 bytes into a swizzled shared-memory tile, then the warp reads the tile back
+            // row-wise so that every global store instruction covers whole rows (coalesced), whatever the row pitch of C.
+            const int64_t row0 = static_cast<int64_t>(tm) * BM + quarter * 32;
+            const int chunk_cols = p.out_dtype == MHLO_DT_F32 ? 32 : 64;
+            uint8_t* stage_tile = smem + L::kStagingOff + (warp - 2) * 4096;
+            uint8_t* cbase = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(bz) * p.m * p.n * out_es;
+            // bias of this warp's BN/2 columns, spread over the lanes (column i lives in lane i / kBiasPerLane, register
+            // i % kBiasPerLane) and handed out with shuffles: one global load per column per tile instead of one per element
+            constexpr int kBiasPerLane = BN / 2 / 32;
+            float breg[kBiasPerLane];
+            const bool has_bias = p.bias != nullptr;
+#pragma unroll
+            for (int q = 0; q < kBiasPerLane; ++q) {
+                const int64_t col = static_cast<int64_t>(tn) * BN + col_begin + lane * kBiasPerLane + q;
+                float bv = 0.f;
+                if (has_bias && col < p.n) {
+                    if (p.out_dtype == MHLO_DT_F32) bv = static_cast<const float*>(p.bias)[col];
+                    else if (p.out_dtype == MHLO_DT_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+                    else bv = __half2float(static_cast<const __half*>(p.bias)[col]);
+                }
+                breg[q] = bv;
+            }
 #pragma unroll 1
-            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-                uint32_t r[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0);
-                tmem_ld32(taddr, r);
-                tmem_ld_wait();
+            for (int c0 = col_begin; c0 < col_end; c0 += chunk_cols) {
                 const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
-                if (!row_ok || col0 >= p.n) continue;
-                float v[32];
+                uint4 out16[8];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (p.bias != nullptr) {
+                for (int half = 0; half < 2; ++half) {
+                    if (half * 32 >= chunk_cols) break;
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0 + half * 32);
+                    tmem_ld32(taddr, r);
+                    tmem_ld_wait();
+                    float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int64_t col = col0 + j;
-                        float b = 0.f;
-                        if (col < p.n) {
-                            if (p.out_dtype == MHLO_DT_F32) b = static_cast<const float*>(p.bias)[col];
-                            else if (p.out_dtype == MHLO_DT_BF16) b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
-                            else b = __half2float(static_cast<const __half*>(p.bias)[col]);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (has_bias) {
+                        const int i0 = c0 - col_begin + half * 32;  // first column of this group inside the warp's range
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            // (i0 + j) / kBiasPerLane is the owning lane; i0 is a multiple of 32, so the register index is static
+                            v[j] += __shfl_sync(0xffffffffu, breg[j % kBiasPerLane], (i0 + j) / kBiasPerLane);
                         }
-                        v[j] += b;
+                    }
+                    if constexpr (ACT != MHLO_EPILOGUE_NONE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = epilogue_act<ACT>(v[j]);
+                    }
+                    if (p.out_dtype == MHLO_DT_F32) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            out16[j] = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+                    } else if (p.out_dtype == MHLO_DT_BF16) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                __nv_bfloat162 hh = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+                                w[q] = *reinterpret_cast<uint32_t*>(&hh);
+                            }
+                            out16[half * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                __half2 hh = __floats2half2_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+                                w[q] = *reinterpret_cast<uint32_t*>(&hh);
+                            }
+                            out16[half * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                     }
                 }
-                if (p.epilogue != MHLO_EPILOGUE_NONE) {
+                __syncwarp();  // the previous chunk's read-back is finished
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = epilogue_act(v[j], p.epilogue);
-                }
-                const bool full = col0 + 32 <= p.n;
-                if (p.out_dtype == MHLO_DT_F32) {
-                    float* dst = reinterpret_cast<float*>(crow) + col0;
-                    if (full && p.c_vec_ok) {
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(stage_tile + lane * 128 + ((c ^ (lane & 7)) << 4)) = out16[c];
+                __syncwarp();
+                const int64_t cols_left = p.n - col0;  // columns of this chunk that exist
+                if (cols_left <= 0) continue;
+                if (p.c_vec_ok && cols_left >= chunk_cols) {
+                    // 8 lanes cover one row's 128 bytes, four rows per instruction
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = v[j];
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), c = lane & 7;
+                        if (row0 + rr < p.m) {
+                            const uint4 val = *reinterpret_cast<const uint4*>(stage_tile + rr * 128 + ((c ^ (rr & 7)) << 4));
+                            *reinterpret_cast<uint4*>(cbase + ((row0 + rr) * p.n + col0) * out_es + c * 16) = val;
+                        }
                     }
                 } else {
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (p.out_dtype == MHLO_DT_BF16) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                    // ragged edge or a row pitch that is not 16-byte aligned: one row per instruction, 4 bytes per lane
+                    const int per_lane = out_es == 4 ? 1 : 2;  // elements in a lane's 4 bytes
+                    for (int rr = 0; rr < 32 && row0 + rr < p.m; ++rr) {
+                        const uint32_t word = *reinterpret_cast<const uint32_t*>(stage_tile + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
+                        uint8_t* dst = cbase + ((row0 + rr) * p.n + col0) * out_es;
+                        const int e0 = lane * per_lane;
+                        if (out_es == 4) {
+                            if (e0 < cols_left) reinterpret_cast<uint32_t*>(dst)[e0] = word;
                         } else {
-                            __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                            if (e0 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0] = static_cast<uint16_t>(word & 0xffffu);
+                            if (e0 + 1 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0 + 1] = static_cast<uint16_t>(word >> 16);
                         }
-                    }
-                    uint16_t* dst = reinterpret_cast<uint16_t*>(crow) + col0;
-                    if (full && p.c_vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 16; j += 4)
-                            *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.n; ++j)
-                            dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
                     }
                 }
             }
@@ -364,8 +415,8 @@ bool gemm_tc_supported(const GemmProblem& p) {
     return true;
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(const GemmProblem& pr, cudaStream_t stream) {
+template <int BN, int STAGES, int ACT>
+static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     const bool a_k = pr.as[3] == 1 || pr.k == 1;
     const bool b_k = pr.bs[2] == 1 || pr.k == 1;  // K-major B = [n][k] with k contiguous
@@ -395,7 +446,7 @@ static int launch_gemm(const GemmProblem& pr, cudaStream_t stream) {
     const size_t out_es = pr.out_dtype == MHLO_DT_F32 ? 4 : 2;
     p.c_vec_ok = aligned16(pr.c) && (pr.n * out_es) % 16 == 0;
 
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT>;
     static bool attr_set = false;
     if (!attr_set) {
         MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
@@ -405,6 +456,19 @@ static int launch_gemm(const GemmProblem& pr, cudaStream_t stream) {
     kernel<<<grid, kGemmThreads, L::kTotal, stream>>>(map_a, map_b, p);
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
+    switch (p.epilogue) {
+        case MHLO_EPILOGUE_RELU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_RELU>(p, stream);
+        case MHLO_EPILOGUE_GELU_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_TANH>(p, stream);
+        case MHLO_EPILOGUE_GELU_ERF: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_ERF>(p, stream);
+        case MHLO_EPILOGUE_SILU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SILU>(p, stream);
+        case MHLO_EPILOGUE_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_TANH>(p, stream);
+        case MHLO_EPILOGUE_SIGMOID: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SIGMOID>(p, stream);
+        default: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE>(p, stream);
+    }
 }
 
 int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
