@@ -255,6 +255,12 @@ def run_ours(args):
     e2e_ms = (time.perf_counter() - t0) * 1e3
     e2e_launches = exe.launch_count
 
+    extra = None
+    if not args.no_extras:
+        del x, x4, y, y_host
+        torch.cuda.empty_cache()
+        extra = measure_extras(torch, dist, cuda, rank, world, dev, load_peaks())
+
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -290,6 +296,8 @@ def run_ours(args):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
         }
+        if extra is not None:
+            line["extra"] = extra
         if cpu_gbs is not None:
             line["cpu_baseline"] = {
                 "value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
@@ -298,6 +306,114 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
+    """The other headline metrics of the hot path, each sharded the way its configuration prescribes and timed on the
+    device (max over ranks): bf16 GEMM 8192^3 (column split + NCCL all-gather when world > 1), the HBM-limited batched
+    GEMM, fused flash attention B8 H32 S4096 D128 (batch x head sharded), and the GPT-2-small forward pass (batch 32
+    sharded). Returned as a dict for the "extra" key of the JSON line."""
+    import math
+
+    import numpy as np
+
+    out = {}
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    g = torch.Generator(device=dev).manual_seed(42 + rank)
+    # ---- GEMM 8192^3 bf16: B and C column-split across ranks, C slices all-gathered and interleaved to row-major
+    n = 8192
+    ncols = n // world
+    a = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
+    b = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
+    c_slice = torch.empty(n, ncols, device=dev, dtype=torch.bfloat16)
+    c_all = torch.empty(world, n, ncols, device=dev, dtype=torch.bfloat16) if world > 1 else None
+    c_full = torch.empty(n, n, device=dev, dtype=torch.bfloat16) if world > 1 else None
+    a_str, b_str = cuda._i64s([0, 0, n, 1]), cuda._i64s([0, 0, n, 1])
+    b_ptr = b.data_ptr() + rank * ncols * 2
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def gemm_step():
+        cuda.check(cuda.lib.mhlo_cuda_gemm(cuda.BF16, cuda.BF16, a.data_ptr(), a_str, b_ptr, b_str, c_slice.data_ptr(), 1, 1, n,
+                                           ncols, n, None, 0, stream))
+        if world > 1:
+            dist.all_gather_into_tensor(c_all, c_slice)
+            c_full.view(n, world, ncols).copy_(c_all.permute(1, 0, 2))
+
+    ms = timed(gemm_step, 10)
+    tf = 2 * n ** 3 / ms / 1e9
+    out["gemm_bf16_8192"] = {"tflops": tf, "ms": ms, "frac_of_measured_peak": tf / (peaks["bf16_tflops"] * world),
+                             "parallelism": f"column split x{world}" + (" + NCCL all-gather" if world > 1 else "")}
+    del a, b, c_slice, c_all, c_full
+    # ---- batched GEMM [64,2048,128].[64,128,2048]: batch sharded, HBM-limited
+    nb = 64 // world if world <= 64 else 1
+    a = (torch.randn(nb, 2048, 128, device=dev, generator=g) / math.sqrt(128)).to(torch.bfloat16)
+    b = (torch.randn(nb, 128, 2048, device=dev, generator=g) / math.sqrt(128)).to(torch.bfloat16)
+    c = torch.empty(nb, 2048, 2048, device=dev, dtype=torch.bfloat16)
+    ms = timed(lambda: cuda.gemm(a, b, out=c), 10)
+    bytes_total = 603_979_776
+    out["gemm_bf16_batched"] = {"tflops": 68_719_476_736 / ms / 1e9, "gbs": bytes_total / ms / 1e6, "ms": ms,
+                                "frac_of_measured_hbm": bytes_total / ms / 1e6 / (peaks["hbm_gbs"] * world)}
+    del a, b, c
+    # ---- flash attention B8 H32 S4096 D128 bf16, batch sharded
+    bsz = max(1, 8 // world)
+    q, k, v = (torch.randn(bsz, 32, 4096, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
+    o = torch.empty_like(q)
+    for causal, flop in ((False, 2_199_023_255_552), (True, 1_099_780_063_232)):
+        ms = timed(lambda: cuda.attention(q, k, v, 1 / math.sqrt(128), causal=causal, out=o), 5)
+        tf = flop * (bsz * world / 8) / ms / 1e9
+        out["attention_causal" if causal else "attention"] = {"tflops": tf, "ms": ms,
+                                                              "frac_of_measured_peak": tf / (peaks["bf16_tflops"] * world)}
+    assert cuda.device_error() == 0, "a tensor-core kernel gave up on a bounded wait"
+    del q, k, v, o
+    # ---- GPT-2-small forward through the C API (O3), batch 32 sharded across ranks, fp16 compute, fp32 parameters
+    from metalhlo_b200 import capi, modules
+
+    batch = max(1, 32 // world)
+    text, params = modules.gpt2_module(batch=batch, seq=1024)
+    client = capi.Client()
+    exe = client.compile(text, opt_level=3)
+    rng = np.random.default_rng(7)
+    ins = []
+    for name, shape, dt in params:
+        if dt == "i32":
+            arr = rng.integers(0, 50257, size=shape).astype(np.int32)
+        elif name.endswith("_g"):
+            arr = np.ones(shape, np.float32)
+        elif name.endswith(("ln1_b", "ln2_b", "lnf_b")):
+            arr = np.zeros(shape, np.float32)
+        else:
+            arr = (0.02 * rng.standard_normal(shape)).astype(np.float32)
+        ins.append(client.buffer(arr))
+    logits = torch.empty(batch, 1024, 50257, device=dev, dtype=torch.float16)
+    in_ptrs = [b_.device_pointer for b_ in ins]
+
+    def gpt2_step():
+        exe.execute_on_device(in_ptrs, [logits.data_ptr()], stream)
+
+    ms = timed(gpt2_step, 5)
+    out["gpt2_small_fwd"] = {"tokens_per_s": batch * world * 1024 / (ms * 1e-3), "ms": ms, "batch_per_gpu": batch, "seq": 1024,
+                             "launches": exe.launch_count, "compute": "fp16, fp32 parameters converted inside the module",
+                             "logits": "fp16 [batch,1024,50257], left sharded"}
+    return out
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/), scaled to
@@ -320,6 +436,7 @@ def main():
     ap.add_argument("--workload", default="norms")
     ap.add_argument("--rows", type=int, default=ROWS,
                     help="rows of the norm sweep (default: the benchmark configuration; smaller for profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / attention / GPT-2 side measurements")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
