@@ -417,6 +417,42 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
     return out
 
 
+def profile_case(kind: str, launches: int):
+    """A few launches of one tensor-core kernel on a profiler-sized case (a few hundred MB on the device, inputs
+    larger than L2), for `ncu -k regex:<kernel>` captures. Prints the CUDA-event time per launch; no JSON line."""
+    import math
+
+    import torch
+
+    from metalhlo_b200 import cuda
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(1)
+    if kind == "gemm":
+        n = 8192
+        a = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
+        b = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
+        c = torch.empty(n, n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: cuda.gemm(a, b, out=c)  # noqa: E731
+        work, unit = 2 * n ** 3 / 1e12, "TFLOP"
+    else:
+        causal = kind == "attention_causal"
+        q, k, v = (torch.randn(2, 32, 4096, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
+        o = torch.empty_like(q)
+        fn = lambda: cuda.attention(q, k, v, 1 / math.sqrt(128), causal=causal, out=o)  # noqa: E731
+        work, unit = 4 * 2 * 32 * 4096 * 4096 * 128 / 1e12 * (0.5 if causal else 1.0), "TFLOP"
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(launches):
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        print(f"{kind} launch {i}: {ms:.3f} ms, {work / ms * 1e3:.1f} {unit}/s")
+    assert cuda.device_error() == 0
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/), scaled to
 # the full [32768, 4096] launch where the capture used fewer rows. None until a capture exists.
 TRAFFIC_BYTES: dict = {
@@ -440,7 +476,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / attention / GPT-2 side measurements")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (profiler captures)")
+    ap.add_argument("--profile-kernel", choices=["gemm", "attention", "attention_causal"],
+                    help="run a few launches of one tensor-core kernel on a profiler-sized case and exit")
     args = ap.parse_args()
+    if args.profile_kernel:
+        profile_case(args.profile_kernel, max(1, min(args.steps, 5)))
+        return
     if args.warmup < 3 and args.impl == "ours" and not args.kernels_only:
         args.warmup = 3
     ROWS = args.rows

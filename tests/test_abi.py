@@ -16,7 +16,9 @@ LIBDIR = os.path.join(ROOT, "metalhlo_b200", "lib")
 HEADERS = {
     "mhlo_cuda.h": "libmhlo_cuda.so",
     "metalhlo.h": "libCMetalHLO.so",
+    "pjrt_plugin_metalhlo.h": "pjrt_plugin_metalhlo_b200.so",
 }
+MIN_FUNCTIONS = {"pjrt_plugin_metalhlo.h": 1}
 
 
 def declared_functions(header_path):
@@ -36,14 +38,14 @@ def test_library_exports_every_declared_symbol(header):
     assert os.path.exists(so), f"{so} missing: run __graft_entry__.build()"
     lib = ctypes.CDLL(so)
     names = declared_functions(path)
-    assert len(names) >= 10
+    assert len(names) >= MIN_FUNCTIONS.get(header, 10)
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, f"{HEADERS[header]} does not export {missing}"
 
 
 def test_every_header_is_covered():
     for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
-        assert os.path.basename(h) in HEADERS or os.path.basename(h).startswith("pjrt"), h
+        assert os.path.basename(h) in HEADERS, h
 
 
 def test_python_binding_matches_header():
