@@ -84,6 +84,91 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         : "memory");
 }
 
+// Exponentials of one row's 128 scores: p = 2^(s * scale*log2e - m), packed to 16 bit and written over the score
+// columns they came from (keys [c, c+64) become 32 packed columns at c/2); returns the row's sum of p.
+// kMask: the block crosses the causal diagonal or the end of the keys; scores right of last_visible become -inf.
+// kCheck: m is a reference maximum carried over from earlier key blocks rather than this block's own. The
+// probabilities are then held back until the whole warp has seen sums below 2^15, which bounds every p below the
+// largest f16 / bf16 value; otherwise nothing is written, *stored is false and the caller redoes the block with its
+// true maximum (the scores are still intact).
+constexpr float kCarryLimit = 32768.f;
+template <bool kMask, bool kCheck>
+__device__ __forceinline__ float softmax_exp(uint32_t s_taddr, float scale_log2, float m_use, int key0, int last_visible, bool is_bf16,
+                                             bool* stored) {
+    const float2 c2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
+    float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    uint32_t packed[kBlockN / 64][32];
+#pragma unroll
+    for (int ci = 0; ci < kBlockN / 64; ++ci) {
+        uint32_t sr[64];
+        tmem_ld32(s_taddr + ci * 64, sr);
+        tmem_ld32(s_taddr + ci * 64 + 32, sr + 32);
+        tmem_ld_wait();
+        if (kMask) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+                if (key0 + ci * 64 + c > last_visible) sr[c] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
+            const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
+            packed[ci][c / 2] = pack16(e.x, e.y, is_bf16);
+        }
+        if (!kCheck) tmem_st32(s_taddr + ci * 32, packed[ci]);  // those score columns have been consumed already
+    }
+    const float rs = (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
+    if (kCheck) {
+        const bool safe = !__any_sync(0xffffffffu, !(rs < kCarryLimit));
+        if (safe) {
+#pragma unroll
+            for (int ci = 0; ci < kBlockN / 64; ++ci) tmem_st32(s_taddr + ci * 32, packed[ci]);
+        }
+        *stored = safe;
+    }
+    return rs;
+}
+
+// One unit of work: 256 query rows of one (batch, head).
+struct Tile {
+    int bat, head, m0;
+    int nblk;  // key blocks this tile visits (0: no key is visible to any of its rows)
+};
+
+// The tiles of one CTA. Tiles are numbered g = (batch*heads + head) * n_m + s, where position s inside a (batch, head)
+// alternates long and short query blocks (last, first, second-to-last, second, ...), so that under a causal mask two
+// consecutive tiles always add up to the same number of key blocks. A CTA takes pairs 2u, 2u+1 for
+// u = blockIdx.x, blockIdx.x + gridDim.x, ...: CTAs running at the same time work on neighbouring (batch, head)
+// and share their K and V through L2.
+struct TileWalk {
+    int n_m, total, u, e, step;
+    __device__ TileWalk(const AttnParams& p, int first, int stride)
+        : n_m((p.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM)), u(first), e(0), step(stride) {
+        total = n_m * p.heads * p.batch;
+    }
+    __device__ bool next(const AttnParams& p, Tile* t) {
+        int g = 2 * u + e;
+        if (g >= total) return false;
+        const int hb = g / n_m, s = g - hb * n_m;
+        const int mblk = (s & 1) ? (s >> 1) : n_m - 1 - (s >> 1);
+        t->bat = hb / p.heads;
+        t->head = hb - t->bat * p.heads;
+        t->m0 = mblk * kHalves * kBlockM;
+        int kv_len = p.seq_k;  // keys this tile visits: all, or up to the last key its last query row may see
+        if (p.causal) kv_len = min(p.seq_k, max(0, min(t->m0 + kHalves * kBlockM, p.seq_q) + p.seq_k - p.seq_q));
+        t->nblk = (kv_len + kBlockN - 1) / kBlockN;
+        if (++e == 2) { e = 0; u += step; }
+        return true;
+    }
+    // Next tile that has at least one key block (the producer and the MMA issuer skip the others).
+    __device__ bool next_nonempty(const AttnParams& p, Tile* t) {
+        while (next(p, t))
+            if (t->nblk > 0) return true;
+        return false;
+    }
+};
+
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -92,11 +177,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr int kPanels = D / 64;       // 64-element (128-byte) panels along the head dimension
     constexpr uint32_t kTmemCols = 512;   // S_h: 128 columns per half (P overwrites them in place), O_h: D columns per half
     constexpr uint32_t kSCol = 0, kOCol = kHalves * kBlockN;
+    constexpr int kQHalfBytes = kBlockM * D * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-    uint64_t* q_full = bars;
-    uint64_t* k_full = q_full + 1;
+    uint64_t* q_full = bars;                 // per half: the tile's query rows are in shared memory
+    uint64_t* q_empty = q_full + kHalves;    // per half: the tile's last S product has read them
+    uint64_t* k_full = q_empty + kHalves;
     uint64_t* k_empty = k_full + kKvStages;
     uint64_t* v_full = k_empty + kKvStages;
     uint64_t* v_empty = v_full + kKvStages;
@@ -106,21 +193,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kHalves);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int mblk = gridDim.x - 1 - blockIdx.x;  // heavy (late, for causal) query blocks first
-    const int head = blockIdx.y, bat = blockIdx.z;
-    const int m0 = mblk * kHalves * kBlockM;
     const int causal_off = p.seq_k - p.seq_q;
-    int kv_len = p.seq_k;  // keys this CTA visits: all, or up to the last key its last query row may see
-    if (p.causal) kv_len = min(p.seq_k, max(0, min(m0 + kHalves * kBlockM, p.seq_q) + causal_off));
-    const int nblk = (kv_len + kBlockN - 1) / kBlockN;
 
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&map_q);
         prefetch_tmap(&map_k);
         prefetch_tmap(&map_v);
-        mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int h = 0; h < kHalves; ++h) { mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1); }
+        for (int h = 0; h < kHalves; ++h) {
+            mbar_init(&q_full[h], 1); mbar_init(&q_empty[h], 1);
+            mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1);
+        }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -131,211 +214,234 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    TileWalk walk(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 
     if (warp == 0) {
-        // ---------------- producer ----------------
-        if (lane == 0 && nblk > 0) {
-            mbar_expect_tx(q_full, L::kQBytes);
-            for (int h = 0; h < kHalves; ++h)
-                for (int pn = 0; pn < kPanels; ++pn)
-                    tma_load_4d(smem + L::kQOff + (h * kPanels + pn) * kBlockM * 128, &map_q, q_full, pn * 64, m0 + h * kBlockM, head, bat);
+        // ---------------- producer: runs ahead of the other warps as far as the rings allow, across tile boundaries
+        if (lane == 0) {
+            Tile t;
             int stage = 0;
-            uint32_t phase = 0;
-            for (int j = 0; j < nblk; ++j) {
-                if (!mbar_wait(&k_empty[stage], phase ^ 1)) { atomicExch(&g_attn_error, 1); break; }
-                mbar_expect_tx(&k_full[stage], L::kKBytes);
-                for (int pn = 0; pn < kPanels; ++pn)
-                    tma_load_4d(smem + L::kKOff + stage * L::kKBytes + pn * kBlockN * 128, &map_k, &k_full[stage], pn * 64, j * kBlockN, head, bat);
-                if (!mbar_wait(&v_empty[stage], phase ^ 1)) { atomicExch(&g_attn_error, 2); break; }
-                mbar_expect_tx(&v_full[stage], L::kVBytes);
-                for (int pn = 0; pn < kPanels; ++pn)
-                    tma_load_4d(smem + L::kVOff + stage * L::kVBytes + pn * kBlockN * 128, &map_v, &v_full[stage], pn * 64, j * kBlockN, head, bat);
-                if (++stage == kKvStages) { stage = 0; phase ^= 1; }
+            uint32_t phase = 0, qn = 0;  // qn: tiles loaded so far (parity of the q barriers)
+            bool ok = true;
+            while (ok && walk.next_nonempty(p, &t)) {
+                for (int h = 0; h < kHalves && ok; ++h) {
+                    if (!mbar_wait(&q_empty[h], (qn & 1) ^ 1)) { atomicExch(&g_attn_error, 11); ok = false; break; }
+                    mbar_expect_tx(&q_full[h], kQHalfBytes);
+                    for (int pn = 0; pn < kPanels; ++pn)
+                        tma_load_4d(smem + L::kQOff + (h * kPanels + pn) * kBlockM * 128, &map_q, &q_full[h], pn * 64, t.m0 + h * kBlockM, t.head, t.bat);
+                }
+                for (int j = 0; j < t.nblk && ok; ++j) {
+                    if (!mbar_wait(&k_empty[stage], phase ^ 1)) { atomicExch(&g_attn_error, 1); ok = false; break; }
+                    mbar_expect_tx(&k_full[stage], L::kKBytes);
+                    for (int pn = 0; pn < kPanels; ++pn)
+                        tma_load_4d(smem + L::kKOff + stage * L::kKBytes + pn * kBlockN * 128, &map_k, &k_full[stage], pn * 64, j * kBlockN, t.head, t.bat);
+                    if (!mbar_wait(&v_empty[stage], phase ^ 1)) { atomicExch(&g_attn_error, 2); ok = false; break; }
+                    mbar_expect_tx(&v_full[stage], L::kVBytes);
+                    for (int pn = 0; pn < kPanels; ++pn)
+                        tma_load_4d(smem + L::kVOff + stage * L::kVBytes + pn * kBlockN * 128, &map_v, &v_full[stage], pn * 64, j * kBlockN, t.head, t.bat);
+                    if (++stage == kKvStages) { stage = 0; phase ^= 1; }
+                }
+                ++qn;
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp walks the schedule (uniform control flow keeps descriptors in
         // uniform registers); one elected lane issues the tcgen05 instructions ----------------
-        if (nblk > 0) {
-            const uint32_t fmt = p.is_bf16 ? 1u : 0u;
-            // S = Q K^T: both operands K-major from shared memory, N = 128 keys.
-            // O += P V: P from tensor memory (K-major), V from shared memory N-major (head dim contiguous), N = D.
-            const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
-            const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(smem + L::kQOff), k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
-            bool ok = mbar_wait(q_full, 0);
-            if (!ok) atomicExch(&g_attn_error, 3);
-            auto issue_s = [&](int h, int stage) {
-                const uint32_t qa = q_addr + h * kPanels * kBlockM * 128, ka = k_addr + stage * L::kKBytes;
+        const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+        // S = Q K^T: both operands K-major from shared memory, N = 128 keys.
+        // O += P V: P from tensor memory (K-major), V from shared memory N-major (head dim contiguous), N = D.
+        const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+        const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+        const uint32_t q_addr = smem_u32(smem + L::kQOff), k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
+        auto issue_s = [&](int h, int stage) {
+            const uint32_t qa = q_addr + h * kPanels * kBlockM * 128, ka = k_addr + stage * L::kKBytes;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t da = make_smem_desc(qa + (kk / 4) * kBlockM * 128 + (kk % 4) * 32, 16, 1024);
-                    const uint64_t db = make_smem_desc(ka + (kk / 4) * kBlockN * 128 + (kk % 4) * 32, 16, 1024);
-                    if (elect_one()) umma_f16(tmem_base + kSCol + h * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
-                }
-                if (elect_one()) umma_commit(&s_full[h]);
-                __syncwarp();
-            };
-            auto issue_pv = [&](int h, int stage, bool accumulate) {
-                const uint32_t va = v_addr + stage * L::kVBytes;
-#pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    // 16 keys of P = 8 packed 32-bit columns; 16 keys of V = 16 rows of 128 bytes in every head-dim panel
-                    const uint64_t db = make_smem_desc(va + kk * 16 * 128, kBlockN * 128, 1024);
-                    if (elect_one()) umma_f16_ts(tmem_base + kOCol + h * D, tmem_base + kSCol + h * kBlockN + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
-                }
-                if (elect_one()) umma_commit(&pv_done[h]);
-                __syncwarp();
-            };
-            int stage = 0;
-            uint32_t phase = 0;
-            if (ok) {
-                ok = mbar_wait(&k_full[0], 0);
-                if (ok) {
-                    tc_fence_after();
-                    issue_s(0, 0);
-                    issue_s(1, 0);
-                    if (elect_one()) umma_commit(&k_empty[0]);
-                    __syncwarp();
-                } else atomicExch(&g_attn_error, 4);
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint64_t da = make_smem_desc(qa + (kk / 4) * kBlockM * 128 + (kk % 4) * 32, 16, 1024);
+                const uint64_t db = make_smem_desc(ka + (kk / 4) * kBlockN * 128 + (kk % 4) * 32, 16, 1024);
+                if (elect_one()) umma_f16(tmem_base + kSCol + h * kBlockN, da, db, idesc_s, kk != 0 ? 1u : 0u);
             }
-            // Tensor-pipe order per key block j: PV_0(j), S_0(j+1), PV_1(j), S_1(j+1). The pipe executes one thread's MMAs in
-            // order, so S_h(j+1) overwrites the S/P columns only after PV_h(j) has read the probabilities from them.
-            for (int j = 0; j < nblk && ok; ++j) {
+            if (elect_one()) umma_commit(&s_full[h]);
+            __syncwarp();
+        };
+        auto issue_pv = [&](int h, int stage, bool accumulate) {
+            const uint32_t va = v_addr + stage * L::kVBytes;
+#pragma unroll
+            for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                // 16 keys of P = 8 packed 32-bit columns; 16 keys of V = 16 rows of 128 bytes in every head-dim panel
+                const uint64_t db = make_smem_desc(va + kk * 16 * 128, kBlockN * 128, 1024);
+                if (elect_one()) umma_f16_ts(tmem_base + kOCol + h * D, tmem_base + kSCol + h * kBlockN + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+            }
+            if (elect_one()) umma_commit(&pv_done[h]);
+            __syncwarp();
+        };
+        auto commit_to = [&](uint64_t* bar) {
+            if (elect_one()) umma_commit(bar);
+            __syncwarp();
+        };
+        Tile cur, nxt;
+        bool has_cur = walk.next_nonempty(p, &cur);
+        int stage = 0;
+        uint32_t phase = 0, it = 0, qn = 0;  // it: key blocks so far (parity of the per-block barriers); qn: tiles so far
+        bool ok = true;
+        if (has_cur) {
+            // first scores of the first tile
+            if (!mbar_wait(&q_full[0], 0) || !mbar_wait(&q_full[1], 0)) { ok = false; atomicExch(&g_attn_error, 3); }
+            if (ok && !mbar_wait(&k_full[0], 0)) { ok = false; atomicExch(&g_attn_error, 4); }
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, 0);
+                if (cur.nblk == 1) commit_to(&q_empty[0]);
+                issue_s(1, 0);
+                if (cur.nblk == 1) commit_to(&q_empty[1]);
+                commit_to(&k_empty[0]);
+            }
+        }
+        // Tensor-pipe order per key block j: PV_0(j), S_0(next), PV_1(j), S_1(next), where "next" is block j+1 of this
+        // tile or block 0 of the CTA's next tile. The pipe executes one thread's MMAs in order, so S_h(next) overwrites
+        // the S/P columns only after PV_h(j) has read the probabilities from them.
+        while (has_cur && ok) {
+            const bool has_nxt = walk.next_nonempty(p, &nxt);
+            for (int j = 0; j < cur.nblk && ok; ++j, ++it) {
                 const int nstage = stage + 1 == kKvStages ? 0 : stage + 1;
                 const uint32_t nphase = stage + 1 == kKvStages ? phase ^ 1 : phase;
+                const bool last = j + 1 == cur.nblk;
+                const bool more = !last || has_nxt;
+                const bool closes_q = more && (last ? nxt.nblk == 1 : j + 2 == cur.nblk);  // the S issued now is its tile's last
                 for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!mbar_wait(&p_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                    if (!mbar_wait(&p_full[h], it & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
                     if (h == 0 && !mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
                     tc_fence_after();
                     issue_pv(h, stage, j > 0);
-                    if (h == kHalves - 1) { if (elect_one()) umma_commit(&v_empty[stage]); __syncwarp(); }
-                    if (j + 1 < nblk) {
+                    if (h == kHalves - 1) commit_to(&v_empty[stage]);
+                    if (more) {
+                        if (last && !mbar_wait(&q_full[h], (qn + 1) & 1)) { ok = false; atomicExch(&g_attn_error, 12); break; }
                         if (h == 0 && !mbar_wait(&k_full[nstage], nphase)) { ok = false; atomicExch(&g_attn_error, 6); break; }
                         tc_fence_after();
                         issue_s(h, nstage);
-                        if (h == kHalves - 1) { if (elect_one()) umma_commit(&k_empty[nstage]); __syncwarp(); }
+                        if (closes_q) commit_to(&q_empty[h]);
+                        if (h == kHalves - 1) commit_to(&k_empty[nstage]);
                     }
                 }
                 stage = nstage;
                 phase = nphase;
             }
+            cur = nxt;
+            has_cur = has_nxt;
+            ++qn;
         }
     } else {
         // ---------------- softmax warpgroups ----------------
         const int h = (warp - 2) >> 2;       // which half of the query block
         const int quarter = warp & 3;        // TMEM lanes this warp may touch
         const int r = quarter * 32 + lane;   // row inside the half
-        const int qi = m0 + h * kBlockM + r; // query index
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t s_taddr = tmem_base + lane_base + kSCol + h * kBlockN;
         const uint32_t o_taddr = tmem_base + lane_base + kOCol + h * D;
-        const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
-        float m_ref = -INFINITY, l = 0.f;
+        Tile t;
+        uint32_t it = 0;  // key blocks so far on this CTA (parity of the per-block barriers)
         bool ok = true;
-        for (int j = 0; j < nblk; ++j) {
-            if (!mbar_wait(&s_full[h], j & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
-            tc_fence_after();
-            const int key0 = j * kBlockN;
-            const bool need_mask = key0 + kBlockN - 1 > last_visible;  // diagonal or ragged block
-            // ---- pass 1: row maximum of the raw scores (scale > 0, so scaling commutes with max) ----
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c0 = 0; c0 < kBlockN; c0 += 64) {
-                uint32_t sr[64];
-                tmem_ld32(s_taddr + c0, sr);
-                tmem_ld32(s_taddr + c0 + 32, sr + 32);
-                tmem_ld_wait();
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (key0 + c0 + c > last_visible) sr[c] = 0xff800000u;  // -inf
+        while (walk.next(p, &t)) {
+            const int qi = t.m0 + h * kBlockM + r;  // query index
+            const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = 0; j < t.nblk && ok; ++j, ++it) {
+                if (!mbar_wait(&s_full[h], it & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
+                tc_fence_after();
+                const int key0 = j * kBlockN;
+                const bool need_mask = key0 + kBlockN - 1 > last_visible;  // diagonal or ragged block
+                // one decision per warp: tcgen05.ld / st are warp-wide instructions and must not sit in divergent code
+                const bool mask_block = __any_sync(0xffffffffu, need_mask);
+                // ---- after a tile's first block: one pass, exponentials against the reference maximum carried over from
+                // the earlier blocks; it fails (rarely) when a row's scores have grown by more than 2^15
+                bool done = false;
+                if (j > 0) {
+                    const float m_carry = m_ref == -INFINITY ? 0.f : m_ref;
+                    const float rs = mask_block ? softmax_exp<true, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done)
+                                                : softmax_exp<false, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done);
+                    if (done) l += rs;
                 }
+                if (!done) {
+                    // ---- pass 1: row maximum of the raw scores (scale > 0, so scaling commutes with max) ----
+                    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 64; c += 4)
+                    for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+                        uint32_t sr[64];
+                        tmem_ld32(s_taddr + c0, sr);
+                        tmem_ld32(s_taddr + c0 + 32, sr + 32);
+                        tmem_ld_wait();
+                        if (need_mask) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(sr[c + u]));
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            // advance the reference maximum only when it would otherwise let exponentials exceed 2^threshold
-            const bool grow = mx > m_ref + kRescaleThreshold;
-            float alpha = 1.f;
-            if (grow) {
-                alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
-                m_ref = mx;
-                l *= alpha;
-            }
-            // every PV product issued so far completed before these scores were signalled, so O may be rescaled here
-            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                            for (int c = 0; c < 64; ++c)
+                                if (key0 + c0 + c > last_visible) sr[c] = 0xff800000u;  // -inf
+                        }
+#pragma unroll
+                        for (int c = 0; c < 64; c += 4) {
+                            mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+                            mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+                        }
+                    }
+                    const float mx = fmaxf(mx0, mx1) * p.scale_log2;
+                    // advance the reference maximum only when it would otherwise let exponentials exceed 2^threshold
+                    const bool grow = mx > m_ref + kRescaleThreshold;
+                    float alpha = 1.f;
+                    if (grow) {
+                        alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
+                        m_ref = mx;
+                        l *= alpha;
+                    }
+                    // every PV product issued so far completed before these scores were signalled, so O may be rescaled here
+                    if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t orow[32];
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            uint32_t orow[32];
+                            tmem_ld32(o_taddr + c0, orow);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                            tmem_st32(o_taddr + c0, orow);
+                        }
+                    }
+                    // ---- pass 2: p = 2^(s * scale*log2e - m), packed to 16 bit and written over the scores ----
+                    const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                    l += mask_block ? softmax_exp<true, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr)
+                                    : softmax_exp<false, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[h]);
+            }
+            if (!ok) break;
+            // ---- write O / l. The next tile's first PV product for this half is issued only after this warp has
+            // arrived on p_full again, which comes after the loads below, so O may be read here without another barrier.
+            if (t.nblk > 0) {
+                if (!mbar_wait(&pv_done[h], (it - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); break; }
+                tc_fence_after();
+            }
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            uint8_t* orow_ptr = static_cast<uint8_t*>(p.o) + (static_cast<int64_t>(t.bat) * p.os[0] + static_cast<int64_t>(t.head) * p.os[1] +
+                                                             static_cast<int64_t>(qi) * p.os[2]) * 2;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t orow[32];
+                if (t.nblk > 0) {
                     tmem_ld32(o_taddr + c0, orow);
                     tmem_ld_wait();
+                } else {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                    tmem_st32(o_taddr + c0, orow);
+                    for (int c = 0; c < 32; ++c) orow[c] = 0u;
                 }
-            }
-            // ---- pass 2: p = 2^(s * scale*log2e - m), packed to 16 bit and written over the scores ----
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
-            float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                if (qi < p.seq_q) {
 #pragma unroll
-            for (int c0 = 0; c0 < kBlockN; c0 += 64) {
-                uint32_t sr[64];
-                tmem_ld32(s_taddr + c0, sr);
-                tmem_ld32(s_taddr + c0 + 32, sr + 32);
-                tmem_ld_wait();
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (key0 + c0 + c > last_visible) sr[c] = 0xff800000u;
-                }
-                uint32_t packed[32];
-#pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
-                    const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                    rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
-                    packed[c / 2] = pack16(e.x, e.y, p.is_bf16 != 0);
-                }
-                // keys [c0, c0+64) as 32 packed columns at column c0/2: those score columns have been consumed already
-                tmem_st32(s_taddr + c0 / 2, packed);
-            }
-            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[h]);
-        }
-        // ---- write O / l ----
-        if (ok && nblk > 0) {
-            if (!mbar_wait(&pv_done[h], (nblk - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 10); }
-            tc_fence_after();
-        }
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        uint8_t* orow_ptr = static_cast<uint8_t*>(p.o) + (static_cast<int64_t>(bat) * p.os[0] + static_cast<int64_t>(head) * p.os[1] +
-                                                         static_cast<int64_t>(qi) * p.os[2]) * 2;
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t orow[32];
-            if (ok && nblk > 0) {
-                tmem_ld32(o_taddr + c0, orow);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) orow[c] = 0u;
-            }
-            if (qi < p.seq_q) {
-#pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    uint4 w;
-                    w.x = pack16(__uint_as_float(orow[c]) * inv, __uint_as_float(orow[c + 1]) * inv, p.is_bf16 != 0);
-                    w.y = pack16(__uint_as_float(orow[c + 2]) * inv, __uint_as_float(orow[c + 3]) * inv, p.is_bf16 != 0);
-                    w.z = pack16(__uint_as_float(orow[c + 4]) * inv, __uint_as_float(orow[c + 5]) * inv, p.is_bf16 != 0);
-                    w.w = pack16(__uint_as_float(orow[c + 6]) * inv, __uint_as_float(orow[c + 7]) * inv, p.is_bf16 != 0);
-                    *reinterpret_cast<uint4*>(orow_ptr + (c0 + c) * 2) = w;
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        w.x = pack16(__uint_as_float(orow[c]) * inv, __uint_as_float(orow[c + 1]) * inv, p.is_bf16 != 0);
+                        w.y = pack16(__uint_as_float(orow[c + 2]) * inv, __uint_as_float(orow[c + 3]) * inv, p.is_bf16 != 0);
+                        w.z = pack16(__uint_as_float(orow[c + 4]) * inv, __uint_as_float(orow[c + 5]) * inv, p.is_bf16 != 0);
+                        w.w = pack16(__uint_as_float(orow[c + 6]) * inv, __uint_as_float(orow[c + 7]) * inv, p.is_bf16 != 0);
+                        *reinterpret_cast<uint4*>(orow_ptr + (c0 + c) * 2) = w;
+                    }
                 }
             }
         }
@@ -408,8 +514,15 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
         MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
         attr_set = true;
     }
-    dim3 grid(static_cast<unsigned>((s.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM)), static_cast<unsigned>(s.heads),
-              static_cast<unsigned>(s.batch));
+    // persistent grid: one CTA per SM, each walking its share of the (batch, head, query block) tiles in pairs
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        MHLO_CUDA_TRY(cudaGetDevice(&dev), MHLO_CUDA_EXECUTION_FAILED);
+        MHLO_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), MHLO_CUDA_EXECUTION_FAILED);
+    }
+    const int64_t tiles = (s.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM) * s.heads * s.batch;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>((tiles + 1) / 2, sm_count));
     kernel<<<grid, kAttnThreads, L::kTotal, stream>>>(mq, mk, mv, p);
     MHLO_CUDA_CHECK_LAUNCH("attention_tcgen05");
     return MHLO_CUDA_OK;
@@ -434,6 +547,7 @@ bool attention_tc_supported(int dtype, const AttnShape& s, const void* mask) {
     if (s.head_dim != 64 && s.head_dim != 128) return false;
     if (s.seq_q < 1 || s.seq_k < 1 || s.heads < 1 || s.batch < 1 || s.heads > 65535 || s.batch > 65535) return false;
     if (s.seq_q > 0x3fffffff || s.seq_k > 0x3fffffff) return false;
+    if ((s.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM) * s.heads * s.batch > 0x3fffffff) return false;  // tile index is an int
     if (s.seq_q * s.seq_k < 64 * 64) return false;  // tiny problems: the row kernel has less fixed cost
     auto ok3 = [&](const int64_t* st, int64_t seq) {
         return (seq == 1 || stride16(st[2])) && (s.heads == 1 || stride16(st[1])) && (s.batch == 1 || stride16(st[0]));
