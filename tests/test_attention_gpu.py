@@ -67,6 +67,49 @@ def test_large_scores_trigger_rescaling():
     assert_close(to_np(got), reference(q, k, v, 0.5, False, "BHSD"), 2e-2, "rescale")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+def test_scores_growing_past_the_carried_reference(dtype):
+    """After a tile's first key block the kernel exponentiates against the maximum carried over from earlier blocks and
+    falls back to a fresh maximum when a row sum reaches 2^15. Keys whose norm jumps by 40x half way force that fallback
+    (and, for f16, would overflow the probabilities without it)."""
+    cuda = cuda_mod()
+    b, h, s, d = 1, 2, 1024, 128
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(b, h, s, d, generator=g)
+    gain = torch.where(torch.arange(s) < 640, 0.05, 2.0).view(1, 1, s, 1)
+    k = torch.randn(b, h, s, d, generator=g) * gain
+    v = torch.randn(b, h, s, d, generator=g)
+    q, k, v = (t.to(dtype) for t in (q, k, v))
+    for causal in (False, True):
+        got = cuda.attention(q.cuda(), k.cuda(), v.cuda(), 0.5, causal=causal)
+        assert cuda.device_error() == 0
+        assert np.isfinite(to_np(got)).all()
+        assert_close(to_np(got), reference(q, k, v, 0.5, causal, "BHSD"), 2e-2, f"carried reference causal={causal}")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_more_tiles_than_resident_ctas(causal):
+    """320 tiles on at most 148 persistent CTAs: every CTA walks several tiles, so barrier phases, the Q buffers and the
+    TMEM accumulators are handed from one tile to the next."""
+    cuda = cuda_mod()
+    q, k, v = qkv(4, 20, 1024, 1024, 64, torch.bfloat16, "BHSD", seed=21)
+    got = cuda.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, causal=causal)
+    assert cuda.device_error() == 0
+    assert_close(to_np(got), reference(q, k, v, 0.125, causal, "BHSD"), 2e-2, f"many tiles causal={causal}", row_scale=True)
+
+
+def test_causal_tiles_without_any_visible_key():
+    """seq_q > seq_k under a causal mask: the first query blocks see no key at all (rows of zeros, as the oracle
+    gives), and such tiles sit between ordinary ones in a CTA's walk."""
+    cuda = cuda_mod()
+    q, k, v = qkv(2, 40, 768, 256, 128, torch.bfloat16, "BHSD", seed=23)
+    got = cuda.attention(q.cuda(), k.cuda(), v.cuda(), 0.1, causal=True)
+    assert cuda.device_error() == 0
+    want = reference(q, k, v, 0.1, True, "BHSD")
+    assert np.all(to_np(got)[:, :, :512, :] == 0) and np.all(want[:, :, :512, :] == 0)
+    assert_close(to_np(got), want, 2e-2, "empty tiles", row_scale=True)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
 def test_general_layout_kernel(dtype):
     cuda = cuda_mod()
