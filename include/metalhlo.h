@@ -165,6 +165,34 @@ void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer);
 MHLOStatusCode mhlo_b200_execute_on_device(MHLOExecutableRef executable, const void* const* input_ptrs,
                                            void* const* output_ptrs, void* stream);
 
+
+/* ---- kernel tuning (reference: Sources/MetalHLOCore/Tuning/TuningDatabase.swift:15-290, AutoTuner.swift:225-764;
+ * the reference exposes these only to Swift callers). One database per process, opened from `path` (or from
+ * $METALHLO_TUNING_DB on first use). Executables compiled afterwards look their fused LayerNorm / RMSNorm / softmax
+ * launches up in it by (operation, shape, dtype, device name) and fall back to the library's heuristics. */
+/* Opens (and loads, when the file exists) the process database. NULL path: $METALHLO_TUNING_DB. */
+MHLOStatusCode mhlo_b200_tuning_open(const char* path);
+/* Entries currently held; -1 when no database is open. */
+int64_t mhlo_b200_tuning_count(void);
+/* Measures every candidate launch configuration of a row kernel on the client's device (5 warm-up + 20 timed
+ * launches each, median) and stores the best. kernel: "fused_layer_norm" | "fused_rms_norm" | "fused_softmax".
+ * max_trials <= 0: all candidates. *out_record_json (optional) receives the stored record; free with mhlo_free_string. */
+MHLOStatusCode mhlo_b200_tuning_tune_row_kernel(MHLOClientRef client, const char* kernel, MHLOElementType element_type,
+                                                int64_t rows, int64_t hidden, int32_t max_trials, char** out_record_json);
+/* Merges records given as a database document (the file format: {"version": 1, "entries": [key, result, ...]});
+ * existing keys win unless overwrite. Host-only. *out_taken (optional) = entries taken. */
+MHLOStatusCode mhlo_b200_tuning_merge_json(const char* database_json, bool overwrite, int32_t* out_taken);
+/* The whole database as JSON text (the file format); free with mhlo_free_string. NULL when none is open. */
+char* mhlo_b200_tuning_to_json(void);
+/* Writes the file if anything changed. */
+MHLOStatusCode mhlo_b200_tuning_save(void);
+/* Merges another database file (existing keys win unless overwrite); *out_taken (optional) = entries taken. */
+MHLOStatusCode mhlo_b200_tuning_import(const char* other_path, bool overwrite, int32_t* out_taken);
+/* Drops entries older than max_age_days; returns how many, -1 when no database is open. */
+int32_t mhlo_b200_tuning_prune(double max_age_days);
+/* Forgets every entry (the file changes on the next save). */
+void mhlo_b200_tuning_clear(void);
+
 #ifdef __cplusplus
 }
 #endif

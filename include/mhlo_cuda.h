@@ -67,6 +67,8 @@ size_t mhlo_cuda_dtype_size(int dtype);
 int mhlo_cuda_device_count(int* out_count);
 /* Makes `ordinal` current on the calling thread. */
 int mhlo_cuda_device_set(int ordinal);
+/* Ordinal of the device that is current on the calling thread. */
+int mhlo_cuda_device_current(int* out_ordinal);
 /* Writes the device name into out_name (NUL-terminated, truncated to cap). */
 int mhlo_cuda_device_name(int ordinal, char* out_name, size_t cap);
 int mhlo_cuda_stream_create(mhlo_cuda_stream_t* out_stream);

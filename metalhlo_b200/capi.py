@@ -110,6 +110,15 @@ _PROTOTYPES = {
     "mhlo_b200_executable_steps": (_vp, [_vp]),
     "mhlo_b200_buffer_device_pointer": (_vp, [_vp]),
     "mhlo_b200_execute_on_device": (C.c_int, [_vp, _P(_vp), _P(_vp), _vp]),
+    "mhlo_b200_tuning_open": (C.c_int, [C.c_char_p]),
+    "mhlo_b200_tuning_count": (_i64, []),
+    "mhlo_b200_tuning_tune_row_kernel": (C.c_int, [_vp, C.c_char_p, C.c_int, _i64, _i64, _i32, _P(_vp)]),
+    "mhlo_b200_tuning_merge_json": (C.c_int, [C.c_char_p, C.c_bool, _P(_i32)]),
+    "mhlo_b200_tuning_to_json": (_vp, []),
+    "mhlo_b200_tuning_save": (C.c_int, []),
+    "mhlo_b200_tuning_import": (C.c_int, [C.c_char_p, C.c_bool, _P(_i32)]),
+    "mhlo_b200_tuning_prune": (_i32, [C.c_double]),
+    "mhlo_b200_tuning_clear": (None, []),
 }
 for _name, (_res, _args) in _PROTOTYPES.items():
     _fn = getattr(lib, _name)
@@ -146,6 +155,59 @@ def optimize_text(mlir: str, opt_level: int = 3) -> str:
     out = _vp()
     _check(lib.mhlo_b200_optimize_text(mlir.encode(), opt_level, C.byref(out)))
     return _take_string(out.value)
+
+
+class tuning:
+    """The process tuning database (mhlo_b200_tuning_*): measured launch configurations keyed by operation, shape,
+    dtype and device name, persisted as JSON."""
+
+    @staticmethod
+    def open(path: str) -> None:
+        _check(lib.mhlo_b200_tuning_open(path.encode()))
+
+    @staticmethod
+    def count() -> int:
+        return int(lib.mhlo_b200_tuning_count())
+
+    @staticmethod
+    def merge(document: dict, overwrite: bool = False) -> int:
+        import json
+
+        taken = _i32(0)
+        _check(lib.mhlo_b200_tuning_merge_json(json.dumps(document).encode(), overwrite, C.byref(taken)))
+        return taken.value
+
+    @staticmethod
+    def to_dict() -> dict:
+        import json
+
+        return json.loads(_take_string(lib.mhlo_b200_tuning_to_json()))
+
+    @staticmethod
+    def save() -> None:
+        _check(lib.mhlo_b200_tuning_save())
+
+    @staticmethod
+    def import_file(path: str, overwrite: bool = False) -> int:
+        taken = _i32(0)
+        _check(lib.mhlo_b200_tuning_import(path.encode(), overwrite, C.byref(taken)))
+        return taken.value
+
+    @staticmethod
+    def prune(max_age_days: float) -> int:
+        return int(lib.mhlo_b200_tuning_prune(max_age_days))
+
+    @staticmethod
+    def clear() -> None:
+        lib.mhlo_b200_tuning_clear()
+
+    @staticmethod
+    def tune_row_kernel(client, kernel: str, element_type: int, rows: int, hidden: int, max_trials: int = 0) -> dict:
+        import json
+
+        out = _vp()
+        _check(lib.mhlo_b200_tuning_tune_row_kernel(client._h, kernel.encode(), element_type, rows, hidden, max_trials, C.byref(out)))
+        return json.loads(_take_string(out.value))
 
 
 class Buffer:

@@ -5,6 +5,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <ctime>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -14,6 +15,7 @@
 #include "../../../include/metalhlo.h"
 #include "../../../include/mhlo_cuda.h"
 #include "compiler.h"
+#include "tuning.h"
 
 using namespace mhlo;
 
@@ -468,6 +470,88 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
     } catch (const std::exception& e) {
         return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
     }
+}
+
+// ---- kernel tuning -----------------------------------------------------------------------------------------------
+
+MHLOStatusCode mhlo_b200_tuning_open(const char* path) {
+    if (path && *path) {
+        TuningDatabase::open_global(path);
+        return MHLO_OK;
+    }
+    if (!TuningDatabase::global()) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no path given and METALHLO_TUNING_DB is not set"));
+    return MHLO_OK;
+}
+
+int64_t mhlo_b200_tuning_count(void) {
+    TuningDatabase* db = TuningDatabase::global();
+    return db ? static_cast<int64_t>(db->count()) : -1;
+}
+
+MHLOStatusCode mhlo_b200_tuning_tune_row_kernel(MHLOClientRef client, const char* kernel, MHLOElementType element_type, int64_t rows,
+                                                int64_t hidden, int32_t max_trials, char** out_record_json) {
+    if (out_record_json) *out_record_json = nullptr;
+    Client* c = static_cast<Client*>(client);
+    if (!c || !kernel) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null client or kernel name"));
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open"));
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    TuningRecord rec;
+    std::string why;
+    const int st = tune_row_kernel(kernel, static_cast<int>(element_type), rows, hidden, max_trials, db, &rec, &why);
+    if (st == MHLO_CUDA_INVALID_ARGUMENT) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, why));
+    if (st != MHLO_CUDA_OK) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_EXECUTION_FAILED, why));
+    if (out_record_json) {
+        char buf[512];
+        snprintf(buf, sizeof buf,
+                 "{\"bestConfig\": {\"threads\": %d, \"vectorsPerThread\": %d, \"ctasPerSM\": %d}, \"measuredTime\": %.9g, "
+                 "\"gbytesPerSecond\": %.6g, \"configsTried\": %d}",
+                 rec.best.threads, rec.best.vectors_per_thread, rec.best.ctas_per_sm, rec.measured_time_s, rec.gbytes_per_s, rec.configs_tried);
+        *out_record_json = strdup(buf);
+    }
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_b200_tuning_merge_json(const char* database_json, bool overwrite, int32_t* out_taken) {
+    if (out_taken) *out_taken = 0;
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open"));
+    if (!database_json) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null document"));
+    std::string why;
+    const int taken = db->merge_json(database_json, overwrite, &why);
+    if (taken < 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_PARSE_FAILED, why));
+    if (out_taken) *out_taken = taken;
+    return MHLO_OK;
+}
+
+char* mhlo_b200_tuning_to_json(void) {
+    TuningDatabase* db = TuningDatabase::global();
+    return db ? strdup(db->to_json().c_str()) : nullptr;
+}
+
+MHLOStatusCode mhlo_b200_tuning_save(void) {
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open"));
+    if (!db->save()) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, "cannot write " + db->path()));
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_b200_tuning_import(const char* other_path, bool overwrite, int32_t* out_taken) {
+    if (out_taken) *out_taken = 0;
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db || !other_path) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open, or null path"));
+    const int taken = db->import_from(other_path, overwrite);
+    if (out_taken) *out_taken = taken;
+    return MHLO_OK;
+}
+
+int32_t mhlo_b200_tuning_prune(double max_age_days) {
+    TuningDatabase* db = TuningDatabase::global();
+    return db ? db->prune(max_age_days, static_cast<double>(std::time(nullptr))) : -1;
+}
+
+void mhlo_b200_tuning_clear(void) {
+    if (TuningDatabase* db = TuningDatabase::global()) db->clear();
 }
 
 // Kernel launches one execution enqueues, the arena size and a newline-separated list of step labels.

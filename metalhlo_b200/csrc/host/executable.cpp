@@ -16,6 +16,7 @@
 
 #include "../../../include/mhlo_cuda.h"
 #include "compiler.h"
+#include "tuning.h"
 #include "numeric.h"
 
 namespace mhlo {
@@ -196,6 +197,29 @@ int ew_opcode(const std::string& n) {
 }  // namespace
 
 int elementwise_opcode(const std::string& name) { return ew_opcode(name); }
+
+// Launch configuration of a fused row kernel from the process tuning database, when it holds one for this operation,
+// shape, dtype and device (TuningDatabase.get in the reference's compile path, Tuning/AutoTuner.swift:301-333).
+bool lookup_row_tuning(const std::string& kind, int64_t rows, int64_t hidden, DType dt, mhlo_cuda_row_tuning* out) {
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return false;
+    static std::string device_name = [] {
+        char name[256] = "";
+        int ordinal = 0;
+        if (mhlo_cuda_device_current(&ordinal) == MHLO_CUDA_OK) mhlo_cuda_device_name(ordinal, name, sizeof name);
+        return std::string(name);
+    }();
+    TuningKey key;
+    key.op_type = kind;
+    key.shapes = {{rows, hidden}};
+    key.dtype = dt == DType::BF16 ? "bf16" : dt == DType::F16 ? "f16" : "f32";
+    key.device = device_name;
+    TuningRecord rec;
+    if (!db->get(key, &rec)) return false;
+    if (!rec.best.threads && !rec.best.vectors_per_thread && !rec.best.ctas_per_sm) return false;  // the default won
+    *out = mhlo_cuda_row_tuning{rec.best.threads, rec.best.vectors_per_thread, rec.best.ctas_per_sm};
+    return true;
+}
 
 class Lowering {
   public:
@@ -813,11 +837,14 @@ void Lowering::lower_custom_call(const Op& op) {
         if (has_g) { dg = dev(g); keep_alive(g); }
         if (has_b) { db = dev(b); keep_alive(b); }
         const int dt = static_cast<int>(x.type.dtype);
-        add_step(target, [=](const Ctx& c) {
+        mhlo_cuda_row_tuning tuning{0, 0, 0};
+        const bool tuned = lookup_row_tuning(target, rows, hidden, x.type.dtype, &tuning);
+        add_step(tuned ? target + " [tuned]" : target, [=](const Ctx& c) {
             const void* gp = has_g ? bind(dg, c).base : nullptr;
             const void* bp = has_b ? bind(db, c).base : nullptr;
-            if (ln) return mhlo_cuda_layer_norm(dt, bind(dx, c).base, gp, bp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, nullptr, c.stream);
-            return mhlo_cuda_rms_norm(dt, bind(dx, c).base, gp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, nullptr, c.stream);
+            const mhlo_cuda_row_tuning* tp = tuned ? &tuning : nullptr;
+            if (ln) return mhlo_cuda_layer_norm(dt, bind(dx, c).base, gp, bp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, tp, c.stream);
+            return mhlo_cuda_rms_norm(dt, bind(dx, c).base, gp, const_cast<void*>(bind(dout, c).base), rows, hidden, eps, tp, c.stream);
         });
         return set(op.results[0], out);
     }
@@ -834,8 +861,10 @@ void Lowering::lower_custom_call(const Op& op) {
         DevView dx = dev(x), dout = dev(out);
         keep_alive(x); keep_alive(out);
         const int dt = static_cast<int>(x.type.dtype);
-        add_step(target, [=](const Ctx& c) {
-            return mhlo_cuda_softmax(dt, bind(dx, c).base, const_cast<void*>(bind(dout, c).base), outer, len, inner, nullptr, c.stream);
+        mhlo_cuda_row_tuning tuning{0, 0, 0};
+        const bool tuned = inner == 1 && lookup_row_tuning(target, outer, len, x.type.dtype, &tuning);
+        add_step(tuned ? target + " [tuned]" : target, [=](const Ctx& c) {
+            return mhlo_cuda_softmax(dt, bind(dx, c).base, const_cast<void*>(bind(dout, c).base), outer, len, inner, tuned ? &tuning : nullptr, c.stream);
         });
         return set(op.results[0], out);
     }

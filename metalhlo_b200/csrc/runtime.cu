@@ -57,6 +57,12 @@ int mhlo_cuda_device_set(int ordinal) {
     return MHLO_CUDA_OK;
 }
 
+int mhlo_cuda_device_current(int* out_ordinal) {
+    if (!out_ordinal) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_current: null output");
+    MHLO_CUDA_TRY(cudaGetDevice(out_ordinal), MHLO_CUDA_NO_DEVICE);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_device_name(int ordinal, char* out_name, size_t cap) {
     if (!out_name || cap == 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_name: no output buffer");
     cudaDeviceProp prop;

@@ -57,6 +57,7 @@ _PROTOTYPES = {
     "mhlo_cuda_dtype_size": (_sz, [C.c_int]),
     "mhlo_cuda_device_count": (C.c_int, [C.POINTER(C.c_int)]),
     "mhlo_cuda_device_set": (C.c_int, [C.c_int]),
+    "mhlo_cuda_device_current": (C.c_int, [C.POINTER(C.c_int)]),
     "mhlo_cuda_device_name": (C.c_int, [C.c_int, C.c_char_p, _sz]),
     "mhlo_cuda_stream_create": (C.c_int, [C.POINTER(_vp)]),
     "mhlo_cuda_stream_destroy": (C.c_int, [_vp]),
