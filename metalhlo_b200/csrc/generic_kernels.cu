@@ -508,6 +508,95 @@ __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ Red
     }
 }
 
+// ---- split reduce: few outputs, long reductions -------------------------------------------------------------------
+// reduce_kernel gives one output element to at most one CTA, so a reduction to a scalar (or a handful of values) would
+// run on a single SM. Here every output's reduced range is cut into `splits` segments, one CTA each, whose partial
+// accumulators go to scratch memory (partials[o * splits + s]); a second kernel folds the partials, and the init
+// value, in a fixed order and writes the result. Scratch = n_out * splits * sizeof(Acc) bytes.
+
+struct SplitPlan {
+    int splits;
+    int64_t chunk;  // reduced elements per segment (multiple of 256)
+    size_t scratch_bytes;
+};
+
+// splits == 0: chosen so that n_out * splits is about four CTAs per SM.
+inline bool plan_split(int64_t n_out, int64_t n_red, int requested_splits, SplitPlan* plan) {
+    if (n_out < 1 || n_out > 65535 || n_red < 1) return false;
+    int64_t splits = requested_splits > 0 ? requested_splits : std::max<int64_t>(1, (148 * 4) / n_out);
+    splits = std::min<int64_t>(splits, (n_red + 255) / 256);
+    int64_t chunk = (n_red + splits - 1) / splits;
+    chunk = (chunk + 255) / 256 * 256;
+    splits = (n_red + chunk - 1) / chunk;
+    plan->splits = static_cast<int>(splits);
+    plan->chunk = chunk;
+    plan->scratch_bytes = static_cast<size_t>(n_out) * static_cast<size_t>(splits) * sizeof(Acc<int64_t>);
+    return true;
+}
+
+template <typename A>
+__global__ void __launch_bounds__(256) reduce_split_kernel(const __grid_constant__ ReduceParams p, Acc<A>* partials, int splits, int64_t chunk) {
+    __shared__ Acc<A> sm[8];
+    const int64_t o = blockIdx.y;
+    const int s = blockIdx.x;
+    const int n_red_dims = p.in.rank - p.n_kept;
+    int64_t base = 0, rem_o = o;
+    for (int d = p.n_kept - 1; d >= 0; --d) {
+        base += (rem_o % p.in.shape[d]) * p.in.stride[d];
+        rem_o /= p.in.shape[d];
+    }
+    const int64_t r_end = min(p.n_red, (static_cast<int64_t>(s) + 1) * chunk);
+    Acc<A> acc = red_identity<A>(p.op);
+    for (int64_t r = static_cast<int64_t>(s) * chunk + threadIdx.x; r < r_end; r += 256) {
+        int64_t off = base;
+        if (n_red_dims == 1) {
+            off += r * p.in.stride[p.n_kept];
+        } else {
+            int64_t rem = r;
+            for (int d = p.in.rank - 1; d >= p.n_kept; --d) {
+                off += (rem % p.in.shape[d]) * p.in.stride[d];
+                rem /= p.in.shape[d];
+            }
+        }
+        Acc<A> e;
+        e.v = load_as<A>(p.in.base, p.in.dtype, off);
+        e.idx = r;
+        acc = red_combine<A>(p.op, acc, e);
+    }
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) acc = red_combine<A>(p.op, acc, red_shfl(acc, w));
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        acc = sm[0];
+        for (int w = 1; w < 8; ++w) acc = red_combine<A>(p.op, acc, sm[w]);
+        partials[o * splits + s] = acc;
+    }
+}
+
+// One warp per output folds that output's partials (lane-strided, then a shuffle tree), then the init value.
+template <typename A>
+__global__ void __launch_bounds__(32) reduce_finish_kernel(const __grid_constant__ ReduceParams p, const Acc<A>* partials, int splits) {
+    const int64_t o = blockIdx.x;
+    Acc<A> acc = red_identity<A>(p.op);
+    for (int s = threadIdx.x; s < splits; s += 32) acc = red_combine<A>(p.op, acc, partials[o * splits + s]);
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) acc = red_combine<A>(p.op, acc, red_shfl(acc, w));
+    if (threadIdx.x != 0) return;
+    if (p.init != nullptr && p.op != MHLO_REDUCE_ARGMAX && p.op != MHLO_REDUCE_ARGMIN) {
+        Acc<A> e;
+        e.v = load_as<A>(p.init, p.in.dtype, 0);
+        e.idx = INT64_MAX;
+        acc = red_combine<A>(p.op, acc, e);
+    }
+    store_as<A>(p.out, p.in.dtype, o, acc.v);
+    if (p.index_out != nullptr) {
+        const int64_t ix = acc.idx == INT64_MAX ? 0 : acc.idx;
+        if (p.index_dtype == MHLO_DT_I64) static_cast<int64_t*>(p.index_out)[o] = ix;
+        else static_cast<int32_t*>(p.index_out)[o] = static_cast<int32_t>(ix);
+    }
+}
+
 // ---- gather --------------------------------------------------------------------------------------------------------
 
 struct GatherParams {
@@ -812,6 +901,30 @@ int mhlo_cuda_elementwise_to_view(const mhlo_cuda_view* inputs, int32_t n_inputs
                             out->rank, out->stride, stream);
 }
 
+namespace {
+// Enqueues both kernels of a split reduce over `scratch` (plan.scratch_bytes, no initial contents required).
+inline int launch_split_reduce(const ReduceParams& p, const SplitPlan& plan, void* scratch, cudaStream_t s) {
+    const dim3 grid(static_cast<unsigned>(plan.splits), static_cast<unsigned>(p.n_out));
+    const int dt = p.in.dtype;
+#define MHLO_SPLIT_LAUNCH(A)                                                                                         \
+    do {                                                                                                             \
+        reduce_split_kernel<A><<<grid, 256, 0, s>>>(p, static_cast<Acc<A>*>(scratch), plan.splits, plan.chunk);       \
+        reduce_finish_kernel<A><<<static_cast<unsigned>(p.n_out), 32, 0, s>>>(p, static_cast<const Acc<A>*>(scratch), plan.splits); \
+    } while (0)
+    if (dt == MHLO_DT_F64) MHLO_SPLIT_LAUNCH(double);
+    else if (is_float_dt(dt)) MHLO_SPLIT_LAUNCH(float);
+    else if (mhlo_cuda_dtype_size(dt) != 0) MHLO_SPLIT_LAUNCH(int64_t);
+    else return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce: bad dtype %d", dt);
+#undef MHLO_SPLIT_LAUNCH
+    MHLO_CUDA_CHECK_LAUNCH("reduce (split)");
+    return MHLO_CUDA_OK;
+}
+
+// The split path pays off when the single-stage kernel would leave most SMs idle on a long reduction.
+inline bool wants_split(int64_t n_out, int64_t n_red) { return n_out <= 148 && n_red >= (1 << 16) && n_out * 1024 <= n_red; }
+
+}  // namespace
+
 int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const void* init_dev, void* out_dev,
                      void* index_out_dev, int32_t index_dtype, mhlo_cuda_stream_t stream) {
     if (!in || in->rank < 0 || in->rank > MHLO_CUDA_MAX_RANK || n_kept < 0 || n_kept > in->rank)
@@ -840,6 +953,15 @@ int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int dt = in->dtype;
+    SplitPlan plan;
+    if (wants_split(p.n_out, p.n_red) && plan_split(p.n_out, p.n_red, 0, &plan) && plan.splits > 1) {
+        // partial accumulators live in stream-ordered scratch: allocated, used and released on `stream`
+        void* scratch = nullptr;
+        MHLO_CUDA_TRY(cudaMallocAsync(&scratch, plan.scratch_bytes, s), MHLO_CUDA_BUFFER_FAILED);
+        const int st = launch_split_reduce(p, plan, scratch, s);
+        MHLO_CUDA_TRY(cudaFreeAsync(scratch, s), MHLO_CUDA_EXECUTION_FAILED);
+        return st;
+    }
 #define MHLO_RED_LAUNCH(A)                                                                                   \
     do {                                                                                                     \
         if (p.n_red >= 2048 && p.n_out < 148 * 16)                                                           \

@@ -189,6 +189,41 @@ def build_cases():
                        "      %10 = stablehlo.select %8, %ai, %bi : tensor<i1>, tensor<i32>\n"
                        "      stablehlo.return %9, %10 : tensor<f32>, tensor<i32>\n"
                        "    }", "%1#1"), [xa])
+    # reductions to very few outputs over long ranges: the split (partials in scratch memory + finish) path
+    rs = np.random.default_rng(77)
+    xs = rs.random((512, 2048), dtype=np.float32)
+    add("reduce_add_all_split", func([tt((512, 2048), "f32")], [tt((), "f32")],
+                                     "    %c = stablehlo.constant dense<0.000000e+00> : tensor<f32>\n"
+                                     f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.add across dimensions = [0, 1] : ({tt((512, 2048), 'f32')}, tensor<f32>) -> {tt((), 'f32')}", "%0"), [xs])
+    xm = rs.standard_normal((2, 300000)).astype(np.float32)
+    add("reduce_max_split", func([tt((2, 300000), "f32")], [tt((2,), "f32")],
+                                 "    %c = stablehlo.constant dense<0xFF800000> : tensor<f32>\n"
+                                 f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.maximum across dimensions = [1] : ({tt((2, 300000), 'f32')}, tensor<f32>) -> {tt((2,), 'f32')}", "%0"), [xm])
+    xis = rs.integers(-1000, 1000, size=(1, 200000)).astype(np.int32)
+    add("reduce_add_i32_split", func([tt((1, 200000), "i32")], [tt((1,), "i32")],
+                                     "    %c = stablehlo.constant dense<5> : tensor<i32>\n"
+                                     f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.add across dimensions = [1] : ({tt((1, 200000), 'i32')}, tensor<i32>) -> {tt((1,), 'i32')}", "%0"), [xis])
+    xas = rs.standard_normal((2, 150000)).astype(np.float32)
+    xas[0, [140000, 70001, 99999]] = 9.5   # ties: the first position wins
+    xas[1, 149999] = 11.0                  # the very last element
+    tas, tis = tt((2, 150000), "f32"), tt((2, 150000), "i32")
+    add("argmax_split", func([tas], [tt((2,), "i32")],
+                             f"    %0 = stablehlo.iota dim = 1 : {tis}\n"
+                             "    %c = stablehlo.constant dense<0xFF800000> : tensor<f32>\n"
+                             "    %c0 = stablehlo.constant dense<0> : tensor<i32>\n"
+                             f"    %1:2 = stablehlo.reduce(%arg0 init: %c), (%0 init: %c0) across dimensions = [1] : ({tas}, {tis}, tensor<f32>, tensor<i32>) -> ({tt((2,), 'f32')}, {tt((2,), 'i32')})\n"
+                             "     reducer(%a: tensor<f32>, %b: tensor<f32>) (%ai: tensor<i32>, %bi: tensor<i32>)  {\n"
+                             "      %2 = stablehlo.compare  GT, %a, %b,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>\n"
+                             "      %3 = stablehlo.compare  NE, %a, %a,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>\n"
+                             "      %4 = stablehlo.or %2, %3 : tensor<i1>\n"
+                             "      %5 = stablehlo.compare  EQ, %a, %b,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>\n"
+                             "      %6 = stablehlo.compare  LT, %ai, %bi,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>\n"
+                             "      %7 = stablehlo.and %5, %6 : tensor<i1>\n"
+                             "      %8 = stablehlo.or %4, %7 : tensor<i1>\n"
+                             "      %9 = stablehlo.select %4, %a, %b : tensor<i1>, tensor<f32>\n"
+                             "      %10 = stablehlo.select %8, %ai, %bi : tensor<i1>, tensor<i32>\n"
+                             "      stablehlo.return %9, %10 : tensor<f32>, tensor<i32>\n"
+                             "    }", "%1#1"), [xas])
     # ---- dot_general
     def dot_case(name, ashape, bshape, attrs, oshape, dt):
         if dt not in NP:
