@@ -225,6 +225,31 @@ enum {
 int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const void* init_dev, void* out_dev,
                      void* index_out_dev, int32_t index_dtype, mhlo_cuda_stream_t stream);
 
+/*
+ * mhlo_cuda_reduce for callers that cannot let the library allocate. No counterpart in the reference (its reduce
+ * kernels use no scratch memory; this entry point exists because the split reduce above does).
+ *
+ * mhlo_cuda_reduce takes the partial accumulators of a split reduce from the stream-ordered allocator. A host that
+ * has given all free device memory to its own pool and treats any later allocation as an error, or that is inside
+ * a stream capture on a device without a configured memory pool, cannot accept that. This entry point always runs
+ * the split algorithm and keeps the partials in an array that is part of the library image:
+ *   - it allocates and frees nothing, on the device or on the host;
+ *   - the array holds 65536 bytes per device = 4096 partial accumulators (16 bytes each); a call needs
+ *     (number of outputs) x (segments per output) of them and is refused with MHLO_CUDA_UNSUPPORTED and a message
+ *     naming both numbers when that is more. At most 65535 outputs; the reduced range must not be empty;
+ *   - `splits` = segments per output; 0 picks the same count mhlo_cuda_reduce would use, which makes the results of
+ *     the two entry points identical bit for bit whenever mhlo_cuda_reduce takes its split path;
+ *   - nothing in the array has to be cleared beforehand, every partial that is read has been written by the same call;
+ *   - there is one array per device: calls that overlap in time on one device (other streams, other threads) race
+ *     on it and give wrong results. Calls on one stream are ordered and safe;
+ *   - the first call on each device looks the array's address up (with that device current). If that first call is
+ *     to happen around a stream capture, make one call on that device before the capture begins.
+ * All other arguments as for mhlo_cuda_reduce.
+ */
+int mhlo_cuda_reduce_static_scratch(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const void* init_dev,
+                                    void* out_dev, void* index_out_dev, int32_t index_dtype, int32_t splits,
+                                    mhlo_cuda_stream_t stream);
+
 /* Dimension numbers of stablehlo.gather; counts say how many entries of each array are used. */
 typedef struct {
     int32_t n_offset_dims, n_collapsed, n_operand_batching, n_start_index_map;

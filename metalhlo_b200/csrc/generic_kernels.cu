@@ -5,6 +5,8 @@
 // in its own files.
 #include <cfloat>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mhlo {
@@ -978,6 +980,81 @@ int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const
 #undef MHLO_RED_LAUNCH
     MHLO_CUDA_CHECK_LAUNCH("reduce");
     return MHLO_CUDA_OK;
+}
+
+// ---- split reduce on scratch that is part of the library image -----------------------------------------------------
+// Some hosts must not trigger a device allocation while they run: a serving loop that has handed every free byte
+// of HBM to its own pool and treats any further allocation as a fault, or code that is already between
+// cudaStreamBeginCapture and EndCapture on a stream whose device has no memory pool configured. For them the
+// partial accumulators of the split reduce live in a fixed array inside this module instead of coming from the
+// stream-ordered allocator. The price: one array per device, so two calls that overlap in time on the same device
+// (different streams, or different threads) overwrite each other's partials.
+constexpr size_t kStaticScratchBytes = 64 * 1024;
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mu;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Address of the current device's copy of the array; looked up once per device, with that device current.
+int static_scratch_for_current_device(void** out) {
+    int dev = 0;
+    MHLO_CUDA_TRY(cudaGetDevice(&dev), MHLO_CUDA_NO_DEVICE);
+    if (dev < 0 || dev >= kMaxDevices) return fail(MHLO_CUDA_UNSUPPORTED, "reduce_static_scratch: device ordinal %d is beyond %d", dev, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        MHLO_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_reduce_static_scratch), MHLO_CUDA_EXECUTION_FAILED);
+        if (ptr == nullptr) return fail(MHLO_CUDA_EXECUTION_FAILED, "reduce_static_scratch: the scratch symbol has no address on device %d", dev);
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return MHLO_CUDA_OK;
+}
+}  // namespace
+
+int mhlo_cuda_reduce_static_scratch(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const void* init_dev, void* out_dev,
+                                    void* index_out_dev, int32_t index_dtype, int32_t splits, mhlo_cuda_stream_t stream) {
+    if (!in || in->rank < 0 || in->rank > MHLO_CUDA_MAX_RANK || n_kept < 0 || n_kept > in->rank)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: bad view or kept-dimension count");
+    if (op < MHLO_REDUCE_SUM || op > MHLO_REDUCE_ARGMIN) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: bad op %d", op);
+    if (splits < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: negative split count");
+    const bool arg = op == MHLO_REDUCE_ARGMAX || op == MHLO_REDUCE_ARGMIN;
+    if (arg && (index_out_dev == nullptr || (index_dtype != MHLO_DT_I32 && index_dtype != MHLO_DT_I64)))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: argmax/argmin need an I32 or I64 index output");
+    if (mhlo_cuda_dtype_size(in->dtype) == 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: bad dtype %d", in->dtype);
+    ReduceParams p;
+    memset(&p, 0, sizeof p);
+    p.in = *in;
+    p.n_kept = n_kept;
+    p.op = op;
+    p.init = init_dev;
+    p.out = out_dev;
+    p.index_out = arg ? index_out_dev : nullptr;
+    p.index_dtype = index_dtype;
+    p.n_out = 1;
+    p.n_red = 1;
+    for (int d = 0; d < in->rank; ++d) {
+        if (in->shape[d] < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: negative extent");
+        (d < n_kept ? p.n_out : p.n_red) *= in->shape[d];
+    }
+    if (p.n_out == 0) return MHLO_CUDA_OK;
+    if (p.n_red == 0) return fail(MHLO_CUDA_UNSUPPORTED, "reduce_static_scratch: empty reduced range; use mhlo_cuda_reduce");
+    if (out_dev == nullptr || in->base == nullptr) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_static_scratch: null pointer");
+    SplitPlan plan;
+    if (!plan_split(p.n_out, p.n_red, splits, &plan))
+        return fail(MHLO_CUDA_UNSUPPORTED, "reduce_static_scratch: %lld outputs are more than the 65535 this entry point takes", static_cast<long long>(p.n_out));
+    if (plan.scratch_bytes > kStaticScratchBytes)
+        return fail(MHLO_CUDA_UNSUPPORTED,
+                    "reduce_static_scratch: %lld outputs x %d segments need %zu bytes of partial accumulators, the built-in scratch holds %zu; "
+                    "ask for fewer segments or use mhlo_cuda_reduce",
+                    static_cast<long long>(p.n_out), plan.splits, plan.scratch_bytes, kStaticScratchBytes);
+    void* scratch = nullptr;
+    const int st = static_scratch_for_current_device(&scratch);
+    if (st != MHLO_CUDA_OK) return st;
+    // nothing in the scratch has to start at zero: the first kernel writes every partial the second one reads
+    return launch_split_reduce(p, plan, scratch, static_cast<cudaStream_t>(stream));
 }
 
 int mhlo_cuda_gather(const void* operand_dev, int32_t elem_size, const int64_t* operand_shape, int32_t operand_rank,

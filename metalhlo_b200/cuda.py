@@ -80,6 +80,7 @@ _PROTOTYPES = {
     "mhlo_cuda_elementwise": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp]),
     "mhlo_cuda_elementwise_to_view": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, C.POINTER(View), _vp]),
     "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
                                    _vp, C.POINTER(_i64), _i32, _vp]),
     "mhlo_cuda_dynamic_slice": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, C.POINTER(_vp), _i32, C.POINTER(_i64), _vp, _vp]),
