@@ -226,6 +226,21 @@ int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const
                      void* index_out_dev, int32_t index_dtype, mhlo_cuda_stream_t stream);
 
 /*
+ * Many independent dense dtype conversions in one launch (per 96 jobs): dst[i] = convert(src[i]) for i < count, with
+ * the rounding of MHLO_EW_COPY (round to nearest even). Pairs supported: F32 <-> F16, F32 <-> BF16, and same-type
+ * copies of those three. A model whose parameters arrive as fp32 and compute in 16 bit converts every weight at the
+ * start of each forward pass; done one tensor per launch, the small ones cost a launch latency each. No counterpart
+ * in the reference, which dispatches one kernel per convert (CodeGenerator.swift:1012-1075).
+ */
+typedef struct {
+    const void* src;
+    void* dst;
+    int64_t count;
+    int32_t src_dtype, dst_dtype;
+} mhlo_cuda_convert_job;
+int mhlo_cuda_convert_many(const mhlo_cuda_convert_job* jobs, int32_t n_jobs, mhlo_cuda_stream_t stream);
+
+/*
  * mhlo_cuda_reduce for callers that cannot let the library allocate. No counterpart in the reference (its reduce
  * kernels use no scratch memory; this entry point exists because the split reduce above does).
  *

@@ -778,6 +778,84 @@ bool is_float_dt(int dt) { return dt == MHLO_DT_F16 || dt == MHLO_DT_F32 || dt =
 
 using namespace mhlo;
 
+// ---- batched dtype conversion ---------------------------------------------------------------------------------------
+
+constexpr int kConvertJobsPerLaunch = 96;
+constexpr int kConvertTile = 4096;  // elements per CTA: 256 threads x 16
+
+struct ConvertTable {
+    const void* src[kConvertJobsPerLaunch];
+    void* dst[kConvertJobsPerLaunch];
+    int64_t count[kConvertJobsPerLaunch];
+    int32_t first_tile[kConvertJobsPerLaunch + 1];  // tiles of job j are [first_tile[j], first_tile[j+1])
+    int8_t src_dtype[kConvertJobsPerLaunch], dst_dtype[kConvertJobsPerLaunch];
+    int8_t vector_ok[kConvertJobsPerLaunch];  // both pointers 16-byte aligned
+    int32_t n_jobs;
+};
+
+template <typename TI, typename TO>
+__device__ __forceinline__ void convert_tile(const TI* __restrict__ src, TO* __restrict__ dst, int64_t begin, int64_t end, bool vector_ok) {
+    // 16 consecutive elements per thread when the tile is full and aligned, element-wise otherwise
+    if (vector_ok && end - begin == kConvertTile) {
+        const int64_t i = begin + static_cast<int64_t>(threadIdx.x) * 16;
+        float v[16];
+        if constexpr (sizeof(TI) == 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 f = __ldcs(reinterpret_cast<const float4*>(src + i) + q);
+                v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const uint4 u = __ldcs(reinterpret_cast<const uint4*>(src + i) + q);
+                const TI* h = reinterpret_cast<const TI*>(&u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[8 * q + e] = static_cast<float>(h[e]);
+            }
+        }
+        if constexpr (sizeof(TO) == 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(dst + i)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint4 u;
+                TO* h = reinterpret_cast<TO*>(&u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = static_cast<TO>(v[8 * q + e]);
+                reinterpret_cast<uint4*>(dst + i)[q] = u;
+            }
+        }
+        return;
+    }
+    for (int64_t i = begin + threadIdx.x; i < end; i += 256) dst[i] = static_cast<TO>(static_cast<float>(src[i]));
+}
+
+__global__ void __launch_bounds__(256) convert_many_kernel(const __grid_constant__ ConvertTable t) {
+    const int tile = blockIdx.x;
+    int lo = 0, hi = t.n_jobs - 1;  // last job whose first tile is <= tile
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (t.first_tile[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    const int j = lo;
+    const int64_t begin = static_cast<int64_t>(tile - t.first_tile[j]) * kConvertTile;
+    const int64_t end = min(t.count[j], begin + kConvertTile);
+    const bool vec = t.vector_ok[j] != 0;
+    const int sd = t.src_dtype[j], dd = t.dst_dtype[j];
+#define MHLO_CONVERT_CASE(SD, TI, DD, TO) \
+    if (sd == SD && dd == DD) return convert_tile<TI, TO>(static_cast<const TI*>(t.src[j]), static_cast<TO*>(t.dst[j]), begin, end, vec)
+    MHLO_CONVERT_CASE(MHLO_DT_F32, float, MHLO_DT_F16, __half);
+    MHLO_CONVERT_CASE(MHLO_DT_F32, float, MHLO_DT_BF16, __nv_bfloat16);
+    MHLO_CONVERT_CASE(MHLO_DT_F16, __half, MHLO_DT_F32, float);
+    MHLO_CONVERT_CASE(MHLO_DT_BF16, __nv_bfloat16, MHLO_DT_F32, float);
+    MHLO_CONVERT_CASE(MHLO_DT_F32, float, MHLO_DT_F32, float);
+    MHLO_CONVERT_CASE(MHLO_DT_F16, __half, MHLO_DT_F16, __half);
+    MHLO_CONVERT_CASE(MHLO_DT_BF16, __nv_bfloat16, MHLO_DT_BF16, __nv_bfloat16);
+#undef MHLO_CONVERT_CASE
+}
+
 extern "C" {
 
 static int elementwise_impl(const mhlo_cuda_view* inputs, int32_t n_inputs, const mhlo_cuda_ew_inst* prog,
@@ -979,6 +1057,51 @@ int mhlo_cuda_reduce(const mhlo_cuda_view* in, int32_t n_kept, int32_t op, const
     else return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce: bad dtype %d", dt);
 #undef MHLO_RED_LAUNCH
     MHLO_CUDA_CHECK_LAUNCH("reduce");
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_convert_many(const mhlo_cuda_convert_job* jobs, int32_t n_jobs, mhlo_cuda_stream_t stream) {
+    if (n_jobs < 0 || (n_jobs > 0 && jobs == nullptr)) return fail(MHLO_CUDA_INVALID_ARGUMENT, "convert_many: bad job list");
+    auto ok_dtype = [](int d) { return d == MHLO_DT_F32 || d == MHLO_DT_F16 || d == MHLO_DT_BF16; };
+    for (int32_t j = 0; j < n_jobs; ++j) {
+        const mhlo_cuda_convert_job& job = jobs[j];
+        if (job.count < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "convert_many: job %d has a negative count", j);
+        if (job.count > 0 && (job.src == nullptr || job.dst == nullptr)) return fail(MHLO_CUDA_INVALID_ARGUMENT, "convert_many: job %d has a null pointer", j);
+        const bool pair_ok = ok_dtype(job.src_dtype) && ok_dtype(job.dst_dtype) &&
+                             (job.src_dtype == job.dst_dtype || job.src_dtype == MHLO_DT_F32 || job.dst_dtype == MHLO_DT_F32);
+        if (!pair_ok) return fail(MHLO_CUDA_UNSUPPORTED, "convert_many: job %d converts dtype %d to %d", j, job.src_dtype, job.dst_dtype);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int32_t j = 0;
+    while (j < n_jobs) {
+        ConvertTable t;
+        memset(&t, 0, sizeof t);
+        int64_t tiles = 0;
+        int n = 0;
+        for (; j < n_jobs && n < kConvertJobsPerLaunch; ++j) {
+            const mhlo_cuda_convert_job& job = jobs[j];
+            if (job.count == 0) continue;
+            const int64_t job_tiles = (job.count + kConvertTile - 1) / kConvertTile;
+            if (tiles + job_tiles > 0x7fffffff) {
+                if (n == 0) return fail(MHLO_CUDA_UNSUPPORTED, "convert_many: job %d is too large for one launch", j);
+                break;
+            }
+            t.src[n] = job.src;
+            t.dst[n] = job.dst;
+            t.count[n] = job.count;
+            t.src_dtype[n] = static_cast<int8_t>(job.src_dtype);
+            t.dst_dtype[n] = static_cast<int8_t>(job.dst_dtype);
+            t.vector_ok[n] = aligned16(job.src) && aligned16(job.dst);
+            t.first_tile[n] = static_cast<int32_t>(tiles);
+            tiles += job_tiles;
+            ++n;
+        }
+        if (n == 0) continue;
+        t.first_tile[n] = static_cast<int32_t>(tiles);
+        t.n_jobs = n;
+        convert_many_kernel<<<static_cast<unsigned>(tiles), 256, 0, s>>>(t);
+        MHLO_CUDA_CHECK_LAUNCH("convert_many");
+    }
     return MHLO_CUDA_OK;
 }
 

@@ -234,6 +234,7 @@ class Lowering {
             set(f_.args[i], dense_view(add_buffer(b), f_.type_of(f_.args[i])));
             exe_->input_types_.push_back(f_.type_of(f_.args[i]));
         }
+        open_parameter_converts();
         for (const Op& op : f_.ops) {
             if (op.dead) continue;
             if (op.name == "return") { lower_return(op); break; }
@@ -368,10 +369,62 @@ class Lowering {
     }
 
     // ---- per-op lowering --------------------------------------------------------------------------------------------
+    // ---- dtype conversions of whole function parameters, gathered into one launch at the start of the program --------
+    // A module whose parameters arrive as fp32 and which computes in 16 bit converts every weight once per run (148
+    // converts in the GPT-2 module, most of them a few KB). They depend on nothing but the inputs, so they all run in
+    // step 0 as one batched launch instead of one launch each.
+    struct ParamConvert {
+        std::function<char*(const Ctx&)> src, dst;
+        int64_t count;
+        int32_t src_dtype, dst_dtype;
+    };
+    std::shared_ptr<std::vector<ParamConvert>> param_converts_;
+
+    static bool batchable_float(DType d) { return d == DType::F32 || d == DType::F16 || d == DType::BF16; }
+    bool is_parameter_convert(const Op& op) const {
+        if (op.name != "convert" || op.operands.size() != 1 || op.results.empty()) return false;
+        const int v = op.operands[0];
+        if (!have_[v]) return false;
+        const View& x = views_[v];
+        if (buffers_[x.buf].kind != Buffer::Input || x.offset != 0 || !is_dense(x)) return false;
+        const TensorType& rt = op.result_types[0];
+        if (!batchable_float(x.type.dtype) || !batchable_float(rt.dtype)) return false;
+        return x.type.dtype == rt.dtype || x.type.dtype == DType::F32 || rt.dtype == DType::F32;
+    }
+    // Reserves step 0 for the batch when at least two converts qualify (called when only the parameters have views).
+    void open_parameter_converts() {
+        int n = 0;
+        for (const Op& op : f_.ops) n += !op.dead && is_parameter_convert(op);
+        if (n < 2) return;
+        param_converts_ = std::make_shared<std::vector<ParamConvert>>();
+        auto jobs = param_converts_;
+        add_step("convert_parameters(x" + std::to_string(n) + ")", [jobs](const Ctx& c) {
+            std::vector<mhlo_cuda_convert_job> list(jobs->size());
+            for (size_t i = 0; i < jobs->size(); ++i) {
+                const ParamConvert& j = (*jobs)[i];
+                list[i] = mhlo_cuda_convert_job{j.src(c), j.dst(c), j.count, j.src_dtype, j.dst_dtype};
+            }
+            return mhlo_cuda_convert_many(list.data(), static_cast<int32_t>(list.size()), c.stream);
+        }, (n + 95) / 96);
+    }
+    void lower_parameter_convert(const Op& op) {
+        const View& x = get(op.operands[0]);
+        const TensorType& rt = op.result_types[0];
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        // both buffers are in use from step 0 on, whatever the position of the convert in the program
+        buffers_[x.buf].first = 0;
+        buffers_[out.buf].first = 0;
+        buffers_[out.buf].last = std::max(buffers_[out.buf].last, 0);
+        param_converts_->push_back(ParamConvert{resolver(x.buf), resolver(out.buf), rt.count(), static_cast<int32_t>(x.type.dtype),
+                                                static_cast<int32_t>(rt.dtype)});
+        set(op.results[0], out);
+    }
+
     void lower(const Op& op) {
         const std::string& n = op.name;
         if (op.results.empty()) return;  // ops without results have no effect here
         const TensorType& rt = op.result_types[0];
+        if (param_converts_ && is_parameter_convert(op)) return lower_parameter_convert(op);
         if (n == "constant") return lower_constant(op);
         if (n == "reshape" || n == "bitcast") return lower_reshape(op);
         if (n == "transpose") {

@@ -35,6 +35,10 @@ class EwInst(C.Structure):
     _fields_ = [("op", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("c", C.c_int32), ("imm", C.c_double)]
 
 
+class ConvertJob(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("count", C.c_int64), ("src_dtype", C.c_int32), ("dst_dtype", C.c_int32)]
+
+
 class GatherDims(C.Structure):
     _fields_ = [("n_offset_dims", C.c_int32), ("n_collapsed", C.c_int32), ("n_operand_batching", C.c_int32),
                 ("n_start_index_map", C.c_int32), ("offset_dims", C.c_int32 * 8), ("collapsed_slice_dims", C.c_int32 * 8),
@@ -80,6 +84,7 @@ _PROTOTYPES = {
     "mhlo_cuda_elementwise": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp]),
     "mhlo_cuda_elementwise_to_view": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, C.POINTER(View), _vp]),
     "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "mhlo_cuda_convert_many": (C.c_int, [C.POINTER(ConvertJob), _i32, _vp]),
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
                                    _vp, C.POINTER(_i64), _i32, _vp]),
