@@ -129,6 +129,20 @@ int mhlo_cuda_rms_norm(int dtype, const void* x_dev, const void* gamma_dev, void
                        mhlo_cuda_stream_t stream);
 
 /*
+ * Residual add fused into the norm: sum = x + residual (rounded to `dtype`, exactly what a separate add writes),
+ * y = LayerNorm(sum) or RMSNorm(sum). sum_dev receives the sum (the residual stream later layers read); x, residual,
+ * sum, y: [rows, hidden]. One pass over x and residual instead of an add kernel plus a re-read by the norm. No
+ * counterpart in the reference (its "residual-chain-fusion" pass is registered without an implementation,
+ * Compiler/PassManager.swift:214-221).
+ */
+int mhlo_cuda_add_layer_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev,
+                             const void* beta_dev, void* sum_dev, void* y_dev, int64_t rows, int64_t hidden,
+                             float eps, const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
+int mhlo_cuda_add_rms_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev,
+                           void* sum_dev, void* y_dev, int64_t rows, int64_t hidden, float eps,
+                           const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
+
+/*
  * Softmax along one axis of a tensor viewed as [outer, axis_len, inner] (inner = 1 for the last axis):
  * y = exp(x - max) / sum(exp(x - max)). Replaces kernel_softmax (CodeGenerator.swift:4690-4794) and
  * softmax_kernel(_half) (Sources/MetalHLOCore/Metal/Kernels/SoftmaxKernel.swift:23-167), semantics of

@@ -268,6 +268,8 @@ struct EwVecParams {
     int32_t scalar_mask;  // bit k: input k is one broadcast element
     int32_t n_inputs, op;
     double imm;
+    int64_t period[3];    // > 0: input k is dense over its trailing dimensions and repeats every `period` elements
+                          // (broadcast over the leading ones: a bias row, a position table); a multiple of 8
 };
 
 template <typename TI, typename TO>
@@ -282,7 +284,8 @@ __global__ void __launch_bounds__(256) ew_vec_kernel(const EwVecParams p) {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
             if (k < p.n_inputs && !((p.scalar_mask >> k) & 1)) {
-                load8(static_cast<const TI*>(p.in[k]) + v * 8, x[k]);
+                const int64_t at = p.period[k] > 0 ? (v * 8) % p.period[k] : v * 8;
+                load8(static_cast<const TI*>(p.in[k]) + at, x[k]);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[k][e] = sc[k];
@@ -297,7 +300,9 @@ __global__ void __launch_bounds__(256) ew_vec_kernel(const EwVecParams p) {
         const int64_t i = nvec * 8 + threadIdx.x;
         float x[3];
         for (int k = 0; k < 3; ++k)
-            x[k] = k < p.n_inputs ? (((p.scalar_mask >> k) & 1) ? sc[k] : VecTraits<TI>::to_float(static_cast<const TI*>(p.in[k])[i])) : 0.f;
+            x[k] = k < p.n_inputs ? (((p.scalar_mask >> k) & 1) ? sc[k]
+                                                                : VecTraits<TI>::to_float(static_cast<const TI*>(p.in[k])[p.period[k] > 0 ? i % p.period[k] : i]))
+                                  : 0.f;
         static_cast<TO*>(p.out)[i] = VecTraits<TO>::from_float(ew_float_op<float>(p.op, x[0], x[1], x[2], p.imm));
     }
 }
@@ -596,6 +601,22 @@ __global__ void __launch_bounds__(32) reduce_finish_kernel(const __grid_constant
         const int64_t ix = acc.idx == INT64_MAX ? 0 : acc.idx;
         if (p.index_dtype == MHLO_DT_I64) static_cast<int64_t*>(p.index_out)[o] = ix;
         else static_cast<int32_t*>(p.index_out)[o] = static_cast<int32_t>(ix);
+    }
+}
+
+// ---- row gather: out[i, :] = operand[clamp(index[i]), :] (an embedding lookup) ------------------------------------
+// One warp per output row, 16-byte vectors; the start index is clamped into the table like the general kernel does.
+template <typename I>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ table, const I* __restrict__ index, uint4* __restrict__ out,
+                                                          int64_t n_rows, int64_t table_rows, int vecs_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n_rows; r += warps) {
+        int64_t src = static_cast<int64_t>(index[r]);
+        src = src < 0 ? 0 : (src > table_rows - 1 ? table_rows - 1 : src);
+        const uint4* from = table + src * vecs_per_row;
+        uint4* to = out + r * vecs_per_row;
+        for (int v = lane; v < vecs_per_row; v += 32) to[v] = __ldg(from + v);
     }
 }
 
@@ -940,7 +961,21 @@ static int elementwise_impl(const mhlo_cuda_view* inputs, int32_t n_inputs, cons
             bool scalar = true;
             for (int d = 0; d < p.rank; ++d) scalar &= p.in[k].stride[d] == 0;
             const bool dense = (p.contiguous_mask >> k) & 1;
-            ok = p.in[k].dtype == in_dt && (scalar || (dense && aligned16(p.in[k].base)));
+            // broadcast over leading dimensions, dense over the rest: the input repeats with a fixed period
+            int64_t period = 0;
+            if (!scalar && !dense) {
+                int q = 0;
+                while (q < p.rank && p.in[k].stride[q] == 0) ++q;
+                int64_t expect = 1;
+                bool tail_dense = q > 0 && q < p.rank;
+                for (int d = p.rank - 1; d >= q && tail_dense; --d) {
+                    tail_dense = p.out_shape[d] == 1 || p.in[k].stride[d] == expect;
+                    expect *= p.out_shape[d];
+                }
+                if (tail_dense && expect % 8 == 0) period = expect;
+            }
+            vp.period[k] = period;
+            ok = p.in[k].dtype == in_dt && (scalar || ((dense || period > 0) && aligned16(p.in[k].base)));
             if (scalar && !(dense && p.n == 1)) vp.scalar_mask |= 1 << k;
             vp.in[k] = p.in[k].base;
         }
@@ -1213,6 +1248,36 @@ int mhlo_cuda_gather(const void* operand_dev, int32_t elem_size, const int64_t* 
     p.operand_rank = operand_rank; p.indices_rank = indices_rank; p.out_rank = out_rank;
     p.elem_size = elem_size; p.index_dtype = index_dtype == MHLO_DT_UI32 ? MHLO_DT_I32 : index_dtype;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Embedding-style lookup: whole rows of a [rows, ...] table selected by one index each.
+    {
+        bool rows_only = operand_rank >= 2 && dims->n_collapsed == 1 && dims->collapsed_slice_dims[0] == 0 && dims->n_start_index_map == 1 &&
+                         dims->start_index_map[0] == 0 && dims->n_operand_batching == 0 && dims->slice_sizes[0] == 1 &&
+                         dims->n_offset_dims == operand_rank - 1 && out_rank >= operand_rank - 1;
+        int64_t row_elems = 1;
+        for (int d = 1; rows_only && d < operand_rank; ++d) {
+            rows_only = dims->slice_sizes[d] == operand_shape[d] && dims->offset_dims[d - 1] == out_rank - (operand_rank - 1) + (d - 1);
+            row_elems *= operand_shape[d];
+        }
+        rows_only = rows_only && (dims->index_vector_dim == indices_rank ||
+                                  (dims->index_vector_dim == indices_rank - 1 && indices_rank >= 1 && indices_shape[indices_rank - 1] == 1));
+        const int64_t row_bytes = row_elems * elem_size;
+        if (rows_only && row_bytes > 0 && row_bytes % 16 == 0 && row_bytes / 16 <= 0x7fffffff && aligned16(operand_dev) && aligned16(out_dev)) {
+            const int64_t n_rows = p.n / row_elems;
+            const int vecs = static_cast<int>(row_bytes / 16);
+            const int grid_rows = static_cast<int>(std::min<int64_t>((n_rows + 7) / 8, 148 * 16));
+            if (p.index_dtype == MHLO_DT_I64)
+                gather_rows_kernel<int64_t><<<grid_rows, 256, 0, s>>>(static_cast<const uint4*>(operand_dev), static_cast<const int64_t*>(indices_dev),
+                                                                     static_cast<uint4*>(out_dev), n_rows, operand_shape[0], vecs);
+            else if (index_dtype == MHLO_DT_UI32)
+                gather_rows_kernel<uint32_t><<<grid_rows, 256, 0, s>>>(static_cast<const uint4*>(operand_dev), static_cast<const uint32_t*>(indices_dev),
+                                                                      static_cast<uint4*>(out_dev), n_rows, operand_shape[0], vecs);
+            else
+                gather_rows_kernel<int32_t><<<grid_rows, 256, 0, s>>>(static_cast<const uint4*>(operand_dev), static_cast<const int32_t*>(indices_dev),
+                                                                     static_cast<uint4*>(out_dev), n_rows, operand_shape[0], vecs);
+            MHLO_CUDA_CHECK_LAUNCH("gather (rows)");
+            return MHLO_CUDA_OK;
+        }
+    }
     const int grid = grid_for(p.n, 256);
     switch (elem_size) {
         case 1: gather_kernel<uint8_t><<<grid, 256, 0, s>>>(p); break;

@@ -901,6 +901,55 @@ void Lowering::lower_custom_call(const Op& op) {
         });
         return set(op.results[0], out);
     }
+    if (target == "fused_add_layer_norm" || target == "fused_add_rms_norm") {
+        // results: [0] the sum a + b (the residual stream), [1] its norm
+        const bool ln = target == "fused_add_layer_norm";
+        if (op.results.size() != 2) fail_compile(target + " must have two results");
+        if (!is_dense(operand(0)) || !is_dense(operand(1))) {
+            // a broadcast or transposed addend would have to be copied first: the strided elementwise add reads it in
+            // place, and the norm then runs on its result
+            mhlo_cuda_ew_inst add_inst = {ew_opcode("add"), 0, 1, 0, 0.0};
+            View sum = emit_elementwise({operand(0), operand(1)}, {add_inst}, op.result_types[0], "add");
+            set(op.results[0], sum);
+            Op plain = op;
+            plain.operands[0] = op.results[0];
+            plain.operands.erase(plain.operands.begin() + 1);
+            plain.results = {op.results[1]};
+            plain.result_types = {op.result_types[1]};
+            plain.attrs["call_target_name"] = Attr::make_string(ln ? "fused_layer_norm" : "fused_rms_norm");
+            return lower_custom_call(plain);
+        }
+        View a = materialize(operand(0), target + ".a"), r = materialize(operand(1), target + ".b");
+        if (!last_axis_only(json_int_array(cfg, "axes"), a.type.rank())) fail_unsupported(target + " over an axis other than the last");
+        const int64_t hidden = a.type.rank() ? a.type.shape.back() : 1;
+        const int64_t rows = hidden ? a.type.count() / hidden : 0;
+        const bool has_g = op.operands.size() > 2, has_b = ln && op.operands.size() > 3;
+        View g, b;
+        if (has_g) g = materialize(expand_to(operand(2), {hidden}), target + ".gamma");
+        if (has_b) b = materialize(expand_to(operand(3), {hidden}), target + ".beta");
+        const float eps = static_cast<float>(json_number(cfg, "eps", json_number(cfg, "epsilon", 1e-5)));
+        const TensorType& st = op.result_types[0];
+        const TensorType& yt = op.result_types[1];
+        View sum = dense_view(new_arena(st.bytes()), st), out = dense_view(new_arena(yt.bytes()), yt);
+        DevView da = dev(a), dr = dev(r), dg, db, dsum = dev(sum), dout = dev(out);
+        keep_alive(a); keep_alive(r); keep_alive(sum); keep_alive(out);
+        if (has_g) { dg = dev(g); keep_alive(g); }
+        if (has_b) { db = dev(b); keep_alive(b); }
+        const int dt = static_cast<int>(a.type.dtype);
+        mhlo_cuda_row_tuning tuning{0, 0, 0};
+        const bool tuned = lookup_row_tuning(ln ? "fused_layer_norm" : "fused_rms_norm", rows, hidden, a.type.dtype, &tuning);
+        add_step(target, [=](const Ctx& c) {
+            const void* gp = has_g ? bind(dg, c).base : nullptr;
+            const void* bp = has_b ? bind(db, c).base : nullptr;
+            const mhlo_cuda_row_tuning* tp = tuned ? &tuning : nullptr;
+            void* sp = const_cast<void*>(bind(dsum, c).base);
+            void* yp = const_cast<void*>(bind(dout, c).base);
+            if (ln) return mhlo_cuda_add_layer_norm(dt, bind(da, c).base, bind(dr, c).base, gp, bp, sp, yp, rows, hidden, eps, tp, c.stream);
+            return mhlo_cuda_add_rms_norm(dt, bind(da, c).base, bind(dr, c).base, gp, sp, yp, rows, hidden, eps, tp, c.stream);
+        });
+        set(op.results[0], sum);
+        return set(op.results[1], out);
+    }
     if (target == "fused_softmax") {
         View x = materialize(operand(0), target);
         int64_t axis = static_cast<int64_t>(json_number(cfg, "axis", -1));

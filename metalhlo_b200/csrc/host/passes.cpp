@@ -644,6 +644,48 @@ void cone_values(const Graph& g, int v, std::vector<int>* out, int depth = 0) {
     for (int x : o->operands) cone_values(g, x, out, depth + 1);
 }
 
+// Residual add feeding a norm: y = norm(a + b) where the sum is also the residual stream read later.
+//   s = add(a, b); y = custom_call @fused_layer_norm(s, gamma, beta)
+// becomes one op with two results,
+//   s, y = custom_call @fused_add_layer_norm(a, b, gamma, beta)
+// whose kernel reads a and b once, writes the rounded sum and normalises it in registers (the sum is not read back).
+// Every other user of the sum has to come after the norm in program order. The reference registers
+// "residual-chain-fusion" without an implementation (Compiler/PassManager.swift:214-221).
+bool fuse_residual_norm(Function& f) {
+    Graph g(f);
+    bool changed = false;
+    for (size_t idx = 0; idx < f.ops.size(); ++idx) {
+        Op& o = f.ops[idx];
+        if (o.dead || o.name != "custom_call" || o.results.size() != 1 || o.operands.empty()) continue;
+        const std::string target = o.str_attr("call_target_name");
+        if (target != "fused_layer_norm" && target != "fused_rms_norm") continue;
+        const int s = o.operands[0];
+        Op* add = g.def_mut(s);
+        if (!add || add->name != "add" || add->operands.size() != 2 || add->results.size() != 1) continue;
+        const TensorType& st = g.type(s);
+        if (!is_float(st.dtype) || st.dtype == DType::F64) continue;
+        if (!(g.type(add->operands[0]) == st) || !(g.type(add->operands[1]) == st)) continue;
+        bool ordered = true;
+        for (int user : g.users[s]) ordered = ordered && user >= static_cast<int>(idx);
+        // gamma / beta must not be computed from the sum itself
+        for (size_t k = 1; k < o.operands.size(); ++k) ordered = ordered && o.operands[k] != s;
+        if (!ordered) continue;
+        const int y = o.results[0];
+        const TensorType yt = o.result_types[0];
+        std::vector<int> operands = {add->operands[0], add->operands[1]};
+        for (size_t k = 1; k < o.operands.size(); ++k) operands.push_back(o.operands[k]);
+        o.operands = operands;
+        o.attrs["call_target_name"] = Attr::make_string(target == "fused_layer_norm" ? "fused_add_layer_norm" : "fused_add_rms_norm");
+        o.results = {s, y};
+        o.result_types = {st, yt};
+        add->dead = true;
+        add->results.clear();
+        changed = true;
+    }
+    if (changed) f.compact();
+    return changed;
+}
+
 bool fuse_activations(Function& f) {
     Graph g(f);
     bool changed = false;
@@ -1158,7 +1200,7 @@ const std::vector<PassDef>& registry() {
         {"elementwise-chain-fusion", [](Function&) { return false; }},  // no-op in the reference
         // phase 5: cross-layer
         {"cross-layer-fusion", [](Function&) { return false; }},
-        {"residual-chain-fusion", [](Function&) { return false; }},
+        {"residual-chain-fusion", fuse_residual_norm},
         // phase 6: layout
         {"layout-assignment", [](Function&) { return false; }},  // analysis-only in the reference
         {"transpose-folding", canonicalize_transpose},

@@ -70,10 +70,13 @@ __device__ __forceinline__ float cta_reduce1(float v, float* scratch, int nwarps
 // vector (no predicates in the loop).
 constexpr int kDepth = 2;
 
-template <typename T, int VPT, int OP, bool FULL>
+//
+// ADD (norms only): the row is x + res, rounded to T as a separate add would leave it; that sum is written to sum_out
+// (the residual stream a later layer reads) and normalised from registers.
+template <typename T, int VPT, int OP, bool FULL, bool ADD>
 __global__ void __launch_bounds__((row_vec_max_threads<T, VPT>()))
 row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-               T* __restrict__ y, int64_t rows, int hidden, float eps) {
+               T* __restrict__ y, int64_t rows, int hidden, float eps, const T* __restrict__ res, T* __restrict__ sum_out) {
     using VT = VecTraits<T>;
     constexpr int E = VT::kElems;
     constexpr int H = E / 2;  // float2 per vector
@@ -131,6 +134,7 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
     // Register ring of kDepth rows: row r + kDepth*gridDim.x is requested as soon as row r has been unpacked,
     // so kDepth rows per CTA are in flight while one is being worked on.
     uint4 raw[kDepth][VPT];
+    uint4 raw_res[ADD ? kDepth : 1][ADD ? VPT : 1];
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) {
         const int64_t r = blockIdx.x + static_cast<int64_t>(d) * gridDim.x;
@@ -139,6 +143,12 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
                 if (live[i]) raw[d][i] = ld_stream16(xr + tid + i * nthreads);
+            if constexpr (ADD) {
+                const uint4* rr = reinterpret_cast<const uint4*>(res + r * hidden);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (live[i]) raw_res[d][i] = ld_stream16(rr + tid + i * nthreads);
+            }
         }
     }
     int ph = 0;
@@ -152,6 +162,15 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
         for (int i = 0; i < VPT; ++i) {
             if (live[i]) {
                 VT::unpack2(raw[d][i], v[i]);
+                if constexpr (ADD) {
+                    float2 rv[H];
+                    VT::unpack2(raw_res[d][i], rv);
+#pragma unroll
+                    for (int h = 0; h < H; ++h) v[i][h] = add2(v[i][h], rv[h]);
+                    const uint4 packed = VT::pack2(v[i]);  // the sum as the element type holds it
+                    st_stream16(reinterpret_cast<uint4*>(sum_out + row * hidden) + tid + i * nthreads, packed);
+                    VT::unpack2(packed, v[i]);
+                }
             } else {
 #pragma unroll
                 for (int h = 0; h < H; ++h) v[i][h] = splat2((OP == kSoftmax) ? -INFINITY : 0.f);
@@ -163,6 +182,12 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
                 if (live[i]) raw[d][i] = ld_stream16(xn + tid + i * nthreads);
+            if constexpr (ADD) {
+                const uint4* rn = reinterpret_cast<const uint4*>(res + next * hidden);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (live[i]) raw_res[d][i] = ld_stream16(rn + tid + i * nthreads);
+            }
         }
         uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
 
@@ -307,10 +332,19 @@ __global__ void __launch_bounds__(256) row_strided_kernel(const T* __restrict__ 
     }
 }
 
+// out = round(a + b) elementwise: the sum a fused add + norm has to produce when the row kernel's fast path is not
+// available (odd lengths, unaligned pointers).
+template <typename T>
+__global__ void __launch_bounds__(256) add_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step)
+        out[i] = static_cast<T>(static_cast<float>(a[i]) + static_cast<float>(b[i]));
+}
+
 template <typename T, int OP>
 int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int64_t outer, int64_t len,
                 int64_t inner, float eps, const mhlo_cuda_row_tuning* tuning, cudaStream_t stream,
-                const char* what) {
+                const char* what, const void* res = nullptr, void* sum_out = nullptr) {
     constexpr int E = VecTraits<T>::kElems;
     const int64_t rows = outer * inner;
     if (rows == 0 || len == 0) return MHLO_CUDA_OK;
@@ -323,18 +357,37 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
     // Largest row the register-resident kernel covers: 8 vectors per thread at the CTA size that leaves
     // room for 8*E fp32 values per thread.
     const int64_t max_vecs = 8 * (8 * E > 32 ? 256 : 512);
+    const bool with_add = res != nullptr;
     const bool vec_ok = inner == 1 && len % E == 0 && nvec <= max_vecs && aligned16(x) && aligned16(y) &&
-                        aligned16(gamma) && aligned16(beta);
+                        aligned16(gamma) && aligned16(beta) && aligned16(res) && aligned16(sum_out);
     if (!vec_ok) {
         const int grid = static_cast<int>(rows < 148LL * 64 ? rows : 148LL * 64);
+        if (with_add) {
+            const int64_t n = rows * len;
+            add_rows_kernel<T><<<static_cast<int>(n < 148LL * 2048 ? (n + 255) / 256 : 148 * 8), 256, 0, stream>>>(
+                xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n);
+            xp = static_cast<const T*>(sum_out);
+        }
         row_strided_kernel<T, OP><<<grid, 256, 0, stream>>>(xp, gp, bp, yp, rows, len, inner, eps);
         MHLO_CUDA_CHECK_LAUNCH(what);
         return MHLO_CUDA_OK;
     }
 
+    if (with_add && sizeof(T) == 4 && nvec > 2 * 1024) {
+        // an fp32 row too long for two vectors per thread: separate add, then the plain norm on the sum
+        const int64_t n = rows * len;
+        add_rows_kernel<T><<<static_cast<int>(n < 148LL * 2048 ? (n + 255) / 256 : 148 * 8), 256, 0, stream>>>(
+            xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n);
+        MHLO_CUDA_CHECK_LAUNCH(what);
+        return launch_rows<T, OP>(sum_out, gamma, beta, y, outer, len, inner, eps, tuning, stream, what);
+    }
     int vpt = tuning ? tuning->vecs_per_thread : 0;
     int threads = tuning ? tuning->threads : 0;
     const int ctas_per_sm = tuning ? tuning->ctas_per_sm : 0;
+    if (with_add && sizeof(T) == 4 && (vpt == 0 || vpt > 2)) {
+        vpt = nvec > 1024 ? 2 : 1;
+        threads = 0;
+    }
     if (vpt == 0) {
         // 32 fp32 values per thread measured best on B200 (128 threads for a 4096-wide bf16 row); short rows
         // shrink the share so that a CTA still has at least one full warp.
@@ -361,12 +414,18 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: %d threads x %d vectors need %zu bytes of shared memory",
                     what, threads, vpt, smem);
 
-    using Kernel = void (*)(const T*, const T*, const T*, T*, int64_t, int, float);
+    using Kernel = void (*)(const T*, const T*, const T*, T*, int64_t, int, float, const T*, T*);
     Kernel kernel = nullptr;
-#define MHLO_ROW_PICK(V)                                                                      \
-    case V:                                                                                   \
-        kernel = full ? row_vec_kernel<T, V, OP, true> : row_vec_kernel<T, V, OP, false>;     \
-        break;
+    // the residual ring doubles the registers held per vector: fp32 rows take it only up to two vectors per thread
+#define MHLO_ROW_PICK(V)                                                                                              \
+    case V: {                                                                                                         \
+        constexpr bool kAddable = OP != kSoftmax && (sizeof(T) == 2 || V <= 2);                                       \
+        if (kAddable && with_add)                                                                                     \
+            kernel = full ? row_vec_kernel<T, V, OP, true, kAddable> : row_vec_kernel<T, V, OP, false, kAddable>;     \
+        else                                                                                                          \
+            kernel = full ? row_vec_kernel<T, V, OP, true, false> : row_vec_kernel<T, V, OP, false, false>;           \
+        break;                                                                                                        \
+    }
     switch (vpt) {
         MHLO_ROW_PICK(1)
         MHLO_ROW_PICK(2)
@@ -392,7 +451,8 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         if (grid > static_cast<int64_t>(kNumSMs) * per_sm) grid = static_cast<int64_t>(kNumSMs) * per_sm;
     }
     if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
-    kernel<<<static_cast<int>(grid), threads, smem, stream>>>(xp, gp, bp, yp, rows, static_cast<int>(len), eps);
+    kernel<<<static_cast<int>(grid), threads, smem, stream>>>(xp, gp, bp, yp, rows, static_cast<int>(len), eps,
+                                                                static_cast<const T*>(res), static_cast<T*>(sum_out));
     MHLO_CUDA_CHECK_LAUNCH(what);
     return MHLO_CUDA_OK;
 }
@@ -400,19 +460,21 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
 template <int OP>
 int dispatch_rows(int dtype, const void* x, const void* gamma, const void* beta, void* y, int64_t outer,
                   int64_t len, int64_t inner, float eps, const mhlo_cuda_row_tuning* tuning, void* stream,
-                  const char* what) {
+                  const char* what, const void* res = nullptr, void* sum_out = nullptr) {
     if (outer < 0 || len < 0 || inner < 0)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: negative extent", what);
     if (outer * len * inner > 0 && (x == nullptr || y == nullptr))
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: null tensor pointer", what);
+    if ((res == nullptr) != (sum_out == nullptr))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: the residual operand and the sum output go together", what);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case MHLO_DT_F32:
-            return launch_rows<float, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what);
+            return launch_rows<float, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
         case MHLO_DT_F16:
-            return launch_rows<__half, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what);
+            return launch_rows<__half, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
         case MHLO_DT_BF16:
-            return launch_rows<__nv_bfloat16, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what);
+            return launch_rows<__nv_bfloat16, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
         default:
             return fail(MHLO_CUDA_UNSUPPORTED, "%s: dtype %d is not a float type this kernel handles", what,
                         dtype);
@@ -435,6 +497,23 @@ int mhlo_cuda_rms_norm(int dtype, const void* x_dev, const void* gamma_dev, void
                        int64_t hidden, float eps, const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream) {
     return mhlo::dispatch_rows<mhlo::kRmsNorm>(dtype, x_dev, gamma_dev, nullptr, y_dev, rows, hidden, 1, eps,
                                                tuning, stream, "rms_norm");
+}
+
+int mhlo_cuda_add_layer_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev, const void* beta_dev,
+                             void* sum_dev, void* y_dev, int64_t rows, int64_t hidden, float eps, const mhlo_cuda_row_tuning* tuning,
+                             mhlo_cuda_stream_t stream) {
+    if (rows * hidden > 0 && (residual_dev == nullptr || sum_dev == nullptr))
+        return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "add_layer_norm: null residual or sum pointer");
+    return mhlo::dispatch_rows<mhlo::kLayerNorm>(dtype, x_dev, gamma_dev, beta_dev, y_dev, rows, hidden, 1, eps, tuning, stream,
+                                                 "add_layer_norm", residual_dev, sum_dev);
+}
+
+int mhlo_cuda_add_rms_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev, void* sum_dev, void* y_dev,
+                           int64_t rows, int64_t hidden, float eps, const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream) {
+    if (rows * hidden > 0 && (residual_dev == nullptr || sum_dev == nullptr))
+        return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "add_rms_norm: null residual or sum pointer");
+    return mhlo::dispatch_rows<mhlo::kRmsNorm>(dtype, x_dev, gamma_dev, nullptr, y_dev, rows, hidden, 1, eps, tuning, stream,
+                                               "add_rms_norm", residual_dev, sum_dev);
 }
 
 int mhlo_cuda_softmax(int dtype, const void* x_dev, void* y_dev, int64_t outer, int64_t axis_len, int64_t inner,

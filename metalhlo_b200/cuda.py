@@ -84,6 +84,8 @@ _PROTOTYPES = {
     "mhlo_cuda_elementwise": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp]),
     "mhlo_cuda_elementwise_to_view": (C.c_int, [C.POINTER(View), _i32, C.POINTER(EwInst), _i32, C.POINTER(View), _vp]),
     "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "mhlo_cuda_add_layer_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
+    "mhlo_cuda_add_rms_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_convert_many": (C.c_int, [C.POINTER(ConvertJob), _i32, _vp]),
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
@@ -167,6 +169,31 @@ def rms_norm(x, gamma, eps: float = 1e-5, out=None, tuning=None, stream=None):
     check(lib.mhlo_cuda_rms_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(gamma), _ptr(out), rows, hidden, eps,
                                  _tuning(tuning), _stream(stream)))
     return out
+
+
+def add_layer_norm(x, residual, gamma, beta, eps: float = 1e-5, tuning=None, stream=None):
+    """(x + residual, LayerNorm(x + residual)) in one pass (see ``mhlo_cuda_add_layer_norm``)."""
+    import torch
+
+    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous() and residual.shape == x.shape
+    total, out = torch.empty_like(x), torch.empty_like(x)
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    check(lib.mhlo_cuda_add_layer_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), _ptr(gamma), _ptr(beta), _ptr(total), _ptr(out),
+                                       rows, hidden, eps, _tuning(tuning), _stream(stream)))
+    return total, out
+
+
+def add_rms_norm(x, residual, gamma, eps: float = 1e-5, tuning=None, stream=None):
+    import torch
+
+    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous() and residual.shape == x.shape
+    total, out = torch.empty_like(x), torch.empty_like(x)
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    check(lib.mhlo_cuda_add_rms_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), _ptr(gamma), _ptr(total), _ptr(out), rows, hidden,
+                                     eps, _tuning(tuning), _stream(stream)))
+    return total, out
 
 
 def device_error() -> int:

@@ -293,6 +293,15 @@ def pattern_cases(rng, dt):
     out.append((f"pattern_layer_norm_plain_{dt}", func([t], [t], body.rstrip("\n"), res), [x]))
     body, res = layer_norm_text("%arg0", shape, dt, "%arg1", None, eps=1e-6, rms=True)
     out.append((f"pattern_rms_norm_{dt}", func([t, tv], [t], body.rstrip("\n"), res), [x, g]))
+    # residual add feeding a norm, the sum also returned (fused_add_layer_norm / fused_add_rms_norm at O3)
+    r2 = np.random.default_rng(sum(map(ord, dt)))
+    xr = (0.5 * r2.standard_normal(shape)).astype(np.float32).astype(NP[dt])
+    body, res = layer_norm_text("%s0", shape, dt, "%arg2", "%arg3")
+    out.append((f"pattern_residual_layer_norm_{dt}", func([t, t, tv, tv], [t, t], f"    %s0 = stablehlo.add %arg0, %arg1 : {t}\n" + body.rstrip("\n"),
+                                                           f"%s0, {res}"), [x, xr, g, b]))
+    body, res = layer_norm_text("%s0", shape, dt, "%arg2", None, eps=1e-6, rms=True)
+    out.append((f"pattern_residual_rms_norm_{dt}", func([t, t, tv], [t, t], f"    %s0 = stablehlo.add %arg0, %arg1 : {t}\n" + body.rstrip("\n"),
+                                                         f"%s0, {res}"), [x, xr, g]))
     body, res = gelu_text("%arg0", shape, dt)
     out.append((f"pattern_gelu_{dt}", func([t], [t], body.rstrip("\n"), res), [x]))
     # dense layer: x.w + b then GELU (fused_matmul_bias_activation at O3)

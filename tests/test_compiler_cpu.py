@@ -52,6 +52,7 @@ def test_o3_rewrites_patterns_to_the_reference_custom_call_targets(dt):
         f"pattern_softmax_{dt}": ["fused_softmax"], f"pattern_softmax_axis1_{dt}": ["fused_softmax"],
         f"pattern_layer_norm_{dt}": ["fused_layer_norm"], f"pattern_layer_norm_plain_{dt}": ["fused_layer_norm"],
         f"pattern_rms_norm_{dt}": ["fused_rms_norm"], f"pattern_gelu_{dt}": ["fused_gelu"],
+        f"pattern_residual_layer_norm_{dt}": ["fused_add_layer_norm"], f"pattern_residual_rms_norm_{dt}": ["fused_add_rms_norm"],
         f"pattern_dense_gelu_{dt}": ["fused_matmul_bias_activation"],
         f"pattern_attention_BHSD_full_{dt}": ["fused_scaled_dot_product_attention"],
         f"pattern_attention_BSHD_causal_{dt}": ["fused_scaled_dot_product_attention"],

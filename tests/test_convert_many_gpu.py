@@ -18,7 +18,7 @@ def test_every_pair_size_and_alignment_bit_exact():
 
     g = torch.Generator().manual_seed(9)
     jobs, checks = [], []
-    for si, n in enumerate(SIZES):
+    for si, n in enumerate(SIZES + SIZES):
         for pi, (sd, dd) in enumerate(PAIRS):
             shift = (si + pi) % 2  # every other job starts one element past a 16-byte boundary
             src_store = (torch.randn(n + 1, generator=g) * 300).to(sd).cuda()

@@ -42,6 +42,23 @@ def test_layer_norm_rms_softmax_vector_path(dtype, rows, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("rows,hidden", [(64, 4096), (33, 768), (7, 8), (300, 1024), (3, 12288), (5, 1001), (2, 16384)])
+def test_residual_add_fused_into_the_norm(dtype, rows, hidden):
+    """sum = x + r must be bit-identical to a separate add in the element type; the norm is that of the rounded sum."""
+    cuda = cuda_mod()
+    x, gamma, beta = make_rows(rows, hidden, dtype, seed=5)
+    r = make_rows(rows, hidden, dtype, seed=6, scale=0.5)[0]
+    want_sum = (x.float() + r.float()).to(dtype)
+    rel = rel_for(dtype)
+    total, out = cuda.add_layer_norm(x.cuda(), r.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    assert torch.equal(total.cpu().view(torch.uint8), want_sum.view(torch.uint8))
+    assert_close(to_np(out), oracle.layer_norm(want_sum, gamma, beta, 1e-5), rel, "add_layer_norm")
+    total, out = cuda.add_rms_norm(x.cuda(), r.cuda(), gamma.cuda(), 1e-5)
+    assert torch.equal(total.cpu().view(torch.uint8), want_sum.view(torch.uint8))
+    assert_close(to_np(out), oracle.rms_norm(want_sum, gamma, 1e-5), rel, "add_rms_norm")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
 @pytest.mark.parametrize("rows,hidden", [(9, 1), (4, 7), (3, 1001), (2, 70001), (1, 300000)])
 def test_ragged_hidden_takes_the_strided_path(dtype, rows, hidden):
     cuda = cuda_mod()
