@@ -85,6 +85,16 @@ int mhlo_cuda_download(void* dst_host, const void* src_dev, size_t bytes, mhlo_c
 int mhlo_cuda_copy(void* dst_dev, const void* src_dev, size_t bytes, mhlo_cuda_stream_t stream);
 int mhlo_cuda_memset(void* dst_dev, int byte_value, size_t bytes, mhlo_cuda_stream_t stream);
 
+/*
+ * Sharing one allocation between the processes of a multi-GPU job (one process per GPU on one node): the owner
+ * exports a 64-byte handle of memory it got from mhlo_cuda_alloc, the others open it and receive an address that is
+ * valid in their own process and reaches the owner's GPU over NVLink (peer access is enabled on first use). Close
+ * before the owner frees. No counterpart in the reference, which runs on one device.
+ */
+int mhlo_cuda_ipc_export(const void* dev_ptr, unsigned char out_handle[64]);
+int mhlo_cuda_ipc_open(const unsigned char handle[64], void** out_dev_ptr);
+int mhlo_cuda_ipc_close(void* dev_ptr);
+
 /* Device-side timing (replaces MTLCommandBuffer GPUStartTime/GPUEndTime, Executable.swift:164). */
 int mhlo_cuda_event_create(void** out_event);
 int mhlo_cuda_event_destroy(void* event);
@@ -347,6 +357,22 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
                    const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
                    int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
                    mhlo_cuda_stream_t stream);
+
+/*
+ * C = A . B for a B (and C) split by columns over n_ranks GPUs, with the all-gather of C fused into the epilogue:
+ * this rank computes columns [rank * n_local, (rank + 1) * n_local) of the [m, n_local * n_ranks] row-major result
+ * and every tile is stored, straight from the epilogue, into that column range of all n_ranks copies of C
+ * (c_devs[r] = base of rank r's copy: c_devs[rank] is local memory, the others are peer addresses from
+ * mhlo_cuda_ipc_open). Transfers over NVLink therefore overlap the tensor-core work tile by tile, and no separate
+ * gather or interleave pass runs. A: [m, k], B: [k, n_local] (this rank's columns), strides {row, col} in elements.
+ * When every rank's kernel has finished (a barrier across the ranks after a stream sync), every copy of C is complete.
+ * bf16 / f16 operands on the tensor-core path only; n_ranks <= 8. The reference has no multi-device path; this
+ * is the exchange step of the column-split GEMM.
+ */
+int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2],
+                              const void* b_dev, const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks,
+                              int32_t rank, int64_t m, int64_t n_local, int64_t k, const void* bias_dev,
+                              int32_t epilogue, mhlo_cuda_stream_t stream);
 
 /*
  * Every wait inside the tensor-core kernels (mbarrier phases fed by TMA and tcgen05.commit) is bounded; a kernel

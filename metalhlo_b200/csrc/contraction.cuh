@@ -13,6 +13,11 @@ struct GemmProblem {
     int64_t as[4], bs[4];  // {batch0, batch1, row, col} element strides
     int64_t batch0, batch1, m, n, k;
     int32_t in_dtype, out_dtype, epilogue;
+    // Output placement. ldc = elements between rows of C (0: dense, = n); c_col0 = first column this product fills
+    // inside a wider matrix; copies[] = further matrices (peers' memory) that receive the same tile stores.
+    int64_t ldc = 0, c_col0 = 0;
+    void* copies[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int32_t n_copies = 0;
 };
 
 struct AttnShape {

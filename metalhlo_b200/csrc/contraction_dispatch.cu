@@ -139,6 +139,34 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
     return mhlo_cuda_elementwise(in, n_in, prog, ni, c_dev, out_dtype, shape, 2, stream);
 }
 
+int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2], const void* b_dev,
+                              const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks, int32_t rank, int64_t m, int64_t n_local,
+                              int64_t k, const void* bias_dev, int32_t epilogue, mhlo_cuda_stream_t stream) {
+    if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: unknown epilogue %d", epilogue);
+    if (!a_strides || !b_strides || !c_devs) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: null argument");
+    if (n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: rank %d of %d (1 to 8 ranks)", rank, n_ranks);
+    if (m < 0 || n_local < 0 || k < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: negative extent");
+    if (m == 0 || n_local == 0) return MHLO_CUDA_OK;
+    for (int r = 0; r < n_ranks; ++r)
+        if (c_devs[r] == nullptr) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: destination %d is null", r);
+    GemmProblem p;
+    p.a = a_dev; p.b = b_dev; p.c = c_devs[rank]; p.bias = bias_dev;
+    p.as[0] = p.as[1] = 0; p.as[2] = a_strides[0]; p.as[3] = a_strides[1];
+    p.bs[0] = p.bs[1] = 0; p.bs[2] = b_strides[0]; p.bs[3] = b_strides[1];
+    p.batch0 = p.batch1 = 1; p.m = m; p.n = n_local; p.k = k;
+    p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
+    p.ldc = n_local * n_ranks;
+    p.c_col0 = n_local * rank;
+    p.n_copies = 0;
+    for (int r = 0; r < n_ranks; ++r)
+        if (r != rank) p.copies[p.n_copies++] = c_devs[r];
+    if (!gemm_tc_supported(p))
+        return fail(MHLO_CUDA_UNSUPPORTED, "gemm_all_gather: needs the tensor-core path (bf16 / f16 operands, 16-byte aligned rows, k > 0)");
+    return gemm_tc_launch(p, static_cast<cudaStream_t>(stream));
+}
+
 int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_strides[3], const void* k_dev,
                         const int64_t k_strides[3], const void* v_dev, const int64_t v_strides[3],
                         const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,

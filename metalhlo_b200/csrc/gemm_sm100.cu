@@ -68,6 +68,9 @@ struct GemmParams {
     int32_t out_dtype;               // MHLO_DT_BF16 / F16 / F32
     int32_t epilogue;
     int32_t c_vec_ok;                // rows of C start 16-byte aligned: vector stores allowed
+    int64_t ldc, c_col0;             // row pitch of C in elements; first column of this product inside the wider matrix
+    void* copies[7];                 // further destinations of every tile store (the same matrix in peers' memory)
+    int32_t n_copies;
 };
 
 template <int BN, int STAGES>
@@ -223,7 +226,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int64_t row0 = static_cast<int64_t>(tm) * BM + quarter * 32;
             const int chunk_cols = p.out_dtype == MHLO_DT_F32 ? 32 : 64;
             uint8_t* stage_tile = smem + L::kStagingOff + (warp - 2) * 4096;
-            uint8_t* cbase = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(bz) * p.m * p.n * out_es;
+            const int64_t batch_off = static_cast<int64_t>(bz) * p.m * p.ldc * out_es;
+            uint8_t* cbase = static_cast<uint8_t*>(p.c) + batch_off;
             // bias of this warp's BN/2 columns, spread over the lanes (column i lives in lane i / kBiasPerLane, register
             // i % kBiasPerLane) and handed out with shuffles: one global load per column per tile instead of one per element
             constexpr int kBiasPerLane = BN / 2 / 32;
@@ -307,7 +311,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int rr = it * 4 + (lane >> 3), c = lane & 7;
                         if (row0 + rr < p.m) {
                             const uint4 val = *reinterpret_cast<const uint4*>(stage_tile + rr * 128 + ((c ^ (rr & 7)) << 4));
-                            *reinterpret_cast<uint4*>(cbase + ((row0 + rr) * p.n + col0) * out_es + c * 16) = val;
+                            const int64_t at = ((row0 + rr) * p.ldc + p.c_col0 + col0) * out_es + c * 16;
+                            *reinterpret_cast<uint4*>(cbase + at) = val;
+                            // the same 16 bytes into every other copy of C (peer GPUs' memory, plain stores over NVLink)
+                            for (int d = 0; d < p.n_copies; ++d)
+                                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.copies[d]) + batch_off + at) = val;
                         }
                     }
                 } else {
@@ -315,13 +323,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int per_lane = out_es == 4 ? 1 : 2;  // elements in a lane's 4 bytes
                     for (int rr = 0; rr < 32 && row0 + rr < p.m; ++rr) {
                         const uint32_t word = *reinterpret_cast<const uint32_t*>(stage_tile + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
-                        uint8_t* dst = cbase + ((row0 + rr) * p.n + col0) * out_es;
+                        const int64_t at = ((row0 + rr) * p.ldc + p.c_col0 + col0) * out_es;
                         const int e0 = lane * per_lane;
-                        if (out_es == 4) {
-                            if (e0 < cols_left) reinterpret_cast<uint32_t*>(dst)[e0] = word;
-                        } else {
-                            if (e0 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0] = static_cast<uint16_t>(word & 0xffffu);
-                            if (e0 + 1 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0 + 1] = static_cast<uint16_t>(word >> 16);
+                        for (int d = -1; d < p.n_copies; ++d) {
+                            uint8_t* dst = (d < 0 ? cbase : static_cast<uint8_t*>(p.copies[d]) + batch_off) + at;
+                            if (out_es == 4) {
+                                if (e0 < cols_left) reinterpret_cast<uint32_t*>(dst)[e0] = word;
+                            } else {
+                                if (e0 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0] = static_cast<uint16_t>(word & 0xffffu);
+                                if (e0 + 1 < cols_left) reinterpret_cast<uint16_t*>(dst)[e0 + 1] = static_cast<uint16_t>(word >> 16);
+                            }
                         }
                     }
                 }
@@ -444,7 +455,15 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     p.out_dtype = pr.out_dtype;
     p.epilogue = pr.epilogue;
     const size_t out_es = pr.out_dtype == MHLO_DT_F32 ? 4 : 2;
-    p.c_vec_ok = aligned16(pr.c) && (pr.n * out_es) % 16 == 0;
+    p.ldc = pr.ldc > 0 ? pr.ldc : pr.n;
+    p.c_col0 = pr.c_col0;
+    p.n_copies = pr.n_copies;
+    bool aligned = aligned16(pr.c) && (p.ldc * out_es) % 16 == 0 && (p.c_col0 * out_es) % 16 == 0;
+    for (int d = 0; d < 7; ++d) {
+        p.copies[d] = d < pr.n_copies ? pr.copies[d] : nullptr;
+        if (d < pr.n_copies) aligned = aligned && aligned16(pr.copies[d]);
+    }
+    p.c_vec_ok = aligned;
 
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT>;
     static bool attr_set = false;

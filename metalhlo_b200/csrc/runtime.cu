@@ -71,6 +71,29 @@ int mhlo_cuda_device_name(int ordinal, char* out_name, size_t cap) {
     return MHLO_CUDA_OK;
 }
 
+int mhlo_cuda_ipc_export(const void* dev_ptr, unsigned char out_handle[64]) {
+    if (!dev_ptr || !out_handle) return fail(MHLO_CUDA_INVALID_ARGUMENT, "ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    MHLO_CUDA_TRY(cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr)), MHLO_CUDA_BUFFER_FAILED);
+    memcpy(out_handle, &h, sizeof h);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_ipc_open(const unsigned char handle[64], void** out_dev_ptr) {
+    if (!handle || !out_dev_ptr) return fail(MHLO_CUDA_INVALID_ARGUMENT, "ipc_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    MHLO_CUDA_TRY(cudaIpcOpenMemHandle(out_dev_ptr, h, cudaIpcMemLazyEnablePeerAccess), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_ipc_close(void* dev_ptr) {
+    if (!dev_ptr) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaIpcCloseMemHandle(dev_ptr), MHLO_CUDA_BUFFER_FAILED);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_stream_create(mhlo_cuda_stream_t* out_stream) {
     if (!out_stream) return fail(MHLO_CUDA_INVALID_ARGUMENT, "stream_create: null output");
     cudaStream_t s;
