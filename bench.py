@@ -165,7 +165,7 @@ def run_ours(args):
         raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
 
@@ -342,14 +342,17 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
     g = torch.Generator(device=dev).manual_seed(42 + rank)
     # ---- GEMM 8192^3 bf16: B and C column-split across ranks, C slices all-gathered and interleaved to row-major
     n = 8192
-    ncols = n // world
+    from metalhlo_b200 import sharding
+
+    col_block = sharding.column_shard(n, world, rank)
+    ncols = col_block.count
     a = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
     b = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
     c_slice = torch.empty(n, ncols, device=dev, dtype=torch.bfloat16)
     c_all = torch.empty(world, n, ncols, device=dev, dtype=torch.bfloat16) if world > 1 else None
     c_full = torch.empty(n, n, device=dev, dtype=torch.bfloat16) if world > 1 else None
     a_str, b_str = cuda._i64s([0, 0, n, 1]), cuda._i64s([0, 0, n, 1])
-    b_ptr = b.data_ptr() + rank * ncols * 2
+    b_ptr = b.data_ptr() + col_block.start * 2
     stream = torch.cuda.current_stream().cuda_stream
 
     def gemm_step():
@@ -372,8 +375,7 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
         cuda.check(cuda.lib.mhlo_cuda_alloc(n * n * 2, C.byref(own)))
         handle = C.create_string_buffer(64)
         cuda.check(cuda.lib.mhlo_cuda_ipc_export(own, handle))
-        handles = [None] * world
-        dist.all_gather_object(handles, handle.raw)
+        handles = sharding.exchange_handles(handle.raw, dist)
         peers = []
         for r in range(world):
             if r == rank:
@@ -413,7 +415,7 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
         cuda.check(cuda.lib.mhlo_cuda_free(own))
     del a, b, c_slice, c_all, c_full
     # ---- batched GEMM [64,2048,128].[64,128,2048]: batch sharded, HBM-limited
-    nb = 64 // world if world <= 64 else 1
+    nb = max(1, sharding.contiguous_shard(64, world, rank).count)
     a = (torch.randn(nb, 2048, 128, device=dev, generator=g) / math.sqrt(128)).to(torch.bfloat16)
     b = (torch.randn(nb, 128, 2048, device=dev, generator=g) / math.sqrt(128)).to(torch.bfloat16)
     c = torch.empty(nb, 2048, 2048, device=dev, dtype=torch.bfloat16)
@@ -423,7 +425,7 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
                                 "frac_of_measured_hbm": bytes_total / ms / 1e6 / (peaks["hbm_gbs"] * world)}
     del a, b, c
     # ---- flash attention B8 H32 S4096 D128 bf16, batch sharded
-    bsz = max(1, 8 // world)
+    bsz = max(1, sharding.contiguous_shard(8, world, rank).count)
     q, k, v = (torch.randn(bsz, 32, 4096, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
     o = torch.empty_like(q)
     for causal, flop in ((False, 2_199_023_255_552), (True, 1_099_780_063_232)):
@@ -436,7 +438,7 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
     # ---- GPT-2-small forward through the C API (O3), batch 32 sharded across ranks, fp16 compute, fp32 parameters
     from metalhlo_b200 import capi, modules
 
-    batch = max(1, 32 // world)
+    batch = max(1, sharding.contiguous_shard(32, world, rank).count)
     text, params = modules.gpt2_module(batch=batch, seq=1024)
     client = capi.Client()
     exe = client.compile(text, opt_level=3)
@@ -511,8 +513,19 @@ TRAFFIC_BYTES: dict = {
 }
 
 
+def _reserve_stdout():
+    """Stdout carries exactly one JSON line. Libraries (NCCL's version banner, for one) write to file descriptor 1
+    directly, so descriptor 1 is pointed at stderr for the whole run and the JSON line goes to a private copy of the
+    original descriptor."""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(keep, "w", buffering=1)
+
+
 def main():
     global ROWS, KERNEL_BYTES
+    _reserve_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
