@@ -459,7 +459,7 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
     *out_text = nullptr;
     try {
         Module m = parse_module(mlir_text);
-        Function f = m.main();
+        Function f = flatten_main(m);
         CompileOptions opt;
         opt.opt_level = optimization_level;
         run_pass_pipeline(f, opt);

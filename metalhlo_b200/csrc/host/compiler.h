@@ -37,6 +37,15 @@ std::set<std::string> passes_for_level(int opt_level);
 // Runs the pipeline once over f (single sweep, as the reference does). Returns one record per registered pass.
 std::vector<PassRecord> run_pass_pipeline(Function& f, const CompileOptions& options);
 
+// ---- flattening (inline.cpp) ----
+// Inlines every `call` of @main (transitively) from the module's other functions. True when something changed.
+bool inline_calls(Module& m);
+// Unrolls stablehlo.while loops whose trip count is static: a counter compared with a constant in the condition,
+// advanced by a constant in the body, starting from a constant. Other loops are left in place.
+bool unroll_static_whiles(Function& f);
+// Both, repeated until neither applies; returns the flattened @main.
+Function flatten_main(Module& m);
+
 // ---- memory plan -----------------------------------------------------------------------------------------------
 
 struct PlanInterval {

@@ -1125,7 +1125,7 @@ Executable::~Executable() {
 
 std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const CompileOptions& options) {
     Module m = parse_module(mlir);
-    Function f = m.main();
+    Function f = flatten_main(m);
     if (std::getenv("METALHLO_DUMP_MLIR")) fprintf(stderr, "[metalhlo] parsed module:\n%s\n", print_function(f).c_str());
     std::unique_ptr<Executable> exe(new Executable());
     exe->pass_log_ = run_pass_pipeline(f, options);

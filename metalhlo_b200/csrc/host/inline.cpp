@@ -1,0 +1,263 @@
+// Flattening of the module a jitted JAX function lowers to: `call`s of private functions are inlined into @main and
+// `stablehlo.while` loops with a static trip count (what lax.fori_loop emits) are unrolled, so that the straight-line
+// executor can run them. The reference does both on the module text before compiling
+// (Sources/PJRTMetalHLO/PJRTExecutable.swift:458-1657: inlineSimpleCallWrapper, inlineCallsInBody,
+// unrollStaticWhileLoops, iterated until nothing changes); here they work on the parsed IR.
+#include <map>
+
+#include "compiler.h"
+
+namespace mhlo {
+namespace {
+
+constexpr int kMaxInlineRounds = 64;     // nesting depth of calls
+constexpr int64_t kMaxTripCount = 4096;  // loops longer than this stay loops (and are rejected by the executor)
+constexpr size_t kMaxUnrolledOps = 2000000;
+
+// Copies ops from `src` into `dst`, giving every value they define a fresh id in dst. Values that are not in the map
+// are taken to be visible at the destination as they are (only valid when src and dst are the same function).
+struct Cloner {
+    Function& dst;
+    const Function& src;
+    bool same_function;
+    std::map<int, int> map;
+
+    int remap(int v) const {
+        auto it = map.find(v);
+        if (it != map.end()) return it->second;
+        if (!same_function) fail_compile("internal: value " + src.values[v].name + " of an inlined function has no definition at the call site");
+        return v;
+    }
+    int fresh(int v) {
+        const int nv = dst.new_value(src.values[v].type, src.values[v].name);
+        map[v] = nv;
+        return nv;
+    }
+    Op clone(const Op& o) {
+        Op c = o;
+        for (int& v : c.operands) v = remap(v);
+        c.regions.clear();
+        for (const auto& r : o.regions) {
+            auto nr = std::make_shared<Region>();
+            for (int a : r->args) nr->args.push_back(fresh(a));
+            for (const Op& ro : r->ops) nr->ops.push_back(clone(ro));
+            c.regions.push_back(nr);
+        }
+        for (int& v : c.results) v = fresh(v);
+        return c;
+    }
+};
+
+void apply_alias(Op& o, const std::map<int, int>& alias) {
+    if (alias.empty()) return;
+    for (int& v : o.operands) {
+        for (auto it = alias.find(v); it != alias.end(); it = alias.find(v)) v = it->second;
+    }
+    for (auto& r : o.regions)
+        for (Op& ro : r->ops) apply_alias(ro, alias);
+}
+
+const Function* find_function(const Module& m, const std::string& name) {
+    for (const Function& f : m.functions)
+        if (f.name == name) return &f;
+    return nullptr;
+}
+
+// ---- while analysis -------------------------------------------------------------------------------------------------
+
+const Op* def_in(const std::vector<Op>& ops, int v) {
+    for (const Op& o : ops)
+        for (int r : o.results)
+            if (r == v) return &o;
+    return nullptr;
+}
+
+// Scalar integer constant defined in `inner` (a region) or among the top-level ops `outer`.
+bool int_constant(const std::vector<Op>& outer, const std::vector<Op>& inner, int v, int64_t* out) {
+    const Op* o = def_in(inner, v);
+    if (!o) o = def_in(outer, v);
+    if (!o || o->name != "constant") return false;
+    const Attr* a = o->attr("value");
+    if (!a || a->kind != Attr::Dense || o->result_types.empty()) return false;
+    const TensorType& t = o->result_types[0];  // the payload is stored in the result's element type
+    if (t.count() != 1 || is_float(t.dtype) || t.dtype == DType::I1) return false;
+    const size_t es = dtype_size(t.dtype);
+    if (a->dense.size() < es || es > 8) return false;
+    uint64_t raw = 0;
+    for (size_t i = 0; i < es; ++i) raw |= static_cast<uint64_t>(a->dense[i]) << (8 * i);
+    if (!is_unsigned(t.dtype) && es < 8 && (raw >> (8 * es - 1)) & 1) raw |= ~0ull << (8 * es);  // sign-extend
+    *out = static_cast<int64_t>(raw);
+    return true;
+}
+
+struct LoopShape {
+    int counter = -1;  // index of the iteration argument that counts
+    int64_t init = 0, limit = 0, step = 0;
+    std::string direction;
+    int64_t trips = 0;
+};
+
+bool compare(const std::string& dir, int64_t a, int64_t b) {
+    if (dir == "LT") return a < b;
+    if (dir == "LE") return a <= b;
+    if (dir == "GT") return a > b;
+    if (dir == "GE") return a >= b;
+    if (dir == "NE") return a != b;
+    return false;
+}
+
+// cond: return(compare(dir, iter_k, const)); body: result_k = add/subtract(iter_k, const); init_k constant.
+// `f` = the top-level ops that precede the loop.
+bool analyse_loop(const std::vector<Op>& f, const Op& w, LoopShape* shape) {
+    if (w.regions.size() != 2) return false;
+    const Region& cond = *w.regions[0];
+    const Region& body = *w.regions[1];
+    if (cond.ops.empty() || body.ops.empty() || cond.ops.back().name != "return" || body.ops.back().name != "return") return false;
+    if (cond.ops.back().operands.size() != 1 || body.ops.back().operands.size() != w.operands.size()) return false;
+    const Op* cmp = def_in(cond.ops, cond.ops.back().operands[0]);
+    if (!cmp || cmp->name != "compare" || cmp->operands.size() != 2) return false;
+    std::string dir = cmp->str_attr("comparison_direction");
+    int k = -1;
+    int64_t limit = 0;
+    for (int side = 0; side < 2 && k < 0; ++side) {
+        for (size_t i = 0; i < cond.args.size(); ++i)
+            if (cmp->operands[side] == cond.args[i] && int_constant(f, cond.ops, cmp->operands[1 - side], &limit)) {
+                k = static_cast<int>(i);
+                if (side == 1) {  // const <dir> iter  ==  iter <mirrored dir> const
+                    if (dir == "LT") dir = "GT"; else if (dir == "LE") dir = "GE"; else if (dir == "GT") dir = "LT"; else if (dir == "GE") dir = "LE";
+                }
+                break;
+            }
+    }
+    if (k < 0) return false;
+    const Op* upd = def_in(body.ops, body.ops.back().operands[static_cast<size_t>(k)]);
+    if (!upd || (upd->name != "add" && upd->name != "subtract") || upd->operands.size() != 2) return false;
+    int64_t step = 0;
+    if (upd->operands[0] == body.args[static_cast<size_t>(k)] && int_constant(f, body.ops, upd->operands[1], &step)) {
+        if (upd->name == "subtract") step = -step;
+    } else if (upd->name == "add" && upd->operands[1] == body.args[static_cast<size_t>(k)] && int_constant(f, body.ops, upd->operands[0], &step)) {
+    } else {
+        return false;
+    }
+    int64_t init = 0;
+    if (step == 0 || !int_constant(f, {}, w.operands[static_cast<size_t>(k)], &init)) return false;
+    int64_t trips = 0;
+    for (int64_t i = init; compare(dir, i, limit); i += step)
+        if (++trips > kMaxTripCount) return false;
+    shape->counter = k;
+    shape->init = init;
+    shape->limit = limit;
+    shape->step = step;
+    shape->direction = dir;
+    shape->trips = trips;
+    return true;
+}
+
+}  // namespace
+
+bool inline_calls(Module& m) {
+    Function& main = m.main();
+    bool changed = false;
+    for (int round = 0; round < kMaxInlineRounds; ++round) {
+        bool any = false;
+        std::vector<Op> out;
+        std::map<int, int> alias;  // results of removed calls -> the values that replace them
+        for (Op& op : main.ops) {
+            apply_alias(op, alias);
+            if (op.dead || op.name != "call") {
+                out.push_back(std::move(op));
+                continue;
+            }
+            const std::string callee_name = op.str_attr("callee");
+            const Function* callee = find_function(m, callee_name);
+            if (!callee) fail_compile("call to unknown function @" + callee_name);
+            if (callee == &main) fail_unsupported("recursive call of @" + callee_name);
+            if (callee->args.size() != op.operands.size()) fail_compile("call of @" + callee_name + " with the wrong number of arguments");
+            Cloner c{main, *callee, false, {}};
+            for (size_t i = 0; i < callee->args.size(); ++i) c.map[callee->args[i]] = op.operands[i];
+            for (const Op& co : callee->ops) {
+                if (co.dead) continue;
+                if (co.name == "return") {
+                    if (co.operands.size() != op.results.size()) fail_compile("call of @" + callee_name + " binds the wrong number of results");
+                    for (size_t r = 0; r < op.results.size(); ++r) alias[op.results[r]] = c.remap(co.operands[r]);
+                    break;
+                }
+                out.push_back(c.clone(co));
+            }
+            any = true;
+        }
+        main.ops.swap(out);
+        main.compact();
+        if (!any) break;
+        changed = true;
+        if (round + 1 == kMaxInlineRounds) fail_unsupported("calls nested deeper than " + std::to_string(kMaxInlineRounds));
+    }
+    return changed;
+}
+
+bool unroll_static_whiles(Function& f) {
+    bool changed = false;
+    for (int round = 0; round < kMaxInlineRounds; ++round) {  // an unrolled body may contain further loops
+        bool any = false;
+        std::vector<Op> out;
+        std::map<int, int> alias;
+        for (Op& op : f.ops) {
+            apply_alias(op, alias);
+            LoopShape shape;
+            if (op.dead || op.name != "while" || !analyse_loop(out, op, &shape)) {
+                out.push_back(std::move(op));
+                continue;
+            }
+            const Region& body = *op.regions[1];
+            if (static_cast<size_t>(shape.trips) * body.ops.size() + out.size() > kMaxUnrolledOps)
+                fail_unsupported("unrolling a loop of " + std::to_string(shape.trips) + " iterations would exceed " + std::to_string(kMaxUnrolledOps) + " operations");
+            std::vector<int> current = op.operands;
+            const Op counter_init = *def_in(out, op.operands[static_cast<size_t>(shape.counter)]);  // a scalar integer constant
+            for (int64_t t = 0; t < shape.trips; ++t) {
+                if (t > 0) {
+                    // the counter of iteration t is known: give the body a constant instead of a chain of scalar adds
+                    Op k = counter_init;
+                    const int64_t value = shape.init + t * shape.step;
+                    Attr& payload = k.attrs["value"];
+                    const size_t es = dtype_size(k.result_types[0].dtype);
+                    payload.dense.assign(es, 0);
+                    for (size_t b = 0; b < es; ++b) payload.dense[b] = static_cast<uint8_t>(static_cast<uint64_t>(value) >> (8 * b));
+                    payload.splat = true;
+                    k.results = {f.new_value(k.result_types[0], "")};
+                    current[static_cast<size_t>(shape.counter)] = k.results[0];
+                    out.push_back(k);
+                }
+                Cloner c{f, f, true, {}};
+                for (size_t i = 0; i < body.args.size(); ++i) c.map[body.args[i]] = current[i];
+                std::vector<int> next = current;
+                for (const Op& bo : body.ops) {
+                    if (bo.name == "return") {
+                        for (size_t i = 0; i < next.size(); ++i) next[i] = c.remap(bo.operands[i]);
+                        break;
+                    }
+                    out.push_back(c.clone(bo));
+                }
+                current.swap(next);
+            }
+            for (size_t r = 0; r < op.results.size(); ++r) alias[op.results[r]] = current[r];
+            any = true;
+        }
+        f.ops.swap(out);
+        f.compact();
+        if (!any) break;
+        changed = true;
+    }
+    return changed;
+}
+
+Function flatten_main(Module& m) {
+    // calls and loops can hide each other (a loop body that calls, a callee that loops): repeat until neither changes
+    for (int round = 0; round < kMaxInlineRounds; ++round) {
+        const bool a = inline_calls(m);
+        const bool b = unroll_static_whiles(m.main());
+        if (!a && !b) break;
+    }
+    return m.main();
+}
+
+}  // namespace mhlo

@@ -840,8 +840,9 @@ class Parser {
             op->operands = inputs;
             op->operands.insert(op->operands.end(), inits.begin(), inits.end());
         } else if (op->name == "while" && accept('(')) {
-            // stablehlo.while(%iter = %init, ...) : types cond {..} do {..}: parsed for completeness; the
-            // executor rejects control flow
+            // stablehlo.while(%iter = %init, ...) : types [attributes {...}] cond {..} do {..}
+            // The iteration arguments are block arguments shared by both regions (regions[0] = cond, regions[1] = body).
+            std::vector<int> iter_vals;
             skip();
             while (cur() != ')') {
                 std::string n = value_name();
@@ -850,10 +851,32 @@ class Parser {
                 op->operands.push_back(v);
                 int bv = fn_->new_value(fn_->values[v].type, n);
                 names_[n] = bv;
+                iter_vals.push_back(bv);
                 if (!accept(',')) break;
                 skip();
             }
             expect(')');
+            skip();
+            if (accept(':')) {
+                for (;;) {
+                    op->result_types.push_back(type());
+                    skip();
+                    if (!accept(',')) break;
+                }
+            }
+            skip();
+            if (peek_word("attributes")) { word(); skip(); merge_attrs(op, attr_dict('{', '}')); skip(); }
+            for (const char* introducer : {"cond", "do"}) {
+                skip();
+                if (!peek_word(introducer)) error(std::string("expected '") + introducer + "' region of stablehlo.while");
+                word();
+                skip();
+                auto r = region();
+                r->args = iter_vals;
+                op->regions.push_back(r);
+            }
+            for (size_t i = 0; i < iter_vals.size() && i < op->result_types.size(); ++i) fn_->values[iter_vals[i]].type = op->result_types[i];
+            return;
         }
         for (;;) {
             skip();

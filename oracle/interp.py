@@ -559,6 +559,32 @@ class ModuleParser(Scanner):
                     continue
                 break
             op.operands = ins + inits
+        if name == "while" and self.accept("("):
+            # stablehlo.while(%iterArg = %init, ...) : types cond { ... } do { ... }: both regions see the iteration arguments
+            iters = []
+            while self.peek() != ")":
+                it_name = self.value()
+                self.expect("=")
+                op.operands.append(self.value())
+                iters.append(it_name)
+                if not self.accept(","):
+                    break
+            self.expect(")")
+            self.expect(":")
+            while True:
+                op.types.append(self.type())
+                if not self.accept(","):
+                    break
+            if self.accept("attributes"):
+                self.balanced("{", "}")
+            for word in ("cond", "do"):
+                self.expect(word)
+                r = self.region()
+                r.args = [(n, t) for n, t in zip(iters, op.types)]
+                op.regions.append(r)
+            op.in_types = list(op.types)
+            op.attrs["_kw"] = kw
+            return
         while True:
             self.ws()
             c = self.peek()
@@ -687,8 +713,31 @@ def _float_to_int(arr, ttype):
 
 
 class Interpreter:
-    def __init__(self, round_floats: bool = False):
+    def __init__(self, round_floats: bool = False, funcs=None):
         self.round_floats = round_floats
+        self.funcs = {f.name: f for f in (funcs or [])}
+
+    def op_call(self, op, a, t):
+        """func.call: the callee is interpreted on the argument arrays (no inlining)."""
+        callee = self.funcs.get(op.attrs.get("call_target_name") or op.attrs.get("callee"))
+        if callee is None:
+            raise Unsupported(f"call of unknown function {op.attrs}")
+        env = {name: x for name, x in zip(callee.args, a)}
+        return self._run_ops(callee.ops, env)
+
+    def op_while(self, op, a, t, env):
+        """stablehlo.while: the loop is run, condition first, for as long as the condition region returns true."""
+        cond, body = op.regions
+        state = list(a)
+        for _ in range(1_000_000):
+            scope = dict(env)
+            scope.update({name: x for (name, _), x in zip(cond.args, state)})
+            if not bool(np.asarray(self._run_ops(cond.ops, scope)[0]).reshape(())):
+                return state
+            scope = dict(env)
+            scope.update({name: x for (name, _), x in zip(body.args, state)})
+            state = self._run_ops(body.ops, scope)
+        raise Unsupported("while loop did not terminate within 1e6 iterations")
 
     def run(self, func, inputs):
         env = {}
@@ -725,6 +774,8 @@ class Interpreter:
         n, t = op.name, (op.types[0] if op.types else None)
         A = op.attrs
         it = op.in_types
+        if n == "while":
+            return self.op_while(op, a, t, env)
         f = getattr(self, "op_" + n, None)
         if f is not None:
             return f(op, a, t)
@@ -1074,4 +1125,4 @@ def evaluate(text, inputs, function: str | None = None, round_floats: bool = Fal
     """Runs @main (or `function`) of a StableHLO module on numpy inputs; returns a list of arrays (floats in fp64)."""
     funcs = parse(text)
     f = next((g for g in funcs if g.name == (function or "main")), funcs[0])
-    return Interpreter(round_floats).run(f, inputs)
+    return Interpreter(round_floats, funcs).run(f, inputs)

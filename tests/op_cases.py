@@ -224,6 +224,74 @@ def build_cases():
                              "      %10 = stablehlo.select %8, %ai, %bi : tensor<i1>, tensor<i32>\n"
                              "      stablehlo.return %9, %10 : tensor<f32>, tensor<i32>\n"
                              "    }", "%1#1"), [xas])
+    # ---- what jax.jit emits around the straight-line ops: calls of private functions and fori_loop-style while loops
+    rc = np.random.default_rng(99)
+    xa, xb = rc.standard_normal((4, 8)).astype(np.float32), rc.standard_normal(8).astype(np.float32)
+    add("call_nested", """module @jit_f attributes {mhlo.num_partitions = 1 : i32, mhlo.num_replicas = 1 : i32} {
+  func.func public @main(%arg0: tensor<4x8xf32>, %arg1: tensor<8xf32>) -> (tensor<4x8xf32> {jax.result_info = ""}) {
+    %0 = call @helper(%arg0, %arg1) : (tensor<4x8xf32>, tensor<8xf32>) -> tensor<4x8xf32>
+    %1 = stablehlo.exponential %0 : tensor<4x8xf32>
+    %2 = call @helper(%1, %arg1) : (tensor<4x8xf32>, tensor<8xf32>) -> tensor<4x8xf32>
+    return %2 : tensor<4x8xf32>
+  }
+  func.func private @helper(%arg0: tensor<4x8xf32>, %arg1: tensor<8xf32>) -> tensor<4x8xf32> {
+    %0 = stablehlo.broadcast_in_dim %arg1, dims = [1] : (tensor<8xf32>) -> tensor<4x8xf32>
+    %1 = stablehlo.add %arg0, %0 : tensor<4x8xf32>
+    %2 = call @inner(%1) : (tensor<4x8xf32>) -> tensor<4x8xf32>
+    return %2 : tensor<4x8xf32>
+  }
+  func.func private @inner(%arg0: tensor<4x8xf32>) -> tensor<4x8xf32> {
+    %0 = stablehlo.tanh %arg0 : tensor<4x8xf32>
+    return %0 : tensor<4x8xf32>
+  }
+}
+""", [xa, xb])
+    add("while_fori_loop", """module @jit_loop {
+  func.func public @main(%arg0: tensor<8xf32>) -> (tensor<8xf32>) {
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %0:2 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0) : tensor<i32>, tensor<8xf32>
+     cond {
+      %c_1 = stablehlo.constant dense<5> : tensor<i32>
+      %1 = stablehlo.compare  LT, %iterArg, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    } do {
+      %c_1 = stablehlo.constant dense<1> : tensor<i32>
+      %1 = stablehlo.add %iterArg, %c_1 : tensor<i32>
+      %cst = stablehlo.constant dense<1.500000e+00> : tensor<8xf32>
+      %2 = stablehlo.multiply %iterArg_0, %cst : tensor<8xf32>
+      %3 = stablehlo.convert %iterArg : (tensor<i32>) -> tensor<f32>
+      %4 = stablehlo.broadcast_in_dim %3, dims = [] : (tensor<f32>) -> tensor<8xf32>
+      %5 = stablehlo.add %2, %4 : tensor<8xf32>
+      stablehlo.return %1, %5 : tensor<i32>, tensor<8xf32>
+    }
+    return %0#1 : tensor<8xf32>
+  }
+}
+""", [xb])
+    add("while_countdown_with_call", """module @jit_loop2 {
+  func.func public @main(%arg0: tensor<4x8xf32>, %arg1: tensor<8xf32>) -> (tensor<4x8xf32>, tensor<i32>) {
+    %c = stablehlo.constant dense<7> : tensor<i32>
+    %0:2 = stablehlo.while(%iterArg = %arg0, %iterArg_0 = %c) : tensor<4x8xf32>, tensor<i32>
+     cond {
+      %c_1 = stablehlo.constant dense<1> : tensor<i32>
+      %1 = stablehlo.compare  GT, %iterArg_0, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    } do {
+      %c_1 = stablehlo.constant dense<2> : tensor<i32>
+      %1 = stablehlo.subtract %iterArg_0, %c_1 : tensor<i32>
+      %2 = call @step(%iterArg, %arg1) : (tensor<4x8xf32>, tensor<8xf32>) -> tensor<4x8xf32>
+      stablehlo.return %2, %1 : tensor<4x8xf32>, tensor<i32>
+    }
+    return %0#0, %0#1 : tensor<4x8xf32>, tensor<i32>
+  }
+  func.func private @step(%arg0: tensor<4x8xf32>, %arg1: tensor<8xf32>) -> tensor<4x8xf32> {
+    %0 = stablehlo.broadcast_in_dim %arg1, dims = [1] : (tensor<8xf32>) -> tensor<4x8xf32>
+    %1 = stablehlo.multiply %arg0, %0 : tensor<4x8xf32>
+    %2 = stablehlo.sine %1 : tensor<4x8xf32>
+    return %2 : tensor<4x8xf32>
+  }
+}
+""", [xa, xb])
     # ---- dot_general
     def dot_case(name, ashape, bshape, attrs, oshape, dt):
         if dt not in NP:
