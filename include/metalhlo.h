@@ -156,12 +156,17 @@ char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable);
 int32_t mhlo_b200_executable_launch_count(MHLOExecutableRef executable);
 /* Bytes of the statically planned arena that holds every intermediate. */
 int64_t mhlo_b200_executable_arena_bytes(MHLOExecutableRef executable);
+/* Executions of this program that were served by replaying a recorded CUDA graph. A program is recorded when it runs a
+ * second time on the same stream with the same input and output addresses (mhlo_b200_execute_on_device with buffers
+ * the caller keeps); METALHLO_CUDA_GRAPH=0 turns recording off. */
+int64_t mhlo_b200_executable_graph_replays(MHLOExecutableRef executable);
 /* Newline-separated labels of the launch list; free with mhlo_free_string. */
 char* mhlo_b200_executable_steps(MHLOExecutableRef executable);
 /* Device address of a buffer's storage (dense row-major). */
 void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer);
 /* Enqueues the program on `stream` (a cudaStream_t) reading/writing caller-owned dense device tensors of the
- * executable's declared types. Allocates nothing and does not synchronise. */
+ * executable's declared types. Does not synchronise; the only device allocations are stream-ordered scratch of split
+ * reductions. On a non-default stream, repeated calls with the same addresses replay a recorded CUDA graph. */
 MHLOStatusCode mhlo_b200_execute_on_device(MHLOExecutableRef executable, const void* const* input_ptrs,
                                            void* const* output_ptrs, void* stream);
 

@@ -86,6 +86,18 @@ int mhlo_cuda_copy(void* dst_dev, const void* src_dev, size_t bytes, mhlo_cuda_s
 int mhlo_cuda_memset(void* dst_dev, int byte_value, size_t bytes, mhlo_cuda_stream_t stream);
 
 /*
+ * CUDA graphs: record everything the calling thread enqueues on `stream` between begin and end into an executable
+ * graph, then replay it with one launch (replaces the per-dispatch encoder loop of IntegratedExecutor.swift:150-270
+ * for programs that run repeatedly on the same buffers). `stream` must not be the default stream. Nothing runs
+ * during capture. end returns the instantiated graph in *out_graph (NULL when the recorded work could not be
+ * instantiated); a capture that failed half-way is ended and reported as MHLO_CUDA_UNSUPPORTED.
+ */
+int mhlo_cuda_graph_capture_begin(mhlo_cuda_stream_t stream);
+int mhlo_cuda_graph_capture_end(mhlo_cuda_stream_t stream, void** out_graph);
+int mhlo_cuda_graph_launch(void* graph, mhlo_cuda_stream_t stream);
+int mhlo_cuda_graph_destroy(void* graph);
+
+/*
  * Sharing one allocation between the processes of a multi-GPU job (one process per GPU on one node): the owner
  * exports a 64-byte handle of memory it got from mhlo_cuda_alloc, the others open it and receive an address that is
  * valid in their own process and reaches the owner's GPU over NVLink (peer access is enabled on first use). Close

@@ -107,6 +107,7 @@ _PROTOTYPES = {
     "mhlo_b200_executable_optimized_text": (_vp, [_vp]),
     "mhlo_b200_executable_launch_count": (_i32, [_vp]),
     "mhlo_b200_executable_arena_bytes": (_i64, [_vp]),
+    "mhlo_b200_executable_graph_replays": (_i64, [_vp]),
     "mhlo_b200_executable_steps": (_vp, [_vp]),
     "mhlo_b200_buffer_device_pointer": (_vp, [_vp]),
     "mhlo_b200_execute_on_device": (C.c_int, [_vp, _P(_vp), _P(_vp), _vp]),
@@ -310,6 +311,10 @@ class Executable:
     @property
     def arena_bytes(self) -> int:
         return lib.mhlo_b200_executable_arena_bytes(self._h)
+
+    @property
+    def graph_replays(self) -> int:
+        return int(lib.mhlo_b200_executable_graph_replays(self._h))
 
     @property
     def steps(self):

@@ -559,6 +559,11 @@ int32_t mhlo_b200_executable_launch_count(MHLOExecutableRef executable) {
     ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
     return h ? h->exe->num_kernel_launches() : 0;
 }
+int64_t mhlo_b200_executable_graph_replays(MHLOExecutableRef executable) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    return h ? h->exe->graph_replays : 0;
+}
+
 int64_t mhlo_b200_executable_arena_bytes(MHLOExecutableRef executable) {
     ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
     return h ? h->exe->arena_bytes() : 0;

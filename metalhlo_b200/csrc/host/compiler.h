@@ -115,6 +115,20 @@ class Executable {
     std::vector<PassRecord> pass_log_;
     std::string optimized_text_;
     std::string error_;
+
+    // CUDA-graph replay of the launch list. A (stream, input pointers, output pointers) combination that comes back
+    // is recorded once and replayed from then on; combinations seen once run launch by launch.
+    struct GraphSlot {
+        std::vector<const void*> key;  // stream, inputs..., outputs...
+        void* graph = nullptr;         // instantiated graph; null until the key has been seen twice
+        uint64_t last_use = 0;
+    };
+    std::vector<GraphSlot> graph_slots_;
+    uint64_t graph_clock_ = 0;
+    bool graphs_usable_ = true;  // cleared when a capture of this program failed
+    int run_steps(const Ctx& c, bool debug, bool profile);
+  public:
+    int64_t graph_replays = 0;   // executions served by a graph launch
 };
 
 // Small helpers over backend_config JSON strings of fused custom calls.

@@ -1119,6 +1119,8 @@ void Lowering::plan() {
 // ---- Executable --------------------------------------------------------------------------------------------------------
 
 Executable::~Executable() {
+    for (GraphSlot& g : graph_slots_)
+        if (g.graph) mhlo_cuda_graph_destroy(g.graph);
     if (const_dev_) mhlo_cuda_free(const_dev_);
     if (arena_dev_) mhlo_cuda_free(arena_dev_);
 }
@@ -1149,11 +1151,8 @@ std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const C
     return exe;
 }
 
-int Executable::execute(const void* const* inputs, void* const* outputs, void* stream) {
-    Ctx c{inputs, outputs, arena_dev_, const_dev_, stream};
-    const bool debug = std::getenv("METALHLO_DEBUG_DISPATCH") != nullptr;
-    // METALHLO_PROFILE_GPU: per-step device times from CUDA events (synchronises after every step)
-    const bool profile = std::getenv("METALHLO_PROFILE_GPU") != nullptr;
+int Executable::run_steps(const Ctx& c, bool debug, bool profile) {
+    void* stream = c.stream;
     void *e0 = nullptr, *e1 = nullptr;
     if (profile) { mhlo_cuda_event_create(&e0); mhlo_cuda_event_create(&e1); }
     std::map<std::string, std::pair<int, double>> by_label;
@@ -1180,6 +1179,66 @@ int Executable::execute(const void* const* inputs, void* const* outputs, void* s
         mhlo_cuda_event_destroy(e0);
         mhlo_cuda_event_destroy(e1);
     }
+    return 0;
+}
+
+int Executable::execute(const void* const* inputs, void* const* outputs, void* stream) {
+    Ctx c{inputs, outputs, arena_dev_, const_dev_, stream};
+    const bool debug = std::getenv("METALHLO_DEBUG_DISPATCH") != nullptr;
+    // METALHLO_PROFILE_GPU: per-step device times from CUDA events (synchronises after every step)
+    const bool profile = std::getenv("METALHLO_PROFILE_GPU") != nullptr;
+    static const bool graphs_enabled = [] {
+        const char* v = std::getenv("METALHLO_CUDA_GRAPH");
+        return !(v && std::string(v) == "0");
+    }();
+    // Graph replay needs a capturable stream, a program worth recording and no per-step host work.
+    constexpr size_t kMinStepsForGraph = 8, kMaxSlots = 4;
+    if (!graphs_enabled || !graphs_usable_ || stream == nullptr || debug || profile || steps_.size() < kMinStepsForGraph)
+        return run_steps(c, debug, profile);
+
+    std::vector<const void*> key;
+    key.push_back(stream);
+    for (size_t i = 0; i < input_types_.size(); ++i) key.push_back(inputs[i]);
+    for (size_t i = 0; i < output_types_.size(); ++i) key.push_back(outputs[i]);
+    ++graph_clock_;
+    GraphSlot* slot = nullptr;
+    for (GraphSlot& s : graph_slots_)
+        if (s.key == key) { slot = &s; break; }
+    if (slot == nullptr) {
+        // first time with these buffers: run launch by launch and remember the combination
+        if (graph_slots_.size() < kMaxSlots) {
+            graph_slots_.emplace_back();
+            slot = &graph_slots_.back();
+        } else {
+            slot = &graph_slots_[0];
+            for (GraphSlot& s : graph_slots_)
+                if (s.last_use < slot->last_use) slot = &s;
+            if (slot->graph) mhlo_cuda_graph_destroy(slot->graph);
+            slot->graph = nullptr;
+        }
+        slot->key = key;
+        slot->last_use = graph_clock_;
+        return run_steps(c, false, false);
+    }
+    slot->last_use = graph_clock_;
+    if (slot->graph == nullptr) {
+        // second time: record the launch list (nothing executes while recording), then fall through to the replay
+        if (mhlo_cuda_graph_capture_begin(stream) != MHLO_CUDA_OK) return run_steps(c, false, false);  // e.g. the caller is recording
+        const int st = run_steps(c, false, false);
+        void* graph = nullptr;
+        const int end = mhlo_cuda_graph_capture_end(stream, &graph);
+        if (st != 0 || end != MHLO_CUDA_OK || graph == nullptr) {
+            if (graph) mhlo_cuda_graph_destroy(graph);
+            graphs_usable_ = false;  // something in this program cannot be recorded: stay with plain launches
+            return run_steps(c, false, false);
+        }
+        slot->graph = graph;
+    }
+    if (mhlo_cuda_graph_launch(slot->graph, stream) != MHLO_CUDA_OK) {
+        error_ = std::string("graph launch: ") + mhlo_cuda_last_error();
+        return MHLO_CUDA_EXECUTION_FAILED;
+    }
+    ++graph_replays;
     return 0;
 }
 

@@ -71,6 +71,50 @@ int mhlo_cuda_device_name(int ordinal, char* out_name, size_t cap) {
     return MHLO_CUDA_OK;
 }
 
+int mhlo_cuda_graph_capture_begin(mhlo_cuda_stream_t stream) {
+    if (stream == nullptr) return fail(MHLO_CUDA_INVALID_ARGUMENT, "graph_capture_begin: the default stream cannot be captured");
+    // a stream the caller is already recording (its own graph) is left alone: the launches simply join that recording
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    MHLO_CUDA_TRY(cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &status), MHLO_CUDA_UNSUPPORTED);
+    if (status != cudaStreamCaptureStatusNone) return fail(MHLO_CUDA_UNSUPPORTED, "graph_capture_begin: the stream is already being captured");
+    // thread-local mode: other threads of the process may keep allocating and synchronising while this one records
+    MHLO_CUDA_TRY(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal), MHLO_CUDA_UNSUPPORTED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_graph_capture_end(mhlo_cuda_stream_t stream, void** out_graph) {
+    if (!out_graph) return fail(MHLO_CUDA_INVALID_ARGUMENT, "graph_capture_end: null output");
+    *out_graph = nullptr;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph);
+    if (e != cudaSuccess || graph == nullptr) {
+        cudaGetLastError();  // the capture was invalidated by something that cannot be recorded
+        if (graph) cudaGraphDestroy(graph);
+        return fail(MHLO_CUDA_UNSUPPORTED, "graph_capture_end: %s", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        cudaGetLastError();
+        return fail(MHLO_CUDA_UNSUPPORTED, "graph_capture_end: instantiate: %s", cudaGetErrorString(ie));
+    }
+    *out_graph = exec;
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_graph_launch(void* graph, mhlo_cuda_stream_t stream) {
+    if (!graph) return fail(MHLO_CUDA_INVALID_ARGUMENT, "graph_launch: null graph");
+    MHLO_CUDA_TRY(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), static_cast<cudaStream_t>(stream)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_graph_destroy(void* graph) {
+    if (!graph) return MHLO_CUDA_OK;
+    MHLO_CUDA_TRY(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_ipc_export(const void* dev_ptr, unsigned char out_handle[64]) {
     if (!dev_ptr || !out_handle) return fail(MHLO_CUDA_INVALID_ARGUMENT, "ipc_export: null argument");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");

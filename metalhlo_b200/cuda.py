@@ -86,6 +86,10 @@ _PROTOTYPES = {
     "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
     "mhlo_cuda_add_layer_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_add_rms_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
+    "mhlo_cuda_graph_capture_begin": (C.c_int, [_vp]),
+    "mhlo_cuda_graph_capture_end": (C.c_int, [_vp, C.POINTER(_vp)]),
+    "mhlo_cuda_graph_launch": (C.c_int, [_vp, _vp]),
+    "mhlo_cuda_graph_destroy": (C.c_int, [_vp]),
     "mhlo_cuda_ipc_export": (C.c_int, [_vp, C.c_char_p]),
     "mhlo_cuda_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(_vp)]),
     "mhlo_cuda_ipc_close": (C.c_int, [_vp]),
