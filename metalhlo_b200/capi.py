@@ -216,7 +216,7 @@ class Buffer:
         self._h, self._client = handle, client
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # lib is None while the interpreter shuts down
             lib.mhlo_buffer_destroy(self._h)
             self._h = None
 
@@ -251,7 +251,7 @@ class Executable:
         self._h, self._client = handle, client
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.mhlo_executable_destroy(self._h)
             self._h = None
 
@@ -328,7 +328,7 @@ class Client:
         self._h = h.value
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.mhlo_client_destroy(self._h)
             self._h = None
 

@@ -71,6 +71,7 @@ struct GemmParams {
     int64_t ldc, c_col0;             // row pitch of C in elements; first column of this product inside the wider matrix
     void* copies[7];                 // further destinations of every tile store (the same matrix in peers' memory)
     int32_t n_copies;
+    int32_t c_tma;                   // C has a tensor map: the epilogue stores its staged boxes with bulk tensor copies
 };
 
 template <int BN, int STAGES>
@@ -102,7 +103,7 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
 template <int BN, int STAGES, int ACT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -119,6 +120,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&map_a);
         prefetch_tmap(&map_b);
+        if (p.c_tma) prefetch_tmap(&map_c);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
         fence_barrier_init();
@@ -298,11 +300,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
+                if (p.c_tma) {
+                    if (lane == 0) tma_store_wait_read();  // the previous chunk's bulk store has read the staging tile
+                }
                 __syncwarp();  // the previous chunk's read-back is finished
 #pragma unroll
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(stage_tile + lane * 128 + ((c ^ (lane & 7)) << 4)) = out16[c];
-                __syncwarp();
                 const int64_t cols_left = p.n - col0;  // columns of this chunk that exist
+                if (p.c_tma) {
+                    // the staging tile is exactly a 128-byte-swizzled box of 32 rows: one bulk tensor store writes it, clipped
+                    // at the edges of C by the hardware
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && cols_left > 0 && row0 < p.m) {
+                        const int b1 = static_cast<int>(bz % p.batch1), b0 = static_cast<int>(bz / p.batch1);
+                        tma_store_4d(&map_c, stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
+                __syncwarp();
                 if (cols_left <= 0) continue;
                 if (p.c_vec_ok && cols_left >= chunk_cols) {
                     // 8 lanes cover one row's 128 bytes, four rows per instruction
@@ -342,6 +359,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (p.c_tma && lane == 0) tma_store_wait_all();  // shared memory stays allocated until the last box has been read
     }
 
     tc_fence_before();
@@ -402,6 +420,37 @@ bool operand_map(CUtensorMap* map, const void* base, int64_t inner, int64_t oute
 }
 
 bool stride_ok(int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0; }
+
+// C [batch0, batch1, m, n] with row pitch ldc as a 4-D map {n, m, batch1, batch0}; one box = 128 bytes x 32 rows, the
+// staging tile of one epilogue warp.
+bool output_map(CUtensorMap* map, void* base, int out_dtype, int64_t n, int64_t m, int64_t ldc, int64_t b1, int64_t b0, std::string* why) {
+    const int64_t es = out_dtype == MHLO_DT_F32 ? 4 : 2;
+    cuuint64_t gdim[4] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(b1), static_cast<cuuint64_t>(b0)};
+    cuuint64_t gstr[3] = {static_cast<cuuint64_t>(ldc * es), static_cast<cuuint64_t>(m * ldc * es), static_cast<cuuint64_t>(b1 * m * ldc * es)};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), 32, 1, 1}, estr[4] = {1, 1, 1, 1};
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+            *why = "cuTensorMapEncodeTiled is not available from this driver";
+            return false;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUtensorMapDataType dt = out_dtype == MHLO_DT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (out_dtype == MHLO_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const CUresult r = encode(map, dt, 4, base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        *why = "cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string(static_cast<int>(r));
+        return false;
+    }
+    return true;
+}
 
 }  // namespace
 
@@ -464,6 +513,19 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         if (d < pr.n_copies) aligned = aligned && aligned16(pr.copies[d]);
     }
     p.c_vec_ok = aligned;
+    // Bulk tensor stores need 16-byte aligned rows and a 16-byte aligned base; copies in peers' memory keep plain stores.
+    CUtensorMap map_c;
+    memset(&map_c, 0, sizeof map_c);
+    p.c_tma = 0;
+    static const bool tma_store_enabled = [] {
+        const char* v = getenv("METALHLO_GEMM_TMA_STORE");
+        return v && v[0] == '1';  // opt-in
+    }();
+    if (tma_store_enabled && aligned && pr.n_copies == 0 && p.c_col0 == 0 && pr.m * p.ldc * static_cast<int64_t>(out_es) % 16 == 0) {
+        if (!output_map(&map_c, pr.c, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
+            return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for C: %s", why.c_str());
+        p.c_tma = 1;
+    }
 
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT>;
     static bool attr_set = false;
@@ -472,7 +534,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         attr_set = true;
     }
     const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
-    kernel<<<grid, kGemmThreads, L::kTotal, stream>>>(map_a, map_b, p);
+    kernel<<<grid, kGemmThreads, L::kTotal, stream>>>(map_a, map_b, map_c, p);
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
 }
