@@ -519,7 +519,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     p.c_tma = 0;
     static const bool tma_store_enabled = [] {
         const char* v = getenv("METALHLO_GEMM_TMA_STORE");
-        return v && v[0] == '1';  // opt-in
+        return !(v && v[0] == '0');  // METALHLO_GEMM_TMA_STORE=0 keeps the per-lane stores
     }();
     if (tma_store_enabled && aligned && pr.n_copies == 0 && p.c_col0 == 0 && pr.m * p.ldc * static_cast<int64_t>(out_es) % 16 == 0) {
         if (!output_map(&map_c, pr.c, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))

@@ -435,6 +435,48 @@ static void device_cases() {
         destroy_loaded(sm);
     }
 
+    // the module shape jax.jit prints: @main calls a private function from inside a counted loop. Three trips of
+    // x -> 2 * x + 1 take [1, 2, 3, 4] to [15, 23, 31, 39].
+    {
+        const std::string text =
+            "module @jit_f attributes {mhlo.num_partitions = 1 : i32, mhlo.num_replicas = 1 : i32} {\n"
+            "  func.func public @main(%arg0: tensor<4xf32>) -> (tensor<4xf32> {jax.result_info = \"\"}) {\n"
+            "    %c = stablehlo.constant dense<0> : tensor<i32>\n"
+            "    %0:2 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0) : tensor<i32>, tensor<4xf32>\n"
+            "     cond {\n"
+            "      %c_1 = stablehlo.constant dense<3> : tensor<i32>\n"
+            "      %1 = stablehlo.compare  LT, %iterArg, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>\n"
+            "      stablehlo.return %1 : tensor<i1>\n"
+            "    } do {\n"
+            "      %c_1 = stablehlo.constant dense<1> : tensor<i32>\n"
+            "      %1 = stablehlo.add %iterArg, %c_1 : tensor<i32>\n"
+            "      %2 = call @step(%iterArg_0) : (tensor<4xf32>) -> tensor<4xf32>\n"
+            "      stablehlo.return %1, %2 : tensor<i32>, tensor<4xf32>\n"
+            "    }\n"
+            "    return %0#1 : tensor<4xf32>\n"
+            "  }\n"
+            "  func.func private @step(%arg0: tensor<4xf32>) -> tensor<4xf32> {\n"
+            "    %cst = stablehlo.constant dense<2.000000e+00> : tensor<4xf32>\n"
+            "    %cst_0 = stablehlo.constant dense<1.000000e+00> : tensor<4xf32>\n"
+            "    %0 = stablehlo.multiply %arg0, %cst : tensor<4xf32>\n"
+            "    %1 = stablehlo.add %0, %cst_0 : tensor<4xf32>\n"
+            "    return %1 : tensor<4xf32>\n"
+            "  }\n"
+            "}\n";
+        PJRT_LoadedExecutable* loop = compile(c, text, &e);
+        const float in4[4] = {1.f, 2.f, 3.f, 4.f};
+        std::string e2;
+        PJRT_Buffer* xb = loop ? make_buffer(c, in4, PJRT_Buffer_Type_F32, {4}, nullptr, &e2) : nullptr;
+        std::vector<PJRT_Buffer*> outs(1, nullptr);
+        if (loop && xb) e = execute(loop, {xb}, &outs);
+        float got[4] = {};
+        if (e.empty() && outs[0]) e = read_buffer(outs[0], got, sizeof got);
+        report("execute_loop_with_call", loop && e.empty() && got[0] == 15.f && got[1] == 23.f && got[2] == 31.f && got[3] == 39.f, e + e2);
+        destroy_buffer(outs[0]);
+        destroy_buffer(xb);
+        destroy_loaded(loop);
+    }
+
     // compile errors surface as PJRT errors with the compiler's message
     {
         PJRT_LoadedExecutable* badexe = compile(c, "module { func.func @main() -> tensor<f32> { %0 = stablehlo.nonsense : tensor<f32> return %0 : tensor<f32> } }", &e);
