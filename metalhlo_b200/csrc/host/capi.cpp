@@ -39,7 +39,61 @@ struct Client {
     // in-process executable cache keyed by (text, level): MetalHLOCompiler.swift:730-782 keeps the same
     std::map<std::string, std::shared_ptr<Executable>> cache;
     int64_t cache_hits = 0, cache_misses = 0;
+    // Device memory of destroyed buffers, kept for the next buffer of the same size: a serving loop creates and destroys
+    // the same few shapes over and over, and cudaMalloc / cudaFree cost far more than the transfers they bracket are
+    // allowed to (the reference allocates and zero-fills per call, IntegratedExecutor.swift:170-215).
+    // Bounded by METALHLO_BUFFER_POOL_MB (default 8192, 0 = off); everything goes back to the driver with the client.
+    std::multimap<size_t, void*> pool;
+    size_t pooled_bytes = 0, pool_limit = 0;
 };
+
+size_t pool_limit_from_env() {
+    const char* v = std::getenv("METALHLO_BUFFER_POOL_MB");
+    const long long mb = v && *v ? std::atoll(v) : 8192;
+    return mb <= 0 ? 0 : static_cast<size_t>(mb) << 20;
+}
+
+// Takes exactly `bytes` from the pool or the driver. Pool memory was released only after its client's stream had
+// drained, so it is free of pending work.
+int pool_alloc(Client* c, size_t bytes, void** out) {
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        auto it = c->pool.find(bytes);
+        if (it != c->pool.end()) {
+            *out = it->second;
+            c->pooled_bytes -= bytes;
+            c->pool.erase(it);
+            return 0;
+        }
+    }
+    int st = mhlo_cuda_alloc(bytes, out);
+    if (st != 0) {
+        // out of memory with blocks parked in the pool: give them back and try once more
+        std::multimap<size_t, void*> drained;
+        {
+            std::lock_guard<std::mutex> lock(c->mu);
+            drained.swap(c->pool);
+            c->pooled_bytes = 0;
+        }
+        if (drained.empty()) return st;
+        for (auto& kv : drained) mhlo_cuda_free(kv.second);
+        st = mhlo_cuda_alloc(bytes, out);
+    }
+    return st;
+}
+
+void pool_release(Client* c, void* dev, size_t bytes) {
+    if (!dev) return;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        if (bytes >= (1u << 20) && c->pooled_bytes + bytes <= c->pool_limit) {  // small blocks are cheap to allocate afresh
+            c->pool.emplace(bytes, dev);
+            c->pooled_bytes += bytes;
+            return;
+        }
+    }
+    mhlo_cuda_free(dev);
+}
 
 struct ExecutableHandle {
     Client* client;
@@ -64,7 +118,7 @@ MHLOStatusCode make_buffer(Client* c, const TensorType& t, Buffer** out) {
     b->type = t;
     b->bytes = buffer_bytes(t);
     if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
-    if (b->bytes > 0 && mhlo_cuda_alloc(b->bytes, &b->dev) != 0)
+    if (b->bytes > 0 && pool_alloc(c, b->bytes, &b->dev) != 0)
         return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_BUFFER_FAILED, mhlo_cuda_last_error()));
     *out = b.release();
     return MHLO_OK;
@@ -99,7 +153,7 @@ MHLOStatusCode run(ExecutableHandle* h, const MHLOBufferRef* inputs, int32_t num
     if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
     std::vector<Buffer*> outs;
     std::vector<void*> out_ptrs;
-    auto cleanup = [&]() { for (Buffer* b : outs) { mhlo_cuda_free(b->dev); delete b; } };
+    auto cleanup = [&]() { for (Buffer* b : outs) { pool_release(b->client, b->dev, b->bytes); delete b; } };
     for (int i = 0; i < exe.num_outputs(); ++i) {
         Buffer* b = nullptr;
         MHLOStatusCode st = make_buffer(c, exe.output_type(i), &b);
@@ -213,6 +267,7 @@ MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) {
     if (mhlo_cuda_device_count(&n) != 0 || n == 0)
         return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, std::string("No CUDA device available: ") + mhlo_cuda_last_error()));
     std::unique_ptr<Client> c(new Client());
+    c->pool_limit = pool_limit_from_env();
     // one process drives one GPU: LOCAL_RANK picks it when several ranks share a box
     if (const char* lr = std::getenv("METALHLO_DEVICE")) c->device = std::atoi(lr);
     else if (const char* lr2 = std::getenv("LOCAL_RANK")) c->device = std::atoi(lr2) % n;
@@ -228,6 +283,8 @@ void mhlo_client_destroy(MHLOClientRef client) {
     if (!c) return;
     mhlo_cuda_device_set(c->device);
     c->cache.clear();
+    for (auto& kv : c->pool) mhlo_cuda_free(kv.second);
+    c->pool.clear();
     if (c->stream) mhlo_cuda_stream_destroy(c->stream);
     delete c;
 }
@@ -381,7 +438,7 @@ void mhlo_buffer_destroy(MHLOBufferRef buffer) {
     if (!b) return;
     mhlo_cuda_device_set(b->client->device);
     mhlo_cuda_stream_sync(b->client->stream);
-    mhlo_cuda_free(b->dev);
+    pool_release(b->client, b->dev, b->bytes);
     delete b;
 }
 
