@@ -335,8 +335,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.copies[d]) + batch_off + at) = val;
                         }
                     }
+                } else if (cols_left >= chunk_cols && p.n_copies == 0) {
+                    // Rows of C that do not start on 16-byte boundaries (a row pitch such as 50257 f16): every row's 128
+                    // bytes are still written mostly with 16-byte stores. With a = (address of the row's chunk) mod 16, the
+                    // aligned 16-byte pieces of global memory inside the chunk hold staged bytes [16 g - a, 16 g - a + 16):
+                    // 8 lanes per row fetch them as five 32-bit words from the staging tile and realign them with a funnel
+                    // shift; the (16 - a) head bytes and a tail bytes, 16 bytes together, go out one element per lane.
+                    const int edge_elems = 16 / static_cast<int>(out_es);
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), c = lane & 7;
+                        if (row0 + rr >= p.m) continue;
+                        uint8_t* dst = cbase + ((row0 + rr) * p.ldc + p.c_col0 + col0) * out_es;
+                        const int a = static_cast<int>(reinterpret_cast<uintptr_t>(dst) & 15);
+                        const uint8_t* srow = stage_tile + rr * 128;
+                        auto staged_word = [&](int wi) {  // 32-bit word wi of the row, through the tile's swizzle
+                            return *reinterpret_cast<const uint32_t*>(srow + ((((wi >> 2) ^ (rr & 7)) << 4) | ((wi & 3) << 2)));
+                        };
+                        const int g = a == 0 ? c : c + 1;  // aligned piece this lane writes (pieces 1..7 when a > 0)
+                        if (g <= 7) {
+                            const int byte0 = 16 * g - a;  // first staged byte of the piece, a multiple of 2
+                            const int w0 = byte0 >> 2;
+                            uint32_t w[5];
+#pragma unroll
+                            for (int q = 0; q < 5; ++q) w[q] = staged_word(min(w0 + q, 31));
+                            uint4 v;
+                            if (byte0 & 2) {
+                                v.x = __funnelshift_r(w[0], w[1], 16); v.y = __funnelshift_r(w[1], w[2], 16);
+                                v.z = __funnelshift_r(w[2], w[3], 16); v.w = __funnelshift_r(w[3], w[4], 16);
+                            } else {
+                                v = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                            *reinterpret_cast<uint4*>(dst + byte0) = v;
+                        }
+                        if (a != 0 && c < edge_elems) {
+                            const int head = (16 - a) / static_cast<int>(out_es);             // elements before the first aligned piece
+                            const int e = c < head ? c : 128 / static_cast<int>(out_es) - (edge_elems - head) + (c - head);
+                            if (out_es == 2) {
+                                const uint32_t word = staged_word(e >> 1);
+                                reinterpret_cast<uint16_t*>(dst)[e] = static_cast<uint16_t>((e & 1) ? word >> 16 : word & 0xffffu);
+                            } else {
+                                reinterpret_cast<uint32_t*>(dst)[e] = staged_word(e);
+                            }
+                        }
+                    }
                 } else {
-                    // ragged edge or a row pitch that is not 16-byte aligned: one row per instruction, 4 bytes per lane
+                    // ragged edge (or copies in peers' memory behind an unaligned pitch): one row per instruction, 4 bytes per lane
                     const int per_lane = out_es == 4 ? 1 : 2;  // elements in a lane's 4 bytes
                     for (int rr = 0; rr < 32 && row0 + rr < p.m; ++rr) {
                         const uint32_t word = *reinterpret_cast<const uint32_t*>(stage_tile + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
