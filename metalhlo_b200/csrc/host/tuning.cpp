@@ -416,12 +416,19 @@ TuningDatabase* TuningDatabase::open_global(const std::string& path) {
 std::vector<TuningConfig> row_kernel_candidates(int64_t hidden, int elem_bytes) {
     std::vector<TuningConfig> out;
     const int64_t per_vec = 16 / elem_bytes;
-    for (int threads : {64, 128, 256, 512, 1024})
+    const int64_t nvec = hidden / per_vec;
+    std::vector<int> thread_counts = {64, 128, 256, 512, 1024};
+    // CTAs of whole warps that cover the row exactly (no idle threads, no predicates)
+    for (int vecs : {1, 2, 4, 8})
+        if (nvec % (32LL * vecs) == 0 && nvec / vecs <= 1024) thread_counts.push_back(static_cast<int>(nvec / vecs));
+    std::sort(thread_counts.begin(), thread_counts.end());
+    thread_counts.erase(std::unique(thread_counts.begin(), thread_counts.end()), thread_counts.end());
+    for (int threads : thread_counts)
         for (int vecs : {1, 2, 4, 8}) {
             const int64_t cover = static_cast<int64_t>(threads) * vecs * per_vec;
             // a row must fit the registers of one CTA, and a CTA more than four times wider than the row wastes threads
             if (cover < hidden || cover >= hidden * 4) continue;
-            for (int ctas : {0, 2, 4, 8}) {
+            for (int ctas : {0, 2, 4, 8, 16}) {
                 if (ctas * threads > 2048) continue;
                 TuningConfig c;
                 c.threads = threads;
