@@ -335,6 +335,68 @@ int mhlo_cuda_dynamic_update_slice(void* operand_inout_dev, int32_t elem_size, c
                                    int32_t rank, const void* update_dev, const int64_t* update_shape,
                                    const void* const* index_devs, int32_t index_dtype, mhlo_cuda_stream_t stream);
 
+/* Window of stablehlo.reduce_window / select_and_scatter over a rank-`rank` operand. */
+typedef struct {
+    int32_t rank;
+    int64_t size[MHLO_CUDA_MAX_RANK];             /* window_dimensions */
+    int64_t stride[MHLO_CUDA_MAX_RANK];           /* window_strides */
+    int64_t base_dilation[MHLO_CUDA_MAX_RANK];
+    int64_t window_dilation[MHLO_CUDA_MAX_RANK];
+    int64_t pad_low[MHLO_CUDA_MAX_RANK];          /* may be negative; the high padding is implied by out_shape */
+} mhlo_cuda_window;
+
+/*
+ * stablehlo.reduce_window with the full attribute set: out[o] = op over the window positions w of
+ * padded(dilated(in))[o * stride + w * window_dilation], where positions that fall into the padding or between
+ * dilated elements hold the init value. `in` may be any strided view; out_dev is contiguous in in->dtype and
+ * init_dev is a device scalar of that dtype. op is one of MHLO_REDUCE_SUM/MAX/MIN/PROD/AND/OR/XOR; floats
+ * accumulate in fp32 (f64 in fp64), integers in int64, in row-major window order. The reference covers the 2-D
+ * NHWC pooling subset through MPSGraph pooling (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift:3056-3200).
+ */
+int mhlo_cuda_reduce_window(const mhlo_cuda_view* in, const mhlo_cuda_window* window, int32_t op, const void* init_dev,
+                            void* out_dev, const int64_t* out_shape, mhlo_cuda_stream_t stream);
+
+typedef struct {
+    int32_t n_update_window_dims, n_inserted_window_dims, n_input_batching, n_scatter_dims_to_operand;
+    int32_t update_window_dims[MHLO_CUDA_MAX_RANK];
+    int32_t inserted_window_dims[MHLO_CUDA_MAX_RANK];
+    int32_t input_batching_dims[MHLO_CUDA_MAX_RANK];
+    int32_t scatter_indices_batching_dims[MHLO_CUDA_MAX_RANK];
+    int32_t scatter_dims_to_operand_dims[MHLO_CUDA_MAX_RANK];
+    int32_t index_vector_dim;
+} mhlo_cuda_scatter_dims;
+
+enum { MHLO_SCATTER_SET = 0, MHLO_SCATTER_ADD, MHLO_SCATTER_MUL, MHLO_SCATTER_MAX, MHLO_SCATTER_MIN };
+
+/*
+ * stablehlo.scatter with the full dimension numbers, applied in place: result_inout_dev must already hold the
+ * operand (contiguous, `dtype`). Every element of `updates` (contiguous) is combined into the element it addresses
+ * with an atomic read-modify-write (mode = the update computation); updates whose target lies outside the operand
+ * are skipped. Colliding updates are applied in an unspecified order: SET keeps one of them, and floating-point ADD
+ * / MUL may differ from a sequential sum in the last bits. Modes match the reference's scatter modes
+ * (MPSGraphCompiler.swift:1639-1690).
+ */
+int mhlo_cuda_scatter(void* result_inout_dev, int32_t dtype, const int64_t* operand_shape, int32_t operand_rank,
+                      const void* indices_dev, int32_t index_dtype, const int64_t* indices_shape, int32_t indices_rank,
+                      const void* updates_dev, const int64_t* updates_shape, int32_t updates_rank,
+                      const mhlo_cuda_scatter_dims* dims, int32_t mode, mhlo_cuda_stream_t stream);
+
+/*
+ * stablehlo.sort along one dimension by the first operand, the other operands carried along (argsort passes an
+ * iota as the second operand). All n_operands tensors share `shape` (contiguous); operand i has dtypes[i] and is
+ * written sorted to outs_dev[i] (must not alias the inputs). Ascending or descending order of the key under the
+ * total order -NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN; the sort is always stable. Slices of up to
+ * MHLO_CUDA_SORT_SMEM_MAX keys are sorted in shared memory by one CTA each; longer ones use `scratch_dev`
+ * (mhlo_cuda_sort_scratch_bytes() bytes) for a bitonic network over global memory. Replaces argSort +
+ * gatherAlongAxis (MPSGraphCompiler.swift:3599-3613).
+ */
+#define MHLO_CUDA_SORT_SMEM_MAX 8192
+#define MHLO_CUDA_SORT_MAX_OPERANDS 8
+int64_t mhlo_cuda_sort_scratch_bytes(const int64_t* shape, int32_t rank, int32_t dimension);
+int mhlo_cuda_sort(const void* const* operands_dev, void* const* outs_dev, const int32_t* dtypes, int32_t n_operands,
+                   const int64_t* shape, int32_t rank, int32_t dimension, int32_t descending, void* scratch_dev,
+                   int64_t scratch_bytes, mhlo_cuda_stream_t stream);
+
 /*
  * C[b0,b1,m,n] = sum_k A(b0,b1,m,k) * B(b0,b1,k,n) for arbitrary element strides (a_strides / b_strides =
  * {batch0, batch1, row, col} strides in elements; C is contiguous). Any dtype: floats accumulate in fp32

@@ -43,7 +43,9 @@ bool inline_calls(Module& m);
 // Unrolls stablehlo.while loops whose trip count is static: a counter compared with a constant in the condition,
 // advanced by a constant in the body, starting from a constant. Other loops are left in place.
 bool unroll_static_whiles(Function& f);
-// Both, repeated until neither applies; returns the flattened @main.
+// Replaces stablehlo.if / stablehlo.case by their branches, all computed, and `select`s on the selector.
+bool flatten_conditionals(Function& f);
+// All three, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
 
 // ---- memory plan -----------------------------------------------------------------------------------------------

@@ -426,7 +426,27 @@ class Lowering {
         const TensorType& rt = op.result_types[0];
         if (param_converts_ && is_parameter_convert(op)) return lower_parameter_convert(op);
         if (n == "constant") return lower_constant(op);
-        if (n == "reshape" || n == "bitcast") return lower_reshape(op);
+        if (n == "reshape" || n == "bitcast" || n == "dynamic_reshape") return lower_reshape(op);
+        if (n == "bitcast_convert") return lower_bitcast_convert(op);
+        if (n == "dynamic_pad") {  // the padding amounts are operands; they must be constants of the module
+            if (op.operands.size() != 5) fail_compile("dynamic_pad takes five operands");
+            Op p = op;
+            p.name = "pad";
+            p.operands.resize(2);
+            p.attrs["edge_padding_low"] = Attr::make_ints(constant_ints(op.operands[2], "dynamic_pad: edge_padding_low"));
+            p.attrs["edge_padding_high"] = Attr::make_ints(constant_ints(op.operands[3], "dynamic_pad: edge_padding_high"));
+            p.attrs["interior_padding"] = Attr::make_ints(constant_ints(op.operands[4], "dynamic_pad: interior_padding"));
+            return lower_pad(p);
+        }
+        if (n == "dynamic_gather") {
+            if (op.operands.size() != 3) fail_compile("dynamic_gather takes three operands");
+            Op g = op;
+            g.name = "gather";
+            g.operands.resize(2);
+            g.attrs["slice_sizes"] = Attr::make_ints(constant_ints(op.operands[2], "dynamic_gather: slice_sizes"));
+            return lower_gather(g);
+        }
+        if (n == "batch_norm_inference") return lower_batch_norm_inference(op);
         if (n == "transpose") {
             const View& x = get(op.operands[0]);
             std::vector<int64_t> perm = op.int_list("permutation");
@@ -436,7 +456,7 @@ class Lowering {
             for (size_t d = 0; d < perm.size(); ++d) o.strides[d] = x.strides[perm[d]];
             return set(op.results[0], o);
         }
-        if (n == "broadcast_in_dim") {
+        if (n == "broadcast_in_dim" || n == "dynamic_broadcast_in_dim") {  // the dynamic form's result type is static here
             const View& x = get(op.operands[0]);
             std::vector<int64_t> dims = op.int_list("broadcast_dimensions");
             if (static_cast<int>(dims.size()) != x.type.rank()) fail_compile("broadcast_in_dim: dims rank mismatch");
@@ -474,7 +494,7 @@ class Lowering {
             }
             return set(op.results[0], o);
         }
-        if (n == "iota") {
+        if (n == "iota" || n == "dynamic_iota") {
             std::vector<mhlo_cuda_ew_inst> prog = {{MHLO_EW_IOTA, 0, 0, 0, static_cast<double>(op.int_attr("iota_dimension", 0))}};
             return set(op.results[0], emit_elementwise({}, prog, rt, "iota"));
         }
@@ -491,11 +511,14 @@ class Lowering {
         if (n == "reduce") return lower_reduce(op);
         if (n == "dot_general" || n == "dot") return lower_dot(op);
         if (n == "gather") return lower_gather(op);
+        if (n == "reduce_window") return lower_reduce_window(op);
+        if (n == "scatter") return lower_scatter(op);
+        if (n == "sort") return lower_sort(op);
         if (n == "dynamic_slice") return lower_dynamic_slice(op);
         if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
         if (n == "custom_call") return lower_custom_call(op);
-        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "sort" ||
-            n == "convolution" || n == "fft" || n == "scatter" || n == "reduce_window" || n == "select_and_scatter" ||
+        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" ||
+            n == "convolution" || n == "fft" || n == "select_and_scatter" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         const int code = ew_opcode(n);
@@ -545,6 +568,83 @@ class Lowering {
         o.type = rt;
         o.strides = dense_strides(rt.shape);
         set(op.results[0], o);
+    }
+
+    // stablehlo.bitcast_convert: the same bits under another element type. Equal element sizes re-type the view; a
+    // narrower result gains a minor dimension of (old size / new size), a wider one loses it.
+    void lower_bitcast_convert(const Op& op) {
+        const View& x = get(op.operands[0]);
+        const TensorType& rt = op.result_types[0];
+        const int64_t from = static_cast<int64_t>(dtype_size(x.type.dtype)), to = static_cast<int64_t>(dtype_size(rt.dtype));
+        if (x.type.dtype == DType::I1 || rt.dtype == DType::I1) fail_unsupported("bitcast_convert of i1");
+        if (from == to) {
+            if (x.type.shape != rt.shape) fail_compile("bitcast_convert: " + x.type.str() + " -> " + rt.str());
+            View o = x;
+            o.type = rt;
+            return set(op.results[0], o);
+        }
+        if (x.type.bytes() != rt.bytes()) fail_compile("bitcast_convert: " + x.type.str() + " -> " + rt.str());
+        View m = materialize(x, "bitcast_convert");
+        if ((m.offset * from) % to != 0) fail_unsupported("bitcast_convert of a misaligned view");
+        View o = m;
+        o.type = rt;
+        o.offset = m.offset * from / to;
+        o.strides = dense_strides(rt.shape);
+        set(op.results[0], o);
+    }
+
+    // Integer payload of a value that the module defines as a constant.
+    std::vector<int64_t> constant_ints(int value, const std::string& what) {
+        const View& v = get(value);
+        const Buffer& b = buffers_[v.buf];
+        if (b.kind != Buffer::Const || is_float(v.type.dtype)) fail_unsupported(what + " must be an integer constant");
+        const size_t es = dtype_size(v.type.dtype);
+        std::vector<int64_t> out;
+        const int64_t n = v.type.count();
+        if (v.type.rank() > 1) fail_unsupported(what + " must be a vector");
+        const int64_t stride = v.type.rank() == 1 ? v.strides[0] : 0;
+        for (int64_t i = 0; i < n; ++i) {
+            const uint8_t* p = exe_->const_pool_.data() + b.offset + (v.offset + i * stride) * static_cast<int64_t>(es);
+            uint64_t raw = 0;
+            for (size_t k = 0; k < es; ++k) raw |= static_cast<uint64_t>(p[k]) << (8 * k);
+            if (!is_unsigned(v.type.dtype) && es < 8 && (raw >> (8 * es - 1)) & 1) raw |= ~0ull << (8 * es);
+            out.push_back(static_cast<int64_t>(raw));
+        }
+        return out;
+    }
+
+    // stablehlo.batch_norm_inference: (x - mean) * rsqrt(variance + epsilon) * scale + offset with the four statistics
+    // broadcast along feature_index; one elementwise launch.
+    void lower_batch_norm_inference(const Op& op) {
+        if (op.operands.size() != 5) fail_compile("batch_norm_inference takes five operands");
+        const TensorType& rt = op.result_types[0];
+        const View& x = get(op.operands[0]);
+        const int64_t axis = op.int_attr("feature_index", 0);
+        if (axis < 0 || axis >= rt.rank()) fail_compile("batch_norm_inference: feature_index out of range");
+        const Attr* ea = op.attr("epsilon");
+        const double eps = ea ? ea->as_float() : 0.0;
+        std::vector<View> ins = {x};
+        for (int i = 1; i < 5; ++i) {  // scale, offset, mean, variance: [C] viewed as [1, .., C, .., 1]
+            const View& s = get(op.operands[static_cast<size_t>(i)]);
+            if (s.type.rank() != 1 || s.type.shape[0] != rt.shape[static_cast<size_t>(axis)])
+                fail_compile("batch_norm_inference: statistics must have the feature dimension's length");
+            View b = s;
+            b.type.shape = rt.shape;
+            b.strides.assign(rt.shape.size(), 0);
+            b.strides[static_cast<size_t>(axis)] = s.strides[0];
+            ins.push_back(b);
+        }
+        // registers: inputs 0..4 (x, scale, offset, mean, variance), the result of instruction i at 5 + i
+        std::vector<mhlo_cuda_ew_inst> prog = {
+            {MHLO_EW_SUB, 0, 3, 0, 0.0},    // r5 = x - mean
+            {MHLO_EW_IMM, 0, 0, 0, eps},    // r6 = epsilon
+            {MHLO_EW_ADD, 4, 6, 0, 0.0},    // r7 = variance + epsilon
+            {MHLO_EW_RSQRT, 7, 0, 0, 0.0},  // r8
+            {MHLO_EW_MUL, 5, 8, 0, 0.0},    // r9
+            {MHLO_EW_MUL, 9, 1, 0, 0.0},    // r10 = .. * scale
+            {MHLO_EW_ADD, 10, 2, 0, 0.0},   // r11 = .. + offset
+        };
+        set(op.results[0], emit_elementwise(ins, prog, rt, "batch_norm_inference"));
     }
 
     void lower_concatenate(const Op& op) {
@@ -765,6 +865,144 @@ class Lowering {
         View out = dense_view(new_arena(p.type.bytes()), p.type);
         copy_view(p, out, "copy(" + why + ")");
         return out;
+    }
+
+    // stablehlo.reduce_window of one operand with a recognised reducer; the operand is read through its view.
+    void lower_reduce_window(const Op& op) {
+        if (op.operands.size() != 2) fail_unsupported("variadic reduce_window");
+        static const std::map<std::string, int> kinds = {{"add", MHLO_REDUCE_SUM}, {"maximum", MHLO_REDUCE_MAX}, {"minimum", MHLO_REDUCE_MIN},
+                                                         {"multiply", MHLO_REDUCE_PROD}, {"and", MHLO_REDUCE_AND}, {"or", MHLO_REDUCE_OR},
+                                                         {"xor", MHLO_REDUCE_XOR}};
+        auto it = kinds.find(op.str_attr("reducer"));
+        if (it == kinds.end()) fail_unsupported("reduce_window with a reducer body this backend does not recognise (" + op.str_attr("reducer") + ")");
+        const int kind = it->second;
+        const View& x = get(op.operands[0]);
+        View init = materialize(get(op.operands[1]), "reduce_window.init");
+        const TensorType& rt = op.result_types[0];
+        const int rank = x.type.rank();
+        if (rank > MHLO_CUDA_MAX_RANK) fail_unsupported("tensor rank above 8: " + x.type.str());
+        mhlo_cuda_window w;
+        std::memset(&w, 0, sizeof w);
+        w.rank = rank;
+        auto fill = [&](const char* key, int64_t* dst, int64_t dflt) {
+            std::vector<int64_t> v = op.int_list(key);
+            if (!v.empty() && static_cast<int>(v.size()) != rank) fail_compile(std::string("reduce_window: ") + key + " does not match the operand's rank");
+            for (int d = 0; d < rank; ++d) dst[d] = v.empty() ? dflt : v[static_cast<size_t>(d)];
+        };
+        fill("window_dimensions", w.size, 1);
+        fill("window_strides", w.stride, 1);
+        fill("base_dilations", w.base_dilation, 1);
+        fill("window_dilations", w.window_dilation, 1);
+        std::vector<int64_t> pad = op.int_list("padding");  // [rank][2], row-major
+        if (!pad.empty() && static_cast<int>(pad.size()) != 2 * rank) fail_compile("reduce_window: padding must be rank x 2");
+        for (int d = 0; d < rank; ++d) w.pad_low[d] = pad.empty() ? 0 : pad[static_cast<size_t>(2 * d)];
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView dx = dev(x), di = dev(init), dout = dev(out);
+        keep_alive(x); keep_alive(init); keep_alive(out);
+        const std::vector<int64_t> oshape = rt.shape;
+        add_step("reduce_window", [=](const Ctx& c) {
+            mhlo_cuda_view xv = bind(dx, c);
+            return mhlo_cuda_reduce_window(&xv, &w, kind, bind(di, c).base, const_cast<void*>(bind(dout, c).base), oshape.data(), c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.scatter of one operand: the operand is copied into the result, then the updates are combined in place.
+    void lower_scatter(const Op& op) {
+        if (op.operands.size() != 3) fail_unsupported("variadic scatter");
+        static const std::map<std::string, int> modes = {{"set", MHLO_SCATTER_SET}, {"add", MHLO_SCATTER_ADD}, {"multiply", MHLO_SCATTER_MUL},
+                                                         {"maximum", MHLO_SCATTER_MAX}, {"minimum", MHLO_SCATTER_MIN}};
+        auto it = modes.find(op.str_attr("reducer"));
+        if (it == modes.end()) fail_unsupported("scatter with an update computation this backend does not recognise (" + op.str_attr("reducer") + ")");
+        const int mode = it->second;
+        const TensorType& rt = op.result_types[0];
+        View indices = materialize(get(op.operands[1]), "scatter.indices");
+        View updates = materialize(get(op.operands[2]), "scatter.updates");
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        copy_view(get(op.operands[0]), out, "scatter.operand");
+        mhlo_cuda_scatter_dims g;
+        std::memset(&g, 0, sizeof g);
+        auto fill = [&](const char* key, int32_t* dst, int32_t* count) {
+            std::vector<int64_t> v = op.int_list(key);
+            if (v.size() > MHLO_CUDA_MAX_RANK) fail_unsupported(std::string("scatter: ") + key + " longer than 8");
+            for (size_t i = 0; i < v.size(); ++i) dst[i] = static_cast<int32_t>(v[i]);
+            if (count) *count = static_cast<int32_t>(v.size());
+        };
+        fill("update_window_dims", g.update_window_dims, &g.n_update_window_dims);
+        fill("inserted_window_dims", g.inserted_window_dims, &g.n_inserted_window_dims);
+        fill("input_batching_dims", g.input_batching_dims, &g.n_input_batching);
+        fill("scatter_indices_batching_dims", g.scatter_indices_batching_dims, nullptr);
+        fill("scatter_dims_to_operand_dims", g.scatter_dims_to_operand_dims, &g.n_scatter_dims_to_operand);
+        g.index_vector_dim = static_cast<int32_t>(op.int_attr("index_vector_dim", indices.type.rank()));
+        DevView din = dev(indices), dup = dev(updates), dout = dev(out);
+        keep_alive(indices); keep_alive(updates); keep_alive(out);
+        const TensorType ot = rt, it_ = indices.type, ut = updates.type;
+        add_step("scatter", [=](const Ctx& c) {
+            return mhlo_cuda_scatter(const_cast<void*>(bind(dout, c).base), static_cast<int>(ot.dtype), ot.shape.data(), ot.rank(), bind(din, c).base,
+                                     static_cast<int>(it_.dtype), it_.shape.data(), it_.rank(), bind(dup, c).base, ut.shape.data(), ut.rank(), &g,
+                                     mode, c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.sort: every operand permuted by the order of the first one along `dimension`.
+    void lower_sort(const Op& op) {
+        const size_t n = op.operands.size();
+        if (n < 1 || n > MHLO_CUDA_SORT_MAX_OPERANDS || op.results.size() != n) fail_unsupported("sort of " + std::to_string(n) + " operands");
+        const std::string order = op.str_attr("sort_order");
+        if (order != "ascending" && order != "descending")
+            fail_unsupported("sort with a comparator other than one LT / GT compare of the first operand");
+        std::vector<View> ins, outs;
+        for (size_t j = 0; j < n; ++j) {
+            ins.push_back(materialize(get(op.operands[j]), "sort.operand"));
+            if (ins[j].type.shape != ins[0].type.shape) fail_compile("sort: operands of different shapes");
+            outs.push_back(dense_view(new_arena(op.result_types[j].bytes()), op.result_types[j]));
+        }
+        const TensorType kt = ins[0].type;
+        int64_t dim = op.int_attr("dimension", -1);
+        if (dim < 0) dim += kt.rank();
+        if (kt.rank() < 1 || dim < 0 || dim >= kt.rank()) fail_compile("sort: dimension out of range");
+        const int64_t scratch_bytes = mhlo_cuda_sort_scratch_bytes(kt.shape.data(), kt.rank(), static_cast<int32_t>(dim));
+        if (scratch_bytes < 0) fail_compile("sort: bad shape");
+        View scratch;
+        const bool has_scratch = scratch_bytes > 0;
+        if (has_scratch) {
+            TensorType st;
+            st.dtype = DType::UI8;
+            st.shape = {scratch_bytes};
+            scratch = dense_view(new_arena(scratch_bytes), st);
+        }
+        std::vector<DevView> din, dout;
+        std::vector<int32_t> dts;
+        for (size_t j = 0; j < n; ++j) {
+            din.push_back(dev(ins[j]));
+            dout.push_back(dev(outs[j]));
+            dts.push_back(static_cast<int32_t>(ins[j].type.dtype));
+            keep_alive(ins[j]);
+            keep_alive(outs[j]);
+        }
+        DevView dscratch;
+        if (has_scratch) { dscratch = dev(scratch); keep_alive(scratch); }
+        const int descending = order == "descending" ? 1 : 0;
+        int launches = 1;
+        if (has_scratch) {  // keys, chunk sort, then per merge size its global stages and one chunk merge, apply
+            int64_t padded = 1;
+            while (padded < kt.shape[static_cast<size_t>(dim)]) padded <<= 1;
+            launches = 3;
+            for (int64_t k = 2 * MHLO_CUDA_SORT_SMEM_MAX; k <= padded; k <<= 1) {
+                for (int64_t j = k >> 1; j >= MHLO_CUDA_SORT_SMEM_MAX; j >>= 1) ++launches;
+                ++launches;
+            }
+        }
+        add_step("sort", [=](const Ctx& c) {
+            const void* in[MHLO_CUDA_SORT_MAX_OPERANDS];
+            void* out[MHLO_CUDA_SORT_MAX_OPERANDS];
+            for (size_t j = 0; j < din.size(); ++j) { in[j] = bind(din[j], c).base; out[j] = const_cast<void*>(bind(dout[j], c).base); }
+            void* sc = has_scratch ? const_cast<void*>(bind(dscratch, c).base) : nullptr;
+            return mhlo_cuda_sort(in, out, dts.data(), static_cast<int32_t>(din.size()), kt.shape.data(), kt.rank(), static_cast<int32_t>(dim),
+                                  descending, sc, scratch_bytes, c.stream);
+        }, launches);
+        for (size_t j = 0; j < n; ++j) set(op.results[j], outs[j]);
     }
 
     void lower_gather(const Op& op) {

@@ -2,7 +2,10 @@
 // `stablehlo.while` loops with a static trip count (what lax.fori_loop emits) are unrolled, so that the straight-line
 // executor can run them. The reference does both on the module text before compiling
 // (Sources/PJRTMetalHLO/PJRTExecutable.swift:458-1657: inlineSimpleCallWrapper, inlineCallsInBody,
-// unrollStaticWhileLoops, iterated until nothing changes); here they work on the parsed IR.
+// unrollStaticWhileLoops, iterated until nothing changes); here they work on the parsed IR. `stablehlo.if` and
+// `stablehlo.case` become straight-line code too: every branch is computed and the results are picked with `select`,
+// which is exact because StableHLO ops have no side effects (the reference runs them through MPSGraph's if/else,
+// Sources/MetalHLOCore/MPSGraph/MPSGraphCompiler.swift, with the same results).
 #include <map>
 
 #include "compiler.h"
@@ -250,12 +253,112 @@ bool unroll_static_whiles(Function& f) {
     return changed;
 }
 
+namespace {
+
+Op scalar_constant(Function& f, DType dt, int64_t value) {
+    Op k;
+    k.name = "constant";
+    k.dialect = "stablehlo";
+    TensorType t;
+    t.dtype = dt;
+    Attr a;
+    a.kind = Attr::Dense;
+    a.dense_type = t;
+    a.splat = true;
+    const size_t es = dtype_size(dt);
+    a.dense.assign(es, 0);
+    for (size_t b = 0; b < es && b < 8; ++b) a.dense[b] = static_cast<uint8_t>(static_cast<uint64_t>(value) >> (8 * b));
+    k.attrs["value"] = a;
+    k.result_types = {t};
+    k.results = {f.new_value(t, "")};
+    return k;
+}
+
+Op simple_op(Function& f, const std::string& name, std::vector<int> operands, const TensorType& rt) {
+    Op o;
+    o.name = name;
+    o.dialect = "stablehlo";
+    o.operands = std::move(operands);
+    o.result_types = {rt};
+    o.results = {f.new_value(rt, "")};
+    return o;
+}
+
+}  // namespace
+
+bool flatten_conditionals(Function& f) {
+    bool changed = false;
+    for (int round = 0; round < kMaxInlineRounds; ++round) {  // a branch may hold further conditionals
+        bool any = false;
+        std::vector<Op> out;
+        std::map<int, int> alias;
+        for (Op& op : f.ops) {
+            apply_alias(op, alias);
+            if (op.dead || (op.name != "if" && op.name != "case")) {
+                out.push_back(std::move(op));
+                continue;
+            }
+            const bool is_if = op.name == "if";
+            if (op.operands.size() != 1 || op.regions.empty() || (is_if && op.regions.size() != 2))
+                fail_compile("stablehlo." + op.name + " with " + std::to_string(op.operands.size()) + " operands and " +
+                             std::to_string(op.regions.size()) + " branches");
+            const TensorType st = f.type_of(op.operands[0]);  // a copy: new values reallocate the table
+            if (st.count() != 1) fail_compile("stablehlo." + op.name + ": the selector must be a scalar, got " + st.str());
+            std::vector<std::vector<int>> branch_results;
+            for (const auto& r : op.regions) {
+                Cloner c{f, f, true, {}};
+                std::vector<int> res;
+                bool returned = false;
+                for (const Op& bo : r->ops) {
+                    if (bo.name == "return") {
+                        for (int v : bo.operands) res.push_back(c.remap(v));
+                        returned = true;
+                        break;
+                    }
+                    out.push_back(c.clone(bo));
+                }
+                if (!returned || res.size() != op.results.size())
+                    fail_compile("stablehlo." + op.name + ": a branch returns " + std::to_string(res.size()) + " values for " +
+                                 std::to_string(op.results.size()) + " results");
+                branch_results.push_back(res);
+            }
+            TensorType pred_t;
+            pred_t.dtype = DType::I1;
+            std::vector<int> current = branch_results.back();  // `if`: the false branch; `case`: the default branch
+            for (int b = static_cast<int>(branch_results.size()) - 2; b >= 0; --b) {
+                int pred = op.operands[0];
+                if (!is_if) {
+                    Op k = scalar_constant(f, st.dtype, b);
+                    Op eq = simple_op(f, "compare", {op.operands[0], k.results[0]}, pred_t);
+                    eq.attrs["comparison_direction"] = Attr::make_string("EQ");
+                    pred = eq.results[0];
+                    out.push_back(k);
+                    out.push_back(eq);
+                }
+                for (size_t r = 0; r < current.size(); ++r) {
+                    Op sel = simple_op(f, "select", {pred, branch_results[static_cast<size_t>(b)][r], current[r]}, op.result_types[r]);
+                    current[r] = sel.results[0];
+                    out.push_back(sel);
+                }
+            }
+            for (size_t r = 0; r < op.results.size(); ++r) alias[op.results[r]] = current[r];
+            any = true;
+        }
+        f.ops.swap(out);
+        f.compact();
+        if (!any) break;
+        changed = true;
+    }
+    return changed;
+}
+
 Function flatten_main(Module& m) {
-    // calls and loops can hide each other (a loop body that calls, a callee that loops): repeat until neither changes
+    // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat until neither changes
     for (int round = 0; round < kMaxInlineRounds; ++round) {
         const bool a = inline_calls(m);
         const bool b = unroll_static_whiles(m.main());
-        if (!a && !b) break;
+        const bool c = flatten_conditionals(m.main());
+        if (!a && !b && !c) break;
     }
     return m.main();
 }

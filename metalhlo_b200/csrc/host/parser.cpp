@@ -48,6 +48,18 @@ std::vector<int64_t> Attr::as_ints() const {
     std::vector<int64_t> out;
     if (kind == Array)
         for (const Attr& e : elems) out.push_back(e.kind == Float ? static_cast<int64_t>(e.f) : e.i);
+    if (kind == Dense && !is_float(dense_type.dtype)) {  // dense<[[0, 0], [1, 1]]> : tensor<2x2xi64>, row-major
+        const size_t es = dtype_size(dense_type.dtype);
+        const int64_t n = dense_type.count();
+        for (int64_t k = 0; k < n && es > 0 && es <= 8; ++k) {
+            const size_t at = splat ? 0 : static_cast<size_t>(k) * es;
+            if (at + es > dense.size()) break;
+            uint64_t raw = 0;
+            for (size_t b = 0; b < es; ++b) raw |= static_cast<uint64_t>(dense[at + b]) << (8 * b);
+            if (!is_unsigned(dense_type.dtype) && es < 8 && (raw >> (8 * es - 1)) & 1) raw |= ~0ull << (8 * es);
+            out.push_back(static_cast<int64_t>(raw));
+        }
+    }
     return out;
 }
 
@@ -1106,6 +1118,32 @@ class Parser {
             const char* key = n == "gather" ? "dimension_numbers" : "scatter_dimension_numbers";
             if (const Attr* d = op->attr(key))
                 for (const auto& kv : d->dict) op->attrs[kv.first] = kv.second.kind == Attr::Int || kv.second.kind == Attr::IntArray || kv.second.kind == Attr::Array ? (kv.second.kind == Attr::Int ? kv.second : Attr::make_ints(kv.second.as_ints())) : kv.second;
+        }
+        if (n == "reduce_window" && !op->attr("reducer") && !op->regions.empty())
+            op->attrs["reducer"] = Attr::make_string(classify_reducer(*op->regions[0]));
+        if (n == "scatter" && !op->attr("reducer") && !op->regions.empty()) {
+            // the update computation takes (current, update): returning the update itself is an assignment
+            const Region& r = *op->regions[0];
+            if (r.ops.size() == 1 && r.ops[0].name == "return" && r.args.size() == 2 && r.ops[0].operands.size() == 1 &&
+                r.ops[0].operands[0] == r.args[1])
+                op->attrs["reducer"] = Attr::make_string("set");
+            else
+                op->attrs["reducer"] = Attr::make_string(r.ops.size() == 2 ? classify_reducer(r) : "unknown");
+        }
+        if (n == "sort" && !op->regions.empty()) {
+            // comparator(lhs0, rhs0, lhs1, rhs1, ..): one strict compare of the first operand's pair gives the order
+            const Region& r = *op->regions[0];
+            std::string order = "unknown";
+            if (r.ops.size() == 2 && r.ops[0].name == "compare" && r.ops[1].name == "return" && r.args.size() >= 2 &&
+                r.ops[1].operands.size() == 1 && r.ops[1].operands[0] == r.ops[0].results[0]) {
+                const Op& c = r.ops[0];
+                std::string dir = c.str_attr("comparison_direction");
+                const bool straight = c.operands[0] == r.args[0] && c.operands[1] == r.args[1];
+                const bool swapped = c.operands[0] == r.args[1] && c.operands[1] == r.args[0];
+                if ((dir == "LT" || dir == "GT") && (straight || swapped))
+                    order = ((dir == "LT") == straight) ? "ascending" : "descending";
+            }
+            op->attrs["sort_order"] = Attr::make_string(order);
         }
         if (n == "dynamic_slice") { rename("sizes", "slice_sizes"); }
         if (n == "pad") { rename("low", "edge_padding_low"); rename("high", "edge_padding_high"); rename("interior", "interior_padding"); }

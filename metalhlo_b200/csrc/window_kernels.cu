@@ -1,0 +1,606 @@
+// Operators either side of the fused hot path that need kernels of their own: reduce_window (pooling, windowed
+// sums), scatter (indexed updates with atomics) and sort (bitonic networks in shared and global memory).
+// HBM / L2-bound integer and byte work: one thread per output element (reduce_window, scatter) or one CTA per
+// sorted slice, grids sized in multiples of the SM count.
+#include <cstring>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace mhlo {
+namespace {
+
+int grid_of(int64_t n, int threads) {
+    const int64_t blocks = (n + threads - 1) / threads;
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 16;
+    return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+// Element type tags -> storage and accumulator types.
+template <typename E> struct AccOf { using type = int64_t; };
+template <> struct AccOf<float> { using type = float; };
+template <> struct AccOf<__half> { using type = float; };
+template <> struct AccOf<__nv_bfloat16> { using type = float; };
+template <> struct AccOf<double> { using type = double; };
+template <> struct AccOf<uint64_t> { using type = uint64_t; };
+
+template <typename E> __device__ __forceinline__ typename AccOf<E>::type widen(E v) { return static_cast<typename AccOf<E>::type>(v); }
+template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename E> __device__ __forceinline__ E narrow(typename AccOf<E>::type v) { return static_cast<E>(v); }
+template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename A>
+__device__ __forceinline__ A combine(int op, A a, A b) {
+    switch (op) {
+        case MHLO_REDUCE_SUM: return a + b;
+        case MHLO_REDUCE_PROD: return a * b;
+        case MHLO_REDUCE_MAX:
+            if constexpr (std::is_floating_point<A>::value) return (a != a || b != b) ? A(NAN) : (a > b ? a : b);
+            else return a > b ? a : b;
+        case MHLO_REDUCE_MIN:
+            if constexpr (std::is_floating_point<A>::value) return (a != a || b != b) ? A(NAN) : (a < b ? a : b);
+            else return a < b ? a : b;
+        default:
+            if constexpr (std::is_floating_point<A>::value) {
+                const bool x = a != A(0), y = b != A(0);
+                return A(op == MHLO_REDUCE_AND ? (x && y) : op == MHLO_REDUCE_OR ? (x || y) : (x != y));
+            } else {
+                return op == MHLO_REDUCE_AND ? (a & b) : op == MHLO_REDUCE_OR ? (a | b) : (a ^ b);
+            }
+    }
+}
+
+// Calls f(tag) with a value of the storage type of `dtype`; false for an unknown dtype. I1 is stored as a byte.
+template <typename F>
+bool with_element_type(int dtype, F&& f) {
+    switch (dtype) {
+        case MHLO_DT_F32: f(float{}); return true;
+        case MHLO_DT_F16: f(__half{}); return true;
+        case MHLO_DT_BF16: f(__nv_bfloat16{}); return true;
+        case MHLO_DT_F64: f(double{}); return true;
+        case MHLO_DT_I1: case MHLO_DT_UI8: f(uint8_t{}); return true;
+        case MHLO_DT_I8: f(int8_t{}); return true;
+        case MHLO_DT_I16: f(int16_t{}); return true;
+        case MHLO_DT_UI16: f(uint16_t{}); return true;
+        case MHLO_DT_I32: f(int32_t{}); return true;
+        case MHLO_DT_UI32: f(uint32_t{}); return true;
+        case MHLO_DT_I64: f(int64_t{}); return true;
+        case MHLO_DT_UI64: f(uint64_t{}); return true;
+        default: return false;
+    }
+}
+
+int dtype_bytes(int dtype) {
+    int n = 0;
+    with_element_type(dtype, [&](auto tag) { n = static_cast<int>(sizeof(tag)); });
+    return n;
+}
+
+// ---- reduce_window ---------------------------------------------------------------------------------------------------
+
+struct WindowParams {
+    mhlo_cuda_window w;
+    int64_t in_shape[MHLO_CUDA_MAX_RANK], in_stride[MHLO_CUDA_MAX_RANK], out_shape[MHLO_CUDA_MAX_RANK];
+    const void* in;
+    const void* init;
+    void* out;
+    int64_t n_out, window_count;
+    int32_t op;
+};
+
+template <typename E>
+__global__ void __launch_bounds__(256) reduce_window_kernel(const __grid_constant__ WindowParams p) {
+    using A = typename AccOf<E>::type;
+    const int rank = p.w.rank;
+    const A init = widen<E>(*static_cast<const E*>(p.init));
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < p.n_out; o += step) {
+        int64_t origin[MHLO_CUDA_MAX_RANK];  // position of window element 0 in the dilated, unpadded operand
+        int64_t rem = o;
+        for (int d = rank - 1; d >= 0; --d) {
+            origin[d] = (rem % p.out_shape[d]) * p.w.stride[d] - p.w.pad_low[d];
+            rem /= p.out_shape[d];
+        }
+        A acc = init;
+        int64_t wi[MHLO_CUDA_MAX_RANK];
+        for (int d = 0; d < rank; ++d) wi[d] = 0;
+        for (int64_t k = 0; k < p.window_count; ++k) {
+            int64_t off = 0;
+            bool inside = true;
+            for (int d = 0; d < rank; ++d) {
+                const int64_t pos = origin[d] + wi[d] * p.w.window_dilation[d];
+                const int64_t bd = p.w.base_dilation[d];
+                const int64_t src = pos / bd;
+                inside = inside && pos >= 0 && src < p.in_shape[d] && src * bd == pos;
+                off += src * p.in_stride[d];
+            }
+            const A v = inside ? widen<E>(static_cast<const E*>(p.in)[off]) : init;
+            acc = combine<A>(p.op, acc, v);
+            for (int d = rank - 1; d >= 0; --d) {  // next window coordinate, row-major
+                if (++wi[d] < p.w.size[d]) break;
+                wi[d] = 0;
+            }
+        }
+        static_cast<E*>(p.out)[o] = narrow<E>(acc);
+    }
+}
+
+// ---- scatter ---------------------------------------------------------------------------------------------------------
+
+struct ScatterParams {
+    mhlo_cuda_scatter_dims d;
+    int64_t operand_shape[MHLO_CUDA_MAX_RANK], indices_shape[MHLO_CUDA_MAX_RANK], updates_shape[MHLO_CUDA_MAX_RANK];
+    void* result;
+    const void* indices;
+    const void* updates;
+    int64_t n;
+    int32_t operand_rank, indices_rank, updates_rank, index_dtype, mode;
+};
+
+// Atomic read-modify-write of one element of any width through compare-and-swap on the word that holds it.
+template <typename E, typename F>
+__device__ __forceinline__ void cas_update(E* addr, F f) {
+    if constexpr (sizeof(E) == 8) {
+        auto* a = reinterpret_cast<unsigned long long*>(addr);
+        unsigned long long old = *a, assumed;
+        do {
+            assumed = old;
+            E cur;
+            memcpy(&cur, &assumed, 8);
+            const E nv = f(cur);
+            unsigned long long nb;
+            memcpy(&nb, &nv, 8);
+            old = atomicCAS(a, assumed, nb);
+        } while (old != assumed);
+    } else if constexpr (sizeof(E) == 4) {
+        auto* a = reinterpret_cast<unsigned int*>(addr);
+        unsigned int old = *a, assumed;
+        do {
+            assumed = old;
+            E cur;
+            memcpy(&cur, &assumed, 4);
+            const E nv = f(cur);
+            unsigned int nb;
+            memcpy(&nb, &nv, 4);
+            old = atomicCAS(a, assumed, nb);
+        } while (old != assumed);
+    } else {  // 1 or 2 bytes: swap the aligned 32-bit word around the element
+        const uintptr_t at = reinterpret_cast<uintptr_t>(addr);
+        auto* a = reinterpret_cast<unsigned int*>(at & ~uintptr_t(3));
+        const unsigned shift = static_cast<unsigned>(at & 3) * 8;
+        const unsigned int mask = (sizeof(E) == 1 ? 0xffu : 0xffffu) << shift;
+        unsigned int old = *a, assumed;
+        do {
+            assumed = old;
+            const unsigned int field = (assumed & mask) >> shift;
+            E cur;
+            memcpy(&cur, &field, sizeof(E));
+            const E nv = f(cur);
+            unsigned int nb = 0;
+            memcpy(&nb, &nv, sizeof(E));
+            old = atomicCAS(a, assumed, (assumed & ~mask) | (nb << shift));
+        } while (old != assumed);
+    }
+}
+
+template <typename E>
+__device__ __forceinline__ void scatter_apply(E* addr, E upd, int mode) {
+    using A = typename AccOf<E>::type;
+    if (mode == MHLO_SCATTER_SET) { *addr = upd; return; }
+    if (mode == MHLO_SCATTER_ADD) {
+        if constexpr (std::is_same<E, float>::value || std::is_same<E, double>::value || std::is_same<E, __half>::value ||
+                      std::is_same<E, __nv_bfloat16>::value || std::is_same<E, int32_t>::value || std::is_same<E, uint32_t>::value) {
+            atomicAdd(addr, upd);
+            return;
+        } else if constexpr (sizeof(E) == 8) {  // two's complement: signed and unsigned 64-bit adds are the same bits
+            atomicAdd(reinterpret_cast<unsigned long long*>(addr), static_cast<unsigned long long>(upd));
+            return;
+        }
+    }
+    const int op = mode == MHLO_SCATTER_ADD ? MHLO_REDUCE_SUM : mode == MHLO_SCATTER_MUL ? MHLO_REDUCE_PROD
+                 : mode == MHLO_SCATTER_MAX ? MHLO_REDUCE_MAX : MHLO_REDUCE_MIN;
+    const A u = widen<E>(upd);
+    cas_update<E>(addr, [&](E cur) { return narrow<E>(combine<A>(op, widen<E>(cur), u)); });
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ ScatterParams p) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool has_ivd = p.d.index_vector_dim < p.indices_rank;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += step) {
+        int64_t uidx[MHLO_CUDA_MAX_RANK];
+        int64_t rem = i;
+        for (int d = p.updates_rank - 1; d >= 0; --d) { uidx[d] = rem % p.updates_shape[d]; rem /= p.updates_shape[d]; }
+        // split the update index into scatter coordinates (into scatter_indices) and window coordinates
+        int64_t batch[MHLO_CUDA_MAX_RANK], win[MHLO_CUDA_MAX_RANK];
+        int nb = 0, nw = 0;
+        for (int d = 0; d < p.updates_rank; ++d) {
+            bool is_win = false;
+            for (int k = 0; k < p.d.n_update_window_dims; ++k) is_win |= p.d.update_window_dims[k] == d;
+            if (is_win) win[nw++] = uidx[d]; else batch[nb++] = uidx[d];
+        }
+        int64_t target[MHLO_CUDA_MAX_RANK];
+        for (int d = 0; d < p.operand_rank; ++d) target[d] = 0;
+        for (int k = 0; k < p.d.n_scatter_dims_to_operand; ++k) {
+            int64_t off = 0, bi = 0;
+            for (int d = 0; d < p.indices_rank; ++d) {
+                const int64_t c = (has_ivd && d == p.d.index_vector_dim) ? k : batch[bi++];
+                off = off * p.indices_shape[d] + c;
+            }
+            target[p.d.scatter_dims_to_operand_dims[k]] = p.index_dtype == MHLO_DT_I64 ? static_cast<const int64_t*>(p.indices)[off]
+                                                        : p.index_dtype == MHLO_DT_UI32 ? static_cast<int64_t>(static_cast<const uint32_t*>(p.indices)[off])
+                                                                                        : static_cast<const int32_t*>(p.indices)[off];
+        }
+        for (int k = 0; k < p.d.n_input_batching; ++k) {
+            int sd = p.d.scatter_indices_batching_dims[k];
+            if (has_ivd && sd > p.d.index_vector_dim) --sd;
+            target[p.d.input_batching_dims[k]] += batch[sd];
+        }
+        int64_t dst = 0;
+        int wi = 0;
+        bool inside = true;
+        for (int d = 0; d < p.operand_rank; ++d) {
+            bool skip = false;
+            for (int k = 0; k < p.d.n_inserted_window_dims; ++k) skip |= p.d.inserted_window_dims[k] == d;
+            for (int k = 0; k < p.d.n_input_batching; ++k) skip |= p.d.input_batching_dims[k] == d;
+            const int64_t c = target[d] + (skip ? 0 : win[wi++]);
+            inside = inside && c >= 0 && c < p.operand_shape[d];
+            dst = dst * p.operand_shape[d] + c;
+        }
+        if (inside) scatter_apply<E>(static_cast<E*>(p.result) + dst, static_cast<const E*>(p.updates)[i], p.mode);
+    }
+}
+
+// ---- sort --------------------------------------------------------------------------------------------------------------
+// Every key becomes an unsigned 64-bit number whose order is the wanted one (descending = complemented); the pair
+// (key, position in the slice) is unique, so a bitonic network over pairs gives the stable order. Slices are padded to
+// a power of two with pairs that sort last.
+
+constexpr int kSortChunk = MHLO_CUDA_SORT_SMEM_MAX;  // pairs a CTA holds in shared memory
+constexpr int kSortThreads = 1024;
+
+struct SortParams {
+    const void* in[MHLO_CUDA_SORT_MAX_OPERANDS];
+    void* out[MHLO_CUDA_SORT_MAX_OPERANDS];
+    int32_t elem_size[MHLO_CUDA_SORT_MAX_OPERANDS];
+    uint64_t* keys;   // global scratch (long slices only)
+    uint32_t* order;
+    int64_t n, inner, rows, padded;  // slice length, stride of the sorted dimension, number of slices, power of two >= n
+    int32_t n_operands, key_dtype, descending;
+};
+
+template <typename E>
+__device__ __forceinline__ uint64_t order_key(E v) {
+    if constexpr (std::is_same<E, double>::value) {
+        const uint64_t b = static_cast<uint64_t>(__double_as_longlong(v));
+        return b ^ ((b >> 63) ? ~0ull : (1ull << 63));
+    } else if constexpr (std::is_same<E, float>::value || std::is_same<E, __half>::value || std::is_same<E, __nv_bfloat16>::value) {
+        const uint32_t b = __float_as_uint(widen<E>(v));
+        return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+    } else if constexpr (std::is_signed<E>::value) {
+        return static_cast<uint64_t>(static_cast<int64_t>(v)) ^ (1ull << 63);
+    } else {
+        return static_cast<uint64_t>(v);
+    }
+}
+
+__device__ __forceinline__ uint64_t load_order_key(const void* base, int dtype, int64_t off, bool descending) {
+    uint64_t k = 0;
+    switch (dtype) {
+        case MHLO_DT_F32: k = order_key(static_cast<const float*>(base)[off]); break;
+        case MHLO_DT_F16: k = order_key(static_cast<const __half*>(base)[off]); break;
+        case MHLO_DT_BF16: k = order_key(static_cast<const __nv_bfloat16*>(base)[off]); break;
+        case MHLO_DT_F64: k = order_key(static_cast<const double*>(base)[off]); break;
+        case MHLO_DT_I8: k = order_key(static_cast<const int8_t*>(base)[off]); break;
+        case MHLO_DT_I16: k = order_key(static_cast<const int16_t*>(base)[off]); break;
+        case MHLO_DT_UI16: k = order_key(static_cast<const uint16_t*>(base)[off]); break;
+        case MHLO_DT_I32: k = order_key(static_cast<const int32_t*>(base)[off]); break;
+        case MHLO_DT_UI32: k = order_key(static_cast<const uint32_t*>(base)[off]); break;
+        case MHLO_DT_I64: k = order_key(static_cast<const int64_t*>(base)[off]); break;
+        case MHLO_DT_UI64: k = order_key(static_cast<const uint64_t*>(base)[off]); break;
+        default: k = order_key(static_cast<const uint8_t*>(base)[off]); break;  // I1, UI8
+    }
+    return descending ? ~k : k;
+}
+
+__device__ __forceinline__ int64_t slice_base(const SortParams& p, int64_t row) { return (row / p.inner) * p.n * p.inner + row % p.inner; }
+
+__device__ __forceinline__ void move_element(const SortParams& p, int j, int64_t dst, int64_t src) {
+    switch (p.elem_size[j]) {
+        case 1: static_cast<uint8_t*>(p.out[j])[dst] = static_cast<const uint8_t*>(p.in[j])[src]; break;
+        case 2: static_cast<uint16_t*>(p.out[j])[dst] = static_cast<const uint16_t*>(p.in[j])[src]; break;
+        case 4: static_cast<uint32_t*>(p.out[j])[dst] = static_cast<const uint32_t*>(p.in[j])[src]; break;
+        default: static_cast<uint64_t*>(p.out[j])[dst] = static_cast<const uint64_t*>(p.in[j])[src]; break;
+    }
+}
+
+// Compare-exchange stages j = j_first, j_first/2, .., 1 of merge size k over `count` pairs in shared memory whose
+// first pair has position `origin` in its (padded) slice.
+__device__ __forceinline__ void bitonic_stages(uint64_t* keys, uint32_t* order, int count, int64_t origin, int64_t k, int j_first) {
+    for (int j = j_first; j > 0; j >>= 1) {
+        for (int t = threadIdx.x; t < count / 2; t += blockDim.x) {
+            const int i = 2 * t - (t & (j - 1));
+            const int l = i + j;
+            const bool ascending = ((origin + i) & k) == 0;
+            const uint64_t ki = keys[i], kl = keys[l];
+            const uint32_t oi = order[i], ol = order[l];
+            const bool greater = ki > kl || (ki == kl && oi > ol);
+            if (greater == ascending) {
+                keys[i] = kl; keys[l] = ki;
+                order[i] = ol; order[l] = oi;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// One CTA sorts one slice of at most kSortChunk elements entirely in shared memory and writes every operand permuted.
+__global__ void __launch_bounds__(kSortThreads) sort_slices_kernel(const __grid_constant__ SortParams p) {
+    extern __shared__ __align__(16) unsigned char sort_smem[];
+    const int padded = static_cast<int>(p.padded);
+    uint64_t* keys = reinterpret_cast<uint64_t*>(sort_smem);
+    uint32_t* order = reinterpret_cast<uint32_t*>(keys + padded);
+    for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const int64_t base = slice_base(p, row);
+        for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+            const bool real = i < p.n;
+            keys[i] = real ? load_order_key(p.in[0], p.key_dtype, base + i * p.inner, p.descending != 0) : ~0ull;
+            order[i] = real ? static_cast<uint32_t>(i) : 0xffffffffu;
+        }
+        __syncthreads();
+        for (int k = 2; k <= padded; k <<= 1) bitonic_stages(keys, order, padded, 0, k, k >> 1);
+        for (int j = 0; j < p.n_operands; ++j)
+            for (int i = threadIdx.x; i < p.n; i += blockDim.x) move_element(p, j, base + i * p.inner, base + static_cast<int64_t>(order[i]) * p.inner);
+        __syncthreads();
+    }
+}
+
+// Long slices: pairs live in global scratch, rows * padded of them.
+__global__ void __launch_bounds__(256) sort_init_kernel(const __grid_constant__ SortParams p) {
+    const int64_t total = p.rows * p.padded;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += step) {
+        const int64_t row = g / p.padded, i = g % p.padded;
+        const bool real = i < p.n;
+        p.keys[g] = real ? load_order_key(p.in[0], p.key_dtype, slice_base(p, row) + i * p.inner, p.descending != 0) : ~0ull;
+        p.order[g] = real ? static_cast<uint32_t>(i) : 0xffffffffu;
+    }
+}
+
+// A CTA takes chunks of kSortChunk pairs through the stages that stay inside a chunk: the whole network up to merge
+// size kSortChunk when k == 0 (first pass), else the stages j < kSortChunk of merge size k.
+__global__ void __launch_bounds__(kSortThreads) sort_chunks_kernel(const __grid_constant__ SortParams p, int64_t k) {
+    extern __shared__ __align__(16) unsigned char sort_smem[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(sort_smem);
+    uint32_t* order = reinterpret_cast<uint32_t*>(keys + kSortChunk);
+    const int64_t chunks = p.rows * p.padded / kSortChunk;
+    for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+        const int64_t g0 = c * kSortChunk;
+        const int64_t origin = g0 % p.padded;
+        for (int i = threadIdx.x; i < kSortChunk; i += blockDim.x) { keys[i] = p.keys[g0 + i]; order[i] = p.order[g0 + i]; }
+        __syncthreads();
+        if (k == 0) {
+            for (int kk = 2; kk <= kSortChunk; kk <<= 1) bitonic_stages(keys, order, kSortChunk, origin, kk, kk >> 1);
+        } else {
+            bitonic_stages(keys, order, kSortChunk, origin, k, kSortChunk >> 1);
+        }
+        for (int i = threadIdx.x; i < kSortChunk; i += blockDim.x) { p.keys[g0 + i] = keys[i]; p.order[g0 + i] = order[i]; }
+        __syncthreads();
+    }
+}
+
+// One compare-exchange stage (k, j) with j >= kSortChunk over all slices.
+__global__ void __launch_bounds__(256) sort_global_stage_kernel(const __grid_constant__ SortParams p, int64_t k, int64_t j) {
+    const int64_t half = p.padded / 2, total = p.rows * half;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += step) {
+        const int64_t row = g / half, t = g % half;
+        const int64_t i = 2 * t - (t & (j - 1)), l = i + j;
+        const bool ascending = (i & k) == 0;
+        uint64_t* keys = p.keys + row * p.padded;
+        uint32_t* order = p.order + row * p.padded;
+        const uint64_t ki = keys[i], kl = keys[l];
+        const uint32_t oi = order[i], ol = order[l];
+        const bool greater = ki > kl || (ki == kl && oi > ol);
+        if (greater == ascending) {
+            keys[i] = kl; keys[l] = ki;
+            order[i] = ol; order[l] = oi;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) sort_apply_kernel(const __grid_constant__ SortParams p) {
+    const int64_t total = p.rows * p.n;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += step) {
+        const int64_t row = g / p.n, i = g % p.n;
+        const int64_t base = slice_base(p, row);
+        const int64_t src = base + static_cast<int64_t>(p.order[row * p.padded + i]) * p.inner;
+        for (int j = 0; j < p.n_operands; ++j) move_element(p, j, base + i * p.inner, src);
+    }
+}
+
+int64_t next_pow2(int64_t n) {
+    int64_t p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+}  // namespace
+}  // namespace mhlo
+
+using namespace mhlo;
+
+extern "C" int mhlo_cuda_reduce_window(const mhlo_cuda_view* in, const mhlo_cuda_window* window, int32_t op, const void* init_dev,
+                                       void* out_dev, const int64_t* out_shape, mhlo_cuda_stream_t stream) {
+    if (!in || !window || !out_shape) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_window: null argument");
+    if (window->rank != in->rank || in->rank < 0 || in->rank > MHLO_CUDA_MAX_RANK)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_window: window rank %d for an operand of rank %d", window->rank, in->rank);
+    if (op < MHLO_REDUCE_SUM || op > MHLO_REDUCE_XOR) return fail(MHLO_CUDA_UNSUPPORTED, "reduce_window: reducer %d", op);
+    WindowParams p;
+    memset(&p, 0, sizeof p);
+    p.w = *window;
+    p.n_out = 1;
+    p.window_count = 1;
+    for (int d = 0; d < in->rank; ++d) {
+        if (window->size[d] < 1 || window->stride[d] < 1 || window->base_dilation[d] < 1 || window->window_dilation[d] < 1)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_window: window size, stride and dilations must be positive (dimension %d)", d);
+        p.in_shape[d] = in->shape[d];
+        p.in_stride[d] = in->stride[d];
+        p.out_shape[d] = out_shape[d];
+        p.n_out *= out_shape[d];
+        p.window_count *= window->size[d];
+    }
+    if (p.n_out == 0) return MHLO_CUDA_OK;
+    if (!in->base || !init_dev || !out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "reduce_window: null pointer");
+    p.in = in->base;
+    p.init = init_dev;
+    p.out = out_dev;
+    p.op = op;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = grid_of(p.n_out, 256);
+    if (!with_element_type(in->dtype, [&](auto tag) { reduce_window_kernel<decltype(tag)><<<grid, 256, 0, s>>>(p); }))
+        return fail(MHLO_CUDA_UNSUPPORTED, "reduce_window: dtype %d", in->dtype);
+    MHLO_CUDA_CHECK_LAUNCH("reduce_window");
+    return MHLO_CUDA_OK;
+}
+
+extern "C" int mhlo_cuda_scatter(void* result_inout_dev, int32_t dtype, const int64_t* operand_shape, int32_t operand_rank,
+                                 const void* indices_dev, int32_t index_dtype, const int64_t* indices_shape, int32_t indices_rank,
+                                 const void* updates_dev, const int64_t* updates_shape, int32_t updates_rank,
+                                 const mhlo_cuda_scatter_dims* dims, int32_t mode, mhlo_cuda_stream_t stream) {
+    if (!dims || operand_rank < 0 || operand_rank > MHLO_CUDA_MAX_RANK || indices_rank < 0 || indices_rank > MHLO_CUDA_MAX_RANK ||
+        updates_rank < 0 || updates_rank > MHLO_CUDA_MAX_RANK)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: bad rank");
+    if (index_dtype != MHLO_DT_I32 && index_dtype != MHLO_DT_I64 && index_dtype != MHLO_DT_UI32)
+        return fail(MHLO_CUDA_UNSUPPORTED, "scatter: index dtype %d (I32, UI32 or I64 expected)", index_dtype);
+    if (mode < MHLO_SCATTER_SET || mode > MHLO_SCATTER_MIN) return fail(MHLO_CUDA_UNSUPPORTED, "scatter: update computation %d", mode);
+    if (dims->n_update_window_dims < 0 || dims->n_update_window_dims > updates_rank || dims->n_inserted_window_dims < 0 ||
+        dims->n_input_batching < 0 || dims->n_scatter_dims_to_operand < 0 || dims->n_scatter_dims_to_operand > MHLO_CUDA_MAX_RANK ||
+        dims->n_inserted_window_dims + dims->n_input_batching + dims->n_update_window_dims != operand_rank)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: window, inserted and batching dimensions do not cover the operand's rank %d", operand_rank);
+    const bool has_ivd = dims->index_vector_dim < indices_rank;
+    if (dims->index_vector_dim < 0 || dims->index_vector_dim > indices_rank)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: index_vector_dim %d for indices of rank %d", dims->index_vector_dim, indices_rank);
+    if (updates_rank - dims->n_update_window_dims != indices_rank - (has_ivd ? 1 : 0))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: updates have %d scatter dimensions, indices have %d",
+                    updates_rank - dims->n_update_window_dims, indices_rank - (has_ivd ? 1 : 0));
+    for (int k = 0; k < dims->n_scatter_dims_to_operand; ++k)
+        if (dims->scatter_dims_to_operand_dims[k] < 0 || dims->scatter_dims_to_operand_dims[k] >= operand_rank)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: scatter_dims_to_operand_dims entry out of range");
+    ScatterParams p;
+    memset(&p, 0, sizeof p);
+    p.d = *dims;
+    p.n = 1;
+    for (int d = 0; d < operand_rank; ++d) p.operand_shape[d] = operand_shape[d];
+    for (int d = 0; d < indices_rank; ++d) p.indices_shape[d] = indices_shape[d];
+    for (int d = 0; d < updates_rank; ++d) { p.updates_shape[d] = updates_shape[d]; p.n *= updates_shape[d]; }
+    if (p.n == 0) return MHLO_CUDA_OK;
+    if (!result_inout_dev || !indices_dev || !updates_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: null pointer");
+    p.result = result_inout_dev;
+    p.indices = indices_dev;
+    p.updates = updates_dev;
+    p.operand_rank = operand_rank;
+    p.indices_rank = indices_rank;
+    p.updates_rank = updates_rank;
+    p.index_dtype = index_dtype;
+    p.mode = mode;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = grid_of(p.n, 256);
+    if (!with_element_type(dtype, [&](auto tag) { scatter_kernel<decltype(tag)><<<grid, 256, 0, s>>>(p); }))
+        return fail(MHLO_CUDA_UNSUPPORTED, "scatter: dtype %d", dtype);
+    MHLO_CUDA_CHECK_LAUNCH("scatter");
+    return MHLO_CUDA_OK;
+}
+
+namespace {
+
+// rows, slice length and inner stride of sorting `shape` along `dimension`; false when the arguments are invalid
+bool sort_geometry(const int64_t* shape, int32_t rank, int32_t dimension, int64_t* rows, int64_t* n, int64_t* inner) {
+    if (!shape || rank < 1 || rank > MHLO_CUDA_MAX_RANK || dimension < 0 || dimension >= rank) return false;
+    *rows = 1;
+    *inner = 1;
+    for (int d = 0; d < rank; ++d) {
+        if (shape[d] < 0) return false;
+        if (d != dimension) *rows *= shape[d];
+        if (d > dimension) *inner *= shape[d];
+    }
+    *n = shape[dimension];
+    return true;
+}
+
+}  // namespace
+
+extern "C" int64_t mhlo_cuda_sort_scratch_bytes(const int64_t* shape, int32_t rank, int32_t dimension) {
+    int64_t rows, n, inner;
+    if (!sort_geometry(shape, rank, dimension, &rows, &n, &inner)) return -1;
+    if (n <= MHLO_CUDA_SORT_SMEM_MAX) return 0;
+    return rows * next_pow2(n) * static_cast<int64_t>(sizeof(uint64_t) + sizeof(uint32_t));
+}
+
+extern "C" int mhlo_cuda_sort(const void* const* operands_dev, void* const* outs_dev, const int32_t* dtypes, int32_t n_operands,
+                              const int64_t* shape, int32_t rank, int32_t dimension, int32_t descending, void* scratch_dev,
+                              int64_t scratch_bytes, mhlo_cuda_stream_t stream) {
+    if (!operands_dev || !outs_dev || !dtypes || n_operands < 1 || n_operands > MHLO_CUDA_SORT_MAX_OPERANDS)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "sort: between 1 and %d operands expected", MHLO_CUDA_SORT_MAX_OPERANDS);
+    SortParams p;
+    memset(&p, 0, sizeof p);
+    if (!sort_geometry(shape, rank, dimension, &p.rows, &p.n, &p.inner))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "sort: dimension %d of a rank-%d tensor", dimension, rank);
+    if (p.n >= (int64_t{1} << 31)) return fail(MHLO_CUDA_UNSUPPORTED, "sort: slices of 2^31 or more elements");
+    for (int j = 0; j < n_operands; ++j) {
+        p.elem_size[j] = dtype_bytes(dtypes[j]);
+        if (p.elem_size[j] == 0) return fail(MHLO_CUDA_UNSUPPORTED, "sort: dtype %d", dtypes[j]);
+        if (p.rows * p.n > 0 && (!operands_dev[j] || !outs_dev[j])) return fail(MHLO_CUDA_INVALID_ARGUMENT, "sort: null pointer");
+        if (operands_dev[j] == outs_dev[j] && p.rows * p.n > 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "sort: operand %d aliases its output", j);
+        p.in[j] = operands_dev[j];
+        p.out[j] = outs_dev[j];
+    }
+    if (p.rows * p.n == 0) return MHLO_CUDA_OK;
+    p.n_operands = n_operands;
+    p.key_dtype = dtypes[0];
+    p.descending = descending ? 1 : 0;
+    p.padded = next_pow2(p.n);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t pair_bytes = sizeof(uint64_t) + sizeof(uint32_t);
+    if (p.n <= kSortChunk) {
+        const size_t smem = static_cast<size_t>(p.padded) * pair_bytes;
+        MHLO_CUDA_TRY(cudaFuncSetAttribute(sort_slices_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSortChunk * pair_bytes)),
+                      MHLO_CUDA_EXECUTION_FAILED);
+        int threads = static_cast<int>(p.padded / 2);
+        threads = threads < 32 ? 32 : (threads > kSortThreads ? kSortThreads : threads);
+        const int grid = static_cast<int>(p.rows < kNumSMs * 8 ? p.rows : kNumSMs * 8);
+        sort_slices_kernel<<<grid, threads, smem, s>>>(p);
+        MHLO_CUDA_CHECK_LAUNCH("sort (shared memory)");
+        return MHLO_CUDA_OK;
+    }
+    const int64_t need = p.rows * p.padded * static_cast<int64_t>(pair_bytes);
+    if (!scratch_dev || scratch_bytes < need)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "sort: slices of %lld elements need %lld bytes of scratch, got %lld", static_cast<long long>(p.n),
+                    static_cast<long long>(need), static_cast<long long>(scratch_bytes));
+    p.keys = static_cast<uint64_t*>(scratch_dev);
+    p.order = reinterpret_cast<uint32_t*>(p.keys + p.rows * p.padded);
+    MHLO_CUDA_TRY(cudaFuncSetAttribute(sort_chunks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSortChunk * pair_bytes)),
+                  MHLO_CUDA_EXECUTION_FAILED);
+    const int64_t chunks = p.rows * p.padded / kSortChunk;
+    const int chunk_grid = static_cast<int>(chunks < kNumSMs * 2 ? chunks : kNumSMs * 2);
+    const size_t chunk_smem = kSortChunk * pair_bytes;
+    sort_init_kernel<<<grid_of(p.rows * p.padded, 256), 256, 0, s>>>(p);
+    MHLO_CUDA_CHECK_LAUNCH("sort (keys)");
+    sort_chunks_kernel<<<chunk_grid, kSortThreads, chunk_smem, s>>>(p, 0);
+    MHLO_CUDA_CHECK_LAUNCH("sort (chunks)");
+    for (int64_t k = 2 * static_cast<int64_t>(kSortChunk); k <= p.padded; k <<= 1) {
+        for (int64_t j = k >> 1; j >= kSortChunk; j >>= 1) {
+            sort_global_stage_kernel<<<grid_of(p.rows * p.padded / 2, 256), 256, 0, s>>>(p, k, j);
+            MHLO_CUDA_CHECK_LAUNCH("sort (global stage)");
+        }
+        sort_chunks_kernel<<<chunk_grid, kSortThreads, chunk_smem, s>>>(p, k);
+        MHLO_CUDA_CHECK_LAUNCH("sort (chunk merge)");
+    }
+    sort_apply_kernel<<<grid_of(p.rows * p.n, 256), 256, 0, s>>>(p);
+    MHLO_CUDA_CHECK_LAUNCH("sort (apply)");
+    return MHLO_CUDA_OK;
+}

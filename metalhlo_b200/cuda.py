@@ -46,6 +46,19 @@ class GatherDims(C.Structure):
                 ("start_index_map", C.c_int32 * 8), ("index_vector_dim", C.c_int32), ("slice_sizes", C.c_int64 * 8)]
 
 
+class Window(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("size", C.c_int64 * 8), ("stride", C.c_int64 * 8), ("base_dilation", C.c_int64 * 8),
+                ("window_dilation", C.c_int64 * 8), ("pad_low", C.c_int64 * 8)]
+
+
+class ScatterDims(C.Structure):
+    _fields_ = [("n_update_window_dims", C.c_int32), ("n_inserted_window_dims", C.c_int32), ("n_input_batching", C.c_int32),
+                ("n_scatter_dims_to_operand", C.c_int32), ("update_window_dims", C.c_int32 * 8),
+                ("inserted_window_dims", C.c_int32 * 8), ("input_batching_dims", C.c_int32 * 8),
+                ("scatter_indices_batching_dims", C.c_int32 * 8), ("scatter_dims_to_operand_dims", C.c_int32 * 8),
+                ("index_vector_dim", C.c_int32)]
+
+
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: build it with `make -C metalhlo_b200/csrc` "
@@ -99,6 +112,11 @@ _PROTOTYPES = {
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
                                    _vp, C.POINTER(_i64), _i32, _vp]),
+    "mhlo_cuda_reduce_window": (C.c_int, [C.POINTER(View), C.POINTER(Window), _i32, _vp, _vp, C.POINTER(_i64), _vp]),
+    "mhlo_cuda_scatter": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp, C.POINTER(_i64), _i32,
+                                    C.POINTER(ScatterDims), _i32, _vp]),
+    "mhlo_cuda_sort_scratch_bytes": (_i64, [C.POINTER(_i64), _i32, _i32]),
+    "mhlo_cuda_sort": (C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i32), _i32, C.POINTER(_i64), _i32, _i32, _i32, _vp, _i64, _vp]),
     "mhlo_cuda_dynamic_slice": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, C.POINTER(_vp), _i32, C.POINTER(_i64), _vp, _vp]),
     "mhlo_cuda_dynamic_update_slice": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, C.POINTER(_i64), C.POINTER(_vp), _i32, _vp]),
     "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),

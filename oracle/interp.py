@@ -66,6 +66,17 @@ def round_to(arr, dtype):
     return arr
 
 
+def _storage_dtype(dtype):
+    """numpy dtype with the bit layout of a StableHLO element type (floats are carried as float64 elsewhere)."""
+    if dtype in FLOAT_DTYPES:
+        if dtype == "bf16":
+            if _BF16 is None:
+                raise Unsupported("bf16 bit patterns need ml_dtypes")
+            return _BF16
+        return {"f16": np.float16, "f32": np.float32, "f64": np.float64}[dtype]
+    return INT_DTYPES[dtype]
+
+
 class Scanner:
     def __init__(self, text):
         self.s, self.p = text, 0
@@ -712,6 +723,31 @@ def _float_to_int(arr, ttype):
     return np.clip(a, float(info.min), float(info.max)).astype(dt)
 
 
+def _total_order_key(values, dtype):
+    """uint64 keys whose unsigned order is the total order of the values (-NaN < -inf < .. < -0 < +0 < .. < +NaN)."""
+    if dtype in FLOAT_DTYPES:
+        if dtype == "f64":
+            b = np.ascontiguousarray(values, dtype=np.float64).view(np.uint64)
+            return np.where(b >> np.uint64(63), ~b, b | np.uint64(1 << 63))
+        b = np.ascontiguousarray(values.astype(np.float32)).view(np.uint32).astype(np.uint64)
+        flipped = np.where(b >> np.uint64(31), b ^ np.uint64(0xFFFFFFFF), b | np.uint64(0x80000000))
+        return flipped
+    v = np.asarray(values)
+    if v.dtype == np.bool_:
+        return v.astype(np.uint64)
+    if np.issubdtype(v.dtype, np.signedinteger):
+        return (v.astype(np.int64).view(np.uint64)) ^ np.uint64(1 << 63)
+    return v.astype(np.uint64)
+
+
+def _with_attrs(op, **extra):
+    import copy
+    o = copy.copy(op)
+    o.attrs = dict(op.attrs)
+    o.attrs.update(extra)
+    return o
+
+
 class Interpreter:
     def __init__(self, round_floats: bool = False, funcs=None):
         self.round_floats = round_floats
@@ -738,6 +774,136 @@ class Interpreter:
             scope.update({name: x for (name, _), x in zip(body.args, state)})
             state = self._run_ops(body.ops, scope)
         raise Unsupported("while loop did not terminate within 1e6 iterations")
+
+    def op_branch(self, op, a, env):
+        """stablehlo.if / stablehlo.case: only the selected region is interpreted (if: true branch first; case: an
+        index outside [0, N) selects the last branch)."""
+        sel = np.asarray(a[0]).reshape(())
+        if op.name == "if":
+            k = 0 if bool(sel) else 1
+        else:
+            k = int(sel)
+            if k < 0 or k >= len(op.regions):
+                k = len(op.regions) - 1
+        return self._run_ops(op.regions[k].ops, dict(env))
+
+    def _apply(self, region, env, values):
+        """Runs a region on scalar arguments and returns its results."""
+        scope = dict(env)
+        scope.update({name: np.asarray(v) for (name, _), v in zip(region.args, values)})
+        return self._run_ops(region.ops, scope)
+
+    def region_reduce_window(self, op, a, env):
+        """stablehlo.reduce_window: the operand is dilated and padded with the init value, and every window is folded
+        through the body region in row-major order, starting from the init value."""
+        if len(a) != 2:
+            raise Unsupported("variadic reduce_window")
+        x, init = a[0], a[1].reshape(())
+        t = op.types[0]
+        A = op.attrs
+        rank = x.ndim
+        size = _ints(A.get("window_dimensions"))
+        stride = _ints(A.get("window_strides")) or [1] * rank
+        bdil = _ints(A.get("base_dilations")) or [1] * rank
+        wdil = _ints(A.get("window_dilations")) or [1] * rank
+        pad = A.get("padding")
+        pad = np.asarray(dense_value(pad[1], pad[2]) if isinstance(pad, tuple) else (pad if pad is not None else np.zeros((rank, 2))), dtype=np.int64).reshape(rank, 2)
+        dil_shape = [(n - 1) * b + 1 if n > 0 else 0 for n, b in zip(x.shape, bdil)]
+        dil = np.full(dil_shape, init, dtype=x.dtype)
+        dil[tuple(slice(None, None, b) for b in bdil)] = x
+        padded_shape = [max(0, n + int(lo) + int(hi)) for n, (lo, hi) in zip(dil_shape, pad)]
+        padded = np.full(padded_shape, init, dtype=x.dtype)
+        src, dst = [], []
+        for n, (lo, hi), m in zip(dil_shape, pad, padded_shape):
+            s0, s1 = max(0, -int(lo)), n - max(0, -int(hi))
+            src.append(slice(s0, max(s0, s1)))
+            d0 = max(0, int(lo))
+            dst.append(slice(d0, d0 + max(0, s1 - s0)))
+        padded[tuple(dst)] = dil[tuple(src)]
+        out = np.empty(t.shape, dtype=x.dtype)
+        body = op.regions[0]
+        for o in np.ndindex(*t.shape):
+            acc = init
+            for w in np.ndindex(*size):
+                pos = tuple(oi * st + wi * wd for oi, st, wi, wd in zip(o, stride, w, wdil))
+                acc = self._apply(body, env, [acc, padded[pos]])[0].reshape(())
+            out[o] = acc
+        return out
+
+    def region_scatter(self, op, a, env):
+        """stablehlo.scatter: updates are applied one by one, in row-major order of `updates`, through the update
+        computation; an update whose target lies outside the operand is skipped."""
+        if len(a) != 3:
+            raise Unsupported("variadic scatter")
+        A = op.attrs
+        d = A.get("scatter_dimension_numbers", A)
+        uwd = _ints(d.get("update_window_dims"))
+        iwd = _ints(d.get("inserted_window_dims"))
+        ib = _ints(d.get("input_batching_dims"))
+        sb = _ints(d.get("scatter_indices_batching_dims"))
+        sdod = _ints(d.get("scatter_dims_to_operand_dims"))
+        ivd = int(d.get("index_vector_dim"))
+        result, idx, upd = a[0].copy(), a[1].astype(np.int64), a[2]
+        if ivd == idx.ndim:
+            idx = idx[..., None]
+        idx = np.moveaxis(idx, ivd, -1)
+        scatter_dims = [k for k in range(upd.ndim) if k not in uwd]
+        window_operand_dims = [k for k in range(result.ndim) if k not in iwd and k not in ib]
+        sb_pos = [b - (1 if b > ivd else 0) for b in sb]
+        body = op.regions[0]
+        for u in np.ndindex(*upd.shape):
+            batch = tuple(u[k] for k in scatter_dims)
+            target = [0] * result.ndim
+            for k, od in enumerate(sdod):
+                target[od] = int(idx[batch + (k,)])
+            for k, od in enumerate(ib):
+                target[od] += batch[sb_pos[k]]
+            for k, od in enumerate(window_operand_dims):
+                target[od] += u[uwd[k]]
+            if all(0 <= c < n for c, n in zip(target, result.shape)):
+                result[tuple(target)] = self._apply(body, env, [result[tuple(target)], upd[u]])[0].reshape(())
+        return result
+
+    def region_sort(self, op, a, env):
+        """stablehlo.sort: slices along `dimension` are put in the order of the comparator region with a stable
+        sort (slices longer than 2048 elements use the comparator's recognised LT / GT form on a total-order key)."""
+        import functools
+        A = op.attrs
+        dim = int(A.get("dimension", -1))
+        if dim < 0:
+            dim += a[0].ndim
+        comp = op.regions[0]
+        n = a[0].shape[dim]
+        moved = [np.moveaxis(x, dim, -1) for x in a]
+        outs = [np.empty_like(m) for m in moved]
+
+        def less(i, j, row):
+            args = []
+            for m in moved:
+                args += [m[row + (i,)], m[row + (j,)]]
+            return bool(self._apply(comp, env, args)[0].reshape(()))
+
+        direction = None
+        if n > 2048:
+            cmp_ops = [o for o in comp.ops if o.name.endswith("compare")]
+            if len(comp.ops) != 2 or len(cmp_ops) != 1:
+                raise Unsupported("long sort with a comparator that is not a single compare")
+            c = cmp_ops[0]
+            dname = c.attrs.get("comparison_direction") or [k for k in c.attrs.get("_kw", []) if k in _DIRS][0]
+            names = [name for name, _ in comp.args]
+            straight = list(c.operands) == names[:2]
+            if dname not in ("LT", "GT") or (not straight and list(c.operands) != names[1::-1]):
+                raise Unsupported("long sort with a comparator other than LT / GT of the first operand")
+            direction = "asc" if (dname == "LT") == straight else "desc"
+        for row in np.ndindex(*moved[0].shape[:-1]):
+            if direction is None:
+                order = sorted(range(n), key=functools.cmp_to_key(lambda i, j: -1 if less(i, j, row) else (1 if less(j, i, row) else 0)))
+            else:
+                key = _total_order_key(moved[0][row], op.in_types[0].dtype)
+                order = np.argsort(~key if direction == "desc" else key, kind="stable")
+            for m, o in zip(moved, outs):
+                o[row] = m[row][np.asarray(order, dtype=np.int64)]
+        return [np.moveaxis(o, -1, dim) for o in outs]
 
     def run(self, func, inputs):
         env = {}
@@ -776,6 +942,10 @@ class Interpreter:
         it = op.in_types
         if n == "while":
             return self.op_while(op, a, t, env)
+        if n in ("if", "case"):
+            return self.op_branch(op, a, env)
+        if n in ("reduce_window", "scatter", "sort"):
+            return getattr(self, "region_" + n)(op, a, env)
         f = getattr(self, "op_" + n, None)
         if f is not None:
             return f(op, a, t)
@@ -888,6 +1058,11 @@ class Interpreter:
         d = op.attrs.get("comparison_direction")
         if d is None:
             d = [k for k in op.attrs.get("_kw", []) if k in _DIRS][0]
+        ctype = op.attrs.get("compare_type") or next((k for k in op.attrs.get("_kw", []) if k in ("TOTALORDER", "FLOAT", "SIGNED", "UNSIGNED")), None)
+        if ctype == "TOTALORDER" and op.in_types and op.in_types[0].is_float:
+            # -NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN: compare order-preserving integer keys
+            dt = op.in_types[0].dtype
+            return _DIRS[d](_total_order_key(np.asarray(a[0]), dt), _total_order_key(np.asarray(a[1]), dt))
         return _DIRS[d](a[0], a[1])
 
     def op_select(self, op, a, t):
@@ -1058,6 +1233,39 @@ class Interpreter:
         st = [min(max(int(a[2 + d].reshape(())), 0), x.shape[d] - u.shape[d]) for d in range(x.ndim)]
         x[tuple(slice(s, s + n) for s, n in zip(st, u.shape))] = u
         return x
+
+    # -- forms whose shape operands are constants of the module (the result type is static)
+    def op_dynamic_reshape(self, op, a, t):
+        return a[0].reshape(t.shape)
+
+    def op_dynamic_broadcast_in_dim(self, op, a, t):
+        return self.op_broadcast_in_dim(op, a[:1], t)
+
+    def op_dynamic_iota(self, op, a, t):
+        return self.op_iota(op, [], t)
+
+    def op_dynamic_pad(self, op, a, t):
+        op2 = _with_attrs(op, edge_padding_low=[int(v) for v in a[2]], edge_padding_high=[int(v) for v in a[3]],
+                          interior_padding=[int(v) for v in a[4]])
+        return self.op_pad(op2, a[:2], t)
+
+    def op_dynamic_gather(self, op, a, t):
+        return self.op_gather(_with_attrs(op, slice_sizes=[int(v) for v in a[2]]), a[:2], t)
+
+    def op_bitcast_convert(self, op, a, t):
+        """Same bits, other element type; a narrower result gains a minor dimension, a wider one loses it."""
+        raw = np.ascontiguousarray(a[0].astype(_storage_dtype(op.in_types[0].dtype)))
+        out = (raw if raw.ndim else raw.reshape(1)).view(_storage_dtype(t.dtype)).reshape(t.shape)
+        return out.astype(np.float64) if t.is_float else out
+
+    def op_batch_norm_inference(self, op, a, t):
+        x, scale, offset, mean, var = a
+        axis = int(op.attrs.get("feature_index", 0))
+        eps = float(op.attrs.get("epsilon", 0.0))
+        shape = [1] * x.ndim
+        shape[axis] = x.shape[axis]
+        r = lambda v: v.reshape(shape)
+        return (x - r(mean)) / np.sqrt(r(var) + eps) * r(scale) + r(offset)
 
     def op_optimization_barrier(self, op, a, t):
         return a

@@ -389,4 +389,265 @@ def pattern_cases(rng, dt):
     return out
 
 
-CASES = build_cases()
+def widening_cases():
+    """Control flow with branches, the dynamic_* forms with constant shape operands, bitcast_convert and
+    batch_norm_inference: the operators either side of the fused hot path."""
+    rng = np.random.default_rng(977)
+    out = []
+    t48 = tt((4, 8), "f32")
+    x48 = rand(rng, (4, 8), "f32")
+    y48 = rand(rng, (4, 8), "f32")
+    # ---- if: lax.cond prints the generic form with two regions that capture outer values
+    if_text = f"""module @jit_cond {{
+  func.func public @main(%arg0: tensor<i32>, %arg1: {t48}, %arg2: {t48}) -> ({t48}, tensor<f32>) {{
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %p = stablehlo.compare  GT, %arg0, %c,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+    %0:2 = "stablehlo.if"(%p) ({{
+      %1 = stablehlo.multiply %arg1, %arg2 : {t48}
+      %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+      %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [0, 1] : ({t48}, tensor<f32>) -> tensor<f32>
+      stablehlo.return %1, %2 : {t48}, tensor<f32>
+    }}, {{
+      %1 = stablehlo.subtract %arg1, %arg2 : {t48}
+      %cst = stablehlo.constant dense<1.000000e+00> : tensor<f32>
+      stablehlo.return %1, %cst : {t48}, tensor<f32>
+    }}) : (tensor<i1>) -> ({t48}, tensor<f32>)
+    return %0#0, %0#1 : {t48}, tensor<f32>
+  }}
+}}
+"""
+    for v in (1, 0):
+        out.append((f"if_{'true' if v else 'false'}", if_text, [np.asarray(v, np.int32), x48, y48]))
+    case_text = f"""module @jit_switch {{
+  func.func public @main(%arg0: tensor<i32>, %arg1: {t48}) -> ({t48}) {{
+    %0 = "stablehlo.case"(%arg0) ({{
+      %1 = stablehlo.negate %arg1 : {t48}
+      stablehlo.return %1 : {t48}
+    }}, {{
+      %1 = stablehlo.tanh %arg1 : {t48}
+      %2 = "stablehlo.if"(%p0) ({{
+        stablehlo.return %1 : {t48}
+      }}, {{
+        stablehlo.return %arg1 : {t48}
+      }}) : (tensor<i1>) -> {t48}
+      stablehlo.return %2 : {t48}
+    }}, {{
+      %1 = stablehlo.abs %arg1 : {t48}
+      stablehlo.return %1 : {t48}
+    }}) : (tensor<i32>) -> {t48}
+    return %0 : {t48}
+  }}
+}}
+""".replace("    %0 = \"stablehlo.case\"", "    %p0 = stablehlo.constant dense<true> : tensor<i1>\n    %0 = \"stablehlo.case\"")
+    for v in (0, 1, 2, 7, -3):
+        out.append((f"case_index_{v}".replace("-", "m"), case_text, [np.asarray(v, np.int32), x48]))
+    # ---- bitcast_convert
+    bits = x48.view(np.int32)
+    out.append(("bitcast_convert_f32_i32", func([t48], [tt((4, 8), "i32")],
+                f"    %0 = stablehlo.bitcast_convert %arg0 : ({t48}) -> {tt((4, 8), 'i32')}", "%0"), [x48]))
+    out.append(("bitcast_convert_i32_f32", func([tt((4, 8), "i32")], [t48],
+                f"    %0 = stablehlo.bitcast_convert %arg0 : ({tt((4, 8), 'i32')}) -> {t48}", "%0"), [bits.copy()]))
+    out.append(("bitcast_convert_transposed_ui32", func([t48], [tt((8, 4), "ui32")],
+                f"    %0 = stablehlo.transpose %arg0, dims = [1, 0] : ({t48}) -> {tt((8, 4), 'f32')}\n"
+                f"    %1 = stablehlo.bitcast_convert %0 : ({tt((8, 4), 'f32')}) -> {tt((8, 4), 'ui32')}", "%1"), [x48]))
+    out.append(("bitcast_convert_f32_to_bytes", func([t48], [tt((4, 8, 4), "ui8")],
+                f"    %0 = stablehlo.bitcast_convert %arg0 : ({t48}) -> {tt((4, 8, 4), 'ui8')}", "%0"), [x48]))
+    out.append(("bitcast_convert_halves_to_f32", func([tt((4, 8, 2), "ui16")], [t48],
+                f"    %0 = stablehlo.bitcast_convert %arg0 : ({tt((4, 8, 2), 'ui16')}) -> {t48}", "%0"),
+                [x48.view(np.uint16).reshape(4, 8, 2).copy()]))
+    # ---- dynamic_* with constant shape operands
+    out.append(("dynamic_reshape", func([t48], [tt((2, 16), "f32")],
+                "    %s = stablehlo.constant dense<[2, 16]> : tensor<2xi32>\n"
+                f"    %0 = stablehlo.dynamic_reshape %arg0, %s : ({t48}, tensor<2xi32>) -> {tt((2, 16), 'f32')}", "%0"), [x48]))
+    out.append(("dynamic_broadcast_in_dim", func([tt((8,), "f32")], [tt((3, 8, 2), "f32")],
+                "    %s = stablehlo.constant dense<[3, 8, 2]> : tensor<3xi64>\n"
+                f"    %0 = \"stablehlo.dynamic_broadcast_in_dim\"(%arg0, %s) <{{broadcast_dimensions = array<i64: 1>}}> : ({tt((8,), 'f32')}, tensor<3xi64>) -> {tt((3, 8, 2), 'f32')}",
+                "%0"), [x48[0].copy()]))
+    out.append(("dynamic_iota", func([t48], [tt((4, 8), "i32")],
+                "    %s = stablehlo.constant dense<[4, 8]> : tensor<2xi32>\n"
+                f"    %0 = \"stablehlo.dynamic_iota\"(%s) <{{iota_dimension = 1 : i64}}> : (tensor<2xi32>) -> {tt((4, 8), 'i32')}",
+                "%0"), [x48]))
+    out.append(("dynamic_pad", func([t48], [tt((7, 16), "f32")],
+                "    %z = stablehlo.constant dense<-1.000000e+00> : tensor<f32>\n"
+                "    %lo = stablehlo.constant dense<[1, 0]> : tensor<2xi32>\n"
+                "    %hi = stablehlo.constant dense<[2, 1]> : tensor<2xi32>\n"
+                "    %in = stablehlo.constant dense<[0, 1]> : tensor<2xi32>\n"
+                f"    %0 = stablehlo.dynamic_pad %arg0, %z, %lo, %hi, %in : ({t48}, tensor<f32>, tensor<2xi32>, tensor<2xi32>, tensor<2xi32>) -> {tt((7, 16), 'f32')}",
+                "%0"), [x48]))
+    ids = rng.integers(0, 4, size=(5, 1)).astype(np.int32)
+    out.append(("dynamic_gather", func([t48, tt((5, 1), "i32")], [tt((5, 8), "f32")],
+                "    %s = stablehlo.constant dense<[1, 8]> : tensor<2xi32>\n"
+                f"    %0 = \"stablehlo.dynamic_gather\"(%arg0, %arg1, %s) <{{dimension_numbers = #stablehlo.gather<offset_dims = [1], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 1>, indices_are_sorted = false}}> : ({t48}, {tt((5, 1), 'i32')}, tensor<2xi32>) -> {tt((5, 8), 'f32')}",
+                "%0"), [x48, ids]))
+    # ---- batch_norm_inference over NHWC and NCHW feature positions
+    for dt in ("f32", "bf16"):
+        if dt not in NP:
+            continue
+        for axis, shape in ((3, (2, 5, 6, 16)), (1, (2, 16, 5, 6))):
+            t, tc = tt(shape, dt), tt((16,), dt)
+            x = rand(rng, shape, dt)
+            scale, offset, mean = (rand(rng, (16,), dt) for _ in range(3))
+            var = rand(rng, (16,), dt, 0.2, 2.0)
+            out.append((f"batch_norm_inference_axis{axis}_{dt}", func([t, tc, tc, tc, tc], [t],
+                        f"    %0 = \"stablehlo.batch_norm_inference\"(%arg0, %arg1, %arg2, %arg3, %arg4) <{{epsilon = 1.000000e-03 : f32, feature_index = {axis} : i64}}> : ({t}, {tc}, {tc}, {tc}, {tc}) -> {t}",
+                        "%0"), [x, scale, offset, mean, var]))
+    return out
+
+
+def _region(kind, dt, names=("a", "b")):
+    """Body region of reduce_window / scatter: one binary op on two scalars, or the assignment form of scatter."""
+    st = f"tensor<{dt}>"
+    head = f"    ^bb0(%{names[0]}: {st}, %{names[1]}: {st}):\n"
+    if kind == "set":
+        return head + f"      stablehlo.return %{names[1]} : {st}\n"
+    return head + f"      %r = stablehlo.{kind} %{names[0]}, %{names[1]} : {st}\n      stablehlo.return %r : {st}\n"
+
+
+def _const(dt, value):
+    if dt in ("f32", "f16", "bf16", "f64"):
+        if value in ("-inf", "inf"):
+            bits = {"f32": "0xFF800000", "f16": "0xFC00", "bf16": "0xFF80", "f64": "0xFFF0000000000000"}[dt]
+            if value == "inf":
+                bits = "0x7" + bits[3:]
+            return f"stablehlo.constant dense<{bits}> : tensor<{dt}>"
+        return f"stablehlo.constant dense<{float(value):e}> : tensor<{dt}>"
+    return f"stablehlo.constant dense<{int(value)}> : tensor<{dt}>"
+
+
+def reduce_window_case(name, x, dt, kind, init, window, out_shape, strides=None, padding=None, base_dil=None, win_dil=None, pre=None):
+    """One stablehlo.reduce_window in the generic form jax prints. pre = (text, shape): ops applied to %arg0 first."""
+    rank = len(window)
+    arr = lambda v: "array<i64: " + ", ".join(str(i) for i in v) + ">"
+    props = [f"window_dimensions = {arr(window)}"]
+    if strides: props.append(f"window_strides = {arr(strides)}")
+    if base_dil: props.append(f"base_dilations = {arr(base_dil)}")
+    if win_dil: props.append(f"window_dilations = {arr(win_dil)}")
+    if padding:
+        rows = ", ".join(f"[{lo}, {hi}]" for lo, hi in padding)
+        props.append(f"padding = dense<[{rows}]> : tensor<{rank}x2xi64>")
+    t_in = tt(x.shape, dt)
+    src, t_src, body = "%arg0", t_in, ""
+    if pre:
+        body, t_src, src = pre[0] + "\n", tt(pre[1], dt), "%pre"
+    t_out = tt(out_shape, dt)
+    body += (f"    %init = {_const(dt, init)}\n"
+             f"    %0 = \"stablehlo.reduce_window\"({src}, %init) <{{{', '.join(props)}}}> ({{\n{_region(kind, dt)}    }}) : ({t_src}, tensor<{dt}>) -> {t_out}")
+    return (name, func([t_in], [t_out], body, "%0"), [x])
+
+
+def scatter_case(name, operand, indices, updates, dt, kind, dims, idt="i32"):
+    t_op, t_idx, t_upd = tt(operand.shape, dt), tt(indices.shape, idt), tt(updates.shape, dt)
+    body = (f"    %0 = \"stablehlo.scatter\"(%arg0, %arg1, %arg2) <{{indices_are_sorted = false, scatter_dimension_numbers = #stablehlo.scatter<{dims}>, "
+            f"unique_indices = false}}> ({{\n{_region(kind, dt)}    }}) : ({t_op}, {t_idx}, {t_upd}) -> {t_op}")
+    return (name, func([t_op, t_idx, t_upd], [t_op], body, "%0"), [operand, indices, updates])
+
+
+def sort_case(name, arrays, dts, dimension, direction="LT", swapped=False):
+    """stablehlo.sort of len(arrays) operands by the first one, the comparator a single compare as jax.lax.sort prints."""
+    types = [tt(a.shape, dt) for a, dt in zip(arrays, dts)]
+    block = ", ".join(f"%l{i}: tensor<{dt}>, %r{i}: tensor<{dt}>" for i, dt in enumerate(dts))
+    lhs, rhs = ("%r0", "%l0") if swapped else ("%l0", "%r0")
+    ctype = "TOTALORDER" if dts[0] in ("f32", "f16", "bf16", "f64") else ("UNSIGNED" if dts[0].startswith("ui") else "SIGNED")
+    args = ", ".join(f"%arg{i}" for i in range(len(arrays)))
+    results = ", ".join(f"%0#{i}" for i in range(len(arrays))) if len(arrays) > 1 else "%0"
+    lhs_bind = f"%0:{len(arrays)}" if len(arrays) > 1 else "%0"
+    sig_out = ", ".join(types)
+    body = (f"    {lhs_bind} = \"stablehlo.sort\"({args}) <{{dimension = {dimension} : i64, is_stable = true}}> ({{\n"
+            f"    ^bb0({block}):\n"
+            f"      %c = stablehlo.compare  {direction}, {lhs}, {rhs},  {ctype} : (tensor<{dts[0]}>, tensor<{dts[0]}>) -> tensor<i1>\n"
+            f"      stablehlo.return %c : tensor<i1>\n"
+            f"    }}) : ({sig_out}) -> ({sig_out})" if len(arrays) > 1 else
+            f"    {lhs_bind} = \"stablehlo.sort\"({args}) <{{dimension = {dimension} : i64, is_stable = true}}> ({{\n"
+            f"    ^bb0({block}):\n"
+            f"      %c = stablehlo.compare  {direction}, {lhs}, {rhs},  {ctype} : (tensor<{dts[0]}>, tensor<{dts[0]}>) -> tensor<i1>\n"
+            f"      stablehlo.return %c : tensor<i1>\n"
+            f"    }}) : ({sig_out}) -> {sig_out}")
+    return (name, func(types, types, body, results), list(arrays))
+
+
+def window_scatter_sort_cases():
+    rng = np.random.default_rng(4242)
+    out = []
+    # ---- reduce_window: pooling as flax / jax.lax.reduce_window print it
+    x = rand(rng, (2, 8, 8, 4), "f32")
+    out.append(reduce_window_case("reduce_window_maxpool_2x2", x, "f32", "maximum", "-inf", (1, 2, 2, 1), (2, 4, 4, 4), strides=(1, 2, 2, 1)))
+    out.append(reduce_window_case("reduce_window_sum_3x3_same", x, "f32", "add", 0, (1, 3, 3, 1), (2, 8, 8, 4),
+                                  padding=((0, 0), (1, 1), (1, 1), (0, 0))))
+    if "bf16" in NP:
+        out.append(reduce_window_case("reduce_window_sum_3x3_same_bf16", rand(rng, (2, 8, 8, 4), "bf16"), "bf16", "add", 0, (1, 3, 3, 1), (2, 8, 8, 4),
+                                      padding=((0, 0), (1, 1), (1, 1), (0, 0))))
+    out.append(reduce_window_case("reduce_window_maxpool_3x3_s2_pad", x, "f32", "maximum", "-inf", (1, 3, 3, 1), (2, 4, 4, 4), strides=(1, 2, 2, 1),
+                                  padding=((0, 0), (0, 1), (0, 1), (0, 0))))
+    xi = rand(rng, (5, 9), "i32")
+    # dilated operand (9 -> 17), dilated window (3 taps spanning 5), negative low padding: (17 - 1 + 2 - 5) / 2 + 1 = 7
+    out.append(reduce_window_case("reduce_window_dilations_i32", xi, "i32", "add", 0, (2, 3), (4, 7), strides=(1, 2),
+                                  padding=((0, 0), (-1, 2)), base_dil=(1, 2), win_dil=(1, 2)))
+    out.append(reduce_window_case("reduce_window_min_i32", xi, "i32", "minimum", 2147483647, (3, 3), (3, 7)))
+    out.append(reduce_window_case("reduce_window_nonzero_init", rand(rng, (6, 6), "f32"), "f32", "add", 0.5, (2, 2), (7, 7),
+                                  padding=((1, 1), (1, 1))))
+    xc = rand(rng, (3, 33), "f32")
+    out.append(reduce_window_case("reduce_window_cumsum", xc, "f32", "add", 0, (1, 33), (3, 33), padding=((0, 0), (32, 0))))
+    xt = rand(rng, (9, 6), "f32")
+    out.append(reduce_window_case("reduce_window_of_transpose", xt, "f32", "maximum", "-inf", (2, 3), (3, 3), strides=(2, 3),
+                                  pre=(f"    %pre = stablehlo.transpose %arg0, dims = [1, 0] : ({tt((9, 6), 'f32')}) -> {tt((6, 9), 'f32')}", (6, 9))))
+    out.append(reduce_window_case("reduce_window_or_i1", rand(rng, (4, 10), "i1"), "i1", "or", 0, (1, 3), (4, 8)))
+    # ---- scatter
+    point = "inserted_window_dims = [0], scatter_dims_to_operand_dims = [0], index_vector_dim = 1"
+    rows = "update_window_dims = [1], inserted_window_dims = [0], scatter_dims_to_operand_dims = [0], index_vector_dim = 1"
+    base = rand(rng, (20,), "f32")
+    uniq = rng.permutation(20)[:6].astype(np.int32).reshape(6, 1)
+    out.append(scatter_case("scatter_set_points", base, uniq, rand(rng, (6,), "f32"), "f32", "set", point))
+    out.append(scatter_case("scatter_set_points_i64_index", base, uniq.astype(np.int64), rand(rng, (6,), "f32"), "f32", "set", point, idt="i64"))
+    table = rand(rng, (10, 8), "f32")
+    dup = np.array([[3], [7], [3], [0], [9], [3]], np.int32)
+    out.append(scatter_case("scatter_add_rows_duplicates", table, dup, rand(rng, (6, 8), "f32"), "f32", "add", rows))
+    oob = np.array([[-1], [4], [10], [2], [12345], [9]], np.int32)
+    out.append(scatter_case("scatter_add_rows_out_of_bounds", table, oob, rand(rng, (6, 8), "f32"), "f32", "add", rows))
+    for dt, kind in (("i32", "maximum"), ("f32", "minimum"), ("f32", "multiply"), ("i8", "add"), ("i64", "add"), ("f16", "maximum"),
+                     ("bf16", "add"), ("f64", "add"), ("ui8", "minimum"), ("i16", "multiply")):
+        if dt not in NP:
+            continue
+        lo, hi = (-3, 3) if kind == "multiply" else (-2.0, 2.0)
+        out.append(scatter_case(f"scatter_{kind}_{dt}_duplicates", rand(rng, (10, 8), dt, lo, hi) if dt[0] in "fb" else rand(rng, (10, 8), dt),
+                                dup, rand(rng, (6, 8), dt, lo, hi) if dt[0] in "fb" else rng.integers(-3 if dt[0] == "i" else 0, 4, size=(6, 8)).astype(NP[dt]),
+                                dt, kind, rows))
+    batched = ("inserted_window_dims = [1], input_batching_dims = [0], scatter_indices_batching_dims = [0], "
+               "scatter_dims_to_operand_dims = [1], index_vector_dim = 2")
+    out.append(scatter_case("scatter_add_batched", rand(rng, (3, 10), "f32"), rng.integers(0, 10, size=(3, 4, 1)).astype(np.int32),
+                            rand(rng, (3, 4), "f32"), "f32", "add", batched))
+    window2d = "update_window_dims = [1, 2], scatter_dims_to_operand_dims = [0, 1], index_vector_dim = 1"
+    out.append(scatter_case("scatter_add_windows_partly_outside", rand(rng, (6, 7), "i32"), np.array([[0, 0], [5, 5], [2, 6], [-1, 3]], np.int32),
+                            rand(rng, (4, 2, 3), "i32"), "i32", "add", window2d))
+    # ---- sort
+    keys = rand(rng, (37,), "f32")
+    keys[[3, 11]] = np.nan
+    keys[5], keys[6], keys[20], keys[21] = 0.0, -0.0, np.inf, -np.inf
+    keys[30] = keys[2]
+    out.append(sort_case("sort_f32_special_values", [keys], ["f32"], 0))
+    out.append(sort_case("sort_f32_descending", [keys], ["f32"], 0, direction="GT"))
+    out.append(sort_case("sort_f32_swapped_comparator", [keys], ["f32"], 0, direction="LT", swapped=True))
+    m = rng.integers(-5, 6, size=(9, 7)).astype(np.int32)
+    out.append(sort_case("sort_i32_dim0_descending", [m], ["i32"], 0, direction="GT"))
+    ties = rng.integers(0, 6, size=(4, 100)).astype(np.float32)
+    iota = np.broadcast_to(np.arange(100, dtype=np.int32), (4, 100)).copy()
+    out.append(sort_case("argsort_stable_ties", [ties, iota], ["f32", "i32"], 1))
+    out.append(sort_case("argsort_stable_ties_descending", [ties, iota], ["f32", "i32"], 1, direction="GT"))
+    for dt in ("bf16", "ui8", "i64", "f64", "f16", "i8", "ui32"):
+        if dt not in NP:
+            continue
+        k = rand(rng, (3, 50), dt)
+        out.append(sort_case(f"sort_pairs_{dt}", [k, rand(rng, (3, 50), "f32")], [dt, "f32"], 1))
+    three = [rng.integers(0, 4, size=(2, 5, 3)).astype(np.int32), rand(rng, (2, 5, 3), "f32"), rand(rng, (2, 5, 3), "i8")]
+    out.append(sort_case("sort_three_operands_middle_dim", three, ["i32", "f32", "i8"], 1))
+    big = rand(rng, (2, 5000), "f32")
+    out.append(sort_case("sort_long_rows_shared_memory", [big, np.broadcast_to(np.arange(5000, dtype=np.int32), (2, 5000)).copy()], ["f32", "i32"], 1))
+    for n in (8192, 8193, 20000):
+        kk = rng.integers(-1000, 1000, size=(3, n)).astype(np.int32)
+        out.append(sort_case(f"sort_global_{n}", [kk, np.broadcast_to(np.arange(n, dtype=np.int32), (3, n)).copy()], ["i32", "i32"], 1,
+                             direction="GT" if n == 8193 else "LT"))
+    cols = rand(rng, (9000, 3), "f32")
+    out.append(sort_case("sort_global_strided_dim0", [cols], ["f32"], 0))
+    return out
+
+
+CASES = build_cases() + widening_cases() + window_scatter_sort_cases()

@@ -1,0 +1,113 @@
+"""The oracle's reduce_window / scatter / sort / if / case against independent numpy formulations of the same
+StableHLO semantics (the interpreter folds the body regions; numpy computes the closed form)."""
+import numpy as np
+import pytest
+
+from op_cases import CASES
+from oracle import interp
+
+BY_NAME = {c[0]: c for c in CASES}
+
+
+def run(name):
+    _, text, inputs = BY_NAME[name]
+    return interp.evaluate(text, inputs), inputs
+
+
+def test_maxpool_matches_numpy_blocks():
+    (got,), (x,) = run("reduce_window_maxpool_2x2")
+    want = x.reshape(2, 4, 2, 4, 2, 4).max(axis=(2, 4))
+    np.testing.assert_array_equal(got, want)
+
+
+def test_same_padded_window_sum_matches_shifted_adds():
+    (got,), (x,) = run("reduce_window_sum_3x3_same")
+    padded = np.pad(x.astype(np.float64), ((0, 0), (1, 1), (1, 1), (0, 0)))
+    want = sum(padded[:, i:i + 8, j:j + 8, :] for i in range(3) for j in range(3))
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_cumsum_window_is_a_prefix_sum():
+    (got,), (x,) = run("reduce_window_cumsum")
+    np.testing.assert_allclose(got, np.cumsum(x.astype(np.float64), axis=1), rtol=1e-5, atol=1e-5)
+
+
+def test_nonzero_init_pads_with_the_init_value():
+    (got,), (x,) = run("reduce_window_nonzero_init")
+    padded = np.pad(x.astype(np.float64), 1, constant_values=0.5)
+    want = 0.5 + sum(padded[i:i + 7, j:j + 7] for i in range(2) for j in range(2))
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_dilated_window_sum_matches_explicit_dilation():
+    (got,), (x,) = run("reduce_window_dilations_i32")
+    dil = np.zeros((5, 17), np.int64)
+    dil[:, ::2] = x
+    padded = np.pad(dil, ((0, 0), (0, 2)))[:, 1:]  # low padding of -1 trims one column
+    want = np.zeros((4, 7), np.int64)
+    for o0 in range(4):
+        for o1 in range(7):
+            want[o0, o1] = sum(padded[o0 + w0, 2 * o1 + 2 * w1] for w0 in range(2) for w1 in range(3))
+    np.testing.assert_array_equal(got, want)
+
+
+def test_scatter_add_matches_add_at():
+    (got,), (table, idx, upd) = run("scatter_add_rows_duplicates")
+    want = table.astype(np.float64).copy()
+    np.add.at(want, idx[:, 0], upd.astype(np.float64))
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_scatter_skips_targets_outside_the_operand():
+    (got,), (table, idx, upd) = run("scatter_add_rows_out_of_bounds")
+    want = table.astype(np.float64).copy()
+    for r, i in enumerate(idx[:, 0]):
+        if 0 <= i < 10:
+            want[i] += upd[r]
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_scatter_batched_indexes_inside_each_batch():
+    (got,), (x, idx, upd) = run("scatter_add_batched")
+    want = x.astype(np.float64).copy()
+    for b in range(3):
+        np.add.at(want[b], idx[b, :, 0], upd[b].astype(np.float64))
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_sort_orders_special_values_totally():
+    (got,), (keys,) = run("sort_f32_special_values")
+    assert np.isnan(got[-2:]).all() and got[0] == -np.inf and got[-3] == np.inf
+    zeros = np.flatnonzero(got == 0)
+    assert np.signbit(got[zeros[0]]) and not np.signbit(got[zeros[1]])
+    finite = got[:-2]
+    assert (np.diff(finite) >= 0).all()
+
+
+def test_argsort_is_stable_in_both_directions():
+    (vals, order), (ties, _) = run("argsort_stable_ties")
+    for r in range(4):
+        np.testing.assert_array_equal(order[r], np.argsort(ties[r], kind="stable"))
+    (vals, order), _ = run("argsort_stable_ties_descending")
+    for r in range(4):
+        np.testing.assert_array_equal(order[r], np.argsort(-ties[r], kind="stable"))
+
+
+@pytest.mark.parametrize("n", [8192, 8193, 20000])
+def test_long_sort_is_a_stable_permutation(n):
+    (vals, order), (keys, _) = run(f"sort_global_{n}")
+    k = -keys.astype(np.int64) if n == 8193 else keys.astype(np.int64)
+    for r in range(3):
+        np.testing.assert_array_equal(order[r], np.argsort(k[r], kind="stable"))
+        np.testing.assert_array_equal(vals[r], keys[r][order[r]])
+
+
+def test_branches_pick_one_region():
+    (a, b), (_, x, y) = run("if_true")
+    np.testing.assert_allclose(a, x.astype(np.float64) * y, rtol=1e-6)
+    (a, b), (_, x, y) = run("if_false")
+    np.testing.assert_allclose(a, x.astype(np.float64) - y, rtol=1e-6)
+    assert float(b) == 1.0
+    for v, f in ((0, np.negative), (1, np.tanh), (2, np.abs), (7, np.abs), (-3, np.abs)):
+        (got,), (_, x) = run(f"case_index_{v}".replace("-", "m"))
+        np.testing.assert_allclose(got, f(x.astype(np.float64)), rtol=1e-6)
