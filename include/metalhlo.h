@@ -150,6 +150,10 @@ MHLOStatusCode mhlo_execute_with_profile(MHLOExecutableRef executable, const MHL
 /* Host-only (no CUDA device needed): parse, run the pass pipeline of the given level, return the module text
  * (free with mhlo_free_string). */
 MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimization_level, char** out_text);
+/* Host-only: lowers the module to the executor's step list without touching a device. *out_steps = one step label
+ * per line (free with mhlo_free_string); out_launches / out_arena_bytes may be NULL. */
+MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_level, char** out_steps,
+                                   int32_t* out_launches, int64_t* out_arena_bytes);
 /* StableHLO text after the pass pipeline; free with mhlo_free_string. */
 char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable);
 /* Kernel launches one execution enqueues. */

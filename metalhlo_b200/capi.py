@@ -104,6 +104,7 @@ _PROTOTYPES = {
                                            _P(C.c_double)]),
     "mhlo_execute_with_profile": (C.c_int, [_vp, _P(_vp), _i32, _P(_vp), _P(_i32), _P(ExecutionProfile)]),
     "mhlo_b200_optimize_text": (C.c_int, [C.c_char_p, _i32, _P(_vp)]),
+    "mhlo_b200_plan_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i32), _P(_i64)]),
     "mhlo_b200_executable_optimized_text": (_vp, [_vp]),
     "mhlo_b200_executable_launch_count": (_i32, [_vp]),
     "mhlo_b200_executable_arena_bytes": (_i64, [_vp]),
@@ -156,6 +157,13 @@ def optimize_text(mlir: str, opt_level: int = 3) -> str:
     out = _vp()
     _check(lib.mhlo_b200_optimize_text(mlir.encode(), opt_level, C.byref(out)))
     return _take_string(out.value)
+
+
+def plan_text(mlir: str, opt_level: int = 3):
+    """Lowering on the host only (no GPU): (step labels, kernel launches per execution, arena bytes)."""
+    out, launches, arena = _vp(), _i32(0), _i64(0)
+    _check(lib.mhlo_b200_plan_text(mlir.encode(), opt_level, C.byref(out), C.byref(launches), C.byref(arena)))
+    return _take_string(out.value).splitlines(), launches.value, arena.value
 
 
 class tuning:

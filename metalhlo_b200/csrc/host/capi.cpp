@@ -529,6 +529,30 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
     }
 }
 
+// Host-only: lowers `mlir_text` to the executor's step list without touching a device. *out_steps receives one step
+// label per line (malloc'd; free with mhlo_free_string); *out_launches and *out_arena_bytes (either may be null) the
+// kernel launches per execution and the planned scratch arena.
+MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_level, char** out_steps, int32_t* out_launches,
+                                   int64_t* out_arena_bytes) {
+    if (!mlir_text || !out_steps) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    *out_steps = nullptr;
+    try {
+        CompileOptions opt;
+        opt.opt_level = optimization_level;
+        std::unique_ptr<Executable> exe = Executable::plan_only(mlir_text, opt);
+        std::string s;
+        for (const std::string& l : exe->step_labels()) s += l + "\n";
+        *out_steps = strdup(s.c_str());
+        if (out_launches) *out_launches = exe->num_kernel_launches();
+        if (out_arena_bytes) *out_arena_bytes = exe->arena_bytes();
+        return MHLO_OK;
+    } catch (const CompileError& e) {
+        return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));
+    } catch (const std::exception& e) {
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
+    }
+}
+
 // ---- kernel tuning -----------------------------------------------------------------------------------------------
 
 MHLOStatusCode mhlo_b200_tuning_open(const char* path) {

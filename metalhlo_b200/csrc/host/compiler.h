@@ -73,6 +73,8 @@ class Executable {
     // Parses, optimises, lowers and plans `mlir`; uploads constants and allocates the arena on the current CUDA
     // device. Throws CompileError.
     static std::unique_ptr<Executable> compile(const std::string& mlir, const CompileOptions& options);
+    // The same without touching a device: the step list, launch count and memory plan of `mlir`. The result cannot run.
+    static std::unique_ptr<Executable> plan_only(const std::string& mlir, const CompileOptions& options);
 
     int num_inputs() const { return static_cast<int>(input_types_.size()); }
     int num_outputs() const { return static_cast<int>(output_types_.size()); }

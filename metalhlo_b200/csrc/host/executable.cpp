@@ -1363,6 +1363,17 @@ Executable::~Executable() {
     if (arena_dev_) mhlo_cuda_free(arena_dev_);
 }
 
+std::unique_ptr<Executable> Executable::plan_only(const std::string& mlir, const CompileOptions& options) {
+    Module m = parse_module(mlir);
+    Function f = flatten_main(m);
+    std::unique_ptr<Executable> exe(new Executable());
+    exe->pass_log_ = run_pass_pipeline(f, options);
+    exe->optimized_text_ = print_function(f);
+    Lowering lower(f, exe.get());
+    lower.run();
+    return exe;
+}
+
 std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const CompileOptions& options) {
     Module m = parse_module(mlir);
     Function f = flatten_main(m);

@@ -266,10 +266,11 @@ def dense_value(body, ttype):
 
 
 class Op:
-    __slots__ = ("name", "operands", "results", "types", "attrs", "regions", "in_types")
+    __slots__ = ("name", "operands", "results", "types", "attrs", "regions", "in_types", "bare_type_list")
 
     def __init__(self):
         self.name, self.operands, self.results, self.types, self.attrs, self.regions, self.in_types = "", [], [], [], {}, [], []
+        self.bare_type_list = False  # the signature was "t0, t1" without parentheses or arrow
 
 
 class Region:
@@ -411,6 +412,8 @@ class ModuleParser(Scanner):
             op.results = [f"{names[0]}#{i}" for i in range(declared)]
         else:
             op.results = names
+        if len(op.results) > 1 and getattr(op, "bare_type_list", False) and len(op.in_types) == len(op.results):
+            op.types = list(op.in_types)  # "%a, %b = op %x, %y : t0, t1": one type per result
         return op
 
     def operands(self, op, close):
@@ -448,6 +451,7 @@ class ModuleParser(Scanner):
                 outs = [self.type()]
             else:
                 ins, outs = ts, [ts[-1]]
+                op.bare_type_list = True
         op.in_types, op.types = ins, outs
 
     def attr(self):
@@ -1254,6 +1258,8 @@ class Interpreter:
 
     def op_bitcast_convert(self, op, a, t):
         """Same bits, other element type; a narrower result gains a minor dimension, a wider one loses it."""
+        if "i1" in (op.in_types[0].dtype, t.dtype):
+            raise Unsupported("bitcast_convert of i1 (packed bits)")
         raw = np.ascontiguousarray(a[0].astype(_storage_dtype(op.in_types[0].dtype)))
         out = (raw if raw.ndim else raw.reshape(1)).view(_storage_dtype(t.dtype)).reshape(t.shape)
         return out.astype(np.float64) if t.is_float else out

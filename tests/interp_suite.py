@@ -18,7 +18,10 @@ FILES = ["abs", "add", "and", "atan2", "broadcast_in_dim", "cbrt", "ceil", "clam
          "exponential", "exponential_minus_one", "floor", "gather", "iota", "is_finite", "log", "log_plus_one", "logistic",
          "maximum", "minimum", "multiply", "negate", "not", "or", "pad", "popcnt", "power", "reduce", "remainder", "reshape",
          "reverse", "round_nearest_afz", "round_nearest_even", "rsqrt", "select", "shift_left", "shift_right_arithmetic",
-         "shift_right_logical", "sign", "sine", "slice", "sqrt", "subtract", "tan", "tanh", "transpose", "xor"]
+         "shift_right_logical", "sign", "sine", "slice", "sqrt", "subtract", "tan", "tanh", "transpose", "xor",
+         # control flow and the operators either side of the fused path
+         "bitcast_convert", "call", "case", "if", "while", "dynamic_broadcast_in_dim", "dynamic_gather", "dynamic_iota",
+         "dynamic_pad", "dynamic_reshape", "optimization_barrier", "reduce_window", "scatter", "sort"]
 
 
 class Case:

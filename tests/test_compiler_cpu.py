@@ -32,6 +32,31 @@ def test_oracle_and_compiler_accept_case(name):
     assert live_ops(again) == live_ops(capi.optimize_text(text, 0))
 
 
+@pytest.mark.parametrize("name", [c[0] for c in CASES])
+def test_every_case_lowers_to_a_step_list_without_a_device(name):
+    _, text, _ = BY_NAME[name]
+    for level in (0, 2, 3):
+        steps, launches, arena = capi.plan_text(text, level)
+        assert launches >= len(steps)
+        assert arena >= 0
+        assert all(steps), steps
+
+
+def test_long_sort_plans_its_global_stages():
+    _, text, _ = BY_NAME["sort_global_20000"]
+    steps, launches, arena = capi.plan_text(text, 3)
+    # 32768 padded keys: key build, chunk sort, (1 global stage + merge) for 16384, (2 + merge) for 32768, apply
+    assert steps == ["sort"] and launches == 8
+    assert arena >= 3 * 32768 * 12
+
+
+def test_conditionals_become_selects():
+    _, text, _ = BY_NAME["case_index_1"]
+    flat = capi.optimize_text(text, 0)
+    assert "stablehlo.case" not in flat and "stablehlo.if" not in flat
+    assert flat.count('"stablehlo.select"') >= 3  # two for the case, one for the nested if
+
+
 def test_parse_errors_report_status_3_with_a_line_number():
     with pytest.raises(capi.MetalHLOError) as e:
         capi.optimize_text("module { func.func @main(%a: tensor<2xf32>) -> tensor<2xf32> { %0 = stablehlo.add %a, %b : tensor<2xf32>\n return %0 : tensor<2xf32> } }", 0)
