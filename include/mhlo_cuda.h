@@ -398,6 +398,44 @@ int mhlo_cuda_sort(const void* const* operands_dev, void* const* outs_dev, const
                    int64_t scratch_bytes, mhlo_cuda_stream_t stream);
 
 /*
+ * Geometry of stablehlo.convolution in canonical order: input [batch, spatial.., feature], kernel [spatial..,
+ * input feature, output feature], output [batch, spatial.., feature]. The three tensors are addressed through
+ * element strides, so any dimension_numbers layout (NHWC, NCHW, HWIO, OIHW, ..) is a choice of strides.
+ */
+#define MHLO_CUDA_CONV_MAX_SPATIAL 6
+typedef struct {
+    int32_t n_spatial;
+    int32_t reverse[MHLO_CUDA_CONV_MAX_SPATIAL];       /* window_reversal */
+    int64_t batch, in_features, out_features;           /* of the input, the input, the kernel */
+    int64_t feature_group_count, batch_group_count;
+    int64_t in_size[MHLO_CUDA_CONV_MAX_SPATIAL], kernel_size[MHLO_CUDA_CONV_MAX_SPATIAL], out_size[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t stride[MHLO_CUDA_CONV_MAX_SPATIAL], pad_low[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t lhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL], rhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t in_batch_stride, in_feature_stride, in_spatial_stride[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t kernel_in_stride, kernel_out_stride, kernel_spatial_stride[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t out_batch_stride, out_feature_stride, out_spatial_stride[MHLO_CUDA_CONV_MAX_SPATIAL];
+} mhlo_cuda_conv;
+
+/*
+ * Direct convolution, one thread per output element, every attribute of the op honoured (strides, padding, both
+ * dilations, window reversal, feature and batch groups). Floats accumulate in fp32 (f64 in fp64), integers in
+ * int64. The general path; the reference lowers convolution to MPSGraph convolution2D
+ * (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift:2695-3050).
+ */
+int mhlo_cuda_convolution(int32_t dtype, const void* in_dev, const void* kernel_dev, void* out_dev, const mhlo_cuda_conv* conv,
+                          mhlo_cuda_stream_t stream);
+
+/*
+ * The patch matrix of a convolution with batch_group_count 1: cols[g][m][k] for feature group g, output position
+ * m = (batch, output spatial..) row-major and k = (kernel spatial.., input feature within the group) row-major,
+ * rows padded with zeros to `row_pitch` elements (>= kernel volume x features per group). Positions that fall into
+ * the padding or between dilated input elements are zero. The convolution is then one (batched over groups) GEMM
+ * of cols with the kernel viewed as [k, output feature], which runs on the tcgen05 kernel of mhlo_cuda_gemm.
+ */
+int mhlo_cuda_im2col(int32_t dtype, const void* in_dev, void* cols_dev, int64_t row_pitch, const mhlo_cuda_conv* conv,
+                     mhlo_cuda_stream_t stream);
+
+/*
  * C[b0,b1,m,n] = sum_k A(b0,b1,m,k) * B(b0,b1,k,n) for arbitrary element strides (a_strides / b_strides =
  * {batch0, batch1, row, col} strides in elements; C is contiguous). Any dtype: floats accumulate in fp32
  * (f64 in fp64), integers in int64. This is the general-layout path of dot_general - strict fp32 as the

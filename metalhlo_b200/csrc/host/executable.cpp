@@ -511,14 +511,14 @@ class Lowering {
         if (n == "reduce") return lower_reduce(op);
         if (n == "dot_general" || n == "dot") return lower_dot(op);
         if (n == "gather") return lower_gather(op);
+        if (n == "convolution") return lower_convolution(op);
         if (n == "reduce_window") return lower_reduce_window(op);
         if (n == "scatter") return lower_scatter(op);
         if (n == "sort") return lower_sort(op);
         if (n == "dynamic_slice") return lower_dynamic_slice(op);
         if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
         if (n == "custom_call") return lower_custom_call(op);
-        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" ||
-            n == "convolution" || n == "fft" || n == "select_and_scatter" ||
+        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "fft" || n == "select_and_scatter" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         const int code = ew_opcode(n);
@@ -865,6 +865,178 @@ class Lowering {
         View out = dense_view(new_arena(p.type.bytes()), p.type);
         copy_view(p, out, "copy(" + why + ")");
         return out;
+    }
+
+    // stablehlo.convolution. Floating-point convolutions without batch groups become a patch matrix and one GEMM
+    // (batched over feature groups) on the tensor-core path; everything else runs the direct kernel. Both read the
+    // operands through their views, so no layout needs a copy.
+    void lower_convolution(const Op& op) {
+        if (op.operands.size() != 2) fail_compile("convolution takes two operands");
+        const View& x = get(op.operands[0]);
+        const View& w = get(op.operands[1]);
+        const TensorType& rt = op.result_types[0];
+        const int rank = x.type.rank(), ns = rank - 2;
+        if (ns < 0 || ns > MHLO_CUDA_CONV_MAX_SPATIAL || w.type.rank() != rank || rt.rank() != rank)
+            fail_unsupported("convolution of rank " + std::to_string(rank));
+        if (w.type.dtype != x.type.dtype || rt.dtype != x.type.dtype) fail_unsupported("convolution with mixed element types");
+        auto dim = [&](const char* k) {
+            const int64_t d = op.int_attr(k, -1);
+            if (d < 0 || d >= rank) fail_compile(std::string("convolution: ") + k + " out of range");
+            return static_cast<size_t>(d);
+        };
+        auto dims = [&](const char* k) {
+            std::vector<int64_t> v = op.int_list(k);
+            if (static_cast<int>(v.size()) != ns) fail_compile(std::string("convolution: ") + k + " must list the spatial dimensions");
+            for (int64_t d : v) if (d < 0 || d >= rank) fail_compile(std::string("convolution: ") + k + " out of range");
+            return v;
+        };
+        const size_t ib = dim("input_batch_dimension"), ifd = dim("input_feature_dimension"), ki = dim("kernel_input_feature_dimension"),
+                     ko = dim("kernel_output_feature_dimension"), ob = dim("output_batch_dimension"), ofd = dim("output_feature_dimension");
+        const std::vector<int64_t> isp = dims("input_spatial_dimensions"), ksp = dims("kernel_spatial_dimensions"), osp = dims("output_spatial_dimensions");
+        mhlo_cuda_conv c;
+        std::memset(&c, 0, sizeof c);
+        c.n_spatial = ns;
+        c.batch = x.type.shape[ib];
+        c.in_features = x.type.shape[ifd];
+        c.out_features = w.type.shape[ko];
+        c.feature_group_count = op.int_attr("feature_group_count", 1);
+        c.batch_group_count = op.int_attr("batch_group_count", 1);
+        if (c.feature_group_count < 1 || c.batch_group_count < 1 || (c.feature_group_count > 1 && c.batch_group_count > 1))
+            fail_compile("convolution: bad feature_group_count / batch_group_count");
+        if (c.in_features % c.feature_group_count || c.out_features % c.feature_group_count || c.out_features % c.batch_group_count ||
+            c.batch % c.batch_group_count || w.type.shape[ki] != c.in_features / c.feature_group_count)
+            fail_compile("convolution: group counts do not match the feature dimensions");
+        auto list = [&](const char* k, size_t want, int64_t dflt) {
+            std::vector<int64_t> v = op.int_list(k);
+            if (v.empty()) v.assign(want, dflt);
+            if (v.size() != want) fail_compile(std::string("convolution: ") + k + " has the wrong length");
+            return v;
+        };
+        const std::vector<int64_t> st = list("window_strides", ns, 1), pad = list("padding", 2 * ns, 0), ld = list("lhs_dilation", ns, 1),
+                                   rd = list("rhs_dilation", ns, 1), rev = list("window_reversal", ns, 0);
+        int64_t out_positions = 1, kernel_volume = 1;
+        for (int d = 0; d < ns; ++d) {
+            c.in_size[d] = x.type.shape[static_cast<size_t>(isp[d])];
+            c.kernel_size[d] = w.type.shape[static_cast<size_t>(ksp[d])];
+            c.out_size[d] = rt.shape[static_cast<size_t>(osp[d])];
+            c.stride[d] = st[d];
+            c.pad_low[d] = pad[2 * d];
+            c.lhs_dilation[d] = ld[d];
+            c.rhs_dilation[d] = rd[d];
+            c.reverse[d] = rev[d] ? 1 : 0;
+            if (st[d] < 1 || ld[d] < 1 || rd[d] < 1) fail_compile("convolution: strides and dilations must be positive");
+            // the result type must agree with the window arithmetic
+            const int64_t dil_in = c.in_size[d] > 0 ? (c.in_size[d] - 1) * ld[d] + 1 : 0;
+            const int64_t dil_k = c.kernel_size[d] > 0 ? (c.kernel_size[d] - 1) * rd[d] + 1 : 0;
+            const int64_t padded = dil_in + pad[2 * d] + pad[2 * d + 1];
+            const int64_t expect = (padded < dil_k || dil_k == 0) ? 0 : (padded - dil_k) / st[d] + 1;
+            if (expect != c.out_size[d]) fail_compile("convolution: result type " + rt.str() + " does not match the window (dimension " + std::to_string(d) + ")");
+            c.in_spatial_stride[d] = x.strides[static_cast<size_t>(isp[d])];
+            c.kernel_spatial_stride[d] = w.strides[static_cast<size_t>(ksp[d])];
+            out_positions *= c.out_size[d];
+            kernel_volume *= c.kernel_size[d];
+        }
+        c.in_batch_stride = x.strides[ib];
+        c.in_feature_stride = x.strides[ifd];
+        c.kernel_in_stride = w.strides[ki];
+        c.kernel_out_stride = w.strides[ko];
+        if (rt.shape[ob] != c.batch / c.batch_group_count || rt.shape[ofd] != c.out_features)
+            fail_compile("convolution: result type " + rt.str() + " does not match the batch / feature sizes");
+        const int dt = static_cast<int>(x.type.dtype);
+        const int64_t G = c.feature_group_count, Og = c.out_features / G, Cg = c.in_features / G;
+        const bool gemm_path = is_float(x.type.dtype) && x.type.dtype != DType::F64 && c.batch_group_count == 1 && (G == 1 || Og >= 8) &&
+                               !std::getenv("METALHLO_CONV_DIRECT") && rt.count() > 0 && kernel_volume * Cg > 0;
+        DevView dx = dev(x), dw = dev(w);
+        keep_alive(x);
+        keep_alive(w);
+        if (!gemm_path) {
+            View out = dense_view(new_arena(rt.bytes()), rt);
+            c.out_batch_stride = out.strides[ob];
+            c.out_feature_stride = out.strides[ofd];
+            for (int d = 0; d < ns; ++d) c.out_spatial_stride[d] = out.strides[static_cast<size_t>(osp[d])];
+            DevView dout = dev(out);
+            keep_alive(out);
+            add_step("convolution", [=](const Ctx& cx) {
+                return mhlo_cuda_convolution(dt, bind(dx, cx).base, bind(dw, cx).base, const_cast<void*>(bind(dout, cx).base), &c, cx.stream);
+            });
+            return set(op.results[0], out);
+        }
+        // ---- patch matrix + GEMM
+        const int64_t M = c.batch * out_positions, Kc = kernel_volume * Cg, pitch = (Kc + 7) / 8 * 8;
+        TensorType cols_t;
+        cols_t.dtype = x.type.dtype;
+        cols_t.shape = {G, M, pitch};
+        View cols = dense_view(new_arena(cols_t.bytes()), cols_t);
+        DevView dcols = dev(cols);
+        keep_alive(cols);
+        add_step("convolution.patches", [=](const Ctx& cx) {
+            return mhlo_cuda_im2col(dt, bind(dx, cx).base, const_cast<void*>(bind(dcols, cx).base), pitch, &c, cx.stream);
+        });
+        // the kernel as [spatial.., input feature, output feature], then as the matrix [Kc, O]
+        View wc = w;
+        wc.type.shape.clear();
+        wc.strides.clear();
+        for (int d = 0; d < ns; ++d) { wc.type.shape.push_back(c.kernel_size[d]); wc.strides.push_back(c.kernel_spatial_stride[d]); }
+        wc.type.shape.push_back(Cg);
+        wc.strides.push_back(c.kernel_in_stride);
+        wc.type.shape.push_back(c.out_features);
+        wc.strides.push_back(c.kernel_out_stride);
+        View wm = wc;
+        if (!reshape_view(wc, {Kc, c.out_features}, &wm)) {
+            wc = materialize(wc, "convolution.kernel");
+            wm = wc;
+            if (!reshape_view(wc, {Kc, c.out_features}, &wm)) fail_compile("internal: dense kernel did not reshape");
+        }
+        wm.type.shape = {Kc, c.out_features};
+        DevView dwm = dev(wm);
+        keep_alive(wm);
+        TensorType prod_t;
+        prod_t.dtype = rt.dtype;
+        prod_t.shape = {G, M, Og};
+        View prod = dense_view(new_arena(prod_t.bytes()), prod_t);
+        DevView dprod = dev(prod);
+        keep_alive(cols);
+        keep_alive(prod);
+        std::array<int64_t, 4> as = {0, M * pitch, pitch, 1}, bs = {0, Og * wm.strides[1], wm.strides[0], wm.strides[1]};
+        add_step("convolution.gemm", [=](const Ctx& cx) {
+            return mhlo_cuda_gemm(dt, dt, bind(dcols, cx).base, as.data(), bind(dwm, cx).base, bs.data(), const_cast<void*>(bind(dprod, cx).base), 1, G,
+                                  M, Og, Kc, nullptr, MHLO_EPILOGUE_NONE, cx.stream);
+        });
+        // [G, batch, spatial.., Og] -> canonical [batch, spatial.., O] -> the result's own dimension order
+        View canon = prod;
+        canon.type.shape.clear();
+        canon.strides.clear();
+        canon.type.shape.push_back(c.batch);
+        canon.strides.push_back(out_positions * Og);
+        int64_t inner = out_positions;
+        for (int d = 0; d < ns; ++d) {
+            inner /= std::max<int64_t>(1, c.out_size[d]);
+            canon.type.shape.push_back(c.out_size[d]);
+            canon.strides.push_back(inner * Og);
+        }
+        if (G == 1) {
+            canon.type.shape.push_back(Og);
+            canon.strides.push_back(1);
+        } else {
+            canon.type.shape.push_back(G);
+            canon.strides.push_back(M * Og);
+            canon.type.shape.push_back(Og);
+            canon.strides.push_back(1);
+            View dense = dense_view(new_arena(rt.bytes()), canon.type);
+            copy_view(canon, dense, "convolution.groups");
+            canon = dense;
+            std::vector<int64_t> merged(canon.type.shape.begin(), canon.type.shape.end() - 2);
+            merged.push_back(c.out_features);
+            canon.type.shape = merged;
+            canon.strides = dense_strides(merged);
+        }
+        View out = canon;
+        out.type = rt;
+        out.strides.assign(static_cast<size_t>(rank), 0);
+        out.strides[ob] = canon.strides[0];
+        for (int d = 0; d < ns; ++d) out.strides[static_cast<size_t>(osp[d])] = canon.strides[static_cast<size_t>(d) + 1];
+        out.strides[ofd] = canon.strides[static_cast<size_t>(ns) + 1];
+        set(op.results[0], out);
     }
 
     // stablehlo.reduce_window of one operand with a recognised reducer; the operand is read through its view.

@@ -471,6 +471,11 @@ class Parser {
             size_t save = p_;
             ++p_;
             skip();
+            if (tag == "stablehlo.conv" && cur() == '[') {
+                Attr a = conv_dimension_spec();
+                expect('>');
+                return a;
+            }
             // enum form: "<comparison_direction GT>" / "<precision DEFAULT>"
             if (ident_char(cur())) {
                 size_t q = p_;
@@ -534,6 +539,45 @@ class Parser {
         }
         error("unsupported attribute syntax");
     }
+    // Convolution layout "[b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f]" (input x kernel -> output; b = batch, f = feature,
+    // i / o = kernel input / output feature, k = spatial dimension k) as a dictionary of the nine dimension attributes.
+    Attr conv_dimension_spec() {
+        Attr d;
+        d.kind = Attr::Dict;
+        auto side = [&](const char* batch_key, char batch_c, const char* feature_key, char feature_c, const char* spatial_key) {
+            skip();
+            expect('[');
+            std::map<int64_t, int64_t> spatial;
+            int64_t pos = 0;
+            skip();
+            while (cur() != ']') {
+                if (std::isdigit(static_cast<unsigned char>(cur()))) {
+                    spatial[number().i] = pos;
+                } else {
+                    const std::string w = ident();
+                    if (w.size() != 1 || (w[0] != batch_c && w[0] != feature_c)) error("unexpected '" + w + "' in a convolution layout");
+                    d.dict[w[0] == batch_c ? batch_key : feature_key] = Attr::make_int(pos);
+                }
+                ++pos;
+                if (!accept(',')) break;
+                skip();
+            }
+            expect(']');
+            std::vector<int64_t> sp;
+            for (const auto& kv : spatial) sp.push_back(kv.second);
+            d.dict[spatial_key] = Attr::make_ints(sp);
+        };
+        side("input_batch_dimension", 'b', "input_feature_dimension", 'f', "input_spatial_dimensions");
+        skip();
+        if (cur() != 'x') error("expected 'x' in a convolution layout");
+        ++p_;
+        side("kernel_input_feature_dimension", 'i', "kernel_output_feature_dimension", 'o', "kernel_spatial_dimensions");
+        skip();
+        if (!accept_str("->")) error("expected '->' in a convolution layout");
+        side("output_batch_dimension", 'b', "output_feature_dimension", 'f', "output_spatial_dimensions");
+        return d;
+    }
+
     void maybe_type_suffix() {  // "1 : i64", "1.0 : f32", "0 : index"; a tensor type after ':' belongs to the op
         size_t save = p_;
         skip();
@@ -937,7 +981,7 @@ class Parser {
                 continue;
             }
             if (c == '(') {  // reducer(...) block header of the pretty reduce with a region, or call operands
-                if (op->name == "call") { ++p_; operand_list(op, ')'); continue; }
+                if (op->name == "call" || op->name == "convolution") { ++p_; operand_list(op, ')'); continue; }
                 skip_balanced('(', ')');
                 continue;
             }
@@ -968,6 +1012,10 @@ class Parser {
                     ++p_;
                     skip();
                     // "batching_dims = [0] x [0]" style pairs
+                    if (w == "dim_numbers") {  // [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f]
+                        op->attrs["dimension_numbers"] = conv_dimension_spec();
+                        continue;
+                    }
                     Attr v = attr_value();
                     skip();
                     if (cur() == 'x' && !ident_char(at(1))) {
@@ -1145,6 +1193,7 @@ class Parser {
             }
             op->attrs["sort_order"] = Attr::make_string(order);
         }
+        if (n == "convolution") normalise_convolution(op);
         if (n == "dynamic_slice") { rename("sizes", "slice_sizes"); }
         if (n == "pad") { rename("low", "edge_padding_low"); rename("high", "edge_padding_high"); rename("interior", "interior_padding"); }
         if (n == "custom_call") {
@@ -1154,6 +1203,68 @@ class Parser {
         if (n == "select" && op->result_types.size() == 1 && !op->operands.empty()) {
             // "tensor<i1>, tensor<f32>" was parsed as a bare list: result = last, already handled
         }
+    }
+
+    // Flattens [[a, b], [c, d]] (Array of IntArray), dense<..> : tensor<Nx2xi64> or a flat list to a flat integer list.
+    static std::vector<int64_t> nested_ints(const Attr& a) {
+        if (a.kind != Attr::Array) return a.as_ints();
+        std::vector<int64_t> out;
+        for (const Attr& e : a.elems) {
+            std::vector<int64_t> part = e.kind == Attr::Bool ? std::vector<int64_t>{e.b ? 1 : 0} : nested_ints(e);
+            out.insert(out.end(), part.begin(), part.end());
+        }
+        return out;
+    }
+
+    // Canonical convolution attributes: the nine dimension numbers (default NHWC x HWIO -> NHWC, the layout of the
+    // short form "stablehlo.convolution %x, %w window_strides = [..], padding = [[..]]"), window_strides, padding
+    // (flat, rank x 2), lhs_dilation, rhs_dilation, window_reversal, feature_group_count, batch_group_count.
+    void normalise_convolution(Op* op) {
+        if (op->operands.size() != 2 || op->result_types.empty()) return;
+        const int rank = fn_->values[op->operands[0]].type.rank();
+        const int ns = rank - 2;
+        if (ns < 0) fail_parse("convolution of a tensor of rank " + std::to_string(rank));
+        if (const Attr* d = op->attr("dimension_numbers")) {
+            if (d->kind == Attr::Dict) {
+                const Attr dict = *d;
+                for (const auto& kv : dict.dict) op->attrs[kv.first] = kv.second.kind == Attr::Int ? kv.second : Attr::make_ints(nested_ints(kv.second));
+            }
+            op->attrs.erase("dimension_numbers");
+        }
+        if (const Attr* w = op->attr("window")) {
+            if (w->kind == Attr::Dict) {
+                const Attr dict = *w;
+                static const std::map<std::string, std::string> keys = {{"stride", "window_strides"}, {"pad", "padding"}, {"lhs_dilate", "lhs_dilation"},
+                                                                        {"rhs_dilate", "rhs_dilation"}, {"reverse", "window_reversal"}};
+                for (const auto& kv : dict.dict) {
+                    auto it = keys.find(kv.first);
+                    if (it == keys.end()) fail_parse("convolution: unknown window attribute '" + kv.first + "'");
+                    op->attrs[it->second] = Attr::make_ints(nested_ints(kv.second));
+                }
+            }
+            op->attrs.erase("window");
+        }
+        for (const char* k : {"window_strides", "padding", "lhs_dilation", "rhs_dilation", "window_reversal"})
+            if (const Attr* a = op->attr(k)) op->attrs[k] = Attr::make_ints(nested_ints(*a));
+        auto dflt_int = [&](const char* k, int64_t v) { if (!op->attr(k)) op->attrs[k] = Attr::make_int(v); };
+        auto dflt_list = [&](const char* k, int64_t first) {
+            if (op->attr(k)) return;
+            std::vector<int64_t> v;
+            for (int i = 0; i < ns; ++i) v.push_back(first + i);
+            op->attrs[k] = Attr::make_ints(v);
+        };
+        dflt_int("input_batch_dimension", 0);
+        dflt_int("input_feature_dimension", rank - 1);
+        dflt_list("input_spatial_dimensions", 1);
+        dflt_int("kernel_input_feature_dimension", rank - 2);
+        dflt_int("kernel_output_feature_dimension", rank - 1);
+        dflt_list("kernel_spatial_dimensions", 0);
+        dflt_int("output_batch_dimension", 0);
+        dflt_int("output_feature_dimension", rank - 1);
+        dflt_list("output_spatial_dimensions", 1);
+        dflt_int("feature_group_count", 1);
+        dflt_int("batch_group_count", 1);
+        op->attrs.erase("precision_config");
     }
 
     static std::string classify_reducer(const Region& r) {

@@ -51,6 +51,16 @@ class Window(C.Structure):
                 ("window_dilation", C.c_int64 * 8), ("pad_low", C.c_int64 * 8)]
 
 
+class Conv(C.Structure):
+    _fields_ = [("n_spatial", C.c_int32), ("reverse", C.c_int32 * 6), ("batch", C.c_int64), ("in_features", C.c_int64),
+                ("out_features", C.c_int64), ("feature_group_count", C.c_int64), ("batch_group_count", C.c_int64),
+                ("in_size", C.c_int64 * 6), ("kernel_size", C.c_int64 * 6), ("out_size", C.c_int64 * 6), ("stride", C.c_int64 * 6),
+                ("pad_low", C.c_int64 * 6), ("lhs_dilation", C.c_int64 * 6), ("rhs_dilation", C.c_int64 * 6),
+                ("in_batch_stride", C.c_int64), ("in_feature_stride", C.c_int64), ("in_spatial_stride", C.c_int64 * 6),
+                ("kernel_in_stride", C.c_int64), ("kernel_out_stride", C.c_int64), ("kernel_spatial_stride", C.c_int64 * 6),
+                ("out_batch_stride", C.c_int64), ("out_feature_stride", C.c_int64), ("out_spatial_stride", C.c_int64 * 6)]
+
+
 class ScatterDims(C.Structure):
     _fields_ = [("n_update_window_dims", C.c_int32), ("n_inserted_window_dims", C.c_int32), ("n_input_batching", C.c_int32),
                 ("n_scatter_dims_to_operand", C.c_int32), ("update_window_dims", C.c_int32 * 8),
@@ -112,6 +122,8 @@ _PROTOTYPES = {
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
                                    _vp, C.POINTER(_i64), _i32, _vp]),
+    "mhlo_cuda_convolution": (C.c_int, [_i32, _vp, _vp, _vp, C.POINTER(Conv), _vp]),
+    "mhlo_cuda_im2col": (C.c_int, [_i32, _vp, _vp, _i64, C.POINTER(Conv), _vp]),
     "mhlo_cuda_reduce_window": (C.c_int, [C.POINTER(View), C.POINTER(Window), _i32, _vp, _vp, C.POINTER(_i64), _vp]),
     "mhlo_cuda_scatter": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp, C.POINTER(_i64), _i32,
                                     C.POINTER(ScatterDims), _i32, _vp]),

@@ -477,6 +477,11 @@ class ModuleParser(Scanner):
             tag = self.ident()
             if self.peek() != "<":
                 return tag
+            if tag == "stablehlo.conv":
+                self.expect("<")
+                spec = self.conv_dimension_spec()
+                self.expect(">")
+                return spec
             save = self.p
             body = self.balanced("<", ">")
             if "=" not in body:
@@ -558,6 +563,32 @@ class ModuleParser(Scanner):
         self.expect(":")
         self.signature(op)
 
+    def conv_dimension_spec(self):
+        """'[b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f]' as the nine dimension attributes of stablehlo.convolution."""
+        out = {}
+
+        def side(batch_key, batch_c, feature_key, feature_c, spatial_key):
+            body = self.balanced("[", "]")
+            spatial = {}
+            for pos, tok in enumerate(t.strip() for t in body.split(",")):
+                if tok.isdigit():
+                    spatial[int(tok)] = pos
+                elif tok == batch_c:
+                    out[batch_key] = pos
+                elif tok == feature_c:
+                    out[feature_key] = pos
+                else:
+                    raise Unsupported(f"convolution layout token {tok!r}")
+            out[spatial_key] = [spatial[k] for k in sorted(spatial)]
+
+        self.ws()
+        side("input_batch_dimension", "b", "input_feature_dimension", "f", "input_spatial_dimensions")
+        self.expect("x")
+        side("kernel_input_feature_dimension", "i", "kernel_output_feature_dimension", "o", "kernel_spatial_dimensions")
+        self.expect("->")
+        side("output_batch_dimension", "b", "output_feature_dimension", "f", "output_spatial_dimensions")
+        return out
+
     def pretty(self, op):
         kw = []
         name = op.name.split(".")[-1]
@@ -624,6 +655,9 @@ class ModuleParser(Scanner):
                     op.attrs.update(start_indices=st, limit_indices=li, strides=sd)
                 else:
                     op.attrs["indices"] = [int(x) for x in body.split(",") if x.strip()]
+            elif c == "(" and name == "convolution":
+                self.p += 1
+                self.operands(op, ")")
             elif c == "(":
                 self.balanced("(", ")")
             elif self.peek(2) == "<{":
@@ -650,6 +684,8 @@ class ModuleParser(Scanner):
                         self.balanced("(", ")")
                     if self.peek() == "{":
                         op.regions.append(self.region())
+                elif w == "dim_numbers" and self.accept("="):
+                    op.attrs["dimension_numbers"] = self.conv_dimension_spec()
                 elif self.accept("="):
                     v = self.attr()
                     self.ws()
@@ -1263,6 +1299,89 @@ class Interpreter:
         raw = np.ascontiguousarray(a[0].astype(_storage_dtype(op.in_types[0].dtype)))
         out = (raw if raw.ndim else raw.reshape(1)).view(_storage_dtype(t.dtype)).reshape(t.shape)
         return out.astype(np.float64) if t.is_float else out
+
+    def op_convolution(self, op, a, t):
+        """stablehlo.convolution: the input is dilated and padded with zeros, and every output element is the dot
+        product of a (dilated, possibly reversed) kernel window with the input features of its group."""
+        A = op.attrs
+        lhs, rhs = a
+        rank = lhs.ndim
+        ns = rank - 2
+        d = dict(A.get("dimension_numbers") or {})
+        for k in ("input_batch_dimension", "input_feature_dimension", "input_spatial_dimensions", "kernel_input_feature_dimension",
+                  "kernel_output_feature_dimension", "kernel_spatial_dimensions", "output_batch_dimension", "output_feature_dimension",
+                  "output_spatial_dimensions"):
+            if k in A:
+                d[k] = A[k]
+        d.setdefault("input_batch_dimension", 0); d.setdefault("input_feature_dimension", rank - 1)
+        d.setdefault("input_spatial_dimensions", list(range(1, rank - 1)))
+        d.setdefault("kernel_input_feature_dimension", rank - 2); d.setdefault("kernel_output_feature_dimension", rank - 1)
+        d.setdefault("kernel_spatial_dimensions", list(range(0, rank - 2)))
+        d.setdefault("output_batch_dimension", 0); d.setdefault("output_feature_dimension", rank - 1)
+        d.setdefault("output_spatial_dimensions", list(range(1, rank - 1)))
+        win = A.get("window") or {}
+
+        def flat(v):
+            if v is None:
+                return None
+            if isinstance(v, tuple) and v and v[0] == "dense":
+                return [int(i) for i in np.asarray(dense_value(v[1], v[2])).reshape(-1)]
+            return [int(i) for i in np.asarray(v).reshape(-1)]
+
+        def pick(short, long, default):
+            v = flat(win.get(short)) if short in win else flat(A.get(long))
+            return v if v else default
+
+        stride = pick("stride", "window_strides", [1] * ns)
+        pad = pick("pad", "padding", [0] * (2 * ns))
+        ldil = pick("lhs_dilate", "lhs_dilation", [1] * ns)
+        rdil = pick("rhs_dilate", "rhs_dilation", [1] * ns)
+        rev = pick("reverse", "window_reversal", [0] * ns)
+        fgc = int(A.get("feature_group_count", 1))
+        bgc = int(A.get("batch_group_count", 1))
+        # canonical orders: input [B, spatial.., C], kernel [spatial.., I, O], output [B, spatial.., O]
+        x = np.transpose(lhs, [d["input_batch_dimension"]] + _ints(d["input_spatial_dimensions"]) + [d["input_feature_dimension"]])
+        w = np.transpose(rhs, _ints(d["kernel_spatial_dimensions"]) + [d["kernel_input_feature_dimension"], d["kernel_output_feature_dimension"]])
+        wide = np.float64 if x.dtype == np.float64 else (np.uint64 if x.dtype == np.uint64 else np.int64)
+        x, w = x.astype(wide), w.astype(wide)
+        for k in range(ns):
+            if rev[k]:
+                w = np.flip(w, axis=k)
+        B, C, O = x.shape[0], x.shape[-1], w.shape[-1]
+        dil_shape = [(n - 1) * l + 1 if n > 0 else 0 for n, l in zip(x.shape[1:-1], ldil)]
+        xd = np.zeros([B] + dil_shape + [C], dtype=wide)
+        xd[(slice(None),) + tuple(slice(None, None, l) for l in ldil)] = x
+        padded_shape = [max(0, n + pad[2 * k] + pad[2 * k + 1]) for k, n in enumerate(dil_shape)]
+        xp = np.zeros([B] + padded_shape + [C], dtype=wide)
+        src, dst = [slice(None)], [slice(None)]
+        for k, n in enumerate(dil_shape):
+            lo, hi = pad[2 * k], pad[2 * k + 1]
+            s0, s1 = max(0, -lo), n - max(0, -hi)
+            src.append(slice(s0, max(s0, s1)))
+            d0 = max(0, lo)
+            dst.append(slice(d0, d0 + max(0, s1 - s0)))
+        xp[tuple(dst)] = xd[tuple(src)]
+        out_sp = [t.shape[i] for i in _ints(d["output_spatial_dimensions"])]
+        Bo = B // bgc
+        out = np.zeros([Bo] + out_sp + [O], dtype=wide)
+        Cg, Og_f, Og_b = C // fgc, O // fgc, O // bgc
+        for kidx in np.ndindex(*w.shape[:-2]):
+            window = tuple(slice(kk * rd, kk * rd + (n - 1) * st + 1, st) if n > 0 else slice(0, 0)
+                           for kk, rd, st, n in zip(kidx, rdil, stride, out_sp))
+            patch = xp[(slice(None),) + window]  # [B, out spatial.., C]
+            wk = w[kidx]                          # [I, O]
+            for oc in range(O):
+                g, gb = oc // Og_f, oc // Og_b
+                xs = patch[gb * Bo:(gb + 1) * Bo, ..., g * Cg:(g + 1) * Cg]
+                with np.errstate(all="ignore"):
+                    out[..., oc] += xs @ wk[:, oc]
+        perm = [0] * rank
+        perm[d["output_batch_dimension"]] = 0
+        for k, od in enumerate(_ints(d["output_spatial_dimensions"])):
+            perm[od] = 1 + k
+        perm[d["output_feature_dimension"]] = rank - 1
+        res = np.transpose(out, perm)
+        return res if t.is_float else res.astype(t.np_dtype())
 
     def op_batch_norm_inference(self, op, a, t):
         x, scale, offset, mean, var = a

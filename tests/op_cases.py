@@ -650,4 +650,70 @@ def window_scatter_sort_cases():
     return out
 
 
-CASES = build_cases() + widening_cases() + window_scatter_sort_cases()
+def conv_case(name, x, w, dt, out_shape, layout="[b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f]", window="", fgc=1, bgc=1, form="pretty"):
+    """One stablehlo.convolution. form: "pretty" (what jax prints), "short" (the reference benchmarks' form, NHWC x HWIO
+    only) or "generic"."""
+    tx, tw, to = tt(x.shape, dt), tt(w.shape, dt), tt(out_shape, dt)
+    if form == "short":
+        body = f"    %0 = stablehlo.convolution %arg0, %arg1 {window}feature_group_count = {fgc} : ({tx}, {tw}) -> {to}"
+    elif form == "generic":
+        body = (f"    %0 = \"stablehlo.convolution\"(%arg0, %arg1) {{batch_group_count = {bgc} : i64, dimension_numbers = #stablehlo.conv<{layout}>, "
+                f"feature_group_count = {fgc} : i64{window}}} : ({tx}, {tw}) -> {to}")
+    else:
+        body = (f"    %0 = stablehlo.convolution(%arg0, %arg1) dim_numbers = {layout}, window = {{{window}}} "
+                f"{{batch_group_count = {bgc} : i64, feature_group_count = {fgc} : i64, precision_config = [#stablehlo<precision DEFAULT>, #stablehlo<precision DEFAULT>]}} "
+                f": ({tx}, {tw}) -> {to}")
+    return (name, func([tx, tw], [to], body, "%0"), [x, w])
+
+
+def convolution_cases():
+    rng = np.random.default_rng(31337)
+    out = []
+
+    def data(shape, dt, scale=1.0):
+        if dt in ("i32", "i8", "i64"):
+            return rng.integers(-4, 5, size=shape).astype(NP[dt])
+        return (scale * rng.standard_normal(shape)).astype(np.float32).astype(NP[dt])
+
+    same = "stride = [1, 1], pad = [[1, 1], [1, 1]], rhs_dilate = [1, 1]"
+    for dt in ("f32", "bf16", "f16"):
+        if dt not in NP:
+            continue
+        out.append(conv_case(f"conv_3x3_same_{dt}", data((2, 12, 12, 16), dt), data((3, 3, 16, 32), dt, 0.1), dt, (2, 12, 12, 32), window=same))
+        out.append(conv_case(f"conv_first_layer_rgb_{dt}", data((2, 16, 16, 3), dt), data((3, 3, 3, 32), dt, 0.2), dt, (2, 8, 8, 32),
+                             window="stride = [2, 2], pad = [[0, 1], [0, 1]]"))
+        out.append(conv_case(f"conv_1x1_{dt}", data((2, 9, 9, 24), dt), data((1, 1, 24, 16), dt, 0.2), dt, (2, 9, 9, 16)))
+    out.append(conv_case("conv_nchw_oihw_f32", data((2, 8, 10, 10), "f32"), data((16, 8, 3, 3), "f32", 0.1), "f32", (2, 16, 8, 8),
+                         layout="[b, f, 0, 1]x[o, i, 0, 1]->[b, f, 0, 1]"))
+    if "bf16" in NP:
+        out.append(conv_case("conv_nchw_oihw_bf16", data((2, 8, 10, 10), "bf16"), data((16, 8, 3, 3), "bf16", 0.1), "bf16", (2, 16, 8, 8),
+                             layout="[b, f, 0, 1]x[o, i, 0, 1]->[b, f, 0, 1]"))
+    out.append(conv_case("conv_dilated_kernel_f32", data((1, 11, 11, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (1, 7, 7, 8),
+                         window="rhs_dilate = [2, 2]"))
+    # the gradient-of-strided-convolution form: dilated input, negative-free padding of kernel - 1
+    out.append(conv_case("conv_transposed_f32", data((1, 5, 5, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (1, 11, 11, 8),
+                         window="pad = [[2, 2], [2, 2]], lhs_dilate = [2, 2]"))
+    out.append(conv_case("conv_reversed_window_f32", data((1, 8, 8, 4), "f32"), data((3, 2, 4, 8), "f32", 0.2), "f32", (1, 6, 7, 8),
+                         window="reverse = [true, false]"))
+    out.append(conv_case("conv_negative_padding_f32", data((1, 8, 8, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (1, 4, 5, 8),
+                         window="pad = [[-1, -1], [0, -1]]"))
+    out.append(conv_case("conv_feature_groups_2_f32", data((2, 8, 8, 8), "f32"), data((3, 3, 4, 16), "f32", 0.2), "f32", (2, 6, 6, 16), fgc=2))
+    if "bf16" in NP:
+        out.append(conv_case("conv_feature_groups_2_bf16", data((2, 8, 8, 16), "bf16"), data((3, 3, 8, 32), "bf16", 0.1), "bf16", (2, 6, 6, 32), fgc=2))
+    out.append(conv_case("conv_depthwise_f32", data((2, 8, 8, 6), "f32"), data((3, 3, 1, 6), "f32", 0.3), "f32", (2, 6, 6, 6), fgc=6))
+    out.append(conv_case("conv_batch_groups_2_f32", data((4, 6, 6, 3), "f32"), data((2, 2, 3, 4), "f32", 0.3), "f32", (2, 5, 5, 4), bgc=2))
+    out.append(conv_case("conv_1d_f32", data((3, 20, 5), "f32"), data((4, 5, 7), "f32", 0.3), "f32", (3, 9, 7),
+                         layout="[b, 0, f]x[0, i, o]->[b, 0, f]", window="stride = [2]"))
+    out.append(conv_case("conv_3d_f32", data((1, 5, 6, 7, 2), "f32"), data((2, 3, 2, 2, 4), "f32", 0.3), "f32", (1, 4, 4, 6, 4),
+                         layout="[b, 0, 1, 2, f]x[0, 1, 2, i, o]->[b, 0, 1, 2, f]"))
+    out.append(conv_case("conv_i32", data((1, 6, 6, 2), "i32"), data((3, 3, 2, 3), "i32"), "i32", (1, 4, 4, 3)))
+    out.append(conv_case("conv_mixed_layouts_f32", data((6, 6, 2, 5), "f32"), data((3, 4, 3, 5), "f32", 0.3), "f32", (4, 2, 4, 4),
+                         layout="[0, 1, b, f]x[0, o, 1, i]->[0, b, f, 1]"))
+    out.append(conv_case("conv_short_form_f32", data((2, 8, 8, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (2, 8, 8, 8),
+                         window="window_strides = [1, 1], padding = [[1, 1], [1, 1]], ", form="short"))
+    out.append(conv_case("conv_generic_form_f32", data((2, 8, 8, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (2, 4, 4, 8),
+                         window=", padding = dense<[[1, 1], [1, 1]]> : tensor<2x2xi64>, window_strides = array<i64: 2, 2>", form="generic"))
+    return out
+
+
+CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases()

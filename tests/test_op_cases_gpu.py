@@ -46,3 +46,20 @@ def test_case_matches_oracle(name, level):
             if name.startswith(("power", "tan_", "atan2")) and tag == "f32":
                 rel = 4e-5  # pow/atan2 on the device are accurate to a few ulp of fp32, relative to larger intermediates
             assert_close(g.astype(np.float64), w, rel, f"{name} O{level}")
+
+
+@pytest.mark.parametrize("name", [c[0] for c in CASES if c[0].startswith("conv_")])
+def test_convolution_direct_kernel_matches_oracle(name, monkeypatch):
+    """Every convolution case again through the direct kernel (METALHLO_CONV_DIRECT=1 is read when the module is lowered)."""
+    monkeypatch.setenv("METALHLO_CONV_DIRECT", "1")
+    _, text, inputs = next(c for c in CASES if c[0] == name)
+    want = interp.evaluate(text, inputs)
+    exe = client().compile(text, opt_level=2, caching=False)
+    assert "convolution" in exe.steps()
+    got = [o.to_numpy() for o in exe.execute([client().buffer(x) for x in inputs])]
+    for g, w in zip(got, want):
+        tag = dtype_tag(g)
+        if tag is None:
+            np.testing.assert_array_equal(g, w.astype(g.dtype), err_msg=name)
+        else:
+            assert_close(g.astype(np.float64), w, REL[tag], name)

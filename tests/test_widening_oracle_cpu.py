@@ -111,3 +111,45 @@ def test_branches_pick_one_region():
     for v, f in ((0, np.negative), (1, np.tanh), (2, np.abs), (7, np.abs), (-3, np.abs)):
         (got,), (_, x) = run(f"case_index_{v}".replace("-", "m"))
         np.testing.assert_allclose(got, f(x.astype(np.float64)), rtol=1e-6)
+
+
+def _torch_conv(x_nhwc, w_hwio, **kw):
+    import torch
+
+    x = torch.from_numpy(np.ascontiguousarray(x_nhwc.astype(np.float64))).permute(0, 3, 1, 2)
+    w = torch.from_numpy(np.ascontiguousarray(w_hwio.astype(np.float64))).permute(3, 2, 0, 1)
+    return torch.nn.functional.conv2d(x, w, **kw).permute(0, 2, 3, 1).numpy()
+
+
+def test_convolution_matches_torch_conv2d():
+    (got,), (x, w) = run("conv_3x3_same_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, padding=1), rtol=1e-9, atol=1e-9)
+    (got,), (x, w) = run("conv_dilated_kernel_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, dilation=2), rtol=1e-9, atol=1e-9)
+    (got,), (x, w) = run("conv_feature_groups_2_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, groups=2), rtol=1e-9, atol=1e-9)
+    (got,), (x, w) = run("conv_depthwise_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, groups=6), rtol=1e-9, atol=1e-9)
+    (got,), (x, w) = run("conv_short_form_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, padding=1), rtol=1e-9, atol=1e-9)
+    (got,), (x, w) = run("conv_generic_form_f32")
+    np.testing.assert_allclose(got, _torch_conv(x, w, padding=1, stride=2), rtol=1e-9, atol=1e-9)
+
+
+def test_nchw_convolution_matches_torch_conv2d():
+    import torch
+
+    (got,), (x, w) = run("conv_nchw_oihw_f32")
+    want = torch.nn.functional.conv2d(torch.from_numpy(x.astype(np.float64)), torch.from_numpy(w.astype(np.float64))).numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-9, atol=1e-9)
+
+
+def test_transposed_convolution_matches_torch_conv_transpose2d():
+    import torch
+
+    (got,), (x, w) = run("conv_transposed_f32")
+    xt = torch.from_numpy(x.astype(np.float64)).permute(0, 3, 1, 2)
+    # conv_transpose2d correlates with the flipped kernel: flip it back to express the plain dilated-input convolution
+    wt = torch.from_numpy(np.ascontiguousarray(w[::-1, ::-1].astype(np.float64))).permute(2, 3, 0, 1)
+    want = torch.nn.functional.conv_transpose2d(xt, wt, stride=2).permute(0, 2, 3, 1).numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-9, atol=1e-9)
