@@ -1227,6 +1227,43 @@ int mhlo_cuda_gather(const void* operand_dev, int32_t elem_size, const int64_t* 
     if (dims->n_offset_dims > MHLO_CUDA_MAX_RANK || dims->n_collapsed > MHLO_CUDA_MAX_RANK ||
         dims->n_operand_batching > MHLO_CUDA_MAX_RANK || dims->n_start_index_map > MHLO_CUDA_MAX_RANK)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: dimension-number list too long");
+    {   // the dimension numbers must account for every output and operand dimension, or the kernel would index outside
+        const bool has_ivd = dims->index_vector_dim < indices_rank;
+        if (dims->index_vector_dim < 0 || dims->index_vector_dim > indices_rank)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: index_vector_dim %d for indices of rank %d", dims->index_vector_dim, indices_rank);
+        if (dims->n_offset_dims + dims->n_collapsed + dims->n_operand_batching != operand_rank)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: offset, collapsed and batching dimensions do not cover the operand's rank %d", operand_rank);
+        if (out_rank != dims->n_offset_dims + indices_rank - (has_ivd ? 1 : 0))
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: result rank %d does not match %d offset + %d batch dimensions", out_rank,
+                        dims->n_offset_dims, indices_rank - (has_ivd ? 1 : 0));
+        const int64_t index_len = has_ivd ? indices_shape[dims->index_vector_dim] : 1;
+        if (dims->n_start_index_map > index_len)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: start_index_map has %d entries, index vectors have %lld", dims->n_start_index_map,
+                        static_cast<long long>(index_len));
+        for (int k = 0; k < dims->n_offset_dims; ++k)
+            if (dims->offset_dims[k] < 0 || dims->offset_dims[k] >= out_rank)
+                return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: offset_dims entry out of range");
+        int oi = 0;  // the offset dimensions of the result walk the slice: their extents must be the slice sizes
+        for (int d = 0; d < operand_rank; ++d) {
+            bool skip = false;
+            for (int k = 0; k < dims->n_collapsed; ++k) skip |= dims->collapsed_slice_dims[k] == d;
+            for (int k = 0; k < dims->n_operand_batching; ++k) skip |= dims->operand_batching_dims[k] == d;
+            if (skip) continue;
+            if (oi >= dims->n_offset_dims || out_shape[dims->offset_dims[oi]] != dims->slice_sizes[d])
+                return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: the result's offset dimensions do not match slice_sizes (operand dimension %d)", d);
+            ++oi;
+        }
+        int bi = 0;  // the batch dimensions of the result walk `indices`: their extents must agree
+        for (int d = 0; d < out_rank; ++d) {
+            bool is_off = false;
+            for (int k = 0; k < dims->n_offset_dims; ++k) is_off |= dims->offset_dims[k] == d;
+            if (is_off) continue;
+            if (has_ivd && bi == dims->index_vector_dim) ++bi;
+            if (bi >= indices_rank || out_shape[d] != indices_shape[bi])
+                return fail(MHLO_CUDA_INVALID_ARGUMENT, "gather: dimension %d of the result does not match the start indices", d);
+            ++bi;
+        }
+    }
     GatherParams p;
     memset(&p, 0, sizeof p);
     p.d = *dims;

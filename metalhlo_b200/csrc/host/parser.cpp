@@ -1162,8 +1162,8 @@ class Parser {
                                   "rhs_contracting_dimensions"})
                 if (!op->attr(k)) op->attrs[k] = Attr::make_ints({});
         }
-        if (n == "gather" || n == "scatter") {
-            const char* key = n == "gather" ? "dimension_numbers" : "scatter_dimension_numbers";
+        if (n == "gather" || n == "dynamic_gather" || n == "scatter") {
+            const char* key = n == "scatter" ? "scatter_dimension_numbers" : "dimension_numbers";
             if (const Attr* d = op->attr(key))
                 for (const auto& kv : d->dict) op->attrs[kv.first] = kv.second.kind == Attr::Int || kv.second.kind == Attr::IntArray || kv.second.kind == Attr::Array ? (kv.second.kind == Attr::Int ? kv.second : Attr::make_ints(kv.second.as_ints())) : kv.second;
         }

@@ -491,6 +491,26 @@ extern "C" int mhlo_cuda_scatter(void* result_inout_dev, int32_t dtype, const in
     for (int k = 0; k < dims->n_scatter_dims_to_operand; ++k)
         if (dims->scatter_dims_to_operand_dims[k] < 0 || dims->scatter_dims_to_operand_dims[k] >= operand_rank)
             return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: scatter_dims_to_operand_dims entry out of range");
+    {   // the scatter dimensions of `updates` walk `indices`: their extents must agree, or the index reads would leave it
+        int bi = 0;
+        for (int d = 0; d < updates_rank; ++d) {
+            bool is_win = false;
+            for (int k = 0; k < dims->n_update_window_dims; ++k) is_win |= dims->update_window_dims[k] == d;
+            if (is_win) continue;
+            if (has_ivd && bi == dims->index_vector_dim) ++bi;
+            if (bi >= indices_rank || updates_shape[d] != indices_shape[bi])
+                return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: dimension %d of the updates does not match the scatter indices", d);
+            ++bi;
+        }
+        const int64_t index_len = has_ivd ? indices_shape[dims->index_vector_dim] : 1;
+        if (dims->n_scatter_dims_to_operand > index_len)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: scatter_dims_to_operand_dims has %d entries, index vectors have %lld",
+                        dims->n_scatter_dims_to_operand, static_cast<long long>(index_len));
+        for (int k = 0; k < dims->n_input_batching; ++k)
+            if (dims->input_batching_dims[k] < 0 || dims->input_batching_dims[k] >= operand_rank || dims->scatter_indices_batching_dims[k] < 0 ||
+                dims->scatter_indices_batching_dims[k] >= indices_rank)
+                return fail(MHLO_CUDA_INVALID_ARGUMENT, "scatter: batching dimension out of range");
+    }
     ScatterParams p;
     memset(&p, 0, sizeof p);
     p.d = *dims;

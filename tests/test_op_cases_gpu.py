@@ -55,7 +55,7 @@ def test_convolution_direct_kernel_matches_oracle(name, monkeypatch):
     _, text, inputs = next(c for c in CASES if c[0] == name)
     want = interp.evaluate(text, inputs)
     exe = client().compile(text, opt_level=2, caching=False)
-    assert "convolution" in exe.steps()
+    assert "convolution" in exe.steps
     got = [o.to_numpy() for o in exe.execute([client().buffer(x) for x in inputs])]
     for g, w in zip(got, want):
         tag = dtype_tag(g)
