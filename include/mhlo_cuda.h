@@ -212,6 +212,7 @@ enum {
     MHLO_EW_GELU_TANH, MHLO_EW_GELU_ERF, MHLO_EW_SILU, MHLO_EW_RELU,
     MHLO_EW_ROUND_TO,  /* r = a rounded to the float dtype (int)imm and widened again: keeps the unfused rounding
                           points of a fused chain */
+    MHLO_EW_ERF,       /* chlo.erf */
     MHLO_EW_OP_COUNT
 };
 

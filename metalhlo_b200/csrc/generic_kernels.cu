@@ -132,6 +132,7 @@ __device__ __forceinline__ C ew_float_op(int op, C a, C b, C c, double imm) {
             if (dt == MHLO_DT_F32) return C(static_cast<float>(a));
             return a;
         }
+        case MHLO_EW_ERF: return erf(a);
         default: return a;
     }
 }

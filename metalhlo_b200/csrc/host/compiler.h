@@ -45,7 +45,9 @@ bool inline_calls(Module& m);
 bool unroll_static_whiles(Function& f);
 // Replaces stablehlo.if / stablehlo.case by their branches, all computed, and `select`s on the selector.
 bool flatten_conditionals(Function& f);
-// All three, repeated until none applies; returns the flattened @main.
+// Replaces stablehlo.map by its computation applied to whole tensors.
+bool flatten_maps(Function& f);
+// All four, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
 
 // ---- memory plan -----------------------------------------------------------------------------------------------

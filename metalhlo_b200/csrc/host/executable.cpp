@@ -189,6 +189,7 @@ int ew_opcode(const std::string& n) {
         {"count_leading_zeros", MHLO_EW_CLZ}, {"convert", MHLO_EW_COPY}, {"select", MHLO_EW_SELECT},
         {"clamp", MHLO_EW_CLAMP}, {"copy", MHLO_EW_COPY}, {"optimization_barrier", MHLO_EW_COPY},
         {"gelu_tanh", MHLO_EW_GELU_TANH}, {"gelu_erf", MHLO_EW_GELU_ERF}, {"silu", MHLO_EW_SILU}, {"relu", MHLO_EW_RELU},
+        {"erf", MHLO_EW_ERF},
     };
     auto it = table.find(n);
     return it == table.end() ? -1 : it->second;
@@ -447,6 +448,13 @@ class Lowering {
             return lower_gather(g);
         }
         if (n == "batch_norm_inference") return lower_batch_norm_inference(op);
+        if (n == "get_dimension_size") {  // shapes are static: the extent is a constant
+            const View& x = get(op.operands[0]);
+            const int64_t d = op.int_attr("dimension", 0);
+            if (d < 0 || d >= x.type.rank()) fail_compile("get_dimension_size: dimension out of range");
+            std::vector<mhlo_cuda_ew_inst> prog = {{MHLO_EW_IMM, 0, 0, 0, static_cast<double>(x.type.shape[static_cast<size_t>(d)])}};
+            return set(op.results[0], emit_elementwise({}, prog, rt, "get_dimension_size"));
+        }
         if (n == "transpose") {
             const View& x = get(op.operands[0]);
             std::vector<int64_t> perm = op.int_list("permutation");

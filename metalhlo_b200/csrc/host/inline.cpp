@@ -11,6 +11,9 @@
 #include "compiler.h"
 
 namespace mhlo {
+
+int elementwise_opcode(const std::string& name);  // executable.cpp
+
 namespace {
 
 constexpr int kMaxInlineRounds = 64;     // nesting depth of calls
@@ -352,13 +355,75 @@ bool flatten_conditionals(Function& f) {
     return changed;
 }
 
+// stablehlo.map applies a scalar computation to every element: its body becomes the same ops on whole tensors. The
+// dimensions attribute must list every dimension in order (the only form the specification allows).
+bool flatten_maps(Function& f) {
+    bool changed = false;
+    for (int round = 0; round < kMaxInlineRounds; ++round) {
+        bool any = false;
+        std::vector<Op> out;
+        std::map<int, int> alias;
+        for (Op& op : f.ops) {
+            apply_alias(op, alias);
+            if (op.dead || op.name != "map") {
+                out.push_back(std::move(op));
+                continue;
+            }
+            if (op.regions.size() != 1 || op.results.size() != 1 || op.regions[0]->args.size() != op.operands.size())
+                fail_compile("stablehlo.map: one computation with one argument per operand expected");
+            const std::vector<int64_t> shape = op.result_types[0].shape;
+            const Region& body = *op.regions[0];
+            Cloner c{f, f, true, {}};
+            for (size_t i = 0; i < body.args.size(); ++i) c.map[body.args[i]] = op.operands[i];
+            int result = -1;
+            for (const Op& bo : body.ops) {
+                if (bo.name == "return") {
+                    if (bo.operands.size() != 1) fail_compile("stablehlo.map: the computation must return one value");
+                    result = c.remap(bo.operands[0]);
+                    break;
+                }
+                if (!bo.regions.empty()) fail_unsupported("stablehlo.map: nested regions in the computation");
+                Op lifted = c.clone(bo);
+                // scalars computed from the arguments become tensors of the map's shape; constants stay scalars and
+                // broadcast where they are used
+                bool from_args = false;
+                for (int v : lifted.operands) from_args |= f.values[v].type.shape == shape && !shape.empty();
+                if (from_args) {
+                    if (elementwise_opcode(lifted.name) < 0 && lifted.name != "compare")
+                        fail_unsupported("stablehlo.map: " + lifted.name + " in the computation is not elementwise");
+                    for (size_t r = 0; r < lifted.results.size(); ++r) {
+                        lifted.result_types[r].shape = shape;
+                        f.values[lifted.results[r]].type.shape = shape;
+                    }
+                }
+                out.push_back(lifted);
+            }
+            if (result < 0) fail_compile("stablehlo.map: the computation does not return");
+            if (f.values[result].type.shape != shape) {  // the body ignored its arguments: broadcast the scalar
+                Op b = simple_op(f, "broadcast_in_dim", {result}, op.result_types[0]);
+                b.attrs["broadcast_dimensions"] = Attr::make_ints({});
+                result = b.results[0];
+                out.push_back(b);
+            }
+            alias[op.results[0]] = result;
+            any = true;
+        }
+        f.ops.swap(out);
+        f.compact();
+        if (!any) break;
+        changed = true;
+    }
+    return changed;
+}
+
 Function flatten_main(Module& m) {
     // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat until neither changes
     for (int round = 0; round < kMaxInlineRounds; ++round) {
         const bool a = inline_calls(m);
         const bool b = unroll_static_whiles(m.main());
         const bool c = flatten_conditionals(m.main());
-        if (!a && !b && !c) break;
+        const bool d = flatten_maps(m.main());
+        if (!a && !b && !c && !d) break;
     }
     return m.main();
 }

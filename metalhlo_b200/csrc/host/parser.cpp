@@ -1121,7 +1121,7 @@ class Parser {
             rename("dims", n == "broadcast_in_dim" ? "broadcast_dimensions" : (n == "transpose" ? "permutation" : "dimensions"));
             rename("dimensions", n == "broadcast_in_dim" ? "broadcast_dimensions" : (n == "transpose" ? "permutation" : "dimensions"));
         }
-        if (n == "concatenate") { rename("dim", "dimension"); }
+        if (n == "concatenate" || n == "get_dimension_size") { rename("dim", "dimension"); }
         if (n == "iota") { rename("dim", "iota_dimension"); rename("dimension", "iota_dimension"); }
         if (n == "reduce") {
             rename("dims", "dimensions");

@@ -256,3 +256,99 @@ def gpt2_module(batch: int = 32, seq: int = 1024, layers: int = 12, d_model: int
     emit(f"{logits} = stablehlo.dot_general {xf}, {wte}, contracting_dims = [2] x [1] : ({t_act}, {tt((vocab, d_model), dt)}) -> {t_logits}")
     text = func([tt(s, d) for _, s, d in params], [t_logits], "\n".join(lines), logits)
     return text, params
+
+
+def cnn_module(batch: int = 8, size: int = 32, channels: int = 3, width: int = 32, classes: int = 10, dt: str = "bf16", eps: float = 1e-5):
+    """A small residual CNN forward pass in the op forms `jax.jit` prints for a flax model (NHWC, HWIO): 3x3 stem
+    convolution with stride 2, one residual block of two 3x3 convolutions with batch-norm inference and ReLU, 2x2 max
+    pooling (reduce_window), global average pooling (reduce) and a dense classifier. Parameters arrive as fp32 and are
+    converted to `dt` inside the module.
+
+    Returns (text, parameter list [(name, shape, dtype)] in argument order); the result is [batch, classes] logits in `dt`.
+    """
+    half = size // 2
+    params = [("image", (batch, size, size, channels), "f32"), ("stem_w", (3, 3, channels, width), "f32")]
+    for i in (1, 2):
+        params += [(f"conv{i}_w", (3, 3, width, width), "f32"), (f"bn{i}_scale", (width,), "f32"), (f"bn{i}_offset", (width,), "f32"),
+                   (f"bn{i}_mean", (width,), "f32"), (f"bn{i}_var", (width,), "f32")]
+    params += [("dense_w", (width, classes), "f32"), ("dense_b", (classes,), "f32")]
+    arg = {name: f"%arg{i}" for i, (name, _, _) in enumerate(params)}
+    shape = {name: s for name, s, _ in params}
+    lines = []
+    n = [0]
+
+    def fresh():
+        n[0] += 1
+        return f"%c{n[0]}"
+
+    def emit(line):
+        lines.append("    " + line)
+
+    def cvt(name):
+        if dt == "f32":
+            return arg[name]
+        v = fresh()
+        emit(f"{v} = stablehlo.convert {arg[name]} : ({tt(shape[name], 'f32')}) -> {tt(shape[name], dt)}")
+        return v
+
+    def conv(x, xs, w, ws, stride, out_hw):
+        v = fresh()
+        os_ = (xs[0], out_hw, out_hw, ws[3])
+        pad = "[[0, 1], [0, 1]]" if stride == 2 else "[[1, 1], [1, 1]]"
+        emit(f"{v} = stablehlo.convolution({x}, {w}) dim_numbers = [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f], "
+             f"window = {{stride = [{stride}, {stride}], pad = {pad}}} {{batch_group_count = 1 : i64, feature_group_count = 1 : i64}} "
+             f": ({tt(xs, dt)}, {tt(ws, dt)}) -> {tt(os_, dt)}")
+        return v, os_
+
+    def bn(x, xs, i):
+        v = fresh()
+        stats = ", ".join(cvt(f"bn{i}_{k}") for k in ("scale", "offset", "mean", "var"))
+        tc = tt((xs[3],), dt)
+        emit(f"{v} = \"stablehlo.batch_norm_inference\"({x}, {stats}) <{{epsilon = {eps:e} : f32, feature_index = 3 : i64}}> "
+             f": ({tt(xs, dt)}, {tc}, {tc}, {tc}, {tc}) -> {tt(xs, dt)}")
+        return v
+
+    def relu(x, xs):
+        z, b, v = fresh(), fresh(), fresh()
+        emit(f"{z} = stablehlo.constant dense<0.000000e+00> : tensor<{dt}>")
+        emit(f"{b} = stablehlo.broadcast_in_dim {z}, dims = [] : (tensor<{dt}>) -> {tt(xs, dt)}")
+        emit(f"{v} = stablehlo.maximum {x}, {b} : {tt(xs, dt)}")
+        return v
+
+    x, xs = cvt("image"), shape["image"]
+    x, xs = conv(x, xs, cvt("stem_w"), shape["stem_w"], 2, half)
+    x = relu(x, xs)
+    skip = x
+    for i in (1, 2):
+        x, xs = conv(x, xs, cvt(f"conv{i}_w"), shape[f"conv{i}_w"], 1, half)
+        x = bn(x, xs, i)
+        if i == 2:
+            s = fresh()
+            emit(f"{s} = stablehlo.add {x}, {skip} : {tt(xs, dt)}")
+            x = s
+        x = relu(x, xs)
+    ninf = {"f32": "0xFF800000", "f16": "0xFC00", "bf16": "0xFF80"}[dt]
+    init, pooled = fresh(), fresh()
+    ps = (xs[0], half // 2, half // 2, xs[3])
+    emit(f"{init} = stablehlo.constant dense<{ninf}> : tensor<{dt}>")
+    emit(f"{pooled} = \"stablehlo.reduce_window\"({x}, {init}) <{{window_dimensions = array<i64: 1, 2, 2, 1>, window_strides = array<i64: 1, 2, 2, 1>}}> ({{")
+    emit(f"^bb0(%a: tensor<{dt}>, %b: tensor<{dt}>):")
+    emit(f"  %m = stablehlo.maximum %a, %b : tensor<{dt}>")
+    emit(f"  stablehlo.return %m : tensor<{dt}>")
+    emit(f"}}) : ({tt(xs, dt)}, tensor<{dt}>) -> {tt(ps, dt)}")
+    zero, summed, cnt, cb, mean = fresh(), fresh(), fresh(), fresh(), fresh()
+    fs = (ps[0], ps[3])
+    emit(f"{zero} = stablehlo.constant dense<0.000000e+00> : tensor<{dt}>")
+    emit(f"{summed} = stablehlo.reduce({pooled} init: {zero}) applies stablehlo.add across dimensions = [1, 2] : ({tt(ps, dt)}, tensor<{dt}>) -> {tt(fs, dt)}")
+    emit(f"{cnt} = stablehlo.constant dense<{float(ps[1] * ps[2]):e}> : tensor<{dt}>")
+    emit(f"{cb} = stablehlo.broadcast_in_dim {cnt}, dims = [] : (tensor<{dt}>) -> {tt(fs, dt)}")
+    emit(f"{mean} = stablehlo.divide {summed}, {cb} : {tt(fs, dt)}")
+    logits, bb, res = fresh(), fresh(), fresh()
+    ls = (fs[0], classes)
+    emit(f"{logits} = stablehlo.dot_general {mean}, {cvt('dense_w')}, contracting_dims = [1] x [0] : ({tt(fs, dt)}, {tt(shape['dense_w'], dt)}) -> {tt(ls, dt)}")
+    emit(f"{bb} = stablehlo.broadcast_in_dim {cvt('dense_b')}, dims = [1] : ({tt((classes,), dt)}) -> {tt(ls, dt)}")
+    emit(f"{res} = stablehlo.add {logits}, {bb} : {tt(ls, dt)}")
+    sig = ", ".join(f"%arg{i}: {tt(s, d)}" for i, (_, s, d) in enumerate(params))
+    text = (f"module @jit_cnn {{\n  func.func public @main({sig}) -> ({tt(ls, dt)}) {{\n" + "\n".join(lines) +
+            f"\n    return {res} : {tt(ls, dt)}\n  }}\n}}\n")
+    return text, params

@@ -833,6 +833,17 @@ class Interpreter:
         scope.update({name: np.asarray(v) for (name, _), v in zip(region.args, values)})
         return self._run_ops(region.ops, scope)
 
+    def region_map(self, op, a, env):
+        """stablehlo.map: the computation is applied to each tuple of corresponding elements."""
+        t = op.types[0]
+        out = np.empty(t.shape, dtype=np.float64 if t.is_float else t.np_dtype())
+        for idx in np.ndindex(*t.shape):
+            out[idx] = self._apply(op.regions[0], env, [x[idx] for x in a])[0].reshape(())
+        return out
+
+    def op_get_dimension_size(self, op, a, t):
+        return np.asarray(a[0].shape[int(op.attrs.get("dim", op.attrs.get("dimension", 0)))], dtype=t.np_dtype())
+
     def region_reduce_window(self, op, a, env):
         """stablehlo.reduce_window: the operand is dilated and padded with the init value, and every window is folded
         through the body region in row-major order, starting from the init value."""
@@ -984,6 +995,8 @@ class Interpreter:
             return self.op_while(op, a, t, env)
         if n in ("if", "case"):
             return self.op_branch(op, a, env)
+        if n == "map":
+            return self.region_map(op, a, env)
         if n in ("reduce_window", "scatter", "sort"):
             return getattr(self, "region_" + n)(op, a, env)
         f = getattr(self, "op_" + n, None)
@@ -993,7 +1006,8 @@ class Interpreter:
               "log_plus_one": np.log1p, "sqrt": np.sqrt, "rsqrt": lambda x: 1.0 / np.sqrt(x), "cbrt": np.cbrt, "tanh": np.tanh,
               "logistic": lambda x: 1.0 / (1.0 + np.exp(-x)), "sine": np.sin, "cosine": np.cos, "tan": np.tan, "floor": np.floor,
               "ceil": np.ceil, "round_nearest_even": np.rint, "sign": np.sign, "is_finite": np.isfinite,
-              "round_nearest_afz": lambda x: np.sign(x) * np.floor(np.abs(x) + 0.5)}
+              "round_nearest_afz": lambda x: np.sign(x) * np.floor(np.abs(x) + 0.5),
+              "erf": np.vectorize(math.erf, otypes=[np.float64])}
         if n in un:
             with np.errstate(all="ignore"):
                 return un[n](a[0])

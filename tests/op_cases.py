@@ -479,6 +479,29 @@ def widening_cases():
                 "    %s = stablehlo.constant dense<[1, 8]> : tensor<2xi32>\n"
                 f"    %0 = \"stablehlo.dynamic_gather\"(%arg0, %arg1, %s) <{{dimension_numbers = #stablehlo.gather<offset_dims = [1], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 1>, indices_are_sorted = false}}> : ({t48}, {tt((5, 1), 'i32')}, tensor<2xi32>) -> {tt((5, 8), 'f32')}",
                 "%0"), [x48, ids]))
+    # ---- map: a scalar computation with a constant, a compare and a select, applied elementwise
+    map_text = f"""module @jit_map {{
+  func.func public @main(%arg0: {t48}, %arg1: {t48}) -> ({t48}) {{
+    %0 = "stablehlo.map"(%arg0, %arg1) <{{dimensions = array<i64: 0, 1>}}> ({{
+    ^bb0(%a: tensor<f32>, %b: tensor<f32>):
+      %half = stablehlo.constant dense<5.000000e-01> : tensor<f32>
+      %p = stablehlo.multiply %a, %b : tensor<f32>
+      %q = stablehlo.add %p, %half : tensor<f32>
+      %c = stablehlo.compare  GT, %a, %b,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %r = stablehlo.select %c, %q, %b : tensor<i1>, tensor<f32>
+      stablehlo.return %r : tensor<f32>
+    }}) : ({t48}, {t48}) -> {t48}
+    return %0 : {t48}
+  }}
+}}
+"""
+    out.append(("map_scalar_computation", map_text, [x48, y48]))
+    out.append(("get_dimension_size", func([t48], [tt((), "i32")],
+                f"    %0 = stablehlo.get_dimension_size %arg0, dim = 1 : ({t48}) -> tensor<i32>", "%0"), [x48]))
+    for dt in ("f32", "bf16", "f16"):
+        if dt in NP:
+            t = tt((5, 37), dt)
+            out.append((f"erf_{dt}", func([t], [t], f"    %0 = chlo.erf %arg0 : {t} -> {t}", "%0"), [rand(rng, (5, 37), dt, -3.0, 3.0)]))
     # ---- batch_norm_inference over NHWC and NCHW feature positions
     for dt in ("f32", "bf16"):
         if dt not in NP:

@@ -75,3 +75,38 @@ def test_reduced_gpt2_forward(level, dt):
     top2 = np.sort(want, axis=-1)[..., -2:]
     clear = (top2[..., 1] - top2[..., 0]) > 0.05 * np.abs(top2[..., 1]) + 1e-3
     assert np.array_equal(got.argmax(-1)[clear], want.argmax(-1)[clear])
+
+
+def cnn_inputs(params):
+    rng = np.random.default_rng(99)
+    out = []
+    for name, shape, _ in params:
+        if name.endswith("_var"):
+            out.append(rng.uniform(0.5, 1.5, size=shape).astype(np.float32))
+        elif name.endswith("_scale"):
+            out.append((1 + 0.1 * rng.standard_normal(shape)).astype(np.float32))
+        elif name.endswith(("_offset", "_mean", "_b")):
+            out.append((0.1 * rng.standard_normal(shape)).astype(np.float32))
+        elif name == "image":
+            out.append(rng.standard_normal(shape).astype(np.float32))
+        else:
+            fan_in = int(np.prod(shape[:-1]))
+            out.append((rng.standard_normal(shape) / np.sqrt(fan_in)).astype(np.float32))
+    return out
+
+
+@pytest.mark.parametrize("level", [0, 2, 3])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_residual_cnn_forward(level, dt):
+    """Convolution (patch matrix + GEMM), batch-norm inference, max pooling and the dense head in one module."""
+    text, params = modules.cnn_module(batch=4, size=16, channels=3, width=16, classes=10, dt=dt)
+    ins = cnn_inputs(params)
+    want = interp.evaluate(text, ins)[0]
+    c = client()
+    exe = c.compile(text, level)
+    got = exe.execute([c.buffer(a) for a in ins])[0].to_numpy().astype(np.float64)
+    rel_l2 = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert rel_l2 < (1e-5 if dt == "f32" else 2e-2), f"cnn {dt} O{level}: relative L2 error {rel_l2:.3e}"
+    steps = exe.steps
+    assert steps.count("convolution.gemm") == 3 and steps.count("reduce_window") == 1
+    assert any(s.startswith("batch_norm_inference") or s.startswith("fused_elementwise") for s in steps)
