@@ -473,6 +473,95 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
     return out
 
 
+def _conv_text(dt="bf16"):
+    from metalhlo_b200.modules import tt
+
+    x, w, o = tt((32, 56, 56, 64), dt), tt((3, 3, 64, 64), dt), tt((32, 56, 56, 64), dt)
+    return (f"func.func @main(%x: {x}, %w: {w}) -> {o} {{\n  %0 = stablehlo.convolution(%x, %w) dim_numbers = [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f], "
+            f"window = {{stride = [1, 1], pad = [[1, 1], [1, 1]]}} {{batch_group_count = 1 : i64, feature_group_count = 1 : i64}} : ({x}, {w}) -> {o}\n"
+            f"  return %0 : {o}\n}}\n")
+
+
+def _pool_text(dt="bf16"):
+    from metalhlo_b200.modules import tt
+
+    x, o = tt((32, 112, 112, 64), dt), tt((32, 56, 56, 64), dt)
+    return (f"func.func @main(%x: {x}) -> {o} {{\n  %i = stablehlo.constant dense<0xFF80> : tensor<{dt}>\n"
+            f"  %0 = \"stablehlo.reduce_window\"(%x, %i) <{{window_dimensions = array<i64: 1, 3, 3, 1>, window_strides = array<i64: 1, 2, 2, 1>, "
+            f"padding = dense<[[0, 0], [0, 1], [0, 1], [0, 0]]> : tensor<4x2xi64>}}> ({{\n  ^bb0(%a: tensor<{dt}>, %b: tensor<{dt}>):\n"
+            f"    %m = stablehlo.maximum %a, %b : tensor<{dt}>\n    stablehlo.return %m : tensor<{dt}>\n  }}) : ({x}, tensor<{dt}>) -> {o}\n"
+            f"  return %0 : {o}\n}}\n")
+
+
+def _sort_text(rows, n):
+    from metalhlo_b200.modules import tt
+
+    t, ti = tt((rows, n), "f32"), tt((rows, n), "i32")
+    return (f"func.func @main(%x: {t}) -> ({t}, {ti}) {{\n  %i = stablehlo.iota dim = 1 : {ti}\n"
+            f"  %0:2 = \"stablehlo.sort\"(%x, %i) <{{dimension = 1 : i64, is_stable = true}}> ({{\n"
+            f"  ^bb0(%a: tensor<f32>, %b: tensor<f32>, %c: tensor<i32>, %d: tensor<i32>):\n"
+            f"    %p = stablehlo.compare  LT, %a, %b,  TOTALORDER : (tensor<f32>, tensor<f32>) -> tensor<i1>\n    stablehlo.return %p : tensor<i1>\n"
+            f"  }}) : ({t}, {ti}) -> ({t}, {ti})\n  return %0#0, %0#1 : {t}, {ti}\n}}\n")
+
+
+def _scatter_text():
+    from metalhlo_b200.modules import tt
+
+    table, idx, upd = tt((50257, 768), "f32"), tt((32768, 1), "i32"), tt((32768, 768), "f32")
+    return (f"func.func @main(%t: {table}, %i: {idx}, %u: {upd}) -> {table} {{\n"
+            f"  %0 = \"stablehlo.scatter\"(%t, %i, %u) <{{indices_are_sorted = false, scatter_dimension_numbers = #stablehlo.scatter<update_window_dims = [1], "
+            f"inserted_window_dims = [0], scatter_dims_to_operand_dims = [0], index_vector_dim = 1>, unique_indices = false}}> ({{\n"
+            f"  ^bb0(%a: tensor<f32>, %b: tensor<f32>):\n    %s = stablehlo.add %a, %b : tensor<f32>\n    stablehlo.return %s : tensor<f32>\n"
+            f"  }}) : ({table}, {idx}, {upd}) -> {table}\n  return %0 : {table}\n}}\n")
+
+
+# name -> (module text builder, work per execution, unit): operators either side of the fused path, as whole modules
+MODULE_CASES = {
+    "conv": (lambda: _conv_text(), 2 * 32 * 56 * 56 * 64 * 9 * 64 / 1e12, "TFLOP"),                    # ResNet 3x3, 64 -> 64 channels
+    "maxpool": (lambda: _pool_text(), (32 * 112 * 112 * 64 + 32 * 56 * 56 * 64) * 2 / 1e9, "GB"),     # read once + write once
+    "sort_rows": (lambda: _sort_text(4096, 4096), 4096 * 4096 * 4 * 4 / 1e9, "GB"),                    # keys + order out, keys in (+iota)
+    "sort_long": (lambda: _sort_text(4, 4194304), 4 * 4194304 * 4 * 4 / 1e9, "GB"),
+    "scatter_add": (lambda: _scatter_text(), (2 * 50257 * 768 + 3 * 32768 * 768) * 4 / 1e9, "GB"),     # copy of the table + read-modify-write of the rows
+}
+
+
+def profile_module_case(kind: str, launches: int):
+    """One module of MODULE_CASES through the C API on device memory: compile, then `launches` timed executions."""
+    import numpy as np
+    import torch
+
+    from metalhlo_b200 import capi
+
+    torch.cuda.set_device(0)
+    build, work, unit = MODULE_CASES[kind]
+    client = capi.Client()
+    exe = client.compile(build(), 3)
+    rng = np.random.default_rng(5)
+    ins = []
+    for i in range(exe.input_count):
+        shape, code = exe.input_type(i)
+        dt = capi.np_dtype(code)
+        if np.issubdtype(dt, np.integer):
+            arr = rng.integers(0, 50257, size=shape).astype(dt)
+        else:
+            arr = rng.standard_normal(shape).astype(np.float32).astype(dt)
+        ins.append(client.buffer(arr))
+    outs = []
+    for i in range(exe.output_count):
+        shape, code = exe.output_type(i)
+        outs.append(torch.empty(int(np.prod(shape)) * capi.np_dtype(code).itemsize, dtype=torch.uint8, device="cuda"))
+    in_ptrs, out_ptrs = [b.device_pointer for b in ins], [o.data_ptr() for o in outs]
+    print(f"{kind}: steps {exe.steps}, {exe.launch_count} launches per execution, arena {exe.arena_bytes / 1e6:.1f} MB", file=sys.stderr)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(launches):
+        e0.record()
+        exe.execute_on_device(in_ptrs, out_ptrs, torch.cuda.current_stream().cuda_stream)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        print(f"{kind} execution {i}: {ms:.3f} ms, {work / ms * 1e3:.1f} {unit}/s")
+
+
 def profile_case(kind: str, launches: int):
     """A few launches of one tensor-core kernel on a profiler-sized case (a few hundred MB on the device, inputs
     larger than L2), for `ncu -k regex:<kernel>` captures. Prints the CUDA-event time per launch; no JSON line."""
@@ -485,6 +574,8 @@ def profile_case(kind: str, launches: int):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(1)
+    if kind in MODULE_CASES:
+        return profile_module_case(kind, launches)
     if kind == "gemm":
         n = 8192
         a = (torch.randn(n, n, device=dev, generator=g) / math.sqrt(n)).to(torch.bfloat16)
@@ -543,8 +634,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / attention / GPT-2 side measurements")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (profiler captures)")
-    ap.add_argument("--profile-kernel", choices=["gemm", "attention", "attention_causal"],
-                    help="run a few launches of one tensor-core kernel on a profiler-sized case and exit")
+    ap.add_argument("--profile-kernel", choices=["gemm", "attention", "attention_causal"] + sorted(MODULE_CASES),
+                    help="run a few launches of one kernel (or one single-operator module) on a profiler-sized case and exit")
     args = ap.parse_args()
     if args.profile_kernel:
         profile_case(args.profile_kernel, max(1, min(args.steps, 5)))

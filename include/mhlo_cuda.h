@@ -357,6 +357,19 @@ typedef struct {
 int mhlo_cuda_reduce_window(const mhlo_cuda_view* in, const mhlo_cuda_window* window, int32_t op, const void* init_dev,
                             void* out_dev, const int64_t* out_shape, mhlo_cuda_stream_t stream);
 
+/*
+ * stablehlo.select_and_scatter (the gradient of a pooling): for every element of `source` the matching window of
+ * the operand (padded with the init value; dilations are not part of this op) is scanned in row-major order keeping
+ * the element e for which select(kept, e) fails, select(a, b) = a <cmp> b with cmp one of MHLO_EW_CMP_GE/GT/LE/LT;
+ * the source element is then combined (scatter_mode: MHLO_SCATTER_ADD/MUL/MAX/MIN, atomically) into the result at the
+ * kept element's position unless that lies in the padding. result_inout_dev (contiguous, operand's shape and dtype)
+ * must already be filled with the init value. The reference covers the 2-D NHWC max-pool gradient through
+ * maxPooling2DGradient (MPSGraphCompiler.swift:4203-4245).
+ */
+int mhlo_cuda_select_and_scatter(const mhlo_cuda_view* operand, const void* source_dev, const int64_t* source_shape,
+                                 const void* init_dev, const mhlo_cuda_window* window, int32_t select_cmp,
+                                 int32_t scatter_mode, void* result_inout_dev, mhlo_cuda_stream_t stream);
+
 typedef struct {
     int32_t n_update_window_dims, n_inserted_window_dims, n_input_batching, n_scatter_dims_to_operand;
     int32_t update_window_dims[MHLO_CUDA_MAX_RANK];

@@ -522,11 +522,12 @@ class Lowering {
         if (n == "convolution") return lower_convolution(op);
         if (n == "reduce_window") return lower_reduce_window(op);
         if (n == "scatter") return lower_scatter(op);
+        if (n == "select_and_scatter") return lower_select_and_scatter(op);
         if (n == "sort") return lower_sort(op);
         if (n == "dynamic_slice") return lower_dynamic_slice(op);
         if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
         if (n == "custom_call") return lower_custom_call(op);
-        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "fft" || n == "select_and_scatter" ||
+        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "fft" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         const int code = ew_opcode(n);
@@ -1083,6 +1084,54 @@ class Lowering {
         add_step("reduce_window", [=](const Ctx& c) {
             mhlo_cuda_view xv = bind(dx, c);
             return mhlo_cuda_reduce_window(&xv, &w, kind, bind(di, c).base, const_cast<void*>(bind(dout, c).base), oshape.data(), c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.select_and_scatter: the result is filled with the init value, then every source element is combined
+    // into the position its window selects.
+    void lower_select_and_scatter(const Op& op) {
+        if (op.operands.size() != 3) fail_compile("select_and_scatter takes three operands");
+        static const std::map<std::string, int> cmps = {{"GE", MHLO_EW_CMP_GE}, {"GT", MHLO_EW_CMP_GT}, {"LE", MHLO_EW_CMP_LE}, {"LT", MHLO_EW_CMP_LT}};
+        static const std::map<std::string, int> modes = {{"add", MHLO_SCATTER_ADD}, {"multiply", MHLO_SCATTER_MUL}, {"maximum", MHLO_SCATTER_MAX},
+                                                         {"minimum", MHLO_SCATTER_MIN}};
+        auto ci = cmps.find(op.str_attr("select_direction"));
+        auto mi = modes.find(op.str_attr("reducer"));
+        if (ci == cmps.end()) fail_unsupported("select_and_scatter with a select body other than one GE / GT / LE / LT compare of its arguments");
+        if (mi == modes.end()) fail_unsupported("select_and_scatter with a scatter body this backend does not recognise (" + op.str_attr("reducer") + ")");
+        const int cmp = ci->second, mode = mi->second;
+        const View& x = get(op.operands[0]);
+        View source = materialize(get(op.operands[1]), "select_and_scatter.source");
+        View init = materialize(get(op.operands[2]), "select_and_scatter.init");
+        const TensorType& rt = op.result_types[0];
+        const int rank = x.type.rank();
+        if (rank > MHLO_CUDA_MAX_RANK || source.type.rank() != rank) fail_unsupported("select_and_scatter of rank " + std::to_string(rank));
+        mhlo_cuda_window w;
+        std::memset(&w, 0, sizeof w);
+        w.rank = rank;
+        std::vector<int64_t> size = op.int_list("window_dimensions"), stride = op.int_list("window_strides"), pad = op.int_list("padding");
+        if (static_cast<int>(size.size()) != rank) fail_compile("select_and_scatter: window_dimensions does not match the operand's rank");
+        if (!stride.empty() && static_cast<int>(stride.size()) != rank) fail_compile("select_and_scatter: window_strides does not match the operand's rank");
+        if (!pad.empty() && static_cast<int>(pad.size()) != 2 * rank) fail_compile("select_and_scatter: padding must be rank x 2");
+        for (int d = 0; d < rank; ++d) {
+            w.size[d] = size[static_cast<size_t>(d)];
+            w.stride[d] = stride.empty() ? 1 : stride[static_cast<size_t>(d)];
+            w.base_dilation[d] = w.window_dilation[d] = 1;
+            w.pad_low[d] = pad.empty() ? 0 : pad[static_cast<size_t>(2 * d)];
+            const int64_t hi = pad.empty() ? 0 : pad[static_cast<size_t>(2 * d + 1)];
+            const int64_t padded = x.type.shape[static_cast<size_t>(d)] + w.pad_low[d] + hi;
+            const int64_t windows = padded < w.size[d] ? 0 : (padded - w.size[d]) / w.stride[d] + 1;
+            if (windows != source.type.shape[static_cast<size_t>(d)]) fail_compile("select_and_scatter: source shape does not match the windows of the operand");
+        }
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        copy_view(expand_to(init, rt.shape), out, "select_and_scatter.fill");
+        DevView dx = dev(x), ds = dev(source), di = dev(init), dout = dev(out);
+        keep_alive(x); keep_alive(source); keep_alive(init); keep_alive(out);
+        const std::vector<int64_t> sshape = source.type.shape;
+        add_step("select_and_scatter", [=](const Ctx& c) {
+            mhlo_cuda_view xv = bind(dx, c);
+            return mhlo_cuda_select_and_scatter(&xv, bind(ds, c).base, sshape.data(), bind(di, c).base, &w, cmp, mode,
+                                                const_cast<void*>(bind(dout, c).base), c.stream);
         });
         set(op.results[0], out);
     }

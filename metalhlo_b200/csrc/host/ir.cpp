@@ -136,12 +136,12 @@ static std::string vname(int v) { return "%v" + std::to_string(v); }
 static void print_op(const Function& f, const Op& o, int indent, std::ostringstream& os);
 
 static void print_region(const Function& f, const Region& r, int indent, std::ostringstream& os) {
-    os << "({\n" << std::string(indent + 2, ' ') << "^bb0(";
+    os << "{\n" << std::string(indent + 2, ' ') << "^bb0(";
     for (size_t i = 0; i < r.args.size(); ++i)
         os << (i ? ", " : "") << vname(r.args[i]) << ": " << f.values[r.args[i]].type.str();
     os << "):\n";
     for (const Op& o : r.ops) print_op(f, o, indent + 4, os);
-    os << std::string(indent, ' ') << "})";
+    os << std::string(indent, ' ') << "}";
 }
 
 static void print_op(const Function& f, const Op& o, int indent, std::ostringstream& os) {
@@ -161,7 +161,11 @@ static void print_op(const Function& f, const Op& o, int indent, std::ostringstr
     os << "\"" << (o.dialect.empty() ? "" : o.dialect + ".") << o.name << "\"(";
     for (size_t i = 0; i < o.operands.size(); ++i) os << (i ? ", " : "") << vname(o.operands[i]);
     os << ")";
-    for (size_t i = 0; i < o.regions.size(); ++i) { os << " "; print_region(f, *o.regions[i], indent, os); }
+    if (!o.regions.empty()) {  // "op"(operands) ({region}, {region}) {attrs}
+        os << " (";
+        for (size_t i = 0; i < o.regions.size(); ++i) { if (i) os << ", "; print_region(f, *o.regions[i], indent, os); }
+        os << ")";
+    }
     bool first = true;
     for (const auto& kv : o.attrs) {
         if (kv.first[0] == '_' || kv.first.find('.') != std::string::npos) continue;

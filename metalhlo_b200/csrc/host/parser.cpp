@@ -1178,6 +1178,22 @@ class Parser {
             else
                 op->attrs["reducer"] = Attr::make_string(r.ops.size() == 2 ? classify_reducer(r) : "unknown");
         }
+        if (n == "select_and_scatter" && op->regions.size() == 2) {
+            // select(a, b): one compare of the two arguments; scatter(a, b): one arithmetic op
+            const Region& sel = *op->regions[0];
+            std::string dir = "unknown";
+            if (sel.ops.size() == 2 && sel.ops[0].name == "compare" && sel.args.size() == 2 && sel.ops[1].name == "return" &&
+                sel.ops[1].operands.size() == 1 && sel.ops[1].operands[0] == sel.ops[0].results[0]) {
+                const Op& c = sel.ops[0];
+                dir = c.str_attr("comparison_direction");
+                if (c.operands[0] == sel.args[1] && c.operands[1] == sel.args[0])  // b <dir> a  ==  a <mirrored dir> b
+                    dir = dir == "GE" ? "LE" : dir == "GT" ? "LT" : dir == "LE" ? "GE" : dir == "LT" ? "GT" : "unknown";
+                else if (!(c.operands[0] == sel.args[0] && c.operands[1] == sel.args[1]))
+                    dir = "unknown";
+            }
+            op->attrs["select_direction"] = Attr::make_string(dir);
+            op->attrs["reducer"] = Attr::make_string(op->regions[1]->ops.size() == 2 ? classify_reducer(*op->regions[1]) : "unknown");
+        }
         if (n == "sort" && !op->regions.empty()) {
             // comparator(lhs0, rhs0, lhs1, rhs1, ..): one strict compare of the first operand's pair gives the order
             const Region& r = *op->regions[0];

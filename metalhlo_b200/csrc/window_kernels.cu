@@ -254,6 +254,69 @@ __global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ Sc
     }
 }
 
+// ---- select_and_scatter -----------------------------------------------------------------------------------------------
+
+struct SelectScatterParams {
+    mhlo_cuda_window w;
+    int64_t in_shape[MHLO_CUDA_MAX_RANK], in_stride[MHLO_CUDA_MAX_RANK], src_shape[MHLO_CUDA_MAX_RANK];
+    const void* in;
+    const void* source;
+    const void* init;
+    void* result;
+    int64_t n_src, window_count;
+    int32_t cmp, mode;
+};
+
+template <typename A>
+__device__ __forceinline__ bool select_holds(int cmp, A a, A b) {
+    switch (cmp) {
+        case MHLO_EW_CMP_GE: return a >= b;
+        case MHLO_EW_CMP_GT: return a > b;
+        case MHLO_EW_CMP_LE: return a <= b;
+        default: return a < b;
+    }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256) select_and_scatter_kernel(const __grid_constant__ SelectScatterParams p) {
+    using A = typename AccOf<E>::type;
+    const int rank = p.w.rank;
+    const A init = widen<E>(*static_cast<const E*>(p.init));
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < p.n_src; s += step) {
+        int64_t origin[MHLO_CUDA_MAX_RANK];
+        int64_t rem = s;
+        for (int d = rank - 1; d >= 0; --d) {
+            origin[d] = (rem % p.src_shape[d]) * p.w.stride[d] - p.w.pad_low[d];
+            rem /= p.src_shape[d];
+        }
+        int64_t wi[MHLO_CUDA_MAX_RANK];
+        for (int d = 0; d < rank; ++d) wi[d] = 0;
+        A kept = init;
+        int64_t kept_at = -1;  // dense offset into the result, -1 = in the padding
+        for (int64_t k = 0; k < p.window_count; ++k) {
+            int64_t off = 0, dense = 0;
+            bool inside = true;
+            for (int d = 0; d < rank; ++d) {
+                const int64_t pos = origin[d] + wi[d];
+                inside = inside && pos >= 0 && pos < p.in_shape[d];
+                off += pos * p.in_stride[d];
+                dense = dense * p.in_shape[d] + pos;
+            }
+            const A v = inside ? widen<E>(static_cast<const E*>(p.in)[off]) : init;
+            if (k == 0 || !select_holds<A>(p.cmp, kept, v)) {
+                kept = v;
+                kept_at = inside ? dense : -1;
+            }
+            for (int d = rank - 1; d >= 0; --d) {
+                if (++wi[d] < p.w.size[d]) break;
+                wi[d] = 0;
+            }
+        }
+        if (kept_at >= 0) scatter_apply<E>(static_cast<E*>(p.result) + kept_at, static_cast<const E*>(p.source)[s], p.mode);
+    }
+}
+
 // ---- sort --------------------------------------------------------------------------------------------------------------
 // Every key becomes an unsigned 64-bit number whose order is the wanted one (descending = complemented); the pair
 // (key, position in the slice) is unique, so a bitonic network over pairs gives the stable order. Slices are padded to
@@ -622,5 +685,45 @@ extern "C" int mhlo_cuda_sort(const void* const* operands_dev, void* const* outs
     }
     sort_apply_kernel<<<grid_of(p.rows * p.n, 256), 256, 0, s>>>(p);
     MHLO_CUDA_CHECK_LAUNCH("sort (apply)");
+    return MHLO_CUDA_OK;
+}
+
+extern "C" int mhlo_cuda_select_and_scatter(const mhlo_cuda_view* operand, const void* source_dev, const int64_t* source_shape, const void* init_dev,
+                                            const mhlo_cuda_window* window, int32_t select_cmp, int32_t scatter_mode, void* result_inout_dev,
+                                            mhlo_cuda_stream_t stream) {
+    if (!operand || !window || !source_shape) return fail(MHLO_CUDA_INVALID_ARGUMENT, "select_and_scatter: null argument");
+    if (window->rank != operand->rank || operand->rank < 0 || operand->rank > MHLO_CUDA_MAX_RANK)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "select_and_scatter: window rank %d for an operand of rank %d", window->rank, operand->rank);
+    if (select_cmp != MHLO_EW_CMP_GE && select_cmp != MHLO_EW_CMP_GT && select_cmp != MHLO_EW_CMP_LE && select_cmp != MHLO_EW_CMP_LT)
+        return fail(MHLO_CUDA_UNSUPPORTED, "select_and_scatter: select comparison %d", select_cmp);
+    if (scatter_mode < MHLO_SCATTER_ADD || scatter_mode > MHLO_SCATTER_MIN)
+        return fail(MHLO_CUDA_UNSUPPORTED, "select_and_scatter: scatter computation %d", scatter_mode);
+    SelectScatterParams p;
+    memset(&p, 0, sizeof p);
+    p.w = *window;
+    p.n_src = 1;
+    p.window_count = 1;
+    for (int d = 0; d < operand->rank; ++d) {
+        if (window->size[d] < 1 || window->stride[d] < 1) return fail(MHLO_CUDA_INVALID_ARGUMENT, "select_and_scatter: window size and stride must be positive");
+        if (window->base_dilation[d] > 1 || window->window_dilation[d] > 1) return fail(MHLO_CUDA_INVALID_ARGUMENT, "select_and_scatter has no dilations");
+        p.in_shape[d] = operand->shape[d];
+        p.in_stride[d] = operand->stride[d];
+        p.src_shape[d] = source_shape[d];
+        p.n_src *= source_shape[d];
+        p.window_count *= window->size[d];
+    }
+    if (p.n_src == 0) return MHLO_CUDA_OK;
+    if (!operand->base || !source_dev || !init_dev || !result_inout_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "select_and_scatter: null pointer");
+    p.in = operand->base;
+    p.source = source_dev;
+    p.init = init_dev;
+    p.result = result_inout_dev;
+    p.cmp = select_cmp;
+    p.mode = scatter_mode;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = grid_of(p.n_src, 256);
+    if (!with_element_type(operand->dtype, [&](auto tag) { select_and_scatter_kernel<decltype(tag)><<<grid, 256, 0, s>>>(p); }))
+        return fail(MHLO_CUDA_UNSUPPORTED, "select_and_scatter: dtype %d", operand->dtype);
+    MHLO_CUDA_CHECK_LAUNCH("select_and_scatter");
     return MHLO_CUDA_OK;
 }

@@ -125,6 +125,7 @@ _PROTOTYPES = {
     "mhlo_cuda_convolution": (C.c_int, [_i32, _vp, _vp, _vp, C.POINTER(Conv), _vp]),
     "mhlo_cuda_im2col": (C.c_int, [_i32, _vp, _vp, _i64, C.POINTER(Conv), _vp]),
     "mhlo_cuda_reduce_window": (C.c_int, [C.POINTER(View), C.POINTER(Window), _i32, _vp, _vp, C.POINTER(_i64), _vp]),
+    "mhlo_cuda_select_and_scatter": (C.c_int, [C.POINTER(View), _vp, C.POINTER(_i64), _vp, C.POINTER(Window), _i32, _i32, _vp, _vp]),
     "mhlo_cuda_scatter": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, _vp, C.POINTER(_i64), _i32,
                                     C.POINTER(ScatterDims), _i32, _vp]),
     "mhlo_cuda_sort_scratch_bytes": (_i64, [C.POINTER(_i64), _i32, _i32]),

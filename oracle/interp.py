@@ -881,6 +881,32 @@ class Interpreter:
             out[o] = acc
         return out
 
+    def region_select_and_scatter(self, op, a, env):
+        """stablehlo.select_and_scatter: each window of the operand (padded with the init value) keeps the element e
+        for which select(kept, e) fails, scanning in row-major order; the source element of the window is combined by
+        the scatter region into the result (filled with the init value) at the kept position, unless it is padding."""
+        x, source, init = a[0], a[1], a[2].reshape(())
+        t = op.types[0]
+        A = op.attrs
+        rank = x.ndim
+        size = _ints(A.get("window_dimensions"))
+        stride = _ints(A.get("window_strides")) or [1] * rank
+        pad = A.get("padding")
+        pad = np.asarray(dense_value(pad[1], pad[2]) if isinstance(pad, tuple) else (pad if pad is not None else np.zeros((rank, 2))), dtype=np.int64).reshape(rank, 2)
+        select, scatter = op.regions
+        result = np.full(t.shape, init, dtype=x.dtype)
+        for s_idx in np.ndindex(*source.shape):
+            kept, kept_at = None, None
+            for w in np.ndindex(*size):
+                pos = tuple(si * st + wi - int(lo) for si, st, wi, (lo, _) in zip(s_idx, stride, w, pad))
+                inside = all(0 <= c < n for c, n in zip(pos, x.shape))
+                v = x[pos] if inside else init
+                if kept is None or not bool(self._apply(select, env, [kept, v])[0].reshape(())):
+                    kept, kept_at = v, (pos if inside else None)
+            if kept_at is not None:
+                result[kept_at] = self._apply(scatter, env, [result[kept_at], source[s_idx]])[0].reshape(())
+        return result
+
     def region_scatter(self, op, a, env):
         """stablehlo.scatter: updates are applied one by one, in row-major order of `updates`, through the update
         computation; an update whose target lies outside the operand is skipped."""
@@ -997,7 +1023,7 @@ class Interpreter:
             return self.op_branch(op, a, env)
         if n == "map":
             return self.region_map(op, a, env)
-        if n in ("reduce_window", "scatter", "sort"):
+        if n in ("reduce_window", "scatter", "sort", "select_and_scatter"):
             return getattr(self, "region_" + n)(op, a, env)
         f = getattr(self, "op_" + n, None)
         if f is not None:

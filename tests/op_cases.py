@@ -614,6 +614,34 @@ def window_scatter_sort_cases():
     out.append(reduce_window_case("reduce_window_of_transpose", xt, "f32", "maximum", "-inf", (2, 3), (3, 3), strides=(2, 3),
                                   pre=(f"    %pre = stablehlo.transpose %arg0, dims = [1, 0] : ({tt((9, 6), 'f32')}) -> {tt((6, 9), 'f32')}", (6, 9))))
     out.append(reduce_window_case("reduce_window_or_i1", rand(rng, (4, 10), "i1"), "i1", "or", 0, (1, 3), (4, 8)))
+    # ---- select_and_scatter: the gradient of max pooling as jax prints it (GE select, add scatter)
+    def sas_case(name, x, src, dt, window, strides, padding=None, select="GE", kind="add", init=0):
+        arr = lambda v: "array<i64: " + ", ".join(str(i) for i in v) + ">"
+        props = [f"window_dimensions = {arr(window)}", f"window_strides = {arr(strides)}"]
+        if padding:
+            props.append("padding = dense<[" + ", ".join(f"[{lo}, {hi}]" for lo, hi in padding) + f"]> : tensor<{len(window)}x2xi64>")
+        st = f"tensor<{dt}>"
+        ctype = "FLOAT" if dt[0] in "fb" else "SIGNED"
+        t_x, t_s = tt(x.shape, dt), tt(src.shape, dt)
+        body = (f"    %init = {_const(dt, init)}\n"
+                f"    %0 = \"stablehlo.select_and_scatter\"(%arg0, %arg1, %init) <{{{', '.join(props)}}}> ({{\n"
+                f"    ^bb0(%a: {st}, %b: {st}):\n      %c = stablehlo.compare  {select}, %a, %b,  {ctype} : ({st}, {st}) -> tensor<i1>\n"
+                f"      stablehlo.return %c : tensor<i1>\n    }}, {{\n{_region(kind, dt, ('p', 'q'))}    }}) : ({t_x}, {t_s}, {st}) -> {t_x}")
+        return (name, func([t_x, t_s], [t_x], body, "%0"), [x, src])
+
+    img = rand(rng, (2, 8, 8, 3), "f32")
+    out.append(sas_case("select_and_scatter_maxpool_grad_2x2", img, rand(rng, (2, 4, 4, 3), "f32"), "f32", (1, 2, 2, 1), (1, 2, 2, 1)))
+    out.append(sas_case("select_and_scatter_overlapping_3x3", img, rand(rng, (2, 4, 4, 3), "f32"), "f32", (1, 3, 3, 1), (1, 2, 2, 1),
+                        padding=((0, 0), (0, 1), (0, 1), (0, 0))))
+    if "bf16" in NP:
+        out.append(sas_case("select_and_scatter_maxpool_grad_bf16", rand(rng, (2, 8, 8, 3), "bf16"), rand(rng, (2, 4, 4, 3), "bf16"), "bf16",
+                            (1, 2, 2, 1), (1, 2, 2, 1)))
+    out.append(sas_case("select_and_scatter_minpool_i32_ties", rng.integers(0, 3, size=(6, 6)).astype(np.int32), rand(rng, (3, 3), "i32"), "i32",
+                        (2, 2), (2, 2), select="LE"))
+    out.append(sas_case("select_and_scatter_strict_compare", rng.integers(0, 3, size=(6, 6)).astype(np.int32), rand(rng, (5, 5), "i32"), "i32",
+                        (2, 2), (1, 1), select="GT"))
+    out.append(sas_case("select_and_scatter_padding_can_win", -np.abs(rand(rng, (5, 5), "f32")) - 0.1, rand(rng, (3, 3), "f32"), "f32",
+                        (3, 3), (2, 2), padding=((1, 1), (1, 1))))
     # ---- scatter
     point = "inserted_window_dims = [0], scatter_dims_to_operand_dims = [0], index_vector_dim = 1"
     rows = "update_window_dims = [1], inserted_window_dims = [0], scatter_dims_to_operand_dims = [0], index_vector_dim = 1"

@@ -153,3 +153,19 @@ def test_transposed_convolution_matches_torch_conv_transpose2d():
     wt = torch.from_numpy(np.ascontiguousarray(w[::-1, ::-1].astype(np.float64))).permute(2, 3, 0, 1)
     want = torch.nn.functional.conv_transpose2d(xt, wt, stride=2).permute(0, 2, 3, 1).numpy()
     np.testing.assert_allclose(got, want, rtol=1e-9, atol=1e-9)
+
+
+def test_select_and_scatter_is_the_max_pool_gradient():
+    import torch
+
+    (got,), (x, src) = run("select_and_scatter_maxpool_grad_2x2")
+    xt = torch.from_numpy(x.astype(np.float64)).permute(0, 3, 1, 2).requires_grad_(True)
+    y = torch.nn.functional.max_pool2d(xt, 2, 2)
+    y.backward(torch.from_numpy(src.astype(np.float64)).permute(0, 3, 1, 2))
+    np.testing.assert_allclose(got, xt.grad.permute(0, 2, 3, 1).numpy(), rtol=1e-12, atol=1e-12)
+
+
+def test_select_and_scatter_drops_windows_won_by_the_padding():
+    (got,), (x, src) = run("select_and_scatter_padding_can_win")
+    # every operand value is negative and the init value 0 pads the border: border windows select the padding
+    assert got[0].sum() == 0 and got[:, 0].sum() == 0 or np.count_nonzero(got) < src.size
