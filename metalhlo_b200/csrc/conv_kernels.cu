@@ -119,6 +119,92 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Con
     }
 }
 
+// The same patch matrix moved as 16-byte vectors along the feature dimension: one thread per vector of `V` features of
+// one tap, 32-bit index arithmetic. Needs unit feature stride, features per group, pitch and all other input strides
+// multiples of V, 16-byte aligned bases and fewer than 2^31 vectors.
+struct Im2colVecParams {
+    const uint4* in;
+    uint4* out;
+    uint32_t total_vecs, pitch_vecs, row_vecs, cg_vecs, n_rows, groups;
+    int32_t ns;
+    uint32_t kernel_size[MHLO_CUDA_CONV_MAX_SPATIAL], out_size[MHLO_CUDA_CONV_MAX_SPATIAL], in_size[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int32_t stride[MHLO_CUDA_CONV_MAX_SPATIAL], pad_low[MHLO_CUDA_CONV_MAX_SPATIAL], lhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL],
+        rhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL], reverse[MHLO_CUDA_CONV_MAX_SPATIAL];
+    int64_t in_batch_vecs, in_spatial_vecs[MHLO_CUDA_CONV_MAX_SPATIAL];  // strides in vectors
+};
+
+// NS > 0: the number of spatial dimensions at compile time; DILATED = false promises lhs_dilation == 1 everywhere.
+template <int NS, bool DILATED>
+__global__ void __launch_bounds__(256) im2col_vec_kernel(const __grid_constant__ Im2colVecParams p) {
+    const int ns = NS > 0 ? NS : p.ns;
+    const uint32_t step = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vecs; i += step) {
+        const uint32_t kvec = i % p.pitch_vecs;
+        uint32_t rem = i / p.pitch_vecs;
+        uint32_t m = rem % p.n_rows;
+        const uint32_t g = rem / p.n_rows;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (kvec < p.row_vecs) {
+            const uint32_t icv = kvec % p.cg_vecs;
+            uint32_t kv = kvec / p.cg_vecs;
+            int64_t off = static_cast<int64_t>(g) * p.cg_vecs + icv;
+            bool inside = true;
+#pragma unroll
+            for (int d = ns - 1; d >= 0; --d) {
+                uint32_t kd = kv % p.kernel_size[d];
+                kv /= p.kernel_size[d];
+                const uint32_t od = m % p.out_size[d];
+                m /= p.out_size[d];
+                if (p.reverse[d]) kd = p.kernel_size[d] - 1 - kd;
+                const int32_t pos = static_cast<int32_t>(od) * p.stride[d] - p.pad_low[d] + static_cast<int32_t>(kd) * p.rhs_dilation[d];
+                const int32_t src = DILATED ? pos / p.lhs_dilation[d] : pos;
+                inside = inside && pos >= 0 && src < static_cast<int32_t>(p.in_size[d]) && (!DILATED || src * p.lhs_dilation[d] == pos);
+                off += src * p.in_spatial_vecs[d];
+            }
+            off += m * p.in_batch_vecs;
+            if (inside) v = __ldg(p.in + off);
+        }
+        p.out[i] = v;
+    }
+}
+
+// Fills the vector parameters; false when the layout does not allow the vector path.
+bool vec_im2col_params(const ConvParams& p, int elem_bytes, Im2colVecParams* q) {
+    const mhlo_cuda_conv& c = p.c;
+    const int64_t V = 16 / elem_bytes;
+    if (elem_bytes > 16 || 16 % elem_bytes) return false;
+    if (c.in_feature_stride != 1 || p.features_per_group % V || p.row_pitch % V || c.in_batch_stride % V) return false;
+    if (!aligned16(p.in) || !aligned16(p.out)) return false;
+    const int64_t total = c.feature_group_count * p.n_rows * (p.row_pitch / V);
+    if (total >= (int64_t{1} << 31) || p.n_rows >= (int64_t{1} << 31)) return false;
+    memset(q, 0, sizeof *q);
+    for (int d = 0; d < c.n_spatial; ++d) {
+        if (c.in_spatial_stride[d] % V) return false;
+        const int64_t reach = c.out_size[d] * c.stride[d] + c.kernel_size[d] * c.rhs_dilation[d] + (c.pad_low[d] < 0 ? -c.pad_low[d] : c.pad_low[d]);
+        if (reach >= (int64_t{1} << 30) || c.in_size[d] >= (int64_t{1} << 30)) return false;
+        q->kernel_size[d] = static_cast<uint32_t>(c.kernel_size[d]);
+        q->out_size[d] = static_cast<uint32_t>(c.out_size[d]);
+        q->in_size[d] = static_cast<uint32_t>(c.in_size[d]);
+        q->stride[d] = static_cast<int32_t>(c.stride[d]);
+        q->pad_low[d] = static_cast<int32_t>(c.pad_low[d]);
+        q->lhs_dilation[d] = static_cast<int32_t>(c.lhs_dilation[d]);
+        q->rhs_dilation[d] = static_cast<int32_t>(c.rhs_dilation[d]);
+        q->reverse[d] = c.reverse[d];
+        q->in_spatial_vecs[d] = c.in_spatial_stride[d] / V;
+    }
+    q->in = static_cast<const uint4*>(p.in);
+    q->out = static_cast<uint4*>(p.out);
+    q->total_vecs = static_cast<uint32_t>(total);
+    q->pitch_vecs = static_cast<uint32_t>(p.row_pitch / V);
+    q->row_vecs = static_cast<uint32_t>(p.kernel_volume * p.features_per_group / V);
+    q->cg_vecs = static_cast<uint32_t>(p.features_per_group / V);
+    q->n_rows = static_cast<uint32_t>(p.n_rows);
+    q->groups = static_cast<uint32_t>(c.feature_group_count);
+    q->ns = c.n_spatial;
+    q->in_batch_vecs = c.in_batch_stride / V;
+    return q->row_vecs > 0 && q->cg_vecs > 0;
+}
+
 int fill_params(const mhlo_cuda_conv* conv, ConvParams* p, const char* what) {
     if (!conv) return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: null geometry", what);
     if (conv->n_spatial < 0 || conv->n_spatial > MHLO_CUDA_CONV_MAX_SPATIAL)
@@ -204,6 +290,25 @@ extern "C" int mhlo_cuda_im2col(int32_t dtype, const void* in_dev, void* cols_de
     p.in = in_dev;
     p.out = cols_dev;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int elem_bytes = 0;
+    switch (dtype) {
+        case MHLO_DT_I1: case MHLO_DT_I8: case MHLO_DT_UI8: elem_bytes = 1; break;
+        case MHLO_DT_F16: case MHLO_DT_BF16: case MHLO_DT_I16: case MHLO_DT_UI16: elem_bytes = 2; break;
+        case MHLO_DT_F32: case MHLO_DT_I32: case MHLO_DT_UI32: elem_bytes = 4; break;
+        case MHLO_DT_F64: case MHLO_DT_I64: case MHLO_DT_UI64: elem_bytes = 8; break;
+        default: break;
+    }
+    Im2colVecParams q;
+    if (elem_bytes && vec_im2col_params(p, elem_bytes, &q)) {
+        bool dilated = false;
+        for (int d = 0; d < q.ns; ++d) dilated |= q.lhs_dilation[d] != 1;
+        const int vgrid = conv_grid(q.total_vecs);
+        if (dilated) im2col_vec_kernel<0, true><<<vgrid, 256, 0, s>>>(q);
+        else if (q.ns == 2) im2col_vec_kernel<2, false><<<vgrid, 256, 0, s>>>(q);
+        else im2col_vec_kernel<0, false><<<vgrid, 256, 0, s>>>(q);
+        MHLO_CUDA_CHECK_LAUNCH("im2col (vectors)");
+        return MHLO_CUDA_OK;
+    }
     const int grid = conv_grid(total);
     MHLO_CONV_DISPATCH(dtype, im2col_kernel, grid, s, p, "im2col");
     MHLO_CUDA_CHECK_LAUNCH("im2col");

@@ -128,6 +128,104 @@ __global__ void __launch_bounds__(256) reduce_window_kernel(const __grid_constan
     }
 }
 
+// Pooling over the leading dimensions of a tensor whose last dimension (channels of NHWC) is contiguous and not
+// windowed: one thread per 16-byte vector of channels, 32-bit index arithmetic, fp32 accumulation.
+struct WindowVecParams {
+    const uint4* in;
+    uint4* out;
+    uint32_t n_vecs, last_vecs, window_count;
+    int32_t rank;  // of the windowed dimensions (the operand's rank - 1)
+    uint32_t out_shape[MHLO_CUDA_MAX_RANK], in_shape[MHLO_CUDA_MAX_RANK], size[MHLO_CUDA_MAX_RANK];
+    int32_t stride[MHLO_CUDA_MAX_RANK], pad_low[MHLO_CUDA_MAX_RANK], base_dilation[MHLO_CUDA_MAX_RANK], window_dilation[MHLO_CUDA_MAX_RANK];
+    int64_t in_stride_vecs[MHLO_CUDA_MAX_RANK];
+    const void* init;  // device scalar of the element type
+    int32_t op;
+};
+
+// RANK > 0: the number of leading dimensions is known at compile time (loops unroll); 0 = read it from the parameters.
+// DILATED = false promises base_dilation == 1 everywhere (no divisions in the tap loop).
+template <typename T, int RANK, bool DILATED>
+__global__ void __launch_bounds__(256) reduce_window_vec_kernel(const __grid_constant__ WindowVecParams p) {
+    constexpr int V = VecTraits<T>::kElems;
+    const int rank = RANK > 0 ? RANK : p.rank;
+    const float init = widen<T>(*static_cast<const T*>(p.init));
+    const uint32_t step = gridDim.x * blockDim.x;
+    for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < p.n_vecs; o += step) {
+        const uint32_t cv = o % p.last_vecs;
+        uint32_t rem = o / p.last_vecs;
+        int32_t origin[MHLO_CUDA_MAX_RANK];
+#pragma unroll
+        for (int d = rank - 1; d >= 0; --d) {
+            origin[d] = static_cast<int32_t>(rem % p.out_shape[d]) * p.stride[d] - p.pad_low[d];
+            rem /= p.out_shape[d];
+        }
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = init;
+        uint32_t wi[MHLO_CUDA_MAX_RANK];
+        for (int d = 0; d < rank; ++d) wi[d] = 0;
+        for (uint32_t k = 0; k < p.window_count; ++k) {
+            int64_t off = cv;
+            bool inside = true;
+#pragma unroll
+            for (int d = 0; d < rank; ++d) {
+                const int32_t pos = origin[d] + static_cast<int32_t>(wi[d]) * p.window_dilation[d];
+                const int32_t src = DILATED ? pos / p.base_dilation[d] : pos;
+                inside = inside && pos >= 0 && src < static_cast<int32_t>(p.in_shape[d]) && (!DILATED || src * p.base_dilation[d] == pos);
+                off += src * p.in_stride_vecs[d];
+            }
+            float v[V];
+            if (inside) {
+                VecTraits<T>::unpack(__ldg(p.in + off), v);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] = init;
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = combine<float>(p.op, acc[e], v[e]);
+            for (int d = rank - 1; d >= 0; --d) {
+                if (++wi[d] < p.size[d]) break;
+                wi[d] = 0;
+            }
+        }
+        p.out[o] = VecTraits<T>::pack(acc);
+    }
+}
+
+bool vec_window_params(const WindowParams& p, int dtype, WindowVecParams* q) {
+    const int rank = p.w.rank;
+    if (rank < 2) return false;
+    if (p.op != MHLO_REDUCE_SUM && p.op != MHLO_REDUCE_MAX && p.op != MHLO_REDUCE_MIN && p.op != MHLO_REDUCE_PROD) return false;
+    const int64_t V = dtype == MHLO_DT_F32 ? 4 : 8;
+    const int L = rank - 1;
+    if (p.w.size[L] != 1 || p.w.stride[L] != 1 || p.w.pad_low[L] != 0 || p.w.base_dilation[L] != 1 || p.w.window_dilation[L] != 1) return false;
+    if (p.in_stride[L] != 1 || p.in_shape[L] != p.out_shape[L] || p.in_shape[L] % V) return false;
+    if (!aligned16(p.in) || !aligned16(p.out) || p.n_out / V >= (int64_t{1} << 31) || p.window_count >= (int64_t{1} << 31)) return false;
+    memset(q, 0, sizeof *q);
+    for (int d = 0; d < L; ++d) {
+        if (p.in_stride[d] % V) return false;
+        const int64_t reach = p.out_shape[d] * p.w.stride[d] + p.w.size[d] * p.w.window_dilation[d] + (p.w.pad_low[d] < 0 ? -p.w.pad_low[d] : p.w.pad_low[d]);
+        if (reach >= (int64_t{1} << 30) || p.in_shape[d] >= (int64_t{1} << 30)) return false;
+        q->out_shape[d] = static_cast<uint32_t>(p.out_shape[d]);
+        q->in_shape[d] = static_cast<uint32_t>(p.in_shape[d]);
+        q->size[d] = static_cast<uint32_t>(p.w.size[d]);
+        q->stride[d] = static_cast<int32_t>(p.w.stride[d]);
+        q->pad_low[d] = static_cast<int32_t>(p.w.pad_low[d]);
+        q->base_dilation[d] = static_cast<int32_t>(p.w.base_dilation[d]);
+        q->window_dilation[d] = static_cast<int32_t>(p.w.window_dilation[d]);
+        q->in_stride_vecs[d] = p.in_stride[d] / V;
+    }
+    q->in = static_cast<const uint4*>(p.in);
+    q->out = static_cast<uint4*>(p.out);
+    q->n_vecs = static_cast<uint32_t>(p.n_out / V);
+    q->last_vecs = static_cast<uint32_t>(p.in_shape[L] / V);
+    q->window_count = static_cast<uint32_t>(p.window_count);
+    q->rank = L;
+    q->init = p.init;
+    q->op = p.op;
+    return true;
+}
+
 // ---- scatter ---------------------------------------------------------------------------------------------------------
 
 struct ScatterParams {
@@ -524,6 +622,26 @@ extern "C" int mhlo_cuda_reduce_window(const mhlo_cuda_view* in, const mhlo_cuda
     p.out = out_dev;
     p.op = op;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in->dtype == MHLO_DT_F32 || in->dtype == MHLO_DT_F16 || in->dtype == MHLO_DT_BF16) {
+        WindowVecParams q;
+        if (vec_window_params(p, in->dtype, &q)) {
+            const int vgrid = grid_of(q.n_vecs, 256);
+            bool dilated = false;
+            for (int d = 0; d < q.rank; ++d) dilated |= q.base_dilation[d] != 1;
+            auto launch = [&](auto tag) {
+                using T = decltype(tag);
+                if (dilated) reduce_window_vec_kernel<T, 0, true><<<vgrid, 256, 0, s>>>(q);
+                else if (q.rank == 3) reduce_window_vec_kernel<T, 3, false><<<vgrid, 256, 0, s>>>(q);
+                else if (q.rank == 2) reduce_window_vec_kernel<T, 2, false><<<vgrid, 256, 0, s>>>(q);
+                else reduce_window_vec_kernel<T, 0, false><<<vgrid, 256, 0, s>>>(q);
+            };
+            if (in->dtype == MHLO_DT_F32) launch(float{});
+            else if (in->dtype == MHLO_DT_F16) launch(__half{});
+            else launch(__nv_bfloat16{});
+            MHLO_CUDA_CHECK_LAUNCH("reduce_window (vectors)");
+            return MHLO_CUDA_OK;
+        }
+    }
     const int grid = grid_of(p.n_out, 256);
     if (!with_element_type(in->dtype, [&](auto tag) { reduce_window_kernel<decltype(tag)><<<grid, 256, 0, s>>>(p); }))
         return fail(MHLO_CUDA_UNSUPPORTED, "reduce_window: dtype %d", in->dtype);

@@ -601,6 +601,14 @@ def window_scatter_sort_cases():
                                       padding=((0, 0), (1, 1), (1, 1), (0, 0))))
     out.append(reduce_window_case("reduce_window_maxpool_3x3_s2_pad", x, "f32", "maximum", "-inf", (1, 3, 3, 1), (2, 4, 4, 4), strides=(1, 2, 2, 1),
                                   padding=((0, 0), (0, 1), (0, 1), (0, 0))))
+    # channel counts that are whole 16-byte vectors take the vector kernel
+    for dt in ("bf16", "f16", "f32"):
+        if dt in NP:
+            xv = rand(rng, (2, 9, 9, 16), dt)
+            out.append(reduce_window_case(f"reduce_window_vectors_maxpool_{dt}", xv, dt, "maximum", "-inf", (1, 3, 3, 1), (2, 5, 5, 16),
+                                          strides=(1, 2, 2, 1), padding=((0, 0), (1, 1), (1, 1), (0, 0))))
+            out.append(reduce_window_case(f"reduce_window_vectors_dilated_sum_{dt}", xv, dt, "add", 0.25, (1, 2, 2, 1), (2, 15, 8, 16),
+                                          padding=((0, 0), (0, 0), (1, 0), (0, 0)), base_dil=(1, 2, 1, 1), win_dil=(1, 2, 2, 1)))
     xi = rand(rng, (5, 9), "i32")
     # dilated operand (9 -> 17), dilated window (3 taps spanning 5), negative low padding: (17 - 1 + 2 - 5) / 2 + 1 = 7
     out.append(reduce_window_case("reduce_window_dilations_i32", xi, "i32", "add", 0, (2, 3), (4, 7), strides=(1, 2),
