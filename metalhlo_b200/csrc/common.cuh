@@ -41,6 +41,33 @@ void clear_error();
         }                                                                                        \
     } while (0)
 
+// Division of n < 2^31 by a divisor fixed at launch: one multiply-high and a shift instead of the ~20 instructions of
+// a 32-bit division. mul = ceil(2^(31+s) / d) with s = ceil(log2 d) fits 32 bits, and floor(n * mul / 2^(31+s)) equals
+// floor(n / d) because the rounding error of mul contributes less than 2^-s <= 1/d.
+struct FastDiv {
+    uint32_t mul = 0, shift = 0, d = 1;
+    FastDiv() = default;
+    explicit FastDiv(uint32_t divisor) : d(divisor < 1 ? 1 : divisor) {
+        if (d > 1) {
+            uint32_t s = 0;
+            while ((uint64_t{1} << s) < d) ++s;
+            shift = s - 1;
+            mul = static_cast<uint32_t>(((uint64_t{1} << (31 + s)) + d - 1) / d);
+        }
+    }
+    __host__ __device__ __forceinline__ uint32_t div(uint32_t n) const {
+#ifdef __CUDA_ARCH__
+        return d == 1 ? n : (__umulhi(n, mul) >> shift);
+#else
+        return d == 1 ? n : static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> 32) >> shift;
+#endif
+    }
+    __host__ __device__ __forceinline__ void divmod(uint32_t n, uint32_t* q, uint32_t* r) const {
+        *q = div(n);
+        *r = n - *q * d;
+    }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- 16-byte vectors of T <-> fp32 ------------------------------------------------------------------

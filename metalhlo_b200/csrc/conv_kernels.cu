@@ -127,6 +127,7 @@ struct Im2colVecParams {
     uint4* out;
     uint32_t total_vecs, pitch_vecs, row_vecs, cg_vecs, n_rows, groups;
     int32_t ns;
+    FastDiv by_pitch, by_rows, by_cg, by_kernel[MHLO_CUDA_CONV_MAX_SPATIAL], by_out[MHLO_CUDA_CONV_MAX_SPATIAL];
     uint32_t kernel_size[MHLO_CUDA_CONV_MAX_SPATIAL], out_size[MHLO_CUDA_CONV_MAX_SPATIAL], in_size[MHLO_CUDA_CONV_MAX_SPATIAL];
     int32_t stride[MHLO_CUDA_CONV_MAX_SPATIAL], pad_low[MHLO_CUDA_CONV_MAX_SPATIAL], lhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL],
         rhs_dilation[MHLO_CUDA_CONV_MAX_SPATIAL], reverse[MHLO_CUDA_CONV_MAX_SPATIAL];
@@ -139,22 +140,20 @@ __global__ void __launch_bounds__(256) im2col_vec_kernel(const __grid_constant__
     const int ns = NS > 0 ? NS : p.ns;
     const uint32_t step = gridDim.x * blockDim.x;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vecs; i += step) {
-        const uint32_t kvec = i % p.pitch_vecs;
-        uint32_t rem = i / p.pitch_vecs;
-        uint32_t m = rem % p.n_rows;
-        const uint32_t g = rem / p.n_rows;
+        uint32_t kvec, rem, m, g;
+        p.by_pitch.divmod(i, &rem, &kvec);
+        p.by_rows.divmod(rem, &g, &m);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (kvec < p.row_vecs) {
-            const uint32_t icv = kvec % p.cg_vecs;
-            uint32_t kv = kvec / p.cg_vecs;
+            uint32_t icv, kv;
+            p.by_cg.divmod(kvec, &kv, &icv);
             int64_t off = static_cast<int64_t>(g) * p.cg_vecs + icv;
             bool inside = true;
 #pragma unroll
             for (int d = ns - 1; d >= 0; --d) {
-                uint32_t kd = kv % p.kernel_size[d];
-                kv /= p.kernel_size[d];
-                const uint32_t od = m % p.out_size[d];
-                m /= p.out_size[d];
+                uint32_t kd, od;
+                p.by_kernel[d].divmod(kv, &kv, &kd);
+                p.by_out[d].divmod(m, &m, &od);
                 if (p.reverse[d]) kd = p.kernel_size[d] - 1 - kd;
                 const int32_t pos = static_cast<int32_t>(od) * p.stride[d] - p.pad_low[d] + static_cast<int32_t>(kd) * p.rhs_dilation[d];
                 const int32_t src = DILATED ? pos / p.lhs_dilation[d] : pos;
@@ -177,7 +176,7 @@ bool vec_im2col_params(const ConvParams& p, int elem_bytes, Im2colVecParams* q) 
     if (!aligned16(p.in) || !aligned16(p.out)) return false;
     const int64_t total = c.feature_group_count * p.n_rows * (p.row_pitch / V);
     if (total >= (int64_t{1} << 31) || p.n_rows >= (int64_t{1} << 31)) return false;
-    memset(q, 0, sizeof *q);
+    *q = Im2colVecParams{};
     for (int d = 0; d < c.n_spatial; ++d) {
         if (c.in_spatial_stride[d] % V) return false;
         const int64_t reach = c.out_size[d] * c.stride[d] + c.kernel_size[d] * c.rhs_dilation[d] + (c.pad_low[d] < 0 ? -c.pad_low[d] : c.pad_low[d]);
@@ -202,6 +201,10 @@ bool vec_im2col_params(const ConvParams& p, int elem_bytes, Im2colVecParams* q) 
     q->groups = static_cast<uint32_t>(c.feature_group_count);
     q->ns = c.n_spatial;
     q->in_batch_vecs = c.in_batch_stride / V;
+    q->by_pitch = FastDiv(q->pitch_vecs);
+    q->by_rows = FastDiv(q->n_rows);
+    q->by_cg = FastDiv(q->cg_vecs);
+    for (int d = 0; d < c.n_spatial; ++d) { q->by_kernel[d] = FastDiv(q->kernel_size[d]); q->by_out[d] = FastDiv(q->out_size[d]); }
     return q->row_vecs > 0 && q->cg_vecs > 0;
 }
 

@@ -132,6 +132,7 @@ class Executable {
     std::vector<GraphSlot> graph_slots_;
     uint64_t graph_clock_ = 0;
     bool graphs_usable_ = true;  // cleared when a capture of this program failed
+    bool host_control_ = false;  // the program has a loop that the host drives: it synchronises, so it is never recorded
     int run_steps(const Ctx& c, bool debug, bool profile);
   public:
     int64_t graph_replays = 0;   // executions served by a graph launch

@@ -309,12 +309,14 @@ class Lowering {
         return v;
     }
 
+    // Steps go to the executable's list, or to the list of a loop region while one is being lowered.
+    std::vector<Executable::Step>* sink_ = nullptr;
     void add_step(const std::string& label, std::function<int(const Ctx&)> run, int launches = 1) {
         Executable::Step s;
         s.label = label;
         s.run = std::move(run);
         s.launches = launches;
-        exe_->steps_.push_back(std::move(s));
+        (sink_ ? *sink_ : exe_->steps_).push_back(std::move(s));
         exe_->launches_per_run_ += launches;
     }
 
@@ -521,13 +523,14 @@ class Lowering {
         if (n == "gather") return lower_gather(op);
         if (n == "convolution") return lower_convolution(op);
         if (n == "reduce_window") return lower_reduce_window(op);
+        if (n == "while") return lower_while(op);
         if (n == "scatter") return lower_scatter(op);
         if (n == "select_and_scatter") return lower_select_and_scatter(op);
         if (n == "sort") return lower_sort(op);
         if (n == "dynamic_slice") return lower_dynamic_slice(op);
         if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
         if (n == "custom_call") return lower_custom_call(op);
-        if (n == "tuple" || n == "get_tuple_element" || n == "while" || n == "if" || n == "case" || n == "call" || n == "fft" ||
+        if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         const int code = ew_opcode(n);
@@ -1086,6 +1089,101 @@ class Lowering {
             return mhlo_cuda_reduce_window(&xv, &w, kind, bind(di, c).base, const_cast<void*>(bind(dout, c).base), oshape.data(), c.stream);
         });
         set(op.results[0], out);
+    }
+
+    // stablehlo.while whose trip count is not static: the loop runs on the host. The loop-carried values live in arena
+    // buffers that both regions read; each iteration launches the condition's steps, reads the predicate back (one byte,
+    // one stream synchronisation), launches the body's steps and copies the body's results into the carried buffers (in
+    // two phases, through temporaries, so that a result that is a view of another carried value is read before that
+    // value is overwritten). Such a program is not replayed as a CUDA graph.
+    void lower_while(const Op& op) {
+        if (op.regions.size() != 2) fail_compile("while needs a condition and a body");
+        const size_t n = op.operands.size();
+        const Region& cond = *op.regions[0];
+        const Region& body = *op.regions[1];
+        if (cond.args.size() != n || body.args.size() != n || op.results.size() != n) fail_compile("while: region arguments do not match the operands");
+        std::vector<View> state;
+        for (size_t i = 0; i < n; ++i) {
+            const TensorType& t = f_.type_of(op.operands[i]);
+            View st = dense_view(new_arena(std::max<int64_t>(t.bytes(), 1)), t);
+            copy_view(get(op.operands[i]), st, "while.init");
+            state.push_back(st);
+            set(cond.args[i], st);
+            set(body.args[i], st);
+        }
+        auto lower_region = [&](const Region& r, std::vector<Executable::Step>* steps, std::vector<int>* returned) {
+            std::vector<Executable::Step>* outer = sink_;
+            sink_ = steps;
+            bool done = false;
+            for (const Op& ro : r.ops) {
+                if (ro.dead) continue;
+                if (ro.name == "return") { *returned = ro.operands; done = true; break; }
+                lower(ro);
+            }
+            sink_ = outer;
+            if (!done) fail_compile("while: a region does not return");
+        };
+        auto cond_steps = std::make_shared<std::vector<Executable::Step>>();
+        auto body_steps = std::make_shared<std::vector<Executable::Step>>();
+        std::vector<int> cond_ret, body_ret;
+        lower_region(cond, cond_steps.get(), &cond_ret);
+        if (cond_ret.size() != 1 || f_.type_of(cond_ret[0]).count() != 1) fail_compile("while: the condition must return one scalar");
+        View pred;
+        {
+            std::vector<Executable::Step>* outer = sink_;
+            sink_ = cond_steps.get();
+            // the predicate as one byte in its own buffer (0 / 1), whatever view or integer type the region produced
+            TensorType pt;
+            pt.dtype = DType::I1;
+            pred = dense_view(new_arena(256), pt);
+            View src = get(cond_ret[0]);
+            src.type.shape.clear();
+            src.strides.clear();
+            DevView ds = dev(src), dp = dev(pred);
+            keep_alive(src); keep_alive(pred);
+            add_step("while.predicate", [ds, dp](const Ctx& c) {
+                mhlo_cuda_view sv = bind(ds, c), dv = bind(dp, c);
+                mhlo_cuda_ew_inst inst = {MHLO_EW_COPY, 0, 0, 0, 0.0};
+                return mhlo_cuda_elementwise_to_view(&sv, 1, &inst, 1, &dv, c.stream);
+            });
+            sink_ = outer;
+        }
+        lower_region(body, body_steps.get(), &body_ret);
+        if (body_ret.size() != n) fail_compile("while: the body must return one value per operand");
+        {
+            std::vector<Executable::Step>* outer = sink_;
+            sink_ = body_steps.get();
+            std::vector<std::pair<size_t, View>> staged;
+            for (size_t i = 0; i < n; ++i) {
+                const View& r = get(body_ret[i]);
+                if (r.buf == state[i].buf && r.offset == state[i].offset && r.strides == state[i].strides) continue;  // carried unchanged
+                View tmp = dense_view(new_arena(std::max<int64_t>(state[i].type.bytes(), 1)), state[i].type);
+                copy_view(r, tmp, "while.stage");
+                staged.emplace_back(i, tmp);
+            }
+            for (const auto& st : staged) copy_view(st.second, state[st.first], "while.carry");
+            sink_ = outer;
+        }
+        DevView dpred = dev(pred);
+        for (const View& st : state) keep_alive(st);
+        keep_alive(pred);
+        exe_->host_control_ = true;
+        const int per_iteration = static_cast<int>(cond_steps->size() + body_steps->size());
+        add_step("while(" + std::to_string(per_iteration) + " steps per iteration)", [cond_steps, body_steps, dpred](const Ctx& c) -> int {
+            constexpr int64_t kMaxIterations = 100000000;  // a loop that never ends is reported, not run forever
+            for (int64_t it = 0; it < kMaxIterations; ++it) {
+                for (const Executable::Step& s : *cond_steps)
+                    if (int st = s.run(c)) return st;
+                unsigned char flag = 0;
+                if (int st = mhlo_cuda_download(&flag, bind(dpred, c).base, 1, c.stream)) return st;
+                if (int st = mhlo_cuda_stream_sync(c.stream)) return st;
+                if (!flag) return 0;
+                for (const Executable::Step& s : *body_steps)
+                    if (int st = s.run(c)) return st;
+            }
+            return static_cast<int>(MHLO_CUDA_EXECUTION_FAILED);  // more than 1e8 iterations
+        }, 0);
+        for (size_t i = 0; i < n; ++i) set(op.results[i], state[i]);
     }
 
     // stablehlo.select_and_scatter: the result is filled with the init value, then every source element is combined
@@ -1671,7 +1769,7 @@ int Executable::execute(const void* const* inputs, void* const* outputs, void* s
     }();
     // Graph replay needs a capturable stream, a program worth recording and no per-step host work.
     constexpr size_t kMinStepsForGraph = 8, kMaxSlots = 4;
-    if (!graphs_enabled || !graphs_usable_ || stream == nullptr || debug || profile || steps_.size() < kMinStepsForGraph)
+    if (!graphs_enabled || !graphs_usable_ || host_control_ || stream == nullptr || debug || profile || steps_.size() < kMinStepsForGraph)
         return run_steps(c, debug, profile);
 
     std::vector<const void*> key;

@@ -6,6 +6,7 @@
 // `stablehlo.case` become straight-line code too: every branch is computed and the results are picked with `select`,
 // which is exact because StableHLO ops have no side effects (the reference runs them through MPSGraph's if/else,
 // Sources/MetalHLOCore/MPSGraph/MPSGraphCompiler.swift, with the same results).
+#include <functional>
 #include <map>
 
 #include "compiler.h"
@@ -416,16 +417,48 @@ bool flatten_maps(Function& f) {
     return changed;
 }
 
-Function flatten_main(Module& m) {
-    // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat until neither changes
-    for (int round = 0; round < kMaxInlineRounds; ++round) {
-        const bool a = inline_calls(m);
-        const bool b = unroll_static_whiles(m.main());
-        const bool c = flatten_conditionals(m.main());
-        const bool d = flatten_maps(m.main());
-        if (!a && !b && !c && !d) break;
+namespace {
+
+// Runs `pass` (which works on f.ops) on the region bodies of the loops that stay loops, innermost included, by letting
+// each body stand in for the function's op list while the pass runs.
+bool sweep_loop_regions(Function& f, const std::function<bool()>& pass, int depth) {
+    bool changed = false;
+    std::vector<std::shared_ptr<Region>> regions;
+    for (Op& op : f.ops)
+        if (!op.dead && op.name == "while")
+            for (auto& r : op.regions) regions.push_back(r);
+    for (auto& r : regions) {
+        std::vector<Op> saved;
+        saved.swap(f.ops);
+        f.ops.swap(r->ops);
+        changed |= pass();
+        if (depth < 8) changed |= sweep_loop_regions(f, pass, depth + 1);
+        f.ops.swap(r->ops);
+        saved.swap(f.ops);
     }
-    return m.main();
+    return changed;
+}
+
+}  // namespace
+
+Function flatten_main(Module& m) {
+    // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat
+    // until nothing changes
+    Function& main = m.main();
+    auto all = [&]() {
+        const bool a = inline_calls(m);
+        const bool b = unroll_static_whiles(main);
+        const bool c = flatten_conditionals(main);
+        const bool d = flatten_maps(main);
+        return a || b || c || d;
+    };
+    for (int round = 0; round < kMaxInlineRounds; ++round) {
+        const bool top = all();
+        const bool inner = sweep_loop_regions(main, all, 0);  // bodies of the loops whose trip count is not static
+        if (!top && !inner) break;
+    }
+    main.compact();
+    return main;
 }
 
 }  // namespace mhlo

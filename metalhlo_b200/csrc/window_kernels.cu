@@ -192,6 +192,139 @@ __global__ void __launch_bounds__(256) reduce_window_vec_kernel(const __grid_con
     }
 }
 
+// Accumulator of one 16-byte vector of a pooling window. Sums (and products) run in fp32; maximum and minimum of 16-bit
+// types compare the packed pairs directly, which is exact and needs no conversion.
+template <typename T, int OP, bool PACKED = (OP == MHLO_REDUCE_MAX || OP == MHLO_REDUCE_MIN) && !std::is_same<T, float>::value>
+struct PoolAcc;
+
+template <typename T, int OP>
+struct PoolAcc<T, OP, false> {
+    static constexpr int V = VecTraits<T>::kElems;
+    float acc[V];
+    float init;
+    __device__ __forceinline__ void start(float i) {
+        init = i;
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = i;
+    }
+    __device__ __forceinline__ void take(const uint4& raw) {
+        float v[V];
+        VecTraits<T>::unpack(raw, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = combine<float>(OP, acc[e], v[e]);
+    }
+    __device__ __forceinline__ void take_padding() {
+        if (OP == MHLO_REDUCE_MAX || OP == MHLO_REDUCE_MIN) return;  // the accumulator already dominates the init value
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = combine<float>(OP, acc[e], init);
+    }
+    __device__ __forceinline__ uint4 result() const { return VecTraits<T>::pack(acc); }
+};
+
+template <typename T, int OP>
+struct PoolAcc<T, OP, true> {
+    using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+    T2 acc[4];
+    __device__ __forceinline__ void start(float i) {
+        T2 v;
+        if constexpr (std::is_same<T, __half>::value) v = __float2half2_rn(i); else v = __float2bfloat162_rn(i);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = v;
+    }
+    __device__ __forceinline__ void take(const uint4& raw) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const T2 v = *reinterpret_cast<const T2*>(&w[e]);
+            acc[e] = OP == MHLO_REDUCE_MAX ? __hmax2_nan(acc[e], v) : __hmin2_nan(acc[e], v);
+        }
+    }
+    __device__ __forceinline__ void take_padding() {}
+    __device__ __forceinline__ uint4 result() const {
+        return make_uint4(*reinterpret_cast<const uint32_t*>(&acc[0]), *reinterpret_cast<const uint32_t*>(&acc[1]),
+                          *reinterpret_cast<const uint32_t*>(&acc[2]), *reinterpret_cast<const uint32_t*>(&acc[3]));
+    }
+};
+
+// The common pooling shape: three leading dimensions (batch, rows, columns of NHWC), no base dilation, offsets that fit
+// 32 bits. The window is walked by nested loops with running offsets; divisions use precomputed reciprocals.
+struct Pool3Params {
+    const uint4* in;
+    uint4* out;
+    const void* init;
+    uint32_t n_vecs;
+    FastDiv by_last, by_out[3];
+    int32_t in_shape[3], size[3], stride[3], pad_low[3], window_dilation[3], in_stride_vecs[3];
+};
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) pool3_vec_kernel(const __grid_constant__ Pool3Params p) {
+    const float init = widen<T>(*static_cast<const T*>(p.init));
+    const uint32_t step = gridDim.x * blockDim.x;
+    for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < p.n_vecs; o += step) {
+        uint32_t rem, cv, o0, o1, o2;
+        p.by_last.divmod(o, &rem, &cv);
+        p.by_out[2].divmod(rem, &rem, &o2);
+        p.by_out[1].divmod(rem, &o0, &o1);
+        const int32_t b0 = static_cast<int32_t>(o0) * p.stride[0] - p.pad_low[0];
+        const int32_t b1 = static_cast<int32_t>(o1) * p.stride[1] - p.pad_low[1];
+        const int32_t b2 = static_cast<int32_t>(o2) * p.stride[2] - p.pad_low[2];
+        PoolAcc<T, OP> acc;
+        acc.start(init);
+        for (int32_t w0 = 0, p0 = b0; w0 < p.size[0]; ++w0, p0 += p.window_dilation[0]) {
+            const bool ok0 = static_cast<uint32_t>(p0) < static_cast<uint32_t>(p.in_shape[0]);
+            const int32_t off0 = p0 * p.in_stride_vecs[0] + static_cast<int32_t>(cv);
+            for (int32_t w1 = 0, p1 = b1; w1 < p.size[1]; ++w1, p1 += p.window_dilation[1]) {
+                const bool ok1 = ok0 && static_cast<uint32_t>(p1) < static_cast<uint32_t>(p.in_shape[1]);
+                const int32_t off1 = off0 + p1 * p.in_stride_vecs[1];
+                for (int32_t w2 = 0, p2 = b2; w2 < p.size[2]; ++w2, p2 += p.window_dilation[2]) {
+                    if (ok1 && static_cast<uint32_t>(p2) < static_cast<uint32_t>(p.in_shape[2])) acc.take(__ldg(p.in + off1 + p2 * p.in_stride_vecs[2]));
+                    else acc.take_padding();
+                }
+            }
+        }
+        p.out[o] = acc.result();
+    }
+}
+
+// Fills the parameters of pool3_vec_kernel from the vector parameters; false when the shape does not fit it.
+bool pool3_params(const WindowVecParams& q, Pool3Params* r) {
+    if (q.rank != 3) return false;
+    int64_t span = q.last_vecs;
+    for (int d = 0; d < 3; ++d) {
+        if (q.base_dilation[d] != 1) return false;
+        const int64_t st = q.in_stride_vecs[d] < 0 ? -q.in_stride_vecs[d] : q.in_stride_vecs[d];
+        span += (static_cast<int64_t>(q.in_shape[d]) + q.size[d] * q.window_dilation[d] + (q.pad_low[d] < 0 ? -q.pad_low[d] : q.pad_low[d])) * st;
+    }
+    if (span >= (int64_t{1} << 31)) return false;
+    *r = Pool3Params{};
+    r->in = q.in;
+    r->out = q.out;
+    r->init = q.init;
+    r->n_vecs = q.n_vecs;
+    r->by_last = FastDiv(q.last_vecs);
+    for (int d = 0; d < 3; ++d) {
+        r->by_out[d] = FastDiv(q.out_shape[d]);
+        r->in_shape[d] = static_cast<int32_t>(q.in_shape[d]);
+        r->size[d] = static_cast<int32_t>(q.size[d]);
+        r->stride[d] = q.stride[d];
+        r->pad_low[d] = q.pad_low[d];
+        r->window_dilation[d] = q.window_dilation[d];
+        r->in_stride_vecs[d] = static_cast<int32_t>(q.in_stride_vecs[d]);
+    }
+    return true;
+}
+
+template <typename T>
+bool launch_pool3(const Pool3Params& r, int op, int grid, cudaStream_t s) {
+    switch (op) {
+        case MHLO_REDUCE_SUM: pool3_vec_kernel<T, MHLO_REDUCE_SUM><<<grid, 256, 0, s>>>(r); return true;
+        case MHLO_REDUCE_MAX: pool3_vec_kernel<T, MHLO_REDUCE_MAX><<<grid, 256, 0, s>>>(r); return true;
+        case MHLO_REDUCE_MIN: pool3_vec_kernel<T, MHLO_REDUCE_MIN><<<grid, 256, 0, s>>>(r); return true;
+        default: return false;
+    }
+}
+
 bool vec_window_params(const WindowParams& p, int dtype, WindowVecParams* q) {
     const int rank = p.w.rank;
     if (rank < 2) return false;
@@ -626,6 +759,16 @@ extern "C" int mhlo_cuda_reduce_window(const mhlo_cuda_view* in, const mhlo_cuda
         WindowVecParams q;
         if (vec_window_params(p, in->dtype, &q)) {
             const int vgrid = grid_of(q.n_vecs, 256);
+            Pool3Params r;
+            if (pool3_params(q, &r)) {
+                const bool launched = in->dtype == MHLO_DT_F32 ? launch_pool3<float>(r, p.op, vgrid, s)
+                                    : in->dtype == MHLO_DT_F16 ? launch_pool3<__half>(r, p.op, vgrid, s)
+                                                               : launch_pool3<__nv_bfloat16>(r, p.op, vgrid, s);
+                if (launched) {
+                    MHLO_CUDA_CHECK_LAUNCH("reduce_window (pooling)");
+                    return MHLO_CUDA_OK;
+                }
+            }
             bool dilated = false;
             for (int d = 0; d < q.rank; ++d) dilated |= q.base_dilation[d] != 1;
             auto launch = [&](auto tag) {

@@ -418,6 +418,65 @@ def widening_cases():
 """
     for v in (1, 0):
         out.append((f"if_{'true' if v else 'false'}", if_text, [np.asarray(v, np.int32), x48, y48]))
+    # ---- while with a data-dependent trip count (lax.while_loop): halve until the largest magnitude drops under a bound
+    out.append(("while_dynamic_halving", f"""module @jit_halve {{
+  func.func public @main(%arg0: {t48}) -> ({t48}, tensor<i32>) {{
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %0:2 = stablehlo.while(%iterArg = %arg0, %iterArg_0 = %c) : {t48}, tensor<i32>
+     cond {{
+      %1 = stablehlo.abs %iterArg : {t48}
+      %cst = stablehlo.constant dense<0xFF800000> : tensor<f32>
+      %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.maximum across dimensions = [0, 1] : ({t48}, tensor<f32>) -> tensor<f32>
+      %cst_1 = stablehlo.constant dense<3.000000e-01> : tensor<f32>
+      %3 = stablehlo.compare  GT, %2, %cst_1,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      stablehlo.return %3 : tensor<i1>
+    }} do {{
+      %cst = stablehlo.constant dense<5.000000e-01> : tensor<f32>
+      %1 = stablehlo.broadcast_in_dim %cst, dims = [] : (tensor<f32>) -> {t48}
+      %2 = stablehlo.multiply %iterArg, %1 : {t48}
+      %c_1 = stablehlo.constant dense<1> : tensor<i32>
+      %3 = stablehlo.add %iterArg_0, %c_1 : tensor<i32>
+      stablehlo.return %2, %3 : {t48}, tensor<i32>
+    }}
+    return %0#0, %0#1 : {t48}, tensor<i32>
+  }}
+}}
+""", [x48]))
+    # carried values that trade places (a result is a view of another carried value), a call and an if in the body
+    out.append(("while_dynamic_swap_call_if", f"""module @jit_fib {{
+  func.func public @main(%arg0: tensor<8xf32>, %arg1: tensor<8xf32>, %arg2: tensor<i32>) -> (tensor<8xf32>, tensor<8xf32>, tensor<i32>) {{
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %0:3 = stablehlo.while(%iterArg = %arg0, %iterArg_0 = %arg1, %iterArg_1 = %c) : tensor<8xf32>, tensor<8xf32>, tensor<i32>
+     cond {{
+      %1 = stablehlo.compare  LT, %iterArg_1, %arg2,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    }} do {{
+      %1 = call @combine(%iterArg, %iterArg_0) : (tensor<8xf32>, tensor<8xf32>) -> tensor<8xf32>
+      %c_1 = stablehlo.constant dense<2> : tensor<i32>
+      %2 = stablehlo.remainder %iterArg_1, %c_1 : tensor<i32>
+      %c_2 = stablehlo.constant dense<0> : tensor<i32>
+      %3 = stablehlo.compare  EQ, %2, %c_2,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      %4 = "stablehlo.if"(%3) ({{
+        stablehlo.return %1 : tensor<8xf32>
+      }}, {{
+        %5 = stablehlo.negate %1 : tensor<8xf32>
+        stablehlo.return %5 : tensor<8xf32>
+      }}) : (tensor<i1>) -> tensor<8xf32>
+      %c_3 = stablehlo.constant dense<1> : tensor<i32>
+      %6 = stablehlo.add %iterArg_1, %c_3 : tensor<i32>
+      stablehlo.return %iterArg_0, %4, %6 : tensor<8xf32>, tensor<8xf32>, tensor<i32>
+    }}
+    return %0#0, %0#1, %0#2 : tensor<8xf32>, tensor<8xf32>, tensor<i32>
+  }}
+  func.func private @combine(%arg0: tensor<8xf32>, %arg1: tensor<8xf32>) -> tensor<8xf32> {{
+    %cst = stablehlo.constant dense<5.000000e-01> : tensor<8xf32>
+    %0 = stablehlo.multiply %arg0, %cst : tensor<8xf32>
+    %1 = stablehlo.add %0, %arg1 : tensor<8xf32>
+    return %1 : tensor<8xf32>
+  }}
+}}
+""", [x48[0].copy(), y48[0].copy(), np.asarray(5, np.int32)]))
+    out.append(("while_dynamic_zero_trips", out[-1][1], [x48[0].copy(), y48[0].copy(), np.asarray(0, np.int32)]))
     case_text = f"""module @jit_switch {{
   func.func public @main(%arg0: tensor<i32>, %arg1: {t48}) -> ({t48}) {{
     %0 = "stablehlo.case"(%arg0) ({{
@@ -609,6 +668,10 @@ def window_scatter_sort_cases():
                                           strides=(1, 2, 2, 1), padding=((0, 0), (1, 1), (1, 1), (0, 0))))
             out.append(reduce_window_case(f"reduce_window_vectors_dilated_sum_{dt}", xv, dt, "add", 0.25, (1, 2, 2, 1), (2, 15, 8, 16),
                                           padding=((0, 0), (0, 0), (1, 0), (0, 0)), base_dil=(1, 2, 1, 1), win_dil=(1, 2, 2, 1)))
+    out.append(reduce_window_case("reduce_window_vectors_padded_sum_nonzero_init", rand(rng, (2, 6, 6, 8), "f32"), "f32", "add", 0.5, (1, 2, 2, 1),
+                                  (2, 7, 7, 8), padding=((0, 0), (1, 1), (1, 1), (0, 0))))
+    out.append(reduce_window_case("reduce_window_vectors_min_window_dilation", rand(rng, (2, 9, 9, 8), "f32"), "f32", "minimum", "inf", (1, 2, 3, 1),
+                                  (2, 7, 3, 8), strides=(1, 1, 2, 1), win_dil=(1, 2, 2, 1)))
     xi = rand(rng, (5, 9), "i32")
     # dilated operand (9 -> 17), dilated window (3 taps spanning 5), negative low padding: (17 - 1 + 2 - 5) / 2 + 1 = 7
     out.append(reduce_window_case("reduce_window_dilations_i32", xi, "i32", "add", 0, (2, 3), (4, 7), strides=(1, 2),
