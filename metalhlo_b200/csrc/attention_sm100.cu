@@ -215,6 +215,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     TileWalk walk(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    // the set-up above touched only shared memory and TMEM: it may overlap the previous kernel's tail
+    grid_dependency_wait();
+    grid_dependency_release();
 
     if (warp == 0) {
         // ---------------- producer: runs ahead of the other warps as far as the rings allow, across tile boundaries
@@ -523,7 +526,8 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
     }
     const int64_t tiles = (s.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM) * s.heads * s.batch;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>((tiles + 1) / 2, sm_count));
-    kernel<<<grid, kAttnThreads, L::kTotal, stream>>>(mq, mk, mv, p);
+    const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kAttnThreads), L::kTotal, stream, mq, mk, mv, p);
+    if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of attention_tcgen05 failed: %s", cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH("attention_tcgen05");
     return MHLO_CUDA_OK;
 }

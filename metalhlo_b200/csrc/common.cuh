@@ -68,6 +68,32 @@ struct FastDiv {
     }
 };
 
+// Programmatic dependent launch: a kernel launched through launch_dependent() may start while its predecessor in the
+// stream is still running; it must call grid_dependency_wait() before it touches global memory the predecessor writes
+// (or reads something the predecessor may still be reading before overwriting it). grid_dependency_release() lets the
+// next kernel of the stream begin its own prologue. Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// METALHLO_PDL=0 turns the overlap off (every launch then waits for the previous kernel to finish, as usual).
+bool dependent_launch_enabled();
+
+// Launches `kernel`, which calls grid_dependency_wait(), with the programmatic-serialisation attribute when enabled.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- 16-byte vectors of T <-> fp32 ------------------------------------------------------------------

@@ -133,6 +133,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared memory and TMEM: it may overlap the previous kernel's tail
+    grid_dependency_wait();
+    grid_dependency_release();
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -578,7 +581,8 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         attr_set = true;
     }
     const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
-    kernel<<<grid, kGemmThreads, L::kTotal, stream>>>(map_a, map_b, map_c, p);
+    const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, map_a, map_b, map_c, p);
+    if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of gemm_tcgen05 failed: %s", cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
 }

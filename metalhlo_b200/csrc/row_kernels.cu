@@ -97,6 +97,9 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 #pragma unroll
     for (int i = 0; i < VPT; ++i) live[i] = FULL || (tid + i * nthreads < nvec);
 
+    grid_dependency_wait();  // gamma / beta may be results of the previous kernel too
+    grid_dependency_release();
+
     if (tid < 32) {
         red[0][tid] = (OP == kSoftmax) ? -INFINITY : 0.f;
         red[1][tid] = 0.f;
@@ -461,8 +464,9 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         if (grid > static_cast<int64_t>(kNumSMs) * per_sm) grid = static_cast<int64_t>(kNumSMs) * per_sm;
     }
     if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
-    kernel<<<static_cast<int>(grid), threads, smem, stream>>>(xp, gp, bp, yp, rows, static_cast<int>(len), eps,
-                                                                static_cast<const T*>(res), static_cast<T*>(sum_out));
+    const cudaError_t launched = launch_dependent(kernel, dim3(static_cast<unsigned>(grid)), dim3(static_cast<unsigned>(threads)), smem, stream, xp, gp, bp, yp,
+                                                  rows, static_cast<int>(len), eps, static_cast<const T*>(res), static_cast<T*>(sum_out));
+    if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of %s failed: %s", what, cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH(what);
     return MHLO_CUDA_OK;
 }

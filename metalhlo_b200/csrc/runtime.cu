@@ -3,9 +3,19 @@
 // (Sources/MetalHLOCore/Runtime/IntegratedExecutor.swift:106-141,182-190,232-252).
 #include <cstring>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace mhlo {
+
+bool dependent_launch_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("METALHLO_PDL");
+        return v != nullptr && v[0] == '1';
+    }();
+    return on;
+}
 
 static thread_local char g_error[1024] = "";
 
