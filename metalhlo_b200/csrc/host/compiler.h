@@ -47,6 +47,8 @@ bool unroll_static_whiles(Function& f);
 bool flatten_conditionals(Function& f);
 // Replaces stablehlo.map by its computation applied to whole tensors.
 bool flatten_maps(Function& f);
+// Replaces chlo.top_k by iota + stable descending sort + slices.
+bool flatten_top_k(Function& f);
 // All four, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
 

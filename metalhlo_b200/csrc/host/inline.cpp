@@ -417,6 +417,57 @@ bool flatten_maps(Function& f) {
     return changed;
 }
 
+// chlo.top_k(x, k): the k largest entries of the last dimension and their positions, ties in index order. Rewritten to
+// iota + stable descending sort of (x, iota) + two slices, which the sort kernel and zero-copy slices then run.
+bool flatten_top_k(Function& f) {
+    bool any = false;
+    std::vector<Op> out;
+    for (Op& op : f.ops) {
+        if (op.dead || op.name != "top_k") {
+            out.push_back(std::move(op));
+            continue;
+        }
+        if (op.operands.size() != 1 || op.results.size() != 2) fail_compile("top_k takes one operand and gives values and indices");
+        const TensorType xt = f.type_of(op.operands[0]);
+        const int rank = xt.rank();
+        const int64_t k = op.int_attr("k", -1);
+        if (rank < 1 || k < 0 || k > xt.shape.back()) fail_compile("top_k: k out of range for " + xt.str());
+        TensorType it = xt;
+        it.dtype = op.result_types[1].dtype;
+        Op iota = simple_op(f, "iota", {}, it);
+        iota.attrs["iota_dimension"] = Attr::make_int(rank - 1);
+        Op sort;
+        sort.name = "sort";
+        sort.dialect = "stablehlo";
+        sort.operands = {op.operands[0], iota.results[0]};
+        sort.result_types = {xt, it};
+        sort.results = {f.new_value(xt, ""), f.new_value(it, "")};
+        sort.attrs["dimension"] = Attr::make_int(rank - 1);
+        sort.attrs["is_stable"] = Attr::make_bool(true);
+        sort.attrs["sort_order"] = Attr::make_string("descending");
+        std::vector<int64_t> start(static_cast<size_t>(rank), 0), limit = xt.shape, stride(static_cast<size_t>(rank), 1);
+        limit.back() = k;
+        out.push_back(iota);
+        out.push_back(sort);
+        for (int r = 0; r < 2; ++r) {
+            Op sl;
+            sl.name = "slice";
+            sl.dialect = "stablehlo";
+            sl.operands = {sort.results[static_cast<size_t>(r)]};
+            sl.result_types = {op.result_types[static_cast<size_t>(r)]};
+            sl.results = {op.results[static_cast<size_t>(r)]};  // the slices define the top_k's own result values
+            sl.attrs["start_indices"] = Attr::make_ints(start);
+            sl.attrs["limit_indices"] = Attr::make_ints(limit);
+            sl.attrs["strides"] = Attr::make_ints(stride);
+            out.push_back(sl);
+        }
+        any = true;
+    }
+    f.ops.swap(out);
+    f.compact();
+    return any;
+}
+
 namespace {
 
 // Runs `pass` (which works on f.ops) on the region bodies of the loops that stay loops, innermost included, by letting
@@ -450,7 +501,8 @@ Function flatten_main(Module& m) {
         const bool b = unroll_static_whiles(main);
         const bool c = flatten_conditionals(main);
         const bool d = flatten_maps(main);
-        return a || b || c || d;
+        const bool e = flatten_top_k(main);
+        return a || b || c || d || e;
     };
     for (int round = 0; round < kMaxInlineRounds; ++round) {
         const bool top = all();

@@ -808,6 +808,8 @@ class Parser {
                 names_[n] = v;
             }
         } else {
+            if (result_names.size() > 1 && op.result_types.size() == 1 && in_types.size() == result_names.size())
+                op.result_types = in_types;  // "%a, %b = op %x, %y : t0, t1": one type per result
             if (op.result_types.size() < result_names.size())
                 fail_parse("operation " + op.name + " binds " + std::to_string(result_names.size()) +
                            " results but its type lists " + std::to_string(op.result_types.size()));
@@ -982,6 +984,23 @@ class Parser {
             }
             if (c == '(') {  // reducer(...) block header of the pretty reduce with a region, or call operands
                 if (op->name == "call" || op->name == "convolution") { ++p_; operand_list(op, ')'); continue; }
+                if (op->name == "top_k") {  // chlo.top_k(%x, k = 5)
+                    ++p_;
+                    skip();
+                    while (cur() != ')') {
+                        if (cur() == '%') {
+                            op->operands.push_back(lookup(value_name()));
+                        } else {
+                            const std::string key = ident();
+                            expect('=');
+                            op->attrs[key] = attr_value();
+                        }
+                        if (!accept(',')) break;
+                        skip();
+                    }
+                    expect(')');
+                    continue;
+                }
                 skip_balanced('(', ')');
                 continue;
             }

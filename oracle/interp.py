@@ -448,7 +448,16 @@ class ModuleParser(Scanner):
                 ts.append(self.type())
             if self.accept("->"):
                 ins = ts
-                outs = [self.type()]
+                if self.peek() == "(":  # "t -> (t0, t1)"
+                    self.p += 1
+                    outs = []
+                    while self.peek() != ")":
+                        outs.append(self.type())
+                        if not self.accept(","):
+                            break
+                    self.expect(")")
+                else:
+                    outs = [self.type()]
             else:
                 ins, outs = ts, [ts[-1]]
                 op.bare_type_list = True
@@ -658,6 +667,18 @@ class ModuleParser(Scanner):
             elif c == "(" and name == "convolution":
                 self.p += 1
                 self.operands(op, ")")
+            elif c == "(" and name == "top_k":  # chlo.top_k(%x, k = 5)
+                self.p += 1
+                while self.peek() != ")":
+                    if self.peek() == "%":
+                        op.operands.append(self.value())
+                    else:
+                        key = self.ident()
+                        self.expect("=")
+                        op.attrs[key] = self.attr()
+                    if not self.accept(","):
+                        break
+                self.expect(")")
             elif c == "(":
                 self.balanced("(", ")")
             elif self.peek(2) == "<{":
@@ -840,6 +861,15 @@ class Interpreter:
         for idx in np.ndindex(*t.shape):
             out[idx] = self._apply(op.regions[0], env, [x[idx] for x in a])[0].reshape(())
         return out
+
+    def op_top_k(self, op, a, t):
+        """chlo.top_k: the k largest entries along the last dimension (total order, NaN largest) and their positions,
+        equal entries in index order."""
+        k = int(op.attrs["k"])
+        x = a[0]
+        key = _total_order_key(x, op.in_types[0].dtype)
+        order = np.argsort(~key, axis=-1, kind="stable")[..., :k]
+        return [np.take_along_axis(x, order, axis=-1), order.astype(op.types[1].np_dtype())]
 
     def op_get_dimension_size(self, op, a, t):
         return np.asarray(a[0].shape[int(op.attrs.get("dim", op.attrs.get("dimension", 0)))], dtype=t.np_dtype())

@@ -647,6 +647,55 @@ def sort_case(name, arrays, dts, dimension, direction="LT", swapped=False):
     return (name, func(types, types, body, results), list(arrays))
 
 
+THREEFRY_ROTATIONS = (13, 15, 26, 6, 17, 29, 16, 24)
+
+
+def threefry2x32_text(n):
+    """Threefry-2x32 with 20 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3") over n counters, as the
+    chain of ui32 adds, shifts, ors and xors that jax.random's default generator lowers to. Arguments: key [2], counters
+    x0 [n], x1 [n]; results: the two output words."""
+    t, tk, ts = tt((n,), "ui32"), tt((2,), "ui32"), "tensor<ui32>"
+    lines = []
+    k = [0]
+
+    def v():
+        k[0] += 1
+        return f"%t{k[0]}"
+
+    def emit(text):
+        lines.append("    " + text)
+
+    def splat(value):
+        c, b = v(), v()
+        emit(f"{c} = stablehlo.constant dense<{value}> : {ts}")
+        emit(f"{b} = stablehlo.broadcast_in_dim {c}, dims = [] : ({ts}) -> {t}")
+        return b
+
+    def binary(op, a, b):
+        r = v()
+        emit(f"{r} = stablehlo.{op} {a}, {b} : {t}")
+        return r
+
+    keys = []
+    for i in range(2):
+        sl, rs, bc = v(), v(), v()
+        emit(f"{sl} = stablehlo.slice %arg0 [{i}:{i + 1}] : ({tk}) -> tensor<1xui32>")
+        emit(f"{rs} = stablehlo.reshape {sl} : (tensor<1xui32>) -> {ts}")
+        emit(f"{bc} = stablehlo.broadcast_in_dim {rs}, dims = [] : ({ts}) -> {t}")
+        keys.append(bc)
+    keys.append(binary("xor", binary("xor", keys[0], keys[1]), splat(0x1BD11BDA)))
+    x0 = binary("add", "%arg1", keys[0])
+    x1 = binary("add", "%arg2", keys[1])
+    for group in range(5):
+        for r in THREEFRY_ROTATIONS[4 * (group % 2):4 * (group % 2) + 4]:
+            x0 = binary("add", x0, x1)
+            rot = binary("or", binary("shift_left", x1, splat(r)), binary("shift_right_logical", x1, splat(32 - r)))
+            x1 = binary("xor", rot, x0)
+        x0 = binary("add", x0, keys[(group + 1) % 3])
+        x1 = binary("add", binary("add", x1, keys[(group + 2) % 3]), splat(group + 1))
+    return func([tk, t, t], [t, t], "\n".join(lines), f"{x0}, {x1}")
+
+
 def window_scatter_sort_cases():
     rng = np.random.default_rng(4242)
     out = []
@@ -759,6 +808,18 @@ def window_scatter_sort_cases():
             continue
         k = rand(rng, (3, 50), dt)
         out.append(sort_case(f"sort_pairs_{dt}", [k, rand(rng, (3, 50), "f32")], [dt, "f32"], 1))
+    logits = rng.integers(-6, 7, size=(5, 300)).astype(np.float32) * 0.5  # many ties
+    t_l = tt((5, 300), "f32")
+    out.append(("top_k_with_ties", func([t_l], [tt((5, 7), "f32"), tt((5, 7), "i32")],
+                f"    %0:2 = chlo.top_k(%arg0, k = 7) : {t_l} -> ({tt((5, 7), 'f32')}, {tt((5, 7), 'i32')})", "%0#0, %0#1"), [logits]))
+    if "bf16" in NP:
+        lb = rand(rng, (3, 9000), "bf16")
+        t_b = tt((3, 9000), "bf16")
+        out.append(("top_k_long_rows_bf16", func([t_b], [tt((3, 50), "bf16"), tt((3, 50), "i32")],
+                    f"    %values, %indices = chlo.top_k(%arg0, k = 50) : {t_b} -> ({tt((3, 50), 'bf16')}, {tt((3, 50), 'i32')})", "%values, %indices"), [lb]))
+    counters = rng.integers(0, 1 << 32, size=(2, 1000), dtype=np.uint64).astype(np.uint32)
+    out.append(("threefry2x32_random_bits", threefry2x32_text(1000),
+                [np.array([0x13198A2E, 0x03707344], np.uint32), counters[0].copy(), counters[1].copy()]))
     three = [rng.integers(0, 4, size=(2, 5, 3)).astype(np.int32), rand(rng, (2, 5, 3), "f32"), rand(rng, (2, 5, 3), "i8")]
     out.append(sort_case("sort_three_operands_middle_dim", three, ["i32", "f32", "i8"], 1))
     big = rand(rng, (2, 5000), "f32")

@@ -169,3 +169,30 @@ def test_select_and_scatter_drops_windows_won_by_the_padding():
     (got,), (x, src) = run("select_and_scatter_padding_can_win")
     # every operand value is negative and the init value 0 pads the border: border windows select the padding
     assert got[0].sum() == 0 and got[:, 0].sum() == 0 or np.count_nonzero(got) < src.size
+
+
+def test_threefry_module_matches_a_direct_numpy_threefry():
+    from op_cases import THREEFRY_ROTATIONS
+
+    (w0, w1), (key, x0, x1) = run("threefry2x32_random_bits")
+    ks = [key[0], key[1], key[0] ^ key[1] ^ np.uint32(0x1BD11BDA)]
+    a, b = x0 + ks[0], x1 + ks[1]
+    for group in range(5):
+        for r in THREEFRY_ROTATIONS[4 * (group % 2):4 * (group % 2) + 4]:
+            a = a + b
+            b = ((b << np.uint32(r)) | (b >> np.uint32(32 - r))) ^ a
+        a = a + ks[(group + 1) % 3]
+        b = b + ks[(group + 2) % 3] + np.uint32(group + 1)
+    np.testing.assert_array_equal(w0, a)
+    np.testing.assert_array_equal(w1, b)
+    # the output words look uniform: every bit is set about half of the time
+    bits = np.unpackbits(np.concatenate([w0, w1]).view(np.uint8))
+    assert abs(bits.mean() - 0.5) < 0.01
+
+
+def test_threefry_known_answer():
+    """Known-answer vector of Threefry-2x32-20 from the Random123 distribution's kat_vectors: zero key and counter."""
+    from op_cases import threefry2x32_text
+
+    w0, w1 = interp.evaluate(threefry2x32_text(1), [np.zeros(2, np.uint32), np.zeros(1, np.uint32), np.zeros(1, np.uint32)])
+    assert (int(w0[0]), int(w1[0])) == (0x6B200159, 0x99BA4EFE)
