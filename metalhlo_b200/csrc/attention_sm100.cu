@@ -45,6 +45,7 @@ struct AttnParams {
     float scale_log2;  // scale * log2(e)
     int32_t causal;
     int32_t is_bf16;
+    int32_t by_length;  // tile order: 0 = long/short pairs per (batch, head); 1 = longest tiles first, dealt out in a snake
 };
 
 template <int D>
@@ -142,23 +143,39 @@ struct Tile {
 // u = blockIdx.x, blockIdx.x + gridDim.x, ...: CTAs running at the same time work on neighbouring (batch, head)
 // and share their K and V through L2.
 struct TileWalk {
-    int n_m, total, u, e, step;
+    int n_m, total, u, e, step, cta;
     __device__ TileWalk(const AttnParams& p, int first, int stride)
-        : n_m((p.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM)), u(first), e(0), step(stride) {
+        : n_m((p.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM)), u(first), e(0), step(stride), cta(first) {
         total = n_m * p.heads * p.batch;
+        if (p.by_length) u = 0;  // u counts the passes over the CTAs
     }
     __device__ bool next(const AttnParams& p, Tile* t) {
-        int g = 2 * u + e;
-        if (g >= total) return false;
-        const int hb = g / n_m, s = g - hb * n_m;
-        const int mblk = (s & 1) ? (s >> 1) : n_m - 1 - (s >> 1);
+        int hb, mblk;
+        if (p.by_length) {
+            // Tiles sorted by length (all (batch, head) pairs of the last query block, then of the one before, ...), dealt
+            // to the CTAs forwards on even passes and backwards on odd ones: the CTA that got the longest tile of a pass
+            // gets the shortest of the next. Used when all keys and values fit L2, where the order costs no re-reads from HBM.
+            const int j = u * step + ((u & 1) ? step - 1 - cta : cta);
+            if (j >= total) return false;
+            const int hbs = p.heads * p.batch;
+            const int rank = j / hbs;
+            hb = j - rank * hbs;
+            mblk = n_m - 1 - rank;
+            ++u;
+        } else {
+            const int g = 2 * u + e;
+            if (g >= total) return false;
+            hb = g / n_m;
+            const int s = g - hb * n_m;
+            mblk = (s & 1) ? (s >> 1) : n_m - 1 - (s >> 1);
+            if (++e == 2) { e = 0; u += step; }
+        }
         t->bat = hb / p.heads;
         t->head = hb - t->bat * p.heads;
         t->m0 = mblk * kHalves * kBlockM;
         int kv_len = p.seq_k;  // keys this tile visits: all, or up to the last key its last query row may see
         if (p.causal) kv_len = min(p.seq_k, max(0, min(t->m0 + kHalves * kBlockM, p.seq_q) + p.seq_k - p.seq_q));
         t->nblk = (kv_len + kBlockN - 1) / kBlockN;
-        if (++e == 2) { e = 0; u += step; }
         return true;
     }
     // Next tile that has at least one key block (the producer and the MMA issuer skip the others).
@@ -525,7 +542,22 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
         MHLO_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), MHLO_CUDA_EXECUTION_FAILED);
     }
     const int64_t tiles = (s.seq_q + kHalves * kBlockM - 1) / (kHalves * kBlockM) * s.heads * s.batch;
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>((tiles + 1) / 2, sm_count));
+    // causal tiles differ in length: when K and V of all heads stay in L2 anyway, order them by length (see TileWalk)
+    const int64_t kv_bytes = 2 * s.batch * s.heads * s.seq_k * static_cast<int64_t>(D) * 2;
+    // METALHLO_ATTN_BY_LENGTH: 0 = never, 2 = for every causal call (measurements), otherwise by the size of K and V
+    static const int by_length_mode = [] { const char* v = getenv("METALHLO_ATTN_BY_LENGTH"); return v ? atoi(v) : 1; }();
+    static int64_t l2_bytes = 0;
+    if (l2_bytes == 0) {
+        int dev = 0, v = 0;
+        MHLO_CUDA_TRY(cudaGetDevice(&dev), MHLO_CUDA_EXECUTION_FAILED);
+        MHLO_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev), MHLO_CUDA_EXECUTION_FAILED);
+        l2_bytes = v > 0 ? v : 1;
+    }
+    // measured on B200 (126 MB of L2): 98 MB and 100 MB of K + V gain 10-20 %, 268 MB is neutral, 537 MB loses 15 %
+    const bool fits = by_length_mode == 2 || kv_bytes <= l2_bytes / 100 * 85;
+    // without a mask all tiles are equally long; dealing them one by one still evens out the last pass
+    p.by_length = (by_length_mode != 0 && fits && tiles < (int64_t{1} << 30)) ? 1 : 0;
+    const unsigned grid = static_cast<unsigned>(p.by_length ? std::min<int64_t>(tiles, sm_count) : std::min<int64_t>((tiles + 1) / 2, sm_count));
     const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kAttnThreads), L::kTotal, stream, mq, mk, mv, p);
     if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of attention_tcgen05 failed: %s", cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH("attention_tcgen05");
