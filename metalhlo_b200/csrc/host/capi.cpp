@@ -520,6 +520,7 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
         CompileOptions opt;
         opt.opt_level = optimization_level;
         run_pass_pipeline(f, opt);
+        optimize_loop_bodies(f, opt);
         *out_text = strdup(print_function(f).c_str());
         return MHLO_OK;
     } catch (const CompileError& e) {

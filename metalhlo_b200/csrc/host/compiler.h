@@ -47,6 +47,8 @@ bool unroll_static_whiles(Function& f);
 bool flatten_conditionals(Function& f);
 // Replaces stablehlo.map by its computation applied to whole tensors.
 bool flatten_maps(Function& f);
+// Runs the pass pipeline on the bodies of the loops that stay loops (after it ran on the function itself).
+void optimize_loop_bodies(Function& f, const CompileOptions& options);
 // Replaces chlo.top_k by iota + stable descending sort + slices.
 bool flatten_top_k(Function& f);
 // All four, repeated until none applies; returns the flattened @main.

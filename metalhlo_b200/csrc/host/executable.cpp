@@ -1695,6 +1695,7 @@ std::unique_ptr<Executable> Executable::plan_only(const std::string& mlir, const
     Function f = flatten_main(m);
     std::unique_ptr<Executable> exe(new Executable());
     exe->pass_log_ = run_pass_pipeline(f, options);
+    optimize_loop_bodies(f, options);
     exe->optimized_text_ = print_function(f);
     Lowering lower(f, exe.get());
     lower.run();
@@ -1707,6 +1708,7 @@ std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const C
     if (std::getenv("METALHLO_DUMP_MLIR")) fprintf(stderr, "[metalhlo] parsed module:\n%s\n", print_function(f).c_str());
     std::unique_ptr<Executable> exe(new Executable());
     exe->pass_log_ = run_pass_pipeline(f, options);
+    optimize_loop_bodies(f, options);
     exe->optimized_text_ = print_function(f);
     if (std::getenv("METALHLO_DUMP_OPTIMIZED")) fprintf(stderr, "[metalhlo] optimized module:\n%s\n", exe->optimized_text_.c_str());
     Lowering lower(f, exe.get());

@@ -492,6 +492,15 @@ bool sweep_loop_regions(Function& f, const std::function<bool()>& pass, int dept
 
 }  // namespace
 
+void optimize_loop_bodies(Function& f, const CompileOptions& options) {
+    sweep_loop_regions(f, [&]() {
+        f.compact();  // link the values to the ops of this body; values from outside count as opaque
+        run_pass_pipeline(f, options);
+        return false;
+    }, 0);
+    f.compact();
+}
+
 Function flatten_main(Module& m) {
     // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat
     // until nothing changes

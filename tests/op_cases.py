@@ -442,6 +442,34 @@ def widening_cases():
   }}
 }}
 """, [x48]))
+    # a fusable pattern (softmax) inside a loop whose exit depends on the data: sharpen until one entry dominates
+    sm_body, sm_res = softmax_text("%sc", (4, 8), "f32", 1, prefix="w")
+    out.append(("while_dynamic_softmax_in_body", f"""module @jit_sharpen {{
+  func.func public @main(%arg0: {t48}) -> ({t48}, tensor<i32>) {{
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %0:2 = stablehlo.while(%iterArg = %arg0, %iterArg_0 = %c) : {t48}, tensor<i32>
+     cond {{
+      %c_1 = stablehlo.constant dense<6> : tensor<i32>
+      %1 = stablehlo.compare  LT, %iterArg_0, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      %cst = stablehlo.constant dense<0xFF800000> : tensor<f32>
+      %2 = stablehlo.reduce(%iterArg init: %cst) applies stablehlo.maximum across dimensions = [0, 1] : ({t48}, tensor<f32>) -> tensor<f32>
+      %cst_1 = stablehlo.constant dense<9.000000e-01> : tensor<f32>
+      %3 = stablehlo.compare  LT, %2, %cst_1,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %4 = stablehlo.and %1, %3 : tensor<i1>
+      stablehlo.return %4 : tensor<i1>
+    }} do {{
+      %cst = stablehlo.constant dense<3.000000e+00> : tensor<f32>
+      %1 = stablehlo.broadcast_in_dim %cst, dims = [] : (tensor<f32>) -> {t48}
+      %sc = stablehlo.multiply %iterArg, %1 : {t48}
+{sm_body.rstrip(chr(10)).replace("    %", "      %")}
+      %c_1 = stablehlo.constant dense<1> : tensor<i32>
+      %5 = stablehlo.add %iterArg_0, %c_1 : tensor<i32>
+      stablehlo.return {sm_res}, %5 : {t48}, tensor<i32>
+    }}
+    return %0#0, %0#1 : {t48}, tensor<i32>
+  }}
+}}
+""", [(0.2 * x48).astype(np.float32)]))
     # carried values that trade places (a result is a view of another carried value), a call and an if in the body
     out.append(("while_dynamic_swap_call_if", f"""module @jit_fib {{
   func.func public @main(%arg0: tensor<8xf32>, %arg1: tensor<8xf32>, %arg2: tensor<i32>) -> (tensor<8xf32>, tensor<8xf32>, tensor<i32>) {{
