@@ -1,7 +1,7 @@
 // Operators either side of the fused hot path that need kernels of their own: reduce_window (pooling, windowed
-// sums), scatter (indexed updates with atomics) and sort (bitonic networks in shared and global memory).
-// HBM / L2-bound integer and byte work: one thread per output element (reduce_window, scatter) or one CTA per
-// sorted slice, grids sized in multiples of the SM count.
+// sums; a vector kernel for channel-last pooling and a general one), scatter and select_and_scatter (indexed updates
+// with atomics) and sort (bitonic networks in shared and global memory). HBM / L2-bound integer and byte work: one
+// thread per output element or 16-byte vector, or one CTA per sorted slice; grids sized in multiples of the SM count.
 #include <cstring>
 #include <type_traits>
 
