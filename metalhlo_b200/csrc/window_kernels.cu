@@ -2,6 +2,7 @@
 // sums; a vector kernel for channel-last pooling and a general one), scatter and select_and_scatter (indexed updates
 // with atomics) and sort (bitonic networks in shared and global memory). HBM / L2-bound integer and byte work: one
 // thread per output element or 16-byte vector, or one CTA per sorted slice; grids sized in multiples of the SM count.
+#include <algorithm>
 #include <cstring>
 #include <type_traits>
 
@@ -437,11 +438,14 @@ __device__ __forceinline__ void scatter_apply(E* addr, E upd, int mode) {
     cas_update<E>(addr, [&](E cur) { return narrow<E>(combine<A>(op, widen<E>(cur), u)); });
 }
 
-template <typename E>
+// G = 1: one thread per update element. G = 4 (fp32 add only): one thread per four consecutive elements of the updates'
+// last dimension, which the caller guarantees to be a window dimension that lands on the operand's last dimension and
+// to be a multiple of four long; the four targets are then consecutive and, when 16-byte aligned, take one vector atomic.
+template <typename E, int G>
 __global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ ScatterParams p) {
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
     const bool has_ivd = p.d.index_vector_dim < p.indices_rank;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += step) {
+    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * G; i < p.n; i += step * G) {
         int64_t uidx[MHLO_CUDA_MAX_RANK];
         int64_t rem = i;
         for (int d = p.updates_rank - 1; d >= 0; --d) { uidx[d] = rem % p.updates_shape[d]; rem /= p.updates_shape[d]; }
@@ -470,18 +474,35 @@ __global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ Sc
             if (has_ivd && sd > p.d.index_vector_dim) --sd;
             target[p.d.input_batching_dims[k]] += batch[sd];
         }
-        int64_t dst = 0;
+        int64_t dst = 0, c_last = 0;
         int wi = 0;
-        bool inside = true;
+        bool inside = true;  // for G > 1: of every coordinate but the last
         for (int d = 0; d < p.operand_rank; ++d) {
             bool skip = false;
             for (int k = 0; k < p.d.n_inserted_window_dims; ++k) skip |= p.d.inserted_window_dims[k] == d;
             for (int k = 0; k < p.d.n_input_batching; ++k) skip |= p.d.input_batching_dims[k] == d;
             const int64_t c = target[d] + (skip ? 0 : win[wi++]);
-            inside = inside && c >= 0 && c < p.operand_shape[d];
+            if (G > 1 && d == p.operand_rank - 1) c_last = c;
+            else inside = inside && c >= 0 && c < p.operand_shape[d];
             dst = dst * p.operand_shape[d] + c;
         }
-        if (inside) scatter_apply<E>(static_cast<E*>(p.result) + dst, static_cast<const E*>(p.updates)[i], p.mode);
+        if constexpr (G == 1) {
+            if (inside) scatter_apply<E>(static_cast<E*>(p.result) + dst, static_cast<const E*>(p.updates)[i], p.mode);
+        } else {
+            if (!inside) continue;
+            const int64_t extent = p.operand_shape[p.operand_rank - 1];
+            E* to = static_cast<E*>(p.result) + dst;
+            const E* from = static_cast<const E*>(p.updates) + i;
+            if constexpr (std::is_same<E, float>::value && G == 4) {
+                if (c_last >= 0 && c_last + 3 < extent && (reinterpret_cast<uintptr_t>(to) & 15u) == 0) {
+                    atomicAdd(reinterpret_cast<float4*>(to), *reinterpret_cast<const float4*>(from));
+                    continue;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < G; ++e)
+                if (c_last + e >= 0 && c_last + e < extent) scatter_apply<E>(to + e, from[e], p.mode);
+        }
     }
 }
 
@@ -853,8 +874,24 @@ extern "C" int mhlo_cuda_scatter(void* result_inout_dev, int32_t dtype, const in
     p.index_dtype = index_dtype;
     p.mode = mode;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // rows of fp32 added into a table (an embedding gradient): four elements per thread, one vector atomic each
+    bool rows_of_four = dtype == MHLO_DT_F32 && mode == MHLO_SCATTER_ADD && updates_rank >= 1 && operand_rank >= 1 &&
+                        updates_shape[updates_rank - 1] % 4 == 0 && dims->n_update_window_dims >= 1 &&
+                        (reinterpret_cast<uintptr_t>(updates_dev) & 15u) == 0;
+    if (rows_of_four) {
+        int last_window = -1;
+        for (int k = 0; k < dims->n_update_window_dims; ++k) last_window = std::max(last_window, dims->update_window_dims[k]);
+        rows_of_four = last_window == updates_rank - 1;  // the updates' last dimension is the last window dimension ...
+        for (int k = 0; k < dims->n_inserted_window_dims; ++k) rows_of_four = rows_of_four && dims->inserted_window_dims[k] != operand_rank - 1;
+        for (int k = 0; k < dims->n_input_batching; ++k) rows_of_four = rows_of_four && dims->input_batching_dims[k] != operand_rank - 1;  // ... on the operand's last
+    }
+    if (rows_of_four) {
+        scatter_kernel<float, 4><<<grid_of(p.n / 4, 256), 256, 0, s>>>(p);
+        MHLO_CUDA_CHECK_LAUNCH("scatter (rows of four)");
+        return MHLO_CUDA_OK;
+    }
     const int grid = grid_of(p.n, 256);
-    if (!with_element_type(dtype, [&](auto tag) { scatter_kernel<decltype(tag)><<<grid, 256, 0, s>>>(p); }))
+    if (!with_element_type(dtype, [&](auto tag) { scatter_kernel<decltype(tag), 1><<<grid, 256, 0, s>>>(p); }))
         return fail(MHLO_CUDA_UNSUPPORTED, "scatter: dtype %d", dtype);
     MHLO_CUDA_CHECK_LAUNCH("scatter");
     return MHLO_CUDA_OK;

@@ -817,6 +817,8 @@ def window_scatter_sort_cases():
     window2d = "update_window_dims = [1, 2], scatter_dims_to_operand_dims = [0, 1], index_vector_dim = 1"
     out.append(scatter_case("scatter_add_windows_partly_outside", rand(rng, (6, 7), "i32"), np.array([[0, 0], [5, 5], [2, 6], [-1, 3]], np.int32),
                             rand(rng, (4, 2, 3), "i32"), "i32", "add", window2d))
+    out.append(scatter_case("scatter_add_f32_windows_of_four", rand(rng, (6, 12), "f32"), np.array([[0, 0], [5, 9], [2, 3], [-1, 1], [3, 8], [0, 0]], np.int32),
+                            rand(rng, (6, 2, 4), "f32"), "f32", "add", window2d))
     # ---- sort
     keys = rand(rng, (37,), "f32")
     keys[[3, 11]] = np.nan
