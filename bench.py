@@ -470,6 +470,23 @@ def measure_extras(torch, dist, cuda, rank, world, dev, peaks):
     out["gpt2_small_fwd"] = {"tokens_per_s": batch * world * 1024 / (ms * 1e-3), "ms": ms, "batch_per_gpu": batch, "seq": 1024,
                              "launches": exe.launch_count, "graph_replays": exe.graph_replays, "compute": "fp16, fp32 parameters converted inside the module",
                              "logits": "fp16 [batch,1024,50257], left sharded"}
+    if world == 1:
+        # operators either side of the fused path, each as a one-operator module through the C API on device memory
+        for kind in ("conv", "maxpool", "sort_rows", "scatter_add"):
+            try:
+                run, case_exe, work, unit, keep = module_case_runner(kind, client)
+                stream = torch.cuda.current_stream().cuda_stream
+                ms = timed(lambda: run(stream), 10)
+                touched = sum(b.byte_count for b in keep[1]) + sum(o.numel() for o in keep[2]) + case_exe.arena_bytes
+                out["module_" + kind] = {
+                    "ms": ms, ("tflops" if unit == "TFLOP" else "gbs"): work / ms * 1e3, "launches": case_exe.launch_count,
+                    "steps": case_exe.steps, "device_mb": round(touched / 1e6, 1),
+                    "l2": "back-to-back executions on the same buffers: " +
+                          ("the working set exceeds L2" if touched > 126e6 else "the working set fits L2 and stays warm")}
+                del run, case_exe, keep
+                torch.cuda.empty_cache()
+            except Exception as e:  # a side measurement must not cost the benchmark line
+                out["module_" + kind] = {"error": str(e)[:200]}
     return out
 
 
@@ -523,6 +540,39 @@ MODULE_CASES = {
     "sort_long": (lambda: _sort_text(4, 4194304), 4 * 4194304 * 4 * 4 / 1e9, "GB"),
     "scatter_add": (lambda: _scatter_text(), (2 * 50257 * 768 + 3 * 32768 * 768) * 4 / 1e9, "GB"),     # copy of the table + read-modify-write of the rows
 }
+
+
+def module_case_runner(kind: str, client=None):
+    """Compiles one module of MODULE_CASES and allocates seeded inputs and outputs on the device. Returns
+    (run(stream), executable, work per execution, unit, keep-alive objects)."""
+    import numpy as np
+    import torch
+
+    from metalhlo_b200 import capi
+
+    build, work, unit = MODULE_CASES[kind]
+    client = client or capi.Client()
+    exe = client.compile(build(), 3)
+    rng = np.random.default_rng(5)
+    ins = []
+    for i in range(exe.input_count):
+        shape, code = exe.input_type(i)
+        dt = capi.np_dtype(code)
+        if np.issubdtype(dt, np.integer):
+            arr = rng.integers(0, 50257, size=shape).astype(dt)
+        else:
+            arr = rng.standard_normal(shape).astype(np.float32).astype(dt)
+        ins.append(client.buffer(arr))
+    outs = []
+    for i in range(exe.output_count):
+        shape, code = exe.output_type(i)
+        outs.append(torch.empty(int(np.prod(shape)) * capi.np_dtype(code).itemsize, dtype=torch.uint8, device="cuda"))
+    in_ptrs, out_ptrs = [b.device_pointer for b in ins], [o.data_ptr() for o in outs]
+
+    def run(stream):
+        exe.execute_on_device(in_ptrs, out_ptrs, stream)
+
+    return run, exe, work, unit, (client, ins, outs)
 
 
 def profile_module_case(kind: str, launches: int):
