@@ -513,8 +513,31 @@ class Lowering {
                                                            {"LE", MHLO_EW_CMP_LE}, {"GT", MHLO_EW_CMP_GT}, {"GE", MHLO_EW_CMP_GE}};
             auto it = dir.find(op.str_attr("comparison_direction"));
             if (it == dir.end()) fail_compile("compare without a comparison_direction");
+            const View& lhs = get(op.operands[0]);
+            if (op.str_attr("compare_type") == "TOTALORDER" && is_float(lhs.type.dtype)) {
+                // -NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN: read the operands as signed integers of the same width and
+                // flip the magnitude bits of the negative ones; the integer comparison of the results is the total order
+                const size_t es = dtype_size(lhs.type.dtype);
+                const DType as_int = es == 2 ? DType::I16 : es == 4 ? DType::I32 : DType::I64;
+                View a = lhs, b = get(op.operands[1]);
+                a.type.dtype = as_int;
+                b.type.dtype = as_int;
+                const double top = static_cast<double>(8 * es - 1);
+                std::vector<mhlo_cuda_ew_inst> prog = {
+                    {MHLO_EW_IMM, 0, 0, 0, top},      // r2 = width - 1
+                    {MHLO_EW_IMM, 0, 0, 0, 1.0},      // r3 = 1
+                    {MHLO_EW_SHR_A, 0, 2, 0, 0.0},    // r4 = all ones where a is negative
+                    {MHLO_EW_SHR_L, 4, 3, 0, 0.0},    // r5 = the magnitude mask of those
+                    {MHLO_EW_XOR, 0, 5, 0, 0.0},      // r6 = ordered key of a
+                    {MHLO_EW_SHR_A, 1, 2, 0, 0.0},    // r7
+                    {MHLO_EW_SHR_L, 7, 3, 0, 0.0},    // r8
+                    {MHLO_EW_XOR, 1, 8, 0, 0.0},      // r9 = ordered key of b
+                    {it->second, 6, 9, 0, 0.0},
+                };
+                return set(op.results[0], emit_elementwise({a, b}, prog, rt, "compare.totalorder"));
+            }
             std::vector<mhlo_cuda_ew_inst> prog = {{it->second, 0, 1, 0, 0.0}};
-            return set(op.results[0], emit_elementwise({get(op.operands[0]), get(op.operands[1])}, prog, rt, "compare"));
+            return set(op.results[0], emit_elementwise({lhs, get(op.operands[1])}, prog, rt, "compare"));
         }
         if (n == "concatenate") return lower_concatenate(op);
         if (n == "pad") return lower_pad(op);

@@ -962,6 +962,7 @@ bool fusable_elementwise(const Op& o) {
                                   "log", "sqrt", "rsqrt", "tanh", "logistic", "sine", "cosine", "floor", "ceil", "sign",
                                   "exponential_minus_one", "log_plus_one", "power", "select", "clamp", "compare", "convert"};
     if (o.results.size() != 1) return false;
+    if (o.name == "compare" && o.str_attr("compare_type") == "TOTALORDER") return false;  // lowered on the bit patterns
     for (const char* n : names)
         if (o.name == n) return true;
     return false;

@@ -528,6 +528,18 @@ def widening_cases():
 """.replace("    %0 = \"stablehlo.case\"", "    %p0 = stablehlo.constant dense<true> : tensor<i1>\n    %0 = \"stablehlo.case\"")
     for v in (0, 1, 2, 7, -3):
         out.append((f"case_index_{v}".replace("-", "m"), case_text, [np.asarray(v, np.int32), x48]))
+    # ---- compare under the total order (-NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN)
+    special = np.array([np.nan, -np.nan, np.inf, -np.inf, 0.0, -0.0, 1.5, -1.5, 1e-30, -1e-30, 3.0, np.nan], np.float32)
+    special[1] = np.float32(np.uint32(0xFFC00000).view(np.float32))  # a NaN with the sign bit set
+    lhs_t, rhs_t = np.repeat(special, len(special)), np.tile(special, len(special))
+    for dt in ("f32", "bf16", "f16"):
+        if dt not in NP:
+            continue
+        tcmp, tres = tt((len(lhs_t),), dt), tt((len(lhs_t),), "i1")
+        for direction in ("LT", "EQ", "GE"):
+            out.append((f"compare_totalorder_{direction}_{dt}", func([tcmp, tcmp], [tres],
+                        f"    %0 = stablehlo.compare  {direction}, %arg0, %arg1,  TOTALORDER : ({tcmp}, {tcmp}) -> {tres}", "%0"),
+                        [lhs_t.astype(NP[dt]), rhs_t.astype(NP[dt])]))
     # ---- bitcast_convert
     bits = x48.view(np.int32)
     out.append(("bitcast_convert_f32_i32", func([t48], [tt((4, 8), "i32")],
