@@ -508,10 +508,33 @@ int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a
 int mhlo_cuda_device_error(int32_t* out_code);
 
 /*
+ * The same check without a device-wide synchronisation, for the execution path: _fetch enqueues, on `stream`, copies
+ * of the error words into pinned host memory of the current device; after the caller has synchronised that stream,
+ * _take reads them, clears the device words when one is set and returns MHLO_CUDA_EXECUTION_FAILED with the code in
+ * *out_code and in the error string. The reference's executor has no counterpart (a Metal command buffer reports its
+ * own status, IntegratedExecutor.swift:262-268); mhlo_execute turns a non-zero code into MHLO_ERROR_EXECUTION_FAILED.
+ */
+int mhlo_cuda_device_error_fetch(mhlo_cuda_stream_t stream);
+int mhlo_cuda_device_error_take(int32_t* out_code);
+
+/*
+ * Test hooks for that path; neither faults, traps or hangs the device. _store_device_error writes `code` into the
+ * error word of the GEMM kernel (which = 0) or the attention kernel (which = 1) from the host. _wait_expiry_probe
+ * launches one CTA that waits on an mbarrier nobody arrives at for at most limit_ns (<= 1 s) and then records code 90
+ * exactly as the contraction kernels record an expired wait.
+ */
+int mhlo_cuda_debug_store_device_error(int32_t which, int32_t code);
+/* Test hook of the allocator's failure path: the next `count` mhlo_cuda_alloc calls return MHLO_CUDA_BUFFER_FAILED
+ * without reaching the driver (0 switches it off). */
+int mhlo_cuda_debug_refuse_allocs(int32_t count);
+int mhlo_cuda_debug_wait_expiry_probe(uint64_t limit_ns, mhlo_cuda_stream_t stream);
+
+/*
  * Fused scaled dot-product attention, O = softmax(scale * Q K^T [+ mask] [causal]) V with fp32 softmax and
  * accumulation. Q [B,H,Sq,D], K/V [B,H,Sk,D], O [B,H,Sq,D] logically; *_strides = {batch, head, sequence}
  * element strides (the head dimension D is contiguous), so [B,S,H,D] tensors are read and written in place.
- * causal: key j is visible to query i iff j <= i + (Sk - Sq). mask_dev: optional additive [Sq,Sk] mask of the
+ * causal: key j is visible to query i iff j <= i, also when Sq != Sk (the `kv_pos > q_pos` cut of
+ * FlashAttentionKernel.swift:545,578). mask_dev: optional additive [Sq,Sk] mask of the
  * operand dtype shared by every batch and head. Replaces kernel_attention (CodeGenerator.swift:4527-4595) and
  * flash_attention_tiled_kernel (Sources/MetalHLOCore/Metal/Kernels/FlashAttentionKernel.swift:469-670) with the
  * semantics of FusedScaledDotProductAttentionHandler (CustomCallHandlers.swift:179-278).

@@ -19,6 +19,7 @@
 //
 // Algorithmic work: 4*B*H*Sq*Sk*D FLOP (half of that, plus the diagonal, when causal); HBM bytes: Q, K, V read once
 // per CTA column (K/V re-reads across query blocks are served by L2), O written once.
+#include <atomic>
 #include <algorithm>
 #include <string>
 
@@ -174,7 +175,7 @@ struct TileWalk {
         t->head = hb - t->bat * p.heads;
         t->m0 = mblk * kHalves * kBlockM;
         int kv_len = p.seq_k;  // keys this tile visits: all, or up to the last key its last query row may see
-        if (p.causal) kv_len = min(p.seq_k, max(0, min(t->m0 + kHalves * kBlockM, p.seq_q) + p.seq_k - p.seq_q));
+        if (p.causal) kv_len = min(p.seq_k, min(t->m0 + kHalves * kBlockM, p.seq_q));  // key j is visible to query i iff j <= i
         t->nblk = (kv_len + kBlockN - 1) / kBlockN;
         return true;
     }
@@ -210,7 +211,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kHalves);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int causal_off = p.seq_k - p.seq_q;
 
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&map_q);
@@ -363,7 +363,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool ok = true;
         while (walk.next(p, &t)) {
             const int qi = t.m0 + h * kBlockM + r;  // query index
-            const int last_visible = p.causal ? min(p.seq_k - 1, qi + causal_off) : p.seq_k - 1;
+            const int last_visible = p.causal ? min(p.seq_k - 1, qi) : p.seq_k - 1;
             float m_ref = -INFINITY, l = 0.f;
             for (int j = 0; j < t.nblk && ok; ++j, ++it) {
                 if (!mbar_wait(&s_full[h], it & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
@@ -529,10 +529,13 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
     p.causal = s.causal;
     p.is_bf16 = dtype == MHLO_DT_BF16;
     auto kernel = attention_tcgen05_kernel<D>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // the attribute belongs to the (kernel, device) pair: one flag per device ordinal
+    static std::atomic<bool> attr_set[64];
+    int attr_dev = 0;
+    MHLO_CUDA_TRY(cudaGetDevice(&attr_dev), MHLO_CUDA_EXECUTION_FAILED);
+    if (attr_dev < 0 || attr_dev >= 64 || !attr_set[attr_dev].load(std::memory_order_acquire)) {
         MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
-        attr_set = true;
+        if (attr_dev >= 0 && attr_dev < 64) attr_set[attr_dev].store(true, std::memory_order_release);
     }
     // persistent grid: one CTA per SM, each walking its share of the (batch, head, query block) tiles in pairs
     static int sm_count = 0;
@@ -575,6 +578,12 @@ int attention_device_error() {
     if (v != 0) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof zero);
     return v;
 }
+
+bool attention_error_fetch_async(int* pinned_dst, cudaStream_t stream) {
+    return cudaMemcpyFromSymbolAsync(pinned_dst, g_attn_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+}
+
+bool attention_error_store(int code) { return cudaMemcpyToSymbol(g_attn_error, &code, sizeof code) == cudaSuccess; }
 
 bool attention_tc_supported(int dtype, const AttnShape& s, const void* mask) {
     if (dtype != MHLO_DT_BF16 && dtype != MHLO_DT_F16) return false;

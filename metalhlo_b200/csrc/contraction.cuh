@@ -32,6 +32,12 @@ bool gemm_tc_supported(const GemmProblem& p);
 int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream);
 int gemm_device_error();       // synchronises; returns and clears the GEMM kernel's error word (-1: CUDA error)
 int attention_device_error();  // same for the attention kernel
+// Stream-ordered copies of the error words into pinned host memory, and host stores into them (clearing, or the test hook).
+bool gemm_error_fetch_async(int* pinned_dst, cudaStream_t stream);
+bool attention_error_fetch_async(int* pinned_dst, cudaStream_t stream);
+bool gemm_error_store(int code);
+bool attention_error_store(int code);
+bool gemm_wait_expiry_probe(uint64_t limit_ns, cudaStream_t stream);
 bool attention_tc_supported(int dtype, const AttnShape& s, const void* mask);
 int attention_tc_launch(int dtype, const void* q, const void* k, const void* v, void* o, const AttnShape& s,
                         cudaStream_t stream);

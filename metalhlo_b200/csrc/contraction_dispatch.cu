@@ -1,6 +1,8 @@
 // Entry points of the contractions: mhlo_cuda_gemm and mhlo_cuda_attention choose between the tcgen05
 // tensor-core kernels and the general-layout kernels, and hold the general-layout attention kernel.
 #include "common.cuh"
+#include <mutex>
+
 #include "contraction.cuh"
 
 namespace mhlo {
@@ -34,7 +36,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const T* __restrict
 #pragma unroll
     for (int t = 0; t < kMaxPerLane; ++t) acc[t] = 0.f;
     float m = -INFINITY, l = 0.f;
-    int64_t lim = s.causal ? i + (s.seq_k - s.seq_q) + 1 : s.seq_k;
+    int64_t lim = s.causal ? i + 1 : s.seq_k;  // key j is visible to query i iff j <= i
     if (lim > s.seq_k) lim = s.seq_k;
     for (int64_t j0 = 0; j0 < lim; j0 += 32) {
         const int64_t j = j0 + lane;
@@ -105,6 +107,59 @@ int mhlo_cuda_device_error(int32_t* out_code) {
     *out_code = g != 0 ? g : (a != 0 ? 100 + a : 0);
     if (*out_code != 0) return fail(MHLO_CUDA_EXECUTION_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d)", *out_code);
     return MHLO_CUDA_OK;
+}
+
+namespace {
+// Pinned host landing slots of the error words, one pair per device, allocated on first use and kept until exit.
+std::mutex g_slot_mu;
+int* g_error_slots[64] = {nullptr};
+
+int* error_slot_for_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_slot_mu);
+    if (!g_error_slots[dev]) {
+        void* p = nullptr;
+        if (cudaHostAlloc(&p, 2 * sizeof(int), cudaHostAllocDefault) != cudaSuccess) return nullptr;
+        g_error_slots[dev] = static_cast<int*>(p);
+        g_error_slots[dev][0] = g_error_slots[dev][1] = 0;
+    }
+    return g_error_slots[dev];
+}
+}  // namespace
+
+int mhlo_cuda_device_error_fetch(mhlo_cuda_stream_t stream) {
+    int* slot = error_slot_for_current_device();
+    if (!slot) return fail(MHLO_CUDA_EXECUTION_FAILED, "device_error_fetch: no pinned slot for the current device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!gemm_error_fetch_async(slot, s) || !attention_error_fetch_async(slot + 1, s))
+        return fail(MHLO_CUDA_EXECUTION_FAILED, "device_error_fetch: %s", cudaGetErrorString(cudaGetLastError()));
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_device_error_take(int32_t* out_code) {
+    if (!out_code) return fail(MHLO_CUDA_INVALID_ARGUMENT, "device_error_take: null output");
+    int* slot = error_slot_for_current_device();
+    if (!slot) return fail(MHLO_CUDA_EXECUTION_FAILED, "device_error_take: no pinned slot for the current device");
+    const int g = slot[0], a = slot[1];
+    *out_code = g != 0 ? g : (a != 0 ? 100 + a : 0);
+    if (*out_code == 0) return MHLO_CUDA_OK;
+    slot[0] = slot[1] = 0;
+    if (g != 0) gemm_error_store(0);
+    if (a != 0) attention_error_store(0);
+    return fail(MHLO_CUDA_EXECUTION_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d)", *out_code);
+}
+
+int mhlo_cuda_debug_store_device_error(int32_t which, int32_t code) {
+    const bool ok = which == 0 ? gemm_error_store(code) : attention_error_store(code);
+    return ok ? MHLO_CUDA_OK : fail(MHLO_CUDA_EXECUTION_FAILED, "debug_store_device_error: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+int mhlo_cuda_debug_wait_expiry_probe(uint64_t limit_ns, mhlo_cuda_stream_t stream) {
+    if (limit_ns > 1000000000ull) return fail(MHLO_CUDA_INVALID_ARGUMENT, "wait_expiry_probe: limit above one second");
+    return gemm_wait_expiry_probe(limit_ns, static_cast<cudaStream_t>(stream))
+               ? MHLO_CUDA_OK
+               : fail(MHLO_CUDA_EXECUTION_FAILED, "wait_expiry_probe: %s", cudaGetErrorString(cudaGetLastError()));
 }
 
 int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],

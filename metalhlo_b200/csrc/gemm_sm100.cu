@@ -20,6 +20,7 @@
 // HBM traffic per tile pass: A and B panels are re-read from L2 across tiles; the tile order walks 16 row-tiles
 // per column band so that the 148 concurrently resident tiles share operands in L2. Algorithmic bytes:
 // (M*K + K*N) * 2 read + M*N * sizeof(out) written per batch entry.
+#include <atomic>
 #include <cuda.h>
 
 #include <algorithm>
@@ -575,10 +576,13 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     }
 
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // the attribute belongs to the (kernel, device) pair: one flag per device ordinal
+    static std::atomic<bool> attr_set[64];
+    int attr_dev = 0;
+    MHLO_CUDA_TRY(cudaGetDevice(&attr_dev), MHLO_CUDA_EXECUTION_FAILED);
+    if (attr_dev < 0 || attr_dev >= 64 || !attr_set[attr_dev].load(std::memory_order_acquire)) {
         MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
-        attr_set = true;
+        if (attr_dev >= 0 && attr_dev < 64) attr_set[attr_dev].store(true, std::memory_order_release);
     }
     const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
     const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, map_a, map_b, map_c, p);
@@ -618,6 +622,44 @@ int gemm_device_error() {
     if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof v) != cudaSuccess) return -1;
     if (v != 0) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero);
     return v;
+}
+
+bool gemm_error_fetch_async(int* pinned_dst, cudaStream_t stream) {
+    return cudaMemcpyFromSymbolAsync(pinned_dst, g_gemm_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+}
+
+bool gemm_error_store(int code) { return cudaMemcpyToSymbol(g_gemm_error, &code, sizeof code) == cudaSuccess; }
+
+namespace {
+// One CTA that waits on an mbarrier nobody arrives at, for at most `limit_ns`, and then records code 90 the way the
+// contraction kernels record an expired wait. The wait ends by itself: nothing here can spin for longer than the limit.
+__global__ void wait_expiry_probe_kernel(uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+        const uint32_t addr = smem_u32(&bar);
+        const uint64_t start = global_timer_ns();
+        bool done = false;
+        while (!done && global_timer_ns() - start <= limit_ns) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(addr), "r"(0u)
+                : "memory");
+            done = ok != 0;
+        }
+        if (!done) atomicExch(&g_gemm_error, 90);
+    }
+}
+}  // namespace
+
+bool gemm_wait_expiry_probe(uint64_t limit_ns, cudaStream_t stream) {
+    wait_expiry_probe_kernel<<<1, 32, 0, stream>>>(limit_ns);
+    return cudaGetLastError() == cudaSuccess;
 }
 
 }  // namespace mhlo

@@ -171,8 +171,18 @@ MHLOStatusCode run(ExecutableHandle* h, const MHLOBufferRef* inputs, int32_t num
     }
     const auto t1 = std::chrono::steady_clock::now();
     if (timed) mhlo_cuda_event_record(ev1, c->stream);
+    // The tensor-core kernels bound every wait and record a code instead of hanging; the words ride back behind the
+    // program on the same stream, so a kernel that gave up fails this call instead of returning partly written outputs.
+    const bool words = st == 0 && mhlo_cuda_device_error_fetch(c->stream) == 0;
     if (st == 0 && mhlo_cuda_stream_sync(c->stream) != 0) { st = MHLO_ERROR_EXECUTION_FAILED; set_error(st, mhlo_cuda_last_error()); }
     else if (st != 0) set_error(st, exe.last_error());
+    if (st == 0 && words) {
+        int32_t code = 0;
+        if (mhlo_cuda_device_error_take(&code) != 0 && code != 0) {
+            st = MHLO_ERROR_EXECUTION_FAILED;
+            set_error(st, std::string("Execution failed: ") + mhlo_cuda_last_error());
+        }
+    }
     if (timed) {
         float ms = 0;
         if (st == 0) mhlo_cuda_event_elapsed_ms(ev0, ev1, &ms);

@@ -780,11 +780,6 @@ bool fuse_attention(Function& f) {
             int s = sm.x;
             bool causal = false;
             double scale = 1.0;
-            for (int hops = 0; hops < 4; ++hops) {
-                const Op* o = g.def(s);
-                if (!o || g.n_users(s) != 2) break;  // the scores feed reduce_max and subtract inside the softmax...
-                break;
-            }
             // walk down from the softmax input
             auto single_use_or_softmax_input = [&](int v) { return v == sm.x ? g.n_users(v) == 2 : g.n_users(v) == 1; };
             bool ok = true;

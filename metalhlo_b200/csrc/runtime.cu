@@ -1,6 +1,7 @@
 // Device, memory, stream and event entry points of libmhlo_cuda.so plus the thread-local error slot.
 // They stand where IntegratedExecutor uses MTLDevice/MTLBuffer/MTLCommandBuffer
 // (Sources/MetalHLOCore/Runtime/IntegratedExecutor.swift:106-141,182-190,232-252).
+#include <atomic>
 #include <cstring>
 
 #include <cstdlib>
@@ -166,10 +167,21 @@ int mhlo_cuda_stream_sync(mhlo_cuda_stream_t stream) {
     return MHLO_CUDA_OK;
 }
 
+// Test hook: the next `count` device allocations are refused before they reach the driver.
+static std::atomic<int> g_refuse_allocs{0};
+
+int mhlo_cuda_debug_refuse_allocs(int32_t count) {
+    g_refuse_allocs.store(count < 0 ? 0 : count);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_alloc(size_t bytes, void** out_dev) {
     if (!out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "alloc: null output");
     *out_dev = nullptr;
     if (bytes == 0) return MHLO_CUDA_OK;
+    int left = g_refuse_allocs.load();
+    while (left > 0 && !g_refuse_allocs.compare_exchange_weak(left, left - 1)) {}
+    if (left > 0) return fail(MHLO_CUDA_BUFFER_FAILED, "alloc of %zu bytes refused (test hook)", bytes);
     MHLO_CUDA_TRY(cudaMalloc(out_dev, bytes), MHLO_CUDA_BUFFER_FAILED);
     return MHLO_CUDA_OK;
 }

@@ -136,6 +136,11 @@ _PROTOTYPES = {
     "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                  _i32, _vp]),
     "mhlo_cuda_device_error": (C.c_int, [C.POINTER(_i32)]),
+    "mhlo_cuda_device_error_fetch": (C.c_int, [_vp]),
+    "mhlo_cuda_device_error_take": (C.c_int, [C.POINTER(_i32)]),
+    "mhlo_cuda_debug_store_device_error": (C.c_int, [_i32, _i32]),
+    "mhlo_cuda_debug_refuse_allocs": (C.c_int, [_i32]),
+    "mhlo_cuda_debug_wait_expiry_probe": (C.c_int, [C.c_uint64, _vp]),
     "mhlo_cuda_attention": (C.c_int, [_i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _vp,
                                       C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
 }

@@ -1501,7 +1501,7 @@ class Interpreter:
                 s = s + a[3]
             if cfg.get("is_causal"):
                 sq, sk = s.shape[-2:]
-                s = np.where(np.arange(sk)[None, :] <= np.arange(sq)[:, None] + (sk - sq), s, -np.inf)
+                s = np.where(np.arange(sk)[None, :] <= np.arange(sq)[:, None], s, -np.inf)  # kv_pos > q_pos is cut
             p = np.exp(s - s.max(-1, keepdims=True))
             p = p / p.sum(-1, keepdims=True)
             return np.einsum("...qk,...kd->...qd", p, v)

@@ -150,8 +150,8 @@ ORACLE_API void oracle_gemm(const float* a, const float* b, double* c, int64_t b
 /* ---- scaled dot-product attention: FusedScaledDotProductAttentionHandler.emitManualSDPA,
  * CustomCallHandlers.swift:245-276: scores = Q K^T * scale (+ mask); softmax over keys; out = P V.
  * Q [bh, sq, d], K/V [bh, sk, d] with bh = batch*heads. causal: key j is visible to query i iff
- * j <= i + (sk - sq) (the tiled kernel's `kv_pos > q_pos` cut,
- * Sources/MetalHLOCore/Metal/Kernels/FlashAttentionKernel.swift:469-615, with sq == sk). mask (optional) is
+ * j <= i, also when sq != sk (the tiled kernel's `kv_pos > q_pos` cut,
+ * Sources/MetalHLOCore/Metal/Kernels/FlashAttentionKernel.swift:545,578). mask (optional) is
  * additive, [sq, sk], shared by all bh. */
 ORACLE_API void oracle_attention(const float* q, const float* k, const float* v, const float* mask, double* o,
                                  int64_t bh, int64_t sq, int64_t sk, int64_t d, double scale, int causal) {
@@ -162,7 +162,7 @@ ORACLE_API void oracle_attention(const float* q, const float* k, const float* v,
         for (int64_t h = 0; h < bh; ++h) {
             for (int64_t i = 0; i < sq; ++i) {
                 const float* qi = q + (h * sq + i) * d;
-                int64_t lim = causal ? i + (sk - sq) + 1 : sk;
+                int64_t lim = causal ? i + 1 : sk;
                 if (lim > sk) lim = sk;
                 double m = -INFINITY;
                 for (int64_t j = 0; j < lim; ++j) {
@@ -291,7 +291,7 @@ ORACLE_API void cpu_attention_f32(const float* q, const float* k, const float* v
             float acc[512];
             float m = -INFINITY, l = 0.f;
             for (int64_t t = 0; t < d; ++t) acc[t] = 0.f;
-            int64_t lim = causal ? i + (sk - sq) + 1 : sk;
+            int64_t lim = causal ? i + 1 : sk;
             if (lim > sk) lim = sk;
             for (int64_t j = 0; j < lim; ++j) {
                 const float* kj = k + (h * sk + j) * d;

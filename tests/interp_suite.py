@@ -3,16 +3,23 @@
 `check.expect_*` lines out of each function and rewrites the function so that it returns the checked values.
 Same convention as the reference's InterpretTestParser (Tests/MetalHLOTests/Conformance/InterpretTestParser.swift:62-241).
 
-The suite lives in the reference checkout only; nothing of it is copied into this repository.
+The suite is read from the reference checkout when one is present: the directory named by MHLO_INTERP_SUITE_DIR, else the
+checkout beside this repository. Where there is none (the GPU box), the cases come from tests/golden/interp_suite.json.gz,
+which tests/golden/make_interp_suite.py wrote from that checkout with this same loader.
 """
 from __future__ import annotations
 
+import gzip
+import json
 import os
 import re
 
-SUITE_DIR = "/root/reference/Tests/MetalHLOTests/Conformance/StableHLO/interpret"
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SUITE_DIR = os.environ.get("MHLO_INTERP_SUITE_DIR") or os.path.join(
+    os.path.dirname(_ROOT), "reference", "Tests", "MetalHLOTests", "Conformance", "StableHLO", "interpret")
+FIXTURE = os.path.join(_ROOT, "tests", "golden", "interp_suite.json.gz")
 
-# the operator surface of this backend (SURVEY hot path + the data-movement ops around it)
+# the operator surface of this backend (the fused hot path + the data-movement ops around it)
 FILES = ["abs", "add", "and", "atan2", "broadcast_in_dim", "cbrt", "ceil", "clamp", "compare", "concatenate", "constant",
          "convert", "cosine", "count_leading_zeros", "divide", "dot_general", "dynamic_slice", "dynamic_update_slice",
          "exponential", "exponential_minus_one", "floor", "gather", "iota", "is_finite", "log", "log_plus_one", "logistic",
@@ -88,7 +95,7 @@ def load_cases(file):
     return cases
 
 
-def all_cases():
+def cases_from_checkout():
     out = []
     if not os.path.isdir(SUITE_DIR):
         return out
@@ -96,3 +103,55 @@ def all_cases():
         if os.path.exists(os.path.join(SUITE_DIR, f + ".mlir")):
             out.extend(load_cases(f))
     return out
+
+
+def cases_from_fixture():
+    if not os.path.exists(FIXTURE):
+        return []
+    with gzip.open(FIXTURE, "rt") as f:
+        doc = json.load(f)
+    return [Case(c["file"], c["name"], c["text"], c["checks"]) for c in doc["cases"]]
+
+
+def all_cases():
+    """The suite from the reference checkout; from the committed fixture where there is no checkout."""
+    return cases_from_checkout() or cases_from_fixture()
+
+
+UNSUPPORTED_MARKERS = ("complex<", "f8E", "f4E", "f6E", "i2>", "i4>", "ui2>", "ui4>", "tf32", "quant", "x?x", "<?x", "token")
+
+
+def skip_reason(text):
+    """Element types outside the backend's 13 (MHLOElementType) put a case out of scope."""
+    for bad in UNSUPPORTED_MARKERS:
+        if bad in text:
+            return bad
+    return None
+
+
+def verify(case, outs):
+    """Holds the returned values of one case to its goldens with the reference runner's tolerances: exact for
+    expect_eq, 1e-4 for expect_almost_eq / expect_close (Conformance/InterpretTestRunner.swift:37-45); 16-bit floats are
+    compared after rounding both sides to the type."""
+    import numpy as np
+
+    from oracle import interp
+
+    for chk in case.checks:
+        got = np.asarray(outs[chk["value"]])
+        t = interp.Scanner(chk["type"]).type()
+        want = interp.dense_value(chk["dense"], t) if "dense" in chk else np.asarray(outs[chk["other"]])
+        if t.is_float:
+            tol = 0 if chk["kind"].startswith("expect_eq") else 1e-4
+            got = got.astype(np.float64)
+            want = np.asarray(want, dtype=np.float64)
+            if t.dtype in ("f16", "bf16"):
+                want = interp.round_to(want, t.dtype)
+                got = interp.round_to(got, t.dtype)
+                tol = max(tol, 1e-2)
+            elif t.dtype == "f32":
+                got = interp.round_to(got, "f32")
+                tol = max(tol, 1e-6)
+            np.testing.assert_allclose(got, want, rtol=tol, atol=tol, equal_nan=True, err_msg=case.id)
+        else:
+            np.testing.assert_array_equal(got, np.asarray(want).astype(got.dtype) if got.dtype != np.asarray(want).dtype else want, err_msg=case.id)

@@ -1,10 +1,10 @@
 """Shared helpers of the parity tests: seeded inputs and the tolerance rule.
 
 Tolerance rule (from the north-star statement of the build): bit-exact for integer/index results,
-rel <= 1e-5 for fp32 results, rel <= 2e-2 for f16/bf16 results. "rel" is applied per element as
-|got - want| <= rel * (|want| + mean|want|): the second term keeps elements that sit at a zero crossing of the
-fp64 result (where any finite-precision evaluation has unbounded relative error) on the same scale as the
-rest of the tensor.
+rel <= 1e-5 for fp32 results, rel <= 2e-2 for f16/bf16 results. "rel" is the plain per-element bound
+|got - want| <= rel * |want| for every element whose magnitude reaches the tensor's mean magnitude. Elements below
+the mean (zero crossings of the fp64 result, where any finite-precision evaluation has unbounded relative error) are
+held to the absolute bound rel * mean|want|, i.e. the bound is rel * max(|want|, mean|want|).
 """
 import numpy as np
 
@@ -15,6 +15,28 @@ def rel_for(dtype) -> float:
     return REL[str(dtype).replace("torch.", "")]
 
 
+def error_report(got, want, rel, row_scale=False):
+    """Per-element accounting of one comparison: counts of elements at or above the mean magnitude (held to the plain
+    relative bound) and below it (held to rel * mean), how many of each fail, and the worst plain relative error among
+    the former."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    fin = np.isfinite(want)
+    scale = np.mean(np.abs(want[fin])) if fin.any() else 0.0
+    if row_scale and want.ndim >= 1:
+        # attention rows that see few keys keep the magnitude of single value vectors: scale each row by itself
+        scale = np.broadcast_to(np.mean(np.abs(np.where(fin, want, 0.0)), axis=-1, keepdims=True), want.shape)[fin]
+    w, g = want[fin], got[fin]
+    err = np.abs(g - w)
+    large = np.abs(w) >= scale
+    bound = rel * np.maximum(np.abs(w), scale)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        plain = np.where(large & (np.abs(w) > 0), err / np.abs(w), 0.0)
+    return {"elements": int(w.size), "large": int(large.sum()), "large_failing": int((large & (err > bound)).sum()),
+            "small_failing": int((~large & (err > bound)).sum()), "worst_plain_rel": float(plain.max()) if w.size else 0.0,
+            "err": err, "bound": bound, "got": g, "want": w}
+
+
 def assert_close(got, want, rel, what="", row_scale=False):
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
@@ -22,19 +44,16 @@ def assert_close(got, want, rel, what="", row_scale=False):
     if want.size == 0:
         return
     assert np.all(np.isfinite(got) == np.isfinite(want)), f"{what}: non-finite pattern differs"
-    fin = np.isfinite(want)
-    scale = np.mean(np.abs(want[fin])) if fin.any() else 0.0
-    if row_scale and want.ndim >= 1:
-        # attention rows that see few keys keep the magnitude of single value vectors: scale each row by itself
-        scale = np.broadcast_to(np.mean(np.abs(np.where(fin, want, 0.0)), axis=-1, keepdims=True), want.shape)[fin]
-    err = np.abs(got[fin] - want[fin])
-    bound = rel * (np.abs(want[fin]) + scale)
-    bad = err > bound
-    if bad.any():
-        i = int(np.argmax(err - bound))
+    inf = np.isinf(want)
+    assert np.array_equal(got[inf], want[inf]), f"{what}: infinities differ"
+    r = error_report(got, want, rel, row_scale)
+    bad = r["large_failing"] + r["small_failing"]
+    if bad:
+        i = int(np.argmax(r["err"] - r["bound"]))
         raise AssertionError(
-            f"{what}: {int(bad.sum())}/{bad.size} elements outside rel={rel}; worst got={got[fin][i]!r} "
-            f"want={want[fin][i]!r} err={err[i]:.3e} bound={bound[i]:.3e}")
+            f"{what}: {bad}/{r['elements']} elements outside rel={rel} ({r['large_failing']} of the {r['large']} at or above the "
+            f"mean magnitude, worst plain relative error {r['worst_plain_rel']:.3e}); worst got={r['got'][i]!r} "
+            f"want={r['want'][i]!r} err={r['err'][i]:.3e} bound={r['bound'][i]:.3e}")
 
 
 def to_np(t):

@@ -17,6 +17,7 @@ HEADERS = {
     "mhlo_cuda.h": "libmhlo_cuda.so",
     "metalhlo.h": "libCMetalHLO.so",
     "pjrt_plugin_metalhlo.h": "pjrt_plugin_metalhlo_b200.so",
+    "pjrt_host.h": "libpjrt_host.so",
 }
 MIN_FUNCTIONS = {"pjrt_plugin_metalhlo.h": 1}
 
@@ -25,7 +26,7 @@ def declared_functions(header_path):
     text = open(header_path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     text = re.sub(r"//[^\n]*", " ", text)
-    names = re.findall(r"\b((?:mhlo_|GetPjrtApi)\w*)\s*\(", text)
+    names = re.findall(r"\b((?:mhlo_|pjrt_host_|GetPjrtApi)\w*)\s*\(", text)
     return sorted(set(names))
 
 
@@ -53,6 +54,26 @@ def test_python_binding_matches_header():
 
     declared = set(declared_functions(os.path.join(ROOT, "include", "mhlo_cuda.h")))
     assert set(cuda.declared_symbols()) == declared
+
+
+def test_pjrt_host_binding_matches_header():
+    from metalhlo_b200 import pjrt
+
+    declared = set(declared_functions(os.path.join(ROOT, "include", "pjrt_host.h")))
+    assert set(pjrt.declared_symbols()) == declared
+
+
+def test_pjrt_host_reports_the_plugin_error_without_a_gpu():
+    import torch
+
+    from metalhlo_b200 import pjrt
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(pjrt.PjrtError, match="No CUDA device"):
+        pjrt.Host()
+    with pytest.raises(pjrt.PjrtError, match="dlopen failed"):
+        pjrt.Host("/nonexistent/plugin.so")
 
 
 def test_no_device_calls_report_status_not_crash():

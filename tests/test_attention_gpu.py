@@ -98,16 +98,24 @@ def test_more_tiles_than_resident_ctas(causal):
     assert_close(to_np(got), reference(q, k, v, 0.125, causal, "BHSD"), 2e-2, f"many tiles causal={causal}", row_scale=True)
 
 
-def test_causal_tiles_without_any_visible_key():
-    """seq_q > seq_k under a causal mask: the first query blocks see no key at all (rows of zeros, as the oracle
-    gives), and such tiles sit between ordinary ones in a CTA's walk."""
+@pytest.mark.parametrize("sq,sk", [(768, 256), (256, 768), (300, 170)])
+def test_causal_cut_when_query_and_key_lengths_differ(sq, sk):
+    """Under the causal flag key j is visible to query i iff j <= i whatever the two lengths are: the reference kernel
+    cuts at `kv_pos > q_pos` (Sources/MetalHLOCore/Metal/Kernels/FlashAttentionKernel.swift:545,578). With more queries
+    than keys the late rows see every key; with more keys than queries the keys past the last query are never read.
+    Checked against the oracle and against a numpy statement of the rule written out here."""
     cuda = cuda_mod()
-    q, k, v = qkv(2, 40, 768, 256, 128, torch.bfloat16, "BHSD", seed=23)
-    got = cuda.attention(q.cuda(), k.cuda(), v.cuda(), 0.1, causal=True)
+    q, k, v = qkv(2, 5, sq, sk, 128, torch.bfloat16, "BHSD", seed=23)
+    got = to_np(cuda.attention(q.cuda(), k.cuda(), v.cuda(), 0.1, causal=True))
     assert cuda.device_error() == 0
-    want = reference(q, k, v, 0.1, True, "BHSD")
-    assert np.all(to_np(got)[:, :, :512, :] == 0) and np.all(want[:, :, :512, :] == 0)
-    assert_close(to_np(got), want, 2e-2, "empty tiles", row_scale=True)
+    assert_close(got, reference(q, k, v, 0.1, True, "BHSD"), 2e-2, "oracle", row_scale=True)
+    s = np.einsum("bhqd,bhkd->bhqk", to_np(q), to_np(k)) * 0.1
+    s = np.where(np.arange(sk)[None, :] > np.arange(sq)[:, None], -np.inf, s)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    want = np.einsum("bhqk,bhkd->bhqd", p / p.sum(-1, keepdims=True), to_np(v))
+    assert_close(got, want, 2e-2, "kv_pos > q_pos rule", row_scale=True)
+    # query 0 sees key 0 only: its output row is V[0] exactly
+    np.testing.assert_array_equal(got[:, :, 0, :], to_np(v)[:, :, 0, :])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)

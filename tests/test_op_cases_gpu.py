@@ -23,7 +23,6 @@ def client():
 
 
 REL = {"f32": 1e-5, "f16": 2e-2, "bf16": 2e-2, "f64": 1e-12}
-# transcendental kernels of the device differ from libm by a few ulp; the north-star tolerance for fp32 is 1e-5
 
 
 def dtype_tag(arr):
@@ -42,10 +41,7 @@ def test_case_matches_oracle(name, level):
         if tag is None:
             np.testing.assert_array_equal(g, w.astype(g.dtype), err_msg=f"{name} O{level}")
         else:
-            rel = REL[tag]
-            if name.startswith(("power", "tan_", "atan2")) and tag == "f32":
-                rel = 4e-5  # pow/atan2 on the device are accurate to a few ulp of fp32, relative to larger intermediates
-            assert_close(g.astype(np.float64), w, rel, f"{name} O{level}")
+            assert_close(g.astype(np.float64), w, REL[tag], f"{name} O{level}")
 
 
 @pytest.mark.parametrize("name", [c[0] for c in CASES if c[0].startswith("conv_")])
