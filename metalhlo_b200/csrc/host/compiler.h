@@ -51,6 +51,8 @@ bool flatten_maps(Function& f);
 void optimize_loop_bodies(Function& f, const CompileOptions& options);
 // Replaces chlo.top_k by iota + stable descending sort + slices.
 bool flatten_top_k(Function& f);
+// Replaces the results of stablehlo.optimization_barrier by its operands.
+bool drop_optimization_barriers(Function& f);
 // All four, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
 

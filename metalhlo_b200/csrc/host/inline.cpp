@@ -419,6 +419,28 @@ bool flatten_maps(Function& f) {
 
 // chlo.top_k(x, k): the k largest entries of the last dimension and their positions, ties in index order. Rewritten to
 // iota + stable descending sort of (x, iota) + two slices, which the sort kernel and zero-copy slices then run.
+// stablehlo.optimization_barrier is the identity on each of its operands (it only fences compiler motion): its results
+// are replaced by its operands, whatever their number.
+bool drop_optimization_barriers(Function& f) {
+    bool changed = false;
+    std::vector<Op> out;
+    std::map<int, int> alias;
+    for (Op& op : f.ops) {
+        apply_alias(op, alias);
+        if (!op.dead && op.name == "optimization_barrier" && op.results.size() == op.operands.size()) {
+            for (size_t i = 0; i < op.results.size(); ++i) alias[op.results[i]] = op.operands[i];
+            changed = true;
+            continue;
+        }
+        out.push_back(std::move(op));
+    }
+    if (changed) {
+        f.ops.swap(out);
+        f.compact();
+    }
+    return changed;
+}
+
 bool flatten_top_k(Function& f) {
     bool any = false;
     std::vector<Op> out;
@@ -511,7 +533,8 @@ Function flatten_main(Module& m) {
         const bool c = flatten_conditionals(main);
         const bool d = flatten_maps(main);
         const bool e = flatten_top_k(main);
-        return a || b || c || d || e;
+        const bool g = drop_optimization_barriers(main);
+        return a || b || c || d || e || g;
     };
     for (int round = 0; round < kMaxInlineRounds; ++round) {
         const bool top = all();

@@ -1141,7 +1141,7 @@ class Parser {
             rename("dimensions", n == "broadcast_in_dim" ? "broadcast_dimensions" : (n == "transpose" ? "permutation" : "dimensions"));
         }
         if (n == "concatenate" || n == "get_dimension_size") { rename("dim", "dimension"); }
-        if (n == "iota") { rename("dim", "iota_dimension"); rename("dimension", "iota_dimension"); }
+        if (n == "iota" || n == "dynamic_iota") { rename("dim", "iota_dimension"); rename("dimension", "iota_dimension"); }
         if (n == "reduce") {
             rename("dims", "dimensions");
             // classify the reducer region when there is no `applies` clause

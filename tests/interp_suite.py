@@ -50,18 +50,43 @@ def _split_dense(rest):
     return (m.group(1), m.group(2)) if m else None
 
 
+def _functions(chunk):
+    """Top-level `func.func` definitions of one chunk as (name, start, end of the closing brace)."""
+    out = []
+    for m in re.finditer(r"func\.func\s+(?:private\s+|public\s+)?@([\w.]+)", chunk):
+        if out and m.start() < out[-1][2]:
+            continue  # nested inside the previous function (cannot happen in MLIR, but stay safe)
+        depth, i = 0, chunk.index("{", m.end())
+        while True:
+            c = chunk[i]
+            if c == "{":
+                depth += 1
+            elif c == "}":
+                depth -= 1
+                if depth == 0:
+                    break
+            i += 1
+        out.append((m.group(1), m.start(), i + 1))
+    return out
+
+
 def load_cases(file):
     path = os.path.join(SUITE_DIR, file + ".mlir")
     text = open(path).read()
     cases = []
     for chunk in re.split(r"^// -----\s*$", text, flags=re.M):
-        m = re.search(r"func\.func\s+@([\w.]+)\s*\(\s*\)\s*(?:->\s*[^{]*)?\{", chunk)
+        chunk = re.sub(r"^\s*//[^\n]*$", "", chunk, flags=re.M)  # RUN / comment lines
+        funcs = _functions(chunk)
+        # the function that carries the checks is the test; the others are its callees and are kept as they are
+        tests = [f for f in funcs if "check." in chunk[f[1]:f[2]]]
+        if len(tests) != 1:
+            continue
+        name, start, end = tests[0]
+        m = re.match(r"func\.func\s+(?:private\s+|public\s+)?@[\w.]+\s*\(\s*\)\s*(?:->\s*[^{]*)?\{", chunk[start:end])
         if not m:
             continue
-        name = m.group(1)
-        body_start = m.end()
-        body_end = chunk.rfind("}")
-        body = chunk[body_start:body_end]
+        body = chunk[start + m.end():end - 1]
+        callees = "".join(chunk[s:e] + "\n" for n, s, e in funcs if (n, s, e) != tests[0])
         checks, returns, ret_types = [], [], []
         ok = True
 
@@ -91,6 +116,8 @@ def load_cases(file):
             continue
         new = (f"func.func @main() -> ({', '.join(ret_types)}) {{\n{body}\n  return {', '.join(returns)} : "
                f"{', '.join(ret_types)}\n}}\n")
+        if callees:
+            new = "module {\n" + new + callees + "}\n"
         cases.append(Case(file, name, new, checks))
     return cases
 

@@ -5,6 +5,12 @@ rel <= 1e-5 for fp32 results, rel <= 2e-2 for f16/bf16 results. "rel" is the pla
 |got - want| <= rel * |want| for every element whose magnitude reaches the tensor's mean magnitude. Elements below
 the mean (zero crossings of the fp64 result, where any finite-precision evaluation has unbounded relative error) are
 held to the absolute bound rel * mean|want|, i.e. the bound is rel * max(|want|, mean|want|).
+
+Results of a contraction evaluated in 16-bit steps (attention: 16-bit scores and probabilities feeding P.V) may instead be
+given their `magnitude`: the sum of the absolute values of the contracted terms, sum_j |p_j| |v_j|, per element. That sum
+is what bounds the error of any finite-precision inner product (|fl(x.y) - x.y| <= c * u * sum |x_j y_j|); against
+|x.y| itself the error is unbounded wherever the terms cancel. With a magnitude the bound is
+rel * max(magnitude, mean|want|).
 """
 import numpy as np
 
@@ -15,7 +21,7 @@ def rel_for(dtype) -> float:
     return REL[str(dtype).replace("torch.", "")]
 
 
-def error_report(got, want, rel, row_scale=False):
+def error_report(got, want, rel, row_scale=False, magnitude=None):
     """Per-element accounting of one comparison: counts of elements at or above the mean magnitude (held to the plain
     relative bound) and below it (held to rel * mean), how many of each fail, and the worst plain relative error among
     the former."""
@@ -30,6 +36,10 @@ def error_report(got, want, rel, row_scale=False):
     err = np.abs(g - w)
     large = np.abs(w) >= scale
     bound = rel * np.maximum(np.abs(w), scale)
+    if magnitude is not None:
+        mag = np.asarray(magnitude, dtype=np.float64)[fin]
+        assert np.all(mag >= np.abs(w) * (1 - 1e-9)), "a magnitude is the sum of absolute terms: it cannot be below |want|"
+        bound = np.maximum(bound, rel * mag)
     with np.errstate(divide="ignore", invalid="ignore"):
         plain = np.where(large & (np.abs(w) > 0), err / np.abs(w), 0.0)
     return {"elements": int(w.size), "large": int(large.sum()), "large_failing": int((large & (err > bound)).sum()),
@@ -37,7 +47,7 @@ def error_report(got, want, rel, row_scale=False):
             "err": err, "bound": bound, "got": g, "want": w}
 
 
-def assert_close(got, want, rel, what="", row_scale=False):
+def assert_close(got, want, rel, what="", row_scale=False, magnitude=None):
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, (got.shape, want.shape)
@@ -46,7 +56,7 @@ def assert_close(got, want, rel, what="", row_scale=False):
     assert np.all(np.isfinite(got) == np.isfinite(want)), f"{what}: non-finite pattern differs"
     inf = np.isinf(want)
     assert np.array_equal(got[inf], want[inf]), f"{what}: infinities differ"
-    r = error_report(got, want, rel, row_scale)
+    r = error_report(got, want, rel, row_scale, magnitude)
     bad = r["large_failing"] + r["small_failing"]
     if bad:
         i = int(np.argmax(r["err"] - r["bound"]))

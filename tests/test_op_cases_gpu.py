@@ -36,12 +36,16 @@ def test_case_matches_oracle(name, level):
     want = interp.evaluate(text, inputs)
     got = client().run(text, inputs, opt_level=level)
     assert len(got) == len(want)
+    magnitude = None
+    if name.startswith("pattern_attention") and dtype_tag(got[0]) in ("f16", "bf16"):
+        # sum_j p_ij |v_jd| of the same module: the scale of the terms each output element contracts (tests/parity.py)
+        magnitude = interp.evaluate(text, [inputs[0], inputs[1], np.abs(inputs[2])])[0]
     for g, w in zip(got, want):
         tag = dtype_tag(g)
         if tag is None:
             np.testing.assert_array_equal(g, w.astype(g.dtype), err_msg=f"{name} O{level}")
         else:
-            assert_close(g.astype(np.float64), w, REL[tag], f"{name} O{level}")
+            assert_close(g.astype(np.float64), w, REL[tag], f"{name} O{level}", magnitude=magnitude)
 
 
 @pytest.mark.parametrize("name", [c[0] for c in CASES if c[0].startswith("conv_")])
