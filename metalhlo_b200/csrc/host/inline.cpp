@@ -434,10 +434,8 @@ bool drop_optimization_barriers(Function& f) {
         }
         out.push_back(std::move(op));
     }
-    if (changed) {
-        f.ops.swap(out);
-        f.compact();
-    }
+    f.ops.swap(out);
+    if (changed) f.compact();
     return changed;
 }
 
