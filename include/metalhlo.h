@@ -154,6 +154,30 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
  * per line (free with mhlo_free_string); out_launches / out_arena_bytes may be NULL. */
 MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_level, char** out_steps,
                                    int32_t* out_launches, int64_t* out_arena_bytes);
+/*
+ * Batch sharding. The reference runs every program on one device (Sources/PJRTMetalHLO/PJRTExecutable.swift:1830-1848
+ * fixes num_replicas = num_partitions = 1 and :2033-2036 refuses several devices). Here a program whose results are,
+ * slice by slice along one axis, functions of the same slice of its batched arguments is split into shard_count equal
+ * shards with no exchange on the data path; each GPU (one process per GPU, or one PJRT device each) compiles and runs
+ * one shard. The proof is a propagation of the split axis through every operator; a program that mixes elements along
+ * the split axis (a reduction, contraction, sort, window or gather over it) is refused with
+ * MHLO_ERROR_UNSUPPORTED_OP and the operator's name.
+ *   mhlo_b200_compile_sharded    compiles shard shard_index. input_axes (one per argument: split axis, or -1 for a
+ *                                replicated argument) may be NULL: then every argument whose leading extent equals the
+ *                                first argument's is split along axis 0. The executable's types are one shard's.
+ *   mhlo_b200_executable_sharding  count, index and the split axis of each argument / result (-1: replicated).
+ *   mhlo_b200_shard_text         host-only: the rewritten function as text (free with mhlo_free_string).
+ * A client created with METALHLO_SHARD_COUNT / METALHLO_SHARD_INDEX in the environment applies the same split to every
+ * mhlo_compile* call.
+ */
+MHLOStatusCode mhlo_b200_compile_sharded(MHLOClientRef client, const char* mlir_text, const MHLOCompileConfig* config,
+                                         int32_t shard_count, int32_t shard_index, const int32_t* input_axes,
+                                         int32_t num_input_axes, MHLOExecutableRef* out_executable);
+MHLOStatusCode mhlo_b200_executable_sharding(MHLOExecutableRef executable, int32_t* out_count, int32_t* out_index,
+                                             int32_t* out_input_axes, int32_t* out_output_axes);
+MHLOStatusCode mhlo_b200_shard_text(const char* mlir_text, int32_t shard_count, int32_t shard_index,
+                                    const int32_t* input_axes, int32_t num_input_axes, char** out_text,
+                                    int32_t* out_input_axes, int32_t* out_output_axes);
 /* StableHLO text after the pass pipeline; free with mhlo_free_string. */
 char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable);
 /* Kernel launches one execution enqueues. */

@@ -105,6 +105,9 @@ _PROTOTYPES = {
     "mhlo_execute_with_profile": (C.c_int, [_vp, _P(_vp), _i32, _P(_vp), _P(_i32), _P(ExecutionProfile)]),
     "mhlo_b200_optimize_text": (C.c_int, [C.c_char_p, _i32, _P(_vp)]),
     "mhlo_b200_plan_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i32), _P(_i64)]),
+    "mhlo_b200_compile_sharded": (C.c_int, [_vp, C.c_char_p, _P(CompileConfig), _i32, _i32, _P(_i32), _i32, _P(_vp)]),
+    "mhlo_b200_executable_sharding": (C.c_int, [_vp, _P(_i32), _P(_i32), _P(_i32), _P(_i32)]),
+    "mhlo_b200_shard_text": (C.c_int, [C.c_char_p, _i32, _i32, _P(_i32), _i32, _P(_vp), _P(_i32), _P(_i32)]),
     "mhlo_b200_executable_optimized_text": (_vp, [_vp]),
     "mhlo_b200_executable_launch_count": (_i32, [_vp]),
     "mhlo_b200_executable_arena_bytes": (_i64, [_vp]),
@@ -164,6 +167,15 @@ def plan_text(mlir: str, opt_level: int = 3):
     out, launches, arena = _vp(), _i32(0), _i64(0)
     _check(lib.mhlo_b200_plan_text(mlir.encode(), opt_level, C.byref(out), C.byref(launches), C.byref(arena)))
     return _take_string(out.value).splitlines(), launches.value, arena.value
+
+
+def shard_text(mlir: str, count: int, index: int, input_axes=None, n_inputs: int = 64, n_outputs: int = 16):
+    """Host only: the function that computes shard `index` of `count`, and the split axis of every argument / result."""
+    out = _vp()
+    ia, oa = (_i32 * n_inputs)(*([-2] * n_inputs)), (_i32 * n_outputs)(*([-2] * n_outputs))
+    axes = (_i32 * len(input_axes))(*input_axes) if input_axes is not None else None
+    _check(lib.mhlo_b200_shard_text(mlir.encode(), count, index, axes, len(input_axes) if input_axes is not None else 0, C.byref(out), ia, oa))
+    return _take_string(out.value), [a for a in ia if a != -2], [a for a in oa if a != -2]
 
 
 class tuning:
@@ -300,6 +312,14 @@ class Executable:
         outs = (_vp * max(len(output_ptrs), 1))(*output_ptrs)
         _check(lib.mhlo_b200_execute_on_device(self._h, ins, outs, stream))
 
+    @property
+    def sharding(self):
+        """(shard count, shard index, split axis per input, split axis per output); -1 = replicated."""
+        n, k = _i32(), _i32()
+        ia, oa = (_i32 * max(self.input_count, 1))(), (_i32 * max(self.output_count, 1))()
+        _check(lib.mhlo_b200_executable_sharding(self._h, C.byref(n), C.byref(k), ia, oa))
+        return n.value, k.value, list(ia)[:self.input_count], list(oa)[:self.output_count]
+
     def stats(self) -> ExecutionStats:
         s = ExecutionStats()
         _check(lib.mhlo_executable_get_stats(self._h, C.byref(s)))
@@ -354,6 +374,17 @@ class Client:
             cfg.optimization_level = opt_level
             cfg.enable_caching = caching
             _check(lib.mhlo_compile_with_config(self._h, mlir.encode(), C.byref(cfg), C.byref(h)))
+        return Executable(h.value, self)
+
+    def compile_sharded(self, mlir: str, count: int, index: int, opt_level: int = 3, input_axes=None) -> Executable:
+        """Shard `index` of `count` equal batch shards of the program (mhlo_b200_compile_sharded)."""
+        h = _vp()
+        cfg = CompileConfig()
+        lib.mhlo_compile_config_init(C.byref(cfg))
+        cfg.optimization_level = opt_level
+        axes = (_i32 * len(input_axes))(*input_axes) if input_axes is not None else None
+        _check(lib.mhlo_b200_compile_sharded(self._h, mlir.encode(), C.byref(cfg), count, index, axes,
+                                             len(input_axes) if input_axes is not None else 0, C.byref(h)))
         return Executable(h.value, self)
 
     def buffer(self, array, element_type: int | None = None) -> Buffer:

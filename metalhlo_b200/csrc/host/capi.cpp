@@ -33,6 +33,9 @@ int set_error(int code, const std::string& msg) {
 }
 
 struct Client {
+    // METALHLO_SHARD_COUNT / METALHLO_SHARD_INDEX: every program this client compiles is split over that many equal
+    // batch shards and this client builds and runs the shard with that index (one process per GPU, one shard each).
+    int shard_count = 1, shard_index = 0;
     int device = 0;
     void* stream = nullptr;
     std::mutex mu;
@@ -203,11 +206,14 @@ MHLOStatusCode run(ExecutableHandle* h, const MHLOBufferRef* inputs, int32_t num
     return MHLO_OK;
 }
 
-MHLOStatusCode compile_impl(Client* c, const std::string& text, const MHLOCompileConfig* config, MHLOExecutableRef* out) {
+MHLOStatusCode compile_impl(Client* c, const std::string& text, const MHLOCompileConfig* config, MHLOExecutableRef* out,
+                            const ShardSpec* shard = nullptr) {
     if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "client is null"));
     if (!out) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_executable is null"));
     *out = nullptr;
     CompileOptions opt;
+    if (shard) opt.shard = *shard;
+    else { opt.shard.count = c->shard_count; opt.shard.index = c->shard_index; }
     if (config) {
         if (config->optimization_level < 0 || config->optimization_level > 3)
             return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "optimization_level out of range"));
@@ -218,7 +224,9 @@ MHLOStatusCode compile_impl(Client* c, const std::string& text, const MHLOCompil
     if (const char* env = std::getenv("METALHLO_OPT_LEVEL"))
         if (!config && env[0] >= '0' && env[0] <= '3') opt.opt_level = env[0] - '0';
     if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
-    const std::string key = std::to_string(opt.opt_level) + "|" + text;
+    std::string key = std::to_string(opt.opt_level) + "|" + std::to_string(opt.shard.count) + "/" + std::to_string(opt.shard.index) + ":";
+    for (int a : opt.shard.input_axes) key += std::to_string(a) + ",";
+    key += "|" + text;
     std::shared_ptr<Executable> exe;
     {
         std::lock_guard<std::mutex> lock(c->mu);
@@ -279,6 +287,12 @@ MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) {
     std::unique_ptr<Client> c(new Client());
     c->pool_limit = pool_limit_from_env();
     // one process drives one GPU: LOCAL_RANK picks it when several ranks share a box
+    if (const char* sc = std::getenv("METALHLO_SHARD_COUNT")) {
+        c->shard_count = std::atoi(sc);
+        if (const char* si = std::getenv("METALHLO_SHARD_INDEX")) c->shard_index = std::atoi(si);
+        if (c->shard_count < 1 || c->shard_index < 0 || c->shard_index >= c->shard_count)
+            return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "METALHLO_SHARD_COUNT / METALHLO_SHARD_INDEX out of range"));
+    }
     if (const char* lr = std::getenv("METALHLO_DEVICE")) c->device = std::atoi(lr);
     else if (const char* lr2 = std::getenv("LOCAL_RANK")) c->device = std::atoi(lr2) % n;
     if (c->device < 0 || c->device >= n) c->device = 0;
@@ -556,6 +570,66 @@ MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_l
         *out_steps = strdup(s.c_str());
         if (out_launches) *out_launches = exe->num_kernel_launches();
         if (out_arena_bytes) *out_arena_bytes = exe->arena_bytes();
+        return MHLO_OK;
+    } catch (const CompileError& e) {
+        return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));
+    } catch (const std::exception& e) {
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
+    }
+}
+
+// ---- batch sharding ------------------------------------------------------------------------------------------------
+
+namespace {
+ShardSpec make_spec(int32_t count, int32_t index, const int32_t* input_axes, int32_t num_axes) {
+    ShardSpec s;
+    s.count = count;
+    s.index = index;
+    if (input_axes) s.input_axes.assign(input_axes, input_axes + num_axes);
+    return s;
+}
+}  // namespace
+
+// Compiles shard `shard_index` of `shard_count` equal batch shards of the program. input_axes (num_input_axes entries, one
+// per argument: the split axis or -1 for replicated) may be NULL: then every argument whose leading extent equals the
+// first argument's is split along axis 0. The executable's input and output types are those of one shard. Fails with
+// MHLO_ERROR_UNSUPPORTED_OP, naming the operator, when the shards would depend on one another.
+MHLOStatusCode mhlo_b200_compile_sharded(MHLOClientRef client, const char* mlir_text, const MHLOCompileConfig* config, int32_t shard_count,
+                                         int32_t shard_index, const int32_t* input_axes, int32_t num_input_axes, MHLOExecutableRef* out_executable) {
+    if (!mlir_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "mlir_text is null"));
+    if (shard_count < 1 || shard_index < 0 || shard_index >= shard_count)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "shard index / count out of range"));
+    const ShardSpec spec = make_spec(shard_count, shard_index, input_axes, num_input_axes);
+    return compile_impl(static_cast<Client*>(client), mlir_text, config, out_executable, &spec);
+}
+
+// How an executable was split: shard count and index, and per argument / result the split axis (-1: replicated) and the
+// extents before the split (rank entries each, concatenated; any pointer may be NULL).
+MHLOStatusCode mhlo_b200_executable_sharding(MHLOExecutableRef executable, int32_t* out_count, int32_t* out_index, int32_t* out_input_axes,
+                                             int32_t* out_output_axes) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));
+    const ShardPlan& p = h->exe->shard_plan();
+    if (out_count) *out_count = p.count;
+    if (out_index) *out_index = p.index;
+    if (out_input_axes) for (size_t i = 0; i < p.input_axes.size(); ++i) out_input_axes[i] = p.input_axes[i];
+    if (out_output_axes) for (size_t i = 0; i < p.output_axes.size(); ++i) out_output_axes[i] = p.output_axes[i];
+    return MHLO_OK;
+}
+
+// Host-only: the analysis and rewrite alone. *out_text receives the function that computes the shard (malloc'd; free with
+// mhlo_free_string); out_input_axes / out_output_axes (may be NULL) one entry per argument / result.
+MHLOStatusCode mhlo_b200_shard_text(const char* mlir_text, int32_t shard_count, int32_t shard_index, const int32_t* input_axes,
+                                    int32_t num_input_axes, char** out_text, int32_t* out_input_axes, int32_t* out_output_axes) {
+    if (!mlir_text || !out_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    *out_text = nullptr;
+    try {
+        Module m = parse_module(mlir_text);
+        Function f = flatten_main(m);
+        const ShardPlan p = shard_function(f, make_spec(shard_count, shard_index, input_axes, num_input_axes));
+        *out_text = strdup(print_function(f).c_str());
+        if (out_input_axes) for (size_t i = 0; i < p.input_axes.size(); ++i) out_input_axes[i] = p.input_axes[i];
+        if (out_output_axes) for (size_t i = 0; i < p.output_axes.size(); ++i) out_output_axes[i] = p.output_axes[i];
         return MHLO_OK;
     } catch (const CompileError& e) {
         return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));

@@ -14,7 +14,21 @@
 
 namespace mhlo {
 
+// How a function is split over `count` equal, contiguous shards of its batch; this compilation builds shard `index`.
+struct ShardSpec {
+    int count = 1, index = 0;
+    std::vector<int> input_axes;  // per argument: the split axis, -1 = replicated. Empty = chosen by shard_function.
+};
+// What shard_function decided: the split axis of every argument and result (-1 = replicated, the same on every shard)
+// and their types before the split.
+struct ShardPlan {
+    int count = 1, index = 0;
+    std::vector<int> input_axes, output_axes;
+    std::vector<TensorType> full_input_types, full_output_types;
+};
+
 struct CompileOptions {
+    ShardSpec shard;             // count > 1: compile one shard of the batch (shard.cpp)
     int opt_level = 2;           // 0..3, same meaning as MHLOOptimizationLevel
     bool enable_caching = true;
     bool enable_debug_info = false;
@@ -55,6 +69,12 @@ bool flatten_top_k(Function& f);
 bool drop_optimization_barriers(Function& f);
 // All four, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
+
+// ---- batch sharding (shard.cpp) ----
+// Proves that every result of f is either the same on every shard or, slice by slice along one axis, a function of the
+// same slice of the split arguments, and rewrites f to compute shard spec.index of spec.count. Throws
+// CompileError(4, ...) naming the operator that mixes elements along the split axis when no such proof exists.
+ShardPlan shard_function(Function& f, const ShardSpec& spec);
 
 // ---- memory plan -----------------------------------------------------------------------------------------------
 
@@ -100,6 +120,7 @@ class Executable {
     int64_t constant_bytes() const { return static_cast<int64_t>(const_pool_.size()); }
     const std::vector<PassRecord>& pass_log() const { return pass_log_; }
     const std::string& optimized_text() const { return optimized_text_; }
+    const ShardPlan& shard_plan() const { return shard_plan_; }
     std::vector<std::string> step_labels() const;
     ExecutionStats stats;
 
@@ -126,6 +147,7 @@ class Executable {
     int launches_per_run_ = 0;
     std::vector<PassRecord> pass_log_;
     std::string optimized_text_;
+    ShardPlan shard_plan_;
     std::string error_;
 
     // CUDA-graph replay of the launch list. A (stream, input pointers, output pointers) combination that comes back

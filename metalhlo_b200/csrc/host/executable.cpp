@@ -1717,6 +1717,7 @@ std::unique_ptr<Executable> Executable::plan_only(const std::string& mlir, const
     Module m = parse_module(mlir);
     Function f = flatten_main(m);
     std::unique_ptr<Executable> exe(new Executable());
+    exe->shard_plan_ = shard_function(f, options.shard);
     exe->pass_log_ = run_pass_pipeline(f, options);
     optimize_loop_bodies(f, options);
     exe->optimized_text_ = print_function(f);
@@ -1730,6 +1731,7 @@ std::unique_ptr<Executable> Executable::compile(const std::string& mlir, const C
     Function f = flatten_main(m);
     if (std::getenv("METALHLO_DUMP_MLIR")) fprintf(stderr, "[metalhlo] parsed module:\n%s\n", print_function(f).c_str());
     std::unique_ptr<Executable> exe(new Executable());
+    exe->shard_plan_ = shard_function(f, options.shard);
     exe->pass_log_ = run_pass_pipeline(f, options);
     optimize_loop_bodies(f, options);
     exe->optimized_text_ = print_function(f);

@@ -79,8 +79,12 @@ static std::string dense_text(const Attr& a) {
         const uint8_t* p = a.dense.data() + k * es;
         if (is_float(t.dtype)) {
             double v = decode_as_double(t.dtype, p);
-            if (std::isnan(v)) return std::string("0x7FC00000");
-            if (std::isinf(v)) return std::string(v > 0 ? "0x7F800000" : "0xFF800000");
+            if (std::isnan(v) || std::isinf(v)) {  // the element's own bit pattern, in the width of its type
+                static const char* hex = "0123456789ABCDEF";
+                std::string s = "0x";
+                for (size_t b = es; b-- > 0;) { s += hex[p[b] >> 4]; s += hex[p[b] & 15]; }
+                return s;
+            }
             std::snprintf(buf, sizeof buf, "%.9g", v);
             std::string s = buf;
             if (s.find_first_of(".e") == std::string::npos) s += ".0";

@@ -1143,9 +1143,10 @@ class Interpreter:
     # -- structural ops
     def op_constant(self, op, a, t):
         v = op.attrs.get("value")
-        if v is not None:
-            return dense_value(v[1], t)
-        return dense_value(op.attrs["_dense"], t)
+        arr = dense_value(v[1], t) if v is not None else dense_value(op.attrs["_dense"], t)
+        # a constant holds values of its element type: the literal is rounded to it, as the reference serialises
+        # constants at their element type (Sources/MetalHLOCore/Compiler/MetalHLOCompiler.swift:487-613)
+        return round_to(arr, t.dtype) if t.is_float else arr
 
     def op_iota(self, op, a, t):
         d = int(op.attrs.get("dim", op.attrs.get("iota_dimension", 0)))
