@@ -39,6 +39,7 @@ def lib():
         i64, dbl, flt, cint = C.c_int64, C.c_double, C.c_float, C.c_int
         protos = {
             "oracle_max_threads": (cint, []),
+            "oracle_set_threads": (None, [cint]),
             "oracle_layer_norm": (None, [f32p, f32p, f32p, f64p, i64, i64, dbl]),
             "oracle_rms_norm": (None, [f32p, f32p, f64p, i64, i64, dbl]),
             "oracle_softmax": (None, [f32p, f64p, i64, i64, i64]),
@@ -61,6 +62,10 @@ def lib():
 
 def max_threads() -> int:
     return lib().oracle_max_threads()
+
+
+def set_threads(n: int) -> None:
+    lib().oracle_set_threads(int(n))
 
 
 def _f32(a):

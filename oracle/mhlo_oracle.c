@@ -29,6 +29,15 @@
 
 #define ORACLE_API __attribute__((visibility("default")))
 
+/* Sets the OpenMP team size for the kernels below (launchers such as torchrun export OMP_NUM_THREADS=1). */
+ORACLE_API void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORACLE_API int oracle_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
