@@ -405,6 +405,7 @@ def measure_gpt2(r: Ranks, args, peaks):
 
     os.environ["METALHLO_SHARD_COUNT"], os.environ["METALHLO_SHARD_INDEX"] = str(r.world), str(r.rank)
     os.environ["METALHLO_DEVICE"] = str(r.local)
+    os.environ["METALHLO_OPT_LEVEL"] = "O3"  # the plugin compiles at O2 unless told otherwise, like the reference's (PJRTExecutable.swift:1755-1766)
     host = pjrt.Host()
     pexe = host.compile(text)
     param_bufs = [host.buffer(a) for a in host_inputs[1:]]

@@ -485,6 +485,28 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
                    mhlo_cuda_stream_t stream);
 
 /*
+ * Launch knobs of the tensor-core GEMM (the CUDA counterpart of the tile fields of TuningConfig,
+ * Sources/MetalHLOCore/Tuning/AutoTuner.swift:31-103). 0 leaves a knob to the library's heuristic.
+ *   tile_n     columns of C per tile: 128 or 256 (rows are 128 per CTA)
+ *   stages     depth of the TMA operand ring, 2 .. the kernel's maximum (4 for 128x256 tiles, 6 otherwise)
+ *   cta_group  1: one CTA per 128-row tile; 2: a pair of CTAs on neighbouring SMs per 256 x 256 tile, each staging
+ *              its own rows of A and its own half of B (tcgen05 cta_group::2; no load is multicast)
+ * mhlo_cuda_gemm_tuned is mhlo_cuda_gemm with these knobs; tuning == NULL is mhlo_cuda_gemm. Problems outside the
+ * tensor-core path ignore the knobs.
+ */
+typedef struct {
+    int32_t tile_n;
+    int32_t stages;
+    int32_t cta_group;
+    int32_t reserved;
+} mhlo_cuda_gemm_tuning;
+
+int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                         const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
+                         int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
+                         const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream);
+
+/*
  * C = A . B for a B (and C) split by columns over n_ranks GPUs, with the all-gather of C fused into the epilogue:
  * this rank computes columns [rank * n_local, (rank + 1) * n_local) of the [m, n_local * n_ranks] row-major result
  * and every tile is stored, straight from the epilogue, into that column range of all n_ranks copies of C

@@ -18,6 +18,9 @@ struct GemmProblem {
     int64_t ldc = 0, c_col0 = 0;
     void* copies[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int32_t n_copies = 0;
+    // Launch knobs of the tensor-core kernel; 0 = chosen by the library. tile_n: 128 or 256 columns per tile; stages: depth
+    // of the TMA ring; cta_group: 1 = one CTA per 128-row tile, 2 = a pair of CTAs per 256-row tile.
+    int32_t tile_n = 0, stages = 0, cta_group = 0;
 };
 
 struct AttnShape {

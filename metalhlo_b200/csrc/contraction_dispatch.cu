@@ -166,6 +166,20 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
                    const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
                    int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
                    mhlo_cuda_stream_t stream) {
+    return mhlo_cuda_gemm_tuned(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_dev, batch0, batch1, m, n, k, bias_dev, epilogue,
+                                nullptr, stream);
+}
+
+int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                         const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
+                         int64_t m, int64_t n, int64_t k, const void* bias_dev, int32_t epilogue,
+                         const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream) {
+    if (tuning) {
+        if ((tuning->tile_n != 0 && tuning->tile_n != 128 && tuning->tile_n != 256) || tuning->stages < 0 || tuning->stages > 8 ||
+            tuning->stages == 1 || tuning->cta_group < 0 || tuning->cta_group > 2 || (tuning->cta_group == 2 && tuning->tile_n == 128))
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm: tuning {tile_n %d, stages %d, cta_group %d} is not a configuration of the kernel",
+                        tuning->tile_n, tuning->stages, tuning->cta_group);
+    }
     if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epilogue);
     if (!a_strides || !b_strides) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm: null strides");
@@ -174,6 +188,7 @@ int mhlo_cuda_gemm(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const
     for (int i = 0; i < 4; ++i) { p.as[i] = a_strides[i]; p.bs[i] = b_strides[i]; }
     p.batch0 = batch0; p.batch1 = batch1; p.m = m; p.n = n; p.k = k;
     p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
+    if (tuning) { p.tile_n = tuning->tile_n; p.stages = tuning->stages; p.cta_group = tuning->cta_group; }
     if (gemm_tc_supported(p)) return gemm_tc_launch(p, static_cast<cudaStream_t>(stream));
     int st = mhlo_cuda_dot_strided(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_dev, batch0, batch1, m, n, k, stream);
     if (st != MHLO_CUDA_OK || (bias_dev == nullptr && epilogue == MHLO_EPILOGUE_NONE)) return st;

@@ -73,12 +73,14 @@ struct GemmParams {
     void* copies[7];                 // further destinations of every tile store (the same matrix in peers' memory)
     int32_t n_copies;
     int32_t c_tma;                   // C has a tensor map: the epilogue stores its staged boxes with bulk tensor copies
+    int32_t stages;                  // depth of the TMA ring in use (<= the kernel's STAGES)
 };
 
-template <int BN, int STAGES>
+// CTAS = 2: a pair of CTAs shares one (2 * BM) x BN tile; each stages its own BM rows of A and BN / 2 rows of B.
+template <int BN, int STAGES, int CTAS = 1>
 struct SmemLayout {
     static constexpr int kABytes = BM * BK * 2;
-    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kBBytes = BN / CTAS * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 256;
     static constexpr int kStagingBytes = kEpilogueWarps * 4096;  // one 32-row x 128-byte tile per epilogue warp
@@ -101,11 +103,17 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
     *tn = static_cast<int>(t / rows_in_band);
 }
 
-template <int BN, int STAGES, int ACT>
+template <int BN, int STAGES, int ACT, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, CTAS>;
+    constexpr bool kPair = CTAS == 2;
+    constexpr int BNL = BN / CTAS;  // rows of B (columns of the tile) this CTA stages
+    const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    // the walker of output tiles is the CTA, or the pair: p.tiles_m counts (CTAS * BM)-row tiles
+    const int64_t walker = kPair ? blockIdx.x >> 1 : blockIdx.x, walkers = kPair ? gridDim.x >> 1 : gridDim.x;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarrierOff);
@@ -123,15 +131,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         prefetch_tmap(&map_b);
         if (p.c_tma) prefetch_tmap(&map_c);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps * CTAS); }
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, kTmemCols);
-        tmem_relinquish();
+        if constexpr (kPair) {  // one warp of each CTA of the pair: the columns are taken in both CTAs' TMEM
+            tmem_alloc_pair(tmem_slot, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) {  // both CTAs' barriers exist before either signals the other's
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // everything above touched only this CTA's shared memory and TMEM: it may overlap the previous kernel's tail
@@ -144,49 +161,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int64_t tile = walker; tile < p.num_tiles && ok; tile += walkers) {
                 int bz, tm, tn;
                 tile_coords(tile, p, &bz, &tm, &tn);
                 const int b0 = bz / static_cast<int>(p.batch1), b1 = bz % static_cast<int>(p.batch1);
+                const int row_a = (tm * CTAS + static_cast<int>(cta_rank)) * BM;    // first row of A this CTA stages
+                const int row_b = tn * BN + static_cast<int>(cta_rank) * BNL;       // first row of B (column of the tile)
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; atomicExch(&g_gemm_error, 1); break; }
+                    const bool freed = kPair ? mbar_wait_pair(&empty_bar[stage], phase ^ 1) : mbar_wait(&empty_bar[stage], phase ^ 1);
+                    if (!freed) { ok = false; atomicExch(&g_gemm_error, 1); break; }
                     uint8_t* sa = smem + stage * L::kStageBytes;
                     uint8_t* sb = sa + L::kABytes;
-                    mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+                    // Pair: the bytes of both CTAs are counted on the leader's barrier, which alone is armed (by the leader)
+                    uint32_t full_addr = 0;
+                    if constexpr (kPair) {
+                        full_addr = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                        if (leader) mbar_expect_tx(&full_bar[stage], CTAS * L::kStageBytes);
+                    } else {
+                        mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+                    }
+                    auto load = [&](uint8_t* dst, const CUtensorMap* map, int c0, int c1) {
+                        if constexpr (kPair) tma_load_4d_pair(dst, map, full_addr, c0, c1, b1, b0);
+                        else tma_load_4d(dst, map, &full_bar[stage], c0, c1, b1, b0);
+                    };
                     if (!p.a_mn_major) {
-                        tma_load_4d(sa, &map_a, &full_bar[stage], kb * BK, tm * BM, b1, b0);
+                        load(sa, &map_a, kb * BK, row_a);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j)
-                            tma_load_4d(sa + j * 64 * BK * 2, &map_a, &full_bar[stage], tm * BM + j * 64, kb * BK, b1, b0);
+                        for (int j = 0; j < BM / 64; ++j) load(sa + j * 64 * BK * 2, &map_a, row_a + j * 64, kb * BK);
                     }
                     if (!p.b_mn_major) {
-                        tma_load_4d(sb, &map_b, &full_bar[stage], kb * BK, tn * BN, b1, b0);
+                        load(sb, &map_b, kb * BK, row_b);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_4d(sb + j * 64 * BK * 2, &map_b, &full_bar[stage], tn * BN + j * 64, kb * BK, b1, b0);
+                        for (int j = 0; j < BNL / 64; ++j) load(sb + j * 64 * BK * 2, &map_b, row_b + j * 64, kb * BK);
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp runs the loop so that descriptors stay in uniform registers;
-        // one elected lane issues the tcgen05 instructions ----------------
-        {
+        // one elected lane issues the tcgen05 instructions. In a pair only the leader CTA issues: its MMAs write the
+        // accumulator halves in both CTAs' TMEM and its commits arrive on both CTAs' barriers ----------------
+        if (leader) {
             // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
             const uint32_t fmt = p.in_bf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) |
                                    (static_cast<uint32_t>(p.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                   (static_cast<uint32_t>(BM >> 4) << 24);
+                                   (static_cast<uint32_t>((BM * CTAS) >> 4) << 24);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { atomicExch(&g_gemm_error, 2); break; }
+            auto commit = [&](uint64_t* bar) {  // arrival on `bar` of this CTA and, in a pair, of the other CTA too
+                if constexpr (kPair) {
+                    umma_commit_pair(map_to_cta(smem_u32(bar), 0));
+                    umma_commit_pair(map_to_cta(smem_u32(bar), 1));
+                } else {
+                    umma_commit(bar);
+                }
+            };
+            for (int64_t tile = walker; tile < p.num_tiles && ok; tile += walkers) {
+                const bool drained = kPair ? mbar_wait_pair(&tmem_empty[acc], acc_phase ^ 1) : mbar_wait(&tmem_empty[acc], acc_phase ^ 1);
+                if (!drained) { atomicExch(&g_gemm_error, 2); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
@@ -203,13 +242,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                          : make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
                         const uint64_t db = p.b_mn_major ? make_smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
                                                          : make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
-                        if (elect_one()) umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (elect_one()) {
+                            if constexpr (kPair) umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                            else umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
-                    if (elect_one()) umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    if (elect_one()) commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
                     __syncwarp();
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
-                if (elect_one()) umma_commit(&tmem_full[acc]);  // accumulator complete
+                if (elect_one()) commit(&tmem_full[acc]);  // accumulator complete
                 __syncwarp();
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
@@ -221,15 +263,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int acc = 0;
         uint32_t acc_phase = 0;
         const size_t out_es = p.out_dtype == MHLO_DT_F32 ? 4 : 2;
-        for (int64_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        for (int64_t tile = walker; tile < p.num_tiles; tile += walkers) {
             int bz, tm, tn;
             tile_coords(tile, p, &bz, &tm, &tn);
-            if (!mbar_wait(&tmem_full[acc], acc_phase)) { atomicExch(&g_gemm_error, 4); break; }
+            const bool filled = kPair ? mbar_wait_pair(&tmem_full[acc], acc_phase) : mbar_wait(&tmem_full[acc], acc_phase);
+            if (!filled) { atomicExch(&g_gemm_error, 4); break; }
             tc_fence_after();
             // Each warp turns its 32 rows x (BN/2) columns into output in chunks of 128 bytes per row: the thread that owns
             // a row (TMEM lane) writes its 128 bytes into a swizzled shared-memory tile, then the warp reads the tile back
             // row-wise so that every global store instruction covers whole rows (coalesced), whatever the row pitch of C.
-            const int64_t row0 = static_cast<int64_t>(tm) * BM + quarter * 32;
+            const int64_t row0 = (static_cast<int64_t>(tm) * CTAS + cta_rank) * BM + quarter * 32;
             const int chunk_cols = p.out_dtype == MHLO_DT_F32 ? 32 : 64;
             uint8_t* stage_tile = smem + L::kStagingOff + (warp - 2) * 4096;
             const int64_t batch_off = static_cast<int64_t>(bz) * p.m * p.ldc * out_es;
@@ -404,7 +447,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            if (lane == 0) {  // the accumulator buffer goes back to the MMA issuer (the leader's, in a pair)
+                if (leader) mbar_arrive(&tmem_empty[acc]);
+                else mbar_arrive_remote(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+            }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         if (p.c_tma && lane == 0) tma_store_wait_all();  // shared memory stays allocated until the last box has been read
@@ -412,9 +458,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) {  // neither CTA leaves, or gives up its TMEM, while the other may still address it
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -523,9 +574,9 @@ bool gemm_tc_supported(const GemmProblem& p) {
     return true;
 }
 
-template <int BN, int STAGES, int ACT>
+template <int BN, int STAGES, int ACT, int CTAS>
 static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, CTAS>;
     const bool a_k = pr.as[3] == 1 || pr.k == 1;
     const bool b_k = pr.bs[2] == 1 || pr.k == 1;  // K-major B = [n][k] with k contiguous
     CUtensorMap map_a, map_b;
@@ -534,7 +585,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     if (a_k) ok = operand_map(&map_a, pr.a, pr.k, pr.m, pr.as[2], pr.batch1, pr.as[1], pr.batch0, pr.as[0], BK, BM, &why);
     else ok = operand_map(&map_a, pr.a, pr.m, pr.k, pr.as[3], pr.batch1, pr.as[1], pr.batch0, pr.as[0], 64, BK, &why);
     if (!ok) return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for A: %s", why.c_str());
-    if (b_k) ok = operand_map(&map_b, pr.b, pr.k, pr.n, pr.bs[3], pr.batch1, pr.bs[1], pr.batch0, pr.bs[0], BK, BN, &why);
+    if (b_k) ok = operand_map(&map_b, pr.b, pr.k, pr.n, pr.bs[3], pr.batch1, pr.bs[1], pr.batch0, pr.bs[0], BK, BN / CTAS, &why);
     else ok = operand_map(&map_b, pr.b, pr.n, pr.k, pr.bs[2], pr.batch1, pr.bs[1], pr.batch0, pr.bs[0], 64, BK, &why);
     if (!ok) return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for B: %s", why.c_str());
 
@@ -543,7 +594,8 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     p.bias = pr.bias;
     p.m = pr.m; p.n = pr.n; p.k = pr.k;
     p.batch0 = pr.batch0; p.batch1 = pr.batch1;
-    p.tiles_m = static_cast<int>((pr.m + BM - 1) / BM);
+    p.tiles_m = static_cast<int>((pr.m + BM * CTAS - 1) / (BM * CTAS));
+    p.stages = pr.stages >= 2 && pr.stages <= STAGES ? pr.stages : STAGES;
     p.tiles_n = static_cast<int>((pr.n + BN - 1) / BN);
     p.num_tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n * pr.batch0 * pr.batch1;
     p.a_mn_major = a_k ? 0 : 1;
@@ -575,7 +627,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         p.c_tma = 1;
     }
 
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT, CTAS>;
     // the attribute belongs to the (kernel, device) pair: one flag per device ordinal
     static std::atomic<bool> attr_set[64];
     int attr_dev = 0;
@@ -584,23 +636,46 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
         if (attr_dev >= 0 && attr_dev < 64) attr_set[attr_dev].store(true, std::memory_order_release);
     }
-    const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
-    const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, map_a, map_b, map_c, p);
+    int walkers = kNumSMs;
+    if (CTAS == 2) {
+        // pairs that can be resident at once (a pair sits inside one GPC; not every SM need have a partner free)
+        static std::atomic<int> resident_pairs[64];
+        int pairs = attr_dev >= 0 && attr_dev < 64 ? resident_pairs[attr_dev].load(std::memory_order_acquire) : 0;
+        if (pairs == 0) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3(kNumSMs);
+            q.blockDim = dim3(kGemmThreads);
+            q.dynamicSmemBytes = L::kTotal;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            q.attrs = qa;
+            q.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&pairs, kernel, &q) != cudaSuccess || pairs < 1) { cudaGetLastError(); pairs = kNumSMs / 2; }
+            pairs = std::min(pairs, kNumSMs / 2);
+            if (attr_dev >= 0 && attr_dev < 64) resident_pairs[attr_dev].store(pairs, std::memory_order_release);
+        }
+        walkers = pairs;
+    }
+    const int grid = CTAS * static_cast<int>(std::min<int64_t>(p.num_tiles, walkers));
+    const cudaError_t launched = launch_dependent_cluster(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, CTAS, map_a, map_b, map_c, p);
     if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of gemm_tcgen05 failed: %s", cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CTAS = 1>
 static int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
     switch (p.epilogue) {
-        case MHLO_EPILOGUE_RELU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_RELU>(p, stream);
-        case MHLO_EPILOGUE_GELU_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_TANH>(p, stream);
-        case MHLO_EPILOGUE_GELU_ERF: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_ERF>(p, stream);
-        case MHLO_EPILOGUE_SILU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SILU>(p, stream);
-        case MHLO_EPILOGUE_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_TANH>(p, stream);
-        case MHLO_EPILOGUE_SIGMOID: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SIGMOID>(p, stream);
-        default: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE>(p, stream);
+        case MHLO_EPILOGUE_RELU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_RELU, CTAS>(p, stream);
+        case MHLO_EPILOGUE_GELU_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_TANH, CTAS>(p, stream);
+        case MHLO_EPILOGUE_GELU_ERF: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_ERF, CTAS>(p, stream);
+        case MHLO_EPILOGUE_SILU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SILU, CTAS>(p, stream);
+        case MHLO_EPILOGUE_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_TANH, CTAS>(p, stream);
+        case MHLO_EPILOGUE_SIGMOID: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SIGMOID, CTAS>(p, stream);
+        default: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE, CTAS>(p, stream);
     }
 }
 
@@ -608,6 +683,16 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     // 128 x 256 tiles run the tensor pipe at its full rate; a 128 x 128 tile takes about 0.6 of the time of a wide one
     // (measured: 0.33 us against 0.27 us per 64-deep step at half the work), so narrow tiles only pay when they save
     // whole waves over the SMs.
+    // explicit knobs first (the tuner's records and the tests): 0 leaves a knob to the heuristic below
+    static const int pair_env = [] {
+        const char* v = getenv("METALHLO_GEMM_PAIR");  // 0 = never a CTA pair, 1 = a pair wherever the tile allows
+        return v && (v[0] == '0' || v[0] == '1') ? v[0] - '0' : -1;
+    }();
+    int cta_group = p.cta_group;
+    if (cta_group == 0 && pair_env >= 0 && p.n_copies == 0) cta_group = pair_env + 1;
+    if (cta_group == 2 && p.n_copies == 0) return launch_gemm<256, 6, 2>(p, stream);
+    if (p.tile_n == 256) return launch_gemm<256, 4>(p, stream);
+    if (p.tile_n == 128) return launch_gemm<128, 6>(p, stream);
     if (p.n <= 128) return launch_gemm<128, 6>(p, stream);
     const int64_t rows = (p.m + BM - 1) / BM * p.batch0 * p.batch1;
     const int64_t tiles_256 = rows * ((p.n + 255) / 256), tiles_128 = rows * ((p.n + 127) / 128);

@@ -135,6 +135,8 @@ _PROTOTYPES = {
     "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                  _i32, _vp]),
+    "mhlo_cuda_gemm_tuned": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
+                                       _i32, _vp, _vp]),
     "mhlo_cuda_device_error": (C.c_int, [C.POINTER(_i32)]),
     "mhlo_cuda_device_error_fetch": (C.c_int, [_vp]),
     "mhlo_cuda_device_error_take": (C.c_int, [C.POINTER(_i32)]),
@@ -255,8 +257,12 @@ def _i64s(vals):
     return (C.c_int64 * len(vals))(*[int(v) for v in vals])
 
 
+class GemmTuning(C.Structure):
+    _fields_ = [("tile_n", C.c_int32), ("stages", C.c_int32), ("cta_group", C.c_int32), ("reserved", C.c_int32)]
+
+
 def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool = False, trans_b: bool = False,
-         out=None, stream=None):
+         out=None, stream=None, tuning=None):
     """C[..., M, N] = act(A . B + bias) through ``mhlo_cuda_gemm``.
 
     a: [batch..., M, K] (or [batch..., K, M] with trans_a), b: [batch..., K, N] (or [batch..., N, K] with trans_b);
@@ -276,6 +282,11 @@ def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool 
     out_dtype = a.dtype if out_dtype is None else out_dtype
     if out is None:
         out = torch.empty(batch + [m, n], dtype=out_dtype, device=a.device)
+    if tuning is not None:  # (tile_n, stages, cta_group): mhlo_cuda_gemm_tuned
+        t = GemmTuning(*tuning, 0)
+        check(lib.mhlo_cuda_gemm_tuned(torch_dtype_code(a.dtype), torch_dtype_code(out_dtype), _ptr(a), _i64s(a_str), _ptr(b), _i64s(b_str),
+                                       _ptr(out), b0, b1, m, n, k, _ptr(bias), EPILOGUES[epilogue], C.addressof(t), _stream(stream)))
+        return out
     check(lib.mhlo_cuda_gemm(torch_dtype_code(a.dtype), torch_dtype_code(out_dtype), _ptr(a), _i64s(a_str), _ptr(b),
                              _i64s(b_str), _ptr(out), b0, b1, m, n, k, _ptr(bias), EPILOGUES[epilogue], _stream(stream)))
     return out
