@@ -135,7 +135,9 @@ __device__ __forceinline__ float softmax_exp(uint32_t s_taddr, float scale_log2,
 // One unit of work: 256 query rows of one (batch, head).
 struct Tile {
     int bat, head, m0;
-    int nblk;  // key blocks this tile visits (0: no key is visible to any of its rows)
+    int nblk;   // key blocks this tile visits (0: no key is visible to any of its rows)
+    int nblk0;  // key blocks its first half (rows m0 .. m0 + 127) takes part in: under a causal mask the tile's last block
+                // lies wholly right of that half's diagonal, and the half skips it
 };
 
 // The tiles of one CTA. Tiles are numbered g = (batch*heads + head) * n_m + s, where position s inside a (batch, head)
@@ -177,6 +179,7 @@ struct TileWalk {
         int kv_len = p.seq_k;  // keys this tile visits: all, or up to the last key its last query row may see
         if (p.causal) kv_len = min(p.seq_k, min(t->m0 + kHalves * kBlockM, p.seq_q));  // key j is visible to query i iff j <= i
         t->nblk = (kv_len + kBlockN - 1) / kBlockN;
+        t->nblk0 = p.causal ? min(t->nblk, t->m0 / kBlockN + 1) : t->nblk;
         return true;
     }
     // Next tile that has at least one key block (the producer and the MMA issuer skip the others).
@@ -302,7 +305,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         Tile cur, nxt;
         bool has_cur = walk.next_nonempty(p, &cur);
         int stage = 0;
-        uint32_t phase = 0, it = 0, qn = 0;  // it: key blocks so far (parity of the per-block barriers); qn: tiles so far
+        uint32_t phase = 0, qn = 0;   // qn: tiles so far
+        uint32_t it_h[kHalves] = {0, 0};  // key blocks each half has gone through (parity of its per-block barriers)
         bool ok = true;
         if (has_cur) {
             // first scores of the first tile
@@ -311,7 +315,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (ok) {
                 tc_fence_after();
                 issue_s(0, 0);
-                if (cur.nblk == 1) commit_to(&q_empty[0]);
+                if (cur.nblk0 == 1) commit_to(&q_empty[0]);
                 issue_s(1, 0);
                 if (cur.nblk == 1) commit_to(&q_empty[1]);
                 commit_to(&k_empty[0]);
@@ -322,24 +326,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // the S/P columns only after PV_h(j) has read the probabilities from them.
         while (has_cur && ok) {
             const bool has_nxt = walk.next_nonempty(p, &nxt);
-            for (int j = 0; j < cur.nblk && ok; ++j, ++it) {
+            for (int j = 0; j < cur.nblk && ok; ++j) {
                 const int nstage = stage + 1 == kKvStages ? 0 : stage + 1;
                 const uint32_t nphase = stage + 1 == kKvStages ? phase ^ 1 : phase;
                 const bool last = j + 1 == cur.nblk;
                 const bool more = !last || has_nxt;
-                const bool closes_q = more && (last ? nxt.nblk == 1 : j + 2 == cur.nblk);  // the S issued now is its tile's last
+                if (!mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
                 for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!mbar_wait(&p_full[h], it & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
-                    if (h == 0 && !mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
-                    tc_fence_after();
-                    issue_pv(h, stage, j > 0);
+                    const int nb = h == 0 ? cur.nblk0 : cur.nblk;  // blocks this half takes part in
+                    if (j < nb) {
+                        if (!mbar_wait(&p_full[h], it_h[h] & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                        tc_fence_after();
+                        issue_pv(h, stage, j > 0);
+                        ++it_h[h];
+                    }
                     if (h == kHalves - 1) commit_to(&v_empty[stage]);
                     if (more) {
                         if (last && !mbar_wait(&q_full[h], (qn + 1) & 1)) { ok = false; atomicExch(&g_attn_error, 12); break; }
                         if (h == 0 && !mbar_wait(&k_full[nstage], nphase)) { ok = false; atomicExch(&g_attn_error, 6); break; }
-                        tc_fence_after();
-                        issue_s(h, nstage);
-                        if (closes_q) commit_to(&q_empty[h]);
+                        // the next scores of this half: block j + 1 of this tile when the half takes part in it, block 0 of
+                        // the next tile after this tile's last block
+                        if (last || j + 1 < nb) {
+                            tc_fence_after();
+                            issue_s(h, nstage);
+                            const int nb_of_s = last ? (h == 0 ? nxt.nblk0 : nxt.nblk) : nb;
+                            if (last ? nb_of_s == 1 : j + 2 == nb_of_s) commit_to(&q_empty[h]);  // that was the tile's last S of this half
+                        }
                         if (h == kHalves - 1) commit_to(&k_empty[nstage]);
                     }
                 }
@@ -365,7 +377,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int qi = t.m0 + h * kBlockM + r;  // query index
             const int last_visible = p.causal ? min(p.seq_k - 1, qi) : p.seq_k - 1;
             float m_ref = -INFINITY, l = 0.f;
-            for (int j = 0; j < t.nblk && ok; ++j, ++it) {
+            const int nb = h == 0 ? t.nblk0 : t.nblk;  // under a causal mask the first half has nothing to see in the last block
+            for (int j = 0; j < nb && ok; ++j, ++it) {
                 if (!mbar_wait(&s_full[h], it & 1)) { ok = false; atomicExch(&g_attn_error, 8); break; }
                 tc_fence_after();
                 const int key0 = j * kBlockN;
