@@ -697,7 +697,9 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     // A pair of CTAs per 256 x 256 tile halves the shared-memory traffic of B per SM and measured 5-10 % faster than one
     // CTA per 128 x 256 tile wherever there are enough tiles to occupy the 74 pairs (8192^3: 1481 against 1314 TFLOP/s,
     // [32768,768].[768,3072]: 1124 against 1032); below that the narrower one-CTA tiles spread better over the SMs.
-    if (cta_group == 0 && p.n_copies == 0 && p.m > BM) {
+    // Products with a short K are bound by their epilogue and by HBM (the batched [2048,128].[128,2048] product ran at
+    // 3.5 TB/s in pairs against 4.9 TB/s alone): a pair has to wait for both CTAs' epilogues before it reuses an accumulator.
+    if (cta_group == 0 && p.n_copies == 0 && p.m > BM && p.k >= 8 * BK) {
         const int64_t pair_tiles = (p.m + 2 * BM - 1) / (2 * BM) * ((p.n + 255) / 256) * p.batch0 * p.batch1;
         if (pair_tiles >= 60) return launch_gemm<256, 6, 2>(p, stream);
     }
