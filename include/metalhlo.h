@@ -212,6 +212,19 @@ int64_t mhlo_b200_tuning_count(void);
  * max_trials <= 0: all candidates. *out_record_json (optional) receives the stored record; free with mhlo_free_string. */
 MHLOStatusCode mhlo_b200_tuning_tune_row_kernel(MHLOClientRef client, const char* kernel, MHLOElementType element_type,
                                                 int64_t rows, int64_t hidden, int32_t max_trials, char** out_record_json);
+/* The same for the tensor-core GEMM, over {tile width 128 | 256, TMA ring depth, one CTA per tile | a pair of CTAs per
+ * 256 x 256 tile} (the tile knobs of Sources/MetalHLOCore/Tuning/AutoTuner.swift:31-103 on this hardware), for
+ * [batch, m, k] . [batch, k, n] of bf16 / f16 operands; a_transposed / b_transposed: the operand is stored with its
+ * other dimension contiguous. The record is stored under the key the compiler looks up when it lowers the same
+ * dot_general or fused_matmul_bias_activation; executables compiled afterwards launch the stored configuration. */
+MHLOStatusCode mhlo_b200_tuning_tune_gemm(MHLOClientRef client, MHLOElementType element_type, MHLOElementType out_element_type,
+                                          int64_t batch, int64_t m, int64_t n, int64_t k, bool a_transposed, bool b_transposed,
+                                          int32_t max_trials, char** out_record_json);
+/* The same for the tensor-core attention kernel (head_dim 64 or 128, bf16 / f16) over its tile orders
+ * (AutoTuner.swift:81-103: the attention block options). bshd: tensors laid out [batch, sequence, heads, head_dim]. */
+MHLOStatusCode mhlo_b200_tuning_tune_attention(MHLOClientRef client, MHLOElementType element_type, int64_t batch, int64_t heads,
+                                               int64_t seq_q, int64_t seq_k, int64_t head_dim, bool causal, bool bshd,
+                                               int32_t max_trials, char** out_record_json);
 /* Merges records given as a database document (the file format: {"version": 1, "entries": [key, result, ...]});
  * existing keys win unless overwrite. Host-only. *out_taken (optional) = entries taken. */
 MHLOStatusCode mhlo_b200_tuning_merge_json(const char* database_json, bool overwrite, int32_t* out_taken);

@@ -567,6 +567,26 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
                         int32_t causal, mhlo_cuda_stream_t stream);
 
+/*
+ * Launch knobs of the tensor-core attention kernel (the attention block options of the reference's tuner,
+ * Sources/MetalHLOCore/Tuning/AutoTuner.swift:81-103). 0 leaves a knob to the library.
+ *   tile_order  order in which the persistent CTAs take the 256-query-row tiles: 1 = long and short tiles of one
+ *               (batch, head) in pairs, neighbouring CTAs on neighbouring heads (K and V are read from HBM once);
+ *               2 = longest tiles first, dealt to the CTAs forwards and backwards (balances a causal mask best, costs
+ *               re-reads when K and V of all heads do not fit L2)
+ * mhlo_cuda_attention_tuned is mhlo_cuda_attention with these knobs; tuning == NULL is mhlo_cuda_attention.
+ */
+typedef struct {
+    int32_t tile_order;
+    int32_t reserved[3];
+} mhlo_cuda_attention_tuning;
+
+int mhlo_cuda_attention_tuned(int32_t dtype, const void* q_dev, const int64_t q_strides[3], const void* k_dev,
+                              const int64_t k_strides[3], const void* v_dev, const int64_t v_strides[3],
+                              const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,
+                              int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
+                              int32_t causal, const mhlo_cuda_attention_tuning* tuning, mhlo_cuda_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -118,6 +118,8 @@ _PROTOTYPES = {
     "mhlo_b200_tuning_open": (C.c_int, [C.c_char_p]),
     "mhlo_b200_tuning_count": (_i64, []),
     "mhlo_b200_tuning_tune_row_kernel": (C.c_int, [_vp, C.c_char_p, C.c_int, _i64, _i64, _i32, _P(_vp)]),
+    "mhlo_b200_tuning_tune_gemm": (C.c_int, [_vp, C.c_int, C.c_int, _i64, _i64, _i64, _i64, C.c_bool, C.c_bool, _i32, _P(_vp)]),
+    "mhlo_b200_tuning_tune_attention": (C.c_int, [_vp, C.c_int, _i64, _i64, _i64, _i64, _i64, C.c_bool, C.c_bool, _i32, _P(_vp)]),
     "mhlo_b200_tuning_merge_json": (C.c_int, [C.c_char_p, C.c_bool, _P(_i32)]),
     "mhlo_b200_tuning_to_json": (_vp, []),
     "mhlo_b200_tuning_save": (C.c_int, []),
@@ -229,6 +231,27 @@ class tuning:
         out = _vp()
         _check(lib.mhlo_b200_tuning_tune_row_kernel(client._h, kernel.encode(), element_type, rows, hidden, max_trials, C.byref(out)))
         return json.loads(_take_string(out.value))
+
+
+def _tune_gemm(client, element_type, batch, m, n, k, out_element_type=None, a_transposed=False, b_transposed=False, max_trials=0) -> dict:
+    import json
+
+    out = _vp()
+    _check(lib.mhlo_b200_tuning_tune_gemm(client._h, element_type, element_type if out_element_type is None else out_element_type, batch, m, n, k,
+                                          a_transposed, b_transposed, max_trials, C.byref(out)))
+    return json.loads(_take_string(out.value))
+
+
+def _tune_attention(client, element_type, batch, heads, seq_q, seq_k, head_dim, causal=False, bshd=False, max_trials=0) -> dict:
+    import json
+
+    out = _vp()
+    _check(lib.mhlo_b200_tuning_tune_attention(client._h, element_type, batch, heads, seq_q, seq_k, head_dim, causal, bshd, max_trials, C.byref(out)))
+    return json.loads(_take_string(out.value))
+
+
+tuning.tune_gemm = staticmethod(_tune_gemm)
+tuning.tune_attention = staticmethod(_tune_attention)
 
 
 class Buffer:

@@ -573,6 +573,8 @@ int launch_attention(int dtype, const void* q, const void* k, const void* v, voi
     const bool fits = by_length_mode == 2 || kv_bytes <= l2_bytes / 100 * 85;
     // without a mask all tiles are equally long; dealing them one by one still evens out the last pass
     p.by_length = (by_length_mode != 0 && fits && tiles < (int64_t{1} << 30)) ? 1 : 0;
+    if (s.tile_order == 1) p.by_length = 0;
+    else if (s.tile_order == 2 && tiles < (int64_t{1} << 30)) p.by_length = 1;
     const unsigned grid = static_cast<unsigned>(p.by_length ? std::min<int64_t>(tiles, sm_count) : std::min<int64_t>((tiles + 1) / 2, sm_count));
     const cudaError_t launched = launch_dependent(kernel, dim3(grid), dim3(kAttnThreads), L::kTotal, stream, mq, mk, mv, p);
     if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of attention_tcgen05 failed: %s", cudaGetErrorString(launched));

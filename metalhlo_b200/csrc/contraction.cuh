@@ -28,6 +28,7 @@ struct AttnShape {
     int64_t batch, heads, seq_q, seq_k, head_dim;
     float scale;
     int32_t causal;
+    int32_t tile_order = 0;  // tensor-core kernel: 0 = chosen by the library, 1 = long/short pairs per (batch, head), 2 = longest tiles first
 };
 
 // Tensor-core (tcgen05 + TMA + TMEM) paths; *_supported() says whether the problem meets their layout rules.

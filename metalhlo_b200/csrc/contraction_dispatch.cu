@@ -242,6 +242,17 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,
                         int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
                         int32_t causal, mhlo_cuda_stream_t stream) {
+    return mhlo_cuda_attention_tuned(dtype, q_dev, q_strides, k_dev, k_strides, v_dev, v_strides, mask_dev, o_dev, o_strides, batch, heads, seq_q,
+                                     seq_k, head_dim, scale, causal, nullptr, stream);
+}
+
+int mhlo_cuda_attention_tuned(int32_t dtype, const void* q_dev, const int64_t q_strides[3], const void* k_dev,
+                              const int64_t k_strides[3], const void* v_dev, const int64_t v_strides[3],
+                              const void* mask_dev, void* o_dev, const int64_t o_strides[3], int64_t batch,
+                              int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
+                              int32_t causal, const mhlo_cuda_attention_tuning* tuning, mhlo_cuda_stream_t stream) {
+    if (tuning && (tuning->tile_order < 0 || tuning->tile_order > 2))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: tuning {tile_order %d} is not a configuration of the kernel", tuning->tile_order);
     if (batch < 0 || heads < 0 || seq_q < 0 || seq_k < 0 || head_dim < 0)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: negative extent");
     if (!q_strides || !k_strides || !v_strides || !o_strides) return fail(MHLO_CUDA_INVALID_ARGUMENT, "attention: null strides");
@@ -250,6 +261,7 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
     AttnShape s;
     for (int i = 0; i < 3; ++i) { s.qs[i] = q_strides[i]; s.ks[i] = k_strides[i]; s.vs[i] = v_strides[i]; s.os[i] = o_strides[i]; }
     s.batch = batch; s.heads = heads; s.seq_q = seq_q; s.seq_k = seq_k; s.head_dim = head_dim; s.scale = scale; s.causal = causal;
+    if (tuning) s.tile_order = tuning->tile_order;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (attention_tc_supported(dtype, s, mask_dev) && aligned16(q_dev) && aligned16(k_dev) && aligned16(v_dev) && aligned16(o_dev))
         return attention_tc_launch(dtype, q_dev, k_dev, v_dev, o_dev, s, st);

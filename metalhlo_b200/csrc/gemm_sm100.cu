@@ -297,13 +297,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int c0 = col_begin; c0 < col_end; c0 += chunk_cols) {
                 const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
                 uint4 out16[8];
+                // the chunk's accumulator columns in one go (both 32-column loads are in flight before the one wait)
+                uint32_t racc[64];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0);
+                tmem_ld32(taddr, racc);
+                if (chunk_cols > 32) tmem_ld32(taddr + 32, racc + 32);
+                tmem_ld_wait();
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     if (half * 32 >= chunk_cols) break;
-                    uint32_t r[32];
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0 + half * 32);
-                    tmem_ld32(taddr, r);
-                    tmem_ld_wait();
+                    const uint32_t* r = racc + half * 32;
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);

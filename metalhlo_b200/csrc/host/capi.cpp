@@ -678,6 +678,65 @@ MHLOStatusCode mhlo_b200_tuning_tune_row_kernel(MHLOClientRef client, const char
     return MHLO_OK;
 }
 
+namespace {
+char* record_json(const TuningRecord& rec) {
+    char buf[640];
+    snprintf(buf, sizeof buf,
+             "{\"bestConfig\": {\"tileM\": %d, \"tileN\": %d, \"tileK\": %d, \"stages\": %d, \"ctaGroup\": %d, \"tileOrder\": %d}, "
+             "\"measuredTime\": %.9g, \"gflops\": %.6g, \"gbytesPerSecond\": %.6g, \"configsTried\": %d}",
+             rec.best.tile_m, rec.best.tile_n, rec.best.tile_k, rec.best.stages, rec.best.cta_group, rec.best.tile_order, rec.measured_time_s,
+             rec.gflops, rec.gbytes_per_s, rec.configs_tried);
+    return strdup(buf);
+}
+}  // namespace
+
+// Times every configuration of the tensor-core GEMM on [batch, m, k] . [batch, k, n] (operands of element_type, result of
+// out_element_type; a_transposed / b_transposed: the operand is stored with the other dimension contiguous) and stores the
+// best in the open database under the key the compiler looks up for the same dot_general.
+MHLOStatusCode mhlo_b200_tuning_tune_gemm(MHLOClientRef client, MHLOElementType element_type, MHLOElementType out_element_type, int64_t batch,
+                                          int64_t m, int64_t n, int64_t k, bool a_transposed, bool b_transposed, int32_t max_trials,
+                                          char** out_record_json) {
+    if (out_record_json) *out_record_json = nullptr;
+    Client* c = static_cast<Client*>(client);
+    if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null client"));
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open"));
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    GemmCase gc;
+    gc.dtype = static_cast<int>(element_type); gc.out_dtype = static_cast<int>(out_element_type);
+    gc.batch = batch; gc.m = m; gc.n = n; gc.k = k;
+    gc.a_k_major = !a_transposed; gc.b_k_major = b_transposed;
+    TuningRecord rec;
+    std::string why;
+    const int st = tune_gemm(gc, max_trials, db, &rec, &why);
+    if (st == MHLO_CUDA_INVALID_ARGUMENT) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, why));
+    if (st != MHLO_CUDA_OK) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_EXECUTION_FAILED, why));
+    if (out_record_json) *out_record_json = record_json(rec);
+    return MHLO_OK;
+}
+
+// The same for the tensor-core attention kernel on Q [batch, heads, seq_q, head_dim], K / V [batch, heads, seq_k, head_dim]
+// (bshd: the tensors are laid out [batch, sequence, heads, head_dim]).
+MHLOStatusCode mhlo_b200_tuning_tune_attention(MHLOClientRef client, MHLOElementType element_type, int64_t batch, int64_t heads, int64_t seq_q,
+                                               int64_t seq_k, int64_t head_dim, bool causal, bool bshd, int32_t max_trials, char** out_record_json) {
+    if (out_record_json) *out_record_json = nullptr;
+    Client* c = static_cast<Client*>(client);
+    if (!c) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null client"));
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "no tuning database is open"));
+    if (mhlo_cuda_device_set(c->device) != 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, mhlo_cuda_last_error()));
+    AttentionCase ac;
+    ac.dtype = static_cast<int>(element_type);
+    ac.batch = batch; ac.heads = heads; ac.seq_q = seq_q; ac.seq_k = seq_k; ac.head_dim = head_dim; ac.causal = causal; ac.bshd = bshd;
+    TuningRecord rec;
+    std::string why;
+    const int st = tune_attention(ac, max_trials, db, &rec, &why);
+    if (st == MHLO_CUDA_INVALID_ARGUMENT) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, why));
+    if (st != MHLO_CUDA_OK) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_EXECUTION_FAILED, why));
+    if (out_record_json) *out_record_json = record_json(rec);
+    return MHLO_OK;
+}
+
 MHLOStatusCode mhlo_b200_tuning_merge_json(const char* database_json, bool overwrite, int32_t* out_taken) {
     if (out_taken) *out_taken = 0;
     TuningDatabase* db = TuningDatabase::global();

@@ -222,6 +222,28 @@ bool lookup_row_tuning(const std::string& kind, int64_t rows, int64_t hidden, DT
     return true;
 }
 
+// The same for the tensor-core GEMM and attention kernels: a stored record whose configuration is not the library's own
+// choice becomes the launch's tuning argument.
+bool lookup_gemm_tuning(const GemmCase& c, mhlo_cuda_gemm_tuning* out) {
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db || (c.dtype != MHLO_DT_BF16 && c.dtype != MHLO_DT_F16)) return false;
+    static const std::string device_name = current_device_name();
+    TuningRecord rec;
+    if (!db->get(c.key(device_name), &rec) || rec.best.is_default()) return false;
+    *out = mhlo_cuda_gemm_tuning{rec.best.tile_n, rec.best.stages, rec.best.cta_group, 0};
+    return true;
+}
+
+bool lookup_attention_tuning(const AttentionCase& c, mhlo_cuda_attention_tuning* out) {
+    TuningDatabase* db = TuningDatabase::global();
+    if (!db) return false;
+    static const std::string device_name = current_device_name();
+    TuningRecord rec;
+    if (!db->get(c.key(device_name), &rec) || rec.best.is_default()) return false;
+    *out = mhlo_cuda_attention_tuning{rec.best.tile_order, {0, 0, 0}};
+    return true;
+}
+
 class Lowering {
   public:
     Lowering(const Function& f, Executable* exe) : f_(f), exe_(exe), views_(f.values.size()), have_(f.values.size(), false) {}
@@ -859,10 +881,15 @@ class Lowering {
                 keep_alive(a); keep_alive(b); keep_alive(out);
                 const int in_dt = static_cast<int>(a.type.dtype), out_dt = static_cast<int>(rt.dtype);
                 std::array<int64_t, 4> asv = {as[0], as[1], as[2], as[3]}, bsv = {bs[0], bs[1], bs[2], bs[3]};
-                add_step("dot_general", [=](const Ctx& c) {
-                    return mhlo_cuda_gemm(in_dt, out_dt, bind(da, c).base, asv.data(), bind(db, c).base, bsv.data(),
-                                          const_cast<void*>(bind(dc, c).base), b0, b1, M, N, K, nullptr, MHLO_EPILOGUE_NONE,
-                                          c.stream);
+                GemmCase gc;
+                gc.dtype = in_dt; gc.out_dtype = out_dt; gc.batch = b0 * b1; gc.m = M; gc.n = N; gc.k = K;
+                gc.a_k_major = as[3] == 1 || K == 1; gc.b_k_major = bs[2] == 1 || K == 1;
+                mhlo_cuda_gemm_tuning gt{0, 0, 0, 0};
+                const bool tuned = lookup_gemm_tuning(gc, &gt);
+                add_step(tuned ? "dot_general [tuned]" : "dot_general", [=](const Ctx& c) {
+                    return mhlo_cuda_gemm_tuned(in_dt, out_dt, bind(da, c).base, asv.data(), bind(db, c).base, bsv.data(),
+                                                const_cast<void*>(bind(dc, c).base), b0, b1, M, N, K, nullptr, MHLO_EPILOGUE_NONE,
+                                                tuned ? &gt : nullptr, c.stream);
                 });
                 return set(op.results[0], out);
             }
@@ -1608,10 +1635,15 @@ void Lowering::lower_custom_call(const Op& op) {
         if (has_bias) { dbias = dev(bias); keep_alive(bias); }
         const int in_dt = static_cast<int>(x.type.dtype), out_dt = static_cast<int>(rt.dtype);
         std::array<int64_t, 4> as = {0, 0, K, 1}, bs = {0, 0, w.strides[0], w.strides[1]};
-        add_step(target, [=](const Ctx& c) {
-            return mhlo_cuda_gemm(in_dt, out_dt, bind(dx, c).base, as.data(), bind(dw, c).base, bs.data(),
-                                  const_cast<void*>(bind(dout, c).base), 1, 1, M, N, K, has_bias ? bind(dbias, c).base : nullptr,
-                                  epi, c.stream);
+        GemmCase gc;
+        gc.dtype = in_dt; gc.out_dtype = out_dt; gc.batch = 1; gc.m = M; gc.n = N; gc.k = K;
+        gc.a_k_major = true; gc.b_k_major = w.strides[0] == 1 || K == 1;
+        mhlo_cuda_gemm_tuning gt{0, 0, 0, 0};
+        const bool tuned = lookup_gemm_tuning(gc, &gt);
+        add_step(tuned ? target + " [tuned]" : target, [=](const Ctx& c) {
+            return mhlo_cuda_gemm_tuned(in_dt, out_dt, bind(dx, c).base, as.data(), bind(dw, c).base, bs.data(),
+                                        const_cast<void*>(bind(dout, c).base), 1, 1, M, N, K, has_bias ? bind(dbias, c).base : nullptr,
+                                        epi, tuned ? &gt : nullptr, c.stream);
         });
         return set(op.results[0], out);
     }
@@ -1648,10 +1680,15 @@ void Lowering::lower_custom_call(const Op& op) {
         std::array<int64_t, 3> qs = {q.strides[0], q.strides[1], q.strides[2]}, ks = {k.strides[0], k.strides[1], k.strides[2]},
                                vs = {v.strides[0], v.strides[1], v.strides[2]};
         std::array<int64_t, 3> os = bshd_out ? std::array<int64_t, 3>{Sq * H * D, D, H * D} : std::array<int64_t, 3>{H * Sq * D, Sq * D, D};
-        add_step(target, [=](const Ctx& c) {
-            return mhlo_cuda_attention(dt, bind(dq, c).base, qs.data(), bind(dk, c).base, ks.data(), bind(dv, c).base, vs.data(),
-                                       has_mask ? bind(dm, c).base : nullptr, const_cast<void*>(bind(dout, c).base), os.data(), B, H, Sq,
-                                       Sk, D, scale, causal ? 1 : 0, c.stream);
+        AttentionCase ac;
+        ac.dtype = dt; ac.batch = B; ac.heads = H; ac.seq_q = Sq; ac.seq_k = Sk; ac.head_dim = D; ac.causal = causal;
+        ac.bshd = H > 1 && q.strides[1] == D;  // heads interleaved inside a token: the [batch, sequence, head, dim] layout
+        mhlo_cuda_attention_tuning at{0, {0, 0, 0}};
+        const bool tuned = !has_mask && lookup_attention_tuning(ac, &at);
+        add_step(tuned ? target + " [tuned]" : target, [=](const Ctx& c) {
+            return mhlo_cuda_attention_tuned(dt, bind(dq, c).base, qs.data(), bind(dk, c).base, ks.data(), bind(dv, c).base, vs.data(),
+                                             has_mask ? bind(dm, c).base : nullptr, const_cast<void*>(bind(dout, c).base), os.data(), B, H, Sq,
+                                             Sk, D, scale, causal ? 1 : 0, tuned ? &at : nullptr, c.stream);
         });
         return set(op.results[0], out);
     }

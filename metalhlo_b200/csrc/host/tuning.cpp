@@ -3,6 +3,8 @@
 
 #include <algorithm>
 #include <cmath>
+#include <functional>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <ctime>
@@ -23,8 +25,8 @@ bool TuningKey::operator==(const TuningKey& o) const { return !(*this < o) && !(
 
 std::string TuningConfig::description() const {
     char buf[160];
-    snprintf(buf, sizeof buf, "tile[%dx%dx%d]_stages%d_threads%d_vec%d_ctas%d", tile_m, tile_n, tile_k, stages, threads, vectors_per_thread,
-             ctas_per_sm);
+    snprintf(buf, sizeof buf, "tile[%dx%dx%d]_stages%d_threads%d_vec%d_ctas%d_group%d_order%d", tile_m, tile_n, tile_k, stages, threads,
+             vectors_per_thread, ctas_per_sm, cta_group, tile_order);
     return buf;
 }
 
@@ -266,7 +268,8 @@ std::string TuningDatabase::to_json() const {
         const TuningConfig& c = r.best;
         o += "    {\"bestConfig\": {\"tileM\": " + std::to_string(c.tile_m) + ", \"tileN\": " + std::to_string(c.tile_n) + ", \"tileK\": " +
              std::to_string(c.tile_k) + ", \"stages\": " + std::to_string(c.stages) + ", \"threads\": " + std::to_string(c.threads) +
-             ", \"vectorsPerThread\": " + std::to_string(c.vectors_per_thread) + ", \"ctasPerSM\": " + std::to_string(c.ctas_per_sm) +
+             ", \"vectorsPerThread\": " + std::to_string(c.vectors_per_thread) + ", \"ctasPerSM\": " + std::to_string(c.ctas_per_sm) + ", \"ctaGroup\": " +
+             std::to_string(c.cta_group) + ", \"tileOrder\": " + std::to_string(c.tile_order) +
              "}, \"measuredTime\": " + number(r.measured_time_s) + ", \"gflops\": " + number(r.gflops) + ", \"gbytesPerSecond\": " +
              number(r.gbytes_per_s) + ", \"configsTried\": " + std::to_string(r.configs_tried) + ", \"timestamp\": " +
              number(r.timestamp - kSwiftReferenceDate) + "}";
@@ -311,6 +314,8 @@ bool TuningDatabase::from_json(const std::string& text, std::string* why) {
             rec.best.threads = static_cast<int32_t>(c->number_or("threads", 0));
             rec.best.vectors_per_thread = static_cast<int32_t>(c->number_or("vectorsPerThread", 0));
             rec.best.ctas_per_sm = static_cast<int32_t>(c->number_or("ctasPerSM", 0));
+            rec.best.cta_group = static_cast<int32_t>(c->number_or("ctaGroup", 0));
+            rec.best.tile_order = static_cast<int32_t>(c->number_or("tileOrder", 0));
         }
         rec.measured_time_s = r.number_or("measuredTime", 0);
         rec.gflops = r.number_or("gflops", 0);
@@ -525,6 +530,210 @@ int tune_row_kernel(const std::string& kind, int dtype, int64_t rows, int64_t hi
         key.device = name;
         db->store(key, best);
     }
+    if (out) *out = best;
+    return MHLO_CUDA_OK;
+}
+
+std::string current_device_name() {
+    char name[256] = "";
+    int ordinal = 0;
+    if (mhlo_cuda_device_current(&ordinal) == MHLO_CUDA_OK) mhlo_cuda_device_name(ordinal, name, sizeof name);
+    return name;
+}
+
+namespace {
+
+const char* dtype_key(int dtype) { return dtype == MHLO_DT_BF16 ? "bf16" : dtype == MHLO_DT_F16 ? "f16" : "f32"; }
+
+// 5 warm-up + 20 timed launches of `launch`, median in seconds (AutoTuner.swift:242-245, 479-513); < 0 when a launch failed.
+double median_seconds(const std::function<int()>& launch, void* e0, void* e1) {
+    constexpr int kWarmup = 5, kTimed = 20;
+    for (int i = 0; i < kWarmup; ++i)
+        if (launch() != MHLO_CUDA_OK) return -1;
+    std::vector<float> ms(kTimed, 0.f);
+    for (int i = 0; i < kTimed; ++i) {
+        if (mhlo_cuda_event_record(e0, nullptr) != MHLO_CUDA_OK || launch() != MHLO_CUDA_OK || mhlo_cuda_event_record(e1, nullptr) != MHLO_CUDA_OK ||
+            mhlo_cuda_event_elapsed_ms(e0, e1, &ms[static_cast<size_t>(i)]) != MHLO_CUDA_OK)
+            return -1;
+    }
+    std::sort(ms.begin(), ms.end());
+    return 0.5 * (ms[kTimed / 2 - 1] + ms[kTimed / 2]) * 1e-3;
+}
+
+}  // namespace
+
+std::vector<TuningConfig> gemm_candidates(int64_t m, int64_t n, int64_t k) {
+    std::vector<TuningConfig> out;
+    auto add = [&](int tile_n, int stages, int group) {
+        TuningConfig c;
+        c.tile_m = 128 * group;
+        c.tile_n = tile_n;
+        c.tile_k = 64;
+        c.stages = stages;
+        c.cta_group = group;
+        out.push_back(c);
+    };
+    const int k_blocks = static_cast<int>((k + 63) / 64);
+    for (int stages : {6, 4, 3}) {
+        if (stages != 6 && stages > k_blocks + 1) continue;  // a ring deeper than the K loop is the same as the full one
+        add(128, stages, 1);
+    }
+    if (n > 128) {
+        for (int stages : {4, 3, 2}) add(256, stages, 1);
+        if (m > 128)
+            for (int stages : {6, 5, 4, 3}) add(256, stages, 2);
+    }
+    return out;
+}
+
+TuningKey GemmCase::key(const std::string& device) const {
+    TuningKey k;
+    k.op_type = "dot_general";
+    k.shapes = {{batch, m, this->k}, {batch, this->k, n}, {a_k_major ? 1 : 0, b_k_major ? 1 : 0, out_dtype}};
+    k.dtype = dtype_key(dtype);
+    k.device = device;
+    return k;
+}
+
+int tune_gemm(const GemmCase& c, int max_trials, TuningDatabase* db, TuningRecord* out, std::string* why) {
+    if ((c.dtype != MHLO_DT_BF16 && c.dtype != MHLO_DT_F16) || c.batch < 1 || c.m < 1 || c.n < 1 || c.k < 1) {
+        *why = "tune_gemm: bf16 / f16 operands and positive extents expected";
+        return MHLO_CUDA_INVALID_ARGUMENT;
+    }
+    const size_t out_es = mhlo_cuda_dtype_size(c.out_dtype);
+    if (out_es == 0) { *why = "tune_gemm: bad output dtype"; return MHLO_CUDA_INVALID_ARGUMENT; }
+    const size_t a_bytes = static_cast<size_t>(c.batch * c.m * c.k) * 2, b_bytes = static_cast<size_t>(c.batch * c.k * c.n) * 2,
+                 c_bytes = static_cast<size_t>(c.batch * c.m * c.n) * out_es;
+    void *a = nullptr, *b = nullptr, *d = nullptr, *e0 = nullptr, *e1 = nullptr;
+    auto cleanup = [&] {
+        if (a) mhlo_cuda_free(a);
+        if (b) mhlo_cuda_free(b);
+        if (d) mhlo_cuda_free(d);
+        if (e0) mhlo_cuda_event_destroy(e0);
+        if (e1) mhlo_cuda_event_destroy(e1);
+    };
+    auto failed = [&](int st) {
+        *why = mhlo_cuda_last_error();
+        cleanup();
+        return st;
+    };
+    int st;
+    if ((st = mhlo_cuda_alloc(a_bytes, &a)) || (st = mhlo_cuda_alloc(b_bytes, &b)) || (st = mhlo_cuda_alloc(c_bytes, &d)) ||
+        (st = mhlo_cuda_event_create(&e0)) || (st = mhlo_cuda_event_create(&e1)))
+        return failed(st);
+    // zero operands: the instruction stream and the traffic of the kernel do not depend on the values
+    if ((st = mhlo_cuda_memset(a, 0, a_bytes, nullptr)) || (st = mhlo_cuda_memset(b, 0, b_bytes, nullptr))) return failed(st);
+    const int64_t as[4] = {0, c.m * c.k, c.a_k_major ? c.k : 1, c.a_k_major ? 1 : c.m};
+    const int64_t bs[4] = {0, c.k * c.n, c.b_k_major ? 1 : c.n, c.b_k_major ? c.k : 1};
+    std::vector<TuningConfig> candidates = gemm_candidates(c.m, c.n, c.k);
+    candidates.insert(candidates.begin(), TuningConfig());  // the library's own choice competes too
+    if (max_trials > 0 && static_cast<int>(candidates.size()) > max_trials) candidates.resize(static_cast<size_t>(max_trials));
+    TuningRecord best;
+    best.measured_time_s = 1e30;
+    int tried = 0;
+    for (const TuningConfig& cand : candidates) {
+        mhlo_cuda_gemm_tuning t{cand.tile_n, cand.stages, cand.cta_group, 0};
+        const mhlo_cuda_gemm_tuning* tp = cand.is_default() ? nullptr : &t;
+        const double sec = median_seconds([&] {
+            return mhlo_cuda_gemm_tuned(c.dtype, c.out_dtype, a, as, b, bs, d, 1, c.batch, c.m, c.n, c.k, nullptr, MHLO_EPILOGUE_NONE, tp, nullptr);
+        }, e0, e1);
+        if (sec < 0) continue;
+        ++tried;
+        if (sec < best.measured_time_s) {
+            best.best = cand;
+            best.measured_time_s = sec;
+        }
+    }
+    int32_t device_code = 0;
+    mhlo_cuda_device_error(&device_code);
+    cleanup();
+    if (tried == 0 || device_code != 0) {
+        *why = tried == 0 ? "tune_gemm: no candidate could be launched" : "tune_gemm: a kernel gave up on a bounded wait";
+        return MHLO_CUDA_EXECUTION_FAILED;
+    }
+    best.configs_tried = tried;
+    best.gflops = 2.0 * static_cast<double>(c.batch) * c.m * c.n * c.k / best.measured_time_s / 1e9;
+    best.gbytes_per_s = static_cast<double>(a_bytes + b_bytes + c_bytes) / best.measured_time_s / 1e9;
+    best.timestamp = static_cast<double>(std::time(nullptr));
+    if (db) db->store(c.key(current_device_name()), best);
+    if (out) *out = best;
+    return MHLO_CUDA_OK;
+}
+
+TuningKey AttentionCase::key(const std::string& device) const {
+    TuningKey k;
+    k.op_type = "fused_scaled_dot_product_attention";
+    k.shapes = {{batch, heads, seq_q, head_dim}, {batch, heads, seq_k, head_dim}, {causal ? 1 : 0, bshd ? 1 : 0}};
+    k.dtype = dtype_key(dtype);
+    k.device = device;
+    return k;
+}
+
+int tune_attention(const AttentionCase& c, int max_trials, TuningDatabase* db, TuningRecord* out, std::string* why) {
+    if ((c.dtype != MHLO_DT_BF16 && c.dtype != MHLO_DT_F16) || (c.head_dim != 64 && c.head_dim != 128) || c.batch < 1 || c.heads < 1 ||
+        c.seq_q < 1 || c.seq_k < 1) {
+        *why = "tune_attention: bf16 / f16 operands with head dimension 64 or 128 expected (the tensor-core kernel's domain)";
+        return MHLO_CUDA_INVALID_ARGUMENT;
+    }
+    const size_t q_bytes = static_cast<size_t>(c.batch * c.heads * c.seq_q * c.head_dim) * 2, kv_bytes = static_cast<size_t>(c.batch * c.heads * c.seq_k * c.head_dim) * 2;
+    void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *e0 = nullptr, *e1 = nullptr;
+    auto cleanup = [&] {
+        for (void* p : {q, k, v, o})
+            if (p) mhlo_cuda_free(p);
+        if (e0) mhlo_cuda_event_destroy(e0);
+        if (e1) mhlo_cuda_event_destroy(e1);
+    };
+    auto failed = [&](int st) {
+        *why = mhlo_cuda_last_error();
+        cleanup();
+        return st;
+    };
+    int st;
+    if ((st = mhlo_cuda_alloc(q_bytes, &q)) || (st = mhlo_cuda_alloc(kv_bytes, &k)) || (st = mhlo_cuda_alloc(kv_bytes, &v)) ||
+        (st = mhlo_cuda_alloc(q_bytes, &o)) || (st = mhlo_cuda_event_create(&e0)) || (st = mhlo_cuda_event_create(&e1)))
+        return failed(st);
+    if ((st = mhlo_cuda_memset(q, 0, q_bytes, nullptr)) || (st = mhlo_cuda_memset(k, 0, kv_bytes, nullptr)) || (st = mhlo_cuda_memset(v, 0, kv_bytes, nullptr)))
+        return failed(st);
+    auto strides = [&](int64_t seq, int64_t* s) {
+        if (c.bshd) { s[0] = seq * c.heads * c.head_dim; s[1] = c.head_dim; s[2] = c.heads * c.head_dim; }
+        else { s[0] = c.heads * seq * c.head_dim; s[1] = seq * c.head_dim; s[2] = c.head_dim; }
+    };
+    int64_t qs[3], ks[3];
+    strides(c.seq_q, qs);
+    strides(c.seq_k, ks);
+    std::vector<TuningConfig> candidates(3);
+    candidates[1].tile_order = 1;
+    candidates[2].tile_order = 2;
+    if (max_trials > 0 && static_cast<int>(candidates.size()) > max_trials) candidates.resize(static_cast<size_t>(max_trials));
+    TuningRecord best;
+    best.measured_time_s = 1e30;
+    int tried = 0;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(c.head_dim));
+    for (const TuningConfig& cand : candidates) {
+        mhlo_cuda_attention_tuning t{cand.tile_order, {0, 0, 0}};
+        const mhlo_cuda_attention_tuning* tp = cand.is_default() ? nullptr : &t;
+        const double sec = median_seconds([&] {
+            return mhlo_cuda_attention_tuned(c.dtype, q, qs, k, ks, v, ks, nullptr, o, qs, c.batch, c.heads, c.seq_q, c.seq_k, c.head_dim, scale,
+                                             c.causal ? 1 : 0, tp, nullptr);
+        }, e0, e1);
+        if (sec < 0) continue;
+        ++tried;
+        if (sec < best.measured_time_s) {
+            best.best = cand;
+            best.measured_time_s = sec;
+        }
+    }
+    int32_t device_code = 0;
+    mhlo_cuda_device_error(&device_code);
+    cleanup();
+    if (tried == 0 || device_code != 0) {
+        *why = tried == 0 ? "tune_attention: no candidate could be launched" : "tune_attention: a kernel gave up on a bounded wait";
+        return MHLO_CUDA_EXECUTION_FAILED;
+    }
+    best.configs_tried = tried;
+    best.gflops = 4.0 * static_cast<double>(c.batch) * c.heads * c.seq_q * c.seq_k * c.head_dim * (c.causal ? 0.5 : 1.0) / best.measured_time_s / 1e9;
+    best.timestamp = static_cast<double>(std::time(nullptr));
+    if (db) db->store(c.key(current_device_name()), best);
     if (out) *out = best;
     return MHLO_CUDA_OK;
 }

@@ -28,6 +28,11 @@ struct TuningKey {
 struct TuningConfig {
     int32_t tile_m = 0, tile_n = 0, tile_k = 0, stages = 0;
     int32_t threads = 0, vectors_per_thread = 0, ctas_per_sm = 0;
+    int32_t cta_group = 0;   // GEMM: 1 = one CTA per tile, 2 = a pair of CTAs per 256 x 256 tile (mhlo_cuda_gemm_tuning)
+    int32_t tile_order = 0;  // attention: order of the query tiles over the CTAs (mhlo_cuda_attention_tuning)
+    bool is_default() const {
+        return !tile_m && !tile_n && !tile_k && !stages && !threads && !vectors_per_thread && !ctas_per_sm && !cta_group && !tile_order;
+    }
     std::string description() const;
 };
 
@@ -86,5 +91,32 @@ std::vector<TuningConfig> row_kernel_candidates(int64_t hidden, int elem_bytes);
 // "fused_softmax". Scratch tensors are allocated and freed inside. Returns an mhlo_cuda status; message via *why.
 int tune_row_kernel(const std::string& kind, int dtype, int64_t rows, int64_t hidden, int max_trials, TuningDatabase* db,
                     TuningRecord* out, std::string* why);
+
+// Candidates of the tensor-core GEMM: tile width x ring depth x CTA group, as the kernel provides them.
+std::vector<TuningConfig> gemm_candidates(int64_t m, int64_t n, int64_t k);
+
+// Description of one dot_general as the tuner and the lowering key it: bf16 / f16 operands, `batch` independent products,
+// operand majors as the kernel sees them (k_major: the contracted dimension is the contiguous one).
+struct GemmCase {
+    int dtype = 0, out_dtype = 0;
+    int64_t batch = 1, m = 0, n = 0, k = 0;
+    bool a_k_major = true, b_k_major = false;
+    TuningKey key(const std::string& device) const;
+};
+// Times every candidate on the current device (5 warm-up + 20 timed launches, median) and stores the best under the
+// case's key. Scratch operands are allocated and freed inside.
+int tune_gemm(const GemmCase& c, int max_trials, TuningDatabase* db, TuningRecord* out, std::string* why);
+
+struct AttentionCase {
+    int dtype = 0;
+    int64_t batch = 1, heads = 1, seq_q = 0, seq_k = 0, head_dim = 0;
+    bool causal = false;
+    bool bshd = false;  // operands laid out [batch, sequence, head, dim] instead of [batch, head, sequence, dim]
+    TuningKey key(const std::string& device) const;
+};
+int tune_attention(const AttentionCase& c, int max_trials, TuningDatabase* db, TuningRecord* out, std::string* why);
+
+// Name of the current CUDA device, as the keys carry it.
+std::string current_device_name();
 
 }  // namespace mhlo

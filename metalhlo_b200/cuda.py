@@ -145,6 +145,8 @@ _PROTOTYPES = {
     "mhlo_cuda_debug_wait_expiry_probe": (C.c_int, [C.c_uint64, _vp]),
     "mhlo_cuda_attention": (C.c_int, [_i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _vp,
                                       C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "mhlo_cuda_attention_tuned": (C.c_int, [_i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _vp,
+                                            C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp, _vp]),
 }
 for _name, (_res, _args) in _PROTOTYPES.items():
     _fn = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
@@ -292,7 +294,11 @@ def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool 
     return out
 
 
-def attention(q, k, v, scale: float, causal: bool = False, mask=None, layout: str = "BHSD", out=None, stream=None):
+class AttentionTuning(C.Structure):
+    _fields_ = [("tile_order", C.c_int32), ("reserved", C.c_int32 * 3)]
+
+
+def attention(q, k, v, scale: float, causal: bool = False, mask=None, layout: str = "BHSD", out=None, stream=None, tile_order=None):
     """Fused attention through ``mhlo_cuda_attention``. q/k/v are dense [B,H,S,D] (layout "BHSD") or [B,S,H,D] ("BSHD")."""
     import torch
 
@@ -306,6 +312,12 @@ def attention(q, k, v, scale: float, causal: bool = False, mask=None, layout: st
         Sk = k.shape[1]
         strides = lambda S: [S * H * D, D, H * D]
     out = torch.empty_like(q) if out is None else out
+    if tile_order is not None:  # mhlo_cuda_attention_tuned
+        t = AttentionTuning(tile_order)
+        check(lib.mhlo_cuda_attention_tuned(torch_dtype_code(q.dtype), _ptr(q), _i64s(strides(Sq)), _ptr(k), _i64s(strides(Sk)), _ptr(v),
+                                            _i64s(strides(Sk)), _ptr(mask), _ptr(out), _i64s(strides(Sq)), B, H, Sq, Sk, D, scale,
+                                            1 if causal else 0, C.addressof(t), _stream(stream)))
+        return out
     check(lib.mhlo_cuda_attention(torch_dtype_code(q.dtype), _ptr(q), _i64s(strides(Sq)), _ptr(k), _i64s(strides(Sk)), _ptr(v),
                                   _i64s(strides(Sk)), _ptr(mask), _ptr(out), _i64s(strides(Sq)), B, H, Sq, Sk, D, scale,
                                   1 if causal else 0, _stream(stream)))
