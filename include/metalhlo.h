@@ -154,6 +154,11 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
  * per line (free with mhlo_free_string); out_launches / out_arena_bytes may be NULL. */
 MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_level, char** out_steps,
                                    int32_t* out_launches, int64_t* out_arena_bytes);
+/* CUDA devices visible to this process, and a client bound to one of them (mhlo_client_create takes METALHLO_DEVICE /
+ * LOCAL_RANK, else device 0). A process may hold one client per GPU; the PJRT plugin does so when it exposes several
+ * devices. The reference has one Metal device per client (Sources/MetalHLO/Client.swift). */
+int32_t mhlo_b200_device_count(void);
+MHLOStatusCode mhlo_b200_client_create_on_device(int32_t device_ordinal, MHLOClientRef* out_client);
 /*
  * Batch sharding. The reference runs every program on one device (Sources/PJRTMetalHLO/PJRTExecutable.swift:1830-1848
  * fixes num_replicas = num_partitions = 1 and :2033-2036 refuses several devices). Here a program whose results are,

@@ -105,6 +105,8 @@ _PROTOTYPES = {
     "mhlo_execute_with_profile": (C.c_int, [_vp, _P(_vp), _i32, _P(_vp), _P(_i32), _P(ExecutionProfile)]),
     "mhlo_b200_optimize_text": (C.c_int, [C.c_char_p, _i32, _P(_vp)]),
     "mhlo_b200_plan_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i32), _P(_i64)]),
+    "mhlo_b200_device_count": (_i32, []),
+    "mhlo_b200_client_create_on_device": (C.c_int, [_i32, _P(_vp)]),
     "mhlo_b200_compile_sharded": (C.c_int, [_vp, C.c_char_p, _P(CompileConfig), _i32, _i32, _P(_i32), _i32, _P(_vp)]),
     "mhlo_b200_executable_sharding": (C.c_int, [_vp, _P(_i32), _P(_i32), _P(_i32), _P(_i32)]),
     "mhlo_b200_shard_text": (C.c_int, [C.c_char_p, _i32, _i32, _P(_i32), _i32, _P(_vp), _P(_i32), _P(_i32)]),
@@ -373,9 +375,12 @@ class Executable:
 
 
 class Client:
-    def __init__(self):
+    def __init__(self, device: int | None = None):
         h = _vp()
-        _check(lib.mhlo_client_create(C.byref(h)))
+        if device is None:
+            _check(lib.mhlo_client_create(C.byref(h)))
+        else:
+            _check(lib.mhlo_b200_client_create_on_device(device, C.byref(h)))
         self._h = h.value
 
     def __del__(self):

@@ -278,7 +278,23 @@ size_t mhlo_element_type_size(MHLOElementType type) {
 
 void mhlo_free_string(const char* str) { std::free(const_cast<char*>(str)); }
 
-MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) {
+static MHLOStatusCode client_create_impl(MHLOClientRef* out_client, int forced_device);
+
+MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) { return client_create_impl(out_client, -1); }
+
+// A client bound to CUDA device `device_ordinal` (mhlo_client_create takes METALHLO_DEVICE / LOCAL_RANK, else device 0).
+// One process may hold one client per GPU: each has its own stream, buffer pool and executable cache.
+MHLOStatusCode mhlo_b200_client_create_on_device(int32_t device_ordinal, MHLOClientRef* out_client) {
+    if (device_ordinal < 0) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "negative device ordinal"));
+    return client_create_impl(out_client, device_ordinal);
+}
+
+int32_t mhlo_b200_device_count(void) {
+    int n = 0;
+    return mhlo_cuda_device_count(&n) == 0 ? n : 0;
+}
+
+static MHLOStatusCode client_create_impl(MHLOClientRef* out_client, int forced_device) {
     if (!out_client) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_client is null"));
     *out_client = nullptr;
     int n = 0;
@@ -293,7 +309,12 @@ MHLOStatusCode mhlo_client_create(MHLOClientRef* out_client) {
         if (c->shard_count < 1 || c->shard_index < 0 || c->shard_index >= c->shard_count)
             return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "METALHLO_SHARD_COUNT / METALHLO_SHARD_INDEX out of range"));
     }
-    if (const char* lr = std::getenv("METALHLO_DEVICE")) c->device = std::atoi(lr);
+    if (forced_device >= 0) {
+        if (forced_device >= n)
+            return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_NO_DEVICE, "CUDA device " + std::to_string(forced_device) + " does not exist (" +
+                                                         std::to_string(n) + " visible)"));
+        c->device = forced_device;
+    } else if (const char* lr = std::getenv("METALHLO_DEVICE")) c->device = std::atoi(lr);
     else if (const char* lr2 = std::getenv("LOCAL_RANK")) c->device = std::atoi(lr2) % n;
     if (c->device < 0 || c->device >= n) c->device = 0;
     if (mhlo_cuda_device_set(c->device) != 0 || mhlo_cuda_stream_create(&c->stream) != 0)

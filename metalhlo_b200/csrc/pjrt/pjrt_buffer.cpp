@@ -52,9 +52,10 @@ size_t storage_bytes_per_element(MHLOElementType t) {
     return n ? n : 1;
 }
 
-PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref) {
+PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref, PJRT_Device* device) {
     auto* b = new PJRT_Buffer();
     b->client = client;
+    b->device = device ? device : (client && !client->devices.empty() ? client->devices[0] : nullptr);
     b->mhlo = ref;
     const int32_t rank = mhlo_buffer_rank(ref);
     b->dims.resize(static_cast<size_t>(rank));
@@ -132,12 +133,17 @@ PJRT_Error* buffer_from_host(PJRT_Client_BufferFromHostBuffer_Args* args) {
         pack_dense(static_cast<const uint8_t*>(args->data), packed.data(), dims, args->byte_strides, elem);
         src = packed.data();
     }
+    // the target: the given device, else the device of the given memory, else device 0
+    PJRT_Device* target = args->device;
+    if (!target && args->memory && !args->memory->devices.empty()) target = args->memory->devices[0];
+    if (!target) target = args->client->devices[0];
+    if (target->client != args->client) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "device belongs to another client");
     MHLOBufferRef ref = nullptr;
-    const MHLOStatusCode st = mhlo_buffer_create(args->client->mhlo, src, bytes, dims.data(), static_cast<int32_t>(dims.size()), et, &ref);
+    const MHLOStatusCode st = mhlo_buffer_create(target->mhlo, src, bytes, dims.data(), static_cast<int32_t>(dims.size()), et, &ref);
     if (st != MHLO_OK || !ref)
         return make_error(PJRT_Error_Code_INTERNAL, std::string("Buffer creation failed: ") + mhlo_get_last_error());
     args->done_with_host_buffer = new_ready_event();
-    args->buffer = wrap_buffer(args->client, ref);
+    args->buffer = wrap_buffer(args->client, ref, target);
     return nullptr;
 }
 
@@ -199,13 +205,13 @@ PJRT_Error* buffer_on_device_size(PJRT_Buffer_OnDeviceSizeInBytes_Args* args) {
 
 PJRT_Error* buffer_device(PJRT_Buffer_Device_Args* args) {
     PJRT_B200_REQUIRE(args && args->buffer && args->buffer->client, "NULL args");
-    args->device = args->buffer->client->devices[0];
+    args->device = args->buffer->device;
     return nullptr;
 }
 
 PJRT_Error* buffer_memory(PJRT_Buffer_Memory_Args* args) {
     PJRT_B200_REQUIRE(args && args->buffer && args->buffer->client, "NULL args");
-    args->memory = args->buffer->client->memories[0];
+    args->memory = args->buffer->device->memories[0];
     return nullptr;
 }
 
@@ -221,35 +227,48 @@ PJRT_Error* buffer_is_deleted(PJRT_Buffer_IsDeleted_Args* args) {
     return nullptr;
 }
 
-// Same-device copy into a fresh buffer (PJRTBuffer.swift:392-440): one device-to-device copy, then a stream sync
-// so that the new buffer's ready event can be complete on return.
-PJRT_Error* duplicate(PJRT_Buffer* src, PJRT_Buffer** out, const char* what) {
+// Copy into a fresh buffer on `target` (PJRTBuffer.swift:392-440). Same device: one device-to-device copy on that device.
+// Another GPU of this client: through pinned-size host memory, which needs no peer mapping between the two devices.
+PJRT_Error* duplicate(PJRT_Buffer* src, PJRT_Device* target, PJRT_Buffer** out, const char* what) {
     if (!src->mhlo) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, std::string(what) + ": buffer was deleted");
+    if (!target) target = src->device;
+    if (target->client != src->client) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, std::string(what) + ": device belongs to another client");
     MHLOElementType et;
     to_mhlo_type(src->type, &et);
     MHLOBufferRef ref = nullptr;
-    if (mhlo_buffer_create_uninitialized(src->client->mhlo, src->dims.data(), static_cast<int32_t>(src->dims.size()), et, &ref) != MHLO_OK)
+    if (target != src->device) {
+        std::vector<uint8_t> host(src->bytes);
+        if (src->bytes && mhlo_buffer_to_host(src->mhlo, host.data(), host.size()) != MHLO_OK)
+            return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
+        if (mhlo_buffer_create(target->mhlo, host.data(), host.size(), src->dims.data(), static_cast<int32_t>(src->dims.size()), et, &ref) != MHLO_OK)
+            return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
+        *out = wrap_buffer(src->client, ref, target);
+        return nullptr;
+    }
+    if (mhlo_buffer_create_uninitialized(target->mhlo, src->dims.data(), static_cast<int32_t>(src->dims.size()), et, &ref) != MHLO_OK)
         return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
     if (src->bytes) {
-        int st = mhlo_cuda_copy(mhlo_b200_buffer_device_pointer(ref), mhlo_b200_buffer_device_pointer(src->mhlo), src->bytes, nullptr);
+        int st = mhlo_cuda_device_set(target->cuda_ordinal);
+        if (st == MHLO_CUDA_OK) st = mhlo_cuda_copy(mhlo_b200_buffer_device_pointer(ref), mhlo_b200_buffer_device_pointer(src->mhlo), src->bytes, nullptr);
         if (st == MHLO_CUDA_OK) st = mhlo_cuda_stream_sync(nullptr);
         if (st != MHLO_CUDA_OK) {
             mhlo_buffer_destroy(ref);
             return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_cuda_last_error());
         }
     }
-    *out = wrap_buffer(src->client, ref);
+    *out = wrap_buffer(src->client, ref, target);
     return nullptr;
 }
 
 PJRT_Error* buffer_copy_to_device(PJRT_Buffer_CopyToDevice_Args* args) {
     PJRT_B200_REQUIRE(args && args->buffer, "NULL args");
-    return duplicate(args->buffer, &args->dst_buffer, "CopyToDevice");
+    return duplicate(args->buffer, args->dst_device, &args->dst_buffer, "CopyToDevice");
 }
 
 PJRT_Error* buffer_copy_to_memory(PJRT_Buffer_CopyToMemory_Args* args) {
     PJRT_B200_REQUIRE(args && args->buffer, "NULL args");
-    return duplicate(args->buffer, &args->dst_buffer, "CopyToMemory");
+    PJRT_Device* target = args->dst_memory && !args->dst_memory->devices.empty() ? args->dst_memory->devices[0] : nullptr;
+    return duplicate(args->buffer, target, &args->dst_buffer, "CopyToMemory");
 }
 
 // PJRTBuffer.swift:270-310: a NULL destination asks for the size only.

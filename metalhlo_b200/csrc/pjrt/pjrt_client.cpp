@@ -1,7 +1,9 @@
 // PJRT client, device, device description, memory and topology entries (reference:
 // Sources/PJRTMetalHLO/PJRTClient.swift, PJRTDevice.swift, PJRTMemory.swift, PJRTTopology.swift).
-// One client owns one CUDA device (chosen by mhlo_client_create) and one memory space, kind "device".
+// One client owns one CUDA device (chosen by mhlo_client_create), or the first METALHLO_NUM_GPUS devices of the process,
+// each with its own memory space of kind "device".
 #include <cstdlib>
+#include <string>
 
 #include "pjrt_objects.h"
 
@@ -51,57 +53,78 @@ int env_ordinal() {
     return 0;
 }
 
+// How many GPUs the client exposes as PJRT devices: METALHLO_NUM_GPUS = a count or "all"; unset = 1, the reference's
+// single device (PJRTClient.swift:180-193).
+int wanted_device_count(int visible) {
+    const char* v = std::getenv("METALHLO_NUM_GPUS");
+    if (!v || !*v) return 1;
+    if (std::string(v) == "all") return visible;
+    const int n = std::atoi(v);
+    return n < 1 ? 1 : (n > visible ? visible : n);
+}
+
 // ---- client (PJRTClient.swift:112-259) ----
 PJRT_Error* client_create(PJRT_Client_Create_Args* args) {
     PJRT_B200_REQUIRE(args, "NULL args");
-    MHLOClientRef ref = nullptr;
-    if (mhlo_client_create(&ref) != MHLO_OK || !ref)
-        return make_error(PJRT_Error_Code_INTERNAL, std::string("Failed to create CUDA client: ") + mhlo_get_last_error());
-    auto* c = new PJRT_Client();
-    c->mhlo = ref;
+    const int visible = mhlo_b200_device_count();
+    const int count = wanted_device_count(visible);
+    auto c = std::unique_ptr<PJRT_Client>(new PJRT_Client());
     c->platform_name = kPlatformName;
     c->platform_version = kPlatformVersion;
-    char* name = mhlo_client_device_name(ref);
-    const std::string device_name = name ? name : "CUDA device";
-    if (name) mhlo_free_string(name);
-
-    c->device.reset(new PJRT_Device());
-    c->device->client = c;
-    c->device->cuda_ordinal = env_ordinal();
-    PJRT_DeviceDescription& d = c->device->description;
-    d.id = 0;
-    d.process_index = 0;
-    d.kind = "CUDA";
-    d.debug_string = "CUDA:" + device_name;
-    d.to_string = device_name;
-    // The two attributes the reference always publishes (PJRTDevice.swift:40-66), then this backend's own.
-    add_int_attribute(&d, "ane_available", 0);
     const char* policy = std::getenv("METALHLO_DEVICE_POLICY");
-    add_string_attribute(&d, "device_policy", policy && *policy ? policy : "auto");
-    add_int_attribute(&d, "cuda_ordinal", c->device->cuda_ordinal);
-    seal_attributes(&d);
-
-    c->memory.reset(new PJRT_Memory());
-    c->memory->id = 0;
-    c->memory->kind_id = 0;
-    c->memory->kind = "device";
-    c->memory->debug_string = "CUDA device memory";
-    c->memory->to_string = "CUDA device";
-    c->memory->devices = {c->device.get()};
-    c->device->memories = {c->memory.get()};
-    c->devices = {c->device.get()};
-    c->memories = {c->memory.get()};
-
+    for (int i = 0; i < count; ++i) {
+        MHLOClientRef ref = nullptr;
+        // one device: the C API's own choice (METALHLO_DEVICE / LOCAL_RANK); several: GPUs 0 .. count-1 of this process
+        const MHLOStatusCode st = count == 1 ? mhlo_client_create(&ref) : mhlo_b200_client_create_on_device(i, &ref);
+        if (st != MHLO_OK || !ref) {
+            const std::string why = mhlo_get_last_error() ? mhlo_get_last_error() : "unknown error";
+            for (auto& d : c->owned_devices) mhlo_client_destroy(d->mhlo);
+            return make_error(PJRT_Error_Code_INTERNAL, "Failed to create CUDA client: " + why);
+        }
+        char* name = mhlo_client_device_name(ref);
+        const std::string device_name = name ? name : "CUDA device";
+        if (name) mhlo_free_string(name);
+        std::unique_ptr<PJRT_Device> dev(new PJRT_Device());
+        dev->client = c.get();
+        dev->index = i;
+        dev->cuda_ordinal = count == 1 ? env_ordinal() : i;
+        dev->mhlo = ref;
+        PJRT_DeviceDescription& d = dev->description;
+        d.id = i;
+        d.process_index = 0;
+        d.kind = "CUDA";
+        d.debug_string = "CUDA:" + device_name + (count > 1 ? ":" + std::to_string(i) : "");
+        d.to_string = device_name;
+        // The two attributes the reference always publishes (PJRTDevice.swift:40-66), then this backend's own.
+        add_int_attribute(&d, "ane_available", 0);
+        add_string_attribute(&d, "device_policy", policy && *policy ? policy : "auto");
+        add_int_attribute(&d, "cuda_ordinal", dev->cuda_ordinal);
+        seal_attributes(&d);
+        std::unique_ptr<PJRT_Memory> mem(new PJRT_Memory());
+        mem->id = i;
+        mem->kind_id = 0;
+        mem->kind = "device";
+        mem->debug_string = "CUDA device memory";
+        mem->to_string = "CUDA device";
+        mem->devices = {dev.get()};
+        dev->memories = {mem.get()};
+        c->devices.push_back(dev.get());
+        c->memories.push_back(mem.get());
+        c->owned_devices.push_back(std::move(dev));
+        c->owned_memories.push_back(std::move(mem));
+    }
+    if (c->devices.empty()) return make_error(PJRT_Error_Code_INTERNAL, "Failed to create CUDA client: No CUDA device available");
+    c->mhlo = c->devices[0]->mhlo;
     c->topology.platform_name = kPlatformName;
     c->topology.platform_version = kPlatformVersion;
-    c->topology.descriptions = {&c->device->description};
-    args->client = c;
+    for (PJRT_Device* d : c->devices) c->topology.descriptions.push_back(&d->description);
+    args->client = c.release();
     return nullptr;
 }
 
 PJRT_Error* client_destroy(PJRT_Client_Destroy_Args* args) {
     if (!args || !args->client) return nullptr;
-    mhlo_client_destroy(args->client->mhlo);
+    for (auto& d : args->client->owned_devices) mhlo_client_destroy(d->mhlo);
     delete args->client;
     return nullptr;
 }
@@ -142,16 +165,17 @@ PJRT_Error* client_addressable_devices(PJRT_Client_AddressableDevices_Args* args
 
 PJRT_Error* client_lookup_device(PJRT_Client_LookupDevice_Args* args) {
     PJRT_B200_REQUIRE(args && args->client, "NULL args");
-    if (args->id != 0) return make_error(PJRT_Error_Code_NOT_FOUND, "Device " + std::to_string(args->id) + " not found");
-    args->device = args->client->devices[0];
+    if (args->id < 0 || args->id >= static_cast<int>(args->client->devices.size()))
+        return make_error(PJRT_Error_Code_NOT_FOUND, "Device " + std::to_string(args->id) + " not found");
+    args->device = args->client->devices[static_cast<size_t>(args->id)];
     return nullptr;
 }
 
 PJRT_Error* client_lookup_addressable_device(PJRT_Client_LookupAddressableDevice_Args* args) {
     PJRT_B200_REQUIRE(args && args->client, "NULL args");
-    if (args->local_hardware_id != 0)
+    if (args->local_hardware_id < 0 || args->local_hardware_id >= static_cast<int>(args->client->devices.size()))
         return make_error(PJRT_Error_Code_NOT_FOUND, "Local device " + std::to_string(args->local_hardware_id) + " not found");
-    args->addressable_device = args->client->devices[0];
+    args->addressable_device = args->client->devices[static_cast<size_t>(args->local_hardware_id)];
     return nullptr;
 }
 
@@ -165,8 +189,11 @@ PJRT_Error* client_addressable_memories(PJRT_Client_AddressableMemories_Args* ar
 PJRT_Error* client_default_device_assignment(PJRT_Client_DefaultDeviceAssignment_Args* args) {
     PJRT_B200_REQUIRE(args, "NULL args");
     const size_t want = static_cast<size_t>(std::max(0, args->num_replicas)) * static_cast<size_t>(std::max(0, args->num_partitions));
+    // replica r of a single-partition program runs on device r (all on device 0 when the client exposes only one)
+    const size_t n_dev = args->client ? args->client->devices.size() : 1;
     if (args->default_assignment)
-        for (size_t i = 0; i < want && i < args->default_assignment_size; ++i) args->default_assignment[i] = 0;
+        for (size_t i = 0; i < want && i < args->default_assignment_size; ++i)
+            args->default_assignment[i] = static_cast<int>(args->num_partitions > 0 ? (i / static_cast<size_t>(args->num_partitions)) % n_dev : 0);
     return nullptr;
 }
 
@@ -225,7 +252,7 @@ PJRT_Error* device_is_addressable(PJRT_Device_IsAddressable_Args* args) {
 }
 PJRT_Error* device_local_hardware_id(PJRT_Device_LocalHardwareId_Args* args) {
     PJRT_B200_REQUIRE(args && args->device, "NULL args");
-    args->local_hardware_id = 0;
+    args->local_hardware_id = args->device->index;
     return nullptr;
 }
 PJRT_Error* device_addressable_memories(PJRT_Device_AddressableMemories_Args* args) {

@@ -1,5 +1,6 @@
 // PJRT compile, executable and execution entries (reference: Sources/PJRTMetalHLO/PJRTExecutable.swift:266-400 for
 // the executable objects, :1660-1815 for compile, :1820-2208 for the getters, Execute and DeserializeAndLoad).
+#include <thread>
 #include <cstdio>
 #include <cstdlib>
 
@@ -59,18 +60,114 @@ std::shared_ptr<ExecutableMeta> describe(MHLOExecutableRef exe, const std::strin
     return m;
 }
 
+// ---- the part of CompileOptionsProto this plugin honours (xla/pjrt/proto/compile_options.proto): field 3
+// executable_build_options { 4 num_replicas, 5 num_partitions, 9 device_assignment { 3 computation_devices { 1 replica_device_ids } } }.
+// The reference ignores the options and fixes both counts at 1 (PJRTExecutable.swift:1830-1848). ----
+struct BuildOptions {
+    int64_t num_replicas = 1, num_partitions = 1;
+    std::vector<int64_t> replica_devices;  // device id of replica r (partition 0), when an assignment was sent
+};
+
+struct ProtoReader {
+    const unsigned char* p;
+    const unsigned char* end;
+    bool ok = true;
+    uint64_t varint() {
+        uint64_t v = 0;
+        for (int shift = 0; shift < 64 && p < end; shift += 7) {
+            const unsigned char b = *p++;
+            v |= static_cast<uint64_t>(b & 0x7f) << shift;
+            if (!(b & 0x80)) return v;
+        }
+        ok = false;
+        return 0;
+    }
+    // next field: number, wire type, and for length-delimited fields the payload range
+    bool next(int* field, int* wire, uint64_t* value, ProtoReader* sub) {
+        if (p >= end || !ok) return false;
+        const uint64_t key = varint();
+        *field = static_cast<int>(key >> 3);
+        *wire = static_cast<int>(key & 7);
+        if (*wire == 0) *value = varint();
+        else if (*wire == 2) {
+            const uint64_t n = varint();
+            if (!ok || n > static_cast<uint64_t>(end - p)) { ok = false; return false; }
+            *sub = ProtoReader{p, p + n};
+            p += n;
+        } else if (*wire == 1) { if (end - p < 8) { ok = false; return false; } p += 8; }
+        else if (*wire == 5) { if (end - p < 4) { ok = false; return false; } p += 4; }
+        else { ok = false; return false; }
+        return ok;
+    }
+};
+
+bool parse_build_options(const char* data, size_t size, BuildOptions* out) {
+    if (!data || size == 0) return true;
+    ProtoReader top{reinterpret_cast<const unsigned char*>(data), reinterpret_cast<const unsigned char*>(data) + size};
+    int field, wire;
+    uint64_t value;
+    ProtoReader sub{nullptr, nullptr};
+    while (top.next(&field, &wire, &value, &sub)) {
+        if (field != 3 || wire != 2) continue;
+        ProtoReader build = sub, inner{nullptr, nullptr};
+        while (build.next(&field, &wire, &value, &inner)) {
+            if (field == 4 && wire == 0) out->num_replicas = static_cast<int64_t>(value);
+            else if (field == 5 && wire == 0) out->num_partitions = static_cast<int64_t>(value);
+            else if (field == 9 && wire == 2) {
+                ProtoReader assign = inner, comp{nullptr, nullptr};
+                bool first_computation = true;
+                while (assign.next(&field, &wire, &value, &comp)) {
+                    if (field != 3 || wire != 2 || !first_computation) continue;
+                    first_computation = false;
+                    ProtoReader ids = comp, packed{nullptr, nullptr};
+                    while (ids.next(&field, &wire, &value, &packed)) {
+                        if (field != 1) continue;
+                        if (wire == 0) out->replica_devices.push_back(static_cast<int64_t>(value));
+                        else if (wire == 2) while (packed.p < packed.end && packed.ok) out->replica_devices.push_back(static_cast<int64_t>(packed.varint()));
+                    }
+                }
+            }
+        }
+        if (!build.ok) return false;
+    }
+    return top.ok;
+}
+
+// Compiles `text` once per replica, each on its own device's client. Replica r runs on the r-th device of the assignment,
+// else on device r.
 PJRT_Error* compile_text(PJRT_Client* client, const std::string& text, MHLOOptimizationLevel level, const std::string& name,
-                         const char* failure_prefix, PJRT_LoadedExecutable** out) {
+                         const char* failure_prefix, PJRT_LoadedExecutable** out, const BuildOptions& options = BuildOptions()) {
+    if (options.num_partitions != 1)
+        return make_error(PJRT_Error_Code_UNIMPLEMENTED, std::string(failure_prefix) + "num_partitions = " + std::to_string(options.num_partitions) +
+                                                             ": programs are not partitioned across devices (replicas are)");
+    const size_t replicas = options.num_replicas < 1 ? 1 : static_cast<size_t>(options.num_replicas);
+    if (replicas > client->devices.size())
+        return make_error(PJRT_Error_Code_INVALID_ARGUMENT, std::string(failure_prefix) + std::to_string(replicas) + " replicas on a client with " +
+                                                                std::to_string(client->devices.size()) + " device(s); set METALHLO_NUM_GPUS");
     MHLOCompileConfig config;
     mhlo_compile_config_init(&config);
     config.optimization_level = level;
-    MHLOExecutableRef exe = nullptr;
-    if (mhlo_compile_with_config(client->mhlo, text.c_str(), &config, &exe) != MHLO_OK || !exe)
-        return make_error(PJRT_Error_Code_INTERNAL, std::string(failure_prefix) + mhlo_get_last_error());
     auto* loaded = new PJRT_LoadedExecutable();
     loaded->client = client;
-    loaded->mhlo = exe;
-    loaded->meta = describe(exe, name, text);
+    auto undo = [&](PJRT_Error* e) {
+        for (MHLOExecutableRef x : loaded->replicas) mhlo_executable_destroy(x);
+        delete loaded;
+        return e;
+    };
+    for (size_t r = 0; r < replicas; ++r) {
+        int64_t id = r < options.replica_devices.size() ? options.replica_devices[r] : static_cast<int64_t>(r);
+        if (id < 0 || id >= static_cast<int64_t>(client->devices.size()))
+            return undo(make_error(PJRT_Error_Code_INVALID_ARGUMENT, std::string(failure_prefix) + "device assignment names device " + std::to_string(id)));
+        PJRT_Device* dev = client->devices[static_cast<size_t>(id)];
+        MHLOExecutableRef exe = nullptr;
+        if (mhlo_compile_with_config(dev->mhlo, text.c_str(), &config, &exe) != MHLO_OK || !exe)
+            return undo(make_error(PJRT_Error_Code_INTERNAL, std::string(failure_prefix) + mhlo_get_last_error()));
+        loaded->replicas.push_back(exe);
+        loaded->devices.push_back(dev);
+    }
+    loaded->mhlo = loaded->replicas[0];
+    loaded->meta = describe(loaded->mhlo, name, text);
+    loaded->meta->num_replicas = static_cast<int64_t>(replicas);
     *out = loaded;
     return nullptr;
 }
@@ -96,7 +193,10 @@ PJRT_Error* client_compile(PJRT_Client_Compile_Args* args) {
             std::fclose(f);
         }
     }
-    return compile_text(args->client, text, env_opt_level(), "metalhlo_program", "Compilation failed: ", &args->executable);
+    BuildOptions options;
+    if (!parse_build_options(args->compile_options, args->compile_options_size, &options))
+        return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "Compilation failed: malformed compile options");
+    return compile_text(args->client, text, env_opt_level(), "metalhlo_program", "Compilation failed: ", &args->executable, options);
 }
 
 // ---- PJRT_Executable getters ----
@@ -114,7 +214,7 @@ PJRT_Error* executable_name(PJRT_Executable_Name_Args* args) {
 
 PJRT_Error* executable_num_replicas(PJRT_Executable_NumReplicas_Args* args) {
     PJRT_B200_REQUIRE(args && args->executable, "NULL args");
-    args->num_replicas = 1;
+    args->num_replicas = static_cast<size_t>(args->executable->meta->num_replicas);
     return nullptr;
 }
 
@@ -238,7 +338,7 @@ PJRT_Error* executable_memory_stats(PJRT_Executable_GetCompiledMemoryStats_Args*
 // ---- PJRT_LoadedExecutable ----
 PJRT_Error* loaded_destroy(PJRT_LoadedExecutable_Destroy_Args* args) {
     if (!args || !args->executable) return nullptr;
-    if (args->executable->mhlo) mhlo_executable_destroy(args->executable->mhlo);
+    for (MHLOExecutableRef x : args->executable->replicas) mhlo_executable_destroy(x);
     delete args->executable;
     return nullptr;
 }
@@ -251,8 +351,8 @@ PJRT_Error* loaded_get_executable(PJRT_LoadedExecutable_GetExecutable_Args* args
 
 PJRT_Error* loaded_addressable_devices(PJRT_LoadedExecutable_AddressableDevices_Args* args) {
     PJRT_B200_REQUIRE(args && args->executable, "NULL args");
-    args->addressable_devices = args->executable->client->devices.data();
-    args->num_addressable_devices = args->executable->client->devices.size();
+    args->addressable_devices = args->executable->devices.data();
+    args->num_addressable_devices = args->executable->devices.size();
     return nullptr;
 }
 
@@ -268,45 +368,100 @@ PJRT_Error* loaded_is_deleted(PJRT_LoadedExecutable_IsDeleted_Args* args) {
     return nullptr;
 }
 
-// Single-device, synchronous (PJRTExecutable.swift:2024-2110): inputs from argument_lists[0], fresh output buffers
-// into output_lists[0], and a completion event that is ready on return.
+// Synchronous (PJRTExecutable.swift:2024-2110): replica d takes its inputs from argument_lists[d], writes fresh output
+// buffers into output_lists[d], and its completion event is ready on return. Several replicas run at the same time, one
+// host thread per device (the reference refuses num_devices > 1, PJRTExecutable.swift:2033-2036). With execute_device set,
+// the one argument list runs on that device's replica.
 PJRT_Error* loaded_execute(PJRT_LoadedExecutable_Execute_Args* args) {
     PJRT_B200_REQUIRE(args && args->executable, "NULL args");
     PJRT_LoadedExecutable* loaded = args->executable;
-    if (args->num_devices > 1) return make_error(PJRT_Error_Code_UNIMPLEMENTED, "Multi-device execution not supported");
     if (loaded->deleted) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "Execution failed: executable was deleted");
-    std::vector<MHLOBufferRef> inputs;
-    if (args->num_devices > 0 && args->num_args > 0) {
-        PJRT_B200_REQUIRE(args->argument_lists && args->argument_lists[0], "NULL argument list for device 0");
+    const size_t replicas = loaded->replicas.size();
+    size_t first = 0, count = args->num_devices;
+    if (args->execute_device) {
+        if (args->num_devices != 1) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "Execution failed: execute_device takes one argument list");
+        bool found = false;
+        for (size_t r = 0; r < replicas; ++r)
+            if (loaded->devices[r] == args->execute_device) { first = r; found = true; }
+        if (!found) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "Execution failed: the executable is not loaded on execute_device");
+    } else if (count > replicas) {
+        return make_error(replicas == 1 ? PJRT_Error_Code_UNIMPLEMENTED : PJRT_Error_Code_INVALID_ARGUMENT,
+                          "Multi-device execution not supported: " + std::to_string(count) + " argument lists for " + std::to_string(replicas) +
+                              " replica(s); compile with num_replicas");
+    }
+    if (count == 0) count = 1;
+    std::vector<std::vector<MHLOBufferRef>> inputs(count);
+    for (size_t d = 0; d < count && args->num_devices > 0 && args->num_args > 0; ++d) {
+        PJRT_B200_REQUIRE(args->argument_lists && args->argument_lists[d], "NULL argument list");
         for (size_t i = 0; i < args->num_args; ++i) {
-            PJRT_Buffer* b = args->argument_lists[0][i];
+            PJRT_Buffer* b = args->argument_lists[d][i];
             if (!b) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "NULL buffer at argument index " + std::to_string(i));
             if (!b->mhlo) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "deleted buffer at argument index " + std::to_string(i));
-            inputs.push_back(b->mhlo);
+            if (b->device != loaded->devices[first + d])
+                return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "argument " + std::to_string(i) + " of replica " + std::to_string(first + d) +
+                                                                        " lives on device " + std::to_string(b->device ? b->device->index : -1) +
+                                                                        ", the replica runs on device " + std::to_string(loaded->devices[first + d]->index));
+            inputs[d].push_back(b->mhlo);
         }
     }
-    std::vector<MHLOBufferRef> outputs(loaded->meta->num_outputs, nullptr);
-    int32_t produced = 0;
-    const MHLOStatusCode st = mhlo_execute(loaded->mhlo, inputs.data(), static_cast<int32_t>(inputs.size()), outputs.data(), &produced);
-    if (st != MHLO_OK) return make_error(PJRT_Error_Code_INTERNAL, std::string("Execution failed: ") + mhlo_get_last_error());
-    const bool want_outputs = args->output_lists && args->num_devices > 0 && args->output_lists[0];
-    for (int32_t i = 0; i < produced; ++i) {
-        if (want_outputs) args->output_lists[0][i] = wrap_buffer(loaded->client, outputs[static_cast<size_t>(i)]);
-        else mhlo_buffer_destroy(outputs[static_cast<size_t>(i)]);
+    const size_t n_out = loaded->meta->num_outputs;
+    std::vector<std::vector<MHLOBufferRef>> outputs(count, std::vector<MHLOBufferRef>(n_out, nullptr));
+    std::vector<int32_t> produced(count, 0);
+    std::vector<MHLOStatusCode> status(count, MHLO_OK);
+    std::vector<std::string> messages(count);
+    auto run_one = [&](size_t d) {
+        status[d] = mhlo_execute(loaded->replicas[first + d], inputs[d].data(), static_cast<int32_t>(inputs[d].size()), outputs[d].data(), &produced[d]);
+        if (status[d] != MHLO_OK) {
+            const char* m = mhlo_get_last_error();
+            messages[d] = m ? m : "unknown error";
+        }
+    };
+    if (count == 1) {
+        run_one(0);
+    } else {
+        std::vector<std::thread> workers;
+        for (size_t d = 0; d < count; ++d) workers.emplace_back(run_one, d);
+        for (std::thread& w : workers) w.join();
     }
-    if (args->device_complete_events && args->num_devices > 0) args->device_complete_events[0] = new_ready_event();
+    for (size_t d = 0; d < count; ++d) {
+        if (status[d] == MHLO_OK) continue;
+        for (size_t e = 0; e < count; ++e)
+            for (int32_t i = 0; i < produced[e]; ++i)
+                if (status[e] == MHLO_OK && outputs[e][static_cast<size_t>(i)]) mhlo_buffer_destroy(outputs[e][static_cast<size_t>(i)]);
+        return make_error(PJRT_Error_Code_INTERNAL, "Execution failed" + (count > 1 ? " on replica " + std::to_string(first + d) : std::string()) + ": " + messages[d]);
+    }
+    for (size_t d = 0; d < count; ++d) {
+        const bool want_outputs = args->output_lists && args->num_devices > 0 && args->output_lists[d];
+        for (int32_t i = 0; i < produced[d]; ++i) {
+            if (want_outputs) args->output_lists[d][i] = wrap_buffer(loaded->client, outputs[d][static_cast<size_t>(i)], loaded->devices[first + d]);
+            else mhlo_buffer_destroy(outputs[d][static_cast<size_t>(i)]);
+        }
+        if (args->device_complete_events && args->num_devices > 0) args->device_complete_events[d] = new_ready_event();
+    }
     return nullptr;
 }
 
-// DeviceAssignmentProto for one replica, one computation on device 0 (PJRTExecutable.swift:2112-2145):
-// field 1 (replica_count) = 1, field 2 (computation_count) = 1, field 3 = {field 1 (replica_device_ids) = 0}.
+// DeviceAssignmentProto of the loaded program (PJRTExecutable.swift:2112-2145 writes the one-replica form): field 1
+// replica_count, field 2 computation_count = 1, field 3 = one computation listing the device id of every replica.
 PJRT_Error* loaded_device_assignment(PJRT_LoadedExecutable_GetDeviceAssignment_Args* args) {
-    PJRT_B200_REQUIRE(args, "NULL args");
-    static const unsigned char kProto[] = {0x08, 0x01, 0x10, 0x01, 0x1A, 0x02, 0x08, 0x00};
-    auto* copy = static_cast<unsigned char*>(std::malloc(sizeof kProto));
-    std::memcpy(copy, kProto, sizeof kProto);
+    PJRT_B200_REQUIRE(args && args->executable, "NULL args");
+    std::string comp;
+    for (PJRT_Device* d : args->executable->devices) {
+        comp.push_back(0x08);
+        comp.push_back(static_cast<char>(d->index & 0x7f));  // device ids stay below 128
+    }
+    std::string proto;
+    proto.push_back(0x08);
+    proto.push_back(static_cast<char>(args->executable->devices.size() & 0x7f));
+    proto.push_back(0x10);
+    proto.push_back(0x01);
+    proto.push_back(0x1A);
+    proto.push_back(static_cast<char>(comp.size()));
+    proto += comp;
+    auto* copy = static_cast<unsigned char*>(std::malloc(proto.size()));
+    std::memcpy(copy, proto.data(), proto.size());
     args->serialized_bytes = reinterpret_cast<const char*>(copy);
-    args->serialized_bytes_size = sizeof kProto;
+    args->serialized_bytes_size = proto.size();
     args->serialized_device_assignment = reinterpret_cast<PJRT_DeviceAssignmentSerialized*>(copy);
     args->serialized_device_assignment_deleter = [](PJRT_DeviceAssignmentSerialized* p) { std::free(p); };
     return nullptr;

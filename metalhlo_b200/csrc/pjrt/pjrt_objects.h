@@ -54,7 +54,9 @@ struct PJRT_Memory {
 
 struct PJRT_Device {
     PJRT_Client* client = nullptr;
+    int index = 0;                 // position among the client's devices = PJRT device id = local hardware id
     int cuda_ordinal = 0;
+    MHLOClientRef mhlo = nullptr;  // the C API client bound to this GPU
     PJRT_DeviceDescription description;
     std::vector<PJRT_Memory*> memories;
 };
@@ -66,10 +68,10 @@ struct PJRT_TopologyDescription {
 };
 
 struct PJRT_Client {
-    MHLOClientRef mhlo = nullptr;
+    MHLOClientRef mhlo = nullptr;  // device 0's
     std::string platform_name, platform_version;
-    std::unique_ptr<PJRT_Device> device;
-    std::unique_ptr<PJRT_Memory> memory;
+    std::vector<std::unique_ptr<PJRT_Device>> owned_devices;
+    std::vector<std::unique_ptr<PJRT_Memory>> owned_memories;
     std::vector<PJRT_Device*> devices;
     std::vector<PJRT_Memory*> memories;
     PJRT_TopologyDescription topology;
@@ -78,6 +80,7 @@ struct PJRT_Client {
 
 struct PJRT_Buffer {
     PJRT_Client* client = nullptr;
+    PJRT_Device* device = nullptr;  // where the data lives
     MHLOBufferRef mhlo = nullptr;  // null after PJRT_Buffer_Delete
     PJRT_Buffer_Type type = PJRT_Buffer_Type_INVALID;
     std::vector<int64_t> dims;
@@ -96,6 +99,7 @@ struct ExecutableMeta {
     std::string serialized;   // [u32 version = 1][u64 length][text], built on first use
     std::mutex mu;
     size_t num_outputs = 0;
+    int64_t num_replicas = 1;
     std::vector<PJRT_Buffer_Type> output_types;
     std::vector<int64_t> output_dims;      // all outputs' dims concatenated
     std::vector<size_t> output_dim_sizes;  // rank of each output
@@ -108,9 +112,13 @@ struct PJRT_Executable {
     std::shared_ptr<ExecutableMeta> meta;
 };
 
+// One program loaded on num_replicas devices: replica r runs `replicas[r]` (the same program, compiled by that device's
+// client) on `devices[r]`. The reference loads on its single device only (PJRTExecutable.swift:1830-1848).
 struct PJRT_LoadedExecutable {
     PJRT_Client* client = nullptr;
-    MHLOExecutableRef mhlo = nullptr;
+    MHLOExecutableRef mhlo = nullptr;  // replica 0's
+    std::vector<MHLOExecutableRef> replicas;
+    std::vector<PJRT_Device*> devices;
     std::shared_ptr<ExecutableMeta> meta;
     bool deleted = false;
 };
@@ -128,7 +136,7 @@ bool to_mhlo_type(PJRT_Buffer_Type t, MHLOElementType* out);
 PJRT_Buffer_Type from_mhlo_type(MHLOElementType t);
 size_t storage_bytes_per_element(MHLOElementType t);
 
-PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref);
+PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref, PJRT_Device* device = nullptr);
 std::string hex_hash(const std::string& text);
 
 // Fills every table entry the plugin implements; each group lives in its own translation unit.
