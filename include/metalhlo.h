@@ -154,6 +154,12 @@ MHLOStatusCode mhlo_b200_optimize_text(const char* mlir_text, int32_t optimizati
  * per line (free with mhlo_free_string); out_launches / out_arena_bytes may be NULL. */
 MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_level, char** out_steps,
                                    int32_t* out_launches, int64_t* out_arena_bytes);
+/* MLIR bytecode (magic "ML\xEFR": the VHLO portable artifact JAX hands a plugin) -> StableHLO text. No bytecode reader
+ * is linked; as in the reference (Sources/PJRTMetalHLO/PJRTExecutable.swift:23-239) the interpreter named by
+ * METALHLO_PYTHON runs a jaxlib helper script (METALHLO_BYTECODE_HELPER; default jax_plugins/metalhlo/bytecode_to_text.py
+ * of this package) with the bytecode on stdin and prints the text; METALHLO_HELPER_TIMEOUT_S bounds it. *out_text is
+ * malloc'd (mhlo_free_string). mhlo_compile_n and the PJRT plugin convert bytecode programs the same way. */
+MHLOStatusCode mhlo_b200_bytecode_to_text(const void* bytecode, size_t size, char** out_text);
 /* CUDA devices visible to this process, and a client bound to one of them (mhlo_client_create takes METALHLO_DEVICE /
  * LOCAL_RANK, else device 0). A process may hold one client per GPU; the PJRT plugin does so when it exposes several
  * devices. The reference has one Metal device per client (Sources/MetalHLO/Client.swift). */

@@ -105,6 +105,7 @@ _PROTOTYPES = {
     "mhlo_execute_with_profile": (C.c_int, [_vp, _P(_vp), _i32, _P(_vp), _P(_i32), _P(ExecutionProfile)]),
     "mhlo_b200_optimize_text": (C.c_int, [C.c_char_p, _i32, _P(_vp)]),
     "mhlo_b200_plan_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i32), _P(_i64)]),
+    "mhlo_b200_bytecode_to_text": (C.c_int, [C.c_char_p, _sz, _P(_vp)]),
     "mhlo_b200_device_count": (_i32, []),
     "mhlo_b200_client_create_on_device": (C.c_int, [_i32, _P(_vp)]),
     "mhlo_b200_compile_sharded": (C.c_int, [_vp, C.c_char_p, _P(CompileConfig), _i32, _i32, _P(_i32), _i32, _P(_vp)]),
@@ -157,6 +158,13 @@ def _take_string(ptr) -> str:
     s = C.string_at(ptr).decode()
     lib.mhlo_free_string(ptr)
     return s
+
+
+def bytecode_to_text(bytecode: bytes) -> str:
+    """MLIR bytecode -> StableHLO text through the helper process (host only)."""
+    out = _vp()
+    _check(lib.mhlo_b200_bytecode_to_text(bytecode, len(bytecode), C.byref(out)))
+    return _take_string(out.value)
 
 
 def optimize_text(mlir: str, opt_level: int = 3) -> str:

@@ -359,6 +359,11 @@ MHLOStatusCode mhlo_compile(MHLOClientRef client, const char* mlir_text, MHLOExe
 
 MHLOStatusCode mhlo_compile_n(MHLOClientRef client, const char* mlir_text, size_t mlir_length, MHLOExecutableRef* out_executable) {
     if (!mlir_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "mlir_text is null"));
+    if (is_mlir_bytecode(mlir_text, mlir_length)) {
+        std::string text, why;
+        if (!bytecode_to_text(mlir_text, mlir_length, &text, &why)) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_PARSE_FAILED, why));
+        return compile_impl(static_cast<Client*>(client), text, nullptr, out_executable);
+    }
     return compile_impl(static_cast<Client*>(client), std::string(mlir_text, mlir_length), nullptr, out_executable);
 }
 
@@ -597,6 +602,21 @@ MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_l
     } catch (const std::exception& e) {
         return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
     }
+}
+
+// ---- MLIR bytecode ----
+
+// MLIR bytecode ("ML\xEFR...", what JAX sends) -> StableHLO text through the jaxlib helper process; *out_text is malloc'd
+// (free with mhlo_free_string). mhlo_compile_n accepts bytecode directly and converts it the same way.
+MHLOStatusCode mhlo_b200_bytecode_to_text(const void* bytecode, size_t size, char** out_text) {
+    if (!bytecode || !out_text) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    *out_text = nullptr;
+    if (!is_mlir_bytecode(static_cast<const char*>(bytecode), size))
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "not MLIR bytecode (the magic ML\\xEFR is missing)"));
+    std::string text, why;
+    if (!bytecode_to_text(static_cast<const char*>(bytecode), size, &text, &why)) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_PARSE_FAILED, why));
+    *out_text = strdup(text.c_str());
+    return MHLO_OK;
 }
 
 // ---- batch sharding ------------------------------------------------------------------------------------------------

@@ -70,6 +70,12 @@ bool drop_optimization_barriers(Function& f);
 // All four, repeated until none applies; returns the flattened @main.
 Function flatten_main(Module& m);
 
+// ---- MLIR bytecode (bytecode.cpp) ----
+bool is_mlir_bytecode(const char* data, size_t size);
+// Converts an MLIR bytecode program to StableHLO text by running the jaxlib helper script in a child process
+// (METALHLO_PYTHON, METALHLO_BYTECODE_HELPER, METALHLO_HELPER_TIMEOUT_S). False with a message in *why otherwise.
+bool bytecode_to_text(const char* bytecode, size_t size, std::string* text, std::string* why);
+
 // ---- batch sharding (shard.cpp) ----
 // Proves that every result of f is either the same on every shard or, slice by slice along one axis, a function of the
 // same slice of the split arguments, and rewrites f to compute shard spec.index of spec.count. Throws

@@ -172,20 +172,26 @@ PJRT_Error* compile_text(PJRT_Client* client, const std::string& text, MHLOOptim
     return nullptr;
 }
 
-// The program is StableHLO text. MLIR bytecode (magic "ML\xEFR") is what JAX sends; the reference converts it to text
-// with a jaxlib helper process (PJRTExecutable.swift:1680-1697). No MLIR bytecode reader is linked here, so bytecode
-// is refused with a message that says what to send instead.
+// The program is StableHLO text, or MLIR bytecode (magic "ML\xEFR", what JAX sends), which a jaxlib helper process turns
+// into text first, as in the reference (PJRTExecutable.swift:1680-1697).
 PJRT_Error* client_compile(PJRT_Client_Compile_Args* args) {
     PJRT_B200_REQUIRE(args && args->client, "NULL args or client");
     PJRT_B200_REQUIRE(args->program, "NULL program");
     PJRT_B200_REQUIRE(args->program->code, "NULL program code");
     const char* code = args->program->code;
     const size_t size = args->program->code_size;
+    std::string converted;
     if (size >= 4 && static_cast<unsigned char>(code[0]) == 0x4D && static_cast<unsigned char>(code[1]) == 0x4C &&
-        static_cast<unsigned char>(code[2]) == 0xEF && static_cast<unsigned char>(code[3]) == 0x52)
-        return make_error(PJRT_Error_Code_UNIMPLEMENTED,
-                          "Bytecode conversion failed: this build has no MLIR bytecode reader; pass the module as StableHLO text");
-    const std::string text(code, size);
+        static_cast<unsigned char>(code[2]) == 0xEF && static_cast<unsigned char>(code[3]) == 0x52) {
+        char* out = nullptr;
+        if (mhlo_b200_bytecode_to_text(code, size, &out) != MHLO_OK || !out) {
+            const char* m = mhlo_get_last_error();
+            return make_error(PJRT_Error_Code_INTERNAL, m ? m : "Bytecode conversion failed");
+        }
+        converted = out;
+        mhlo_free_string(out);
+    }
+    const std::string text = converted.empty() ? std::string(code, size) : converted;
     if (const char* dir = std::getenv("METALHLO_DUMP_MLIR")) {
         const std::string path = std::string(dir) + "/mlir_" + hex_hash(text) + ".txt";
         if (FILE* f = std::fopen(path.c_str(), "w")) {
