@@ -567,6 +567,73 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
                         int32_t causal, mhlo_cuda_stream_t stream);
 
+/* ---- dispatch plans ----------------------------------------------------------------------------------------------
+ * The surface a host-side executor binds instead of MTLComputePipelineState / MTLBuffer / compute encoders
+ * (MetalHLOCompiler.compileKernel, Sources/MetalHLOCore/Compiler/MetalHLOCompiler.swift:329-401; IntegratedExecutor,
+ * Runtime/IntegratedExecutor.swift:106-270,390-615). A plan is a list of ops; each names an ahead-of-time kernel of this
+ * library and says where its buffers come from - BufferBinding / BufferSource (Compiler/KernelTypes.swift:77-143) - and
+ * its extents, scalars and launch knobs - the role of DispatchConfig (:12-62).
+ */
+enum { MHLO_CUDA_SRC_NONE = 0, MHLO_CUDA_SRC_INPUT = 1, MHLO_CUDA_SRC_OUTPUT = 2, MHLO_CUDA_SRC_UNIFIED = 3, MHLO_CUDA_SRC_CONSTANT = 4 };
+typedef struct {
+    int32_t source; /* MHLO_CUDA_SRC_*: function input / output number `index`, or `offset` bytes into the plan's arena
+                       (UNIFIED) or constant pool (CONSTANT); NONE = the kernel's optional argument is absent */
+    int32_t index;
+    int64_t offset; /* bytes, added to the input / output pointer as well */
+} mhlo_cuda_binding;
+
+enum {
+    MHLO_CUDA_KERNEL_LAYER_NORM = 1, /* args x, gamma, beta, y; dims rows, hidden; scalars eps; tuning threads, vectors, ctas */
+    MHLO_CUDA_KERNEL_RMS_NORM = 2,   /* args x, gamma, y; dims rows, hidden; scalars eps */
+    MHLO_CUDA_KERNEL_SOFTMAX = 3,    /* args x, y; dims outer, axis_len, inner */
+    MHLO_CUDA_KERNEL_GEMM = 4,       /* args a, b, bias, c; dims batch0, batch1, m, n, k; strides a[4], b[4]; flags epilogue;
+                                        tuning tile_n, stages, cta_group */
+    MHLO_CUDA_KERNEL_ATTENTION = 5,  /* args q, k, v, mask, o; dims batch, heads, seq_q, seq_k, head_dim; strides q[3], k[3],
+                                        v[3], o[3]; scalars scale; flags causal; tuning tile_order */
+    MHLO_CUDA_KERNEL_GELU = 6,       /* args x, y; dims count (tanh approximation) */
+    MHLO_CUDA_KERNEL_SILU = 7        /* args x, y; dims count */
+};
+typedef struct {
+    int32_t kernel; /* MHLO_CUDA_KERNEL_*, e.g. from mhlo_cuda_kernel_lookup */
+    int32_t dtype, out_dtype;
+    mhlo_cuda_binding args[6];
+    int64_t dims[6];
+    int64_t strides[16];
+    float scalars[2];
+    int32_t flags[2];
+    int32_t tuning[4];
+} mhlo_cuda_plan_op;
+typedef void* mhlo_cuda_plan_t;
+
+/* Kernel of a fused-op name as the pass pipeline emits it ("fused_layer_norm", "fused_rms_norm", "fused_softmax",
+ * "fused_gelu", "fused_silu", "fused_matmul_bias_activation", "dot_general", "fused_scaled_dot_product_attention"):
+ * FusedOp.fusedOpTypeFromCustomCall (Compiler/IntegrationTypes.swift:471-600) on the CUDA side. MHLO_CUDA_UNSUPPORTED
+ * when the library has no such kernel for the dtype. */
+int mhlo_cuda_kernel_lookup(const char* fused_op_kind, int32_t dtype, int32_t* out_kernel);
+/* Validates the ops, allocates the arena and uploads the constant pool (either may be empty). The caller owns the plan. */
+int mhlo_cuda_plan_create(const mhlo_cuda_plan_op* ops, int32_t n_ops, int32_t n_inputs, int32_t n_outputs, int64_t arena_bytes,
+                          const void* constants_host, int64_t constant_bytes, mhlo_cuda_plan_t* out_plan);
+/* Enqueues every op in order on `stream`; inputs / outputs are device pointers. No allocation, no synchronisation. */
+int mhlo_cuda_plan_execute(mhlo_cuda_plan_t plan, const void* const* inputs, int32_t n_inputs, void* const* outputs, int32_t n_outputs,
+                           mhlo_cuda_stream_t stream);
+int mhlo_cuda_plan_destroy(mhlo_cuda_plan_t plan);
+/* Median device time of one execution of the plan on the default stream (warmup untimed + iterations timed launches, CUDA
+ * events): the measurement step of the tuner (Tuning/AutoTuner.swift:479-513) for a caller that builds its own candidates. */
+int mhlo_cuda_tuner_measure(mhlo_cuda_plan_t plan, const void* const* inputs, int32_t n_inputs, void* const* outputs, int32_t n_outputs,
+                            int32_t warmup, int32_t iterations, float* out_median_ms);
+
+/* ---- communicator over the GPUs of one process -----------------------------------------------------------------------
+ * The reference has no multi-device path. mhlo_cuda_comm_init(n) joins devices 0 .. n-1 (peer access both ways, one
+ * stream each); mhlo_cuda_all_gather exchanges equal shards: buffers[d] is device d's buffer of n * shard_bytes bytes
+ * whose d-th shard is filled, and on return every buffer holds all n shards. Every device pushes its shard into its
+ * peers' buffers with one kernel of its own over NVLink peer memory (plain 16-byte stores; no library collective). The
+ * call returns when all devices have finished. */
+typedef void* mhlo_cuda_comm_t;
+int mhlo_cuda_comm_init(int32_t n_devices, mhlo_cuda_comm_t* out_comm);
+int mhlo_cuda_comm_size(mhlo_cuda_comm_t comm);
+int mhlo_cuda_all_gather(mhlo_cuda_comm_t comm, void* const* buffers, int64_t shard_bytes);
+int mhlo_cuda_comm_destroy(mhlo_cuda_comm_t comm);
+
 /*
  * Launch knobs of the tensor-core attention kernel (the attention block options of the reference's tuner,
  * Sources/MetalHLOCore/Tuning/AutoTuner.swift:81-103). 0 leaves a knob to the library.

@@ -135,6 +135,15 @@ _PROTOTYPES = {
     "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                  _i32, _vp]),
+    "mhlo_cuda_kernel_lookup": (C.c_int, [C.c_char_p, _i32, C.POINTER(_i32)]),
+    "mhlo_cuda_plan_create": (C.c_int, [_vp, _i32, _i32, _i32, _i64, C.c_char_p, _i64, C.POINTER(_vp)]),
+    "mhlo_cuda_plan_execute": (C.c_int, [_vp, C.POINTER(_vp), _i32, C.POINTER(_vp), _i32, _vp]),
+    "mhlo_cuda_plan_destroy": (C.c_int, [_vp]),
+    "mhlo_cuda_tuner_measure": (C.c_int, [_vp, C.POINTER(_vp), _i32, C.POINTER(_vp), _i32, _i32, _i32, C.POINTER(_f32)]),
+    "mhlo_cuda_comm_init": (C.c_int, [_i32, C.POINTER(_vp)]),
+    "mhlo_cuda_comm_size": (C.c_int, [_vp]),
+    "mhlo_cuda_all_gather": (C.c_int, [_vp, C.POINTER(_vp), _i64]),
+    "mhlo_cuda_comm_destroy": (C.c_int, [_vp]),
     "mhlo_cuda_gemm_tuned": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                        _i32, _vp, _vp]),
     "mhlo_cuda_device_error": (C.c_int, [C.POINTER(_i32)]),
@@ -257,6 +266,61 @@ EPILOGUES = {"none": 0, "relu": 1, "gelu_tanh": 2, "gelu_erf": 3, "silu": 4, "ta
 
 def _i64s(vals):
     return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+class Binding(C.Structure):
+    _fields_ = [("source", C.c_int32), ("index", C.c_int32), ("offset", C.c_int64)]
+
+
+class PlanOp(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("dtype", C.c_int32), ("out_dtype", C.c_int32), ("args", Binding * 6), ("dims", C.c_int64 * 6),
+                ("strides", C.c_int64 * 16), ("scalars", C.c_float * 2), ("flags", C.c_int32 * 2), ("tuning", C.c_int32 * 4)]
+
+
+SRC_NONE, SRC_INPUT, SRC_OUTPUT, SRC_UNIFIED, SRC_CONSTANT = range(5)
+
+
+def plan_op(kernel_name, dtype, args, dims, strides=(), scalars=(), flags=(), tuning=(), out_dtype=None) -> PlanOp:
+    """One op of a dispatch plan. args: (source, index, offset) triples in the kernel's argument order."""
+    k = C.c_int32()
+    check(lib.mhlo_cuda_kernel_lookup(kernel_name.encode(), dtype, C.byref(k)))
+    op = PlanOp()
+    op.kernel, op.dtype, op.out_dtype = k.value, dtype, dtype if out_dtype is None else out_dtype
+    for i, a in enumerate(args):
+        op.args[i] = Binding(*a)
+    for name, vals in (("dims", dims), ("strides", strides), ("scalars", scalars), ("flags", flags), ("tuning", tuning)):
+        arr = getattr(op, name)
+        for i, v in enumerate(vals):
+            arr[i] = v
+    return op
+
+
+class Plan:
+    """mhlo_cuda_plan_*: a list of kernel dispatches with their buffer bindings, an arena and a constant pool."""
+
+    def __init__(self, ops, n_inputs, n_outputs, arena_bytes=0, constants: bytes = b""):
+        arr = (PlanOp * max(len(ops), 1))(*ops)
+        h = C.c_void_p()
+        check(lib.mhlo_cuda_plan_create(arr, len(ops), n_inputs, n_outputs, arena_bytes, constants if constants else None, len(constants), C.byref(h)))
+        self._h = h.value
+
+    def __del__(self):
+        if getattr(self, "_h", None) and lib is not None:
+            lib.mhlo_cuda_plan_destroy(self._h)
+            self._h = None
+
+    def _lists(self, inputs, outputs):
+        return (C.c_void_p * max(len(inputs), 1))(*[_ptr(t) for t in inputs]), (C.c_void_p * max(len(outputs), 1))(*[_ptr(t) for t in outputs])
+
+    def execute(self, inputs, outputs, stream=None):
+        ins, outs = self._lists(inputs, outputs)
+        check(lib.mhlo_cuda_plan_execute(self._h, ins, len(inputs), outs, len(outputs), _stream(stream)))
+
+    def measure(self, inputs, outputs, warmup=5, iterations=20) -> float:
+        ins, outs = self._lists(inputs, outputs)
+        ms = C.c_float()
+        check(lib.mhlo_cuda_tuner_measure(self._h, ins, len(inputs), outs, len(outputs), warmup, iterations, C.byref(ms)))
+        return ms.value
 
 
 class GemmTuning(C.Structure):
