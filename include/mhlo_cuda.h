@@ -213,6 +213,9 @@ enum {
     MHLO_EW_ROUND_TO,  /* r = a rounded to the float dtype (int)imm and widened again: keeps the unfused rounding
                           points of a fused chain */
     MHLO_EW_ERF,       /* chlo.erf */
+    MHLO_EW_REDUCE_PRECISION, /* r = a rounded (to nearest even) to a float format with imm / 64 exponent bits and imm % 64
+                                 mantissa bits, then widened again: overflow gives infinity, underflow zero, NaN stays NaN
+                                 (infinity when the format has no mantissa bits) */
     MHLO_EW_OP_COUNT
 };
 

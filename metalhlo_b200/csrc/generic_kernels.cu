@@ -72,6 +72,35 @@ struct EwParams {
     int64_t out_stride[MHLO_CUDA_MAX_RANK];
 };
 
+// stablehlo.reduce_precision on the bits of a float (8 / 23) or a double (11 / 52): round the mantissa to nearest even at
+// `mant` bits, then clamp the exponent range to `expo` bits (overflow -> infinity, underflow -> signed zero).
+template <typename U, int kExpBits, int kMantBits>
+__device__ __forceinline__ U reduce_precision_bits(U bits, int expo, int mant) {
+    const U one = 1;
+    const U exp_mask = ((one << kExpBits) - 1) << kMantBits, mant_mask = (one << kMantBits) - 1, sign = bits & (one << (kExpBits + kMantBits));
+    const bool is_nan = (bits & exp_mask) == exp_mask && (bits & mant_mask) != 0;
+    if (is_nan) return mant > 0 ? bits : (sign | exp_mask);  // a format without mantissa bits has no NaN: it becomes infinity
+    if (mant < kMantBits) {
+        const U last = one << (kMantBits - mant);
+        const U bias = (last >> 1) - 1 + ((bits & last) >> (kMantBits - mant));
+        bits = (bits + bias) & ~(last - 1);
+    }
+    if (expo < kExpBits) {
+        const long long full_bias = (1ll << (kExpBits - 1)) - 1, reduced_bias = (1ll << (expo - 1)) - 1;
+        const U max_exp = static_cast<U>(full_bias + reduced_bias) << kMantBits, min_exp = static_cast<U>(full_bias - reduced_bias) << kMantBits;
+        const U e = bits & exp_mask;
+        if (e > max_exp) bits = sign | exp_mask;
+        else if (e <= min_exp) bits = sign;
+    }
+    return bits;
+}
+__device__ __forceinline__ float reduce_precision_value(float a, int expo, int mant) {
+    return __uint_as_float(reduce_precision_bits<uint32_t, 8, 23>(__float_as_uint(a), expo, mant));
+}
+__device__ __forceinline__ double reduce_precision_value(double a, int expo, int mant) {
+    return __longlong_as_double(static_cast<long long>(reduce_precision_bits<unsigned long long, 11, 52>(static_cast<unsigned long long>(__double_as_longlong(a)), expo, mant)));
+}
+
 template <typename C>
 __device__ __forceinline__ C ew_float_op(int op, C a, C b, C c, double imm) {
     switch (op) {
@@ -133,6 +162,7 @@ __device__ __forceinline__ C ew_float_op(int op, C a, C b, C c, double imm) {
             return a;
         }
         case MHLO_EW_ERF: return erf(a);
+        case MHLO_EW_REDUCE_PRECISION: return reduce_precision_value(a, static_cast<int>(imm) / 64, static_cast<int>(imm) % 64);
         default: return a;
     }
 }

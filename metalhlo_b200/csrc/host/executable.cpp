@@ -578,6 +578,18 @@ class Lowering {
         if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
+        if (n == "reduce_precision") {
+            // `format = e5m10` in the pretty form, exponent_bits / mantissa_bits in the generic one
+            int64_t e = op.int_attr("exponent_bits", -1), m = op.int_attr("mantissa_bits", -1);
+            const std::string fmt = op.str_attr("format");
+            if (fmt.size() >= 4 && fmt[0] == 'e') {
+                const size_t mpos = fmt.find('m');
+                if (mpos != std::string::npos) { e = std::atoll(fmt.substr(1, mpos - 1).c_str()); m = std::atoll(fmt.substr(mpos + 1).c_str()); }
+            }
+            if (e < 1 || m < 0 || e > 11 || m > 52 || !is_float(rt.dtype)) fail_unsupported("reduce_precision: format e" + std::to_string(e) + "m" + std::to_string(m));
+            mhlo_cuda_ew_inst inst = {MHLO_EW_REDUCE_PRECISION, 0, 0, 0, static_cast<double>(e * 64 + m)};
+            return set(op.results[0], emit_elementwise({get(op.operands[0])}, {inst}, rt, n));
+        }
         const int code = ew_opcode(n);
         if (code >= 0) {
             std::vector<View> ins;

@@ -171,11 +171,14 @@ bool inline_calls(Module& m) {
         std::map<int, int> alias;  // results of removed calls -> the values that replace them
         for (Op& op : main.ops) {
             apply_alias(op, alias);
-            if (op.dead || op.name != "call") {
+            // stablehlo.composite names the private function that implements it: it is a call of that function
+            const bool composite = !op.dead && op.name == "composite" && op.attr("decomposition");
+            if (op.dead || (op.name != "call" && !composite)) {
                 out.push_back(std::move(op));
                 continue;
             }
-            const std::string callee_name = op.str_attr("callee");
+            std::string callee_name = composite ? op.str_attr("decomposition") : op.str_attr("callee");
+            if (!callee_name.empty() && callee_name[0] == '@') callee_name.erase(0, 1);
             const Function* callee = find_function(m, callee_name);
             if (!callee) fail_compile("call to unknown function @" + callee_name);
             if (callee == &main) fail_unsupported("recursive call of @" + callee_name);

@@ -1140,6 +1140,41 @@ class Interpreter:
                 return np.where(big, 0, u >> s.astype(f"uint{bits}")).astype(a[0].dtype)
         raise Unsupported(f"op {n}")
 
+    def op_reduce_precision(self, op, a, t):
+        # stablehlo.reduce_precision: round to nearest even at `m` mantissa bits, then clamp to `e` exponent bits
+        fmt = op.attrs.get("format")
+        if fmt is not None:
+            m_ = re.match(r"e(\d+)m(\d+)", str(fmt if not isinstance(fmt, tuple) else fmt[-1]))
+            e, m = int(m_.group(1)), int(m_.group(2))
+        else:
+            e, m = int(op.attrs["exponent_bits"]), int(op.attrs["mantissa_bits"])
+        x = np.ascontiguousarray(a[0], dtype=np.float64)
+        bits = x.view(np.uint64).copy()
+        sign = bits & np.uint64(1 << 63)
+        exp_mask, mant_mask = np.uint64(0x7FF << 52), np.uint64((1 << 52) - 1)
+        nan = ((bits & exp_mask) == exp_mask) & ((bits & mant_mask) != 0)
+        if m < 52:
+            last = np.uint64(1 << (52 - m))
+            bias = (last >> np.uint64(1)) - np.uint64(1) + ((bits & last) >> np.uint64(52 - m))
+            bits = (bits + bias) & ~(last - np.uint64(1))
+        if e < 11:
+            full, red = 1023, (1 << (e - 1)) - 1
+            ex = bits & exp_mask
+            over, under = ex > np.uint64((full + red) << 52), ex <= np.uint64((full - red) << 52)
+            bits = np.where(over, sign | exp_mask, np.where(under, sign, bits))
+        keep_nan = x.view(np.uint64) if m > 0 else (sign | exp_mask)  # a format without mantissa bits has no NaN
+        out = np.where(nan, keep_nan, bits).astype(np.uint64).view(np.float64)
+        return out.reshape(a[0].shape)
+
+    def op_composite(self, op, a, t):
+        dec = op.attrs.get("decomposition", "")
+        name = str(dec[-1] if isinstance(dec, tuple) else dec).lstrip("@")
+        callee = self.funcs.get(name)
+        if callee is None:
+            raise Unsupported(f"composite without its decomposition @{name}")
+        env = {arg: x for arg, x in zip(callee.args, a)}
+        return self._run_ops(callee.ops, env)
+
     # -- structural ops
     def op_constant(self, op, a, t):
         v = op.attrs.get("value")

@@ -28,7 +28,8 @@ FILES = ["abs", "add", "and", "atan2", "broadcast_in_dim", "cbrt", "ceil", "clam
          "shift_right_logical", "sign", "sine", "slice", "sqrt", "subtract", "tan", "tanh", "transpose", "xor",
          # control flow and the operators either side of the fused path
          "bitcast_convert", "call", "case", "if", "while", "dynamic_broadcast_in_dim", "dynamic_gather", "dynamic_iota",
-         "dynamic_pad", "dynamic_reshape", "optimization_barrier", "reduce_window", "scatter", "sort", "convolution", "select_and_scatter", "map"]
+         "dynamic_pad", "dynamic_reshape", "optimization_barrier", "reduce_window", "scatter", "sort", "convolution", "select_and_scatter", "map",
+         "get_dimension_size", "reduce_precision", "composite"]
 
 
 class Case:
