@@ -189,6 +189,13 @@ MHLOStatusCode mhlo_b200_executable_sharding(MHLOExecutableRef executable, int32
 MHLOStatusCode mhlo_b200_shard_text(const char* mlir_text, int32_t shard_count, int32_t shard_index,
                                     const int32_t* input_axes, int32_t num_input_axes, char** out_text,
                                     int32_t* out_input_axes, int32_t* out_output_axes);
+/* Host-only views of the static memory planner (Sources/MetalHLOCore/Memory/StaticMemoryPlanner.swift:175-253): the
+ * planner alone on n buffers (sizes, inclusive live ranges in steps -> 256-byte aligned arena offsets and the arena size
+ * rounded to 4096), and the plan of a module as lines "bytes first last offset" (free with mhlo_free_string). */
+MHLOStatusCode mhlo_b200_plan_intervals(const int64_t* bytes, const int32_t* first, const int32_t* last, int32_t n,
+                                        int64_t* out_offsets, int64_t* out_total);
+MHLOStatusCode mhlo_b200_plan_memory_text(const char* mlir_text, int32_t optimization_level, char** out_lines,
+                                          int64_t* out_arena_bytes);
 /* StableHLO text after the pass pipeline; free with mhlo_free_string. */
 char* mhlo_b200_executable_optimized_text(MHLOExecutableRef executable);
 /* Kernel launches one execution enqueues. */

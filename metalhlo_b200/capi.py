@@ -105,6 +105,8 @@ _PROTOTYPES = {
     "mhlo_execute_with_profile": (C.c_int, [_vp, _P(_vp), _i32, _P(_vp), _P(_i32), _P(ExecutionProfile)]),
     "mhlo_b200_optimize_text": (C.c_int, [C.c_char_p, _i32, _P(_vp)]),
     "mhlo_b200_plan_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i32), _P(_i64)]),
+    "mhlo_b200_plan_intervals": (C.c_int, [_P(_i64), _P(_i32), _P(_i32), _i32, _P(_i64), _P(_i64)]),
+    "mhlo_b200_plan_memory_text": (C.c_int, [C.c_char_p, _i32, _P(_vp), _P(_i64)]),
     "mhlo_b200_bytecode_to_text": (C.c_int, [C.c_char_p, _sz, _P(_vp)]),
     "mhlo_b200_device_count": (_i32, []),
     "mhlo_b200_client_create_on_device": (C.c_int, [_i32, _P(_vp)]),
@@ -158,6 +160,22 @@ def _take_string(ptr) -> str:
     s = C.string_at(ptr).decode()
     lib.mhlo_free_string(ptr)
     return s
+
+
+def plan_intervals(sizes, firsts, lasts):
+    """The static memory planner alone: (offsets, arena bytes) for buffers with the given sizes and inclusive live ranges."""
+    n = len(sizes)
+    offs, total = (_i64 * max(n, 1))(), _i64()
+    _check(lib.mhlo_b200_plan_intervals((_i64 * max(n, 1))(*sizes), (_i32 * max(n, 1))(*firsts), (_i32 * max(n, 1))(*lasts), n, offs, C.byref(total)))
+    return list(offs)[:n], total.value
+
+
+def plan_memory(mlir: str, opt_level: int = 3):
+    """Arena plan of a module: ([(bytes, first step, last step, offset)], arena bytes). Host only."""
+    out, arena = _vp(), _i64()
+    _check(lib.mhlo_b200_plan_memory_text(mlir.encode(), opt_level, C.byref(out), C.byref(arena)))
+    rows = [tuple(int(x) for x in line.split()) for line in _take_string(out.value).splitlines() if line.strip()]
+    return rows, arena.value
 
 
 def bytecode_to_text(bytecode: bytes) -> str:

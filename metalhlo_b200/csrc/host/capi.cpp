@@ -604,6 +604,48 @@ MHLOStatusCode mhlo_b200_plan_text(const char* mlir_text, int32_t optimization_l
     }
 }
 
+// ---- static memory plan, for inspection ----
+
+// Host-only: the planner alone. n buffers with sizes and inclusive live ranges [first, last] in steps; out_offsets receives
+// the arena offset of each and *out_total the arena size (StaticMemoryPlanner.plan, Memory/StaticMemoryPlanner.swift:175-253).
+MHLOStatusCode mhlo_b200_plan_intervals(const int64_t* bytes, const int32_t* first, const int32_t* last, int32_t n, int64_t* out_offsets,
+                                        int64_t* out_total) {
+    if (n < 0 || (n > 0 && (!bytes || !first || !last || !out_offsets)) || !out_total)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    std::vector<PlanInterval> ivs(static_cast<size_t>(n));
+    for (int32_t i = 0; i < n; ++i) {
+        if (bytes[i] < 0 || first[i] > last[i]) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "negative size or empty live range"));
+        ivs[static_cast<size_t>(i)].bytes = bytes[i];
+        ivs[static_cast<size_t>(i)].first = first[i];
+        ivs[static_cast<size_t>(i)].last = last[i];
+    }
+    *out_total = plan_memory(&ivs);
+    for (int32_t i = 0; i < n; ++i) out_offsets[i] = ivs[static_cast<size_t>(i)].offset;
+    return MHLO_OK;
+}
+
+// Host-only: the arena plan of a module: one line "bytes first last offset" per intermediate buffer (malloc'd; free with
+// mhlo_free_string), *out_arena_bytes the planned arena.
+MHLOStatusCode mhlo_b200_plan_memory_text(const char* mlir_text, int32_t optimization_level, char** out_lines, int64_t* out_arena_bytes) {
+    if (!mlir_text || !out_lines) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "null argument"));
+    *out_lines = nullptr;
+    try {
+        CompileOptions opt;
+        opt.opt_level = optimization_level;
+        std::unique_ptr<Executable> exe = Executable::plan_only(mlir_text, opt);
+        std::string s;
+        for (const PlanInterval& p : exe->plan_intervals())
+            s += std::to_string(p.bytes) + " " + std::to_string(p.first) + " " + std::to_string(p.last) + " " + std::to_string(p.offset) + "\n";
+        *out_lines = strdup(s.c_str());
+        if (out_arena_bytes) *out_arena_bytes = exe->arena_bytes();
+        return MHLO_OK;
+    } catch (const CompileError& e) {
+        return static_cast<MHLOStatusCode>(set_error(e.code, e.what()));
+    } catch (const std::exception& e) {
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_COMPILATION_FAILED, e.what()));
+    }
+}
+
 // ---- MLIR bytecode ----
 
 // MLIR bytecode ("ML\xEFR...", what JAX sends) -> StableHLO text through the jaxlib helper process; *out_text is malloc'd

@@ -127,6 +127,7 @@ class Executable {
     const std::vector<PassRecord>& pass_log() const { return pass_log_; }
     const std::string& optimized_text() const { return optimized_text_; }
     const ShardPlan& shard_plan() const { return shard_plan_; }
+    const std::vector<PlanInterval>& plan_intervals() const { return plan_intervals_; }  // the arena buffers as planned
     std::vector<std::string> step_labels() const;
     ExecutionStats stats;
 
@@ -154,6 +155,7 @@ class Executable {
     std::vector<PassRecord> pass_log_;
     std::string optimized_text_;
     ShardPlan shard_plan_;
+    std::vector<PlanInterval> plan_intervals_;
     std::string error_;
 
     // CUDA-graph replay of the launch list. A (stream, input pointers, output pointers) combination that comes back

@@ -1749,6 +1749,7 @@ void Lowering::plan() {
     if (no_reuse)
         for (PlanInterval& p : ivs) { p.first = 0; p.last = step_index(); }
     exe_->arena_bytes_ = plan_memory(&ivs);
+    exe_->plan_intervals_ = ivs;
     for (size_t k = 0; k < ids.size(); ++k) buffers_[ids[k]].offset = ivs[k].offset;
     *table_ = buffers_;
 }
