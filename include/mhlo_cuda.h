@@ -402,7 +402,9 @@ int mhlo_cuda_scatter(void* result_inout_dev, int32_t dtype, const int64_t* oper
  * stablehlo.sort along one dimension by the first operand, the other operands carried along (argsort passes an
  * iota as the second operand). All n_operands tensors share `shape` (contiguous); operand i has dtypes[i] and is
  * written sorted to outs_dev[i] (must not alias the inputs). Ascending or descending order of the key under the
- * total order -NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN; the sort is always stable. Slices of up to
+ * total order -NaN < -inf < .. < -0 < +0 < .. < +inf < +NaN; the sort is always stable. `descending` is a set of
+ * flags: bit 0 = descending; bit 1 = -0 and +0 compare equal and keep the order they came in (a comparator that
+ * compares with FLOAT semantics instead of TOTALORDER). Slices of up to
  * MHLO_CUDA_SORT_SMEM_MAX keys are sorted in shared memory by one CTA each; longer ones use `scratch_dev`
  * (mhlo_cuda_sort_scratch_bytes() bytes) for a bitonic network over global memory. Replaces argSort +
  * gatherAlongAxis (MPSGraphCompiler.swift:3599-3613).

@@ -168,17 +168,19 @@ MHLOStatusCode run(ExecutableHandle* h, const MHLOBufferRef* inputs, int32_t num
     const bool timed = gpu_s != nullptr;
     if (timed) { mhlo_cuda_event_create(&ev0); mhlo_cuda_event_create(&ev1); mhlo_cuda_event_record(ev0, c->stream); }
     int st;
+    bool words = false;
+    std::chrono::steady_clock::time_point t1;
     {
-        std::lock_guard<std::mutex> lock(c->mu);  // one program at a time per client stream and arena
+        std::lock_guard<std::mutex> lock(c->mu);  // one caller at a time on the client's stream and arena, until the stream has drained
         st = exe.execute(in_ptrs.data(), out_ptrs.data(), c->stream);
+        t1 = std::chrono::steady_clock::now();
+        if (timed) mhlo_cuda_event_record(ev1, c->stream);
+        // The tensor-core kernels bound every wait and record a code instead of hanging; the words ride back behind the
+        // program on the same stream, so a kernel that gave up fails this call instead of returning partly written outputs.
+        words = st == 0 && mhlo_cuda_device_error_fetch(c->stream) == 0;
+        if (st == 0 && mhlo_cuda_stream_sync(c->stream) != 0) { st = MHLO_ERROR_EXECUTION_FAILED; set_error(st, mhlo_cuda_last_error()); }
+        else if (st != 0) set_error(st, exe.last_error());
     }
-    const auto t1 = std::chrono::steady_clock::now();
-    if (timed) mhlo_cuda_event_record(ev1, c->stream);
-    // The tensor-core kernels bound every wait and record a code instead of hanging; the words ride back behind the
-    // program on the same stream, so a kernel that gave up fails this call instead of returning partly written outputs.
-    const bool words = st == 0 && mhlo_cuda_device_error_fetch(c->stream) == 0;
-    if (st == 0 && mhlo_cuda_stream_sync(c->stream) != 0) { st = MHLO_ERROR_EXECUTION_FAILED; set_error(st, mhlo_cuda_last_error()); }
-    else if (st != 0) set_error(st, exe.last_error());
     if (st == 0 && words) {
         int32_t code = 0;
         if (mhlo_cuda_device_error_take(&code) != 0 && code != 0) {
@@ -451,7 +453,12 @@ MHLOStatusCode mhlo_buffer_create(MHLOClientRef client, const void* data, size_t
     Buffer* b = nullptr;
     MHLOStatusCode st = make_buffer(c, t, &b);
     if (st != MHLO_OK) return st;
-    if (need > 0 && (mhlo_cuda_upload(b->dev, data, need, c->stream) != 0 || mhlo_cuda_stream_sync(c->stream) != 0)) {
+    bool copied = true;
+    if (need > 0) {
+        std::lock_guard<std::mutex> lock(c->mu);  // the client's stream is used by one caller at a time (an execution may be capturing on it)
+        copied = mhlo_cuda_upload(b->dev, data, need, c->stream) == 0 && mhlo_cuda_stream_sync(c->stream) == 0;
+    }
+    if (!copied) {
         set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error());
         mhlo_cuda_free(b->dev);
         delete b;
@@ -478,7 +485,10 @@ MHLOStatusCode mhlo_buffer_create_uninitialized(MHLOClientRef client, const int6
     Buffer* b = nullptr;
     MHLOStatusCode st = make_buffer(c, t, &b);
     if (st != MHLO_OK) return st;
-    if (b->bytes) mhlo_cuda_memset(b->dev, 0, b->bytes, c->stream);  // the reference's fresh MTLBuffers read as zero
+    if (b->bytes) {
+        std::lock_guard<std::mutex> lock(c->mu);
+        mhlo_cuda_memset(b->dev, 0, b->bytes, c->stream);  // the reference's fresh MTLBuffers read as zero
+    }
     *out_buffer = b;
     return MHLO_OK;
 }
@@ -487,7 +497,10 @@ void mhlo_buffer_destroy(MHLOBufferRef buffer) {
     Buffer* b = static_cast<Buffer*>(buffer);
     if (!b) return;
     mhlo_cuda_device_set(b->client->device);
-    mhlo_cuda_stream_sync(b->client->stream);
+    {
+        std::lock_guard<std::mutex> lock(b->client->mu);
+        mhlo_cuda_stream_sync(b->client->stream);
+    }
     pool_release(b->client, b->dev, b->bytes);
     delete b;
 }
@@ -515,9 +528,13 @@ MHLOStatusCode mhlo_buffer_to_host(MHLOBufferRef buffer, void* out_data, size_t 
         return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, "Output buffer too small: need " + std::to_string(b->bytes) +
                                                      ", got " + std::to_string(data_size)));
     if (b->bytes == 0) return MHLO_OK;
-    if (mhlo_cuda_device_set(b->client->device) != 0 || mhlo_cuda_download(out_data, b->dev, b->bytes, b->client->stream) != 0 ||
-        mhlo_cuda_stream_sync(b->client->stream) != 0)
-        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error()));
+    bool ok;
+    {
+        std::lock_guard<std::mutex> lock(b->client->mu);
+        ok = mhlo_cuda_device_set(b->client->device) == 0 && mhlo_cuda_download(out_data, b->dev, b->bytes, b->client->stream) == 0 &&
+             mhlo_cuda_stream_sync(b->client->stream) == 0;
+    }
+    if (!ok) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error()));
     return MHLO_OK;
 }
 

@@ -772,6 +772,10 @@ class Lowering {
         const bool arg = kind == MHLO_REDUCE_ARGMAX || kind == MHLO_REDUCE_ARGMIN;
         if ((arg && n_in != 2) || (!arg && n_in != 1)) fail_unsupported("variadic reduce other than the argmax/argmin form");
         const View& x = get(op.operands[0]);
+        // the reduce kernels accumulate every integer type in a signed 64-bit register: sums, products and bitwise reducers
+        // wrap correctly, but an ordering of ui64 values at or above 2^63 would come out wrong
+        if (x.type.dtype == DType::UI64 && (kind == MHLO_REDUCE_MAX || kind == MHLO_REDUCE_MIN || arg))
+            fail_unsupported("reduce: maximum / minimum / argmax / argmin over ui64 is outside this backend's operator surface");
         std::vector<int64_t> dims = op.int_list("dimensions");
         std::vector<bool> reduced(x.type.rank(), false);
         for (int64_t d : dims) reduced[d] = true;
@@ -1372,7 +1376,7 @@ class Lowering {
         }
         DevView dscratch;
         if (has_scratch) { dscratch = dev(scratch); keep_alive(scratch); }
-        const int descending = order == "descending" ? 1 : 0;
+        const int descending = (order == "descending" ? 1 : 0) | (op.str_attr("sort_compare_type") == "FLOAT" ? 2 : 0);
         int launches = 1;
         if (has_scratch) {  // keys, chunk sort, then per merge size its global stages and one chunk merge, apply
             int64_t padded = 1;

@@ -1225,6 +1225,14 @@ class Parser {
                 const bool swapped = c.operands[0] == r.args[1] && c.operands[1] == r.args[0];
                 if ((dir == "LT" || dir == "GT") && (straight || swapped))
                     order = ((dir == "LT") == straight) ? "ascending" : "descending";
+                // the comparison type decides how zeros and the sign of integers are read: FLOAT holds -0 = +0, TOTALORDER
+                // orders them; SIGNED / UNSIGNED must agree with the key's element type
+                const std::string ctype = c.str_attr("compare_type");
+                const DType kd = fn_->values[r.args[0]].type.dtype;
+                if (ctype == "SIGNED" && (is_unsigned(kd) || is_float(kd))) order = "unknown";
+                if (ctype == "UNSIGNED" && !(is_unsigned(kd) || kd == DType::I1)) order = "unknown";
+                if (ctype == "TOTALORDER" && !is_float(kd)) order = "unknown";
+                op->attrs["sort_compare_type"] = Attr::make_string(ctype.empty() && is_float(kd) ? "FLOAT" : ctype);
             }
             op->attrs["sort_order"] = Attr::make_string(order);
         }

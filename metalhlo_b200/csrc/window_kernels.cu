@@ -602,7 +602,8 @@ __device__ __forceinline__ uint64_t order_key(E v) {
     }
 }
 
-__device__ __forceinline__ uint64_t load_order_key(const void* base, int dtype, int64_t off, bool descending) {
+__device__ __forceinline__ uint64_t load_order_key(const void* base, int dtype, int64_t off, int flags) {
+    const bool descending = (flags & 1) != 0, zeros_equal = (flags & 2) != 0;
     uint64_t k = 0;
     switch (dtype) {
         case MHLO_DT_F32: k = order_key(static_cast<const float*>(base)[off]); break;
@@ -617,6 +618,11 @@ __device__ __forceinline__ uint64_t load_order_key(const void* base, int dtype, 
         case MHLO_DT_I64: k = order_key(static_cast<const int64_t*>(base)[off]); break;
         case MHLO_DT_UI64: k = order_key(static_cast<const uint64_t*>(base)[off]); break;
         default: k = order_key(static_cast<const uint8_t*>(base)[off]); break;  // I1, UI8
+    }
+    // a FLOAT comparison holds -0 and +0 equal (the stable order then keeps them as they came): both take +0's key
+    if (zeros_equal) {
+        if (dtype == MHLO_DT_F64) { if (k == 0x7fffffffffffffffull) k = 0x8000000000000000ull; }
+        else if ((dtype == MHLO_DT_F32 || dtype == MHLO_DT_F16 || dtype == MHLO_DT_BF16) && k == 0x7fffffffull) k = 0x80000000ull;
     }
     return descending ? ~k : k;
 }
@@ -654,7 +660,8 @@ __device__ __forceinline__ void bitonic_stages(uint64_t* keys, uint32_t* order, 
 
 // Keys of at most 32 bits: the pair (key, position) packs into one 64-bit word, key in the upper half, so a
 // compare-exchange is one comparison and the network moves 8 bytes per element instead of 12.
-__device__ __forceinline__ uint32_t load_order_key32(const void* base, int dtype, int64_t off, bool descending) {
+__device__ __forceinline__ uint32_t load_order_key32(const void* base, int dtype, int64_t off, int flags) {
+    const bool descending = (flags & 1) != 0, zeros_equal = (flags & 2) != 0;
     uint32_t k = 0;
     switch (dtype) {
         case MHLO_DT_F32: k = static_cast<uint32_t>(order_key(static_cast<const float*>(base)[off])); break;
@@ -667,6 +674,7 @@ __device__ __forceinline__ uint32_t load_order_key32(const void* base, int dtype
         case MHLO_DT_UI32: k = static_cast<const uint32_t*>(base)[off]; break;
         default: k = static_cast<const uint8_t*>(base)[off]; break;  // I1, UI8
     }
+    if (zeros_equal && (dtype == MHLO_DT_F32 || dtype == MHLO_DT_F16 || dtype == MHLO_DT_BF16) && k == 0x7fffffffu) k = 0x80000000u;
     return descending ? ~k : k;
 }
 
@@ -690,7 +698,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_slices_packed_kernel(const 
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const int64_t base = slice_base(p, row);
         for (int i = threadIdx.x; i < padded; i += blockDim.x)
-            v[i] = i < p.n ? (static_cast<uint64_t>(load_order_key32(p.in[0], p.key_dtype, base + i * p.inner, p.descending != 0)) << 32) | static_cast<uint32_t>(i)
+            v[i] = i < p.n ? (static_cast<uint64_t>(load_order_key32(p.in[0], p.key_dtype, base + i * p.inner, p.descending)) << 32) | static_cast<uint32_t>(i)
                            : ~0ull;
         __syncthreads();
         for (int k = 2; k <= padded; k <<= 1) bitonic_stages_packed(v, padded, k, k >> 1);
@@ -711,7 +719,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_slices_kernel(const __grid_
         const int64_t base = slice_base(p, row);
         for (int i = threadIdx.x; i < padded; i += blockDim.x) {
             const bool real = i < p.n;
-            keys[i] = real ? load_order_key(p.in[0], p.key_dtype, base + i * p.inner, p.descending != 0) : ~0ull;
+            keys[i] = real ? load_order_key(p.in[0], p.key_dtype, base + i * p.inner, p.descending) : ~0ull;
             order[i] = real ? static_cast<uint32_t>(i) : 0xffffffffu;
         }
         __syncthreads();
@@ -729,7 +737,7 @@ __global__ void __launch_bounds__(256) sort_init_kernel(const __grid_constant__ 
     for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += step) {
         const int64_t row = g / p.padded, i = g % p.padded;
         const bool real = i < p.n;
-        p.keys[g] = real ? load_order_key(p.in[0], p.key_dtype, slice_base(p, row) + i * p.inner, p.descending != 0) : ~0ull;
+        p.keys[g] = real ? load_order_key(p.in[0], p.key_dtype, slice_base(p, row) + i * p.inner, p.descending) : ~0ull;
         p.order[g] = real ? static_cast<uint32_t>(i) : 0xffffffffu;
     }
 }
@@ -992,7 +1000,7 @@ extern "C" int mhlo_cuda_sort(const void* const* operands_dev, void* const* outs
     if (p.rows * p.n == 0) return MHLO_CUDA_OK;
     p.n_operands = n_operands;
     p.key_dtype = dtypes[0];
-    p.descending = descending ? 1 : 0;
+    p.descending = descending & 3;  // bit 0: descending; bit 1: -0 and +0 compare equal (a FLOAT comparison)
     p.padded = next_pow2(p.n);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t pair_bytes = sizeof(uint64_t) + sizeof(uint32_t);

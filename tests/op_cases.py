@@ -664,12 +664,13 @@ def scatter_case(name, operand, indices, updates, dt, kind, dims, idt="i32"):
     return (name, func([t_op, t_idx, t_upd], [t_op], body, "%0"), [operand, indices, updates])
 
 
-def sort_case(name, arrays, dts, dimension, direction="LT", swapped=False):
+def sort_case(name, arrays, dts, dimension, direction="LT", swapped=False, compare_type=None):
     """stablehlo.sort of len(arrays) operands by the first one, the comparator a single compare as jax.lax.sort prints."""
     types = [tt(a.shape, dt) for a, dt in zip(arrays, dts)]
     block = ", ".join(f"%l{i}: tensor<{dt}>, %r{i}: tensor<{dt}>" for i, dt in enumerate(dts))
     lhs, rhs = ("%r0", "%l0") if swapped else ("%l0", "%r0")
     ctype = "TOTALORDER" if dts[0] in ("f32", "f16", "bf16", "f64") else ("UNSIGNED" if dts[0].startswith("ui") else "SIGNED")
+    ctype = compare_type or ctype
     args = ", ".join(f"%arg{i}" for i in range(len(arrays)))
     results = ", ".join(f"%0#{i}" for i in range(len(arrays))) if len(arrays) > 1 else "%0"
     lhs_bind = f"%0:{len(arrays)}" if len(arrays) > 1 else "%0"
@@ -843,6 +844,13 @@ def window_scatter_sort_cases():
     out.append(sort_case("sort_i32_dim0_descending", [m], ["i32"], 0, direction="GT"))
     ties = rng.integers(0, 6, size=(4, 100)).astype(np.float32)
     iota = np.broadcast_to(np.arange(100, dtype=np.int32), (4, 100)).copy()
+    # signed zeros: a FLOAT comparison holds them equal (the stable order keeps them as they came), TOTALORDER puts -0 first
+    zeros = np.array([[0.0, -0.0, 1.0, -0.0, 0.0, -1.0, -0.0, 0.0]], dtype=np.float32)
+    zpos = np.arange(8, dtype=np.int32).reshape(1, 8)
+    for ctype in ("FLOAT", "TOTALORDER"):
+        out.append(sort_case(f"argsort_signed_zeros_{ctype.lower()}", [zeros, zpos], ["f32", "i32"], 1, compare_type=ctype))
+        out.append(sort_case(f"argsort_signed_zeros_{ctype.lower()}_descending", [zeros, zpos], ["f32", "i32"], 1, direction="GT", compare_type=ctype))
+    out.append(sort_case("argsort_signed_zeros_bf16_float", [zeros.astype(NP["bf16"]), zpos], ["bf16", "i32"], 1, compare_type="FLOAT"))
     out.append(sort_case("argsort_stable_ties", [ties, iota], ["f32", "i32"], 1))
     out.append(sort_case("argsort_stable_ties_descending", [ties, iota], ["f32", "i32"], 1, direction="GT"))
     for dt in ("bf16", "ui8", "i64", "f64", "f16", "i8", "ui32"):
