@@ -572,6 +572,21 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
                         int32_t causal, mhlo_cuda_stream_t stream);
 
+/* ---- dense factorisations and solves (jax.numpy.linalg) -----------------------------------------------------------
+ * stablehlo.cholesky: a_dev holds `batch` symmetric positive-definite n x n matrices; out_dev receives the factor L
+ * (lower != 0: A = L L^T, L lower triangular) or U (A = U^T U), the other triangle set to zero. A matrix that is not
+ * positive definite gives NaN. out_dev must not alias a_dev.
+ * stablehlo.triangular_solve: solves op(a) X = b (left_side != 0; b and X are [batch, m, n]) or X op(a) = b (b and X are
+ * [batch, n, m]) for the m x m triangular matrices a (`lower` says which triangle is read; the other is ignored),
+ * op = identity, or transpose when transpose_a != 0; unit_diagonal != 0 takes the diagonal as ones.
+ * f32 / f16 / bf16 compute in fp32, f64 in fp64. Correctness kernels, O(n^3) on one CTA per matrix; the reference lowers
+ * both operators through MPSGraph (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift). */
+int mhlo_cuda_cholesky(int32_t dtype, const void* a_dev, void* out_dev, int64_t batch, int64_t n, int32_t lower,
+                       mhlo_cuda_stream_t stream);
+int mhlo_cuda_triangular_solve(int32_t dtype, const void* a_dev, const void* b_dev, void* out_dev, int64_t batch, int64_t m,
+                               int64_t n, int32_t left_side, int32_t lower, int32_t unit_diagonal, int32_t transpose_a,
+                               mhlo_cuda_stream_t stream);
+
 /* ---- dispatch plans ----------------------------------------------------------------------------------------------
  * The surface a host-side executor binds instead of MTLComputePipelineState / MTLBuffer / compute encoders
  * (MetalHLOCompiler.compileKernel, Sources/MetalHLOCore/Compiler/MetalHLOCompiler.swift:329-401; IntegratedExecutor,

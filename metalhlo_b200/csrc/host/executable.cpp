@@ -575,6 +575,8 @@ class Lowering {
         if (n == "dynamic_slice") return lower_dynamic_slice(op);
         if (n == "dynamic_update_slice") return lower_dynamic_update_slice(op);
         if (n == "custom_call") return lower_custom_call(op);
+        if (n == "cholesky") return lower_cholesky(op);
+        if (n == "triangular_solve") return lower_triangular_solve(op);
         if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
             n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
@@ -1334,6 +1336,63 @@ class Lowering {
             return mhlo_cuda_scatter(const_cast<void*>(bind(dout, c).base), static_cast<int>(ot.dtype), ot.shape.data(), ot.rank(), bind(din, c).base,
                                      static_cast<int>(it_.dtype), it_.shape.data(), it_.rank(), bind(dup, c).base, ut.shape.data(), ut.rank(), &g,
                                      mode, c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.cholesky: [..., n, n] -> the lower (or upper) factor, other triangle zero.
+    void lower_cholesky(const Op& op) {
+        if (op.operands.size() != 1) fail_compile("cholesky takes one operand");
+        View a = materialize(get(op.operands[0]), "cholesky.operand");
+        const TensorType& t = a.type;
+        if (t.rank() < 2 || t.shape[t.rank() - 1] != t.shape[t.rank() - 2] || !is_float(t.dtype)) fail_unsupported("cholesky of " + t.str());
+        const int64_t n = t.shape[t.rank() - 1], batch = n ? t.count() / (n * n) : 0;
+        const Attr* la = op.attr("lower");
+        const int lower = la ? (la->kind == Attr::Bool ? la->b : la->i != 0) : 0;  // the specification's default is false
+        View out = dense_view(new_arena(t.bytes()), op.result_types[0]);
+        DevView da = dev(a), dout = dev(out);
+        keep_alive(a); keep_alive(out);
+        const int dt = static_cast<int>(t.dtype);
+        add_step("cholesky", [=](const Ctx& c) {
+            return mhlo_cuda_cholesky(dt, bind(da, c).base, const_cast<void*>(bind(dout, c).base), batch, n, lower, c.stream);
+        });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.triangular_solve: op(a) x = b or x op(a) = b with a [..., m, m] triangular.
+    void lower_triangular_solve(const Op& op) {
+        if (op.operands.size() != 2) fail_compile("triangular_solve takes two operands");
+        View a = materialize(get(op.operands[0]), "triangular_solve.a"), b = materialize(get(op.operands[1]), "triangular_solve.b");
+        const TensorType& at = a.type;
+        const TensorType& bt = b.type;
+        if (at.rank() < 2 || bt.rank() != at.rank() || at.shape[at.rank() - 1] != at.shape[at.rank() - 2] || !is_float(at.dtype) || bt.dtype != at.dtype)
+            fail_unsupported("triangular_solve of " + at.str() + " and " + bt.str());
+        auto flag = [&](const char* key) {
+            const Attr* x = op.attr(key);
+            return x ? (x->kind == Attr::Bool ? (x->b ? 1 : 0) : (x->i != 0 ? 1 : 0)) : 0;
+        };
+        const int left_side = flag("left_side"), lower = flag("lower"), unit = flag("unit_diagonal");
+        std::string tr = op.str_attr("transpose_a", "NO_TRANSPOSE");
+        if (const Attr* ta = op.attr("transpose_a"))  // #stablehlo<transpose TRANSPOSE> arrives as a dictionary or keyword list
+            if (tr.empty() || tr == "NO_TRANSPOSE")
+                for (const Attr& e : ta->elems)
+                    if (e.kind == Attr::Keyword || e.kind == Attr::String) tr = e.s;
+        int transpose = 0;
+        if (tr.find("NO_TRANSPOSE") != std::string::npos) transpose = 0;
+        else if (tr.find("TRANSPOSE") != std::string::npos || tr.find("ADJOINT") != std::string::npos) transpose = 1;  // real types: the adjoint is the transpose
+        else fail_unsupported("triangular_solve: transpose_a = " + tr);
+        const int64_t m = at.shape[at.rank() - 1];
+        const int64_t n = left_side ? bt.shape[bt.rank() - 1] : bt.shape[bt.rank() - 2];
+        if ((left_side ? bt.shape[bt.rank() - 2] : bt.shape[bt.rank() - 1]) != m) fail_compile("triangular_solve: the shapes of a and b do not agree");
+        const int64_t batch = m ? at.count() / (m * m) : 0;
+        if (batch * m * n != bt.count()) fail_compile("triangular_solve: batch dimensions of a and b differ");
+        View out = dense_view(new_arena(bt.bytes()), op.result_types[0]);
+        DevView da = dev(a), db = dev(b), dout = dev(out);
+        keep_alive(a); keep_alive(b); keep_alive(out);
+        const int dt = static_cast<int>(at.dtype);
+        add_step("triangular_solve", [=](const Ctx& c) {
+            return mhlo_cuda_triangular_solve(dt, bind(da, c).base, bind(db, c).base, const_cast<void*>(bind(dout, c).base), batch, m, n, left_side, lower,
+                                              unit, transpose, c.stream);
         });
         set(op.results[0], out);
     }

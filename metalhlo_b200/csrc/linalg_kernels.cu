@@ -1,0 +1,146 @@
+// stablehlo.cholesky and stablehlo.triangular_solve: small dense factorisations and solves as jax.numpy.linalg emits them.
+// One CTA per matrix (Cholesky) or per block of right-hand sides (triangular solve); fp32 arithmetic for f32 / f16 / bf16
+// tensors, fp64 for f64. These are correctness kernels for matrices of up to a few thousand rows, not tuned: the work is
+// O(n^3) with one column (or one substitution step) after the other. The reference lowers both through MPSGraph
+// (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift), a route this backend does not have.
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace mhlo {
+namespace {
+
+template <typename T> struct Compute { using type = float; };
+template <> struct Compute<double> { using type = double; };
+
+template <typename T> __device__ __forceinline__ typename Compute<T>::type ld(const T* p) { return static_cast<typename Compute<T>::type>(*p); }
+template <> __device__ __forceinline__ float ld<__half>(const __half* p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void st(T* p, typename Compute<T>::type v) { *p = static_cast<T>(v); }
+template <> __device__ __forceinline__ void st<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// A = L L^T (lower) or U^T U (upper), column by column (left-looking). The factor is written to `out`, the other triangle
+// is set to zero. Element (i, j) of the lower factor lives at out[i*n + j]; of the upper factor at out[j*n + i].
+template <typename T>
+__global__ void cholesky_kernel(const T* __restrict__ a, T* __restrict__ out, int64_t n, int lower) {
+    using C = typename Compute<T>::type;
+    const T* am = a + static_cast<int64_t>(blockIdx.x) * n * n;
+    T* lm = out + static_cast<int64_t>(blockIdx.x) * n * n;
+    auto L = [&](int64_t i, int64_t j) -> T* { return lower ? lm + i * n + j : lm + j * n + i; };
+    auto A = [&](int64_t i, int64_t j) -> const T* { return lower ? am + i * n + j : am + j * n + i; };
+    __shared__ C diag;
+    for (int64_t j = 0; j < n; ++j) {
+        // every row i >= j: s_i = a_ij - sum_{k<j} L_ik L_jk (the factor's earlier columns are final and visible after the barrier)
+        for (int64_t i = j + threadIdx.x; i < n; i += blockDim.x) {
+            C s = ld(A(i, j));
+            for (int64_t k = 0; k < j; ++k) s -= ld(L(i, k)) * ld(L(j, k));
+            if (i == j) {
+                s = sqrt(s);  // a matrix that is not positive definite gives NaN from here on, as LAPACK-style kernels do
+                diag = s;
+            }
+            st(L(i, j), s);
+        }
+        __syncthreads();
+        const C d = diag;
+        for (int64_t i = j + 1 + threadIdx.x; i < n; i += blockDim.x) st(L(i, j), ld(L(i, j)) / d);
+        for (int64_t i = threadIdx.x; i < j; i += blockDim.x) st(L(i, j), C(0));  // the other triangle
+        __syncthreads();
+    }
+}
+
+// Solves T x = b for one right-hand side per thread, T = op(a) read through `at(i, k)`; forward when T is lower
+// triangular, backward otherwise. x is accumulated in `out`, whose element (row i of the unknown, this thread's column) is
+// at xo(i).
+struct SolveParams {
+    int64_t m, n;          // a is m x m; there are n right-hand sides
+    int32_t left_side, lower, unit_diagonal, transpose_a;
+};
+
+template <typename T>
+__global__ void triangular_solve_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, SolveParams p) {
+    using C = typename Compute<T>::type;
+    const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // which right-hand side
+    if (c >= p.n) return;
+    const int64_t batch = blockIdx.y;
+    const T* am = a + batch * p.m * p.m;
+    const int64_t bsz = p.m * p.n;
+    const T* bm = b + batch * bsz;
+    T* xm = out + batch * bsz;
+    // left side:  op(a) X = B, B is [m, n], column c.     right side: X op(a) = B, B is [n, m], row c: op(a)^T x^T = b^T.
+    const bool transposed = (p.transpose_a != 0) != (p.left_side == 0);
+    const bool eff_lower = (p.lower != 0) != transposed;
+    auto at = [&](int64_t i, int64_t k) -> C { return transposed ? ld(am + k * p.m + i) : ld(am + i * p.m + k); };
+    auto idx = [&](int64_t i) -> int64_t { return p.left_side ? i * p.n + c : c * p.m + i; };
+    if (eff_lower) {
+        for (int64_t i = 0; i < p.m; ++i) {
+            C s = ld(bm + idx(i));
+            for (int64_t k = 0; k < i; ++k) s -= at(i, k) * ld(xm + idx(k));
+            st(xm + idx(i), p.unit_diagonal ? s : s / at(i, i));
+        }
+    } else {
+        for (int64_t i = p.m - 1; i >= 0; --i) {
+            C s = ld(bm + idx(i));
+            for (int64_t k = i + 1; k < p.m; ++k) s -= at(i, k) * ld(xm + idx(k));
+            st(xm + idx(i), p.unit_diagonal ? s : s / at(i, i));
+        }
+    }
+}
+
+template <typename T>
+int launch_cholesky(const void* a, void* out, int64_t batch, int64_t n, int lower, cudaStream_t s) {
+    cholesky_kernel<T><<<static_cast<unsigned>(batch), 256, 0, s>>>(static_cast<const T*>(a), static_cast<T*>(out), n, lower);
+    MHLO_CUDA_CHECK_LAUNCH("cholesky");
+    return MHLO_CUDA_OK;
+}
+
+template <typename T>
+int launch_solve(const void* a, const void* b, void* out, int64_t batch, const SolveParams& p, cudaStream_t s) {
+    const dim3 grid(static_cast<unsigned>((p.n + 127) / 128), static_cast<unsigned>(batch));
+    triangular_solve_kernel<T><<<grid, 128, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), p);
+    MHLO_CUDA_CHECK_LAUNCH("triangular_solve");
+    return MHLO_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace mhlo
+
+using namespace mhlo;
+
+extern "C" {
+
+int mhlo_cuda_cholesky(int32_t dtype, const void* a_dev, void* out_dev, int64_t batch, int64_t n, int32_t lower, mhlo_cuda_stream_t stream) {
+    if (batch < 0 || n < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "cholesky: negative extent");
+    if (batch == 0 || n == 0) return MHLO_CUDA_OK;
+    if (!a_dev || !out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "cholesky: null pointer");
+    if (a_dev == out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "cholesky: the factor must not alias the matrix");
+    if (batch > 0x7fffffffLL) return fail(MHLO_CUDA_UNSUPPORTED, "cholesky: too many matrices");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case MHLO_DT_F32: return launch_cholesky<float>(a_dev, out_dev, batch, n, lower, s);
+        case MHLO_DT_F64: return launch_cholesky<double>(a_dev, out_dev, batch, n, lower, s);
+        case MHLO_DT_F16: return launch_cholesky<__half>(a_dev, out_dev, batch, n, lower, s);
+        case MHLO_DT_BF16: return launch_cholesky<__nv_bfloat16>(a_dev, out_dev, batch, n, lower, s);
+        default: return fail(MHLO_CUDA_UNSUPPORTED, "cholesky: dtype %d", dtype);
+    }
+}
+
+int mhlo_cuda_triangular_solve(int32_t dtype, const void* a_dev, const void* b_dev, void* out_dev, int64_t batch, int64_t m, int64_t n,
+                               int32_t left_side, int32_t lower, int32_t unit_diagonal, int32_t transpose_a, mhlo_cuda_stream_t stream) {
+    if (batch < 0 || m < 0 || n < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "triangular_solve: negative extent");
+    if (batch == 0 || m == 0 || n == 0) return MHLO_CUDA_OK;
+    if (!a_dev || !b_dev || !out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "triangular_solve: null pointer");
+    if (batch > 65535) return fail(MHLO_CUDA_UNSUPPORTED, "triangular_solve: more than 65535 matrices");
+    SolveParams p{m, n, left_side, lower, unit_diagonal, transpose_a};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case MHLO_DT_F32: return launch_solve<float>(a_dev, b_dev, out_dev, batch, p, s);
+        case MHLO_DT_F64: return launch_solve<double>(a_dev, b_dev, out_dev, batch, p, s);
+        case MHLO_DT_F16: return launch_solve<__half>(a_dev, b_dev, out_dev, batch, p, s);
+        case MHLO_DT_BF16: return launch_solve<__nv_bfloat16>(a_dev, b_dev, out_dev, batch, p, s);
+        default: return fail(MHLO_CUDA_UNSUPPORTED, "triangular_solve: dtype %d", dtype);
+    }
+}
+
+}  // extern "C"

@@ -135,6 +135,8 @@ _PROTOTYPES = {
     "mhlo_cuda_dot_strided": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "mhlo_cuda_gemm": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp,
                                  _i32, _vp]),
+    "mhlo_cuda_cholesky": (C.c_int, [_i32, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "mhlo_cuda_triangular_solve": (C.c_int, [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),
     "mhlo_cuda_kernel_lookup": (C.c_int, [C.c_char_p, _i32, C.POINTER(_i32)]),
     "mhlo_cuda_plan_create": (C.c_int, [_vp, _i32, _i32, _i32, _i64, C.c_char_p, _i64, C.POINTER(_vp)]),
     "mhlo_cuda_plan_execute": (C.c_int, [_vp, C.POINTER(_vp), _i32, C.POINTER(_vp), _i32, _vp]),

@@ -1166,6 +1166,34 @@ class Interpreter:
         out = np.where(nan, keep_nan, bits).astype(np.uint64).view(np.float64)
         return out.reshape(a[0].shape)
 
+    def op_cholesky(self, op, a, t):
+        # stablehlo.cholesky: the lower (default: upper) factor of every [n, n] matrix, the other triangle zero
+        lower = str(op.attrs.get("lower", "false")).lower() in ("true", "1")
+        x = np.asarray(a[0], dtype=np.float64)
+        with np.errstate(all="ignore"):
+            try:
+                fac = np.linalg.cholesky(x)
+            except np.linalg.LinAlgError:
+                fac = np.full_like(x, np.nan)
+        return fac if lower else np.swapaxes(fac, -1, -2)
+
+    def op_triangular_solve(self, op, a, t):
+        import scipy.linalg
+
+        A = op.attrs
+        flag = lambda k: str(A.get(k, "false")).lower() in ("true", "1")  # noqa: E731
+        tr = str(A.get("transpose_a", "NO_TRANSPOSE"))
+        trans = 0 if "NO_TRANSPOSE" in tr else 1
+        x, b = np.asarray(a[0], dtype=np.float64), np.asarray(a[1], dtype=np.float64)
+        out = np.empty_like(b)
+        for idx in np.ndindex(*x.shape[:-2]):
+            m = np.tril(x[idx]) if flag("lower") else np.triu(x[idx])
+            if flag("left_side"):
+                out[idx] = scipy.linalg.solve_triangular(m, b[idx], trans=trans, lower=flag("lower"), unit_diagonal=flag("unit_diagonal"))
+            else:  # x op(a) = b  <=>  op(a)^T x^T = b^T
+                out[idx] = scipy.linalg.solve_triangular(m, b[idx].T, trans=1 - trans, lower=flag("lower"), unit_diagonal=flag("unit_diagonal")).T
+        return out
+
     def op_composite(self, op, a, t):
         dec = op.attrs.get("decomposition", "")
         name = str(dec[-1] if isinstance(dec, tuple) else dec).lstrip("@")

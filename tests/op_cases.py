@@ -949,4 +949,49 @@ def convolution_cases():
     return out
 
 
-CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases()
+def linalg_cases():
+    """stablehlo.cholesky and stablehlo.triangular_solve in the forms jax.numpy.linalg prints, every combination of side,
+    triangle and transposition."""
+    rng = np.random.default_rng(77)
+    out = []
+
+    def spd(batch, n, dt):
+        m = rng.standard_normal(batch + (n, n))
+        return (m @ np.swapaxes(m, -1, -2) / n + 2 * np.eye(n)).astype(np.float32).astype(NP[dt])
+
+    for dt, batch, n in (("f32", (), 5), ("f32", (3,), 33), ("f64", (2, 2), 16), ("f32", (1,), 300)) + ((("bf16", (2,), 12),) if "bf16" in NP else ()):
+        t = tt(batch + (n, n), dt)
+        for lower in (True, False):
+            body = f"    %0 = stablehlo.cholesky %arg0, lower = {str(lower).lower()} : {t}"
+            out.append((f"cholesky_{dt}_{'x'.join(map(str, batch + (n,)))}_{'lower' if lower else 'upper'}", func([t], [t], body, "%0"), [spd(batch, n, dt)]))
+    for dt, batch, m, n in (("f32", (), 5, 3), ("f32", (2,), 64, 40), ("f64", (3,), 17, 9)):
+        for left in (True, False):
+            for lower in (True, False):
+                for trans in ("NO_TRANSPOSE", "TRANSPOSE"):
+                    a = (rng.standard_normal(batch + (m, m)) / m + 2 * np.eye(m)).astype(NP[dt])  # both triangles filled: only one may be read
+                    bshape = batch + ((m, n) if left else (n, m))
+                    b = rng.standard_normal(bshape).astype(NP[dt])
+                    ta, tb = tt(batch + (m, m), dt), tt(bshape, dt)
+                    body = (f"    %0 = \"stablehlo.triangular_solve\"(%arg0, %arg1) <{{left_side = {str(left).lower()}, lower = {str(lower).lower()}, "
+                            f"transpose_a = #stablehlo<transpose {trans}>, unit_diagonal = false}}> : ({ta}, {tb}) -> {tb}")
+                    name = f"triangular_solve_{dt}_m{m}_{'left' if left else 'right'}_{'lower' if lower else 'upper'}_{trans.lower()}"
+                    out.append((name, func([ta, tb], [tb], body, "%0"), [a, b]))
+    a = (rng.standard_normal((6, 6)) / 6 + 2 * np.eye(6)).astype(np.float32)
+    b = rng.standard_normal((6, 4)).astype(np.float32)
+    ta, tb = tt((6, 6), "f32"), tt((6, 4), "f32")
+    body = (f"    %0 = \"stablehlo.triangular_solve\"(%arg0, %arg1) <{{left_side = true, lower = true, transpose_a = #stablehlo<transpose ADJOINT>, "
+            f"unit_diagonal = true}}> : ({ta}, {tb}) -> {tb}")
+    out.append(("triangular_solve_unit_diagonal_adjoint", func([ta, tb], [tb], body, "%0"), [a, b]))
+    # the solve of a Cholesky factor: A x = b as two triangular solves, the way jax.scipy.linalg.cho_solve lowers
+    n = 24
+    A = spd((), n, "f32")
+    rhs = rng.standard_normal((n, 5)).astype(np.float32)
+    tA, tB = tt((n, n), "f32"), tt((n, 5), "f32")
+    body = (f"    %l = stablehlo.cholesky %arg0, lower = true : {tA}\n"
+            f"    %y = \"stablehlo.triangular_solve\"(%l, %arg1) <{{left_side = true, lower = true, transpose_a = #stablehlo<transpose NO_TRANSPOSE>, unit_diagonal = false}}> : ({tA}, {tB}) -> {tB}\n"
+            f"    %0 = \"stablehlo.triangular_solve\"(%l, %y) <{{left_side = true, lower = true, transpose_a = #stablehlo<transpose TRANSPOSE>, unit_diagonal = false}}> : ({tA}, {tB}) -> {tB}")
+    out.append(("cholesky_solve_f32", func([tA, tB], [tB], body, "%0"), [A, rhs]))
+    return out
+
+
+CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases()
