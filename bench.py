@@ -583,11 +583,15 @@ def measure_extras(r, cuda, peaks):
                              "parallelism": f"column split x{world}" + (" + NCCL all-gather + interleave" if world > 1 else "")}
     if world > 1:
         # The same product with the exchange fused into the GEMM: every rank's epilogue stores its column block into all
-        # ranks' copies of C through peer addresses, then one tiny all-reduce tells every rank that all copies are complete.
+        # ranks' copies of C through peer addresses; a one-CTA kernel behind it publishes this rank's epoch in the peers'
+        # flag words and waits (bounded) for theirs, so the stream carries on once every copy is complete.
         import ctypes as C
 
+        c_bytes = n * n * 2
         own = C.c_void_p()
-        cuda.check(cuda.lib.mhlo_cuda_alloc(n * n * 2, C.byref(own)))
+        cuda.check(cuda.lib.mhlo_cuda_alloc(c_bytes + 256, C.byref(own)))  # C, then the eight flag words
+        cuda.check(cuda.lib.mhlo_cuda_memset(own, 0, c_bytes + 256, stream))
+        torch.cuda.synchronize()
         handle = C.create_string_buffer(64)
         cuda.check(cuda.lib.mhlo_cuda_ipc_export(own, handle))
         handles = sharding.exchange_handles(handle.raw, dist)
@@ -600,29 +604,47 @@ def measure_extras(r, cuda, peaks):
                 cuda.check(cuda.lib.mhlo_cuda_ipc_open(handles[r], C.byref(ptr)))
                 peers.append(ptr.value)
         c_ptrs = (C.c_void_p * world)(*peers)
+        flag_ptrs = (C.c_void_p * world)(*[p + c_bytes for p in peers])
         ab_str = cuda._i64s([n, 1])
         flag = torch.zeros(1, device=dev)
+        epoch = [0]
+        dist.barrier()  # every rank's flag words are zero and mapped before the first epoch is published
 
-        def fused_step():
-            cuda.check(cuda.lib.mhlo_cuda_gemm_all_gather(cuda.BF16, cuda.BF16, a.data_ptr(), ab_str, b_ptr, ab_str, c_ptrs, world, rank, n,
-                                                          ncols, n, None, 0, stream))
-            dist.all_reduce(flag)
+        def fused_step(tuning=None, copy_stores=0, closing="flags"):
+            cuda.check(cuda.lib.mhlo_cuda_gemm_all_gather_tuned(cuda.BF16, cuda.BF16, a.data_ptr(), ab_str, b_ptr, ab_str, c_ptrs, world, rank, n,
+                                                                ncols, n, None, 0, None if tuning is None else C.addressof(tuning), copy_stores,
+                                                                stream))
+            if closing == "flags":
+                epoch[0] += 1
+                cuda.check(cuda.lib.mhlo_cuda_peer_barrier(flag_ptrs, world, rank, epoch[0], 2_000_000_000, stream))
+            elif closing == "nccl":
+                dist.all_reduce(flag)
 
         fused_step()
         torch.cuda.synchronize()
         dist.barrier()
         # correctness against the NCCL path of the same operands, on this rank's copy
         mine = torch.empty(n, n, device=dev, dtype=torch.bfloat16)
-        cuda.check(cuda.lib.mhlo_cuda_copy(mine.data_ptr(), own, n * n * 2, stream))
+        cuda.check(cuda.lib.mhlo_cuda_copy(mine.data_ptr(), own, c_bytes, stream))
         torch.cuda.synchronize()
         same = bool(torch.equal(mine.view(torch.int16), c_full.view(torch.int16)))
-        ms_f = timed(fused_step, 10)
+        variants = {}
+        for name, kw in (("lane_stores", {}), ("lane_stores_tile128", {"tuning": cuda.GemmTuning(128, 0, 0, 0)}),
+                         ("bulk_stores", {"copy_stores": 2}), ("bulk_stores_tile128", {"tuning": cuda.GemmTuning(128, 0, 0, 0), "copy_stores": 2}),
+                         ("pair_lane_stores", {"tuning": cuda.GemmTuning(256, 0, 2, 0)}),
+                         ("pair_bulk_stores", {"tuning": cuda.GemmTuning(256, 0, 2, 0), "copy_stores": 2}),
+                         ("lane_stores_nccl_closing", {"closing": "nccl"}), ("lane_stores_unclosed", {"closing": "none"})):
+            variants[name] = timed(lambda: fused_step(**kw), 10)
+            dist.barrier()
+        best = min((k for k in variants if not k.endswith(("nccl_closing", "unclosed"))), key=variants.get)
+        ms_f = variants[best]
         tf_f = 2 * n ** 3 / ms_f / 1e9
         out["gemm_bf16_8192_fused_all_gather"] = {
             "tflops": tf_f, "ms": ms_f, "roofline": tensor_block(2 * n ** 3, ms_f, world, peaks, kernel="gemm_tcgen05_kernel + peer stores",
                                                                  link_floor_ms=(n * n * 2 / world) * (world - 1) / 770e9 * 1e3),
-            "matches_nccl_path": same,
-            "parallelism": f"column split x{world}, epilogue stores into every rank's C over NVLink, 1-element all-reduce as completion barrier"}
+            "matches_nccl_path": same, "variant": best, "ms_by_variant": {k: round(v, 4) for k, v in variants.items()},
+            "nvlink_bytes_per_rank": (n * n * 2 // world) * (world - 1),
+            "parallelism": f"column split x{world}, epilogue stores into every rank's C over NVLink, flag words in peer memory as completion barrier"}
         assert cuda.device_error() == 0
         dist.barrier()
         for r in range(world):
@@ -856,14 +878,15 @@ def profile_case(kind: str, launches: int):
         # the whole forward pass at 4 sequences (one GPU's share of the batch at 8 GPUs), launch by launch
         from metalhlo_b200 import capi, modules
 
-        text, params = modules.gpt2_module(batch=4, seq=SEQ)
+        pb = int(os.environ.get("BENCH_PROFILE_BATCH", "4"))
+        text, params = modules.gpt2_module(batch=pb, seq=SEQ)
         client = capi.Client()
         exe = client.compile(text, opt_level=3)
         bufs = [client.buffer(a) for a in gpt2_host_inputs(params)]
         ptrs = [b_.device_pointer for b_ in bufs]
-        logits = torch.empty(4, SEQ, VOCAB, device=dev, dtype=torch.float16)
+        logits = torch.empty(pb, SEQ, VOCAB, device=dev, dtype=torch.float16)
         fn = lambda: exe.execute_on_device(ptrs, [logits.data_ptr()], torch.cuda.current_stream().cuda_stream)  # noqa: E731
-        work, unit = FLOP_PER_TOKEN * 4 * SEQ / 1e12, "TFLOP"
+        work, unit = FLOP_PER_TOKEN * pb * SEQ / 1e12, "TFLOP"
     else:
         causal = kind == "attention_causal"
         q, k, v = (torch.randn(2, 32, 4096, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(3))

@@ -528,6 +528,31 @@ int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a
                               int32_t epilogue, mhlo_cuda_stream_t stream);
 
 /*
+ * The same product with its launch knobs set by the caller. tuning: tile width and TMA ring depth as in
+ * mhlo_cuda_gemm_tuned; NULL leaves them to the library.
+ * copy_stores: 0 or 1 = every lane stores 16 bytes into each copy, 2 = one bulk tensor store (TMA, 32 rows x 128 bytes)
+ * per copy from the staged tile. The results are bit-identical in every setting.
+ */
+int mhlo_cuda_gemm_all_gather_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2],
+                                    const void* b_dev, const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks,
+                                    int32_t rank, int64_t m, int64_t n_local, int64_t k, const void* bias_dev,
+                                    int32_t epilogue, const mhlo_cuda_gemm_tuning* tuning, int32_t copy_stores,
+                                    mhlo_cuda_stream_t stream);
+
+/*
+ * Completion barrier between the ranks of such an exchange, on the device: flag_devs[r] = eight 64-bit words in rank
+ * r's memory (flag_devs[rank] local, the others peer addresses), zero before the first use. In stream order after the
+ * kernels whose stores it covers, one small kernel stores `epoch` into word `rank` of every other rank's array
+ * (system-scope release) and waits until every word of its own array has reached `epoch`; work queued behind it on the
+ * stream therefore sees every rank's stores. Epochs must grow from call to call. The wait gives up after limit_ns
+ * (at most 2 s) and records code 95 in the word mhlo_cuda_device_error reads, leaving the context usable. Every rank
+ * must run on its own GPU: kernels that wait on one another are not launched on one device. The reference has no
+ * counterpart (single device).
+ */
+int mhlo_cuda_peer_barrier(void* const* flag_devs, int32_t n_ranks, int32_t rank, uint64_t epoch, uint64_t limit_ns,
+                           mhlo_cuda_stream_t stream);
+
+/*
  * Every wait inside the tensor-core kernels (mbarrier phases fed by TMA and tcgen05.commit) is bounded; a kernel
  * whose wait expires records a non-zero word and drains instead of spinning. This call synchronises the device,
  * reads and clears that word: *out_code = 0 when no kernel gave up since the last call.

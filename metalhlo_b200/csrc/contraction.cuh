@@ -18,6 +18,7 @@ struct GemmProblem {
     int64_t ldc = 0, c_col0 = 0;
     void* copies[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int32_t n_copies = 0;
+    int32_t copy_stores = 0;  // how the copies are written: 0 / 1 = 16-byte stores per lane, 2 = bulk tensor stores (one map per copy)
     // Launch knobs of the tensor-core kernel; 0 = chosen by the library. tile_n: 128 or 256 columns per tile; stages: depth
     // of the TMA ring; cta_group: 1 = one CTA per 128-row tile, 2 = a pair of CTAs per 256-row tile.
     int32_t tile_n = 0, stages = 0, cta_group = 0;
@@ -42,6 +43,9 @@ bool attention_error_fetch_async(int* pinned_dst, cudaStream_t stream);
 bool gemm_error_store(int code);
 bool attention_error_store(int code);
 bool gemm_wait_expiry_probe(uint64_t limit_ns, cudaStream_t stream);
+// One CTA: stores `epoch` into word `rank` of every other rank's flag array, then waits (at most limit_ns) until every word
+// of this rank's own array has reached `epoch`; an expired wait records code 95 in the GEMM error word.
+bool gemm_peer_barrier_launch(uint64_t* const* flag_arrays, int n_ranks, int rank, uint64_t epoch, uint64_t limit_ns, cudaStream_t stream);
 bool attention_tc_supported(int dtype, const AttnShape& s, const void* mask);
 int attention_tc_launch(int dtype, const void* q, const void* k, const void* v, void* o, const AttnShape& s,
                         cudaStream_t stream);

@@ -212,6 +212,36 @@ int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev,
 int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2], const void* b_dev,
                               const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks, int32_t rank, int64_t m, int64_t n_local,
                               int64_t k, const void* bias_dev, int32_t epilogue, mhlo_cuda_stream_t stream) {
+    return mhlo_cuda_gemm_all_gather_tuned(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_devs, n_ranks, rank, m, n_local, k, bias_dev,
+                                           epilogue, nullptr, 0, stream);
+}
+
+int mhlo_cuda_peer_barrier(void* const* flag_devs, int32_t n_ranks, int32_t rank, uint64_t epoch, uint64_t limit_ns, mhlo_cuda_stream_t stream) {
+    if (!flag_devs) return fail(MHLO_CUDA_INVALID_ARGUMENT, "peer_barrier: null argument");
+    if (n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "peer_barrier: rank %d of %d (1 to 8 ranks)", rank, n_ranks);
+    if (limit_ns == 0 || limit_ns > 2000000000ull) return fail(MHLO_CUDA_INVALID_ARGUMENT, "peer_barrier: the wait limit is 1 ns to 2 s");
+    uint64_t* arrays[8] = {nullptr};
+    for (int r = 0; r < n_ranks; ++r) {
+        if (flag_devs[r] == nullptr || (reinterpret_cast<uintptr_t>(flag_devs[r]) & 7u) != 0)
+            return fail(MHLO_CUDA_INVALID_ARGUMENT, "peer_barrier: flag array %d is null or not 8-byte aligned", r);
+        arrays[r] = static_cast<uint64_t*>(flag_devs[r]);
+    }
+    if (n_ranks == 1) return MHLO_CUDA_OK;
+    return gemm_peer_barrier_launch(arrays, n_ranks, rank, epoch, limit_ns, static_cast<cudaStream_t>(stream))
+               ? MHLO_CUDA_OK
+               : fail(MHLO_CUDA_EXECUTION_FAILED, "peer_barrier: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+int mhlo_cuda_gemm_all_gather_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2], const void* b_dev,
+                                    const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks, int32_t rank, int64_t m,
+                                    int64_t n_local, int64_t k, const void* bias_dev, int32_t epilogue, const mhlo_cuda_gemm_tuning* tuning,
+                                    int32_t copy_stores, mhlo_cuda_stream_t stream) {
+    if (copy_stores < 0 || copy_stores > 2) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: copy_stores %d (0 to 2)", copy_stores);
+    if (tuning && ((tuning->tile_n != 0 && tuning->tile_n != 128 && tuning->tile_n != 256) || tuning->stages < 0 || tuning->stages > 8 ||
+                   tuning->stages == 1 || tuning->cta_group < 0 || tuning->cta_group > 2 || (tuning->cta_group == 2 && tuning->tile_n == 128)))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: tuning {tile_n %d, stages %d, cta_group %d} is not a configuration of this product",
+                    tuning->tile_n, tuning->stages, tuning->cta_group);
     if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: unknown epilogue %d", epilogue);
     if (!a_strides || !b_strides || !c_devs) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_all_gather: null argument");
@@ -230,8 +260,10 @@ int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a
     p.ldc = n_local * n_ranks;
     p.c_col0 = n_local * rank;
     p.n_copies = 0;
-    for (int r = 0; r < n_ranks; ++r)
-        if (r != rank) p.copies[p.n_copies++] = c_devs[r];
+    // copies in the order rank + 1, rank + 2, ...: in any one moment the ranks' stores go to different peers
+    for (int i = 1; i < n_ranks; ++i) p.copies[p.n_copies++] = c_devs[(rank + i) % n_ranks];
+    p.copy_stores = copy_stores;
+    if (tuning) { p.tile_n = tuning->tile_n; p.stages = tuning->stages; p.cta_group = tuning->cta_group; }
     if (!gemm_tc_supported(p))
         return fail(MHLO_CUDA_UNSUPPORTED, "gemm_all_gather: needs the tensor-core path (bf16 / f16 operands, 16-byte aligned rows, k > 0)");
     return gemm_tc_launch(p, static_cast<cudaStream_t>(stream));

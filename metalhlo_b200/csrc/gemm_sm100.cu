@@ -57,6 +57,20 @@ __device__ __forceinline__ float epilogue_act(float v) {
     return v;
 }
 
+// GELU (tanh form) on two f16 values at once: five half2 operations and one tanh.approx.f16x2 for the pair, where the fp32
+// form spends five fp32 operations and one tanh.approx per value. The argument is the f16-rounded pre-activation; the
+// arithmetic error (about 1.5e-3 relative) is that of the same chain evaluated op by op on f16 tensors.
+__device__ __forceinline__ uint32_t gelu_tanh_f16x2(uint32_t xbits) {
+    const __half2 x = *reinterpret_cast<const __half2*>(&xbits);
+    const __half2 c0 = __float2half2_rn(0.7978845608028654f), c1 = __float2half2_rn(0.7978845608028654f * 0.044715f);
+    const __half2 inner = __hmul2(x, __hfma2(__hmul2(x, x), c1, c0));
+    uint32_t t;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(*reinterpret_cast<const uint32_t*>(&inner)));
+    const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
+    const __half2 y = __hfma2(hx, *reinterpret_cast<const __half2*>(&t), hx);
+    return *reinterpret_cast<const uint32_t*>(&y);
+}
+
 struct GemmParams {
     void* c;
     const void* bias;
@@ -76,6 +90,12 @@ struct GemmParams {
     int32_t stages;                  // depth of the TMA ring in use (<= the kernel's STAGES)
 };
 
+// Tensor maps of the further copies of C (GemmParams::copies, in the same order), used when the copies are written with
+// bulk tensor stores.
+struct PeerMaps {
+    CUtensorMap m[7];
+};
+
 // CTAS = 2: a pair of CTAs shares one (2 * BM) x BN tile; each stages its own BM rows of A and BN / 2 rows of B.
 template <int BN, int STAGES, int CTAS = 1>
 struct SmemLayout {
@@ -84,8 +104,10 @@ struct SmemLayout {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 256;
     static constexpr int kStagingBytes = kEpilogueWarps * 4096;  // one 32-row x 128-byte tile per epilogue warp
+    static constexpr int kBiasBytes = kEpilogueWarps * 128;      // 32 fp32 bias values per epilogue warp
     static constexpr int kStagingOff = STAGES * kStageBytes;
-    static constexpr int kBarrierOff = kStagingOff + kStagingBytes;
+    static constexpr int kBiasOff = kStagingOff + kStagingBytes;
+    static constexpr int kBarrierOff = kBiasOff + kBiasBytes;
     static constexpr int kTotal = kBarrierOff + kBarrierBytes + 1024;  // + slack for 1024-byte alignment
 };
 
@@ -106,7 +128,8 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
 template <int BN, int STAGES, int ACT, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p,
+                    const __grid_constant__ PeerMaps peer_maps) {
     using L = SmemLayout<BN, STAGES, CTAS>;
     constexpr bool kPair = CTAS == 2;
     constexpr int BNL = BN / CTAS;  // rows of B (columns of the tile) this CTA stages
@@ -129,7 +152,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&map_a);
         prefetch_tmap(&map_b);
-        if (p.c_tma) prefetch_tmap(&map_c);
+        if (p.c_tma) {
+            prefetch_tmap(&map_c);
+            for (int d = 0; d < p.n_copies; ++d) prefetch_tmap(&peer_maps.m[d]);
+        }
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps * CTAS); }
         fence_barrier_init();
@@ -277,14 +303,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint8_t* stage_tile = smem + L::kStagingOff + (warp - 2) * 4096;
             const int64_t batch_off = static_cast<int64_t>(bz) * p.m * p.ldc * out_es;
             uint8_t* cbase = static_cast<uint8_t*>(p.c) + batch_off;
-            // bias of this warp's BN/2 columns, spread over the lanes (column i lives in lane i / kBiasPerLane, register
-            // i % kBiasPerLane) and handed out with shuffles: one global load per column per tile instead of one per element
+            // bias of this warp's BN/2 columns: lane l holds columns l, 32 + l, ... (one global load per column per tile). For
+            // every group of 32 columns the lanes put their value into the warp's 128 bytes of shared memory and each thread
+            // reads all 32 back with broadcast loads: eight 16-byte loads per group instead of 32 shuffles.
             constexpr int kBiasPerLane = BN / 2 / 32;
             float breg[kBiasPerLane];
             const bool has_bias = p.bias != nullptr;
+            float* bias_tile = reinterpret_cast<float*>(smem + L::kBiasOff) + (warp - 2) * 32;
 #pragma unroll
             for (int q = 0; q < kBiasPerLane; ++q) {
-                const int64_t col = static_cast<int64_t>(tn) * BN + col_begin + lane * kBiasPerLane + q;
+                const int64_t col = static_cast<int64_t>(tn) * BN + col_begin + q * 32 + lane;
                 float bv = 0.f;
                 if (has_bias && col < p.n) {
                     if (p.out_dtype == MHLO_DT_F32) bv = static_cast<const float*>(p.bias)[col];
@@ -311,14 +339,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                     if (has_bias) {
-                        const int i0 = c0 - col_begin + half * 32;  // first column of this group inside the warp's range
+                        const int group = (c0 - col_begin) / 32 + half;  // which 32 columns of the warp's range
+                        float mine = breg[0];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            // (i0 + j) / kBiasPerLane is the owning lane; i0 is a multiple of 32, so the register index is static
-                            v[j] += __shfl_sync(0xffffffffu, breg[j % kBiasPerLane], (i0 + j) / kBiasPerLane);
+                        for (int q = 1; q < kBiasPerLane; ++q) mine = group == q ? breg[q] : mine;
+                        bias_tile[lane] = mine;
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 b4 = reinterpret_cast<const float4*>(bias_tile)[j];  // the same address in every lane
+                            v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
                         }
+                        __syncwarp();  // every lane has read the group before the next one is written
                     }
-                    if constexpr (ACT != MHLO_EPILOGUE_NONE) {
+                    // f16 results take the tanh-form GELU in packed f16 arithmetic after the conversion below
+                    constexpr bool kPackedGelu = ACT == MHLO_EPILOGUE_GELU_TANH;
+                    if (ACT != MHLO_EPILOGUE_NONE && !(kPackedGelu && p.out_dtype == MHLO_DT_F16)) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = epilogue_act<ACT>(v[j]);
                     }
@@ -345,6 +381,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             for (int q = 0; q < 4; ++q) {
                                 __half2 hh = __floats2half2_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
                                 w[q] = *reinterpret_cast<uint32_t*>(&hh);
+                                if constexpr (kPackedGelu) w[q] = gelu_tanh_f16x2(w[q]);
                             }
                             out16[half * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
@@ -365,6 +402,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (lane == 0 && cols_left > 0 && row0 < p.m) {
                         const int b1 = static_cast<int>(bz % p.batch1), b0 = static_cast<int>(bz / p.batch1);
                         tma_store_4d(&map_c, stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
+                        // the same box into every other copy of C: bulk stores over NVLink, in the same group
+                        for (int d = 0; d < p.n_copies; ++d)
+                            tma_store_4d(&peer_maps.m[d], stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
                         tma_store_commit();
                     }
                     continue;
@@ -388,37 +428,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 } else if (cols_left >= chunk_cols && p.n_copies == 0) {
                     // Rows of C that do not start on 16-byte boundaries (a row pitch such as 50257 f16): every row's 128
                     // bytes are still written mostly with 16-byte stores. With a = (address of the row's chunk) mod 16, the
-                    // aligned 16-byte pieces of global memory inside the chunk hold staged bytes [16 g - a, 16 g - a + 16):
-                    // 8 lanes per row fetch them as five 32-bit words from the staging tile and realign them with a funnel
-                    // shift; the (16 - a) head bytes and a tail bytes, 16 bytes together, go out one element per lane.
+                    // aligned 16-byte pieces of global memory inside the chunk hold staged bytes [16 g - a, 16 g - a + 16),
+                    // g = 1..7: the tail of staged piece g - 1 and the head of piece g. Rows eight apart share a (eight
+                    // pitches are a multiple of 16 bytes), so one instruction serves rows j, j + 8, j + 16, j + 24 with 8
+                    // lanes each: a is uniform over the warp, the two staged pieces come in with 16-byte loads and one
+                    // funnel shift per word realigns them. The (16 - a) head bytes and a tail bytes of a row, 16 bytes
+                    // together, go out one element per lane.
                     const int edge_elems = 16 / static_cast<int>(out_es);
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rr = it * 4 + (lane >> 3), c = lane & 7;
-                        if (row0 + rr >= p.m) continue;
+#pragma unroll 1
+                    for (int j = 0; j < 8; ++j) {
+                        const int rr = j + 8 * (lane >> 3), c = lane & 7;
                         uint8_t* dst = cbase + ((row0 + rr) * p.ldc + p.c_col0 + col0) * out_es;
-                        const int a = static_cast<int>(reinterpret_cast<uintptr_t>(dst) & 15);
+                        const int a = static_cast<int>(reinterpret_cast<uintptr_t>(dst) & 15);  // the same in every lane
+                        if (row0 + rr >= p.m) continue;
                         const uint8_t* srow = stage_tile + rr * 128;
-                        auto staged_word = [&](int wi) {  // 32-bit word wi of the row, through the tile's swizzle
-                            return *reinterpret_cast<const uint32_t*>(srow + ((((wi >> 2) ^ (rr & 7)) << 4) | ((wi & 3) << 2)));
-                        };
-                        const int g = a == 0 ? c : c + 1;  // aligned piece this lane writes (pieces 1..7 when a > 0)
-                        if (g <= 7) {
-                            const int byte0 = 16 * g - a;  // first staged byte of the piece, a multiple of 2
-                            const int w0 = byte0 >> 2;
-                            uint32_t w[5];
-#pragma unroll
-                            for (int q = 0; q < 5; ++q) w[q] = staged_word(min(w0 + q, 31));
-                            uint4 v;
-                            if (byte0 & 2) {
-                                v.x = __funnelshift_r(w[0], w[1], 16); v.y = __funnelshift_r(w[1], w[2], 16);
-                                v.z = __funnelshift_r(w[2], w[3], 16); v.w = __funnelshift_r(w[3], w[4], 16);
-                            } else {
-                                v = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                            *reinterpret_cast<uint4*>(dst + byte0) = v;
+                        auto staged_piece = [&](int g) { return *reinterpret_cast<const uint4*>(srow + ((g ^ (rr & 7)) << 4)); };
+                        if (a == 0) {
+                            *reinterpret_cast<uint4*>(dst + c * 16) = staged_piece(c);
+                            continue;
                         }
-                        if (a != 0 && c < edge_elems) {
+                        if (c < 7) {
+                            const uint4 lo = staged_piece(c), hi = staged_piece(c + 1);
+                            const int s = 16 - a;  // first byte of the aligned piece inside lo:hi
+                            uint32_t x0, x1, x2, x3, x4;
+                            switch (s >> 2) {
+                                case 0: x0 = lo.x; x1 = lo.y; x2 = lo.z; x3 = lo.w; x4 = hi.x; break;
+                                case 1: x0 = lo.y; x1 = lo.z; x2 = lo.w; x3 = hi.x; x4 = hi.y; break;
+                                case 2: x0 = lo.z; x1 = lo.w; x2 = hi.x; x3 = hi.y; x4 = hi.z; break;
+                                default: x0 = lo.w; x1 = hi.x; x2 = hi.y; x3 = hi.z; x4 = hi.w; break;
+                            }
+                            uint4 v;
+                            if (s & 2) {
+                                v.x = __funnelshift_r(x0, x1, 16); v.y = __funnelshift_r(x1, x2, 16);
+                                v.z = __funnelshift_r(x2, x3, 16); v.w = __funnelshift_r(x3, x4, 16);
+                            } else {
+                                v = make_uint4(x0, x1, x2, x3);
+                            }
+                            *reinterpret_cast<uint4*>(dst + 16 * (c + 1) - a) = v;
+                        }
+                        if (c < edge_elems) {
+                            auto staged_word = [&](int wi) {  // 32-bit word wi of the row, through the tile's swizzle
+                                return *reinterpret_cast<const uint32_t*>(srow + ((((wi >> 2) ^ (rr & 7)) << 4) | ((wi & 3) << 2)));
+                            };
                             const int head = (16 - a) / static_cast<int>(out_es);             // elements before the first aligned piece
                             const int e = c < head ? c : 128 / static_cast<int>(out_es) - (edge_elems - head) + (c - head);
                             if (out_es == 2) {
@@ -616,17 +667,26 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         if (d < pr.n_copies) aligned = aligned && aligned16(pr.copies[d]);
     }
     p.c_vec_ok = aligned;
-    // Bulk tensor stores need 16-byte aligned rows and a 16-byte aligned base; copies in peers' memory keep plain stores.
+    // Bulk tensor stores need 16-byte aligned rows and a 16-byte aligned base. The map of a column block inside a wider
+    // matrix starts at the block's first column and is n columns wide. Copies in peers' memory are written with bulk
+    // stores too (one more map per copy) when the problem asks for it; otherwise they keep the per-lane stores.
     CUtensorMap map_c;
     memset(&map_c, 0, sizeof map_c);
+    PeerMaps peer_maps;
+    memset(&peer_maps, 0, sizeof peer_maps);
     p.c_tma = 0;
     static const bool tma_store_enabled = [] {
         const char* v = getenv("METALHLO_GEMM_TMA_STORE");
         return !(v && v[0] == '0');  // METALHLO_GEMM_TMA_STORE=0 keeps the per-lane stores
     }();
-    if (tma_store_enabled && aligned && pr.n_copies == 0 && p.c_col0 == 0 && pr.m * p.ldc * static_cast<int64_t>(out_es) % 16 == 0) {
-        if (!output_map(&map_c, pr.c, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
+    const bool copies_by_tma = pr.n_copies == 0 || pr.copy_stores == 2;
+    if (tma_store_enabled && aligned && copies_by_tma && pr.m * p.ldc * static_cast<int64_t>(out_es) % 16 == 0) {
+        const size_t col_off = static_cast<size_t>(p.c_col0) * out_es;
+        if (!output_map(&map_c, static_cast<uint8_t*>(pr.c) + col_off, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
             return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for C: %s", why.c_str());
+        for (int d = 0; d < pr.n_copies; ++d)
+            if (!output_map(&peer_maps.m[d], static_cast<uint8_t*>(pr.copies[d]) + col_off, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
+                return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for copy %d of C: %s", d, why.c_str());
         p.c_tma = 1;
     }
 
@@ -663,7 +723,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
         walkers = pairs;
     }
     const int grid = CTAS * static_cast<int>(std::min<int64_t>(p.num_tiles, walkers));
-    const cudaError_t launched = launch_dependent_cluster(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, CTAS, map_a, map_b, map_c, p);
+    const cudaError_t launched = launch_dependent_cluster(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, CTAS, map_a, map_b, map_c, p, peer_maps);
     if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of gemm_tcgen05 failed: %s", cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH("gemm_tcgen05");
     return MHLO_CUDA_OK;
@@ -693,7 +753,7 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     }();
     int cta_group = p.cta_group;
     if (cta_group == 0 && pair_env >= 0 && p.n_copies == 0) cta_group = pair_env + 1;
-    if (cta_group == 2 && p.n_copies == 0) return launch_gemm<256, 6, 2>(p, stream);
+    if (cta_group == 2) return launch_gemm<256, 6, 2>(p, stream);
     if (p.tile_n == 256) return launch_gemm<256, 4>(p, stream);
     if (p.tile_n == 128) return launch_gemm<128, 6>(p, stream);
     if (p.n <= 128) return launch_gemm<128, 6>(p, stream);
@@ -702,7 +762,11 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     // [32768,768].[768,3072]: 1124 against 1032); below that the narrower one-CTA tiles spread better over the SMs.
     // Products with a short K are bound by their epilogue and by HBM (the batched [2048,128].[128,2048] product ran at
     // 3.5 TB/s in pairs against 4.9 TB/s alone): a pair has to wait for both CTAs' epilogues before it reuses an accumulator.
-    if (cta_group == 0 && p.n_copies == 0 && p.m > BM && p.k >= 8 * BK) {
+    // Rows of C off the 16-byte grid (a pitch such as 50257 f16) are written by the lanes, not by bulk stores: that epilogue
+    // is the longer one, and a pair would wait for both of its CTAs (logits [32768,768].[768,50257]: 2.64 ms alone, 2.79 ms in pairs).
+    const int64_t out_es = p.out_dtype == MHLO_DT_F32 ? 4 : 2;
+    const bool rows_on_grid = ((p.ldc > 0 ? p.ldc : p.n) * out_es) % 16 == 0 && (p.c_col0 * out_es) % 16 == 0 && aligned16(p.c);
+    if (cta_group == 0 && p.n_copies == 0 && p.m > BM && p.k >= 8 * BK && rows_on_grid) {
         const int64_t pair_tiles = (p.m + 2 * BM - 1) / (2 * BM) * ((p.n + 255) / 256) * p.batch0 * p.batch1;
         if (pair_tiles >= 60) return launch_gemm<256, 6, 2>(p, stream);
     }
@@ -752,7 +816,40 @@ __global__ void wait_expiry_probe_kernel(uint64_t limit_ns) {
         if (!done) atomicExch(&g_gemm_error, 90);
     }
 }
+
+struct PeerFlags {
+    uint64_t* arrays[8];  // arrays[r] = rank r's flag words (8 of them), in r's memory
+};
+
+// Completion barrier of an exchange whose stores went straight into the peers' memory. It runs in stream order after the
+// kernel that stored, so those stores are complete on this GPU's side; thread r publishes the epoch to rank r with a
+// system-scope release and then waits, with a time limit, for rank r's word in this rank's own array. Epochs only grow,
+// so a word that already holds a later epoch satisfies an earlier wait.
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerFlags f, int n_ranks, int rank, uint64_t epoch, uint64_t limit_ns) {
+    const int r = threadIdx.x;
+    if (r >= n_ranks || r == rank) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f.arrays[r] + rank), "l"(epoch) : "memory");
+    const uint64_t* mine = f.arrays[rank] + r;
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+        uint64_t seen;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+        if (seen >= epoch) break;
+        if (global_timer_ns() - start > limit_ns) {
+            atomicExch(&g_gemm_error, 95);
+            break;
+        }
+    }
+}
 }  // namespace
+
+bool gemm_peer_barrier_launch(uint64_t* const* flag_arrays, int n_ranks, int rank, uint64_t epoch, uint64_t limit_ns, cudaStream_t stream) {
+    PeerFlags f;
+    for (int r = 0; r < 8; ++r) f.arrays[r] = r < n_ranks ? flag_arrays[r] : nullptr;
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(f, n_ranks, rank, epoch, limit_ns);
+    return cudaGetLastError() == cudaSuccess;
+}
 
 bool gemm_wait_expiry_probe(uint64_t limit_ns, cudaStream_t stream) {
     wait_expiry_probe_kernel<<<1, 32, 0, stream>>>(limit_ns);

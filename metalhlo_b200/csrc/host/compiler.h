@@ -142,6 +142,7 @@ class Executable {
     };
     struct Step {
         std::string label;
+        std::string detail;  // result type of the op the step was lowered from (shown by the per-step profile)
         int launches = 1;
         std::function<int(const Ctx&)> run;  // returns an mhlo_cuda status
     };

@@ -333,9 +333,11 @@ class Lowering {
 
     // Steps go to the executable's list, or to the list of a loop region while one is being lowered.
     std::vector<Executable::Step>* sink_ = nullptr;
+    std::string detail_;  // result type of the op being lowered
     void add_step(const std::string& label, std::function<int(const Ctx&)> run, int launches = 1) {
         Executable::Step s;
         s.label = label;
+        s.detail = detail_;
         s.run = std::move(run);
         s.launches = launches;
         (sink_ ? *sink_ : exe_->steps_).push_back(std::move(s));
@@ -449,6 +451,7 @@ class Lowering {
         const std::string& n = op.name;
         if (op.results.empty()) return;  // ops without results have no effect here
         const TensorType& rt = op.result_types[0];
+        detail_ = rt.str();
         if (param_converts_ && is_parameter_convert(op)) return lower_parameter_convert(op);
         if (n == "constant") return lower_constant(op);
         if (n == "reshape" || n == "bitcast" || n == "dynamic_reshape") return lower_reshape(op);
@@ -1872,6 +1875,8 @@ int Executable::run_steps(const Ctx& c, bool debug, bool profile) {
     void *e0 = nullptr, *e1 = nullptr;
     if (profile) { mhlo_cuda_event_create(&e0); mhlo_cuda_event_create(&e1); }
     std::map<std::string, std::pair<int, double>> by_label;
+    const char* profile_env = std::getenv("METALHLO_PROFILE_GPU");
+    const bool every_step = profile && profile_env && profile_env[0] == '2';  // METALHLO_PROFILE_GPU=2: one line per step
     for (size_t i = 0; i < steps_.size(); ++i) {
         if (debug) fprintf(stderr, "[metalhlo] step %zu: %s\n", i, steps_[i].label.c_str());
         if (profile) mhlo_cuda_event_record(e0, stream);
@@ -1887,7 +1892,8 @@ int Executable::run_steps(const Ctx& c, bool debug, bool profile) {
             auto& slot = by_label[steps_[i].label];
             slot.first += 1;
             slot.second += ms;
-            if (ms > 0.5f) fprintf(stderr, "[metalhlo] step %zu %-40s %.3f ms\n", i, steps_[i].label.c_str(), ms);
+            if (ms > 0.5f || every_step)
+                fprintf(stderr, "[metalhlo] step %zu %-40s %-28s %.3f ms\n", i, steps_[i].label.c_str(), steps_[i].detail.c_str(), ms);
         }
     }
     if (profile) {

@@ -118,6 +118,9 @@ _PROTOTYPES = {
     "mhlo_cuda_ipc_close": (C.c_int, [_vp]),
     "mhlo_cuda_gemm_all_gather": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), C.POINTER(_vp), _i32, _i32, _i64, _i64, _i64,
                                             _vp, _i32, _vp]),
+    "mhlo_cuda_gemm_all_gather_tuned": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), C.POINTER(_vp), _i32, _i32, _i64, _i64,
+                                                  _i64, _vp, _i32, _vp, _i32, _vp]),
+    "mhlo_cuda_peer_barrier": (C.c_int, [C.POINTER(_vp), _i32, _i32, C.c_uint64, C.c_uint64, _vp]),
     "mhlo_cuda_convert_many": (C.c_int, [C.POINTER(ConvertJob), _i32, _vp]),
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mhlo_cuda_gather": (C.c_int, [_vp, _i32, C.POINTER(_i64), _i32, _vp, _i32, C.POINTER(_i64), _i32, C.POINTER(GatherDims),
