@@ -512,6 +512,20 @@ int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev,
                          const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream);
 
 /*
+ * C = A . B + bias + R: the product with a residual matrix R of C's shape and type (dense, [batch0, batch1, m, n]) added
+ * before the one rounding to the output type - the residual connection behind a projection, which would otherwise cost
+ * a pass of its own over C. On the tensor-core path (16-bit operands and result, rows of C on the 16-byte grid) the
+ * epilogue reads R tile by tile, under the tile's MMAs; other products run as mhlo_cuda_gemm_tuned followed by an elementwise sum. R may be C itself only on
+ * that second path; pass distinct buffers. residual_dev NULL makes this mhlo_cuda_gemm_tuned without activation.
+ * Stands where the reference's FusedOpType matmul is followed by an add of the residual stream (the reference has no
+ * fused form: Compiler/PassManager.swift registers residual-chain-fusion without an implementation).
+ */
+int mhlo_cuda_gemm_residual(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4],
+                            const void* b_dev, const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1,
+                            int64_t m, int64_t n, int64_t k, const void* bias_dev, const void* residual_dev,
+                            const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream);
+
+/*
  * C = A . B for a B (and C) split by columns over n_ranks GPUs, with the all-gather of C fused into the epilogue:
  * this rank computes columns [rank * n_local, (rank + 1) * n_local) of the [m, n_local * n_ranks] row-major result
  * and every tile is stored, straight from the epilogue, into that column range of all n_ranks copies of C
@@ -531,7 +545,8 @@ int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a
  * The same product with its launch knobs set by the caller. tuning: tile width and TMA ring depth as in
  * mhlo_cuda_gemm_tuned; NULL leaves them to the library.
  * copy_stores: 0 or 1 = every lane stores 16 bytes into each copy, 2 = one bulk tensor store (TMA, 32 rows x 128 bytes)
- * per copy from the staged tile. The results are bit-identical in every setting.
+ * per copy from the staged tile (products without an activation; with one, the copies keep the lane stores). The
+ * results are bit-identical in every setting.
  */
 int mhlo_cuda_gemm_all_gather_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2],
                                     const void* b_dev, const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks,

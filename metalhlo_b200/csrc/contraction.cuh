@@ -10,6 +10,7 @@ struct GemmProblem {
     const void* b;
     void* c;
     const void* bias;
+    const void* residual = nullptr;  // added to the product after the bias: same type, pitch and column offset as C; no activation
     int64_t as[4], bs[4];  // {batch0, batch1, row, col} element strides
     int64_t batch0, batch1, m, n, k;
     int32_t in_dtype, out_dtype, epilogue;

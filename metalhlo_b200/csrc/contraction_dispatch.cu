@@ -209,6 +209,43 @@ int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev,
     return mhlo_cuda_elementwise(in, n_in, prog, ni, c_dev, out_dtype, shape, 2, stream);
 }
 
+int mhlo_cuda_gemm_residual(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4], const void* b_dev,
+                            const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1, int64_t m, int64_t n, int64_t k,
+                            const void* bias_dev, const void* residual_dev, const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream) {
+    if (residual_dev == nullptr)
+        return mhlo_cuda_gemm_tuned(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_dev, batch0, batch1, m, n, k, bias_dev,
+                                    MHLO_EPILOGUE_NONE, tuning, stream);
+    if (!a_strides || !b_strides) return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_residual: null strides");
+    if (tuning && ((tuning->tile_n != 0 && tuning->tile_n != 128 && tuning->tile_n != 256) || tuning->stages < 0 || tuning->stages > 8 ||
+                   tuning->stages == 1 || tuning->cta_group < 0 || tuning->cta_group > 2 || (tuning->cta_group == 2 && tuning->tile_n == 128)))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "gemm_residual: tuning {tile_n %d, stages %d, cta_group %d} is not a configuration of the kernel",
+                    tuning->tile_n, tuning->stages, tuning->cta_group);
+    GemmProblem p;
+    p.a = a_dev; p.b = b_dev; p.c = c_dev; p.bias = bias_dev; p.residual = residual_dev;
+    for (int i = 0; i < 4; ++i) { p.as[i] = a_strides[i]; p.bs[i] = b_strides[i]; }
+    p.batch0 = batch0; p.batch1 = batch1; p.m = m; p.n = n; p.k = k;
+    p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.epilogue = MHLO_EPILOGUE_NONE;
+    if (tuning) { p.tile_n = tuning->tile_n; p.stages = tuning->stages; p.cta_group = tuning->cta_group; }
+    const int64_t out_es = out_dtype == MHLO_DT_F32 ? 4 : 2;
+    // the epilogue reads the residual in 16-byte pieces of a row: rows of C (and of the residual) on the 16-byte grid
+    if (gemm_tc_supported(p) && out_dtype != MHLO_DT_F32 && (n * out_es) % 16 == 0 && aligned16(c_dev) && aligned16(residual_dev))
+        return gemm_tc_launch(p, static_cast<cudaStream_t>(stream));
+    // otherwise the product first, then the sum as an elementwise pass over C
+    int st = mhlo_cuda_gemm_tuned(in_dtype, out_dtype, a_dev, a_strides, b_dev, b_strides, c_dev, batch0, batch1, m, n, k, bias_dev,
+                                  MHLO_EPILOGUE_NONE, tuning, stream);
+    if (st != MHLO_CUDA_OK) return st;
+    mhlo_cuda_view in[2];
+    memset(in, 0, sizeof in);
+    const int64_t rows = batch0 * batch1 * m;
+    in[0].base = c_dev; in[0].dtype = out_dtype; in[0].rank = 2;
+    in[0].shape[0] = rows; in[0].shape[1] = n; in[0].stride[0] = n; in[0].stride[1] = 1;
+    in[1] = in[0];
+    in[1].base = residual_dev;
+    mhlo_cuda_ew_inst prog[1] = {{MHLO_EW_ADD, 0, 1, 0, 0.0}};
+    const int64_t shape[2] = {rows, n};
+    return mhlo_cuda_elementwise(in, 2, prog, 1, c_dev, out_dtype, shape, 2, stream);
+}
+
 int mhlo_cuda_gemm_all_gather(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[2], const void* b_dev,
                               const int64_t b_strides[2], void* const* c_devs, int32_t n_ranks, int32_t rank, int64_t m, int64_t n_local,
                               int64_t k, const void* bias_dev, int32_t epilogue, mhlo_cuda_stream_t stream) {

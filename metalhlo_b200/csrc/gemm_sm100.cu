@@ -74,6 +74,7 @@ __device__ __forceinline__ uint32_t gelu_tanh_f16x2(uint32_t xbits) {
 struct GemmParams {
     void* c;
     const void* bias;
+    const void* residual;  // a matrix of C's type, pitch and column offset that is added to the product (after bias), or null
     int64_t m, n, k;
     int64_t batch0, batch1;
     int32_t tiles_m, tiles_n;
@@ -92,9 +93,12 @@ struct GemmParams {
 
 // Tensor maps of the further copies of C (GemmParams::copies, in the same order), used when the copies are written with
 // bulk tensor stores.
+template <bool PEER>
 struct PeerMaps {
     CUtensorMap m[7];
 };
+template <>
+struct PeerMaps<false> {};  // kernels that never store into copies carry no maps in their parameters
 
 // CTAS = 2: a pair of CTAs shares one (2 * BM) x BN tile; each stages its own BM rows of A and BN / 2 rows of B.
 template <int BN, int STAGES, int CTAS = 1>
@@ -125,12 +129,16 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
     *tn = static_cast<int>(t / rows_in_band);
 }
 
-template <int BN, int STAGES, int ACT, int CTAS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// MODE: 0 = the plain product, 1 = with the tensor maps of further copies of C (bulk stores into peers), 2 = with a residual
+// matrix added in the epilogue. The variants are separate instantiations so that the plain product carries neither the
+// maps in its parameters nor the residual's registers.
+template <int BN, int STAGES, int ACT, int CTAS, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)  // ten warps are allocated as twelve: 168 registers per thread is the ceiling
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p,
-                    const __grid_constant__ PeerMaps peer_maps) {
+                    const __grid_constant__ PeerMaps<MODE == 1> peer_maps) {
     using L = SmemLayout<BN, STAGES, CTAS>;
+    constexpr bool PEER = MODE == 1, RES = MODE == 2;
     constexpr bool kPair = CTAS == 2;
     constexpr int BNL = BN / CTAS;  // rows of B (columns of the tile) this CTA stages
     const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
@@ -154,7 +162,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         prefetch_tmap(&map_b);
         if (p.c_tma) {
             prefetch_tmap(&map_c);
-            for (int d = 0; d < p.n_copies; ++d) prefetch_tmap(&peer_maps.m[d]);
+            if constexpr (PEER)
+                for (int d = 0; d < p.n_copies; ++d) prefetch_tmap(&peer_maps.m[d]);
         }
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps * CTAS); }
@@ -292,6 +301,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int64_t tile = walker; tile < p.num_tiles; tile += walkers) {
             int bz, tm, tn;
             tile_coords(tile, p, &bz, &tm, &tn);
+            // The residual (16-bit results only): this thread's row of the warp's BN/2 columns, at most 256 bytes, asked for
+            // before the wait for the accumulator so that the loads run under the tile's MMAs. Pieces beyond the last
+            // column (n is a multiple of the 16-byte piece here) stay zero.
+            constexpr bool use_res = RES;
+            uint4 res_tile[16];
+            if (use_res) {
+                const int64_t rrow = (static_cast<int64_t>(tm) * CTAS + cta_rank) * BM + quarter * 32 + lane;
+                const int64_t rcol = static_cast<int64_t>(tn) * BN + col_begin;
+                const uint8_t* rp = static_cast<const uint8_t*>(p.residual) + static_cast<int64_t>(bz) * p.m * p.ldc * 2 + (rrow * p.ldc + p.c_col0 + rcol) * 2;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    res_tile[j] = make_uint4(0u, 0u, 0u, 0u);
+                    if (j * 8 < BN / 2 && rrow < p.m && rcol + j * 8 < p.n) res_tile[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
+                }
+            }
             const bool filled = kPair ? mbar_wait_pair(&tmem_full[acc], acc_phase) : mbar_wait(&tmem_full[acc], acc_phase);
             if (!filled) { atomicExch(&g_gemm_error, 4); break; }
             tc_fence_after();
@@ -325,16 +349,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int c0 = col_begin; c0 < col_end; c0 += chunk_cols) {
                 const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
                 uint4 out16[8];
-                // the chunk's accumulator columns in one go (both 32-column loads are in flight before the one wait)
-                uint32_t racc[64];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + c0);
-                tmem_ld32(taddr, racc);
-                if (chunk_cols > 32) tmem_ld32(taddr + 32, racc + 32);
-                tmem_ld_wait();
+                // this chunk's share of the residual pieces fetched at the start of the tile
+                uint4 res[8];
+                if (use_res) {
+                    const bool second = c0 != col_begin;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        res[j].x = second ? res_tile[8 + j].x : res_tile[j].x; res[j].y = second ? res_tile[8 + j].y : res_tile[j].y;
+                        res[j].z = second ? res_tile[8 + j].z : res_tile[j].z; res[j].w = second ? res_tile[8 + j].w : res_tile[j].w;
+                    }
+                }
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     if (half * 32 >= chunk_cols) break;
-                    const uint32_t* r = racc + half * 32;
+                    // 32 accumulator columns at a time: a 64-column load measured no faster and costs 32 more live registers,
+                    // which the 168 available here do not have
+                    uint32_t r[32];
+                    tmem_ld32(taddr + half * 32, r);
+                    tmem_ld_wait();
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -351,6 +384,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
                         }
                         __syncwarp();  // every lane has read the group before the next one is written
+                    }
+                    if (use_res) {  // 16-bit results without activation (the launcher sends every other product elsewhere)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 q4 = res[half * 4 + j];
+                            const uint32_t w4[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float lo, hi;
+                                if (p.out_dtype == MHLO_DT_BF16) {
+                                    lo = __uint_as_float(w4[q] << 16);
+                                    hi = __uint_as_float(w4[q] & 0xffff0000u);
+                                } else {
+                                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[q]));
+                                    lo = f2.x; hi = f2.y;
+                                }
+                                v[8 * j + 2 * q] += lo;
+                                v[8 * j + 2 * q + 1] += hi;
+                            }
+                        }
                     }
                     // f16 results take the tanh-form GELU in packed f16 arithmetic after the conversion below
                     constexpr bool kPackedGelu = ACT == MHLO_EPILOGUE_GELU_TANH;
@@ -403,8 +456,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int b1 = static_cast<int>(bz % p.batch1), b0 = static_cast<int>(bz / p.batch1);
                         tma_store_4d(&map_c, stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
                         // the same box into every other copy of C: bulk stores over NVLink, in the same group
-                        for (int d = 0; d < p.n_copies; ++d)
-                            tma_store_4d(&peer_maps.m[d], stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
+                        if constexpr (PEER)
+                            for (int d = 0; d < p.n_copies; ++d)
+                                tma_store_4d(&peer_maps.m[d], stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
                         tma_store_commit();
                     }
                     continue;
@@ -628,8 +682,9 @@ bool gemm_tc_supported(const GemmProblem& p) {
     return true;
 }
 
-template <int BN, int STAGES, int ACT, int CTAS>
+template <int BN, int STAGES, int ACT, int CTAS, int MODE = 0>
 static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
+    constexpr bool PEER = MODE == 1;
     using L = SmemLayout<BN, STAGES, CTAS>;
     const bool a_k = pr.as[3] == 1 || pr.k == 1;
     const bool b_k = pr.bs[2] == 1 || pr.k == 1;  // K-major B = [n][k] with k contiguous
@@ -646,6 +701,7 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     GemmParams p;
     p.c = pr.c;
     p.bias = pr.bias;
+    p.residual = pr.residual;
     p.m = pr.m; p.n = pr.n; p.k = pr.k;
     p.batch0 = pr.batch0; p.batch1 = pr.batch1;
     p.tiles_m = static_cast<int>((pr.m + BM * CTAS - 1) / (BM * CTAS));
@@ -672,25 +728,26 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
     // stores too (one more map per copy) when the problem asks for it; otherwise they keep the per-lane stores.
     CUtensorMap map_c;
     memset(&map_c, 0, sizeof map_c);
-    PeerMaps peer_maps;
+    PeerMaps<PEER> peer_maps;
     memset(&peer_maps, 0, sizeof peer_maps);
     p.c_tma = 0;
     static const bool tma_store_enabled = [] {
         const char* v = getenv("METALHLO_GEMM_TMA_STORE");
         return !(v && v[0] == '0');  // METALHLO_GEMM_TMA_STORE=0 keeps the per-lane stores
     }();
-    const bool copies_by_tma = pr.n_copies == 0 || pr.copy_stores == 2;
+    const bool copies_by_tma = pr.n_copies == 0 || (PEER && pr.copy_stores == 2);
     if (tma_store_enabled && aligned && copies_by_tma && pr.m * p.ldc * static_cast<int64_t>(out_es) % 16 == 0) {
         const size_t col_off = static_cast<size_t>(p.c_col0) * out_es;
         if (!output_map(&map_c, static_cast<uint8_t*>(pr.c) + col_off, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
             return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for C: %s", why.c_str());
-        for (int d = 0; d < pr.n_copies; ++d)
-            if (!output_map(&peer_maps.m[d], static_cast<uint8_t*>(pr.copies[d]) + col_off, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
+        if constexpr (PEER)
+            for (int d = 0; d < pr.n_copies; ++d)
+                if (!output_map(&peer_maps.m[d], static_cast<uint8_t*>(pr.copies[d]) + col_off, pr.out_dtype, pr.n, pr.m, p.ldc, pr.batch1, pr.batch0, &why))
                 return fail(MHLO_CUDA_EXECUTION_FAILED, "gemm: tensor map for copy %d of C: %s", d, why.c_str());
         p.c_tma = 1;
     }
 
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT, CTAS>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT, CTAS, MODE>;
     // the attribute belongs to the (kernel, device) pair: one flag per device ordinal
     static std::atomic<bool> attr_set[64];
     int attr_dev = 0;
@@ -731,6 +788,15 @@ static int launch_gemm_act(const GemmProblem& pr, cudaStream_t stream) {
 
 template <int BN, int STAGES, int CTAS = 1>
 static int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
+    // bulk stores into the copies: the instantiation that carries the copies' tensor maps exists for products without
+    // an activation; with one, the copies keep the lane stores
+    if (p.n_copies > 0 && p.copy_stores == 2 && p.epilogue == MHLO_EPILOGUE_NONE && p.residual == nullptr)
+        return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE, CTAS, 1>(p, stream);
+    if (p.residual != nullptr) {
+        if (p.epilogue != MHLO_EPILOGUE_NONE || p.out_dtype == MHLO_DT_F32 || p.n_copies > 0)
+            return fail(MHLO_CUDA_UNSUPPORTED, "gemm: a residual goes with a 16-bit result, no activation and no further copies of C");
+        return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE, CTAS, 2>(p, stream);
+    }
     switch (p.epilogue) {
         case MHLO_EPILOGUE_RELU: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_RELU, CTAS>(p, stream);
         case MHLO_EPILOGUE_GELU_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_GELU_TANH, CTAS>(p, stream);

@@ -955,6 +955,53 @@ class Lowering {
     // operands through their views, so no layout needs a copy.
     void lower_convolution(const Op& op) {
         if (op.operands.size() != 2) fail_compile("convolution takes two operands");
+        set(op.results[0], convolution_view(op, nullptr, MHLO_EPILOGUE_NONE, nullptr));
+    }
+
+    // act(convolution(x, w) + bias), the reference's FusedConvBiasActHandler (Compiler/CustomCallHandlers.swift:563-640): the
+    // call carries the convolution's attributes; bias (one value per output feature) and activation ride in the product's
+    // epilogue when the convolution runs as patch matrix x kernel matrix, and follow as one elementwise step otherwise.
+    void lower_fused_conv_bias_act(const Op& op, const std::string& cfg) {
+        if (op.operands.size() < 2) fail_unsupported("fused_conv_bias_act takes x, the weights and an optional bias");
+        const TensorType& rt = op.result_types[0];
+        const bool has_bias = json_bool(cfg, "has_bias", true) && op.operands.size() >= 3;
+        const std::string act = json_string(cfg, "activation", "none");
+        int epi = MHLO_EPILOGUE_NONE, ew = -1;
+        if (act == "relu") { epi = MHLO_EPILOGUE_RELU; ew = MHLO_EW_RELU; }
+        else if (act == "sigmoid" || act == "logistic") { epi = MHLO_EPILOGUE_SIGMOID; ew = MHLO_EW_LOGISTIC; }
+        else if (act == "tanh") { epi = MHLO_EPILOGUE_TANH; ew = MHLO_EW_TANH; }
+        else if (act == "silu" || act == "swish") { epi = MHLO_EPILOGUE_SILU; ew = MHLO_EW_SILU; }
+        else if (act != "none") fail_unsupported("fused_conv_bias_act: activation '" + act + "'");
+        const int64_t ofd = op.int_attr("output_feature_dimension", rt.rank() - 1);
+        View bias;
+        if (has_bias) {
+            bias = get(op.operands[2]);
+            if (bias.type.count() != rt.shape[static_cast<size_t>(ofd)] || bias.type.dtype != rt.dtype)
+                fail_unsupported("fused_conv_bias_act: bias " + bias.type.str() + " for " + rt.str());
+            bias = materialize(expand_to(bias, {rt.shape[static_cast<size_t>(ofd)]}), "fused_conv_bias_act.bias");
+        }
+        bool fused = false;
+        View y = convolution_view(op, has_bias ? &bias : nullptr, epi, &fused);
+        if (fused || (!has_bias && ew < 0)) return set(op.results[0], y);
+        std::vector<View> ins = {y};
+        std::vector<mhlo_cuda_ew_inst> prog;
+        int cur = 0;
+        if (has_bias) {
+            View spread = bias;  // one value per output feature, repeated along every other dimension
+            spread.type.shape = rt.shape;
+            spread.strides.assign(rt.shape.size(), 0);
+            spread.strides[static_cast<size_t>(ofd)] = 1;
+            ins.push_back(spread);
+            prog.push_back({MHLO_EW_ADD, 0, 1, 0, 0.0});
+            cur = 2;
+        }
+        if (ew >= 0) prog.push_back({ew, cur, cur, cur, 0.0});
+        set(op.results[0], emit_elementwise(ins, prog, rt, "fused_conv_bias_act.epilogue"));
+    }
+
+    // The convolution as a view of its result. bias / epilogue: asked to ride in the product's epilogue; *fused says whether they did.
+    View convolution_view(const Op& op, const View* bias, int epilogue, bool* fused) {
+        if (fused) *fused = false;
         const View& x = get(op.operands[0]);
         const View& w = get(op.operands[1]);
         const TensorType& rt = op.result_types[0];
@@ -1042,7 +1089,7 @@ class Lowering {
             add_step("convolution", [=](const Ctx& cx) {
                 return mhlo_cuda_convolution(dt, bind(dx, cx).base, bind(dw, cx).base, const_cast<void*>(bind(dout, cx).base), &c, cx.stream);
             });
-            return set(op.results[0], out);
+            return out;
         }
         // ---- patch matrix + GEMM
         const int64_t M = c.batch * out_positions, Kc = kernel_volume * Cg, pitch = (Kc + 7) / 8 * 8;
@@ -1081,9 +1128,16 @@ class Lowering {
         keep_alive(cols);
         keep_alive(prod);
         std::array<int64_t, 4> as = {0, M * pitch, pitch, 1}, bs = {0, Og * wm.strides[1], wm.strides[0], wm.strides[1]};
-        add_step("convolution.gemm", [=](const Ctx& cx) {
+        // bias and activation in the product's epilogue: one bias vector for the whole product, so one group only
+        const bool in_epilogue = G == 1 && (bias != nullptr || epilogue != MHLO_EPILOGUE_NONE);
+        DevView dbias;
+        if (in_epilogue && bias) { dbias = dev(*bias); keep_alive(*bias); }
+        const bool with_bias = in_epilogue && bias != nullptr;
+        const int epi = in_epilogue ? epilogue : MHLO_EPILOGUE_NONE;
+        if (fused) *fused = in_epilogue;
+        add_step(in_epilogue ? "convolution.gemm+epilogue" : "convolution.gemm", [=](const Ctx& cx) {
             return mhlo_cuda_gemm(dt, dt, bind(dcols, cx).base, as.data(), bind(dwm, cx).base, bs.data(), const_cast<void*>(bind(dprod, cx).base), 1, G,
-                                  M, Og, Kc, nullptr, MHLO_EPILOGUE_NONE, cx.stream);
+                                  M, Og, Kc, with_bias ? bind(dbias, cx).base : nullptr, epi, cx.stream);
         });
         // [G, batch, spatial.., Og] -> canonical [batch, spatial.., O] -> the result's own dimension order
         View canon = prod;
@@ -1119,7 +1173,7 @@ class Lowering {
         out.strides[ob] = canon.strides[0];
         for (int d = 0; d < ns; ++d) out.strides[static_cast<size_t>(osp[d])] = canon.strides[static_cast<size_t>(d) + 1];
         out.strides[ofd] = canon.strides[static_cast<size_t>(ns) + 1];
-        set(op.results[0], out);
+        return out;
     }
 
     // stablehlo.reduce_window of one operand with a recognised reducer; the operand is read through its view.
@@ -1689,15 +1743,23 @@ void Lowering::lower_custom_call(const Op& op) {
         for (int v : op.operands) ins.push_back(get(v));
         return set(op.results[0], emit_elementwise(ins, prog, rt, target));
     }
+    if (target == "fused_conv_bias_act") return lower_fused_conv_bias_act(op, cfg);
     if (target == "fused_matmul_bias_activation") {
         // act(x . w + bias): x [.., M, K] (leading dims flattened), w [K, N], bias [N] (optional)
         View x = materialize(operand(0), target + ".x"), w = operand(1);
         if (w.type.rank() != 2) fail_unsupported(target + ": weight must be rank 2");
         const int64_t K = w.type.shape[0], N = w.type.shape[1];
         const int64_t M = K ? x.type.count() / K : 0;
-        const bool has_bias = op.operands.size() > 2;
-        View bias;
+        const bool has_residual = json_bool(cfg, "has_residual", false);  // the last operand: a tensor of the result's type added to the product
+        const bool has_bias = json_bool(cfg, "has_bias", op.operands.size() > (has_residual ? 3u : 2u));
+        if (op.operands.size() != 2u + (has_bias ? 1u : 0u) + (has_residual ? 1u : 0u)) fail_unsupported(target + ": operand count does not match has_bias / has_residual");
+        View bias, residual;
         if (has_bias) bias = materialize(expand_to(operand(2), {N}), target + ".bias");
+        if (has_residual) {
+            residual = operand(static_cast<int>(op.operands.size()) - 1);
+            if (!(residual.type == rt)) fail_unsupported(target + ": the residual must have the result's type");
+            if (!is_dense(residual)) residual = materialize(residual, target + ".residual");
+        }
         const std::string act = json_string(cfg, "activation", "none");
         int epi = MHLO_EPILOGUE_NONE;
         if (act == "gelu" || act == "gelu_tanh") epi = MHLO_EPILOGUE_GELU_TANH;
@@ -1707,10 +1769,12 @@ void Lowering::lower_custom_call(const Op& op) {
         else if (act == "tanh") epi = MHLO_EPILOGUE_TANH;
         else if (act == "sigmoid" || act == "logistic") epi = MHLO_EPILOGUE_SIGMOID;
         else if (act != "none") fail_unsupported(target + ": activation '" + act + "'");
+        if (has_residual && epi != MHLO_EPILOGUE_NONE) fail_unsupported(target + ": a residual goes with activation 'none'");
         View out = dense_view(new_arena(rt.bytes()), rt);
-        DevView dx = dev(x), dw = dev(w), dbias, dout = dev(out);
+        DevView dx = dev(x), dw = dev(w), dbias, dres, dout = dev(out);
         keep_alive(x); keep_alive(w); keep_alive(out);
         if (has_bias) { dbias = dev(bias); keep_alive(bias); }
+        if (has_residual) { dres = dev(residual); keep_alive(residual); }
         const int in_dt = static_cast<int>(x.type.dtype), out_dt = static_cast<int>(rt.dtype);
         std::array<int64_t, 4> as = {0, 0, K, 1}, bs = {0, 0, w.strides[0], w.strides[1]};
         GemmCase gc;
@@ -1719,6 +1783,10 @@ void Lowering::lower_custom_call(const Op& op) {
         mhlo_cuda_gemm_tuning gt{0, 0, 0, 0};
         const bool tuned = lookup_gemm_tuning(gc, &gt);
         add_step(tuned ? target + " [tuned]" : target, [=](const Ctx& c) {
+            if (has_residual)
+                return mhlo_cuda_gemm_residual(in_dt, out_dt, bind(dx, c).base, as.data(), bind(dw, c).base, bs.data(),
+                                               const_cast<void*>(bind(dout, c).base), 1, 1, M, N, K, has_bias ? bind(dbias, c).base : nullptr,
+                                               bind(dres, c).base, tuned ? &gt : nullptr, c.stream);
             return mhlo_cuda_gemm_tuned(in_dt, out_dt, bind(dx, c).base, as.data(), bind(dw, c).base, bs.data(),
                                         const_cast<void*>(bind(dout, c).base), 1, 1, M, N, K, has_bias ? bind(dbias, c).base : nullptr,
                                         epi, tuned ? &gt : nullptr, c.stream);

@@ -10,6 +10,7 @@
 #include <map>
 
 #include "compiler.h"
+#include "numeric.h"
 
 namespace mhlo {
 
@@ -524,6 +525,178 @@ void optimize_loop_bodies(Function& f, const CompileOptions& options) {
     f.compact();
 }
 
+// The reference's custom-call handlers beyond the ones this backend has kernels for, restated as the StableHLO ops their
+// MPSGraph bodies compute (Sources/MetalHLOCore/Compiler/CustomCallHandlers.swift): fused_batch_norm (:405-447),
+// fused_rope (:715-845), fused_ffn (:848-925), fused_depth_attention (:1075-1135); fused_conv_bias_act is lowered as it is. A module
+// that arrives with these targets already in it (written by hand, or by the reference's own passes) then lowers like the
+// unfused program; the pass pipeline may fuse the pieces again in this backend's own way.
+bool expand_fused_custom_calls(Function& f) {
+    bool any = false;
+    std::vector<Op> out;
+    auto emit = [&](Op o) { const int v = o.results[0]; out.push_back(std::move(o)); return v; };
+    auto float_splat = [&](const TensorType& t, double value) {
+        Op k;
+        k.name = "constant";
+        k.dialect = "stablehlo";
+        Attr a;
+        a.kind = Attr::Dense;
+        a.dense_type = t;
+        a.splat = true;
+        a.dense.assign(dtype_size(t.dtype), 0);
+        encode_scalar(t.dtype, value, static_cast<int64_t>(value), a.dense.data());
+        k.attrs["value"] = a;
+        k.result_types = {t};
+        k.results = {f.new_value(t, "")};
+        return emit(std::move(k));
+    };
+    auto unary = [&](const char* name, int x) { return emit(simple_op(f, name, {x}, f.type_of(x))); };
+    auto binary = [&](const char* name, int a, int b) { return emit(simple_op(f, name, {a, b}, f.type_of(a))); };
+    auto slice_last = [&](int x, int64_t lo, int64_t hi) {
+        TensorType t = f.type_of(x);
+        std::vector<int64_t> st(t.shape.size(), 0), lim = t.shape, strides(t.shape.size(), 1);
+        st.back() = lo;
+        lim.back() = hi;
+        t.shape.back() = hi - lo;
+        Op o = simple_op(f, "slice", {x}, t);
+        o.attrs["start_indices"] = Attr::make_ints(st);
+        o.attrs["limit_indices"] = Attr::make_ints(lim);
+        o.attrs["strides"] = Attr::make_ints(strides);
+        return emit(std::move(o));
+    };
+    // v spread to `to` by the trailing-dimension rule of the reference's graph arithmetic (extents equal or 1)
+    auto broadcast_trailing = [&](int v, const TensorType& to, const std::string& what) {
+        const TensorType vt = f.type_of(v);
+        if (vt.shape == to.shape) return v;
+        const int shift = to.rank() - vt.rank();
+        if (shift < 0) fail_unsupported(what + ": " + vt.str() + " has more dimensions than " + to.str());
+        std::vector<int64_t> dims;
+        for (int d = 0; d < vt.rank(); ++d) {
+            if (vt.shape[d] != 1 && vt.shape[d] != to.shape[d + shift]) fail_unsupported(what + ": " + vt.str() + " does not spread over " + to.str());
+            dims.push_back(d + shift);
+        }
+        TensorType rt = to;
+        rt.dtype = vt.dtype;
+        Op o = simple_op(f, "broadcast_in_dim", {v}, rt);
+        o.attrs["broadcast_dimensions"] = Attr::make_ints(dims);
+        return emit(std::move(o));
+    };
+    auto matmul_call = [&](int x, int w, const std::string& act, const std::string& what) {
+        const TensorType xt = f.type_of(x), wt = f.type_of(w);
+        if (wt.rank() != 2 || xt.rank() < 1 || xt.shape.back() != wt.shape[0]) fail_unsupported(what + ": " + xt.str() + " . " + wt.str());
+        TensorType rt = xt;
+        rt.shape.back() = wt.shape[1];
+        Op o = simple_op(f, "custom_call", {x, w}, rt);
+        o.attrs["call_target_name"] = Attr::make_string("fused_matmul_bias_activation");
+        o.attrs["backend_config"] = Attr::make_string("{\"activation\":\"" + act + "\",\"has_bias\":false}");
+        return emit(std::move(o));
+    };
+    // the last op of an expansion takes the custom call's result value
+    auto finish = [&](int v, const Op& call) {
+        if (!(f.type_of(v) == call.result_types[0]))
+            fail_unsupported("@" + call.str_attr("call_target_name") + ": the operands give " + f.type_of(v).str() + ", the call declares " + call.result_types[0].str());
+        Op& last = out.back();
+        if (last.results.size() != 1 || last.results[0] != v) {  // the value is an operand passed through: copy it
+            Op c = simple_op(f, "copy", {v}, f.type_of(v));
+            out.push_back(std::move(c));
+        }
+        out.back().results = call.results;
+    };
+    for (Op& op : f.ops) {
+        const std::string target = !op.dead && op.name == "custom_call" ? op.str_attr("call_target_name") : "";
+        if (target != "fused_batch_norm" && target != "fused_rope" && target != "fused_ffn" && target != "fused_depth_attention") {
+            out.push_back(std::move(op));
+            continue;
+        }
+        if (op.results.size() != 1) fail_unsupported("@" + target + " gives one result");
+        const std::string cfg = op.str_attr("backend_config", "{}");
+        const Op call = op;
+        any = true;
+        if (target == "fused_batch_norm") {
+            // (x - mean) / sqrt(variance + eps) * gamma + beta with the statistics along x's last dimension
+            if (call.operands.size() < 5) fail_unsupported("@fused_batch_norm takes x, gamma, beta, mean, variance");
+            const TensorType xt = f.type_of(call.operands[0]);
+            for (int i = 1; i < 5; ++i) {
+                const TensorType st = f.type_of(call.operands[i]);
+                if (xt.rank() < 1 || st.rank() != 1 || st.shape[0] != xt.shape.back())
+                    fail_unsupported("@fused_batch_norm: statistics of shape " + st.str() + " for " + xt.str() + " (one value per element of the last dimension expected)");
+            }
+            Op bn = simple_op(f, "batch_norm_inference", {call.operands[0], call.operands[1], call.operands[2], call.operands[3], call.operands[4]}, xt);
+            bn.attrs["epsilon"] = Attr::make_float(json_number(cfg, "eps", json_number(cfg, "epsilon", 1e-5)));
+            bn.attrs["feature_index"] = Attr::make_int(xt.rank() - 1);
+            finish(emit(std::move(bn)), call);
+        } else if (target == "fused_ffn") {
+            // act(x . up) . down; no biases, as in the reference's handler
+            if (call.operands.size() < 3) fail_unsupported("@fused_ffn takes x, the up-projection and the down-projection");
+            std::string act = json_string(cfg, "activation", "gelu");
+            if (act == "gelu" || act == "gelu_approximate" || act == "geluApproximate") act = "gelu_tanh";
+            else if (act == "gelu_exact") act = "gelu_erf";
+            else if (act == "swish") act = "silu";
+            else if (act != "relu" && act != "sigmoid" && act != "tanh" && act != "silu") act = "none";
+            const int h = matmul_call(call.operands[0], call.operands[1], act, "@fused_ffn");
+            finish(matmul_call(h, call.operands[2], "none", "@fused_ffn"), call);
+        } else if (target == "fused_rope") {
+            // rotation of the two halves of the last dimension: [x1 cos - x2 sin, x1 sin + x2 cos]
+            if (call.operands.size() < 2) fail_unsupported("@fused_rope takes x and the frequencies");
+            const int x = call.operands[0], fr = call.operands[1];
+            const TensorType xt = f.type_of(x), ft = f.type_of(fr);
+            if (xt.rank() < 2 || ft.rank() < 1 || xt.shape.back() % 2 != 0) fail_unsupported("@fused_rope: " + xt.str() + " with frequencies " + ft.str());
+            const int64_t hd = xt.shape.back(), half = hd / 2;
+            const int x1 = slice_last(x, 0, half), x2 = slice_last(x, half, hd);
+            int c, s;
+            if (ft.shape.back() == hd) {            // cosines in the first half, sines in the second
+                c = slice_last(fr, 0, half);
+                s = slice_last(fr, half, hd);
+            } else if (ft.shape.back() == half) {   // angles
+                c = unary("cosine", fr);
+                s = unary("sine", fr);
+            } else {                                 // cosines as given; sines from a third operand, else the sine of the operand
+                c = fr;
+                s = call.operands.size() >= 3 ? call.operands[2] : unary("sine", fr);
+            }
+            const TensorType ht = f.type_of(x1);
+            c = broadcast_trailing(c, ht, "@fused_rope");
+            s = broadcast_trailing(s, ht, "@fused_rope");
+            const int o1 = binary("subtract", binary("multiply", x1, c), binary("multiply", x2, s));
+            const int o2 = binary("add", binary("multiply", x1, s), binary("multiply", x2, c));
+            Op cat = simple_op(f, "concatenate", {o1, o2}, xt);
+            cat.attrs["dimension"] = Attr::make_int(xt.rank() - 1);
+            finish(emit(std::move(cat)), call);
+        } else {  // fused_depth_attention: softmax(q . k^T * scale) . v over a short key axis
+            if (call.operands.size() < 3) fail_unsupported("@fused_depth_attention takes query, keys and values");
+            const int q = call.operands[0], k = call.operands[1], v = call.operands[2];
+            const TensorType qt = f.type_of(q), kt = f.type_of(k), vt = f.type_of(v);
+            if (kt.rank() != 3 || vt.rank() != 3 || (qt.rank() != 3 && qt.rank() != 2) || qt.shape[0] != kt.shape[0] || qt.shape.back() != kt.shape[2] ||
+                vt.shape[0] != kt.shape[0] || vt.shape[1] != kt.shape[1])
+                fail_unsupported("@fused_depth_attention: query " + qt.str() + ", keys " + kt.str() + ", values " + vt.str());
+            auto batched_dot = [&](int a, int b, int64_t a_contract, int64_t b_contract, std::vector<int64_t> shape) {
+                TensorType rt = f.type_of(a);
+                rt.shape = std::move(shape);
+                Op d = simple_op(f, "dot_general", {a, b}, rt);
+                d.attrs["lhs_batching_dimensions"] = Attr::make_ints({0});
+                d.attrs["rhs_batching_dimensions"] = Attr::make_ints({0});
+                d.attrs["lhs_contracting_dimensions"] = Attr::make_ints({a_contract});
+                d.attrs["rhs_contracting_dimensions"] = Attr::make_ints({b_contract});
+                return emit(std::move(d));
+            };
+            const bool q3 = qt.rank() == 3;
+            const int64_t B = kt.shape[0], depth = kt.shape[1];
+            std::vector<int64_t> score_shape = q3 ? std::vector<int64_t>{B, qt.shape[1], depth} : std::vector<int64_t>{B, depth};
+            int sc = batched_dot(q, k, qt.rank() - 1, 2, score_shape);
+            const double scale = json_number(cfg, "scale", 1.0);
+            if (scale != 1.0) sc = binary("multiply", sc, float_splat(f.type_of(sc), scale));
+            Op sm = simple_op(f, "custom_call", {sc}, f.type_of(sc));
+            sm.attrs["call_target_name"] = Attr::make_string("fused_softmax");
+            sm.attrs["backend_config"] = Attr::make_string("{\"axis\":-1}");
+            const int w = emit(std::move(sm));
+            std::vector<int64_t> out_shape = q3 ? std::vector<int64_t>{B, qt.shape[1], vt.shape[2]} : std::vector<int64_t>{B, vt.shape[2]};
+            finish(batched_dot(w, v, f.type_of(w).rank() - 1, 1, out_shape), call);
+        }
+    }
+    f.ops.swap(out);
+    if (any) f.compact();
+    return any;
+}
+
 Function flatten_main(Module& m) {
     // calls, loops and conditionals can hide each other (a loop body that calls, a callee that loops or branches): repeat
     // until nothing changes
@@ -535,7 +708,8 @@ Function flatten_main(Module& m) {
         const bool d = flatten_maps(main);
         const bool e = flatten_top_k(main);
         const bool g = drop_optimization_barriers(main);
-        return a || b || c || d || e || g;
+        const bool h = expand_fused_custom_calls(main);
+        return a || b || c || d || e || g || h;
     };
     for (int round = 0; round < kMaxInlineRounds; ++round) {
         const bool top = all();

@@ -1242,6 +1242,8 @@ class Parser {
         if (n == "custom_call") {
             if (const Attr* a = op->attr("call_target_name"))
                 if (a->kind == Attr::Keyword) op->attrs["call_target_name"] = Attr::make_string(a->s);
+            // the fused convolution call carries the attributes of the convolution it stands for
+            if (op->str_attr("call_target_name") == "fused_conv_bias_act") normalise_convolution(op);
         }
         if (n == "select" && op->result_types.size() == 1 && !op->operands.empty()) {
             // "tensor<i1>, tensor<f32>" was parsed as a bare list: result = last, already handled
@@ -1263,7 +1265,7 @@ class Parser {
     // short form "stablehlo.convolution %x, %w window_strides = [..], padding = [[..]]"), window_strides, padding
     // (flat, rank x 2), lhs_dilation, rhs_dilation, window_reversal, feature_group_count, batch_group_count.
     void normalise_convolution(Op* op) {
-        if (op->operands.size() != 2 || op->result_types.empty()) return;
+        if (op->operands.size() < 2 || op->result_types.empty()) return;  // two operands, or a fused call's x, w, bias
         const int rank = fn_->values[op->operands[0]].type.rank();
         const int ns = rank - 2;
         if (ns < 0) fail_parse("convolution of a tensor of rank " + std::to_string(rank));

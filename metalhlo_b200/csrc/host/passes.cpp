@@ -950,6 +950,120 @@ bool fuse_matmul_bias_act(Function& f) {
     return any;
 }
 
+// Residual add behind a projection: s = add(r, y) with y = fused_matmul_bias_activation(x, w[, bias]) without activation
+// and no other user. The sum moves into the product's epilogue,
+//   s = custom_call @fused_matmul_bias_activation(x, w[, bias], r) {has_residual}
+// which adds r before the one rounding to the result type, so y is never written or read back. The fused op takes the
+// place of the add, where r and the product's operands are all defined. Part of "residual-chain-fusion", which the
+// reference registers without an implementation (Compiler/PassManager.swift:214-221).
+bool fuse_matmul_residual(Function& f) {
+    Graph g(f);
+    bool changed = false;
+    for (size_t idx = 0; idx < f.ops.size(); ++idx) {
+        Op& o = f.ops[idx];
+        if (o.dead || o.name != "add" || o.operands.size() != 2 || o.results.size() != 1) continue;
+        const TensorType st = o.result_types[0];
+        if (!is_float(st.dtype) || st.dtype == DType::F64) continue;
+        for (int side = 0; side < 2; ++side) {
+            const int y = o.operands[side], r = o.operands[1 - side];
+            Op* mm = g.def_mut(y);
+            if (!mm || mm->dead || mm->results.size() != 1 || y == r) continue;
+            if (g.n_users(y) != 1 || !(g.type(y) == st) || !(g.type(r) == st)) continue;
+            std::string cfg;
+            if (mm->name == "custom_call") {
+                if (mm->str_attr("call_target_name") != "fused_matmul_bias_activation") continue;
+                cfg = mm->str_attr("backend_config");
+                if (cfg.find("\"activation\":\"none\"") == std::string::npos || cfg.find("has_residual") != std::string::npos) continue;
+            } else if (mm->name == "dot_general" || mm->name == "dot") {
+                // a bare product x [.., K] . w [K, N], the form matmul-bias-act-fusion takes when a bias or activation follows
+                if (mm->operands.size() != 2) continue;
+                const TensorType &xt = g.type(mm->operands[0]), &wt = g.type(mm->operands[1]);
+                if (wt.rank() != 2 || xt.rank() < 1) continue;
+                if (mm->name == "dot_general") {
+                    DotDims d = dot_dims(*mm);
+                    if (!d.lb.empty() || !d.rb.empty() || d.lc != std::vector<int64_t>{xt.rank() - 1} || d.rc != std::vector<int64_t>{0}) continue;
+                } else if (xt.rank() > 2) continue;
+                cfg = "{\"activation\":\"none\",\"has_bias\":false}";
+            } else {
+                continue;
+            }
+            std::vector<int> operands = mm->operands;
+            operands.push_back(r);
+            std::string fused_cfg = cfg;
+            fused_cfg.insert(fused_cfg.rfind('}'), ",\"has_residual\":true");
+            make_custom_call(o, "fused_matmul_bias_activation", operands, fused_cfg);
+            mm->dead = true;
+            mm->results.clear();
+            changed = true;
+            break;
+        }
+    }
+    if (changed) f.compact();
+    return changed;
+}
+
+// convolution -> add(broadcast_in_dim(bias)) -> optional relu / sigmoid / tanh / silu becomes
+//   custom_call @fused_conv_bias_act(x, w, bias) {the convolution's attributes, activation, has_bias}
+// as in the reference (detector Compiler/Analyzer.swift:405-495, rewrite Compiler/PassManager.swift:1325-1410). The bias is one
+// value per output feature; the convolution and the sum have no other user. Here the fused call saves the separate
+// elementwise step: bias and activation ride in the epilogue of the convolution's product.
+bool fuse_conv_bias_act(Function& f) {
+    Graph g(f);
+    bool changed = false;
+    for (size_t idx = 0; idx < f.ops.size(); ++idx) {
+        Op& conv = f.ops[idx];
+        if (conv.dead || conv.name != "convolution" || conv.results.size() != 1 || conv.operands.size() != 2) continue;
+        const int y = conv.results[0];
+        const TensorType yt = conv.result_types[0];
+        if (!is_float(yt.dtype) || g.n_users(y) != 1) continue;
+        Op* add = nullptr;
+        for (int u : g.users[y]) add = &f.ops[static_cast<size_t>(u)];
+        if (!add || add->dead || add->name != "add" || add->operands.size() != 2 || add->results.size() != 1) continue;
+        const int bcast_v = add->operands[0] == y ? add->operands[1] : add->operands[0];
+        if (bcast_v == y) continue;
+        const Op* bc = g.def(bcast_v);
+        if (!bc || bc->name != "broadcast_in_dim" || bc->operands.size() != 1) continue;
+        const int64_t ofd = conv.int_attr("output_feature_dimension", yt.rank() - 1);
+        const TensorType& bt = g.type(bc->operands[0]);
+        if (bt.rank() != 1 || bt.dtype != yt.dtype || bc->int_list("broadcast_dimensions") != std::vector<int64_t>{ofd} ||
+            bt.shape[0] != yt.shape[static_cast<size_t>(ofd)] || !(bc->result_types[0] == yt))
+            continue;
+        Op* root = add;
+        std::string act = "none";
+        const int s = add->results[0];
+        if (g.n_users(s) == 1) {
+            Op* a = nullptr;
+            for (int u : g.users[s]) a = &f.ops[static_cast<size_t>(u)];
+            if (a && !a->dead && a->results.size() == 1 && a->result_types[0] == yt) {
+                double zero = 1.0;
+                if (a->name == "maximum" && a->operands.size() == 2) {
+                    const int other = a->operands[0] == s ? a->operands[1] : a->operands[0];
+                    if (other != s && scalar_constant(g, other, &zero) && zero == 0.0) { act = "relu"; root = a; }
+                } else if (a->name == "logistic") { act = "sigmoid"; root = a; }
+                else if (a->name == "tanh") { act = "tanh"; root = a; }
+                else if (a->name == "custom_call" && a->operands.size() == 1 &&
+                         (a->str_attr("call_target_name") == "fused_silu" || a->str_attr("call_target_name") == "fused_relu")) {
+                    act = a->str_attr("call_target_name") == "fused_silu" ? "silu" : "relu";
+                    root = a;
+                }
+            }
+        }
+        const std::map<std::string, Attr> conv_attrs = conv.attrs;
+        make_custom_call(*root, "fused_conv_bias_act", {conv.operands[0], conv.operands[1], bc->operands[0]},
+                         "{\"activation\":\"" + act + "\",\"has_bias\":true}");
+        for (const auto& kv : conv_attrs) root->attrs[kv.first] = kv.second;
+        if (root != add) { add->dead = true; add->results.clear(); }
+        conv.dead = true;
+        conv.results.clear();
+        changed = true;
+    }
+    if (changed) {
+        f.compact();
+        dce(f);
+    }
+    return changed;
+}
+
 // ---- producer-consumer fusion of elementwise chains -----------------------------------------------------------------------
 
 bool fusable_elementwise(const Op& o) {
@@ -1189,14 +1303,18 @@ const std::vector<PassDef>& registry() {
         {"gelu-fusion", fuse_activations},
         {"softmax-fusion", fuse_softmax},
         {"matmul-bias-act-fusion", fuse_matmul_bias_act},
-        {"conv-bias-act-fusion", [](Function&) { return false; }},
+        {"conv-bias-act-fusion", fuse_conv_bias_act},
         // phase 4: generic fusion
         {"producer-consumer-fusion", fuse_producer_consumer},
         {"sibling-fusion", [](Function&) { return false; }},            // analysis-only in the reference
         {"elementwise-chain-fusion", [](Function&) { return false; }},  // no-op in the reference
         // phase 5: cross-layer
         {"cross-layer-fusion", [](Function&) { return false; }},
-        {"residual-chain-fusion", fuse_residual_norm},
+        {"residual-chain-fusion", [](Function& f) {
+             const bool products = fuse_matmul_residual(f);  // first: a sum taken by a product no longer feeds fuse_residual_norm
+             const bool norms = fuse_residual_norm(f);
+             return products || norms;
+         }},
         // phase 6: layout
         {"layout-assignment", [](Function&) { return false; }},  // analysis-only in the reference
         {"transpose-folding", canonicalize_transpose},

@@ -366,6 +366,15 @@ struct Sharder {
                 for (size_t i = from; i < op.operands.size(); ++i)
                     if (ax(op.operands[i]) >= 0) refuse(op, "@" + target + " has a split parameter operand");
             };
+            if (target == "fused_conv_bias_act") {  // the convolution's rule; the bias is a parameter
+                if (op.operands.size() < 2 || ax(op.operands[1]) >= 0) refuse(op, "@" + target + " has a split kernel");
+                if (op.int_attr("batch_group_count", 1) != 1) refuse(op, "@" + target + " with batch groups");
+                if (d != op.int_attr("input_batch_dimension", 0)) refuse(op, "@" + target + " is split along a feature or spatial axis");
+                rest_replicated(2);
+                set_results(op, static_cast<int>(op.int_attr("output_batch_dimension", 0)));
+                out.push_back(std::move(op));
+                return;
+            }
             if (target == "fused_scaled_dot_product_attention") {
                 if (rank != 4 || d > 1) refuse(op, "@" + target + " is split along the sequence or head dimension");
                 for (size_t i = 0; i < 3 && i < op.operands.size(); ++i) op.operands[i] = demand(op.operands[i], d, op);
@@ -373,7 +382,17 @@ struct Sharder {
             } else if (target == "fused_layer_norm" || target == "fused_rms_norm" || target == "fused_softmax" || target == "fused_gelu" ||
                        target == "fused_silu" || target == "fused_matmul_bias_activation") {
                 if (d == rank - 1) refuse(op, "@" + target + " is split along the axis it works on");
-                rest_replicated(1);
+                // a product's residual (its last operand) has the result's shape and is split with the activations
+                const bool residual = target == "fused_matmul_bias_activation" && op.operands.size() > 2 &&
+                                      op.str_attr("backend_config").find("\"has_residual\":true") != std::string::npos;
+                if (residual) {
+                    const int r = op.operands.back();
+                    op.operands.pop_back();
+                    rest_replicated(1);
+                    op.operands.push_back(demand(r, d, op));
+                } else {
+                    rest_replicated(1);
+                }
             } else {
                 refuse(op, "@" + target + " of a split value");
             }

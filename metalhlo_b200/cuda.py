@@ -120,6 +120,8 @@ _PROTOTYPES = {
                                             _vp, _i32, _vp]),
     "mhlo_cuda_gemm_all_gather_tuned": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), C.POINTER(_vp), _i32, _i32, _i64, _i64,
                                                   _i64, _vp, _i32, _vp, _i32, _vp]),
+    "mhlo_cuda_gemm_residual": (C.c_int, [_i32, _i32, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
+                                          _vp, _vp]),
     "mhlo_cuda_peer_barrier": (C.c_int, [C.POINTER(_vp), _i32, _i32, C.c_uint64, C.c_uint64, _vp]),
     "mhlo_cuda_convert_many": (C.c_int, [C.POINTER(ConvertJob), _i32, _vp]),
     "mhlo_cuda_reduce_static_scratch": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
@@ -333,8 +335,8 @@ class GemmTuning(C.Structure):
 
 
 def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool = False, trans_b: bool = False,
-         out=None, stream=None, tuning=None):
-    """C[..., M, N] = act(A . B + bias) through ``mhlo_cuda_gemm``.
+         out=None, stream=None, tuning=None, residual=None):
+    """C[..., M, N] = act(A . B + bias) through ``mhlo_cuda_gemm`` (+ residual, without activation: ``mhlo_cuda_gemm_residual``).
 
     a: [batch..., M, K] (or [batch..., K, M] with trans_a), b: [batch..., K, N] (or [batch..., N, K] with trans_b);
     up to two leading batch dimensions, both operands dense CUDA tensors of the same dtype.
@@ -353,6 +355,13 @@ def gemm(a, b, bias=None, epilogue: str = "none", out_dtype=None, trans_a: bool 
     out_dtype = a.dtype if out_dtype is None else out_dtype
     if out is None:
         out = torch.empty(batch + [m, n], dtype=out_dtype, device=a.device)
+    if residual is not None:  # C = A . B + bias + residual, one rounding: mhlo_cuda_gemm_residual
+        assert epilogue == "none" and residual.is_contiguous() and tuple(residual.shape) == tuple(out.shape) and residual.dtype == out.dtype
+        t = GemmTuning(*tuning, 0) if tuning is not None else None
+        check(lib.mhlo_cuda_gemm_residual(torch_dtype_code(a.dtype), torch_dtype_code(out_dtype), _ptr(a), _i64s(a_str), _ptr(b), _i64s(b_str),
+                                          _ptr(out), b0, b1, m, n, k, _ptr(bias), _ptr(residual), None if t is None else C.addressof(t),
+                                          _stream(stream)))
+        return out
     if tuning is not None:  # (tile_n, stages, cta_group): mhlo_cuda_gemm_tuned
         t = GemmTuning(*tuning, 0)
         check(lib.mhlo_cuda_gemm_tuned(torch_dtype_code(a.dtype), torch_dtype_code(out_dtype), _ptr(a), _i64s(a_str), _ptr(b), _i64s(b_str),

@@ -1569,10 +1569,57 @@ class Interpreter:
             p = np.exp(s - s.max(-1, keepdims=True))
             p = p / p.sum(-1, keepdims=True)
             return np.einsum("...qk,...kd->...qd", p, v)
+        def activate(y, act):
+            if act in ("gelu", "gelu_tanh", "gelu_approximate", "geluApproximate"):
+                return 0.5 * y * (1 + np.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+            if act in ("gelu_erf", "gelu_exact"):
+                return 0.5 * y * (1 + np.vectorize(math.erf)(y / math.sqrt(2)))
+            if act == "relu":
+                return np.maximum(y, 0)
+            if act in ("silu", "swish"):
+                return y / (1 + np.exp(-y))
+            if act == "tanh":
+                return np.tanh(y)
+            if act in ("sigmoid", "logistic"):
+                return 1 / (1 + np.exp(-y))
+            return y
+
+        # The reference's remaining handlers (Sources/MetalHLOCore/Compiler/CustomCallHandlers.swift): batch norm :405-447,
+        # convolution + bias + activation :563-640, rotary embedding :715-845, feed-forward :848-925, depth attention :1075-1135
+        if target == "fused_batch_norm":
+            eps = float(cfg.get("eps", cfg.get("epsilon", 1e-5)))
+            return (x - a[3]) / np.sqrt(a[4] + eps) * a[1] + a[2]
+        if target == "fused_ffn":
+            return activate(x @ a[1], cfg.get("activation", "gelu")) @ a[2]
+        if target == "fused_rope":
+            hd = x.shape[-1]
+            half = hd // 2
+            x1, x2, fr = x[..., :half], x[..., half:], a[1]
+            if fr.shape[-1] == hd:
+                c, s = fr[..., :half], fr[..., half:]
+            elif fr.shape[-1] == half:
+                c, s = np.cos(fr), np.sin(fr)
+            else:
+                c, s = fr, (a[2] if len(a) > 2 else np.sin(fr))
+            return np.concatenate([x1 * c - x2 * s, x1 * s + x2 * c], axis=-1)
+        if target == "fused_conv_bias_act":
+            y = self.op_convolution(op, a[:2], t)
+            if cfg.get("has_bias", True) and len(a) > 2:
+                y = y + a[2]
+            return activate(y, cfg.get("activation", "none"))
+        if target == "fused_depth_attention":
+            q, k, v = a[0], a[1], a[2]
+            sc = np.einsum("b...h,bdh->b...d", q, k) * float(cfg.get("scale", 1.0))
+            w = np.exp(sc - sc.max(-1, keepdims=True))
+            w = w / w.sum(-1, keepdims=True)
+            return np.einsum("b...d,bdh->b...h", w, v)
         if target == "fused_matmul_bias_activation":
             y = x @ a[1]
-            if len(a) > 2:
+            n_plain = len(a) - (1 if cfg.get("has_residual") else 0)
+            if n_plain > 2:
                 y = y + a[2]
+            if cfg.get("has_residual"):
+                y = y + a[-1]
             act = cfg.get("activation", "none")
             if act in ("gelu", "gelu_tanh"):
                 y = 0.5 * y * (1 + np.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))

@@ -381,6 +381,21 @@ def pattern_cases(rng, dt):
             f"    %1 = stablehlo.broadcast_in_dim %arg2, dims = [2] : ({tbias}) -> {ts}\n"
             f"    %2 = stablehlo.add %0, %1 : {ts}\n" + gb)
     out.append((f"pattern_dense_gelu_{dt}", func([t, tw, tbias], [ts], body.rstrip("\n"), gres), [x, w, bias]))
+    # projection back into the residual stream: r + (x.w + b), the sum normalised next (the product takes the residual into its
+    # epilogue at O3: fused_matmul_bias_activation with has_residual, then fused_layer_norm)
+    resid = (0.5 * r2.standard_normal((6, 40, 128))).astype(np.float32).astype(NP[dt])
+    g128 = (1 + 0.1 * r2.standard_normal(128)).astype(np.float32).astype(NP[dt])
+    b128 = (0.1 * r2.standard_normal(128)).astype(np.float32).astype(NP[dt])
+    lb, lres = layer_norm_text("%3", (6, 40, 128), dt, "%arg4", "%arg5")
+    body = (f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [2] x [0] : ({t}, {tw}) -> {ts}\n"
+            f"    %1 = stablehlo.broadcast_in_dim %arg2, dims = [2] : ({tbias}) -> {ts}\n"
+            f"    %2 = stablehlo.add %0, %1 : {ts}\n"
+            f"    %3 = stablehlo.add %arg3, %2 : {ts}\n" + lb)
+    out.append((f"pattern_dense_residual_norm_{dt}", func([t, tw, tbias, ts, tbias, tbias], [ts, ts], body.rstrip("\n"), f"%3, {lres}"),
+                [x, w, bias, resid, g128, b128]))
+    body = (f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [2] x [0] : ({t}, {tw}) -> {ts}\n"
+            f"    %1 = stablehlo.add %0, %arg2 : {ts}")
+    out.append((f"pattern_dense_residual_plain_{dt}", func([t, tw, ts], [ts], body, "%1"), [x, w, resid]))
     for causal in (False, True):
         for layout in ("BHSD", "BSHD"):
             text, qshape = attention_text(2, 3, 48, 32, dt, causal, layout)
@@ -994,4 +1009,77 @@ def linalg_cases():
     return out
 
 
-CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases()
+def custom_call_cases():
+    """Modules that arrive with the reference's fused custom calls already in them: every target of its handler table
+    (Sources/MetalHLOCore/Compiler/CustomCallHandlers.swift) with the backend_config keys the handlers read."""
+    import json
+
+    rng = np.random.default_rng(4242)
+    out = []
+
+    def call(target, operands, types, rt, cfg=None, extra=""):
+        config = json.dumps(cfg or {}).replace('"', '\\"')
+        args = ", ".join(operands)
+        return f"    %0 = stablehlo.custom_call @{target}({args}) {{backend_config = \"{config}\"{extra}}} : ({', '.join(types)}) -> {rt}"
+
+    def add(name, target, arrays, rt_shape, dt, cfg=None, extra=""):
+        types = [tt(a.shape, dt) for a in arrays]
+        rt = tt(rt_shape, dt)
+        body = call(target, [f"%arg{i}" for i in range(len(arrays))], types, rt, cfg, extra)
+        out.append((name, func(types, [rt], body, "%0"), arrays))
+
+    for dt in ("f32", "f16") + (("bf16",) if "bf16" in NP else ()):
+        r = lambda *shape, scale=1.0: (scale * rng.standard_normal(shape)).astype(np.float32).astype(NP[dt])  # noqa: E731
+        x, g, b = r(6, 40, 128), (1 + 0.1 * rng.standard_normal(128)).astype(np.float32).astype(NP[dt]), r(128, scale=0.1)
+        add(f"call_layer_norm_{dt}", "fused_layer_norm", [x, g, b], x.shape, dt, {"eps": 1e-3})
+        add(f"call_rms_norm_{dt}", "fused_rms_norm", [x, g], x.shape, dt, {"eps": 1e-6})
+        add(f"call_softmax_{dt}", "fused_softmax", [r(6, 40, 128, scale=3.0)], x.shape, dt, {"axis": -1})
+        add(f"call_softmax_axis1_{dt}", "fused_softmax", [r(6, 40, 128, scale=3.0)], x.shape, dt, {"axis": 1})
+        add(f"call_gelu_{dt}", "fused_gelu", [x], x.shape, dt, {"approximate": True})
+        add(f"call_gelu_exact_{dt}", "fused_gelu", [x], x.shape, dt, {"approximate": False})
+        add(f"call_silu_{dt}", "fused_silu", [x], x.shape, dt)
+        w, bias = r(128, 256, scale=1 / 11), r(256, scale=0.1)
+        add(f"call_matmul_bias_gelu_{dt}", "fused_matmul_bias_activation", [x, w, bias], (6, 40, 256), dt, {"activation": "gelu", "has_bias": True})
+        add(f"call_matmul_plain_{dt}", "fused_matmul_bias_activation", [x, w], (6, 40, 256), dt, {"activation": "none", "has_bias": False})
+        add(f"call_matmul_bias_residual_{dt}", "fused_matmul_bias_activation", [x, w, bias, r(6, 40, 256)], (6, 40, 256), dt,
+            {"activation": "none", "has_bias": True, "has_residual": True})
+        q, k, v = r(2, 3, 48, 32), r(2, 3, 80, 32), r(2, 3, 80, 32)
+        add(f"call_attention_{dt}", "fused_scaled_dot_product_attention", [q, k, v], q.shape, dt, {"scale": 0.25, "is_causal": False, "head_dim": 32})
+        kc, vc = r(2, 3, 48, 32), r(2, 3, 48, 32)
+        add(f"call_attention_causal_{dt}", "fused_scaled_dot_product_attention", [q, kc, vc], q.shape, dt,
+            {"scale": 32 ** -0.5, "is_causal": True, "head_dim": 32})
+        # the handlers this backend restates as plain operators
+        stats = lambda: (r(128, scale=0.3), (0.5 + rng.random(128)).astype(np.float32).astype(NP[dt]))  # noqa: E731
+        mean, var = stats()
+        add(f"call_batch_norm_{dt}", "fused_batch_norm", [x, g, b, mean, var], x.shape, dt, {"eps": 1e-3})
+        up, down = r(128, 192, scale=1 / 11), r(192, 64, scale=1 / 14)
+        for act in ("gelu", "relu", "silu", "gelu_exact"):
+            add(f"call_ffn_{act}_{dt}", "fused_ffn", [x, up, down], (6, 40, 64), dt, {"activation": act, "is_gated": False})
+        xr = r(2, 4, 24, 32)  # [batch, heads, sequence, head_dim]
+        ang = (rng.random((24, 16)) * 6.0).astype(np.float32)
+        add(f"call_rope_angles_{dt}", "fused_rope", [xr, ang.astype(NP[dt])], xr.shape, dt)
+        add(f"call_rope_cos_sin_{dt}", "fused_rope", [xr, np.concatenate([np.cos(ang), np.sin(ang)], -1).astype(NP[dt])], xr.shape, dt)
+        img, ker, cb = r(2, 12, 12, 8), r(3, 3, 8, 16, scale=0.2), r(16, scale=0.1)
+        conv_attrs = ", window_strides = array<i64: 1, 1>, padding = dense<[[1, 1], [1, 1]]> : tensor<2x2xi64>, feature_group_count = 1 : i64"
+        for act in ("relu", "none", "silu"):
+            add(f"call_conv_bias_{act}_{dt}", "fused_conv_bias_act", [img, ker, cb], (2, 12, 12, 16), dt, {"activation": act, "has_bias": True}, conv_attrs)
+        add(f"call_conv_strided_{dt}", "fused_conv_bias_act", [img, ker], (2, 5, 5, 16), dt, {"activation": "tanh", "has_bias": False},
+            ", window_strides = array<i64: 2, 2>, padding = dense<0> : tensor<2x2xi64>")
+        # the unfused chain the reference's conv-bias-act-fusion takes: convolution -> add(broadcast bias) -> activation
+        ti, tk, tb, to = tt(img.shape, dt), tt(ker.shape, dt), tt(cb.shape, dt), tt((2, 12, 12, 16), dt)
+        conv_line = (f"    %0 = stablehlo.convolution(%arg0, %arg1) dim_numbers = [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f], "
+                     f"window = {{stride = [1, 1], pad = [[1, 1], [1, 1]]}} {{batch_group_count = 1 : i64, feature_group_count = 1 : i64}} : ({ti}, {tk}) -> {to}\n"
+                     f"    %1 = stablehlo.broadcast_in_dim %arg2, dims = [3] : ({tb}) -> {to}\n"
+                     f"    %2 = stablehlo.add %0, %1 : {to}\n")
+        tails = {"none": ("", "%2"), "relu": (f"    %z = stablehlo.constant dense<0.0> : {to}\n    %3 = stablehlo.maximum %2, %z : {to}\n", "%3"),
+                 "tanh": (f"    %3 = stablehlo.tanh %2 : {to}\n", "%3"), "sigmoid": (f"    %3 = stablehlo.logistic %2 : {to}\n", "%3"),
+                 "silu": (f"    %s = stablehlo.logistic %2 : {to}\n    %3 = stablehlo.multiply %2, %s : {to}\n", "%3")}
+        for act, (tail, res) in tails.items():
+            out.append((f"pattern_conv_bias_{act}_{dt}", func([ti, tk, tb], [to], (conv_line + tail).rstrip("\n"), res), [img, ker, cb]))
+        qd, kd, vd = r(5, 1, 64), r(5, 7, 64), r(5, 7, 64)
+        add(f"call_depth_attention_{dt}", "fused_depth_attention", [qd, kd, vd], (5, 1, 64), dt, {"scale": 0.125})
+        add(f"call_depth_attention_2d_{dt}", "fused_depth_attention", [qd[:, 0], kd, vd], (5, 64), dt, {"scale": 1.0})
+    return out
+
+
+CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases()

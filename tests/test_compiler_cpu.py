@@ -79,6 +79,10 @@ def test_o3_rewrites_patterns_to_the_reference_custom_call_targets(dt):
         f"pattern_rms_norm_{dt}": ["fused_rms_norm"], f"pattern_gelu_{dt}": ["fused_gelu"],
         f"pattern_residual_layer_norm_{dt}": ["fused_add_layer_norm"], f"pattern_residual_rms_norm_{dt}": ["fused_add_rms_norm"],
         f"pattern_dense_gelu_{dt}": ["fused_matmul_bias_activation"],
+        f"pattern_dense_residual_norm_{dt}": ["fused_matmul_bias_activation", "fused_layer_norm"],
+        f"pattern_conv_bias_none_{dt}": ["fused_conv_bias_act"], f"pattern_conv_bias_relu_{dt}": ["fused_conv_bias_act"],
+        f"pattern_conv_bias_tanh_{dt}": ["fused_conv_bias_act"], f"pattern_conv_bias_sigmoid_{dt}": ["fused_conv_bias_act"],
+        f"pattern_conv_bias_silu_{dt}": ["fused_conv_bias_act"],
         f"pattern_attention_BHSD_full_{dt}": ["fused_scaled_dot_product_attention"],
         f"pattern_attention_BSHD_causal_{dt}": ["fused_scaled_dot_product_attention"],
     }
@@ -102,6 +106,18 @@ def test_fused_configs_carry_the_values_of_the_matched_graph():
     assert '\\"is_causal\\":false' in out and '\\"scale\\":0.17677' in out
     out = capi.optimize_text(BY_NAME["pattern_dense_gelu_f32"][1], 3)
     assert '\\"activation\\":\\"gelu_tanh\\"' in out and '\\"has_bias\\":true' in out
+    # the residual add moves into the product: one more operand, no add left
+    out = capi.optimize_text(BY_NAME["pattern_dense_residual_norm_f16"][1], 3)
+    assert '\\"has_residual\\":true' in out and '\\"has_bias\\":true' in out and "stablehlo.add" not in out
+    # Tests/MetalHLOTests/Conformance/StableHLO/OptimizationCorrectnessTests.swift:488-540: one fused_conv_bias_act call that keeps
+    # the convolution's attributes and names the activation
+    for act in ("none", "relu", "tanh", "sigmoid", "silu"):
+        out = capi.optimize_text(BY_NAME[f"pattern_conv_bias_{act}_f32"][1], 3)
+        assert f'\\"activation\\":\\"{act}\\"' in out and '\\"has_bias\\":true' in out and "stablehlo.convolution" not in out
+        assert "window_strides" in out and "feature_group_count" in out
+        assert capi.plan_text(BY_NAME[f"pattern_conv_bias_{act}_f32"][1], 3)[0] == ["convolution.patches", "convolution.gemm+epilogue"]
+    out = capi.optimize_text(BY_NAME["pattern_dense_residual_plain_f32"][1], 3)
+    assert '\\"has_residual\\":true' in out and '\\"has_bias\\":false' in out and "stablehlo.add" not in out
 
 
 def test_pass_sets_per_level_follow_the_reference():

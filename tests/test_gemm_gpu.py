@@ -77,6 +77,28 @@ def test_bias_and_activation_epilogue(epilogue):
     assert_close(to_np(got), want, 2e-2, f"epilogue {epilogue}")
 
 
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.float16, torch.float16), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                             (torch.float32, torch.float32)], ids=str)
+@pytest.mark.parametrize("m,n,k,tuning", [(512, 768, 256, None), (300, 264, 72, None), (1024, 512, 128, (256, 6, 2)), (256, 250, 64, None)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_residual_is_added_before_the_rounding(dtype, out_dtype, m, n, k, tuning, with_bias):
+    """mhlo_cuda_gemm_residual: A . B + bias + R against the fp64 oracle; n = 250 and fp32 operands take the two-pass route."""
+    cuda = cuda_mod()
+    a, b = operands((), m, n, k, dtype, False, False, seed=m + n)
+    g = torch.Generator().manual_seed(n)
+    bias = torch.randn(n, generator=g).to(out_dtype) if with_bias else None
+    res = (3 * torch.randn(m, n, generator=g)).to(out_dtype)
+    got = cuda.gemm(a.cuda(), b.cuda(), bias=None if bias is None else bias.cuda(), out_dtype=out_dtype, residual=res.cuda(), tuning=tuning)
+    assert cuda.device_error() == 0
+    want = reference(a, b, False, False) + res.double().numpy() + (0 if bias is None else bias.double().numpy())
+    assert_close(to_np(got), want, 1e-5 if out_dtype == torch.float32 and dtype == torch.float32 else 2e-2, f"gemm+residual {m}x{n}x{k}")
+    if dtype != torch.float32 and n % 8 == 0:
+        # one rounding: the result is the correctly rounded fp32 sum wherever fp32 accumulation is exact enough to tell
+        plain = cuda.gemm(a.cuda(), b.cuda(), out_dtype=torch.float32).double().cpu()
+        twice = (plain + res.double() + (0 if bias is None else bias.double())).to(out_dtype)
+        assert (got.cpu().double() - twice.double()).abs().max() <= 2e-2 * want.__abs__().max()
+
+
 def test_fp32_output_from_bf16_operands():
     cuda = cuda_mod()
     a, b = operands((), 256, 256, 512, torch.bfloat16, False, True, seed=2)
