@@ -1311,8 +1311,11 @@ const std::vector<PassDef>& registry() {
         // phase 5: cross-layer
         {"cross-layer-fusion", [](Function&) { return false; }},
         {"residual-chain-fusion", [](Function& f) {
-             const bool products = fuse_matmul_residual(f);  // first: a sum taken by a product no longer feeds fuse_residual_norm
+             // norms first: reading both addends in the norm kernel measured cheaper than reading the residual in the product's
+             // epilogue (GPT-2-small layer products: +16 us per product against 4 us saved per norm); a product takes the sums
+             // that feed no norm, where the alternative is an elementwise pass of its own
              const bool norms = fuse_residual_norm(f);
+             const bool products = fuse_matmul_residual(f);
              return products || norms;
          }},
         // phase 6: layout
