@@ -832,7 +832,8 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     // is the longer one, and a pair would wait for both of its CTAs (logits [32768,768].[768,50257]: 2.64 ms alone, 2.79 ms in pairs).
     const int64_t out_es = p.out_dtype == MHLO_DT_F32 ? 4 : 2;
     const bool rows_on_grid = ((p.ldc > 0 ? p.ldc : p.n) * out_es) % 16 == 0 && (p.c_col0 * out_es) % 16 == 0 && aligned16(p.c);
-    if (cta_group == 0 && p.n_copies == 0 && p.m > BM && p.k >= 8 * BK && rows_on_grid) {
+    // (products that also store into peers' copies included: four ranks, 8192^3 split by columns: 0.295 ms in pairs, 0.320 ms alone)
+    if (cta_group == 0 && p.m > BM && p.k >= 8 * BK && rows_on_grid) {
         const int64_t pair_tiles = (p.m + 2 * BM - 1) / (2 * BM) * ((p.n + 255) / 256) * p.batch0 * p.batch1;
         if (pair_tiles >= 60) return launch_gemm<256, 6, 2>(p, stream);
     }
