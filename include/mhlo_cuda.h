@@ -612,6 +612,17 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         int64_t heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, float scale,
                         int32_t causal, mhlo_cuda_stream_t stream);
 
+/*
+ * stablehlo.rng_bit_generator: `count` elements of elem_bytes (1, 2, 4 or 8) of random bits and the advanced state.
+ * state_dev / new_state_dev: two 64-bit words {key, counter}. Word pair b of the stream is Threefry-2x32-20 of the key
+ * (low word k0, high word k1) at counter + b (low word x0, high word x1); elements of up to 32 bits take the low bits of
+ * one word each, 64-bit elements a whole pair (first word low); the new counter is counter + pairs used. One generator
+ * serves every `algorithm` attribute: the bit streams of this operator are implementation-defined, and the reference
+ * draws from MPSGraph's own generator without reading the state (Compiler/MPSGraphCompiler.swift:4250-4263).
+ */
+int mhlo_cuda_rng_bit_generator(const void* state_dev, void* new_state_dev, void* out_dev, int64_t count,
+                                int32_t elem_bytes, mhlo_cuda_stream_t stream);
+
 /* ---- dense factorisations and solves (jax.numpy.linalg) -----------------------------------------------------------
  * stablehlo.cholesky: a_dev holds `batch` symmetric positive-definite n x n matrices; out_dev receives the factor L
  * (lower != 0: A = L L^T, L lower triangular) or U (A = U^T U), the other triangle set to zero. A matrix that is not

@@ -580,8 +580,9 @@ class Lowering {
         if (n == "custom_call") return lower_custom_call(op);
         if (n == "cholesky") return lower_cholesky(op);
         if (n == "triangular_solve") return lower_triangular_solve(op);
+        if (n == "rng_bit_generator") return lower_rng_bit_generator(op);
         if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
-            n == "rng" || n == "rng_bit_generator" || n == "map" || n == "all_reduce" || n == "all_gather")
+            n == "rng" || n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         if (n == "reduce_precision") {
             // `format = e5m10` in the pretty form, exponent_bits / mantissa_bits in the generic one
@@ -1414,6 +1415,33 @@ class Lowering {
             return mhlo_cuda_cholesky(dt, bind(da, c).base, const_cast<void*>(bind(dout, c).base), batch, n, lower, c.stream);
         });
         set(op.results[0], out);
+    }
+
+    // stablehlo.rng_bit_generator: (state) -> (new state, bits). The state is two 64-bit words {key, counter} (a third word,
+    // as the Philox form carries, passes through unchanged).
+    void lower_rng_bit_generator(const Op& op) {
+        if (op.operands.size() != 1 || op.results.size() != 2) fail_compile("rng_bit_generator takes a state and gives the new state and the bits");
+        View st = materialize(get(op.operands[0]), "rng_bit_generator.state");
+        const TensorType& stt = st.type;
+        const TensorType& ot = op.result_types[1];
+        if (stt.dtype != DType::UI64 || stt.rank() != 1 || stt.shape[0] < 2 || stt.shape[0] > 3 || !(op.result_types[0] == stt))
+            fail_unsupported("rng_bit_generator with a state of " + stt.str() + " (two or three ui64 words expected)");
+        if (is_float(ot.dtype) || ot.dtype == DType::I1) fail_unsupported("rng_bit_generator of " + ot.str());
+        View ns = dense_view(new_arena(stt.bytes()), stt), out = dense_view(new_arena(ot.bytes()), ot);
+        DevView dst = dev(st), dns = dev(ns), dout = dev(out);
+        keep_alive(st); keep_alive(ns); keep_alive(out);
+        const int64_t count = ot.count(), extra_words = stt.shape[0] - 2;
+        const int es = static_cast<int>(dtype_size(ot.dtype));
+        add_step("rng_bit_generator", [=](const Ctx& c) {
+            char* nsp = const_cast<char*>(static_cast<const char*>(bind(dns, c).base));
+            if (extra_words > 0) {
+                const int st2 = mhlo_cuda_copy(nsp + 16, static_cast<const char*>(bind(dst, c).base) + 16, static_cast<size_t>(8 * extra_words), c.stream);
+                if (st2 != 0) return st2;
+            }
+            return mhlo_cuda_rng_bit_generator(bind(dst, c).base, nsp, const_cast<void*>(bind(dout, c).base), count, es, c.stream);
+        }, extra_words > 0 ? 2 : 1);
+        set(op.results[0], ns);
+        set(op.results[1], out);
     }
 
     // stablehlo.triangular_solve: op(a) x = b or x op(a) = b with a [..., m, m] triangular.

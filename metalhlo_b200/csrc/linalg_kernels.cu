@@ -1,4 +1,5 @@
-// stablehlo.cholesky and stablehlo.triangular_solve: small dense factorisations and solves as jax.numpy.linalg emits them.
+// stablehlo.cholesky and stablehlo.triangular_solve: small dense factorisations and solves as jax.numpy.linalg emits them;
+// stablehlo.rng_bit_generator: counter-mode Threefry-2x32 (the last section of this file).
 // One CTA per matrix (Cholesky) or per block of right-hand sides (triangular solve); fp32 arithmetic for f32 / f16 / bf16
 // tensors, fp64 for f64. These are correctness kernels for matrices of up to a few thousand rows, not tuned: the work is
 // O(n^3) with one column (or one substitution step) after the other. The reference lowers both through MPSGraph
@@ -108,7 +109,71 @@ int launch_solve(const void* a, const void* b, void* out, int64_t batch, const S
 
 using namespace mhlo;
 
+// Threefry-2x32 with 20 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3"), the generator behind
+// jax.random: key (k0, k1), counter (x0, x1) -> two 32-bit words.
+__device__ __forceinline__ void threefry2x32(uint32_t k0, uint32_t k1, uint32_t& x0, uint32_t& x1) {
+    const uint32_t ks[3] = {k0, k1, k0 ^ k1 ^ 0x1BD11BDAu};
+    const int rot[8] = {13, 15, 26, 6, 17, 29, 16, 24};
+    x0 += ks[0];
+    x1 += ks[1];
+#pragma unroll
+    for (int g = 0; g < 5; ++g) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            x0 += x1;
+            x1 = __funnelshift_l(x1, x1, rot[4 * (g & 1) + r]) ^ x0;
+        }
+        x0 += ks[(g + 1) % 3];
+        x1 += ks[(g + 2) % 3] + static_cast<uint32_t>(g + 1);
+    }
+}
+
+// One thread per block of two words. Elements of 32 bits or fewer take one word each (its low bits), 64-bit elements both
+// words of a block (first word low). state = {key, counter}; the new counter is written by thread 0.
+__global__ void rng_bits_kernel(const uint64_t* __restrict__ state, uint64_t* __restrict__ new_state, void* __restrict__ out, int64_t count,
+                                int32_t elem_bytes, int64_t blocks) {
+    const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t key = state[0], ctr = state[1];
+    if (b == 0) {
+        new_state[0] = key;
+        new_state[1] = ctr + static_cast<uint64_t>(blocks);
+    }
+    if (b >= blocks) return;
+    const uint64_t c = ctr + static_cast<uint64_t>(b);
+    uint32_t x0 = static_cast<uint32_t>(c), x1 = static_cast<uint32_t>(c >> 32);
+    threefry2x32(static_cast<uint32_t>(key), static_cast<uint32_t>(key >> 32), x0, x1);
+    if (elem_bytes == 8) {
+        static_cast<uint64_t*>(out)[b] = static_cast<uint64_t>(x0) | (static_cast<uint64_t>(x1) << 32);
+        return;
+    }
+    const uint32_t w[2] = {x0, x1};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int64_t e = 2 * b + i;
+        if (e >= count) break;
+        if (elem_bytes == 4) static_cast<uint32_t*>(out)[e] = w[i];
+        else if (elem_bytes == 2) static_cast<uint16_t*>(out)[e] = static_cast<uint16_t>(w[i]);
+        else static_cast<uint8_t*>(out)[e] = static_cast<uint8_t>(w[i]);
+    }
+}
+
 extern "C" {
+
+int mhlo_cuda_rng_bit_generator(const void* state_dev, void* new_state_dev, void* out_dev, int64_t count, int32_t elem_bytes,
+                                mhlo_cuda_stream_t stream) {
+    if (count < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng_bit_generator: negative count");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng_bit_generator: elements of %d bytes", elem_bytes);
+    if (!state_dev || !new_state_dev || (count > 0 && !out_dev)) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng_bit_generator: null pointer");
+    if (state_dev == new_state_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng_bit_generator: the new state must not alias the state");
+    const int64_t blocks = elem_bytes == 8 ? count : (count + 1) / 2;
+    const int64_t threads = blocks > 0 ? blocks : 1;
+    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+    rng_bits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint64_t*>(state_dev), static_cast<uint64_t*>(new_state_dev),
+                                                                         out_dev, count, elem_bytes, blocks);
+    MHLO_CUDA_CHECK_LAUNCH("rng_bit_generator");
+    return MHLO_CUDA_OK;
+}
 
 int mhlo_cuda_cholesky(int32_t dtype, const void* a_dev, void* out_dev, int64_t batch, int64_t n, int32_t lower, mhlo_cuda_stream_t stream) {
     if (batch < 0 || n < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "cholesky: negative extent");

@@ -1526,6 +1526,41 @@ class Interpreter:
         r = lambda v: v.reshape(shape)
         return (x - r(mean)) / np.sqrt(r(var) + eps) * r(scale) + r(offset)
 
+    def op_rng_bit_generator(self, op, a, t):
+        """(state) -> (new state, bits): counter-mode Threefry-2x32-20 (Salmon et al. 2011) on state = {key, counter}; word pair
+        b is the generator at counter + b; elements of up to 32 bits take one word each, 64-bit elements a pair. The stream is
+        implementation-defined by the specification; the reference draws from MPSGraph's generator without reading the state
+        (Sources/MetalHLOCore/Compiler/MPSGraphCompiler.swift:4250-4263), so this restates the backend's own choice."""
+        state = np.asarray(a[0], dtype=np.uint64)
+        ot = op.types[1]
+        count = int(np.prod(ot.shape, dtype=np.int64))
+        es = np.dtype(ot.np_dtype()).itemsize
+        blocks = count if es == 8 else (count + 1) // 2
+        key, ctr = int(state[0]), int(state[1])
+        c = (np.arange(blocks, dtype=np.uint64) + np.uint64(ctr))
+        x0, x1 = (c & np.uint64(0xFFFFFFFF)).astype(np.uint32), (c >> np.uint64(32)).astype(np.uint32)
+        k0, k1 = np.uint32(key & 0xFFFFFFFF), np.uint32(key >> 32)
+        ks = [k0, k1, k0 ^ k1 ^ np.uint32(0x1BD11BDA)]
+        rot = [13, 15, 26, 6, 17, 29, 16, 24]
+        with np.errstate(over="ignore"):
+            x0 = x0 + ks[0]
+            x1 = x1 + ks[1]
+            for g in range(5):
+                for r in rot[4 * (g % 2):4 * (g % 2) + 4]:
+                    x0 = x0 + x1
+                    x1 = ((x1 << np.uint32(r)) | (x1 >> np.uint32(32 - r))) ^ x0
+                x0 = x0 + ks[(g + 1) % 3]
+                x1 = x1 + ks[(g + 2) % 3] + np.uint32(g + 1)
+        if es == 8:
+            words = x0.astype(np.uint64) | (x1.astype(np.uint64) << np.uint64(32))
+        else:
+            words = np.stack([x0, x1], axis=1).reshape(-1)[:count]
+        unsigned = {1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[es]
+        bits = words.astype(unsigned).view(ot.np_dtype()).reshape(ot.shape)
+        new_state = state.copy()
+        new_state[1] = np.uint64((ctr + blocks) & 0xFFFFFFFFFFFFFFFF)
+        return [new_state, bits]
+
     def op_optimization_barrier(self, op, a, t):
         return a
 

@@ -1083,4 +1083,23 @@ def custom_call_cases():
     return out
 
 
-CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases()
+def rng_cases():
+    """stablehlo.rng_bit_generator in the forms jax.random emits under the rbg implementations: every output width, a
+    Philox-shaped state of three words, and two draws chained through the state."""
+    out = []
+    for name, shape, dt, algo, words in (("ui32", (7, 33), "ui32", "THREE_FRY", 2), ("ui64", (129,), "ui64", "DEFAULT", 2),
+                                         ("ui8", (5, 5, 5), "ui8", "PHILOX", 3), ("i16", (1001,), "i16", "DEFAULT", 2),
+                                         ("i32_scalar_count", (1,), "i32", "THREE_FRY", 2), ("ui32_empty", (0,), "ui32", "DEFAULT", 2)):
+        ts, to = tt((words,), "ui64"), tt(shape, dt)
+        body = f"    %0, %1 = stablehlo.rng_bit_generator %arg0, algorithm = {algo} : ({ts}) -> ({ts}, {to})"
+        state = np.array([0x0123456789ABCDEF, 0xFFFFFFFFFFFFFFF0, 77][:words], dtype=np.uint64)  # the counter crosses 2^64 in the larger draws
+        out.append((f"rng_bit_generator_{name}", func([ts], [ts, to], body, "%0, %1"), [state]))
+    ts, to = tt((2,), "ui64"), tt((64,), "ui32")
+    body = (f"    %0, %1 = stablehlo.rng_bit_generator %arg0, algorithm = DEFAULT : ({ts}) -> ({ts}, {to})\n"
+            f"    %2, %3 = stablehlo.rng_bit_generator %0, algorithm = DEFAULT : ({ts}) -> ({ts}, {to})\n"
+            f"    %4 = stablehlo.xor %1, %3 : {to}")
+    out.append(("rng_bit_generator_chained", func([ts], [ts, to], body, "%2, %4"), [np.array([42, 0], dtype=np.uint64)]))
+    return out
+
+
+CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()

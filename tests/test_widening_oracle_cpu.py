@@ -196,3 +196,22 @@ def test_threefry_known_answer():
 
     w0, w1 = interp.evaluate(threefry2x32_text(1), [np.zeros(2, np.uint32), np.zeros(1, np.uint32), np.zeros(1, np.uint32)])
     assert (int(w0[0]), int(w1[0])) == (0x6B200159, 0x99BA4EFE)
+
+
+def test_rng_bit_generator_known_answer_and_state():
+    """The generator's word pair at key 0, counter 0 is the Random123 known answer of Threefry-2x32-20; the state advances by
+    the pairs used and a second draw continues the stream."""
+    text = """func.func @main(%arg0: tensor<2xui64>) -> (tensor<2xui64>, tensor<4xui32>) {
+  %0, %1 = stablehlo.rng_bit_generator %arg0, algorithm = THREE_FRY : (tensor<2xui64>) -> (tensor<2xui64>, tensor<4xui32>)
+  return %0, %1 : tensor<2xui64>, tensor<4xui32>
+}"""
+    state, bits = interp.evaluate(text, [np.zeros(2, np.uint64)])
+    assert (int(bits[0]), int(bits[1])) == (0x6B200159, 0x99BA4EFE)
+    assert state.tolist() == [0, 2]
+    state2, bits2 = interp.evaluate(text, [state])
+    whole = interp.evaluate(text.replace("4xui32", "8xui32"), [np.zeros(2, np.uint64)])[1]
+    np.testing.assert_array_equal(np.concatenate([bits, bits2]), whole)
+    assert state2.tolist() == [0, 4]
+    # 64-bit elements are a whole pair, first word low
+    wide = interp.evaluate(text.replace("4xui32", "2xui64"), [np.zeros(2, np.uint64)])[1]
+    assert int(wide[0]) == 0x6B200159 | (0x99BA4EFE << 32)
