@@ -436,6 +436,25 @@ typedef struct {
 } mhlo_cuda_conv;
 
 /*
+ * 2-D convolution on the tensor cores without a patch matrix: dense NHWC input [images, in_h, in_w, channels], dense HWIO
+ * filter [filter_h, filter_w, channels, features], dense NHWC result [images, out_h, out_w, features]; stride 1, one
+ * feature group, zero padding pad_top / pad_left in front (whatever the result's extent needs behind), filter dilation.
+ * out[n, y, x, f] = act(sum over (dy, dx, c) of in[n, y + dy * dilation_h - pad_top, x + dx * dilation_w - pad_left, c]
+ * * filter[dy, dx, c, f] + bias[f]). The product's A tile for one filter tap and 64 channels is an 8 x 16 patch of input
+ * pixels fetched by one bulk tensor copy (pixels outside the image arrive as zeros), so the input is read from HBM
+ * once instead of being expanded to a patch matrix first (mhlo_cuda_im2col + mhlo_cuda_gemm: 9 times the bytes for a 3 x 3
+ * filter). f16 / bf16 tensors, channels a multiple of 64, features a multiple of 8; anything else returns
+ * MHLO_CUDA_UNSUPPORTED and the caller takes the patch-matrix route. bias_dev (of the result's type) may be NULL.
+ * Stands where the reference lowers convolution to MPSGraph convolution2D (Compiler/MPSGraphCompiler.swift) and
+ * FusedConvBiasActHandler (Compiler/CustomCallHandlers.swift:563-640).
+ */
+int mhlo_cuda_conv2d_nhwc(int32_t dtype, int32_t out_dtype, const void* x_dev, const void* filter_dev, void* out_dev,
+                          int64_t images, int64_t in_h, int64_t in_w, int64_t channels, int64_t filter_h, int64_t filter_w,
+                          int64_t features, int64_t out_h, int64_t out_w, int64_t pad_top, int64_t pad_left,
+                          int64_t dilation_h, int64_t dilation_w, const void* bias_dev, int32_t epilogue,
+                          mhlo_cuda_stream_t stream);
+
+/*
  * Direct convolution, one thread per output element, every attribute of the op honoured (strides, padding, both
  * dilations, window reversal, feature and batch groups). Floats accumulate in fp32 (f64 in fp64), integers in
  * int64. The general path; the reference lowers convolution to MPSGraph convolution2D

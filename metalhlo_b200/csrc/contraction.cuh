@@ -25,6 +25,19 @@ struct GemmProblem {
     int32_t tile_n = 0, stages = 0, cta_group = 0;
 };
 
+// A 2-D convolution of dense NHWC input with dense HWIO filters into dense NHWC output, stride 1, one feature group: the
+// form the tensor-core kernel reads without a patch matrix.
+struct ConvProblem {
+    const void* x;
+    const void* wgt;
+    void* out;
+    const void* bias = nullptr;  // one value per output feature, of the output's type
+    int32_t dtype, out_dtype, epilogue = 0;
+    int64_t images, h, w, channels, kh, kw, features, oh, ow, pad_h, pad_w, dil_h, dil_w;
+};
+bool conv_tc_supported(const ConvProblem& c);
+int conv_tc_launch(const ConvProblem& c, cudaStream_t stream);
+
 struct AttnShape {
     int64_t qs[3], ks[3], vs[3], os[3];  // {batch, head, sequence} element strides; head_dim is contiguous
     int64_t batch, heads, seq_q, seq_k, head_dim;

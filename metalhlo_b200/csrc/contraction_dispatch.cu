@@ -209,6 +209,26 @@ int mhlo_cuda_gemm_tuned(int32_t in_dtype, int32_t out_dtype, const void* a_dev,
     return mhlo_cuda_elementwise(in, n_in, prog, ni, c_dev, out_dtype, shape, 2, stream);
 }
 
+int mhlo_cuda_conv2d_nhwc(int32_t dtype, int32_t out_dtype, const void* x_dev, const void* filter_dev, void* out_dev, int64_t images,
+                          int64_t in_h, int64_t in_w, int64_t channels, int64_t filter_h, int64_t filter_w, int64_t features, int64_t out_h,
+                          int64_t out_w, int64_t pad_top, int64_t pad_left, int64_t dilation_h, int64_t dilation_w, const void* bias_dev,
+                          int32_t epilogue, mhlo_cuda_stream_t stream) {
+    if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "conv2d_nhwc: unknown epilogue %d", epilogue);
+    if (images < 0 || in_h < 0 || in_w < 0 || channels < 0 || filter_h < 0 || filter_w < 0 || features < 0 || out_h < 0 || out_w < 0)
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "conv2d_nhwc: negative extent");
+    if (images * out_h * out_w * features == 0) return MHLO_CUDA_OK;
+    if (!x_dev || !filter_dev || !out_dev) return fail(MHLO_CUDA_INVALID_ARGUMENT, "conv2d_nhwc: null pointer");
+    ConvProblem c;
+    c.x = x_dev; c.wgt = filter_dev; c.out = out_dev; c.bias = bias_dev;
+    c.dtype = dtype; c.out_dtype = out_dtype; c.epilogue = epilogue;
+    c.images = images; c.h = in_h; c.w = in_w; c.channels = channels; c.kh = filter_h; c.kw = filter_w; c.features = features;
+    c.oh = out_h; c.ow = out_w; c.pad_h = pad_top; c.pad_w = pad_left; c.dil_h = dilation_h; c.dil_w = dilation_w;
+    if (!conv_tc_supported(c))
+        return fail(MHLO_CUDA_UNSUPPORTED, "conv2d_nhwc: needs f16 / bf16 tensors, channels in multiples of 64, feature rows on the 16-byte grid");
+    return conv_tc_launch(c, static_cast<cudaStream_t>(stream));
+}
+
 int mhlo_cuda_gemm_residual(int32_t in_dtype, int32_t out_dtype, const void* a_dev, const int64_t a_strides[4], const void* b_dev,
                             const int64_t b_strides[4], void* c_dev, int64_t batch0, int64_t batch1, int64_t m, int64_t n, int64_t k,
                             const void* bias_dev, const void* residual_dev, const mhlo_cuda_gemm_tuning* tuning, mhlo_cuda_stream_t stream) {

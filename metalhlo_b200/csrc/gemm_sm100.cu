@@ -89,6 +89,9 @@ struct GemmParams {
     int32_t n_copies;
     int32_t c_tma;                   // C has a tensor map: the epilogue stores its staged boxes with bulk tensor copies
     int32_t stages;                  // depth of the TMA ring in use (<= the kernel's STAGES)
+    // MODE 3 (convolution without a patch matrix): a row tile is an 8 x 16 patch of output positions of one image
+    // (batch index = image, tiles_m = patches per image); k-block kb = (filter tap, 64 input channels)
+    int32_t conv_tiles_x, conv_kw, conv_cblocks, conv_pad_h, conv_pad_w, conv_dil_h, conv_dil_w, conv_oh;
 };
 
 // Tensor maps of the further copies of C (GemmParams::copies, in the same order), used when the copies are written with
@@ -130,8 +133,10 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
 }
 
 // MODE: 0 = the plain product, 1 = with the tensor maps of further copies of C (bulk stores into peers), 2 = with a residual
-// matrix added in the epilogue. The variants are separate instantiations so that the plain product carries neither the
-// maps in its parameters nor the residual's registers.
+// matrix added in the epilogue, 3 = a 2-D convolution read straight from its NHWC input: the A tile of k-block (tap, 64
+// channels) is the 8 x 16 patch of input pixels that tap sees, one bulk tensor load whose out-of-image pixels arrive as
+// zeros (the padding), and the result tile goes back as boxes of the NHWC output. The variants are separate instantiations
+// so that the plain product carries neither the maps in its parameters nor the residual's registers.
 template <int BN, int STAGES, int ACT, int CTAS, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)  // ten warps are allocated as twelve: 168 registers per thread is the ceiling
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -217,9 +222,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     auto load = [&](uint8_t* dst, const CUtensorMap* map, int c0, int c1) {
                         if constexpr (kPair) tma_load_4d_pair(dst, map, full_addr, c0, c1, b1, b0);
+                        else if constexpr (MODE == 3) tma_load_4d(dst, map, &full_bar[stage], c0, c1, 0, 0);  // the filter matrix has no batch
                         else tma_load_4d(dst, map, &full_bar[stage], c0, c1, b1, b0);
                     };
-                    if (!p.a_mn_major) {
+                    if constexpr (MODE == 3) {
+                        const int ty = tm / p.conv_tiles_x, tx = tm - ty * p.conv_tiles_x;
+                        const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+                        const int dy = tap / p.conv_kw, dx = tap - dy * p.conv_kw;
+                        // {channel, x, y, image}: pixels outside the image (the padding) are filled with zeros by the copy
+                        tma_load_4d(sa, &map_a, &full_bar[stage], cb * 64, tx * 16 + dx * p.conv_dil_w - p.conv_pad_w,
+                                    ty * 8 + dy * p.conv_dil_h - p.conv_pad_h, bz);
+                    } else if (!p.a_mn_major) {
                         load(sa, &map_a, kb * BK, row_a);
                     } else {
 #pragma unroll
@@ -452,6 +465,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // at the edges of C by the hardware
                     fence_proxy_async();
                     __syncwarp();
+                    if constexpr (MODE == 3) {
+                        // the warp's 32 rows are two rows of 16 output pixels: one box {columns, 16, 2} of the NHWC result,
+                        // clipped at the image's edges by the copy
+                        const int ty = tm / p.conv_tiles_x, tx = tm - ty * p.conv_tiles_x;
+                        if (lane == 0 && cols_left > 0 && ty * 8 + quarter * 2 < p.conv_oh) {  // no store starts outside the image
+                            tma_store_4d(&map_c, stage_tile, static_cast<int>(col0), tx * 16, ty * 8 + quarter * 2, bz);
+                            tma_store_commit();
+                        }
+                        continue;
+                    }
                     if (lane == 0 && cols_left > 0 && row0 < p.m) {
                         const int b1 = static_cast<int>(bz % p.batch1), b0 = static_cast<int>(bz / p.batch1);
                         tma_store_4d(&map_c, stage_tile, static_cast<int>(col0), static_cast<int>(row0), b1, b0);
@@ -805,6 +828,124 @@ static int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
         case MHLO_EPILOGUE_TANH: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_TANH, CTAS>(p, stream);
         case MHLO_EPILOGUE_SIGMOID: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_SIGMOID, CTAS>(p, stream);
         default: return launch_gemm_act<BN, STAGES, MHLO_EPILOGUE_NONE, CTAS>(p, stream);
+    }
+}
+
+// ---- convolution without a patch matrix (MODE 3) ----
+
+bool conv_map(CUtensorMap* map, const void* base, int64_t elem_bytes, int64_t inner, int64_t w, int64_t h, int64_t n, uint32_t box_inner,
+              uint32_t box_h, bool is_f32, std::string* why) {
+    cuuint64_t gdim[4] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
+    cuuint64_t gstr[3] = {static_cast<cuuint64_t>(inner * elem_bytes), static_cast<cuuint64_t>(w * inner * elem_bytes),
+                          static_cast<cuuint64_t>(h * w * inner * elem_bytes)};
+    cuuint32_t box[4] = {box_inner, 16, box_h, 1}, estr[4] = {1, 1, 1, 1};
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+            *why = "cuTensorMapEncodeTiled is not available from this driver";
+            return false;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUresult r = encode(map, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr,
+                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        *why = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r));
+        return false;
+    }
+    return true;
+}
+
+bool conv_tc_supported(const ConvProblem& c) {
+    const bool f16 = c.dtype == MHLO_DT_F16, bf16 = c.dtype == MHLO_DT_BF16;
+    if (!f16 && !bf16) return false;
+    if (c.out_dtype != c.dtype && c.out_dtype != MHLO_DT_F32) return false;
+    if (c.images <= 0 || c.h <= 0 || c.w <= 0 || c.channels <= 0 || c.kh <= 0 || c.kw <= 0 || c.features <= 0 || c.oh <= 0 || c.ow <= 0) return false;
+    if (c.channels % 64 != 0) return false;  // a k-block is one tap x 64 channels
+    const int64_t out_es = c.out_dtype == MHLO_DT_F32 ? 4 : 2;
+    if ((c.features * 2) % 16 != 0 || (c.features * out_es) % 16 != 0) return false;
+    if (!aligned16(c.x) || !aligned16(c.wgt) || !aligned16(c.out)) return false;
+    if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0) return false;
+    // the window arithmetic of a stride-1 convolution must give the declared result
+    if (c.oh > c.h + 2 * 0x3fff || c.images > 0x7fffffff) return false;
+    return true;
+}
+
+template <int ACT>
+static int launch_conv_act(const ConvProblem& c, cudaStream_t stream) {
+    constexpr int BN = 128, STAGES = 6;
+    using L = SmemLayout<BN, STAGES, 1>;
+    std::string why;
+    CUtensorMap map_a, map_b, map_c;
+    if (!conv_map(&map_a, c.x, 2, c.channels, c.w, c.h, c.images, 64, 8, false, &why))
+        return fail(MHLO_CUDA_EXECUTION_FAILED, "convolution: tensor map for the input: %s", why.c_str());
+    const int64_t kc = c.kh * c.kw * c.channels;
+    if (!operand_map(&map_b, c.wgt, c.features, kc, c.features, 1, 0, 1, 0, 64, BK, &why))
+        return fail(MHLO_CUDA_EXECUTION_FAILED, "convolution: tensor map for the filter: %s", why.c_str());
+    const bool f32_out = c.out_dtype == MHLO_DT_F32;
+    if (!conv_map(&map_c, c.out, f32_out ? 4 : 2, c.features, c.ow, c.oh, c.images, f32_out ? 32 : 64, 2, f32_out, &why))
+        return fail(MHLO_CUDA_EXECUTION_FAILED, "convolution: tensor map for the result: %s", why.c_str());
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.c = c.out;
+    p.bias = c.bias;
+    const int tiles_x = static_cast<int>((c.ow + 15) / 16), tiles_y = static_cast<int>((c.oh + 7) / 8);
+    p.tiles_m = tiles_x * tiles_y;
+    p.m = static_cast<int64_t>(p.tiles_m) * BM;  // every row of a tile "exists": the copies clip at the image's edges
+    p.n = c.features;
+    p.k = kc;
+    p.batch0 = 1;
+    p.batch1 = c.images;
+    p.stages = STAGES;
+    p.tiles_n = static_cast<int>((c.features + BN - 1) / BN);
+    p.num_tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n * c.images;
+    p.a_mn_major = 0;
+    p.b_mn_major = 1;  // the filter matrix [taps x channels, features] has the features contiguous
+    p.in_bf16 = c.dtype == MHLO_DT_BF16;
+    p.out_dtype = c.out_dtype;
+    p.epilogue = c.epilogue;
+    p.ldc = c.features;
+    p.c_vec_ok = 1;
+    p.c_tma = 1;
+    p.conv_tiles_x = tiles_x;
+    p.conv_kw = static_cast<int32_t>(c.kw);
+    p.conv_cblocks = static_cast<int32_t>(c.channels / 64);
+    p.conv_pad_h = static_cast<int32_t>(c.pad_h);
+    p.conv_pad_w = static_cast<int32_t>(c.pad_w);
+    p.conv_dil_h = static_cast<int32_t>(c.dil_h);
+    p.conv_dil_w = static_cast<int32_t>(c.dil_w);
+    p.conv_oh = static_cast<int32_t>(c.oh);
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT, 1, 3>;
+    static std::atomic<bool> attr_set[64];
+    int attr_dev = 0;
+    MHLO_CUDA_TRY(cudaGetDevice(&attr_dev), MHLO_CUDA_EXECUTION_FAILED);
+    if (attr_dev < 0 || attr_dev >= 64 || !attr_set[attr_dev].load(std::memory_order_acquire)) {
+        MHLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal), MHLO_CUDA_EXECUTION_FAILED);
+        if (attr_dev >= 0 && attr_dev < 64) attr_set[attr_dev].store(true, std::memory_order_release);
+    }
+    const int grid = static_cast<int>(std::min<int64_t>(p.num_tiles, kNumSMs));
+    PeerMaps<false> none;
+    const cudaError_t launched = launch_dependent_cluster(kernel, dim3(grid), dim3(kGemmThreads), L::kTotal, stream, 1, map_a, map_b, map_c, p, none);
+    if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of the convolution failed: %s", cudaGetErrorString(launched));
+    MHLO_CUDA_CHECK_LAUNCH("convolution (tcgen05)");
+    return MHLO_CUDA_OK;
+}
+
+int conv_tc_launch(const ConvProblem& c, cudaStream_t stream) {
+    switch (c.epilogue) {
+        case MHLO_EPILOGUE_RELU: return launch_conv_act<MHLO_EPILOGUE_RELU>(c, stream);
+        case MHLO_EPILOGUE_GELU_TANH: return launch_conv_act<MHLO_EPILOGUE_GELU_TANH>(c, stream);
+        case MHLO_EPILOGUE_GELU_ERF: return launch_conv_act<MHLO_EPILOGUE_GELU_ERF>(c, stream);
+        case MHLO_EPILOGUE_SILU: return launch_conv_act<MHLO_EPILOGUE_SILU>(c, stream);
+        case MHLO_EPILOGUE_TANH: return launch_conv_act<MHLO_EPILOGUE_TANH>(c, stream);
+        case MHLO_EPILOGUE_SIGMOID: return launch_conv_act<MHLO_EPILOGUE_SIGMOID>(c, stream);
+        default: return launch_conv_act<MHLO_EPILOGUE_NONE>(c, stream);
     }
 }
 

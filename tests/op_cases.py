@@ -955,6 +955,18 @@ def convolution_cases():
     out.append(conv_case("conv_3d_f32", data((1, 5, 6, 7, 2), "f32"), data((2, 3, 2, 2, 4), "f32", 0.3), "f32", (1, 4, 4, 6, 4),
                          layout="[b, 0, 1, 2, f]x[0, 1, 2, i, o]->[b, 0, 1, 2, f]"))
     out.append(conv_case("conv_i32", data((1, 6, 6, 2), "i32"), data((3, 3, 2, 3), "i32"), "i32", (1, 4, 4, 3)))
+    # the forms the tensor-core kernel reads without a patch matrix: 16-bit NHWC x HWIO, stride 1, channels in multiples of 64
+    for dt in ("f16", "bf16"):
+        if dt not in NP:
+            continue
+        out.append(conv_case(f"conv_direct_3x3_same_{dt}", data((2, 12, 12, 64), dt), data((3, 3, 64, 96), dt, 0.06), dt, (2, 12, 12, 96), window=same))
+        out.append(conv_case(f"conv_direct_wide_image_{dt}", data((1, 20, 37, 64), dt), data((3, 3, 64, 64), dt, 0.06), dt, (1, 20, 37, 64), window=same))
+        out.append(conv_case(f"conv_direct_valid_5x5_{dt}", data((2, 14, 14, 128), dt), data((5, 5, 128, 200), dt, 0.03), dt, (2, 10, 10, 200)))
+        out.append(conv_case(f"conv_direct_1x1_{dt}", data((3, 9, 9, 64), dt), data((1, 1, 64, 8), dt, 0.15), dt, (3, 9, 9, 8)))
+        out.append(conv_case(f"conv_direct_dilated_{dt}", data((1, 17, 17, 64), dt), data((3, 3, 64, 72), dt, 0.06), dt, (1, 17, 17, 72),
+                             window="pad = [[2, 2], [2, 2]], rhs_dilate = [2, 2]"))
+        out.append(conv_case(f"conv_direct_uneven_padding_{dt}", data((2, 9, 10, 64), dt), data((2, 4, 64, 16), dt, 0.07), dt, (2, 11, 9, 16),
+                             window="pad = [[2, 1], [0, 2]]"))
     out.append(conv_case("conv_mixed_layouts_f32", data((6, 6, 2, 5), "f32"), data((3, 4, 3, 5), "f32", 0.3), "f32", (4, 2, 4, 4),
                          layout="[0, 1, b, f]x[0, o, 1, i]->[0, b, f, 1]"))
     out.append(conv_case("conv_short_form_f32", data((2, 8, 8, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (2, 8, 8, 8),
