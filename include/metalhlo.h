@@ -210,6 +210,15 @@ int64_t mhlo_b200_executable_graph_replays(MHLOExecutableRef executable);
 char* mhlo_b200_executable_steps(MHLOExecutableRef executable);
 /* Device address of a buffer's storage (dense row-major). */
 void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer);
+
+/*
+ * mhlo_buffer_to_host without the wait: the copy is queued on the client's transfer stream behind everything already
+ * queued on its compute stream, and done(user) runs on a driver thread when the bytes are in out_data (pinned memory for
+ * the copy to run beside the next program). done must not call into this library. The buffer may be destroyed at any
+ * time afterwards: destruction waits for transfers out of it. An extension: the reference's buffers copy synchronously
+ * (Sources/MetalHLO/CAPI: mhlo_buffer_to_host).
+ */
+MHLOStatusCode mhlo_b200_buffer_to_host_async(MHLOBufferRef buffer, void* out_data, size_t data_size, void (*done)(void*), void* user);
 /* Enqueues the program on `stream` (a cudaStream_t) reading/writing caller-owned dense device tensors of the
  * executable's declared types. Does not synchronise; the only device allocations are stream-ordered scratch of split
  * reductions. On a non-default stream, repeated calls with the same addresses replay a recorded CUDA graph. */

@@ -111,6 +111,13 @@ int mhlo_cuda_ipc_close(void* dev_ptr);
 int mhlo_cuda_event_create(void** out_event);
 int mhlo_cuda_event_destroy(void* event);
 int mhlo_cuda_event_record(void* event, mhlo_cuda_stream_t stream);
+/* Blocks the host until the event's latest record has been reached (cudaEventSynchronize). */
+int mhlo_cuda_event_sync(void* event);
+/* Work queued on `stream` after this call waits for the event's latest record (cudaStreamWaitEvent). */
+int mhlo_cuda_stream_wait_event(mhlo_cuda_stream_t stream, void* event);
+/* fn(user) runs on a driver thread once everything queued on `stream` before it has finished (cudaLaunchHostFunc): how an
+ * asynchronous transfer reports its completion. fn must not call into this library or CUDA. */
+int mhlo_cuda_stream_host_callback(mhlo_cuda_stream_t stream, void (*fn)(void*), void* user);
 /* Synchronises on `stop`, then writes the elapsed milliseconds between the two events. */
 int mhlo_cuda_event_elapsed_ms(void* start, void* stop, float* out_ms);
 

@@ -36,6 +36,10 @@ int pjrt_host_buffer_from_host(void* host, const void* data, int type, const int
 /* Element type, dimensions (up to 8) and host size of a buffer; any output may be NULL. */
 int pjrt_host_buffer_describe(void* host, void* buffer, int* out_type, int64_t* out_dims, int* out_rank, size_t* out_bytes);
 int pjrt_host_buffer_to_host(void* host, void* buffer, void* dst, size_t bytes);
+/* The same in two halves: PJRT_Buffer_ToHostBuffer now, PJRT_Event_Await (which also destroys the event) later, so that
+ * the caller can execute the next program while the bytes travel. */
+int pjrt_host_buffer_to_host_start(void* host, void* buffer, void* dst, size_t bytes, void** out_event);
+int pjrt_host_event_await(void* host, void* event);
 void pjrt_host_buffer_destroy(void* host, void* buffer);
 
 /*

@@ -38,6 +38,8 @@ struct Client {
     int shard_count = 1, shard_index = 0;
     int device = 0;
     void* stream = nullptr;
+    void* copy_stream = nullptr;  // device-to-host transfers that run beside the next program (mhlo_b200_buffer_to_host_async)
+    void* copy_fence = nullptr;   // event that orders such a transfer behind the work already queued on `stream`
     std::mutex mu;
     // in-process executable cache keyed by (text, level): MetalHLOCompiler.swift:730-782 keeps the same
     std::map<std::string, std::shared_ptr<Executable>> cache;
@@ -89,7 +91,9 @@ void pool_release(Client* c, void* dev, size_t bytes) {
     if (!dev) return;
     {
         std::lock_guard<std::mutex> lock(c->mu);
-        if (bytes >= (1u << 20) && c->pooled_bytes + bytes <= c->pool_limit) {  // small blocks are cheap to allocate afresh
+        // (blocks of a few KB are cheap to allocate afresh; anything larger is kept: cudaFree waits for the whole device,
+        // a transfer on the copy stream included, which is exactly what a serving loop's per-step input buffer must not do)
+        if (bytes >= 4096 && c->pooled_bytes + bytes <= c->pool_limit) {
             c->pool.emplace(bytes, dev);
             c->pooled_bytes += bytes;
             return;
@@ -109,6 +113,7 @@ struct Buffer {
     void* dev = nullptr;
     TensorType type;
     size_t bytes = 0;
+    void* copy_done = nullptr;  // recorded behind the latest asynchronous transfer out of this buffer
 };
 
 // I1 tensors occupy one byte per element on the device (mhlo_element_type_size reports 0 for I1, as the
@@ -332,6 +337,8 @@ void mhlo_client_destroy(MHLOClientRef client) {
     c->cache.clear();
     for (auto& kv : c->pool) mhlo_cuda_free(kv.second);
     c->pool.clear();
+    if (c->copy_stream) { mhlo_cuda_stream_sync(c->copy_stream); mhlo_cuda_stream_destroy(c->copy_stream); }
+    if (c->copy_fence) mhlo_cuda_event_destroy(c->copy_fence);
     if (c->stream) mhlo_cuda_stream_destroy(c->stream);
     delete c;
 }
@@ -500,6 +507,10 @@ void mhlo_buffer_destroy(MHLOBufferRef buffer) {
     {
         std::lock_guard<std::mutex> lock(b->client->mu);
         mhlo_cuda_stream_sync(b->client->stream);
+        if (b->copy_done) {  // a transfer out of this buffer may still be reading it (other buffers' transfers are not waited for)
+            mhlo_cuda_event_sync(b->copy_done);
+            mhlo_cuda_event_destroy(b->copy_done);
+        }
     }
     pool_release(b->client, b->dev, b->bytes);
     delete b;
@@ -533,6 +544,30 @@ MHLOStatusCode mhlo_buffer_to_host(MHLOBufferRef buffer, void* out_data, size_t 
         std::lock_guard<std::mutex> lock(b->client->mu);
         ok = mhlo_cuda_device_set(b->client->device) == 0 && mhlo_cuda_download(out_data, b->dev, b->bytes, b->client->stream) == 0 &&
              mhlo_cuda_stream_sync(b->client->stream) == 0;
+    }
+    if (!ok) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error()));
+    return MHLO_OK;
+}
+
+MHLOStatusCode mhlo_b200_buffer_to_host_async(MHLOBufferRef buffer, void* out_data, size_t data_size, void (*done)(void*), void* user) {
+    Buffer* b = static_cast<Buffer*>(buffer);
+    if (!b) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "buffer is null"));
+    if (!out_data || !done) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "out_data or the completion function is null"));
+    if (b->bytes > data_size)
+        return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, "Output buffer too small: need " + std::to_string(b->bytes) +
+                                                     ", got " + std::to_string(data_size)));
+    Client* c = b->client;
+    bool ok;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        ok = mhlo_cuda_device_set(c->device) == 0;
+        if (ok && !c->copy_stream) ok = mhlo_cuda_stream_create(&c->copy_stream) == 0 && mhlo_cuda_event_create(&c->copy_fence) == 0;
+        // behind whatever is queued on the client's stream (the program that wrote the buffer), then on its own
+        ok = ok && mhlo_cuda_event_record(c->copy_fence, c->stream) == 0 && mhlo_cuda_stream_wait_event(c->copy_stream, c->copy_fence) == 0;
+        if (ok && b->bytes) ok = mhlo_cuda_download(out_data, b->dev, b->bytes, c->copy_stream) == 0;
+        if (ok && !b->copy_done) ok = mhlo_cuda_event_create(&b->copy_done) == 0;
+        ok = ok && mhlo_cuda_event_record(b->copy_done, c->copy_stream) == 0;  // what the buffer's destruction waits for
+        ok = ok && mhlo_cuda_stream_host_callback(c->copy_stream, done, user) == 0;
     }
     if (!ok) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_TRANSFER_FAILED, mhlo_cuda_last_error()));
     return MHLO_OK;

@@ -284,10 +284,20 @@ PJRT_Error* buffer_to_host(PJRT_Buffer_ToHostBuffer_Args* args) {
     if (args->dst_size < b->bytes)
         return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "ToHostBuffer: destination holds " + std::to_string(args->dst_size) +
                                                                 " bytes, buffer needs " + std::to_string(b->bytes));
-    if (b->bytes && mhlo_buffer_to_host(b->mhlo, args->dst, b->bytes) != MHLO_OK)
-        return make_error(PJRT_Error_Code_INTERNAL, std::string("ToHostBuffer failed: ") + mhlo_get_last_error());
     args->dst_size = b->bytes;
-    args->event = new_ready_event();
+    if (b->bytes == 0) {
+        args->event = new_ready_event();
+        return nullptr;
+    }
+    // the copy runs on the client's transfer stream; the event turns ready from the stream's completion function, so a
+    // caller may start the next program before it awaits the bytes
+    PJRT_Event* ev = new_pending_event();
+    if (mhlo_b200_buffer_to_host_async(b->mhlo, args->dst, b->bytes, [](void* e) { event_complete(static_cast<PJRT_Event*>(e)); }, ev) != MHLO_OK) {
+        event_release(ev);
+        event_release(ev);
+        return make_error(PJRT_Error_Code_INTERNAL, std::string("ToHostBuffer failed: ") + mhlo_get_last_error());
+    }
+    args->event = ev;
     return nullptr;
 }
 

@@ -13,6 +13,23 @@ PJRT_Error* unimplemented(const char* function_name) {
 }
 
 PJRT_Event* new_ready_event() { return new PJRT_Event(); }
+PJRT_Event* new_pending_event() {
+    PJRT_Event* e = new PJRT_Event();
+    e->ready = false;
+    e->refs.store(2, std::memory_order_relaxed);  // the caller's reference and the producer's, dropped by event_complete()
+    return e;
+}
+void event_complete(PJRT_Event* e) {
+    std::vector<std::pair<PJRT_Event_OnReadyCallback, void*>> callbacks;
+    {
+        std::lock_guard<std::mutex> lock(e->mu);
+        e->ready = true;
+        callbacks.swap(e->callbacks);
+    }
+    e->cv.notify_all();
+    for (auto& cb : callbacks) cb.first(nullptr, cb.second);
+    event_release(e);
+}
 void event_retain(PJRT_Event* e) { e->refs.fetch_add(1, std::memory_order_relaxed); }
 void event_release(PJRT_Event* e) {
     if (e && e->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) delete e;
@@ -87,12 +104,12 @@ PJRT_Error* event_error(PJRT_Event_Error_Args* args) {
     return copy_error(args->event->error.get());
 }
 
-// Every event this plugin hands out is complete on creation (transfers and execution are synchronous), so
-// awaiting never blocks; a pending event would only exist if a caller built one through a future extension.
+// Execution and host-to-device transfers are synchronous, so their events are complete on creation; the event of a
+// device-to-host transfer is pending until the copy stream's completion function has run (event_complete).
 PJRT_Error* event_await(PJRT_Event_Await_Args* args) {
     PJRT_B200_REQUIRE(args && args->event, "NULL args or event");
-    std::lock_guard<std::mutex> lock(args->event->mu);
-    if (!args->event->ready) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "event is pending and has no producer");
+    std::unique_lock<std::mutex> lock(args->event->mu);
+    args->event->cv.wait(lock, [&] { return args->event->ready; });
     return copy_error(args->event->error.get());
 }
 

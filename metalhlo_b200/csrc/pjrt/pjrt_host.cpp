@@ -275,6 +275,30 @@ int pjrt_host_buffer_to_host(void* host, void* buffer, void* dst, size_t bytes) 
     return 0;
 }
 
+// Starts the transfer and returns its event in *out_event; pjrt_host_event_await waits for it (and frees it).
+int pjrt_host_buffer_to_host_start(void* host, void* buffer, void* dst, size_t bytes, void** out_event) {
+    Host* h = static_cast<Host*>(host);
+    if (!h || !buffer || !dst || !out_event) return fail("null argument");
+    *out_event = nullptr;
+    PJRT_Buffer_ToHostBuffer_Args a{};
+    a.struct_size = PJRT_Buffer_ToHostBuffer_Args_STRUCT_SIZE;
+    a.src = static_cast<PJRT_Buffer*>(buffer);
+    a.dst = dst;
+    a.dst_size = bytes;
+    std::string e = h->take(h->api->PJRT_Buffer_ToHostBuffer(&a));
+    if (!e.empty()) return fail("ToHostBuffer: " + e);
+    *out_event = a.event;
+    return 0;
+}
+
+int pjrt_host_event_await(void* host, void* event) {
+    Host* h = static_cast<Host*>(host);
+    if (!h || !event) return fail("null argument");
+    const std::string e = h->await(static_cast<PJRT_Event*>(event));
+    if (!e.empty()) return fail("event: " + e);
+    return 0;
+}
+
 void pjrt_host_buffer_destroy(void* host, void* buffer) {
     Host* h = static_cast<Host*>(host);
     if (!h || !buffer) return;

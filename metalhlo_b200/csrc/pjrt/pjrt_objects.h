@@ -14,6 +14,7 @@
 #include <cstring>
 #include <functional>
 #include <memory>
+#include <condition_variable>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -30,6 +31,7 @@ struct PJRT_Error {
 // receives a handle it must destroy (PJRTEvent.swift:14-100).
 struct PJRT_Event {
     std::mutex mu;
+    std::condition_variable cv;  // signalled when a pending event becomes ready
     bool ready = true;
     std::unique_ptr<PJRT_Error> error;  // set when the awaited work failed
     std::vector<std::pair<PJRT_Event_OnReadyCallback, void*>> callbacks;
@@ -128,6 +130,8 @@ namespace pjrt_b200 {
 PJRT_Error* make_error(PJRT_Error_Code code, const std::string& message);
 PJRT_Error* unimplemented(const char* function_name);
 PJRT_Event* new_ready_event();
+PJRT_Event* new_pending_event();          // becomes ready through event_complete()
+void event_complete(PJRT_Event* e);        // marks a pending event ready, wakes waiters, runs its callbacks; drops one reference
 void event_retain(PJRT_Event* e);
 void event_release(PJRT_Event* e);
 

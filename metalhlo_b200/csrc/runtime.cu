@@ -261,6 +261,24 @@ int mhlo_cuda_event_record(void* event, mhlo_cuda_stream_t stream) {
     return MHLO_CUDA_OK;
 }
 
+int mhlo_cuda_event_sync(void* event) {
+    if (!event) return fail(MHLO_CUDA_INVALID_ARGUMENT, "event_sync: null event");
+    MHLO_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(event)), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_stream_wait_event(mhlo_cuda_stream_t stream, void* event) {
+    if (!event) return fail(MHLO_CUDA_INVALID_ARGUMENT, "stream_wait_event: null event");
+    MHLO_CUDA_TRY(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
+int mhlo_cuda_stream_host_callback(mhlo_cuda_stream_t stream, void (*fn)(void*), void* user) {
+    if (!fn) return fail(MHLO_CUDA_INVALID_ARGUMENT, "stream_host_callback: null function");
+    MHLO_CUDA_TRY(cudaLaunchHostFunc(static_cast<cudaStream_t>(stream), fn, user), MHLO_CUDA_EXECUTION_FAILED);
+    return MHLO_CUDA_OK;
+}
+
 int mhlo_cuda_event_elapsed_ms(void* start, void* stop, float* out_ms) {
     if (!out_ms) return fail(MHLO_CUDA_INVALID_ARGUMENT, "event_elapsed_ms: null output");
     MHLO_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)), MHLO_CUDA_EXECUTION_FAILED);

@@ -47,6 +47,8 @@ _PROTOTYPES = {
     "pjrt_host_buffer_from_host": (C.c_int, [_vp, _vp, C.c_int, _P(_i64), C.c_int, C.c_int, _P(_vp)]),
     "pjrt_host_buffer_describe": (C.c_int, [_vp, _vp, _P(C.c_int), _P(_i64), _P(C.c_int), _P(_sz)]),
     "pjrt_host_buffer_to_host": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "pjrt_host_buffer_to_host_start": (C.c_int, [_vp, _vp, _vp, _sz, C.POINTER(_vp)]),
+    "pjrt_host_event_await": (C.c_int, [_vp, _vp]),
     "pjrt_host_buffer_destroy": (None, [_vp, _vp]),
     "pjrt_host_compile": (C.c_int, [_vp, C.c_char_p, _sz, C.c_int, C.c_int, _P(_i64), _P(_vp)]),
     "pjrt_host_executable_num_outputs": (C.c_int, [_vp]),
@@ -105,6 +107,17 @@ class Buffer:
 
     def to_host_pointer(self, ptr: int, nbytes: int) -> None:
         _check(lib.pjrt_host_buffer_to_host(self._host._h, self._h, ptr, nbytes))
+
+    def to_host_pointer_start(self, ptr: int, nbytes: int):
+        """PJRT_Buffer_ToHostBuffer without the wait; returns a callable that awaits the transfer's event (call it once)."""
+        ev = _vp()
+        _check(lib.pjrt_host_buffer_to_host_start(self._host._h, self._h, ptr, nbytes, C.byref(ev)))
+        host = self._host
+
+        def wait():
+            _check(lib.pjrt_host_event_await(host._h, ev))
+
+        return wait
 
 
 class LoadedExecutable:
