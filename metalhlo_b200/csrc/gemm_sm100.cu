@@ -965,7 +965,7 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     if (p.tile_n == 128) return launch_gemm<128, 6>(p, stream);
     if (p.n <= 128) return launch_gemm<128, 6>(p, stream);
     // A pair of CTAs per 256 x 256 tile halves the shared-memory traffic of B per SM and measured 5-10 % faster than one
-    // CTA per 128 x 256 tile wherever there are enough tiles to occupy the 74 pairs (8192^3: 1481 against 1314 TFLOP/s,
+    // CTA per 128 x 256 tile wherever there are enough tiles to occupy most of the 74 pairs (8192^3: 1481 against 1314 TFLOP/s,
     // [32768,768].[768,3072]: 1124 against 1032); below that the narrower one-CTA tiles spread better over the SMs.
     // Products with a short K are bound by their epilogue and by HBM (the batched [2048,128].[128,2048] product ran at
     // 3.5 TB/s in pairs against 4.9 TB/s alone): a pair has to wait for both CTAs' epilogues before it reuses an accumulator.
@@ -976,7 +976,7 @@ int gemm_tc_launch(const GemmProblem& p, cudaStream_t stream) {
     // (products that also store into peers' copies included: four ranks, 8192^3 split by columns: 0.295 ms in pairs, 0.320 ms alone)
     if (cta_group == 0 && p.m > BM && p.k >= 8 * BK && rows_on_grid) {
         const int64_t pair_tiles = (p.m + 2 * BM - 1) / (2 * BM) * ((p.n + 255) / 256) * p.batch0 * p.batch1;
-        if (pair_tiles >= 60) return launch_gemm<256, 6, 2>(p, stream);
+        if (pair_tiles >= 40) return launch_gemm<256, 6, 2>(p, stream);  // (48 pairs on [4096,3072].[3072,768]: 23.7 us against 25.3 us alone)
     }
     const int64_t rows = (p.m + BM - 1) / BM * p.batch0 * p.batch1;
     const int64_t tiles_256 = rows * ((p.n + 255) / 256), tiles_128 = rows * ((p.n + 127) / 128);
