@@ -639,6 +639,17 @@ int mhlo_cuda_attention(int32_t dtype, const void* q_dev, const int64_t q_stride
                         int32_t causal, mhlo_cuda_stream_t stream);
 
 /*
+ * stablehlo.rng: `count` values of `dtype` between the scalars *a_dev and *b_dev. distribution 0 = UNIFORM (floats in
+ * [a, b), integers in [a, b)), 1 = NORMAL (mean a, standard deviation b; floats only). state_dev: two 64-bit words
+ * {key, counter} in device memory that the caller keeps for this operator; the draw reads the Threefry-2x32-20 stream
+ * at the counter and a one-thread kernel queued behind it advances the counter, so every execution - a replayed graph
+ * included - continues the stream. The operator has no state operand: its stream is implementation-defined, and the
+ * reference draws from MPSGraph's generator (Compiler/MPSGraphCompiler.swift, compileRng).
+ */
+int mhlo_cuda_rng(int32_t dtype, int32_t distribution, void* state_dev, const void* a_dev, const void* b_dev, void* out_dev,
+                  int64_t count, mhlo_cuda_stream_t stream);
+
+/*
  * stablehlo.rng_bit_generator: `count` elements of elem_bytes (1, 2, 4 or 8) of random bits and the advanced state.
  * state_dev / new_state_dev: two 64-bit words {key, counter}. Word pair b of the stream is Threefry-2x32-20 of the key
  * (low word k0, high word k1) at counter + b (low word x0, high word x1); elements of up to 32 bits take the low bits of

@@ -581,8 +581,9 @@ class Lowering {
         if (n == "cholesky") return lower_cholesky(op);
         if (n == "triangular_solve") return lower_triangular_solve(op);
         if (n == "rng_bit_generator") return lower_rng_bit_generator(op);
+        if (n == "rng") return lower_rng(op);
         if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
-            n == "rng" || n == "map" || n == "all_reduce" || n == "all_gather")
+            n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         if (n == "reduce_precision") {
             // `format = e5m10` in the pretty form, exponent_bits / mantissa_bits in the generic one
@@ -1454,6 +1455,56 @@ class Lowering {
         add_step("cholesky", [=](const Ctx& c) {
             return mhlo_cuda_cholesky(dt, bind(da, c).base, const_cast<void*>(bind(dout, c).base), batch, n, lower, c.stream);
         });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.rng(a, b, shape): values between two scalars. The operator carries no state, so each one gets 16 bytes of
+    // its own in the executable's constant pool: key = a hash of its position in the program, counter = 0 at load; the
+    // kernel advances the counter on the device, so executions (and graph replays) continue the stream.
+    void lower_rng(const Op& op) {
+        if (op.operands.size() != 3) fail_compile("rng takes a, b and the shape");
+        const TensorType& rt = op.result_types[0];
+        View a = materialize(get(op.operands[0]), "rng.a"), b = materialize(get(op.operands[1]), "rng.b");
+        if (a.type.count() != 1 || b.type.count() != 1 || a.type.dtype != rt.dtype || b.type.dtype != rt.dtype || rt.dtype == DType::I1)
+            fail_unsupported("rng of " + rt.str() + " between " + a.type.str() + " and " + b.type.str());
+        // `distribution = NORMAL` in the pretty form, rng_distribution = #stablehlo<rng_distribution NORMAL> in the generic one
+        std::string dist;
+        for (const char* key : {"rng_distribution", "distribution"}) {
+            const Attr* d = op.attr(key);
+            if (!d) continue;
+            if (d->s == "UNIFORM" || d->s == "NORMAL") dist = d->s;
+            for (const Attr& e : d->elems)
+                if (e.s == "UNIFORM" || e.s == "NORMAL") dist = e.s;
+            for (const auto& kv : d->dict)
+                if (kv.first == "UNIFORM" || kv.first == "NORMAL" || kv.second.s == "UNIFORM" || kv.second.s == "NORMAL")
+                    dist = (kv.first == "UNIFORM" || kv.first == "NORMAL") ? kv.first : kv.second.s;
+            if (dist.empty()) dist = d->s.empty() ? "?" : d->s;
+        }
+        if (dist.empty()) dist = "UNIFORM";
+        if (dist != "UNIFORM" && dist != "NORMAL") fail_unsupported("rng with distribution '" + dist + "'");
+        const int normal = dist == "NORMAL";
+        if (normal && !is_float(rt.dtype)) fail_unsupported("rng: a normal distribution of " + rt.str());
+        Buffer sb;
+        sb.kind = Buffer::Const;
+        const size_t off = (exe_->const_pool_.size() + 255) / 256 * 256;
+        exe_->const_pool_.resize(off + 16, 0);
+        uint64_t key = 0x9E3779B97F4A7C15ull * (static_cast<uint64_t>(step_index()) + 1) ^ 0xD1B54A32D192ED03ull;
+        std::memcpy(exe_->const_pool_.data() + off, &key, 8);
+        sb.offset = static_cast<int64_t>(off);
+        sb.bytes = 16;
+        TensorType stt;
+        stt.dtype = DType::UI64;
+        stt.shape = {2};
+        View st = dense_view(add_buffer(sb), stt);
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        DevView da = dev(a), db = dev(b), dst = dev(st), dout = dev(out);
+        keep_alive(a); keep_alive(b); keep_alive(st); keep_alive(out);
+        const int dt = static_cast<int>(rt.dtype);
+        const int64_t count = rt.count();
+        add_step(normal ? "rng.normal" : "rng.uniform", [=](const Ctx& c) {
+            return mhlo_cuda_rng(dt, normal, const_cast<void*>(bind(dst, c).base), bind(da, c).base, bind(db, c).base, const_cast<void*>(bind(dout, c).base),
+                                 count, c.stream);
+        }, 2);
         set(op.results[0], out);
     }
 

@@ -269,6 +269,7 @@ bool cse(Function& f) {
     for (size_t i = 0; i < f.ops.size(); ++i) {
         Op& o = f.ops[i];
         if (o.dead || has_side_effect(o) || !o.regions.empty() || o.results.size() != 1) continue;
+        if (o.name == "rng") continue;  // two draws with the same bounds are two different tensors
         if (o.name == "constant" && o.attr("value") && o.attr("value")->dense.size() > 4096) continue;
         const std::string key = op_key(f, o);
         auto it = seen.find(key);

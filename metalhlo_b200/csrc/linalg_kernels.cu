@@ -7,6 +7,7 @@
 #include "common.cuh"
 
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_fp16.h>
 
 namespace mhlo {
@@ -157,7 +158,98 @@ __global__ void rng_bits_kernel(const uint64_t* __restrict__ state, uint64_t* __
     }
 }
 
+// stablehlo.rng: `count` values drawn from the stream of state = {key, counter} (the state stays where it is; a second,
+// one-thread kernel advances its counter behind the draw, so that every execution - a graph replay included - continues the
+// stream). UNIFORM floats: a + (b - a) * u with u = the word's top 24 bits / 2^24 in [0, 1); UNIFORM integers: a + word mod
+// (b - a); NORMAL: Box-Muller on the two words of a pair, a + b * z.
+template <typename T>
+__global__ void rng_kernel(const uint64_t* __restrict__ state, const T* __restrict__ a_ptr, const T* __restrict__ b_ptr, T* __restrict__ out,
+                           int64_t count, int32_t normal) {
+    const int64_t blk = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (2 * blk >= count) return;
+    const uint64_t key = state[0], c = state[1] + static_cast<uint64_t>(blk);
+    uint32_t x0 = static_cast<uint32_t>(c), x1 = static_cast<uint32_t>(c >> 32);
+    threefry2x32(static_cast<uint32_t>(key), static_cast<uint32_t>(key >> 32), x0, x1);
+    const uint32_t w[2] = {x0, x1};
+    if constexpr (std::is_integral<T>::value) {
+        const int64_t lo = static_cast<int64_t>(*a_ptr), hi = static_cast<int64_t>(*b_ptr);
+        const uint64_t span = hi > lo ? static_cast<uint64_t>(hi - lo) : 1;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (2 * blk + i < count) out[2 * blk + i] = static_cast<T>(lo + static_cast<int64_t>((static_cast<uint64_t>(w[i]) | (static_cast<uint64_t>(w[1 - i]) << 32)) % span));
+    } else {
+        const float a = static_cast<float>(ld(a_ptr)), b = static_cast<float>(ld(b_ptr));
+        float v[2];
+        if (normal) {
+            const float u1 = (static_cast<float>(w[0] >> 8) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+            const float u2 = static_cast<float>(w[1] >> 8) * (1.0f / 16777216.0f);
+            const float r = sqrtf(-2.0f * logf(u1));
+            float sn, cs;
+            sincospif(2.0f * u2, &sn, &cs);
+            v[0] = a + b * r * cs;
+            v[1] = a + b * r * sn;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float u = static_cast<float>(w[i] >> 8) * (1.0f / 16777216.0f);
+                float x = a + (b - a) * u;
+                // rounding (of the product, or of the result to a 16-bit type) may reach the open end of the interval
+                T rounded;
+                st(&rounded, static_cast<typename Compute<T>::type>(x));
+                if (!(static_cast<float>(ld(&rounded)) < b) && b > a) x = a;
+                v[i] = x;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (2 * blk + i < count) st(out + 2 * blk + i, v[i]);
+    }
+}
+
+__global__ void rng_advance_kernel(uint64_t* state, uint64_t blocks) { state[1] += blocks; }
+
+template <typename T>
+int launch_rng(uint64_t* state, const void* a, const void* b, void* out, int64_t count, int normal, cudaStream_t s) {
+    const int64_t blocks = (count + 1) / 2;
+    if (blocks > 0) {
+        rng_kernel<T><<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, s>>>(state, static_cast<const T*>(a), static_cast<const T*>(b),
+                                                                                 static_cast<T*>(out), count, normal);
+        MHLO_CUDA_CHECK_LAUNCH("rng");
+    }
+    rng_advance_kernel<<<1, 1, 0, s>>>(state, static_cast<uint64_t>(blocks));
+    MHLO_CUDA_CHECK_LAUNCH("rng state");
+    return MHLO_CUDA_OK;
+}
+
 extern "C" {
+
+int mhlo_cuda_rng(int32_t dtype, int32_t distribution, void* state_dev, const void* a_dev, const void* b_dev, void* out_dev, int64_t count,
+                  mhlo_cuda_stream_t stream) {
+    if (count < 0) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng: negative count");
+    if (distribution != 0 && distribution != 1) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng: distribution %d (0 uniform, 1 normal)", distribution);
+    if (!state_dev || !a_dev || !b_dev || (count > 0 && !out_dev)) return fail(MHLO_CUDA_INVALID_ARGUMENT, "rng: null pointer");
+    uint64_t* st = static_cast<uint64_t*>(state_dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case MHLO_DT_F32: return launch_rng<float>(st, a_dev, b_dev, out_dev, count, distribution, s);
+        case MHLO_DT_F64: return launch_rng<double>(st, a_dev, b_dev, out_dev, count, distribution, s);
+        case MHLO_DT_F16: return launch_rng<__half>(st, a_dev, b_dev, out_dev, count, distribution, s);
+        case MHLO_DT_BF16: return launch_rng<__nv_bfloat16>(st, a_dev, b_dev, out_dev, count, distribution, s);
+        default: break;
+    }
+    if (distribution == 1) return fail(MHLO_CUDA_UNSUPPORTED, "rng: a normal distribution of dtype %d", dtype);
+    switch (dtype) {
+        case MHLO_DT_I32: return launch_rng<int32_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_I64: return launch_rng<int64_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_UI32: return launch_rng<uint32_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_UI64: return launch_rng<uint64_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_I8: return launch_rng<int8_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_I16: return launch_rng<int16_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_UI8: return launch_rng<uint8_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        case MHLO_DT_UI16: return launch_rng<uint16_t>(st, a_dev, b_dev, out_dev, count, 0, s);
+        default: return fail(MHLO_CUDA_UNSUPPORTED, "rng: dtype %d", dtype);
+    }
+}
 
 int mhlo_cuda_rng_bit_generator(const void* state_dev, void* new_state_dev, void* out_dev, int64_t count, int32_t elem_bytes,
                                 mhlo_cuda_stream_t stream) {

@@ -101,3 +101,65 @@ def test_residual_product_outside_the_tensor_core_path():
         tol = 1e-5 if dtype == torch.float32 else 2e-2
         assert (got.double() - want).abs().max() <= tol * want.abs().max()
     assert cuda.device_error() == 0
+
+
+RNG_TEXT = """func.func @main(%a: tensor<{dt}>, %b: tensor<{dt}>) -> tensor<{n}x{dt}> {{
+  %s = stablehlo.constant dense<[{n}]> : tensor<1xi64>
+  %0 = stablehlo.rng %a, %b, %s, distribution = {dist} : (tensor<{dt}>, tensor<{dt}>, tensor<1xi64>) -> tensor<{n}x{dt}>
+  return %0 : tensor<{n}x{dt}>
+}}"""
+
+
+def run_rng(dt, np_dt, dist, a, b, n=200_000, level=2):
+    from metalhlo_b200 import capi
+
+    c = capi.Client()
+    exe = c.compile(RNG_TEXT.format(dt=dt, n=n, dist=dist), level)
+    ins = [c.buffer(np.asarray(a, dtype=np_dt)), c.buffer(np.asarray(b, dtype=np_dt))]
+    return [exe.execute(ins)[0].to_numpy() for _ in range(3)]
+
+
+def test_uniform_floats_fill_the_interval_and_every_execution_continues_the_stream():
+    draws = run_rng("f32", np.float32, "UNIFORM", -2.0, 6.0)
+    for d in draws:
+        assert d.min() >= -2.0 and d.max() < 6.0
+        assert abs(d.mean() - 2.0) < 0.05 and abs(d.std() - 8 / 12 ** 0.5) < 0.05
+        hist = np.histogram(d, bins=16, range=(-2, 6))[0]
+        assert hist.min() > 0.9 * d.size / 16 and hist.max() < 1.1 * d.size / 16
+    assert not np.array_equal(draws[0], draws[1]) and not np.array_equal(draws[1], draws[2])
+    assert len(np.intersect1d(draws[0][:1000], draws[1][:1000])) < 5  # not the same numbers shifted or repeated
+
+
+def test_normal_floats_have_the_asked_moments():
+    for dt, np_dt in (("f32", np.float32), ("f64", np.float64)):
+        d = run_rng(dt, np_dt, "NORMAL", 1.5, 0.5)[0].astype(np.float64)
+        assert abs(d.mean() - 1.5) < 0.01 and abs(d.std() - 0.5) < 0.01
+        z = (d - 1.5) / 0.5
+        assert abs((z ** 3).mean()) < 0.05 and abs((z ** 4).mean() - 3.0) < 0.1
+        assert 0.66 < (np.abs(z) < 1).mean() < 0.70
+
+
+def test_uniform_integers_cover_their_range():
+    for dt, np_dt in (("i32", np.int32), ("ui8", np.uint8), ("i64", np.int64)):
+        d = run_rng(dt, np_dt, "UNIFORM", 3, 13, n=100_000)[0]
+        assert d.min() == 3 and d.max() == 12
+        counts = np.bincount(d.astype(np.int64) - 3, minlength=10)
+        assert counts.min() > 0.9 * d.size / 10 and counts.max() < 1.1 * d.size / 10
+
+
+def test_sixteen_bit_draws_and_two_operators_in_one_program():
+    """Two rng operators of one program draw from different keys; f16 results stay inside the half-open interval."""
+    from metalhlo_b200 import capi
+
+    text = """func.func @main(%a: tensor<f16>, %b: tensor<f16>) -> (tensor<4096xf16>, tensor<4096xf16>) {
+  %s = stablehlo.constant dense<[4096]> : tensor<1xi64>
+  %0 = stablehlo.rng %a, %b, %s, distribution = UNIFORM : (tensor<f16>, tensor<f16>, tensor<1xi64>) -> tensor<4096xf16>
+  %1 = stablehlo.rng %a, %b, %s, distribution = UNIFORM : (tensor<f16>, tensor<f16>, tensor<1xi64>) -> tensor<4096xf16>
+  return %0, %1 : tensor<4096xf16>, tensor<4096xf16>
+}"""
+    c = capi.Client()
+    exe = c.compile(text, 3)
+    x, y = [o.to_numpy() for o in exe.execute([c.buffer(np.float16(0)), c.buffer(np.float16(1))])]
+    assert x.min() >= 0 and x.max() < 1 and y.min() >= 0 and y.max() < 1
+    assert not np.array_equal(x, y)
+    assert abs(float(x.astype(np.float32).mean()) - 0.5) < 0.03
