@@ -170,6 +170,17 @@ int mhlo_cuda_add_layer_norm(int dtype, const void* x_dev, const void* residual_
 int mhlo_cuda_add_rms_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev,
                            void* sum_dev, void* y_dev, int64_t rows, int64_t hidden, float eps,
                            const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
+/*
+ * The same with a residual of residual_rows rows that repeats down the tensor (rows a multiple of residual_rows): row r
+ * adds residual row r mod residual_rows. The position table added to the token embeddings before the first norm of a
+ * transformer is this form: [sequence, hidden] repeated over the batch.
+ */
+int mhlo_cuda_add_layer_norm_rows(int dtype, const void* x_dev, const void* residual_dev, int64_t residual_rows,
+                                  const void* gamma_dev, const void* beta_dev, void* sum_dev, void* y_dev, int64_t rows,
+                                  int64_t hidden, float eps, const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
+int mhlo_cuda_add_rms_norm_rows(int dtype, const void* x_dev, const void* residual_dev, int64_t residual_rows,
+                                const void* gamma_dev, void* sum_dev, void* y_dev, int64_t rows, int64_t hidden, float eps,
+                                const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream);
 
 /*
  * Softmax along one axis of a tensor viewed as [outer, axis_len, inner] (inner = 1 for the last axis):

@@ -129,6 +129,30 @@ std::vector<int64_t> dense_strides(const std::vector<int64_t>& shape) {
     return s;
 }
 
+// A view whose leading dimensions repeat (stride 0) over a dense block that holds whole rows of the last axis, e.g. a
+// [sequence, hidden] table broadcast over the batch: the block as a dense view of its own, and how many rows it has.
+bool repeated_rows(const View& v, View* block, int64_t* block_rows) {
+    const int rank = v.type.rank();
+    if (rank < 2) return false;
+    int d0 = 0;
+    while (d0 < rank - 1 && (v.strides[d0] == 0 || v.type.shape[d0] == 1)) ++d0;
+    if (d0 == 0) return false;
+    int64_t expect = 1, rows = 1;
+    for (int d = rank - 1; d >= d0; --d) {
+        if (v.type.shape[d] != 1 && v.strides[d] != expect) return false;
+        expect *= v.type.shape[d];
+        if (d < rank - 1) rows *= v.type.shape[d];
+    }
+    if (expect == 0) return false;
+    block->buf = v.buf;
+    block->offset = v.offset;
+    block->type = v.type;
+    block->type.shape.assign(v.type.shape.begin() + d0, v.type.shape.end());
+    block->strides = dense_strides(block->type.shape);
+    *block_rows = rows;
+    return true;
+}
+
 bool is_dense(const View& v) {
     int64_t expect = 1;
     for (int d = v.type.rank() - 1; d >= 0; --d) {
@@ -1771,7 +1795,14 @@ void Lowering::lower_custom_call(const Op& op) {
         // results: [0] the sum a + b (the residual stream), [1] its norm
         const bool ln = target == "fused_add_layer_norm";
         if (op.results.size() != 2) fail_compile(target + " must have two results");
-        if (!is_dense(operand(0)) || !is_dense(operand(1))) {
+        View addend_block;
+        int64_t addend_rows = 0;  // > 0: one addend is a block of that many rows repeated down the other
+        int dense_side = -1;
+        for (int side = 0; side < 2 && dense_side < 0; ++side)
+            if (is_dense(operand(side)) && !is_dense(operand(1 - side)) && repeated_rows(operand(1 - side), &addend_block, &addend_rows))
+                dense_side = side;
+        if (dense_side < 0) addend_rows = 0;
+        if (dense_side < 0 && (!is_dense(operand(0)) || !is_dense(operand(1)))) {
             // a broadcast or transposed addend would have to be copied first: the strided elementwise add reads it in
             // place, and the norm then runs on its result
             mhlo_cuda_ew_inst add_inst = {ew_opcode("add"), 0, 1, 0, 0.0};
@@ -1785,7 +1816,8 @@ void Lowering::lower_custom_call(const Op& op) {
             plain.attrs["call_target_name"] = Attr::make_string(ln ? "fused_layer_norm" : "fused_rms_norm");
             return lower_custom_call(plain);
         }
-        View a = materialize(operand(0), target + ".a"), r = materialize(operand(1), target + ".b");
+        View a = materialize(operand(dense_side == 1 ? 1 : 0), target + ".a");
+        View r = dense_side >= 0 ? materialize(addend_block, target + ".b") : materialize(operand(1), target + ".b");
         if (!last_axis_only(json_int_array(cfg, "axes"), a.type.rank())) fail_unsupported(target + " over an axis other than the last");
         const int64_t hidden = a.type.rank() ? a.type.shape.back() : 1;
         const int64_t rows = hidden ? a.type.count() / hidden : 0;
@@ -1804,12 +1836,16 @@ void Lowering::lower_custom_call(const Op& op) {
         const int dt = static_cast<int>(a.type.dtype);
         mhlo_cuda_row_tuning tuning{0, 0, 0};
         const bool tuned = lookup_row_tuning(ln ? "fused_layer_norm" : "fused_rms_norm", rows, hidden, a.type.dtype, &tuning);
-        add_step(target, [=](const Ctx& c) {
+        add_step(addend_rows > 0 ? target + " [repeated addend]" : target, [=](const Ctx& c) {
             const void* gp = has_g ? bind(dg, c).base : nullptr;
             const void* bp = has_b ? bind(db, c).base : nullptr;
             const mhlo_cuda_row_tuning* tp = tuned ? &tuning : nullptr;
             void* sp = const_cast<void*>(bind(dsum, c).base);
             void* yp = const_cast<void*>(bind(dout, c).base);
+            if (addend_rows > 0) {
+                if (ln) return mhlo_cuda_add_layer_norm_rows(dt, bind(da, c).base, bind(dr, c).base, addend_rows, gp, bp, sp, yp, rows, hidden, eps, tp, c.stream);
+                return mhlo_cuda_add_rms_norm_rows(dt, bind(da, c).base, bind(dr, c).base, addend_rows, gp, sp, yp, rows, hidden, eps, tp, c.stream);
+            }
             if (ln) return mhlo_cuda_add_layer_norm(dt, bind(da, c).base, bind(dr, c).base, gp, bp, sp, yp, rows, hidden, eps, tp, c.stream);
             return mhlo_cuda_add_rms_norm(dt, bind(da, c).base, bind(dr, c).base, gp, sp, yp, rows, hidden, eps, tp, c.stream);
         });

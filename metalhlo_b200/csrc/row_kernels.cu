@@ -76,7 +76,8 @@ constexpr int kDepth = 2;
 template <typename T, int VPT, int OP, bool FULL, bool ADD>
 __global__ void __launch_bounds__((row_vec_max_threads<T, VPT>()))
 row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-               T* __restrict__ y, int64_t rows, int hidden, float eps, const T* __restrict__ res, T* __restrict__ sum_out) {
+               T* __restrict__ y, int64_t rows, int hidden, float eps, const T* __restrict__ res, T* __restrict__ sum_out,
+               int64_t res_rows) {  // res has res_rows rows, repeated down the tensor (res_rows = rows: one per row)
     using VT = VecTraits<T>;
     constexpr int E = VT::kElems;
     constexpr int H = E / 2;  // float2 per vector
@@ -147,7 +148,7 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
             for (int i = 0; i < VPT; ++i)
                 if (live[i]) raw[d][i] = ld_stream16(xr + tid + i * nthreads);
             if constexpr (ADD) {
-                const uint4* rr = reinterpret_cast<const uint4*>(res + r * hidden);
+                const uint4* rr = reinterpret_cast<const uint4*>(res + (r % res_rows) * hidden);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
                     if (live[i]) raw_res[d][i] = ld_stream16(rr + tid + i * nthreads);
@@ -186,7 +187,7 @@ row_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
             for (int i = 0; i < VPT; ++i)
                 if (live[i]) raw[d][i] = ld_stream16(xn + tid + i * nthreads);
             if constexpr (ADD) {
-                const uint4* rn = reinterpret_cast<const uint4*>(res + next * hidden);
+                const uint4* rn = reinterpret_cast<const uint4*>(res + (next % res_rows) * hidden);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
                     if (live[i]) raw_res[d][i] = ld_stream16(rn + tid + i * nthreads);
@@ -338,19 +339,21 @@ __global__ void __launch_bounds__(256) row_strided_kernel(const T* __restrict__ 
 // out = round(a + b) elementwise: the sum a fused add + norm has to produce when the row kernel's fast path is not
 // available (odd lengths, unaligned pointers).
 template <typename T>
-__global__ void __launch_bounds__(256) add_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+__global__ void __launch_bounds__(256) add_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n,
+                                                       int64_t b_period) {  // b holds b_period elements, repeated
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step)
-        out[i] = static_cast<T>(static_cast<float>(a[i]) + static_cast<float>(b[i]));
+        out[i] = static_cast<T>(static_cast<float>(a[i]) + static_cast<float>(b[i % b_period]));
 }
 
 template <typename T, int OP>
 int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int64_t outer, int64_t len,
                 int64_t inner, float eps, const mhlo_cuda_row_tuning* tuning, cudaStream_t stream,
-                const char* what, const void* res = nullptr, void* sum_out = nullptr) {
+                const char* what, const void* res = nullptr, void* sum_out = nullptr, int64_t res_rows = 0) {
     constexpr int E = VecTraits<T>::kElems;
     const int64_t rows = outer * inner;
     if (rows == 0 || len == 0) return MHLO_CUDA_OK;
+    if (res_rows <= 0) res_rows = rows;
     const T* xp = static_cast<const T*>(x);
     const T* gp = static_cast<const T*>(gamma);
     const T* bp = static_cast<const T*>(beta);
@@ -368,7 +371,7 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         if (with_add) {
             const int64_t n = rows * len;
             add_rows_kernel<T><<<static_cast<int>(n < 148LL * 2048 ? (n + 255) / 256 : 148 * 8), 256, 0, stream>>>(
-                xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n);
+                xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n, res_rows * len);
             xp = static_cast<const T*>(sum_out);
         }
         row_strided_kernel<T, OP><<<grid, 256, 0, stream>>>(xp, gp, bp, yp, rows, len, inner, eps);
@@ -380,7 +383,7 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         // an fp32 row too long for two vectors per thread: separate add, then the plain norm on the sum
         const int64_t n = rows * len;
         add_rows_kernel<T><<<static_cast<int>(n < 148LL * 2048 ? (n + 255) / 256 : 148 * 8), 256, 0, stream>>>(
-            xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n);
+            xp, static_cast<const T*>(res), static_cast<T*>(sum_out), n, res_rows * len);
         MHLO_CUDA_CHECK_LAUNCH(what);
         return launch_rows<T, OP>(sum_out, gamma, beta, y, outer, len, inner, eps, tuning, stream, what);
     }
@@ -422,7 +425,7 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: %d threads x %d vectors need %zu bytes of shared memory",
                     what, threads, vpt, smem);
 
-    using Kernel = void (*)(const T*, const T*, const T*, T*, int64_t, int, float, const T*, T*);
+    using Kernel = void (*)(const T*, const T*, const T*, T*, int64_t, int, float, const T*, T*, int64_t);
     Kernel kernel = nullptr;
     // the residual ring doubles the registers held per vector: fp32 rows take it only up to two vectors per thread
 #define MHLO_ROW_PICK(V)                                                                                              \
@@ -465,7 +468,7 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
     }
     if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
     const cudaError_t launched = launch_dependent(kernel, dim3(static_cast<unsigned>(grid)), dim3(static_cast<unsigned>(threads)), smem, stream, xp, gp, bp, yp,
-                                                  rows, static_cast<int>(len), eps, static_cast<const T*>(res), static_cast<T*>(sum_out));
+                                                  rows, static_cast<int>(len), eps, static_cast<const T*>(res), static_cast<T*>(sum_out), res_rows);
     if (launched != cudaSuccess) return fail(MHLO_CUDA_EXECUTION_FAILED, "launch of %s failed: %s", what, cudaGetErrorString(launched));
     MHLO_CUDA_CHECK_LAUNCH(what);
     return MHLO_CUDA_OK;
@@ -474,7 +477,9 @@ int launch_rows(const void* x, const void* gamma, const void* beta, void* y, int
 template <int OP>
 int dispatch_rows(int dtype, const void* x, const void* gamma, const void* beta, void* y, int64_t outer,
                   int64_t len, int64_t inner, float eps, const mhlo_cuda_row_tuning* tuning, void* stream,
-                  const char* what, const void* res = nullptr, void* sum_out = nullptr) {
+                  const char* what, const void* res = nullptr, void* sum_out = nullptr, int64_t res_rows = 0) {
+    if (res != nullptr && (res_rows < 0 || (res_rows > 0 && (outer * inner) % res_rows != 0)))
+        return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: %lld residual rows do not tile %lld rows", what, (long long)res_rows, (long long)(outer * inner));
     if (outer < 0 || len < 0 || inner < 0)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "%s: negative extent", what);
     if (outer * len * inner > 0 && (x == nullptr || y == nullptr))
@@ -484,11 +489,11 @@ int dispatch_rows(int dtype, const void* x, const void* gamma, const void* beta,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case MHLO_DT_F32:
-            return launch_rows<float, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
+            return launch_rows<float, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out, res_rows);
         case MHLO_DT_F16:
-            return launch_rows<__half, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
+            return launch_rows<__half, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out, res_rows);
         case MHLO_DT_BF16:
-            return launch_rows<__nv_bfloat16, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out);
+            return launch_rows<__nv_bfloat16, OP>(x, gamma, beta, y, outer, len, inner, eps, tuning, s, what, res, sum_out, res_rows);
         default:
             return fail(MHLO_CUDA_UNSUPPORTED, "%s: dtype %d is not a float type this kernel handles", what,
                         dtype);
@@ -520,6 +525,24 @@ int mhlo_cuda_add_layer_norm(int dtype, const void* x_dev, const void* residual_
         return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "add_layer_norm: null residual or sum pointer");
     return mhlo::dispatch_rows<mhlo::kLayerNorm>(dtype, x_dev, gamma_dev, beta_dev, y_dev, rows, hidden, 1, eps, tuning, stream,
                                                  "add_layer_norm", residual_dev, sum_dev);
+}
+
+int mhlo_cuda_add_layer_norm_rows(int dtype, const void* x_dev, const void* residual_dev, int64_t residual_rows, const void* gamma_dev,
+                                  const void* beta_dev, void* sum_dev, void* y_dev, int64_t rows, int64_t hidden, float eps,
+                                  const mhlo_cuda_row_tuning* tuning, mhlo_cuda_stream_t stream) {
+    if (rows * hidden > 0 && (residual_dev == nullptr || sum_dev == nullptr))
+        return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "add_layer_norm: null residual or sum pointer");
+    return mhlo::dispatch_rows<mhlo::kLayerNorm>(dtype, x_dev, gamma_dev, beta_dev, y_dev, rows, hidden, 1, eps, tuning, stream,
+                                                 "add_layer_norm", residual_dev, sum_dev, residual_rows);
+}
+
+int mhlo_cuda_add_rms_norm_rows(int dtype, const void* x_dev, const void* residual_dev, int64_t residual_rows, const void* gamma_dev, void* sum_dev,
+                                void* y_dev, int64_t rows, int64_t hidden, float eps, const mhlo_cuda_row_tuning* tuning,
+                                mhlo_cuda_stream_t stream) {
+    if (rows * hidden > 0 && (residual_dev == nullptr || sum_dev == nullptr))
+        return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "add_rms_norm: null residual or sum pointer");
+    return mhlo::dispatch_rows<mhlo::kRmsNorm>(dtype, x_dev, gamma_dev, nullptr, y_dev, rows, hidden, 1, eps, tuning, stream,
+                                               "add_rms_norm", residual_dev, sum_dev, residual_rows);
 }
 
 int mhlo_cuda_add_rms_norm(int dtype, const void* x_dev, const void* residual_dev, const void* gamma_dev, void* sum_dev, void* y_dev,

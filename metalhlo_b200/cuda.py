@@ -109,6 +109,8 @@ _PROTOTYPES = {
     "mhlo_cuda_reduce": (C.c_int, [C.POINTER(View), _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
     "mhlo_cuda_add_layer_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_add_rms_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
+    "mhlo_cuda_add_layer_norm_rows": (C.c_int, [C.c_int, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
+    "mhlo_cuda_add_rms_norm_rows": (C.c_int, [C.c_int, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_graph_capture_begin": (C.c_int, [_vp]),
     "mhlo_cuda_graph_capture_end": (C.c_int, [_vp, C.POINTER(_vp)]),
     "mhlo_cuda_graph_launch": (C.c_int, [_vp, _vp]),
@@ -246,10 +248,14 @@ def add_layer_norm(x, residual, gamma, beta, eps: float = 1e-5, tuning=None, str
     """(x + residual, LayerNorm(x + residual)) in one pass (see ``mhlo_cuda_add_layer_norm``)."""
     import torch
 
-    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous() and residual.shape == x.shape
+    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous()
     total, out = torch.empty_like(x), torch.empty_like(x)
     hidden = x.shape[-1]
     rows = x.numel() // hidden if hidden else 0
+    if residual.shape != x.shape:  # a block of rows repeated down x (``mhlo_cuda_add_layer_norm_rows``)
+        check(lib.mhlo_cuda_add_layer_norm_rows(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), residual.numel() // hidden, _ptr(gamma),
+                                                _ptr(beta), _ptr(total), _ptr(out), rows, hidden, eps, _tuning(tuning), _stream(stream)))
+        return total, out
     check(lib.mhlo_cuda_add_layer_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), _ptr(gamma), _ptr(beta), _ptr(total), _ptr(out),
                                        rows, hidden, eps, _tuning(tuning), _stream(stream)))
     return total, out
@@ -258,10 +264,14 @@ def add_layer_norm(x, residual, gamma, beta, eps: float = 1e-5, tuning=None, str
 def add_rms_norm(x, residual, gamma, eps: float = 1e-5, tuning=None, stream=None):
     import torch
 
-    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous() and residual.shape == x.shape
+    assert x.is_cuda and x.is_contiguous() and residual.is_contiguous()
     total, out = torch.empty_like(x), torch.empty_like(x)
     hidden = x.shape[-1]
     rows = x.numel() // hidden if hidden else 0
+    if residual.shape != x.shape:
+        check(lib.mhlo_cuda_add_rms_norm_rows(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), residual.numel() // hidden, _ptr(gamma),
+                                              _ptr(total), _ptr(out), rows, hidden, eps, _tuning(tuning), _stream(stream)))
+        return total, out
     check(lib.mhlo_cuda_add_rms_norm(torch_dtype_code(x.dtype), _ptr(x), _ptr(residual), _ptr(gamma), _ptr(total), _ptr(out), rows, hidden,
                                      eps, _tuning(tuning), _stream(stream)))
     return total, out

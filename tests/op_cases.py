@@ -370,6 +370,20 @@ def pattern_cases(rng, dt):
     body, res = layer_norm_text("%s0", shape, dt, "%arg2", None, eps=1e-6, rms=True)
     out.append((f"pattern_residual_rms_norm_{dt}", func([t, t, tv], [t, t], f"    %s0 = stablehlo.add %arg0, %arg1 : {t}\n" + body.rstrip("\n"),
                                                          f"%s0, {res}"), [x, xr, g]))
+    # the same with an addend that repeats over the leading axis (a position table over the batch): the norm kernel
+    # reads the table's rows modulo its height, on either side of the add
+    tp = tt(shape[1:], dt)
+    xp = (0.5 * np.random.default_rng(7 + sum(map(ord, dt))).standard_normal(shape[1:])).astype(np.float32).astype(NP[dt])
+    dims = list(range(1, len(shape)))
+    for side in (0, 1):
+        add = "%arg0, %p0" if side == 0 else "%p0, %arg0"
+        head = (f"    %p0 = stablehlo.broadcast_in_dim %arg1, dims = {dims} : ({tp}) -> {t}\n"
+                f"    %s0 = stablehlo.add {add} : {t}\n")
+        body, res = layer_norm_text("%s0", shape, dt, "%arg2", "%arg3")
+        out.append((f"pattern_residual_table_layer_norm_side{side}_{dt}", func([t, tp, tv, tv], [t, t], head + body.rstrip("\n"), f"%s0, {res}"),
+                    [x, xp, g, b]))
+    body, res = layer_norm_text("%s0", shape, dt, "%arg2", None, eps=1e-6, rms=True)
+    out.append((f"pattern_residual_table_rms_norm_{dt}", func([t, tp, tv], [t, t], head + body.rstrip("\n"), f"%s0, {res}"), [x, xp, g]))
     body, res = gelu_text("%arg0", shape, dt)
     out.append((f"pattern_gelu_{dt}", func([t], [t], body.rstrip("\n"), res), [x]))
     # dense layer: x.w + b then GELU (fused_matmul_bias_activation at O3)

@@ -78,6 +78,8 @@ def test_o3_rewrites_patterns_to_the_reference_custom_call_targets(dt):
         f"pattern_layer_norm_{dt}": ["fused_layer_norm"], f"pattern_layer_norm_plain_{dt}": ["fused_layer_norm"],
         f"pattern_rms_norm_{dt}": ["fused_rms_norm"], f"pattern_gelu_{dt}": ["fused_gelu"],
         f"pattern_residual_layer_norm_{dt}": ["fused_add_layer_norm"], f"pattern_residual_rms_norm_{dt}": ["fused_add_rms_norm"],
+        f"pattern_residual_table_layer_norm_side0_{dt}": ["fused_add_layer_norm"], f"pattern_residual_table_layer_norm_side1_{dt}": ["fused_add_layer_norm"],
+        f"pattern_residual_table_rms_norm_{dt}": ["fused_add_rms_norm"],
         f"pattern_dense_gelu_{dt}": ["fused_matmul_bias_activation"],
         f"pattern_dense_residual_norm_{dt}": ["fused_matmul_bias_activation", "fused_add_layer_norm"],
         f"pattern_dense_residual_plain_{dt}": ["fused_matmul_bias_activation"],
@@ -183,3 +185,15 @@ def test_dot_general_layout_canonicalisation_inserts_transposes():
     assert live_ops(out).count("transpose") == 2
     assert "lhs_batching_dimensions = [0, 1]" in out and "rhs_contracting_dimensions = [2]" in out
     assert "transpose" not in live_ops(capi.optimize_text(text, 0))
+
+
+def test_position_table_added_before_the_first_norm_is_read_by_the_norm_kernel():
+    # add(gathered tokens, broadcast position table) + LayerNorm: one launch that reads the table's rows modulo its height
+    from metalhlo_b200 import modules
+    text = modules.gpt2_module(batch=2, seq=64, layers=1)
+    text = text[0] if isinstance(text, tuple) else text
+    steps, _, _ = capi.plan_text(text, 3)
+    assert "fused_add_layer_norm [repeated addend]" in steps[:4] and "add" not in steps[:4]
+    for dt in ("f32", "f16", "bf16"):
+        for name in (f"pattern_residual_table_layer_norm_side0_{dt}", f"pattern_residual_table_layer_norm_side1_{dt}", f"pattern_residual_table_rms_norm_{dt}"):
+            assert capi.plan_text(BY_NAME[name][1], 3)[0][0].endswith("[repeated addend]")

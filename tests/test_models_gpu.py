@@ -67,9 +67,10 @@ def test_reduced_gpt2_forward(level, dt):
     if level == 3:
         fused = [s for s in exe.steps if s.startswith("fused")]
         assert fused.count("fused_scaled_dot_product_attention") == 2
-        # the embedding sum feeds the first norm through a broadcast addend (separate add), the other four residual adds
-        # are fused into their norms
-        assert fused.count("fused_layer_norm") == 1 and fused.count("fused_add_layer_norm") == 4
+        # all five residual adds are fused into their norms; the first one (token rows + position table) reads the table
+        # as a block of rows repeated over the batch
+        assert fused.count("fused_layer_norm") == 0 and fused.count("fused_add_layer_norm") == 4
+        assert fused.count("fused_add_layer_norm [repeated addend]") == 1
         assert fused.count("fused_matmul_bias_activation") == 8
     # greedy next-token ids agree wherever the oracle's top-2 margin exceeds the 16-bit resolution
     top2 = np.sort(want, axis=-1)[..., -2:]

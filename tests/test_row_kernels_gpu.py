@@ -59,6 +59,32 @@ def test_residual_add_fused_into_the_norm(dtype, rows, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("batch,block,hidden", [(8, 64, 768), (3, 5, 1024), (1, 7, 256), (37, 1, 4096), (4, 6, 1001), (2, 3, 16384)])
+def test_residual_block_repeated_down_the_rows(dtype, batch, block, hidden):
+    """A [block, hidden] residual added to every one of `batch` groups of rows (a position table over the batch)."""
+    cuda = cuda_mod()
+    x, gamma, beta = make_rows(batch * block, hidden, dtype, seed=15)
+    r = make_rows(block, hidden, dtype, seed=16, scale=0.5)[0]
+    want_sum = (x.float().view(batch, block, hidden) + r.float()).to(dtype).view(batch * block, hidden)
+    rel = rel_for(dtype)
+    total, out = cuda.add_layer_norm(x.cuda(), r.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    assert torch.equal(total.cpu().view(torch.uint8), want_sum.view(torch.uint8))
+    assert_close(to_np(out), oracle.layer_norm(want_sum, gamma, beta, 1e-5), rel, "add_layer_norm_rows")
+    total, out = cuda.add_rms_norm(x.cuda(), r.cuda(), gamma.cuda(), 1e-5)
+    assert torch.equal(total.cpu().view(torch.uint8), want_sum.view(torch.uint8))
+    assert_close(to_np(out), oracle.rms_norm(want_sum, gamma, 1e-5), rel, "add_rms_norm_rows")
+
+
+def test_residual_block_that_does_not_tile_the_rows_is_rejected():
+    cuda = cuda_mod()
+    x, gamma, beta = make_rows(10, 256, torch.float16)
+    r = make_rows(4, 256, torch.float16, seed=3)[0]
+    with pytest.raises(cuda.MhloCudaError) as e:
+        cuda.add_layer_norm(x.cuda(), r.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    assert "do not tile" in str(e.value)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
 @pytest.mark.parametrize("rows,hidden", [(9, 1), (4, 7), (3, 1001), (2, 70001), (1, 300000)])
 def test_ragged_hidden_takes_the_strided_path(dtype, rows, hidden):
     cuda = cuda_mod()
