@@ -686,6 +686,18 @@ int mhlo_cuda_triangular_solve(int32_t dtype, const void* a_dev, const void* b_d
                                int64_t n, int32_t left_side, int32_t lower, int32_t unit_diagonal, int32_t transpose_a,
                                mhlo_cuda_stream_t stream);
 
+/* ---- stablehlo.fft -------------------------------------------------------------------------------------------------
+ * One pass of a discrete Fourier transform along one axis. Complex tensors are (re, im) pairs of f32 or f64 (dtype is the
+ * part type), the layout the reference's FFT kernels read and write on float tensors
+ * (Sources/MetalHLOCore/Compiler/CodeGenerator.swift:2701-2830). kind 0 = forward and 1 = inverse (scaled by 1/n) between
+ * complex tensors [outer, n, inner]; these may run in place (out_dev == in_dev). kind 2 = real [outer, n] to the
+ * n/2 + 1 leading bins [outer, n/2 + 1]; kind 3 = those bins back to the real line, scaled by 1/n (inner must be 1 for
+ * both; not in place). A transform over several axes is one call per axis. n is bounded by the shared memory a line
+ * needs (status MHLO_CUDA_UNSUPPORTED beyond it): powers of two up to 8192 points in f32 take a radix-2 Stockham FFT, every
+ * other length up to 14 000 the direct sum the reference uses for all lengths; half of either in f64. */
+int mhlo_cuda_fft_axis(int32_t dtype, int32_t kind, const void* in_dev, void* out_dev, int64_t outer, int64_t n, int64_t inner,
+                       mhlo_cuda_stream_t stream);
+
 /* ---- dispatch plans ----------------------------------------------------------------------------------------------
  * The surface a host-side executor binds instead of MTLComputePipelineState / MTLBuffer / compute encoders
  * (MetalHLOCompiler.compileKernel, Sources/MetalHLOCore/Compiler/MetalHLOCompiler.swift:329-401; IntegratedExecutor,

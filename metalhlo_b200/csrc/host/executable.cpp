@@ -606,7 +606,8 @@ class Lowering {
         if (n == "triangular_solve") return lower_triangular_solve(op);
         if (n == "rng_bit_generator") return lower_rng_bit_generator(op);
         if (n == "rng") return lower_rng(op);
-        if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" || n == "fft" ||
+        if (n == "fft") return lower_fft(op);
+        if (n == "tuple" || n == "get_tuple_element" || n == "if" || n == "case" || n == "call" ||
             n == "map" || n == "all_reduce" || n == "all_gather")
             fail_unsupported("operation stablehlo." + n + " is outside this backend's operator surface");
         if (n == "reduce_precision") {
@@ -1479,6 +1480,87 @@ class Lowering {
         add_step("cholesky", [=](const Ctx& c) {
             return mhlo_cuda_cholesky(dt, bind(da, c).base, const_cast<void*>(bind(dout, c).base), batch, n, lower, c.stream);
         });
+        set(op.results[0], out);
+    }
+
+    // stablehlo.fft over the last one to three axes. Complex tensors are float tensors of (re, im) pairs by the time they
+    // get here, whether the text had complex types or gave the pairs as floats the way the reference's kernels take them
+    // (Sources/MetalHLOCore/Compiler/CodeGenerator.swift:2701-2830), so only element counts are checked. One launch per
+    // axis: the half transform on the innermost axis first (RFFT) or last (IRFFT), the others in place.
+    void lower_fft(const Op& op) {
+        if (op.operands.size() != 1) fail_compile("fft takes one operand");
+        std::string kind;
+        for (const char* key : {"fft_type", "type"}) {
+            const Attr* a = op.attr(key);
+            if (!a) continue;
+            std::vector<std::string> words = {a->s};
+            for (const Attr& e : a->elems) words.push_back(e.s);
+            for (const auto& kv : a->dict) { words.push_back(kv.first); words.push_back(kv.second.s); }
+            for (const std::string& w : words) {  // "RFFT", or "fft_type RFFT" out of #stablehlo<fft_type RFFT>
+                const std::string last = w.substr(w.find_last_of(' ') == std::string::npos ? 0 : w.find_last_of(' ') + 1);
+                if (last == "FFT" || last == "IFFT" || last == "RFFT" || last == "IRFFT") kind = last;
+            }
+        }
+        if (kind.empty()) fail_compile("fft without an fft_type of FFT, IFFT, RFFT or IRFFT");
+        const std::vector<int64_t> len = op.int_list("fft_length");
+        if (len.empty() || len.size() > 3) fail_unsupported("fft over " + std::to_string(len.size()) + " axes");
+        int64_t points = 1, half_points = 1;
+        for (size_t k = 0; k < len.size(); ++k) {
+            if (len[k] < 1) fail_compile("fft_length entries must be positive");
+            points *= len[k];
+            half_points *= k + 1 == len.size() ? len[k] / 2 + 1 : len[k];
+        }
+        View in = materialize(get(op.operands[0]), "fft.operand");
+        const TensorType& it = in.type;
+        const TensorType& rt = op.result_types[0];
+        if ((it.dtype != DType::F32 && it.dtype != DType::F64) || rt.dtype != it.dtype) fail_unsupported("fft from " + it.str() + " to " + rt.str());
+        const bool real_in = kind == "RFFT", real_out = kind == "IRFFT";
+        const int64_t in_per = real_in ? points : 2 * (real_out ? half_points : points);
+        const int64_t out_per = real_out ? points : 2 * (real_in ? half_points : points);
+        if (it.count() % in_per != 0 || rt.count() != it.count() / in_per * out_per)
+            fail_compile("fft " + kind + " of length " + std::to_string(points) + ": " + it.str() + " -> " + rt.str() + " do not hold the same number of transforms");
+        const int64_t batch = it.count() / in_per;
+        View out = dense_view(new_arena(rt.bytes()), rt);
+        const int dt = static_cast<int>(it.dtype);
+        struct Pass { int kind; int from, to; int64_t outer, n, inner; };  // buffers: 0 operand, 1 result, 2 scratch
+        std::vector<Pass> passes;
+        const int r = static_cast<int>(len.size());
+        auto inner_of = [&](int axis, bool halved) {
+            int64_t m = 1;
+            for (int k = axis + 1; k < r; ++k) m *= (halved && k == r - 1) ? len[k] / 2 + 1 : len[k];
+            return m;
+        };
+        auto outer_of = [&](int axis) {
+            int64_t m = batch;
+            for (int k = 0; k < axis; ++k) m *= len[k];
+            return m;
+        };
+        bool scratch = false;
+        if (kind == "FFT" || kind == "IFFT") {
+            const int k = kind == "IFFT" ? 1 : 0;
+            for (int axis = r - 1; axis >= 0; --axis)
+                passes.push_back({k, axis == r - 1 ? 0 : 1, 1, outer_of(axis), len[axis], inner_of(axis, false)});
+        } else if (real_in) {
+            passes.push_back({2, 0, 1, outer_of(r - 1), len[r - 1], 1});
+            for (int axis = r - 2; axis >= 0; --axis) passes.push_back({0, 1, 1, outer_of(axis), len[axis], inner_of(axis, true)});
+        } else {
+            scratch = r > 1;
+            for (int axis = 0; axis < r - 1; ++axis) passes.push_back({1, axis == 0 ? 0 : 2, 2, outer_of(axis), len[axis], inner_of(axis, true)});
+            passes.push_back({3, scratch ? 2 : 0, 1, outer_of(r - 1), len[r - 1], 1});
+        }
+        View tmp;
+        if (scratch) tmp = dense_view(new_arena(it.bytes()), it);
+        DevView din = dev(in), dout = dev(out), dtmp;
+        keep_alive(in); keep_alive(out);
+        if (scratch) { dtmp = dev(tmp); keep_alive(tmp); }
+        add_step("fft." + kind, [=](const Ctx& c) {
+            const void* bufs[3] = {bind(din, c).base, bind(dout, c).base, scratch ? bind(dtmp, c).base : nullptr};
+            for (const Pass& p : passes) {
+                const int rc = mhlo_cuda_fft_axis(dt, p.kind, bufs[p.from], const_cast<void*>(bufs[p.to]), p.outer, p.n, p.inner, c.stream);
+                if (rc != 0) return rc;
+            }
+            return 0;
+        }, static_cast<int>(passes.size()));
         set(op.results[0], out);
     }
 

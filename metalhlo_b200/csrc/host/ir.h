@@ -35,6 +35,10 @@ bool dtype_from_name(const std::string& s, DType* out);
 struct TensorType {
     DType dtype = DType::F32;
     std::vector<int64_t> shape;
+    // Set by the parser on tensor<...xcomplex<f32|f64>>: the type is then already the float tensor with a trailing
+    // dimension of 2 (re, im) that stores it; the mark only tells the complex legalisation which operations to
+    // rewrite, is cleared by it and takes no part in comparisons.
+    bool was_complex = false;
     int rank() const { return static_cast<int>(shape.size()); }
     int64_t count() const {
         int64_t n = 1;
@@ -159,6 +163,9 @@ struct Module {
     Function& main();
 };
 
+// Rewrites every operation on complex values into operations on float tensors with a trailing (re, im) dimension
+// (complex.cpp); called by parse_module on each function.
+void legalize_complex(Function& f);
 // Parses StableHLO text (pretty and generic op forms) into a Module. Throws CompileError(3, ...).
 Module parse_module(const std::string& text);
 // Prints a function back as StableHLO text (used for METALHLO_DUMP_OPTIMIZED and by the tests).

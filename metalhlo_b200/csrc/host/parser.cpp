@@ -76,6 +76,7 @@ struct DensePending {
     std::vector<Lit> lits;
     std::string raw_hex;  // "0x..." byte string form
     bool nested = false;  // had brackets (not a splat)
+    bool pairs = false;   // elements written as (re, im)
 };
 
 class Parser {
@@ -309,7 +310,14 @@ class Parser {
             break;
         }
         std::string e = ident();
-        if (e == "complex") error("complex element types are not supported");
+        if (e == "complex") {  // stored as (re, im) pairs of the part type: one more dimension of extent 2
+            expect('<');
+            e = ident();
+            expect('>');
+            if (e != "f32" && e != "f64") error("complex<" + e + "> is not supported (complex<f32> and complex<f64> are)");
+            t.shape.push_back(2);
+            t.was_complex = true;
+        }
         if (!dtype_from_name(e, &t.dtype)) error("unsupported element type '" + e + "'");
         skip();
         if (cur() == ',') { ++p_; skip(); while (cur() != '>' && p_ < s_.size()) { if (cur() == '<') skip_balanced('<', '>'); else ++p_; } }  // encoding attr
@@ -380,7 +388,7 @@ class Parser {
             if (cur() == ']') { --depth; ++p_; continue; }
             if (cur() == ',') { ++p_; continue; }
             if (cur() == '>' && depth == 0) { ++p_; break; }
-            if (cur() == '(') error("complex constants are not supported");
+            if (cur() == '(' || cur() == ')') { ++p_; d.pairs = true; continue; }  // (re, im) of a complex element
             d.lits.push_back(number());
         }
         return d;
@@ -407,6 +415,12 @@ class Parser {
         if (d.lits.empty()) {
             if (n != 0) fail_parse("empty dense<> for non-empty type " + t.str());
             return a;
+        }
+        if (t.was_complex && d.lits.size() == 2 && n != 2 && !d.nested) {  // one (re, im) for every element
+            DensePending all;
+            all.nested = true;
+            for (int64_t k = 0; k < n / 2; ++k) { all.lits.push_back(d.lits[0]); all.lits.push_back(d.lits[1]); }
+            return finalize_dense(all, t);
         }
         const bool splat = d.lits.size() == 1 && (n != 1 || !d.nested);
         if (!splat && static_cast<int64_t>(d.lits.size()) != n)
@@ -1141,6 +1155,7 @@ class Parser {
             rename("dimensions", n == "broadcast_in_dim" ? "broadcast_dimensions" : (n == "transpose" ? "permutation" : "dimensions"));
         }
         if (n == "concatenate" || n == "get_dimension_size") { rename("dim", "dimension"); }
+        if (n == "fft") { rename("type", "fft_type"); rename("length", "fft_length"); }
         if (n == "iota" || n == "dynamic_iota") { rename("dim", "iota_dimension"); rename("dimension", "iota_dimension"); }
         if (n == "reduce") {
             rename("dims", "dimensions");
@@ -1336,7 +1351,9 @@ class Parser {
 
 Module parse_module(const std::string& text) {
     Parser p(text);
-    return p.parse();
+    Module m = p.parse();
+    for (Function& f : m.functions) legalize_complex(f);
+    return m;
 }
 
 const Function& Module::main() const {

@@ -33,6 +33,7 @@ INT_DTYPES = {"i1": np.bool_, "i8": np.int8, "i16": np.int16, "i32": np.int32, "
               "ui16": np.uint16, "ui32": np.uint32, "ui64": np.uint64, "si8": np.int8, "si16": np.int16,
               "si32": np.int32, "si64": np.int64}
 FLOAT_DTYPES = ("f16", "f32", "f64", "bf16")
+COMPLEX_DTYPES = ("complex<f32>", "complex<f64>")  # carried as complex128
 
 
 class Unsupported(Exception):
@@ -47,7 +48,13 @@ class TType:
     def is_float(self):
         return self.dtype in FLOAT_DTYPES
 
+    @property
+    def is_complex(self):
+        return self.dtype in COMPLEX_DTYPES
+
     def np_dtype(self):
+        if self.is_complex:
+            return np.complex128
         return np.float64 if self.is_float else INT_DTYPES[self.dtype]
 
     def __repr__(self):
@@ -56,6 +63,8 @@ class TType:
 
 def round_to(arr, dtype):
     """Rounds float64 values to the precision of a storage dtype (used when a convert asks for it)."""
+    if dtype in COMPLEX_DTYPES:
+        return arr.astype(np.complex64).astype(np.complex128) if dtype == "complex<f32>" else arr
     if dtype == "f32":
         return arr.astype(np.float32).astype(np.float64)
     if dtype == "f16":
@@ -194,13 +203,14 @@ class Scanner:
                 return TType((), w)
             raise Unsupported(f"type {w}")
         body = self.balanced("<", ">").split(",")[0].strip()
-        parts = body.split("x")
+        m = re.match(r"((?:(?:\d+|\?|\*)x)*)(.*)$", body)
+        parts = m.group(1).split("x")[:-1]
         if any(p in ("?", "*") for p in parts):
             raise Unsupported("dynamic shape")
-        dt = parts[-1]
-        if dt.startswith("complex") or (dt not in INT_DTYPES and dt not in FLOAT_DTYPES):
+        dt = m.group(2).strip()
+        if dt not in INT_DTYPES and dt not in FLOAT_DTYPES and dt not in COMPLEX_DTYPES:
             raise Unsupported(f"element type {dt}")
-        return TType([int(p) for p in parts[:-1]], dt)
+        return TType([int(p) for p in parts], dt)
 
     def ident_bang(self):
         self.p += 1
@@ -253,6 +263,14 @@ def dense_value(body, ttype):
         if arr.size == 1 and n != 1:
             arr = np.full(ttype.shape, arr[0])
         return arr.reshape(ttype.shape).astype(npdt)
+    if ttype.is_complex:
+        part = TType((), ttype.dtype[len("complex<"):-1])
+        nums = [parse_number(x, part) for x in
+                re.findall(r"[-+]?(?:0x[0-9a-fA-F]+|inf|nan|NaN|\d+\.?\d*(?:[eE][-+]?\d+)?|\.\d+(?:[eE][-+]?\d+)?)", body)]
+        vals = np.array(nums[0::2]) + 1j * np.array(nums[1::2])
+        if vals.size == 1 and (n != 1 or "[" not in body):
+            return np.full(ttype.shape, vals[0], dtype=np.complex128)
+        return vals.astype(np.complex128).reshape(ttype.shape)
     if "(" in body:
         raise Unsupported("complex constant")
     toks = re.findall(r"true|false|[-+]?(?:0x[0-9a-fA-F]+|inf|nan|NaN|\d+\.?\d*(?:[eE][-+]?\d+)?|\.\d+(?:[eE][-+]?\d+)?)", body)
@@ -771,6 +789,8 @@ def _wrap(arr, ttype):
     """Brings a numpy result to the carrier dtype of its declared type."""
     if ttype.is_float:
         return np.asarray(arr, dtype=np.float64)
+    if ttype.is_complex:
+        return np.asarray(arr, dtype=np.complex128)
     return np.asarray(arr).astype(ttype.np_dtype())
 
 
@@ -807,6 +827,11 @@ def _with_attrs(op, **extra):
     o.attrs = dict(op.attrs)
     o.attrs.update(extra)
     return o
+
+
+_COMPLEX_OPS = ("complex", "real", "imag", "abs", "add", "subtract", "multiply", "divide", "negate", "convert", "select", "fft", "exponential", "compare",
+                "reshape", "transpose", "broadcast_in_dim", "slice", "concatenate", "reverse", "constant", "call",
+                "optimization_barrier")
 
 
 class Interpreter:
@@ -1023,6 +1048,9 @@ class Interpreter:
             x = x.detach().cpu()
             x = x.double().numpy() if x.is_floating_point() else x.numpy()
         a = np.asarray(x)
+        if t.is_complex and not np.iscomplexobj(a):  # (re, im) pairs on a last axis of 2, as the C API carries them
+            assert a.shape == t.shape + (2,), (a.shape, t)
+            a = a[..., 0].astype(np.float64) + 1j * a[..., 1].astype(np.float64)
         a = a.astype(np.float64) if t.is_float else a.astype(t.np_dtype())
         assert a.shape == t.shape, (a.shape, t)
         return a
@@ -1038,7 +1066,7 @@ class Interpreter:
                 outs = [outs]
             for name, t, v in zip(op.results, op.types, outs):
                 v = _wrap(v, t)
-                if self.round_floats and t.is_float:
+                if self.round_floats and (t.is_float or t.is_complex):
                     v = round_to(v, t.dtype)
                 env[name] = v.reshape(t.shape)
         return []
@@ -1047,6 +1075,15 @@ class Interpreter:
         n, t = op.name, (op.types[0] if op.types else None)
         A = op.attrs
         it = op.in_types
+        if n not in _COMPLEX_OPS and (any(np.iscomplexobj(x) for x in a) or (t is not None and t.is_complex)):
+            # the backend's surface for complex values (csrc/host/complex.cpp); everything else is out of scope for both
+            raise Unsupported(f"{n} on complex values")
+        if n == "convert" and a and np.iscomplexobj(a[0]) and not t.is_complex:
+            a = [np.real(a[0])]  # the imaginary part is dropped
+        if n == "compare" and a and np.iscomplexobj(a[0]):
+            d = op.attrs.get("comparison_direction") or next((k for k in op.attrs.get("_kw", []) if k in _DIRS), None)
+            if d not in ("EQ", "NE"):
+                raise Unsupported("compare of complex values in a direction other than EQ and NE")
         if n == "while":
             return self.op_while(op, a, t, env)
         if n in ("if", "case"):
@@ -1088,7 +1125,7 @@ class Interpreter:
             if n == "multiply":
                 return np.logical_and(a[0], a[1]) if a[0].dtype == np.bool_ else a[0] * a[1]
             if n == "divide":
-                if t.is_float:
+                if t.is_float or t.is_complex:
                     return a[0] / a[1]
                 q = np.where(a[1] == 0, 1, a[1])
                 r = np.trunc(a[0].astype(np.float64) / q.astype(np.float64)) if a[0].dtype.itemsize < 8 else (np.abs(a[0]) // np.abs(q)) * np.sign(a[0]) * np.sign(q)
@@ -1217,9 +1254,49 @@ class Interpreter:
         shape[d] = t.shape[d]
         return np.broadcast_to(np.arange(t.shape[d]).reshape(shape), t.shape)
 
+    def op_complex(self, op, a, t):
+        return a[0] + 1j * a[1]
+
+    def op_real(self, op, a, t):
+        return np.real(a[0])
+
+    def op_imag(self, op, a, t):
+        return np.imag(a[0])
+
+    def op_fft(self, op, a, t):
+        """stablehlo.fft over the last len(fft_length) axes. Complex tensors may also be given as float tensors of
+        interleaved (re, im) pairs, the form of the reference's kernels (Compiler/CodeGenerator.swift:2701-2830)."""
+        A = op.attrs
+        words = " ".join(str(A.get(k, "")) for k in ("fft_type", "type")) + " " + " ".join(map(str, A.get("_kw", [])))
+        kind = next(k for k in ("IRFFT", "RFFT", "IFFT", "FFT") if re.search(r"\b" + k + r"\b", words))
+        lens = _ints(A.get("fft_length", A.get("length")))
+        axes = tuple(range(-len(lens), 0))
+        x = a[0]
+
+        def as_complex(arr, tail):
+            if np.iscomplexobj(arr):
+                return arr
+            flat = arr.reshape(-1, 2)
+            return (flat[:, 0] + 1j * flat[:, 1]).reshape((-1,) + tuple(tail))
+
+        half = lens[:-1] + [lens[-1] // 2 + 1]
+        if kind == "FFT":
+            z = np.fft.fftn(as_complex(x, lens), axes=axes)
+        elif kind == "IFFT":
+            z = np.fft.ifftn(as_complex(x, lens), axes=axes)
+        elif kind == "RFFT":
+            z = np.fft.rfftn(np.asarray(x, dtype=np.float64).reshape((-1,) + tuple(lens)), s=lens, axes=axes)
+        else:
+            z = np.fft.irfftn(as_complex(x, half), s=lens, axes=axes)
+        if t.is_complex or kind == "IRFFT":
+            return z.reshape(t.shape)
+        return np.stack([z.real, z.imag], axis=-1).reshape(t.shape)
+
     def op_convert(self, op, a, t):
         src = op.in_types[0] if op.in_types else None
         x = a[0]
+        if t.is_complex:
+            return round_to(np.asarray(x).astype(np.complex128), t.dtype)
         if t.is_float:
             return round_to(x.astype(np.float64), t.dtype)  # a convert is a real rounding point
         if x.dtype == np.float64:
@@ -1674,4 +1751,6 @@ def evaluate(text, inputs, function: str | None = None, round_floats: bool = Fal
     """Runs @main (or `function`) of a StableHLO module on numpy inputs; returns a list of arrays (floats in fp64)."""
     funcs = parse(text)
     f = next((g for g in funcs if g.name == (function or "main")), funcs[0])
-    return Interpreter(round_floats, funcs).run(f, inputs)
+    outs = Interpreter(round_floats, funcs).run(f, inputs)
+    # complex results leave as (re, im) pairs on a new last axis, the form they cross the C API in
+    return [np.stack([o.real, o.imag], axis=-1) if np.iscomplexobj(o) else o for o in outs]

@@ -29,7 +29,9 @@ FILES = ["abs", "add", "and", "atan2", "broadcast_in_dim", "cbrt", "ceil", "clam
          # control flow and the operators either side of the fused path
          "bitcast_convert", "call", "case", "if", "while", "dynamic_broadcast_in_dim", "dynamic_gather", "dynamic_iota",
          "dynamic_pad", "dynamic_reshape", "optimization_barrier", "reduce_window", "scatter", "sort", "convolution", "select_and_scatter", "map",
-         "get_dimension_size", "reduce_precision", "composite"]
+         "get_dimension_size", "reduce_precision", "composite",
+         # complex values: (re, im) float pairs behind the parser
+         "complex", "real", "imag"]
 
 
 class Case:
@@ -41,8 +43,8 @@ class Case:
         return f"{self.file}:{self.name}"
 
 
-_CHECK = re.compile(r"check\.(expect_eq_const|expect_almost_eq_const|expect_eq|expect_almost_eq|expect_close)\s+(.*?)\s*:\s*(tensor<[^>]*>)"
-                    r"(?:\s*,\s*tensor<[^>]*>)?", re.S)
+_CHECK = re.compile(r"check\.(expect_eq_const|expect_almost_eq_const|expect_eq|expect_almost_eq|expect_close)\s+(.*?)\s*:\s*(tensor<(?:[^<>]|<[^<>]*>)*>)"
+                    r"(?:\s*,\s*tensor<(?:[^<>]|<[^<>]*>)*>)?", re.S)
 
 
 def _split_dense(rest):
@@ -146,7 +148,7 @@ def all_cases():
     return cases_from_checkout() or cases_from_fixture()
 
 
-UNSUPPORTED_MARKERS = ("complex<", "f8E", "f4E", "f6E", "i2>", "i4>", "ui2>", "ui4>", "tf32", "quant", "x?x", "<?x", "token")
+UNSUPPORTED_MARKERS = ("f8E", "f4E", "f6E", "i2>", "i4>", "ui2>", "ui4>", "tf32", "quant", "x?x", "<?x", "token")
 
 
 def skip_reason(text):
@@ -169,6 +171,14 @@ def verify(case, outs):
         got = np.asarray(outs[chk["value"]])
         t = interp.Scanner(chk["type"]).type()
         want = interp.dense_value(chk["dense"], t) if "dense" in chk else np.asarray(outs[chk["other"]])
+        if t.is_complex:  # results leave as (re, im) pairs on a last axis
+            want = np.asarray(want, dtype=np.complex128)
+            want = np.stack([want.real, want.imag], axis=-1)
+            if np.iscomplexobj(got):
+                got = np.stack([got.real, got.imag], axis=-1)
+            tol = 1e-6 if chk["kind"].startswith("expect_eq") else 1e-4
+            np.testing.assert_allclose(got.astype(np.float64), want, rtol=tol, atol=tol, equal_nan=True, err_msg=case.id)
+            continue
         if t.is_float:
             tol = 0 if chk["kind"].startswith("expect_eq") else 1e-4
             got = got.astype(np.float64)

@@ -1128,4 +1128,83 @@ def rng_cases():
     return out
 
 
-CASES = build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
+def ct(shape, part="f32"):
+    return "tensor<" + "x".join([str(d) for d in shape] + [f"complex<{part}>"]) + ">"
+
+
+def fft_cases():
+    """stablehlo.fft (all four kinds, one to three axes, lengths on and off the powers of two, f32 and f64 parts) and the
+    operations on complex values that surround it in a jax.numpy.fft program. Complex arguments and results of @main are
+    float arrays with a last axis of (re, im)."""
+    rng = np.random.default_rng(1807)
+    out = []
+
+    def parts(z, shape, part):  # spectrum -> (re, im, abs) as real results
+        t, c = tt(shape, part), ct(shape, part)
+        return (f"    %re = stablehlo.real {z} : ({c}) -> {t}\n    %im = stablehlo.imag {z} : ({c}) -> {t}\n"
+                f"    %ab = stablehlo.abs {z} : ({c}) -> {t}"), "%re, %im, %ab", [t, t, t]
+
+    # real input -> half spectrum, one axis
+    for part, cases in (("f32", ((4, 64), (3, 100), (2, 1), (5, 7), (1, 4096), (2, 8192), (2, 3000))), ("f64", ((3, 32), (2, 45)))):
+        for shape in cases:
+            n = shape[-1]
+            hs = shape[:-1] + (n // 2 + 1,)
+            body, res, rts = parts("%0", hs, part)
+            text = func([tt(shape, part)], rts, f"    %0 = stablehlo.fft %arg0, type = RFFT, length = [{n}] : ({tt(shape, part)}) -> {ct(hs, part)}\n" + body, res)
+            out.append((f"fft_rfft_{part}_{n}", text, [rand(rng, shape, part)]))
+    # complex -> complex, forward and back, built from two real arguments
+    for kind in ("FFT", "IFFT"):
+        for shape, lens in (((3, 128), [128]), ((2, 8, 16), [8, 16]), ((2, 4, 6, 8), [4, 6, 8]), ((3, 5, 12), [12]), ((2, 9, 10), [9, 10])):
+            t, c = tt(shape, "f32"), ct(shape)
+            body, res, rts = parts("%1", shape, "f32")
+            text = func([t, t], rts, f"    %0 = stablehlo.complex %arg0, %arg1 : {c}\n"
+                                     f"    %1 = stablehlo.fft %0, type = {kind}, length = {lens} : ({c}) -> {c}\n" + body, res)
+            out.append((f"fft_{kind.lower()}_{'x'.join(map(str, lens))}", text, [rand(rng, shape, "f32"), rand(rng, shape, "f32")]))
+    # real -> half spectrum -> real over two and three axes; the spectrum crosses the boundary as (re, im) pairs
+    for shape, lens in (((2, 12, 10), [12, 10]), ((3, 8, 32), [8, 32]), ((2, 3, 4, 9), [3, 4, 9]), ((4, 16), [16]), ((4, 15), [15])):
+        hs = shape[:-1] + (shape[-1] // 2 + 1,)
+        t, c = tt(shape, "f32"), ct(hs)
+        text = func([t], [c, t], f"    %0 = stablehlo.fft %arg0, type = RFFT, length = {lens} : ({t}) -> {c}\n"
+                                 f"    %1 = stablehlo.fft %0, type = IRFFT, length = {lens} : ({c}) -> {t}", "%0, %1")
+        out.append((f"fft_rfft_irfft_{'x'.join(map(str, lens))}", text, [rand(rng, shape, "f32")]))
+    # a complex argument (pairs) through the generic form of the operation
+    shape = (5, 16)
+    c = ct(shape)
+    text = func([c], [c], f'    %0 = "stablehlo.fft"(%arg0) {{fft_type = #stablehlo<fft_type FFT>, fft_length = array<i64: 16>}} : ({c}) -> {c}', "%0")
+    out.append(("fft_generic_form_complex_argument", text, [rand(rng, shape + (2,), "f32")]))
+    # the reference's form: no complex types, the pairs are float elements (Compiler/CodeGenerator.swift:2701-2830)
+    tp, th, tr = tt((4, 16, 2), "f32"), tt((4, 9, 2), "f32"), tt((4, 16), "f32")
+    out.append(("fft_float_pairs_fft", func([tp], [tp], f"    %0 = stablehlo.fft %arg0, type = FFT, length = [16] : ({tp}) -> {tp}", "%0"),
+                [rand(rng, (4, 16, 2), "f32")]))
+    out.append(("fft_float_pairs_rfft_irfft", func([tr], [th, tr], f"    %0 = stablehlo.fft %arg0, type = RFFT, length = [16] : ({tr}) -> {th}\n"
+                                                                   f"    %1 = stablehlo.fft %0, type = IRFFT, length = [16] : ({th}) -> {tr}", "%0, %1"),
+                [rand(rng, (4, 16), "f32")]))
+    # arithmetic and data movement on complex values
+    shape = (3, 8)
+    t, c = tt(shape, "f32"), ct(shape)
+    a, b = rand(rng, shape + (2,), "f32"), rand(rng, shape + (2,), "f32", 0.5, 2.0)
+    for name in ("add", "subtract", "multiply", "divide"):
+        out.append((f"complex_{name}", func([c, c], [c], f"    %0 = stablehlo.{name} %arg0, %arg1 : {c}", "%0"), [a, b]))
+    out.append(("complex_negate", func([c], [c], f"    %0 = stablehlo.negate %arg0 : {c}", "%0"), [a]))
+    body = (f"    %k = stablehlo.constant dense<(0.5, -2.0)> : {c}\n"
+            f"    %l = stablehlo.constant dense<[(1.0, 0.0), (0.0, 1.0), (-1.0, 0.0), (0.0, -1.0), (2.0, 2.0), (0.5, 0.25), (3.0, -1.0), (0.0, 0.0)]> : {ct((8,))}\n"
+            f"    %lb = stablehlo.broadcast_in_dim %l, dims = [1] : ({ct((8,))}) -> {c}\n"
+            f"    %0 = stablehlo.multiply %arg0, %k : {c}\n"
+            f"    %1 = stablehlo.add %0, %lb : {c}")
+    out.append(("complex_constants_and_broadcast", func([c], [c], body, "%1"), [a]))
+    tc8 = ct((8, 3))
+    body = (f"    %0 = stablehlo.transpose %arg0, dims = [1, 0] : ({c}) -> {tc8}\n"
+            f"    %1 = stablehlo.slice %0 [2:7:2, 0:3] : ({tc8}) -> {ct((3, 3))}\n"
+            f"    %2 = stablehlo.reverse %1, dims = [0] : {ct((3, 3))}\n"
+            f"    %3 = stablehlo.concatenate %1, %2, dim = 1 : ({ct((3, 3))}, {ct((3, 3))}) -> {ct((3, 6))}\n"
+            f"    %4 = stablehlo.reshape %3 : ({ct((3, 6))}) -> {ct((2, 9))}")
+    out.append(("complex_data_movement", func([c], [ct((2, 9))], body, "%4"), [a]))
+    ti = tt(shape, "i1")
+    body = (f"    %0 = stablehlo.convert %arg1 : ({t}) -> {c}\n"
+            f"    %1 = stablehlo.select %arg2, %arg0, %0 : {ti}, {c}")
+    out.append(("complex_convert_and_select", func([c, t, ti], [c], body, "%1"), [a, rand(rng, shape, "f32"), rand(rng, shape, "i1")]))
+    return out
+
+
+CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
+         + fft_cases())

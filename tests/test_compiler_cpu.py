@@ -197,3 +197,29 @@ def test_position_table_added_before_the_first_norm_is_read_by_the_norm_kernel()
     for dt in ("f32", "f16", "bf16"):
         for name in (f"pattern_residual_table_layer_norm_side0_{dt}", f"pattern_residual_table_layer_norm_side1_{dt}", f"pattern_residual_table_rms_norm_{dt}"):
             assert capi.plan_text(BY_NAME[name][1], 3)[0][0].endswith("[repeated addend]")
+
+
+def test_complex_values_become_float_pairs_behind_the_parser():
+    """tensor<..xcomplex<f32>> is read as tensor<..x2xf32>; the operations on it are rewritten so that no later stage sees
+    a complex type. The reference's element-type enum has none either (Sources/CMetalHLO/include/metalhlo.h:61-75) and
+    its FFT kernels take (re, im) float pairs (Compiler/CodeGenerator.swift:2701-2830)."""
+    _, text, _ = BY_NAME["fft_fft_8x16"]
+    flat = capi.optimize_text(text, 0)
+    assert "complex" not in flat and "tensor<2x8x16x2xf32>" in flat
+    assert live_ops(flat).count("fft") == 1 and "concatenate" in live_ops(flat)
+    steps, launches, _ = capi.plan_text(text, 3)
+    assert "fft.FFT" in steps and launches >= 2  # one launch per transformed axis
+    _, text, _ = BY_NAME["fft_rfft_irfft_3x4x9"]
+    steps, launches, _ = capi.plan_text(text, 3)
+    assert steps == ["fft.RFFT", "fft.IRFFT"] and launches == 6
+    c = "tensor<4xcomplex<f32>>"
+    with pytest.raises(capi.MetalHLOError) as e:
+        capi.optimize_text(f"func.func @main(%a: {c}) -> {c} {{ %0 = stablehlo.tanh %a : {c}\n return %0 : {c} }}", 0)
+    assert e.value.status == 4 and "complex" in str(e.value)
+    with pytest.raises(capi.MetalHLOError) as e:
+        capi.optimize_text("func.func @main(%a: tensor<4xcomplex<i32>>) -> tensor<4xcomplex<i32>> { return %a : tensor<4xcomplex<i32>> }", 0)
+    assert e.value.status == 3
+    with pytest.raises(capi.MetalHLOError) as e:
+        capi.plan_text("func.func @main(%a: tensor<4x6xf32>) -> tensor<4x5xcomplex<f32>> { %0 = stablehlo.fft %a, type = RFFT, length = [6] : "
+                       "(tensor<4x6xf32>) -> tensor<4x5xcomplex<f32>>\n return %0 : tensor<4x5xcomplex<f32>> }", 0)
+    assert e.value.status == 5 and "transforms" in str(e.value)
