@@ -76,6 +76,15 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ uint32_t scale16x2(uint32_t v, float a, bool bf16) {
+    if (bf16) {
+        __nv_bfloat162 h = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v), __float2bfloat162_rn(a));
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    __half2 h = __hmul2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(a));
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (the probabilities) is read from tensor memory.
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -94,9 +103,11 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
 // largest f16 / bf16 value; otherwise nothing is written, *stored is false and the caller redoes the block with its
 // true maximum (the scores are still intact).
 constexpr float kCarryLimit = 32768.f;
+// p_taddr: where the packed probabilities go (s_taddr itself when they overwrite the scores). s_read: when not null, the
+// barrier this warp arrives on once its last score has left tensor memory (the next block's scores may then replace them).
 template <bool kMask, bool kCheck>
 __device__ __forceinline__ float softmax_exp(uint32_t s_taddr, float scale_log2, float m_use, int key0, int last_visible, bool is_bf16,
-                                             bool* stored) {
+                                             bool* stored, uint32_t p_taddr, uint64_t* s_read = nullptr) {
     const float2 c2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
     float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     uint32_t packed[kBlockN / 64][32];
@@ -106,6 +117,11 @@ __device__ __forceinline__ float softmax_exp(uint32_t s_taddr, float scale_log2,
         tmem_ld32(s_taddr + ci * 64, sr);
         tmem_ld32(s_taddr + ci * 64 + 32, sr + 32);
         tmem_ld_wait();
+        if (!kCheck && ci == kBlockN / 64 - 1 && s_read != nullptr) {
+            tc_fence_before();
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(s_read);
+        }
         if (kMask) {
 #pragma unroll
             for (int c = 0; c < 64; ++c)
@@ -118,14 +134,14 @@ __device__ __forceinline__ float softmax_exp(uint32_t s_taddr, float scale_log2,
             rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
             packed[ci][c / 2] = pack16(e.x, e.y, is_bf16);
         }
-        if (!kCheck) tmem_st32(s_taddr + ci * 32, packed[ci]);  // those score columns have been consumed already
+        if (!kCheck) tmem_st32(p_taddr + ci * 32, packed[ci]);  // in place: those score columns have been consumed already
     }
     const float rs = (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
     if (kCheck) {
         const bool safe = !__any_sync(0xffffffffu, !(rs < kCarryLimit));
         if (safe) {
 #pragma unroll
-            for (int ci = 0; ci < kBlockN / 64; ++ci) tmem_st32(s_taddr + ci * 32, packed[ci]);
+            for (int ci = 0; ci < kBlockN / 64; ++ci) tmem_st32(p_taddr + ci * 32, packed[ci]);
         }
         *stored = safe;
     }
@@ -198,6 +214,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr int kPanels = D / 64;       // 64-element (128-byte) panels along the head dimension
     constexpr uint32_t kTmemCols = 512;   // S_h: 128 columns per half (P overwrites them in place), O_h: D columns per half
     constexpr uint32_t kSCol = 0, kOCol = kHalves * kBlockN;
+    // At head dim 64 the 512 columns also hold the probabilities beside the scores (64 packed columns per half). The
+    // scores of key block j + 1 are then issued as soon as the softmax warps have read those of block j out of tensor
+    // memory, instead of after P.V of block j: Q.K^T and P.V run under the exponentials and the softmax warps go from
+    // one block to the next without waiting for the tensor pipe. At head dim 128 there is no room: P overwrites S.
+    constexpr bool kEarly = kHalves * (kBlockN + D + kBlockN / 2) <= 512;
+    constexpr uint32_t kPCol = kEarly ? kOCol + kHalves * D : kSCol;
+    constexpr uint32_t kPStride = kEarly ? kBlockN / 2 : kBlockN;  // columns between the two halves' probabilities
     constexpr int kQHalfBytes = kBlockM * D * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -211,7 +234,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* s_full = v_empty + kKvStages;  // per half: scores of the current key block are in TMEM
     uint64_t* p_full = s_full + kHalves;     // per half: probabilities written (and O rescaled if needed)
     uint64_t* pv_done = p_full + kHalves;    // per half: every PV product issued so far has completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kHalves);
+    uint64_t* s_free = pv_done + kHalves;    // per half (kEarly): the softmax warps have read the scores out of TMEM
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + kHalves);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -222,7 +246,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         for (int h = 0; h < kHalves; ++h) {
             mbar_init(&q_full[h], 1); mbar_init(&q_empty[h], 1);
-            mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1);
+            mbar_init(&s_full[h], 1); mbar_init(&p_full[h], 4); mbar_init(&pv_done[h], 1); mbar_init(&s_free[h], 4);
         }
         fence_barrier_init();
     }
@@ -293,7 +317,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int kk = 0; kk < kBlockN / 16; ++kk) {
                 // 16 keys of P = 8 packed 32-bit columns; 16 keys of V = 16 rows of 128 bytes in every head-dim panel
                 const uint64_t db = make_smem_desc(va + kk * 16 * 128, kBlockN * 128, 1024);
-                if (elect_one()) umma_f16_ts(tmem_base + kOCol + h * D, tmem_base + kSCol + h * kBlockN + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+                if (elect_one()) umma_f16_ts(tmem_base + kOCol + h * D, tmem_base + kPCol + h * kPStride + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
             }
             if (elect_one()) umma_commit(&pv_done[h]);
             __syncwarp();
@@ -307,6 +331,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int stage = 0;
         uint32_t phase = 0, qn = 0;   // qn: tiles so far
         uint32_t it_h[kHalves] = {0, 0};  // key blocks each half has gone through (parity of its per-block barriers)
+        uint32_t s_count[kHalves] = {1, 1};  // S products issued per half, the first tile's first ones included (kEarly)
         bool ok = true;
         if (has_cur) {
             // first scores of the first tile
@@ -332,6 +357,41 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const bool last = j + 1 == cur.nblk;
                 const bool more = !last || has_nxt;
                 if (!mbar_wait(&v_full[stage], phase)) { ok = false; atomicExch(&g_attn_error, 7); break; }
+                if constexpr (kEarly) {
+                    // Tensor-pipe order per key block j: S_0(next), S_1(next), PV_0(j), PV_1(j). S_h(next) goes out when
+                    // half h has read its scores of block j (s_free, about half way through its exponentials), PV_h(j)
+                    // when it has written the probabilities: both S products are under way before either half finishes.
+                    if (more) {
+                        for (int h = 0; h < kHalves && ok; ++h) {
+                            const int nb = h == 0 ? cur.nblk0 : cur.nblk;
+                            if (last && !mbar_wait(&q_full[h], (qn + 1) & 1)) { ok = false; atomicExch(&g_attn_error, 12); break; }
+                            if (h == 0 && !mbar_wait(&k_full[nstage], nphase)) { ok = false; atomicExch(&g_attn_error, 6); break; }
+                            if (last || j + 1 < nb) {
+                                // one s_free arrival per S issued: the one before this one has been read
+                                if (!mbar_wait(&s_free[h], (s_count[h] - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 13); break; }
+                                tc_fence_after();
+                                issue_s(h, nstage);
+                                ++s_count[h];
+                                const int nb_of_s = last ? (h == 0 ? nxt.nblk0 : nxt.nblk) : nb;
+                                if (last ? nb_of_s == 1 : j + 2 == nb_of_s) commit_to(&q_empty[h]);
+                            }
+                            if (h == kHalves - 1) commit_to(&k_empty[nstage]);
+                        }
+                    }
+                    for (int h = 0; h < kHalves && ok; ++h) {
+                        const int nb = h == 0 ? cur.nblk0 : cur.nblk;
+                        if (j < nb) {
+                            if (!mbar_wait(&p_full[h], it_h[h] & 1)) { ok = false; atomicExch(&g_attn_error, 5); break; }
+                            tc_fence_after();
+                            issue_pv(h, stage, j > 0);
+                            ++it_h[h];
+                        }
+                        if (h == kHalves - 1) commit_to(&v_empty[stage]);
+                    }
+                    stage = nstage;
+                    phase = nphase;
+                    continue;
+                }
                 for (int h = 0; h < kHalves && ok; ++h) {
                     const int nb = h == 0 ? cur.nblk0 : cur.nblk;  // blocks this half takes part in
                     if (j < nb) {
@@ -370,6 +430,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t s_taddr = tmem_base + lane_base + kSCol + h * kBlockN;
         const uint32_t o_taddr = tmem_base + lane_base + kOCol + h * D;
+        const uint32_t p_taddr = tmem_base + lane_base + kPCol + h * kPStride;
         Tile t;
         uint32_t it = 0;  // key blocks so far on this CTA (parity of the per-block barriers)
         bool ok = true;
@@ -388,13 +449,99 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // ---- after a tile's first block: one pass, exponentials against the reference maximum carried over from
                 // the earlier blocks; it fails (rarely) when a row's scores have grown by more than 2^15
                 bool done = false;
-                if (j > 0) {
+                if constexpr (kEarly) {
+                    // One pass in two chunks of 64 keys, first blocks included (their reference maximum starts at -inf
+                    // and moves to the first chunk's own). After the second chunk's loads the scores are out of tensor
+                    // memory and the next block's may replace them. Each chunk looks at its own maximum first: when that
+                    // would push an exponential past 2^threshold (the first chunk of a tile; rare afterwards), the
+                    // reference maximum moves there and what has been accumulated so far - l, O, the block's first
+                    // chunk of probabilities - is scaled down.
+                    const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+                    float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                    bool pv_waited = it == 0;  // P.V of the block before this one: it reads P and writes O
+#pragma unroll 1
+                    for (int ci = 0; ci < kBlockN / 64; ++ci) {
+                        uint32_t sr[64];
+                        tmem_ld32(s_taddr + ci * 64, sr);
+                        tmem_ld32(s_taddr + ci * 64 + 32, sr + 32);
+                        tmem_ld_wait();
+                        if (ci == kBlockN / 64 - 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&s_free[h]);
+                        }
+                        if (mask_block) {
+#pragma unroll
+                            for (int c = 0; c < 64; ++c)
+                                if (key0 + ci * 64 + c > last_visible) sr[c] = 0xff800000u;  // -inf
+                        }
+                        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                        for (int c = 0; c < 64; c += 4) {
+                            mx0 = fmax3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+                            mx1 = fmax3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+                        }
+                        const float mx = fmaxf(mx0, mx1) * p.scale_log2;
+                        const bool grow = mx > m_ref + kRescaleThreshold;
+                        if (__any_sync(0xffffffffu, grow)) {
+                            float alpha = 1.f;
+                            if (grow) {
+                                alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
+                                m_ref = mx;
+                                l *= alpha;
+                            }
+                            rs2[0].x *= alpha; rs2[0].y *= alpha; rs2[1].x *= alpha; rs2[1].y *= alpha;
+                            if (j > 0 || ci > 0) {
+                                if (!pv_waited) {
+                                    if (!mbar_wait(&pv_done[h], (it - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 14); }
+                                    tc_fence_after();
+                                    pv_waited = true;
+                                }
+                                // O of the earlier blocks (j > 0), then the probabilities of this block's first chunk (ci > 0)
+#pragma unroll 1
+                                for (int c0 = j > 0 ? 0 : D; c0 < D + (ci > 0 ? 32 : 0); c0 += 32) {
+                                    const uint32_t at = c0 < D ? o_taddr + c0 : p_taddr;
+                                    uint32_t row[32];
+                                    if (c0 >= D) tmem_st_wait();  // this thread's own store of that chunk
+                                    tmem_ld32(at, row);
+                                    tmem_ld_wait();
+                                    if (c0 < D) {
+#pragma unroll
+                                        for (int c = 0; c < 32; ++c) row[c] = __float_as_uint(__uint_as_float(row[c]) * alpha);
+                                    } else {
+#pragma unroll
+                                        for (int c = 0; c < 32; ++c) row[c] = scale16x2(row[c], alpha, p.is_bf16 != 0);
+                                    }
+                                    tmem_st32(at, row);
+                                }
+                            }
+                        }
+                        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                        const float2 nm2 = make_float2(-m_use, -m_use);
+                        uint32_t packed[32];
+#pragma unroll
+                        for (int c = 0; c < 64; c += 2) {
+                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), c2, nm2);
+                            const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                            rs2[(c >> 1) & 1] = __fadd2_rn(rs2[(c >> 1) & 1], e);
+                            packed[c / 2] = pack16(e.x, e.y, p.is_bf16 != 0);
+                        }
+                        if (!pv_waited) {  // the probabilities of the block before this one have been read by its P.V
+                            if (!mbar_wait(&pv_done[h], (it - 1) & 1)) { ok = false; atomicExch(&g_attn_error, 15); }
+                            tc_fence_after();
+                            pv_waited = true;
+                        }
+                        tmem_st32(p_taddr + ci * 32, packed);
+                    }
+                    l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
+                    done = true;
+                } else if (j > 0) {
                     const float m_carry = m_ref == -INFINITY ? 0.f : m_ref;
-                    const float rs = mask_block ? softmax_exp<true, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done)
-                                                : softmax_exp<false, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done);
+                    const float rs = mask_block ? softmax_exp<true, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done, p_taddr)
+                                                : softmax_exp<false, true>(s_taddr, p.scale_log2, m_carry, key0, last_visible, p.is_bf16 != 0, &done, p_taddr);
                     if (done) l += rs;
                 }
-                if (!done) {
+                if (!kEarly && !done) {
                     // ---- pass 1: row maximum of the raw scores (scale > 0, so scaling commutes with max) ----
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -437,8 +584,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     // ---- pass 2: p = 2^(s * scale*log2e - m), packed to 16 bit and written over the scores ----
                     const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                    l += mask_block ? softmax_exp<true, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr)
-                                    : softmax_exp<false, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr);
+                    uint64_t* s_read = kEarly ? &s_free[h] : nullptr;
+                    l += mask_block ? softmax_exp<true, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr, p_taddr, s_read)
+                                    : softmax_exp<false, false>(s_taddr, p.scale_log2, m_use, key0, last_visible, p.is_bf16 != 0, nullptr, p_taddr, s_read);
                 }
                 tmem_st_wait();
                 tc_fence_before();
