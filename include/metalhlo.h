@@ -211,6 +211,13 @@ char* mhlo_b200_executable_steps(MHLOExecutableRef executable);
 /* Device address of a buffer's storage (dense row-major). */
 void* mhlo_b200_buffer_device_pointer(MHLOBufferRef buffer);
 
+/* Complex tensors. MHLOElementType has no complex entry (Sources/CMetalHLO/include/metalhlo.h:61-75): a parameter or
+ * result typed tensor<..xcomplex<f32|f64>> in the program is a float buffer of (re, im) pairs with one more dimension of
+ * extent 2, and that is the shape and type the functions above report for it. These two tell a host with a complex buffer
+ * type of its own (PJRT's C64 / C128) which ones they are: 1 complex, 0 not, -1 index out of range. */
+int32_t mhlo_b200_executable_input_is_complex(MHLOExecutableRef executable, int32_t index);
+int32_t mhlo_b200_executable_output_is_complex(MHLOExecutableRef executable, int32_t index);
+
 /*
  * mhlo_buffer_to_host without the wait: the copy is queued on the client's transfer stream behind everything already
  * queued on its compute stream, and done(user) runs on a driver thread when the bytes are in out_data (pinned memory for

@@ -422,6 +422,20 @@ MHLOStatusCode mhlo_executable_output_type(MHLOExecutableRef executable, int32_t
     return describe(h->exe->output_type(index), out_shape, out_rank, out_element_type);
 }
 
+// 1 when input / output `index` was a complex tensor in the program text: its buffer is then the float tensor of
+// (re, im) pairs, one dimension longer, that mhlo_executable_{input,output}_type reports. 0 otherwise, -1 for a bad index.
+int32_t mhlo_b200_executable_input_is_complex(MHLOExecutableRef executable, int32_t index) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h || index < 0 || index >= h->exe->num_inputs()) return -1;
+    return h->exe->input_type(index).was_complex ? 1 : 0;
+}
+
+int32_t mhlo_b200_executable_output_is_complex(MHLOExecutableRef executable, int32_t index) {
+    ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
+    if (!h || index < 0 || index >= h->exe->num_outputs()) return -1;
+    return h->exe->output_type(index).was_complex ? 1 : 0;
+}
+
 MHLOStatusCode mhlo_executable_get_stats(MHLOExecutableRef executable, MHLOExecutionStats* out_stats) {
     ExecutableHandle* h = static_cast<ExecutableHandle*>(executable);
     if (!h) return static_cast<MHLOStatusCode>(set_error(MHLO_ERROR_INVALID_ARGUMENT, "executable is null"));

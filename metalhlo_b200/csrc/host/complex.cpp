@@ -230,6 +230,10 @@ void legalize_complex(Function& f) {
             for (TensorType& t : rw.out.back().result_types) t.was_complex = false;
     }
     f.ops.swap(rw.out);
+    f.arg_complex.clear();
+    f.result_complex.clear();
+    for (int a : f.args) f.arg_complex.push_back(f.values[a].type.was_complex);
+    for (const TensorType& t : f.result_types) f.result_complex.push_back(t.was_complex);
     for (Value& v : f.values) v.type.was_complex = false;
     for (TensorType& t : f.result_types) t.was_complex = false;
     for (Op& o : f.ops)

@@ -280,6 +280,7 @@ class Lowering {
             b.bytes = f_.type_of(f_.args[i]).bytes();
             set(f_.args[i], dense_view(add_buffer(b), f_.type_of(f_.args[i])));
             exe_->input_types_.push_back(f_.type_of(f_.args[i]));
+            exe_->input_types_.back().was_complex = i < f_.arg_complex.size() && f_.arg_complex[i];
         }
         open_parameter_converts();
         for (const Op& op : f_.ops) {
@@ -2083,6 +2084,7 @@ void Lowering::lower_return(const Op& op) {
     for (size_t i = 0; i < op.operands.size(); ++i) {
         const View& v = get(op.operands[i]);
         exe_->output_types_.push_back(v.type);
+        exe_->output_types_.back().was_complex = i < f_.result_complex.size() && f_.result_complex[i];
         Buffer& b = buffers_[v.buf];
         const bool whole = b.kind == Buffer::Arena && v.offset == 0 && is_dense(v) && b.bytes == v.type.bytes() &&
                            !claimed.count(v.buf) && v.type.count() > 0;

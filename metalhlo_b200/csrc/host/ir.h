@@ -137,6 +137,9 @@ struct Function {
     std::vector<Value> values;        // every SSA value of the function, regions included
     std::vector<Op> ops;              // top-level body in program order; the last one is the return
     std::vector<TensorType> result_types;
+    // Which parameters / results were complex tensors in the text (they are float tensors of (re, im) pairs here); empty
+    // when none was. Filled by legalize_complex for hosts that have a complex buffer type of their own (PJRT).
+    std::vector<bool> arg_complex, result_complex;
 
     int new_value(const TensorType& t, const std::string& name = "") {
         Value v;

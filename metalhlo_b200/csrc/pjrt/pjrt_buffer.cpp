@@ -74,6 +74,16 @@ PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref, PJRT_Device* de
     return b;
 }
 
+void present_as_complex(PJRT_Buffer* b) {
+    if (b->dims.empty() || b->dims.back() != 2) return;
+    if (b->type == PJRT_Buffer_Type_F32) b->type = PJRT_Buffer_Type_C64;
+    else if (b->type == PJRT_Buffer_Type_F64) b->type = PJRT_Buffer_Type_C128;
+    else return;
+    b->dims.pop_back();
+    b->minor_to_major.clear();
+    for (int i = static_cast<int>(b->dims.size()) - 1; i >= 0; --i) b->minor_to_major.push_back(i);
+}
+
 namespace {
 
 void release_storage(PJRT_Buffer* b) {
@@ -105,7 +115,10 @@ void pack_dense(const uint8_t* src, uint8_t* dst, const std::vector<int64_t>& di
 PJRT_Error* buffer_from_host(PJRT_Client_BufferFromHostBuffer_Args* args) {
     PJRT_B200_REQUIRE(args && args->client, "NULL args or client");
     MHLOElementType et;
-    if (!to_mhlo_type(args->type, &et))
+    // complex elements are stored as (re, im) pairs of their part type: one more dimension of extent 2 below this layer
+    const bool complex_pairs = args->type == PJRT_Buffer_Type_C64 || args->type == PJRT_Buffer_Type_C128;
+    const PJRT_Buffer_Type part_type = args->type == PJRT_Buffer_Type_C64 ? PJRT_Buffer_Type_F32 : args->type == PJRT_Buffer_Type_C128 ? PJRT_Buffer_Type_F64 : args->type;
+    if (!to_mhlo_type(part_type, &et))
         return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "Unsupported element type: " + std::to_string(static_cast<int>(args->type)));
     std::vector<int64_t> dims;
     if (args->dims) dims.assign(args->dims, args->dims + args->num_dims);
@@ -114,7 +127,7 @@ PJRT_Error* buffer_from_host(PJRT_Client_BufferFromHostBuffer_Args* args) {
         if (d < 0) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "negative dimension");
         count *= d;
     }
-    const size_t elem = storage_bytes_per_element(et);
+    const size_t elem = storage_bytes_per_element(et) * (complex_pairs ? 2 : 1);
     const size_t bytes = static_cast<size_t>(count) * elem;
     PJRT_B200_REQUIRE(args->data || bytes == 0, "NULL data pointer");
 
@@ -139,11 +152,14 @@ PJRT_Error* buffer_from_host(PJRT_Client_BufferFromHostBuffer_Args* args) {
     if (!target) target = args->client->devices[0];
     if (target->client != args->client) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "device belongs to another client");
     MHLOBufferRef ref = nullptr;
-    const MHLOStatusCode st = mhlo_buffer_create(target->mhlo, src, bytes, dims.data(), static_cast<int32_t>(dims.size()), et, &ref);
+    std::vector<int64_t> stored_dims = dims;
+    if (complex_pairs) stored_dims.push_back(2);
+    const MHLOStatusCode st = mhlo_buffer_create(target->mhlo, src, bytes, stored_dims.data(), static_cast<int32_t>(stored_dims.size()), et, &ref);
     if (st != MHLO_OK || !ref)
         return make_error(PJRT_Error_Code_INTERNAL, std::string("Buffer creation failed: ") + mhlo_get_last_error());
     args->done_with_host_buffer = new_ready_event();
     args->buffer = wrap_buffer(args->client, ref, target);
+    if (complex_pairs) present_as_complex(args->buffer);
     return nullptr;
 }
 
@@ -233,19 +249,24 @@ PJRT_Error* duplicate(PJRT_Buffer* src, PJRT_Device* target, PJRT_Buffer** out, 
     if (!src->mhlo) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, std::string(what) + ": buffer was deleted");
     if (!target) target = src->device;
     if (target->client != src->client) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, std::string(what) + ": device belongs to another client");
-    MHLOElementType et;
-    to_mhlo_type(src->type, &et);
+    // shape and type as stored (a complex buffer is a float buffer of pairs, one rank higher)
+    const bool complex_pairs = src->type == PJRT_Buffer_Type_C64 || src->type == PJRT_Buffer_Type_C128;
+    const MHLOElementType et = mhlo_buffer_element_type(src->mhlo);
+    std::vector<int64_t> stored(static_cast<size_t>(mhlo_buffer_rank(src->mhlo)));
+    int32_t stored_rank = 0;
+    mhlo_buffer_shape(src->mhlo, stored.data(), &stored_rank);
     MHLOBufferRef ref = nullptr;
     if (target != src->device) {
         std::vector<uint8_t> host(src->bytes);
         if (src->bytes && mhlo_buffer_to_host(src->mhlo, host.data(), host.size()) != MHLO_OK)
             return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
-        if (mhlo_buffer_create(target->mhlo, host.data(), host.size(), src->dims.data(), static_cast<int32_t>(src->dims.size()), et, &ref) != MHLO_OK)
+        if (mhlo_buffer_create(target->mhlo, host.data(), host.size(), stored.data(), static_cast<int32_t>(stored.size()), et, &ref) != MHLO_OK)
             return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
         *out = wrap_buffer(src->client, ref, target);
+        if (complex_pairs) present_as_complex(*out);
         return nullptr;
     }
-    if (mhlo_buffer_create_uninitialized(target->mhlo, src->dims.data(), static_cast<int32_t>(src->dims.size()), et, &ref) != MHLO_OK)
+    if (mhlo_buffer_create_uninitialized(target->mhlo, stored.data(), static_cast<int32_t>(stored.size()), et, &ref) != MHLO_OK)
         return make_error(PJRT_Error_Code_INTERNAL, std::string(what) + " failed: " + mhlo_get_last_error());
     if (src->bytes) {
         int st = mhlo_cuda_device_set(target->cuda_ordinal);
@@ -257,6 +278,7 @@ PJRT_Error* duplicate(PJRT_Buffer* src, PJRT_Device* target, PJRT_Buffer** out, 
         }
     }
     *out = wrap_buffer(src->client, ref, target);
+    if (complex_pairs) present_as_complex(*out);
     return nullptr;
 }
 

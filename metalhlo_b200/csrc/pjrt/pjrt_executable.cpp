@@ -34,12 +34,16 @@ std::shared_ptr<ExecutableMeta> describe(MHLOExecutableRef exe, const std::strin
         mhlo_executable_output_type(exe, static_cast<int32_t>(i), nullptr, &rank, nullptr);
         std::vector<int64_t> shape(static_cast<size_t>(rank));
         mhlo_executable_output_type(exe, static_cast<int32_t>(i), shape.data(), &rank, &et);
-        m->output_types.push_back(from_mhlo_type(et));
-        m->output_dim_sizes.push_back(static_cast<size_t>(rank));
+        // a complex result is a float tensor of (re, im) pairs below this layer: C64 / C128 of one rank less here
+        const bool cx = mhlo_b200_executable_output_is_complex(exe, static_cast<int32_t>(i)) == 1 && rank > 0 && shape.back() == 2 &&
+                        (et == MHLO_F32 || et == MHLO_F64);
+        m->output_complex.push_back(cx);
+        m->output_types.push_back(cx ? (et == MHLO_F32 ? PJRT_Buffer_Type_C64 : PJRT_Buffer_Type_C128) : from_mhlo_type(et));
+        m->output_dim_sizes.push_back(static_cast<size_t>(cx ? rank - 1 : rank));
         int64_t count = 1;
-        for (int64_t d : shape) {
-            m->output_dims.push_back(d);
-            count *= d;
+        for (size_t k = 0; k < shape.size(); ++k) {
+            if (!cx || k + 1 < shape.size()) m->output_dims.push_back(shape[k]);
+            count *= shape[k];
         }
         m->output_bytes += count * static_cast<int64_t>(storage_bytes_per_element(et));
         m->output_memory_kinds.push_back(kMemoryKind);
@@ -439,7 +443,10 @@ PJRT_Error* loaded_execute(PJRT_LoadedExecutable_Execute_Args* args) {
     for (size_t d = 0; d < count; ++d) {
         const bool want_outputs = args->output_lists && args->num_devices > 0 && args->output_lists[d];
         for (int32_t i = 0; i < produced[d]; ++i) {
-            if (want_outputs) args->output_lists[d][i] = wrap_buffer(loaded->client, outputs[d][static_cast<size_t>(i)], loaded->devices[first + d]);
+            if (want_outputs) {
+                args->output_lists[d][i] = wrap_buffer(loaded->client, outputs[d][static_cast<size_t>(i)], loaded->devices[first + d]);
+                if (loaded->meta->output_complex[static_cast<size_t>(i)]) present_as_complex(args->output_lists[d][i]);
+            }
             else mhlo_buffer_destroy(outputs[d][static_cast<size_t>(i)]);
         }
         if (args->device_complete_events && args->num_devices > 0) args->device_complete_events[d] = new_ready_event();

@@ -105,6 +105,7 @@ struct ExecutableMeta {
     std::vector<PJRT_Buffer_Type> output_types;
     std::vector<int64_t> output_dims;      // all outputs' dims concatenated
     std::vector<size_t> output_dim_sizes;  // rank of each output
+    std::vector<bool> output_complex;      // the output is C64 / C128 here and a float tensor of (re, im) pairs below
     std::vector<const char*> output_memory_kinds;
     std::vector<size_t> output_memory_kind_sizes;
     int64_t code_bytes = 0, argument_bytes = 0, output_bytes = 0, temp_bytes = 0;
@@ -141,6 +142,9 @@ PJRT_Buffer_Type from_mhlo_type(MHLOElementType t);
 size_t storage_bytes_per_element(MHLOElementType t);
 
 PJRT_Buffer* wrap_buffer(PJRT_Client* client, MHLOBufferRef ref, PJRT_Device* device = nullptr);
+// Presents a float buffer of (re, im) pairs as the complex buffer one rank lower that PJRT knows (C64 / C128): the C API
+// below has no complex element type (Sources/CMetalHLO/include/metalhlo.h:61-75); the bytes are the same.
+void present_as_complex(PJRT_Buffer* b);
 std::string hex_hash(const std::string& text);
 
 // Fills every table entry the plugin implements; each group lives in its own translation unit.

@@ -477,6 +477,61 @@ static void device_cases() {
         destroy_loaded(loop);
     }
 
+    // complex values: a C64 argument goes down as (re, im) float pairs, an RFFT spectrum comes back up as C64
+    {
+        const char* text =
+            "module @cx {\n"
+            "  func.func @main(%arg0: tensor<8xf32>, %arg1: tensor<5xcomplex<f32>>) -> (tensor<5xcomplex<f32>>, tensor<5xf32>) {\n"
+            "    %0 = stablehlo.fft %arg0, type = RFFT, length = [8] : (tensor<8xf32>) -> tensor<5xcomplex<f32>>\n"
+            "    %1 = stablehlo.add %0, %arg1 : tensor<5xcomplex<f32>>\n"
+            "    %2 = stablehlo.imag %arg1 : (tensor<5xcomplex<f32>>) -> tensor<5xf32>\n"
+            "    return %1, %2 : tensor<5xcomplex<f32>>, tensor<5xf32>\n"
+            "  }\n"
+            "}\n";
+        PJRT_LoadedExecutable* cx = compile(c, text, &e);
+        const float x8[8] = {1.f, 2.f, 3.f, 4.f, 5.f, 6.f, 7.f, 8.f};
+        const float z5[10] = {10.f, 1.f, 20.f, 2.f, 30.f, 3.f, 40.f, 4.f, 50.f, 5.f};  // (re, im) x 5
+        std::string e2, e3;
+        PJRT_Buffer* xb = cx ? make_buffer(c, x8, PJRT_Buffer_Type_F32, {8}, nullptr, &e2) : nullptr;
+        PJRT_Buffer* zb = cx ? make_buffer(c, z5, PJRT_Buffer_Type_C64, {5}, nullptr, &e3) : nullptr;
+        bool ok = cx && xb && zb;
+        if (ok) {
+            PJRT_Buffer_ElementType_Args et{};
+            et.struct_size = PJRT_Buffer_ElementType_Args_STRUCT_SIZE;
+            et.buffer = zb;
+            api->PJRT_Buffer_ElementType(&et);
+            PJRT_Buffer_Dimensions_Args dm{};
+            dm.struct_size = PJRT_Buffer_Dimensions_Args_STRUCT_SIZE;
+            dm.buffer = zb;
+            api->PJRT_Buffer_Dimensions(&dm);
+            ok = et.type == PJRT_Buffer_Type_C64 && dm.num_dims == 1 && dm.dims[0] == 5;
+        }
+        std::vector<PJRT_Buffer*> outs(2, nullptr);
+        if (ok) e = execute(cx, {xb, zb}, &outs);
+        float spec[10] = {}, im[5] = {};
+        if (ok && e.empty() && outs[0]) e = read_buffer(outs[0], spec, sizeof spec);
+        if (ok && e.empty() && outs[1]) e = read_buffer(outs[1], im, sizeof im);
+        if (ok && e.empty()) {
+            PJRT_Buffer_ElementType_Args et{};
+            et.struct_size = PJRT_Buffer_ElementType_Args_STRUCT_SIZE;
+            et.buffer = outs[0];
+            api->PJRT_Buffer_ElementType(&et);
+            PJRT_Buffer_Dimensions_Args dm{};
+            dm.struct_size = PJRT_Buffer_Dimensions_Args_STRUCT_SIZE;
+            dm.buffer = outs[0];
+            api->PJRT_Buffer_Dimensions(&dm);
+            // bin 0 of the spectrum is the sum (36), bin 4 the alternating sum (-4); both real
+            ok = et.type == PJRT_Buffer_Type_C64 && dm.num_dims == 1 && dm.dims[0] == 5 && std::fabs(spec[0] - 46.f) < 1e-4f &&
+                 std::fabs(spec[1] - 1.f) < 1e-4f && std::fabs(spec[8] - 46.f) < 1e-4f && std::fabs(spec[9] - 5.f) < 1e-4f && im[2] == 3.f;
+        }
+        report("complex_buffers_and_rfft", ok && e.empty(), e + e2 + e3);
+        destroy_buffer(outs[0]);
+        destroy_buffer(outs[1]);
+        destroy_buffer(xb);
+        destroy_buffer(zb);
+        destroy_loaded(cx);
+    }
+
     // compile errors surface as PJRT errors with the compiler's message
     {
         PJRT_LoadedExecutable* badexe = compile(c, "module { func.func @main() -> tensor<f32> { %0 = stablehlo.nonsense : tensor<f32> return %0 : tensor<f32> } }", &e);

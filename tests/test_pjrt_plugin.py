@@ -18,7 +18,7 @@ HOST_CASES = ["load", "api_version", "required_functions", "error_lifecycle", "p
               "deserialize_rejects_null"]
 DEVICE_CASES = ["client_create", "platform_name", "one_device", "memory_kind_device", "device_attributes", "buffer_round_trip",
                 "event_on_ready", "strided_host_buffer", "copy_raw_to_host", "compile_add", "execute_add", "executable_outputs",
-                "serialize_format", "deserialize_and_execute", "fingerprint", "execute_softmax", "execute_loop_with_call", "compile_error_reported",
+                "serialize_format", "deserialize_and_execute", "fingerprint", "execute_softmax", "execute_loop_with_call", "complex_buffers_and_rfft", "compile_error_reported",
                 "bytecode_refused", "delete_and_memory_stats", "client_destroy"]
 
 
