@@ -595,6 +595,14 @@ class Lowering {
         if (n == "dot_general" || n == "dot") return lower_dot(op);
         if (n == "gather") return lower_gather(op);
         if (n == "convolution") return lower_convolution(op);
+        if (n == "dynamic_conv") {  // the padding is an operand ([spatial dims, 2]); it must be a constant of the module
+            if (op.operands.size() != 3) fail_compile("dynamic_conv takes three operands");
+            Op c = op;
+            c.name = "convolution";
+            c.operands.resize(2);
+            c.attrs["padding"] = Attr::make_ints(constant_ints(op.operands[2], "dynamic_conv: padding"));
+            return lower_convolution(c);
+        }
         if (n == "reduce_window") return lower_reduce_window(op);
         if (n == "while") return lower_while(op);
         if (n == "scatter") return lower_scatter(op);
@@ -703,10 +711,15 @@ class Lowering {
         const size_t es = dtype_size(v.type.dtype);
         std::vector<int64_t> out;
         const int64_t n = v.type.count();
-        if (v.type.rank() > 1) fail_unsupported(what + " must be a vector");
-        const int64_t stride = v.type.rank() == 1 ? v.strides[0] : 0;
+        std::vector<int64_t> idx(static_cast<size_t>(v.type.rank()), 0);  // row-major walk over a view of any rank
         for (int64_t i = 0; i < n; ++i) {
-            const uint8_t* p = exe_->const_pool_.data() + b.offset + (v.offset + i * stride) * static_cast<int64_t>(es);
+            int64_t at = v.offset;
+            for (int d = 0; d < v.type.rank(); ++d) at += idx[static_cast<size_t>(d)] * v.strides[static_cast<size_t>(d)];
+            for (int d = v.type.rank() - 1; d >= 0; --d) {
+                if (++idx[static_cast<size_t>(d)] < v.type.shape[static_cast<size_t>(d)]) break;
+                idx[static_cast<size_t>(d)] = 0;
+            }
+            const uint8_t* p = exe_->const_pool_.data() + b.offset + at * static_cast<int64_t>(es);
             uint64_t raw = 0;
             for (size_t k = 0; k < es; ++k) raw |= static_cast<uint64_t>(p[k]) << (8 * k);
             if (!is_unsigned(v.type.dtype) && es < 8 && (raw >> (8 * es - 1)) & 1) raw |= ~0ull << (8 * es);

@@ -443,6 +443,51 @@ bool drop_optimization_barriers(Function& f) {
     return changed;
 }
 
+// stablehlo.tuple / get_tuple_element: a tuple is only a name for a list of values (nested tuples included), so every
+// get_tuple_element of a tuple built in the same function is replaced by the member it names and the tuple itself goes
+// away once nothing reads it. A tuple that crosses the function's boundary stays and is refused by the lowering: buffers
+// of the C API are tensors (Sources/CMetalHLO/include/metalhlo.h).
+bool fold_tuples(Function& f) {
+    bool any = false;
+    for (const Op& op : f.ops) any = any || (!op.dead && (op.name == "tuple" || op.name == "get_tuple_element"));
+    if (!any) return false;
+    bool changed = false;
+    std::map<int, std::vector<int>> members;  // tuple value -> its members
+    std::map<int, int> alias;
+    std::vector<Op> out;
+    for (Op& op : f.ops) {
+        apply_alias(op, alias);
+        if (!op.dead && op.name == "tuple" && op.results.size() == 1) members[op.results[0]] = op.operands;
+        if (!op.dead && op.name == "get_tuple_element" && op.operands.size() == 1 && op.results.size() == 1) {
+            const std::vector<int64_t> idx = op.int_list("indices");
+            const int64_t k = !idx.empty() ? idx[0] : op.int_attr("index", -1);
+            auto it = members.find(op.operands[0]);
+            if (it != members.end()) {
+                if (k < 0 || k >= static_cast<int64_t>(it->second.size())) fail_compile("get_tuple_element: index " + std::to_string(k) + " outside the tuple");
+                alias[op.results[0]] = it->second[static_cast<size_t>(k)];
+                changed = true;
+                continue;
+            }
+        }
+        out.push_back(std::move(op));
+    }
+    f.ops.swap(out);
+    // tuples nothing reads any more
+    const std::vector<std::vector<int>> users = f.users();
+    for (size_t i = f.ops.size(); i-- > 0;) {
+        Op& op = f.ops[i];
+        if (op.name == "tuple" && op.results.size() == 1 && users[static_cast<size_t>(op.results[0])].empty()) {
+            bool read_later = false;  // by a tuple that is itself still alive
+            for (const Op& other : f.ops)
+                if (!other.dead && &other != &op)
+                    for (int v : other.operands) read_later = read_later || v == op.results[0];
+            if (!read_later) { op.dead = true; changed = true; }
+        }
+    }
+    if (changed) f.compact();
+    return changed;
+}
+
 bool flatten_top_k(Function& f) {
     bool any = false;
     std::vector<Op> out;
@@ -707,7 +752,7 @@ Function flatten_main(Module& m) {
         const bool c = flatten_conditionals(main);
         const bool d = flatten_maps(main);
         const bool e = flatten_top_k(main);
-        const bool g = drop_optimization_barriers(main);
+        const bool g = drop_optimization_barriers(main) | fold_tuples(main);
         const bool h = expand_fused_custom_calls(main);
         return a || b || c || d || e || g || h;
     };

@@ -1251,7 +1251,7 @@ class Parser {
             }
             op->attrs["sort_order"] = Attr::make_string(order);
         }
-        if (n == "convolution") normalise_convolution(op);
+        if (n == "convolution" || n == "dynamic_conv") normalise_convolution(op);
         if (n == "dynamic_slice") { rename("sizes", "slice_sizes"); }
         if (n == "pad") { rename("low", "edge_padding_low"); rename("high", "edge_padding_high"); rename("interior", "interior_padding"); }
         if (n == "custom_call") {

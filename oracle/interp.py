@@ -525,7 +525,7 @@ class ModuleParser(Scanner):
             self.p += 5
             body = self.balanced("<", ">")
             vals = body.split(":", 1)[1] if ":" in body else ""
-            return [int(x) for x in vals.replace(" ", "").split(",") if x]
+            return [{"true": 1, "false": 0}.get(x, x) if x in ("true", "false") else int(x) for x in vals.replace(" ", "").split(",") if x]
         if c == "@":
             self.p += 1
             return self.ident()
@@ -1061,6 +1061,13 @@ class Interpreter:
                 return [env[v] for v in op.operands]
             if op.name.startswith("check."):
                 continue
+            if op.name == "tuple":  # a name for a list of values (nested tuples included)
+                env[op.results[0]] = tuple(env[v] for v in op.operands)
+                continue
+            if op.name == "get_tuple_element":
+                idx = op.attrs.get("index", op.attrs.get("indices"))
+                env[op.results[0]] = env[op.operands[0]][_ints(idx)[0]]
+                continue
             outs = self.eval(op, [env[v] if v in env else env[v + "#0"] for v in op.operands], env)
             if not isinstance(outs, (list, tuple)):
                 outs = [outs]
@@ -1510,6 +1517,10 @@ class Interpreter:
         raw = np.ascontiguousarray(a[0].astype(_storage_dtype(op.in_types[0].dtype)))
         out = (raw if raw.ndim else raw.reshape(1)).view(_storage_dtype(t.dtype)).reshape(t.shape)
         return out.astype(np.float64) if t.is_float else out
+
+    def op_dynamic_conv(self, op, a, t):
+        """stablehlo.dynamic_conv: convolution whose padding is its third operand ([spatial dims, 2])."""
+        return self.op_convolution(_with_attrs(op, padding=[int(x) for x in np.asarray(a[2]).reshape(-1)]), a[:2], t)
 
     def op_convolution(self, op, a, t):
         """stablehlo.convolution: the input is dilated and padded with zeros, and every output element is the dot

@@ -31,7 +31,8 @@ FILES = ["abs", "add", "and", "atan2", "broadcast_in_dim", "cbrt", "ceil", "clam
          "dynamic_pad", "dynamic_reshape", "optimization_barrier", "reduce_window", "scatter", "sort", "convolution", "select_and_scatter", "map",
          "get_dimension_size", "reduce_precision", "composite",
          # complex values: (re, im) float pairs behind the parser
-         "complex", "real", "imag"]
+         "complex", "real", "imag",
+         "tuple_and_get_tuple_element", "dynamic_conv"]
 
 
 class Case:
