@@ -471,6 +471,14 @@ int mhlo_cuda_conv2d_nhwc(int32_t dtype, int32_t out_dtype, const void* x_dev, c
                           int64_t features, int64_t out_h, int64_t out_w, int64_t pad_top, int64_t pad_left,
                           int64_t dilation_h, int64_t dilation_w, const void* bias_dev, int32_t epilogue,
                           mhlo_cuda_stream_t stream);
+/* The same with window strides of 1 to 8: the patch of a tap is then every stride-th input pixel, which the bulk tensor
+ * copy takes through its traversal strides, in[n, y * stride_h + dy * dilation_h - pad_top, x * stride_w + dx * dilation_w -
+ * pad_left, c]. */
+int mhlo_cuda_conv2d_nhwc_strided(int32_t dtype, int32_t out_dtype, const void* x_dev, const void* filter_dev, void* out_dev,
+                                  int64_t images, int64_t in_h, int64_t in_w, int64_t channels, int64_t filter_h, int64_t filter_w,
+                                  int64_t features, int64_t out_h, int64_t out_w, int64_t pad_top, int64_t pad_left,
+                                  int64_t dilation_h, int64_t dilation_w, int64_t stride_h, int64_t stride_w, const void* bias_dev,
+                                  int32_t epilogue, mhlo_cuda_stream_t stream);
 
 /*
  * Direct convolution, one thread per output element, every attribute of the op honoured (strides, padding, both

@@ -34,6 +34,7 @@ struct ConvProblem {
     const void* bias = nullptr;  // one value per output feature, of the output's type
     int32_t dtype, out_dtype, epilogue = 0;
     int64_t images, h, w, channels, kh, kw, features, oh, ow, pad_h, pad_w, dil_h, dil_w;
+    int64_t stride_h = 1, stride_w = 1;
 };
 bool conv_tc_supported(const ConvProblem& c);
 int conv_tc_launch(const ConvProblem& c, cudaStream_t stream);

@@ -213,6 +213,14 @@ int mhlo_cuda_conv2d_nhwc(int32_t dtype, int32_t out_dtype, const void* x_dev, c
                           int64_t in_h, int64_t in_w, int64_t channels, int64_t filter_h, int64_t filter_w, int64_t features, int64_t out_h,
                           int64_t out_w, int64_t pad_top, int64_t pad_left, int64_t dilation_h, int64_t dilation_w, const void* bias_dev,
                           int32_t epilogue, mhlo_cuda_stream_t stream) {
+    return mhlo_cuda_conv2d_nhwc_strided(dtype, out_dtype, x_dev, filter_dev, out_dev, images, in_h, in_w, channels, filter_h, filter_w, features,
+                                         out_h, out_w, pad_top, pad_left, dilation_h, dilation_w, 1, 1, bias_dev, epilogue, stream);
+}
+
+int mhlo_cuda_conv2d_nhwc_strided(int32_t dtype, int32_t out_dtype, const void* x_dev, const void* filter_dev, void* out_dev, int64_t images,
+                                  int64_t in_h, int64_t in_w, int64_t channels, int64_t filter_h, int64_t filter_w, int64_t features,
+                                  int64_t out_h, int64_t out_w, int64_t pad_top, int64_t pad_left, int64_t dilation_h, int64_t dilation_w,
+                                  int64_t stride_h, int64_t stride_w, const void* bias_dev, int32_t epilogue, mhlo_cuda_stream_t stream) {
     if (epilogue < MHLO_EPILOGUE_NONE || epilogue > MHLO_EPILOGUE_SIGMOID)
         return fail(MHLO_CUDA_INVALID_ARGUMENT, "conv2d_nhwc: unknown epilogue %d", epilogue);
     if (images < 0 || in_h < 0 || in_w < 0 || channels < 0 || filter_h < 0 || filter_w < 0 || features < 0 || out_h < 0 || out_w < 0)
@@ -224,8 +232,9 @@ int mhlo_cuda_conv2d_nhwc(int32_t dtype, int32_t out_dtype, const void* x_dev, c
     c.dtype = dtype; c.out_dtype = out_dtype; c.epilogue = epilogue;
     c.images = images; c.h = in_h; c.w = in_w; c.channels = channels; c.kh = filter_h; c.kw = filter_w; c.features = features;
     c.oh = out_h; c.ow = out_w; c.pad_h = pad_top; c.pad_w = pad_left; c.dil_h = dilation_h; c.dil_w = dilation_w;
+    c.stride_h = stride_h; c.stride_w = stride_w;
     if (!conv_tc_supported(c))
-        return fail(MHLO_CUDA_UNSUPPORTED, "conv2d_nhwc: needs f16 / bf16 tensors, channels in multiples of 64, feature rows on the 16-byte grid");
+        return fail(MHLO_CUDA_UNSUPPORTED, "conv2d_nhwc: needs f16 / bf16 tensors, channels in multiples of 64, feature rows on the 16-byte grid, strides of 1 to 8");
     return conv_tc_launch(c, static_cast<cudaStream_t>(stream));
 }
 

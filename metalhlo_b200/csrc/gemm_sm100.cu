@@ -91,7 +91,7 @@ struct GemmParams {
     int32_t stages;                  // depth of the TMA ring in use (<= the kernel's STAGES)
     // MODE 3 (convolution without a patch matrix): a row tile is an 8 x 16 patch of output positions of one image
     // (batch index = image, tiles_m = patches per image); k-block kb = (filter tap, 64 input channels)
-    int32_t conv_tiles_x, conv_kw, conv_cblocks, conv_pad_h, conv_pad_w, conv_dil_h, conv_dil_w, conv_oh;
+    int32_t conv_tiles_x, conv_kw, conv_cblocks, conv_pad_h, conv_pad_w, conv_dil_h, conv_dil_w, conv_oh, conv_stride_h, conv_stride_w;
 };
 
 // Tensor maps of the further copies of C (GemmParams::copies, in the same order), used when the copies are written with
@@ -230,8 +230,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
                         const int dy = tap / p.conv_kw, dx = tap - dy * p.conv_kw;
                         // {channel, x, y, image}: pixels outside the image (the padding) are filled with zeros by the copy
-                        tma_load_4d(sa, &map_a, &full_bar[stage], cb * 64, tx * 16 + dx * p.conv_dil_w - p.conv_pad_w,
-                                    ty * 8 + dy * p.conv_dil_h - p.conv_pad_h, bz);
+                        // (a strided convolution reads every conv_stride-th pixel: the tensor map's traversal strides)
+                        tma_load_4d(sa, &map_a, &full_bar[stage], cb * 64, tx * 16 * p.conv_stride_w + dx * p.conv_dil_w - p.conv_pad_w,
+                                    ty * 8 * p.conv_stride_h + dy * p.conv_dil_h - p.conv_pad_h, bz);
                     } else if (!p.a_mn_major) {
                         load(sa, &map_a, kb * BK, row_a);
                     } else {
@@ -833,12 +834,14 @@ static int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
 
 // ---- convolution without a patch matrix (MODE 3) ----
 
+// step_w / step_h: the box takes every step-th pixel (16 x box_h of them), for the input of a strided convolution.
 bool conv_map(CUtensorMap* map, const void* base, int64_t elem_bytes, int64_t inner, int64_t w, int64_t h, int64_t n, uint32_t box_inner,
-              uint32_t box_h, bool is_f32, std::string* why) {
+              uint32_t box_h, bool is_f32, std::string* why, uint32_t step_w = 1, uint32_t step_h = 1) {
     cuuint64_t gdim[4] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
     cuuint64_t gstr[3] = {static_cast<cuuint64_t>(inner * elem_bytes), static_cast<cuuint64_t>(w * inner * elem_bytes),
                           static_cast<cuuint64_t>(h * w * inner * elem_bytes)};
-    cuuint32_t box[4] = {box_inner, 16, box_h, 1}, estr[4] = {1, 1, 1, 1};
+    // with a traversal stride s a box extent of (k - 1) s + 1 elements delivers k of them
+    cuuint32_t box[4] = {box_inner, 15 * step_w + 1, (box_h - 1) * step_h + 1, 1}, estr[4] = {1, step_w, step_h, 1};
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -872,6 +875,7 @@ bool conv_tc_supported(const ConvProblem& c) {
     if ((c.features * 2) % 16 != 0 || (c.features * out_es) % 16 != 0) return false;
     if (!aligned16(c.x) || !aligned16(c.wgt) || !aligned16(c.out)) return false;
     if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0) return false;
+    if (c.stride_h < 1 || c.stride_w < 1 || c.stride_h > 8 || c.stride_w > 8) return false;  // traversal strides of a tensor map
     // the window arithmetic of a stride-1 convolution must give the declared result
     if (c.oh > c.h + 2 * 0x3fff || c.images > 0x7fffffff) return false;
     return true;
@@ -883,7 +887,7 @@ static int launch_conv_act(const ConvProblem& c, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES, 1>;
     std::string why;
     CUtensorMap map_a, map_b, map_c;
-    if (!conv_map(&map_a, c.x, 2, c.channels, c.w, c.h, c.images, 64, 8, false, &why))
+    if (!conv_map(&map_a, c.x, 2, c.channels, c.w, c.h, c.images, 64, 8, false, &why, static_cast<uint32_t>(c.stride_w), static_cast<uint32_t>(c.stride_h)))
         return fail(MHLO_CUDA_EXECUTION_FAILED, "convolution: tensor map for the input: %s", why.c_str());
     const int64_t kc = c.kh * c.kw * c.channels;
     if (!operand_map(&map_b, c.wgt, c.features, kc, c.features, 1, 0, 1, 0, 64, BK, &why))
@@ -921,6 +925,8 @@ static int launch_conv_act(const ConvProblem& c, cudaStream_t stream) {
     p.conv_dil_h = static_cast<int32_t>(c.dil_h);
     p.conv_dil_w = static_cast<int32_t>(c.dil_w);
     p.conv_oh = static_cast<int32_t>(c.oh);
+    p.conv_stride_h = static_cast<int32_t>(c.stride_h);
+    p.conv_stride_w = static_cast<int32_t>(c.stride_w);
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, ACT, 1, 3>;
     static std::atomic<bool> attr_set[64];
     int attr_dev = 0;

@@ -1132,12 +1132,12 @@ class Lowering {
             });
             return out;
         }
-        // ---- two spatial dimensions, dense NHWC input and HWIO filter, stride 1, one group, 16-bit tensors with channels in
+        // ---- two spatial dimensions, dense NHWC input and HWIO filter, window strides up to 8, one group, 16-bit tensors with channels in
         // multiples of 64: the tensor-core kernel reads the input itself (no patch matrix)
         {
             bool direct = ns == 2 && G == 1 && (x.type.dtype == DType::F16 || x.type.dtype == DType::BF16) && c.in_features % 64 == 0 &&
                           c.out_features % 8 == 0 && !std::getenv("METALHLO_CONV_PATCHES");
-            for (int d = 0; d < ns && direct; ++d) direct = st[d] == 1 && ld[d] == 1 && rev[d] == 0 && pad[2 * d] >= 0 && pad[2 * d + 1] >= 0;
+            for (int d = 0; d < ns && direct; ++d) direct = st[d] >= 1 && st[d] <= 8 && ld[d] == 1 && rev[d] == 0 && pad[2 * d] >= 0 && pad[2 * d + 1] >= 0;
             if (direct) {
                 const int64_t H = c.in_size[0], W = c.in_size[1], C = c.in_features, O = c.out_features;
                 direct = is_dense(x) && c.in_feature_stride == 1 && c.in_spatial_stride[1] == C && c.in_spatial_stride[0] == W * C &&
@@ -1156,12 +1156,12 @@ class Lowering {
                 const int out_dt = static_cast<int>(rt.dtype);
                 if (fused) *fused = true;
                 const mhlo_cuda_conv cc = c;
-                const int64_t pad_top = pad[0], pad_left = pad[2], dil_h = rd[0], dil_w = rd[1];
+                const int64_t pad_top = pad[0], pad_left = pad[2], dil_h = rd[0], dil_w = rd[1], stride_h = st[0], stride_w = st[1];
                 add_step(with_bias || epilogue != MHLO_EPILOGUE_NONE ? "convolution.tensor_core+epilogue" : "convolution.tensor_core", [=](const Ctx& cx) {
-                    return mhlo_cuda_conv2d_nhwc(dt, out_dt, bind(dx, cx).base, bind(dw, cx).base, const_cast<void*>(bind(dcanon, cx).base), cc.batch,
-                                                 cc.in_size[0], cc.in_size[1], cc.in_features, cc.kernel_size[0], cc.kernel_size[1], cc.out_features,
-                                                 cc.out_size[0], cc.out_size[1], pad_top, pad_left, dil_h, dil_w,
-                                                 with_bias ? bind(dbias, cx).base : nullptr, epilogue, cx.stream);
+                    return mhlo_cuda_conv2d_nhwc_strided(dt, out_dt, bind(dx, cx).base, bind(dw, cx).base, const_cast<void*>(bind(dcanon, cx).base), cc.batch,
+                                                         cc.in_size[0], cc.in_size[1], cc.in_features, cc.kernel_size[0], cc.kernel_size[1], cc.out_features,
+                                                         cc.out_size[0], cc.out_size[1], pad_top, pad_left, dil_h, dil_w, stride_h, stride_w,
+                                                         with_bias ? bind(dbias, cx).base : nullptr, epilogue, cx.stream);
                 });
                 View out = canon;
                 out.type = rt;

@@ -129,6 +129,7 @@ _PROTOTYPES = {
     "mhlo_cuda_stream_wait_event": (C.c_int, [_vp, _vp]),
     "mhlo_cuda_stream_host_callback": (C.c_int, [_vp, _vp, _vp]),
     "mhlo_cuda_conv2d_nhwc": (C.c_int, [_i32, _i32, _vp, _vp, _vp] + [_i64] * 13 + [_vp, _i32, _vp]),
+    "mhlo_cuda_conv2d_nhwc_strided": (C.c_int, [_i32, _i32, _vp, _vp, _vp] + [_i64] * 15 + [_vp, _i32, _vp]),
     "mhlo_cuda_rng": (C.c_int, [_i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "mhlo_cuda_rng_bit_generator": (C.c_int, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "mhlo_cuda_peer_barrier": (C.c_int, [C.POINTER(_vp), _i32, _i32, C.c_uint64, C.c_uint64, _vp]),

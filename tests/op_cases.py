@@ -969,7 +969,7 @@ def convolution_cases():
     out.append(conv_case("conv_3d_f32", data((1, 5, 6, 7, 2), "f32"), data((2, 3, 2, 2, 4), "f32", 0.3), "f32", (1, 4, 4, 6, 4),
                          layout="[b, 0, 1, 2, f]x[0, 1, 2, i, o]->[b, 0, 1, 2, f]"))
     out.append(conv_case("conv_i32", data((1, 6, 6, 2), "i32"), data((3, 3, 2, 3), "i32"), "i32", (1, 4, 4, 3)))
-    # the forms the tensor-core kernel reads without a patch matrix: 16-bit NHWC x HWIO, stride 1, channels in multiples of 64
+    # the forms the tensor-core kernel reads without a patch matrix: 16-bit NHWC x HWIO, channels in multiples of 64
     for dt in ("f16", "bf16"):
         if dt not in NP:
             continue
@@ -981,6 +981,13 @@ def convolution_cases():
                              window="pad = [[2, 2], [2, 2]], rhs_dilate = [2, 2]"))
         out.append(conv_case(f"conv_direct_uneven_padding_{dt}", data((2, 9, 10, 64), dt), data((2, 4, 64, 16), dt, 0.07), dt, (2, 11, 9, 16),
                              window="pad = [[2, 1], [0, 2]]"))
+        # window strides: the downsampling 3x3 and 1x1 convolutions of a residual network, and unequal strides with a dilated filter
+        out.append(conv_case(f"conv_direct_stride2_3x3_{dt}", data((2, 14, 14, 64), dt), data((3, 3, 64, 128), dt, 0.06), dt, (2, 7, 7, 128),
+                             window="stride = [2, 2], pad = [[0, 1], [0, 1]]"))
+        out.append(conv_case(f"conv_direct_stride2_1x1_{dt}", data((2, 37, 20, 64), dt), data((1, 1, 64, 64), dt, 0.15), dt, (2, 19, 10, 64),
+                             window="stride = [2, 2]"))
+        out.append(conv_case(f"conv_direct_stride_3_by_2_dilated_{dt}", data((1, 40, 45, 128), dt), data((3, 2, 128, 24), dt, 0.05), dt, (1, 13, 22, 24),
+                             window="stride = [3, 2], pad = [[1, 1], [1, 0]], rhs_dilate = [2, 2]"))
     out.append(conv_case("conv_mixed_layouts_f32", data((6, 6, 2, 5), "f32"), data((3, 4, 3, 5), "f32", 0.3), "f32", (4, 2, 4, 4),
                          layout="[0, 1, b, f]x[0, o, 1, i]->[0, b, f, 1]"))
     out.append(conv_case("conv_short_form_f32", data((2, 8, 8, 4), "f32"), data((3, 3, 4, 8), "f32", 0.2), "f32", (2, 8, 8, 8),
