@@ -6,6 +6,7 @@
 // `stablehlo.case` become straight-line code too: every branch is computed and the results are picked with `select`,
 // which is exact because StableHLO ops have no side effects (the reference runs them through MPSGraph's if/else,
 // Sources/MetalHLOCore/MPSGraph/MPSGraphCompiler.swift, with the same results).
+#include <cmath>
 #include <functional>
 #include <map>
 
@@ -647,6 +648,34 @@ bool expand_fused_custom_calls(Function& f) {
         out.back().results = call.results;
     };
     for (Op& op : f.ops) {
+        // uniform_quantize(x, scale) = convert(round(x / scale)) and uniform_dequantize(q, scale) = convert(q) * scale: the
+        // reference's two-operand forms, scale an ordinary tensor (Compiler/MPSGraphCompiler.swift:3615-3640), not the
+        // specification's quantised element types, which neither backend has
+        if (!op.dead && (op.name == "uniform_quantize" || op.name == "uniform_dequantize") && op.operands.size() == 2 && op.results.size() == 1) {
+            const Op call = op;
+            any = true;
+            const TensorType rt = call.result_types[0], xt = f.type_of(call.operands[0]);
+            if (call.name == "uniform_quantize") {
+                if (!is_float(xt.dtype) || is_float(rt.dtype)) fail_unsupported("uniform_quantize from " + xt.str() + " to " + rt.str());
+                const int s = broadcast_trailing(call.operands[1], xt, "uniform_quantize");
+                int q = unary("round_nearest_even", binary("divide", call.operands[0], s));
+                // quantisation saturates at the ends of the storage type (a bare convert of an out-of-range float need not)
+                const int bits = static_cast<int>(dtype_size(rt.dtype)) * 8;
+                if (rt.dtype != DType::I1 && bits <= 32) {
+                    const bool uns = is_unsigned(rt.dtype);
+                    double lo = uns ? 0.0 : -std::ldexp(1.0, bits - 1), hi = std::ldexp(1.0, uns ? bits : bits - 1) - 1.0;
+                    if (bits == 32) hi = uns ? 4294967040.0 : 2147483520.0;  // the largest floats below 2^32 and 2^31
+                    Op cl = simple_op(f, "clamp", {float_splat(xt, lo), q, float_splat(xt, hi)}, xt);
+                    q = emit(std::move(cl));
+                }
+                finish(emit(simple_op(f, "convert", {q}, rt)), call);
+            } else {
+                if (!is_float(rt.dtype)) fail_unsupported("uniform_dequantize from " + xt.str() + " to " + rt.str());
+                const int x = emit(simple_op(f, "convert", {call.operands[0]}, rt));
+                finish(binary("multiply", x, broadcast_trailing(call.operands[1], rt, "uniform_dequantize")), call);
+            }
+            continue;
+        }
         const std::string target = !op.dead && op.name == "custom_call" ? op.str_attr("call_target_name") : "";
         if (target != "fused_batch_norm" && target != "fused_rope" && target != "fused_ffn" && target != "fused_depth_attention") {
             out.push_back(std::move(op));

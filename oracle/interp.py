@@ -1518,6 +1518,21 @@ class Interpreter:
         out = (raw if raw.ndim else raw.reshape(1)).view(_storage_dtype(t.dtype)).reshape(t.shape)
         return out.astype(np.float64) if t.is_float else out
 
+    def op_uniform_quantize(self, op, a, t):
+        """The reference's two-operand form: round(x / scale) in the result's integer type
+        (Compiler/MPSGraphCompiler.swift:3615-3628), ties to even, saturating like convert."""
+        if len(a) != 2:
+            raise Unsupported("uniform_quantize with quantised element types")
+        with np.errstate(all="ignore"):
+            # the quotient is a tensor of the operand's type before it is rounded to an integer
+            return _float_to_int(np.rint(round_to(a[0] / a[1], op.in_types[0].dtype)), t)
+
+    def op_uniform_dequantize(self, op, a, t):
+        """The reference's two-operand form: float(q) * scale (Compiler/MPSGraphCompiler.swift:3630-3640)."""
+        if len(a) != 2:
+            raise Unsupported("uniform_dequantize with quantised element types")
+        return round_to(np.asarray(a[0]).astype(np.float64), t.dtype) * a[1]
+
     def op_dynamic_conv(self, op, a, t):
         """stablehlo.dynamic_conv: convolution whose padding is its third operand ([spatial dims, 2])."""
         return self.op_convolution(_with_attrs(op, padding=[int(x) for x in np.asarray(a[2]).reshape(-1)]), a[:2], t)

@@ -1116,6 +1116,25 @@ def custom_call_cases():
     return out
 
 
+def quantize_cases():
+    """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
+    rng = np.random.default_rng(909)
+    out = []
+    for dt, qt in (("f32", "i8"), ("f32", "i32"), ("f16", "i8"), ("f32", "ui8")):
+        shape = (5, 33)
+        x = (rng.uniform(-40, 40, size=shape)).astype(np.float32).astype(NP[dt])
+        if qt == "ui8":
+            x = np.abs(x)
+        t, q = tt(shape, dt), tt(shape, qt)
+        for sname, sshape in (("scalar", ()), ("per_column", (33,))):
+            ts = tt(sshape, dt)
+            scale = rng.uniform(0.1, 0.5, size=sshape).astype(np.float32).astype(NP[dt])
+            body = (f"    %0 = stablehlo.uniform_quantize %arg0, %arg1 : ({t}, {ts}) -> {q}\n"
+                    f"    %1 = stablehlo.uniform_dequantize %0, %arg1 : ({q}, {ts}) -> {t}")
+            out.append((f"quantize_roundtrip_{dt}_{qt}_{sname}", func([t, ts], [q, t], body, "%0, %1"), [x, scale]))
+    return out
+
+
 def rng_cases():
     """stablehlo.rng_bit_generator in the forms jax.random emits under the rbg implementations: every output width, a
     Philox-shaped state of three words, and two draws chained through the state."""
@@ -1214,4 +1233,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases())
+         + fft_cases() + quantize_cases())
