@@ -9,6 +9,8 @@
 
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace mhlo {
 namespace {
 
@@ -37,21 +39,38 @@ __device__ __forceinline__ C load_as(const void* base, int dtype, int64_t off) {
     }
 }
 
-// float -> integer follows a C cast (toward zero); CUDA saturates out-of-range values and maps NaN to 0.
+// float -> integer follows a C cast (toward zero) that saturates at the ends of the result type and maps NaN to 0, for the
+// types narrower than the 64 bits CUDA converts through as well; integer -> narrower integer keeps the low bits.
+template <typename C>
+__device__ __forceinline__ int64_t to_integer(C v, int64_t lo, int64_t hi) {
+    int64_t i = static_cast<int64_t>(v);
+    if constexpr (std::is_floating_point<C>::value) i = i < lo ? lo : (i > hi ? hi : i);
+    return i;
+}
+
 template <typename C>
 __device__ __forceinline__ void store_as(void* base, int dtype, int64_t off, C v) {
+    if constexpr (std::is_floating_point<C>::value) {
+        // NaN -> 0 for every integer type (the hardware conversion gives 0 or the type's minimum depending on the widths)
+        if (v != v && dtype != MHLO_DT_F32 && dtype != MHLO_DT_F16 && dtype != MHLO_DT_BF16 && dtype != MHLO_DT_F64 && dtype != MHLO_DT_I1) v = C(0);
+    }
     switch (dtype) {
         case MHLO_DT_F32: static_cast<float*>(base)[off] = static_cast<float>(v); break;
         case MHLO_DT_F16: static_cast<__half*>(base)[off] = __float2half_rn(static_cast<float>(v)); break;
         case MHLO_DT_BF16: static_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(static_cast<float>(v)); break;
         case MHLO_DT_F64: static_cast<double*>(base)[off] = static_cast<double>(v); break;
         case MHLO_DT_I1: static_cast<uint8_t*>(base)[off] = v != C(0) ? 1 : 0; break;
-        case MHLO_DT_I8: case MHLO_DT_UI8: static_cast<int8_t*>(base)[off] = static_cast<int8_t>(static_cast<int64_t>(v)); break;
-        case MHLO_DT_I16: case MHLO_DT_UI16: static_cast<int16_t*>(base)[off] = static_cast<int16_t>(static_cast<int64_t>(v)); break;
+        case MHLO_DT_I8: static_cast<int8_t*>(base)[off] = static_cast<int8_t>(to_integer(v, -128, 127)); break;
+        case MHLO_DT_UI8: static_cast<uint8_t*>(base)[off] = static_cast<uint8_t>(to_integer(v, 0, 255)); break;
+        case MHLO_DT_I16: static_cast<int16_t*>(base)[off] = static_cast<int16_t>(to_integer(v, -32768, 32767)); break;
+        case MHLO_DT_UI16: static_cast<uint16_t*>(base)[off] = static_cast<uint16_t>(to_integer(v, 0, 65535)); break;
         case MHLO_DT_I32: static_cast<int32_t*>(base)[off] = static_cast<int32_t>(v); break;
-        case MHLO_DT_UI32: static_cast<uint32_t*>(base)[off] = static_cast<uint32_t>(static_cast<int64_t>(v)); break;
+        case MHLO_DT_UI32: static_cast<uint32_t*>(base)[off] = static_cast<uint32_t>(to_integer(v, 0, 4294967295LL)); break;
         case MHLO_DT_I64: static_cast<int64_t*>(base)[off] = static_cast<int64_t>(v); break;
-        default: static_cast<uint64_t*>(base)[off] = static_cast<uint64_t>(static_cast<int64_t>(v)); break;
+        default:
+            if constexpr (std::is_floating_point<C>::value) static_cast<uint64_t*>(base)[off] = static_cast<uint64_t>(v);  // saturates; negative and NaN -> 0
+            else static_cast<uint64_t*>(base)[off] = static_cast<uint64_t>(static_cast<int64_t>(v));
+            break;
     }
 }
 

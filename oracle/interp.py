@@ -801,7 +801,9 @@ def _float_to_int(arr, ttype):
         return arr != 0
     info = np.iinfo(dt)
     a = np.nan_to_num(np.trunc(arr), nan=0.0, posinf=float(info.max), neginf=float(info.min))
-    return np.clip(a, float(info.min), float(info.max)).astype(dt)
+    a = np.clip(a, float(info.min), float(info.max))
+    top = a >= float(info.max)  # float(info.max) is 2^63 / 2^64 for the 64-bit types: past what astype can take
+    return np.where(top, info.max, np.where(top, 0.0, a).astype(dt)).astype(dt)
 
 
 def _total_order_key(values, dtype):

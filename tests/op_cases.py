@@ -1116,6 +1116,21 @@ def custom_call_cases():
     return out
 
 
+def saturating_convert_cases():
+    """convert from floats outside the integer type's range: saturates at its ends, NaN gives 0 (the device's rule for 32 and
+    64 bits, applied to the narrower types as well)."""
+    vals = np.array([np.nan, np.inf, -np.inf, 1e30, -1e30, 300.7, -300.7, 70000.5, -70000.5, 3e9, -3e9, 1e19, 2e19, -1.5, 0.9, 127.9, -128.9, 255.5],
+                    dtype=np.float32)
+    out = []
+    for src in ("f32", "f64", "f16"):
+        with np.errstate(over="ignore"):
+            x = vals.astype(NP[src])  # the large values become inf in f16
+        for dst in ("i8", "ui8", "i16", "ui16", "i32", "ui32", "i64", "ui64"):
+            ts, td = tt(x.shape, src), tt(x.shape, dst)
+            out.append((f"convert_saturates_{src}_{dst}", func([ts], [td], f"    %0 = stablehlo.convert %arg0 : ({ts}) -> {td}", "%0"), [x]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1233,4 +1248,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases())
