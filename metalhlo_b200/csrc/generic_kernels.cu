@@ -165,7 +165,11 @@ __device__ __forceinline__ C ew_float_op(int op, C a, C b, C c, double imm) {
         case MHLO_EW_CMP_GT: return C(a > b);
         case MHLO_EW_CMP_GE: return C(a >= b);
         case MHLO_EW_SELECT: return a != C(0) ? b : c;
-        case MHLO_EW_CLAMP: { C lo = b < a ? a : b; return lo > c ? c : lo; }
+        case MHLO_EW_CLAMP: {  // minimum(maximum(operand, min), max), each of which hands a NaN on
+            if (a != a || b != b || c != c) return C(NAN);
+            C lo = b < a ? a : b;
+            return lo > c ? c : lo;
+        }
         case MHLO_EW_GELU_TANH: {
             const C inner = C(0.7978845608028654) * (a + C(0.044715) * a * a * a);
             return C(0.5) * a * (C(1) + tanh(inner));

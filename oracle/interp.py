@@ -1137,7 +1137,17 @@ class Interpreter:
                 if t.is_float or t.is_complex:
                     return a[0] / a[1]
                 q = np.where(a[1] == 0, 1, a[1])
-                r = np.trunc(a[0].astype(np.float64) / q.astype(np.float64)) if a[0].dtype.itemsize < 8 else (np.abs(a[0]) // np.abs(q)) * np.sign(a[0]) * np.sign(q)
+                if a[0].dtype.itemsize < 8:
+                    r = np.trunc(a[0].astype(np.float64) / q.astype(np.float64))
+                else:  # exact integers (|INT64_MIN| does not fit int64): truncation toward zero, wrapped to the type
+                    num, den = np.broadcast_arrays(a[0].astype(object), q.astype(object))
+                    r = np.empty(num.shape, dtype=object)
+                    for idx in np.ndindex(num.shape):
+                        n_, d_ = int(num[idx]), int(den[idx])
+                        r[idx] = abs(n_) // abs(d_) * (1 if (n_ < 0) == (d_ < 0) else -1)
+                    info = np.iinfo(a[0].dtype)
+                    span = int(info.max) - int(info.min) + 1
+                    r = np.array([((int(v) - int(info.min)) % span) + int(info.min) for v in r.reshape(-1)], dtype=a[0].dtype).reshape(num.shape)
                 return np.where(a[1] == 0, -1, r)
             if n == "remainder":
                 if t.is_float:

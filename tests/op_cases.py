@@ -1131,6 +1131,58 @@ def saturating_convert_cases():
     return out
 
 
+def special_value_cases():
+    """NaN, infinities, signed zeros, subnormals and integer extremes through the elementwise operators, compares and
+    reductions: the places where a kernel's shortcut (a maximum that drops NaN, a division that traps) shows."""
+    out = []
+    nan, inf = np.nan, np.inf
+    v = np.array([nan, inf, -inf, 0.0, -0.0, 1e-45, -1e-40, 88.8, -104.0, 0.5, -0.5, 1.5, 2.5, -2.5, 3.0, -7.25, 1e10, -1e10], dtype=np.float32)
+    t = tt(v.shape, "f32")
+    for op in ("abs", "negate", "exponential", "log", "sqrt", "rsqrt", "tanh", "logistic", "floor", "ceil", "sign", "round_nearest_even",
+               "round_nearest_afz", "exponential_minus_one", "log_plus_one", "cbrt"):
+        out.append((f"special_unary_{op}_f32", func([t], [t], f"    %0 = stablehlo.{op} %arg0 : {t}", "%0"), [v]))
+    ti = tt(v.shape, "i1")
+    out.append(("special_is_finite_f32", func([t], [ti], f"    %0 = stablehlo.is_finite %arg0 : ({t}) -> {ti}", "%0"), [v]))
+    trig = np.array([nan, inf, -inf, 0.0, -0.0, 1e-40, 0.5, -3.0, 100.0, -1000.0], dtype=np.float32)
+    tg = tt(trig.shape, "f32")
+    for op in ("sine", "cosine"):
+        out.append((f"special_unary_{op}_f32", func([tg], [tg], f"    %0 = stablehlo.{op} %arg0 : {tg}", "%0"), [trig]))
+    # every pair of a short list of specials
+    base = np.array([nan, inf, -inf, 0.0, -0.0, 1.0, -2.5, 3e38], dtype=np.float32)
+    a, b = [x.reshape(-1).copy() for x in np.meshgrid(base, base, indexing="ij")]
+    tp = tt(a.shape, "f32")
+    for op in ("add", "subtract", "multiply", "divide", "maximum", "minimum", "atan2", "power", "remainder"):
+        out.append((f"special_binary_{op}_f32", func([tp, tp], [tp], f"    %0 = stablehlo.{op} %arg0, %arg1 : {tp}", "%0"), [a, b]))
+    tpi = tt(a.shape, "i1")
+    for d in ("EQ", "NE", "LT", "LE", "GT", "GE"):
+        out.append((f"special_compare_{d}_f32", func([tp, tp], [tpi], f"    %0 = stablehlo.compare {d}, %arg0, %arg1, FLOAT : ({tp}, {tp}) -> {tpi}", "%0"), [a, b]))
+    lo, x, hi = [y.reshape(-1).copy() for y in np.meshgrid(np.array([nan, -1.0, 2.0], np.float32), base, np.array([nan, 1.0, -3.0], np.float32), indexing="ij")]
+    tc = tt(x.shape, "f32")
+    out.append(("special_clamp_f32", func([tc, tc, tc], [tc], f"    %0 = stablehlo.clamp %arg0, %arg1, %arg2 : {tc}", "%0"), [lo, x, hi]))
+    # reductions over rows that hold a NaN, both infinities, or only one of them
+    rows = np.array([[1.0, nan, 3.0, -2.0], [inf, 1.0, -inf, 0.0], [inf, 2.0, 5.0, inf], [-0.0, 0.0, -0.0, 0.0], [-inf, -inf, -1.0, -5.0]], dtype=np.float32)
+    tr, tv = tt(rows.shape, "f32"), tt((rows.shape[0],), "f32")
+    for red, init in (("add", "0.0"), ("maximum", "0xFF800000"), ("minimum", "0x7F800000"), ("multiply", "1.0")):
+        body = (f"    %c = stablehlo.constant dense<{init}> : tensor<f32>\n"
+                f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.{red} across dimensions = [1] : ({tr}, tensor<f32>) -> {tv}")
+        out.append((f"special_reduce_{red}_f32", func([tr], [tv], body, "%0"), [rows]))
+    # integers at the ends of their range
+    for dt in ("i32", "i64", "i8", "ui32"):
+        info = np.iinfo(NP[dt])
+        ends = np.array([info.min, info.max, 0, 1, 7, info.max // 3] + ([-1, -7, info.min + 1] if info.min < 0 else [2, 250, info.max - 1]), dtype=NP[dt])
+        p, q = [y.reshape(-1).copy() for y in np.meshgrid(ends, ends, indexing="ij")]
+        tq = tt(p.shape, dt)
+        for op in ("add", "subtract", "multiply", "divide", "remainder", "maximum", "minimum", "and", "or", "xor", "shift_left", "shift_right_arithmetic",
+                   "shift_right_logical"):
+            out.append((f"special_binary_{op}_{dt}", func([tq, tq], [tq], f"    %0 = stablehlo.{op} %arg0, %arg1 : {tq}", "%0"), [p, q]))
+        te = tt(ends.shape, dt)
+        for op in ("abs", "negate", "sign", "not", "popcnt", "count_leading_zeros"):
+            if info.min == 0 and op in ("abs", "negate", "sign"):
+                continue
+            out.append((f"special_unary_{op}_{dt}", func([te], [te], f"    %0 = stablehlo.{op} %arg0 : {te}", "%0"), [ends]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1248,4 +1300,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases())
