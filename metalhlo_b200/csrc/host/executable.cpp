@@ -1449,7 +1449,7 @@ class Lowering {
         if (it == modes.end()) fail_unsupported("scatter with an update computation this backend does not recognise (" + op.str_attr("reducer") + ")");
         const int mode = it->second;
         const TensorType& rt = op.result_types[0];
-        View indices = materialize(get(op.operands[1]), "scatter.indices");
+        View indices = index_view(get(op.operands[1]), "scatter.indices", true);
         View updates = materialize(get(op.operands[2]), "scatter.updates");
         View out = dense_view(new_arena(rt.bytes()), rt);
         copy_view(get(op.operands[0]), out, "scatter.operand");
@@ -1755,7 +1755,7 @@ class Lowering {
 
     void lower_gather(const Op& op) {
         View operand = materialize(get(op.operands[0]), "gather.operand");
-        View indices = materialize(get(op.operands[1]), "gather.indices");
+        View indices = index_view(get(op.operands[1]), "gather.indices", true);
         const TensorType& rt = op.result_types[0];
         mhlo_cuda_gather_dims g;
         std::memset(&g, 0, sizeof g);
@@ -1786,13 +1786,25 @@ class Lowering {
         set(op.results[0], out);
     }
 
+    // Index operands in the types the index kernels read (i32, i64; ui32 too where `ui32_ok`): any other integer type is
+    // widened to i64 by one small elementwise launch first (a ui64 index of 2^63 or more would wrap: no tensor is that long).
+    View index_view(const View& v, const std::string& why, bool ui32_ok) {
+        const DType d = v.type.dtype;
+        if (d == DType::I32 || d == DType::I64 || (ui32_ok && d == DType::UI32)) return materialize(v, why);
+        if (is_float(d)) fail_compile(why + " must be an integer tensor, not " + v.type.str());
+        TensorType wide = v.type;
+        wide.dtype = DType::I64;
+        mhlo_cuda_ew_inst widen = {MHLO_EW_COPY, 0, 0, 0, 0.0};
+        return emit_elementwise({v}, {widen}, wide, "convert(" + why + ")");
+    }
+
     void lower_dynamic_slice(const Op& op) {
         View operand = materialize(get(op.operands[0]), "dynamic_slice.operand");
         const TensorType& rt = op.result_types[0];
         std::vector<DevView> idx;
         DType idt = DType::I32;
         for (size_t i = 1; i < op.operands.size(); ++i) {
-            View iv = materialize(get(op.operands[i]), "dynamic_slice.index");
+            View iv = index_view(get(op.operands[i]), "dynamic_slice.index", false);
             idt = iv.type.dtype;
             idx.push_back(dev(iv));
             keep_alive(iv);
@@ -1821,7 +1833,7 @@ class Lowering {
         std::vector<DevView> idx;
         DType idt = DType::I32;
         for (size_t i = 2; i < op.operands.size(); ++i) {
-            View iv = materialize(get(op.operands[i]), "dynamic_update_slice.index");
+            View iv = index_view(get(op.operands[i]), "dynamic_update_slice.index", false);
             idt = iv.type.dtype;
             idx.push_back(dev(iv));
             keep_alive(iv);

@@ -322,6 +322,17 @@ def build_cases():
                                  f"    %0 = stablehlo.reshape %arg1 : ({tt((4, 7), 'i32')}) -> {tt((4, 7, 1), 'i32')}\n"
                                  f"    %1 = \"stablehlo.gather\"(%arg0, %0) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1, 24>}}> : ({tt((50, 24), 'f32')}, {tt((4, 7, 1), 'i32')}) -> {tt((4, 7, 24), 'f32')}", "%1"),
         [table, ids])
+    # token ids outside the table: start indices are clamped into it (negative ones to row 0, large ones to the last row)
+    wild = np.array([[-3, 0, 49, 50, 1000, -2147483648, 2147483647]], dtype=np.int32)
+    add("gather_embedding_ids_out_of_range", func([tt((50, 24), "f32"), tt((1, 7), "i32")], [tt((1, 7, 24), "f32")],
+                                                  f"    %0 = stablehlo.reshape %arg1 : ({tt((1, 7), 'i32')}) -> {tt((1, 7, 1), 'i32')}\n"
+                                                  f"    %1 = \"stablehlo.gather\"(%arg0, %0) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1, 24>}}> : ({tt((50, 24), 'f32')}, {tt((1, 7, 1), 'i32')}) -> {tt((1, 7, 24), 'f32')}", "%1"),
+        [table, wild])
+    for it, arr in (("ui8", np.array([[0, 49, 7, 200, 255]], np.uint8)), ("i16", np.array([[-5, 3, 49, 32767, -32768]], np.int16))):
+        add(f"gather_embedding_{it}_ids", func([tt((50, 24), "f32"), tt((1, 5), it)], [tt((1, 5, 24), "f32")],
+                                              f"    %0 = stablehlo.reshape %arg1 : ({tt((1, 5), it)}) -> {tt((1, 5, 1), it)}\n"
+                                              f"    %1 = \"stablehlo.gather\"(%arg0, %0) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1, 24>}}> : ({tt((50, 24), 'f32')}, {tt((1, 5, 1), it)}) -> {tt((1, 5, 24), 'f32')}", "%1"),
+            [table, arr])
     op3 = rand(rng, (3, 4, 6), "i32")
     idx = np.array([[[0, 0], [1, 0], [2, 1]], [[0, 1], [1, 1], [0, 9]]], dtype=np.int64)
     add("gather_window", func([tt((3, 4, 6), "i32"), tt((2, 3, 2), "i64")], [tt((2, 3, 2, 3), "i32")],
@@ -335,6 +346,14 @@ def build_cases():
     add("dynamic_update_slice", func([tt((6, 8), "f32"), tt((2, 3), "f32"), tt((), "i32"), tt((), "i32")], [tt((6, 8), "f32")],
                                      f"    %0 = stablehlo.dynamic_update_slice %arg0, %arg1, %arg2, %arg3 : ({tt((6, 8), 'f32')}, {tt((2, 3), 'f32')}, tensor<i32>, tensor<i32>) -> {tt((6, 8), 'f32')}", "%0"),
         [xd, rand(rng, (2, 3), "f32"), np.array(1, np.int32), np.array(7, np.int32)])
+    for nm, s0, s1, it in (("negative_starts", -4, -1, "i32"), ("far_starts_i64", 2 ** 40, -2 ** 40, "i64"), ("ui8_starts", 200, 3, "ui8")):
+        ti_ = f"tensor<{it}>"
+        add(f"dynamic_slice_{nm}", func([tt((6, 8), "f32"), tt((), it), tt((), it)], [tt((2, 3), "f32")],
+                                        f"    %0 = stablehlo.dynamic_slice %arg0, %arg1, %arg2, sizes = [2, 3] : ({tt((6, 8), 'f32')}, {ti_}, {ti_}) -> {tt((2, 3), 'f32')}", "%0"),
+            [xd, np.array(s0, NP[it]), np.array(s1, NP[it])])
+        add(f"dynamic_update_slice_{nm}", func([tt((6, 8), "f32"), tt((2, 3), "f32"), tt((), it), tt((), it)], [tt((6, 8), "f32")],
+                                               f"    %0 = stablehlo.dynamic_update_slice %arg0, %arg1, %arg2, %arg3 : ({tt((6, 8), 'f32')}, {tt((2, 3), 'f32')}, {ti_}, {ti_}) -> {tt((6, 8), 'f32')}", "%0"),
+            [xd, rand(rng, (2, 3), "f32"), np.array(s0, NP[it]), np.array(s1, NP[it])])
     # ---- fusable patterns (unfused text; O3 must agree with O0)
     for dt in ("f32", "f16", "bf16"):
         if dt not in NP:
