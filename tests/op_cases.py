@@ -1202,6 +1202,76 @@ def special_value_cases():
     return out
 
 
+def more_edge_cases():
+    """Special values in the 16-bit and 64-bit float types, integer compares at the ends of the range, reductions of
+    integers that wrap, and tensors with no elements, no dimensions or many dimensions."""
+    out = []
+    nan, inf = np.nan, np.inf
+    for dt in ("f16", "bf16", "f64"):
+        if dt not in NP:
+            continue
+        big = {"f16": 60000.0, "bf16": 3e38, "f64": 1e308}[dt]
+        with np.errstate(over="ignore"):
+            base = np.array([nan, inf, -inf, 0.0, -0.0, 1.0, -2.5, big, -big, 6e-8], dtype=np.float64).astype(NP[dt])
+        a, b = [x.reshape(-1).copy() for x in np.meshgrid(base, base, indexing="ij")]
+        tp, tpi = tt(a.shape, dt), tt(a.shape, "i1")
+        for op in ("add", "subtract", "multiply", "divide", "maximum", "minimum"):
+            out.append((f"special_binary_{op}_{dt}", func([tp, tp], [tp], f"    %0 = stablehlo.{op} %arg0, %arg1 : {tp}", "%0"), [a, b]))
+        for d in ("EQ", "LT", "GE"):
+            out.append((f"special_compare_{d}_{dt}", func([tp, tp], [tpi], f"    %0 = stablehlo.compare {d}, %arg0, %arg1, FLOAT : ({tp}, {tp}) -> {tpi}", "%0"), [a, b]))
+        tb = tt(base.shape, dt)
+        for op in ("abs", "negate", "sqrt", "exponential", "floor", "sign", "tanh"):
+            out.append((f"special_unary_{op}_{dt}", func([tb], [tb], f"    %0 = stablehlo.{op} %arg0 : {tb}", "%0"), [base]))
+    for dt, ctype in (("i32", "SIGNED"), ("ui32", "UNSIGNED"), ("i64", "SIGNED"), ("ui64", "UNSIGNED"), ("i8", "SIGNED"), ("ui8", "UNSIGNED")):
+        info = np.iinfo(NP[dt])
+        ends = np.array([info.min, info.max, 0, 1, info.max // 2, info.max // 2 + 1, info.max - 1] + ([-1, info.min + 1] if info.min < 0 else [2, 3]), dtype=NP[dt])
+        p_, q_ = [y.reshape(-1).copy() for y in np.meshgrid(ends, ends, indexing="ij")]
+        tq, tqi = tt(p_.shape, dt), tt(p_.shape, "i1")
+        for d in ("EQ", "NE", "LT", "LE", "GT", "GE"):
+            out.append((f"special_compare_{d}_{dt}", func([tq, tq], [tqi], f"    %0 = stablehlo.compare {d}, %arg0, %arg1, {ctype} : ({tq}, {tq}) -> {tqi}", "%0"), [p_, q_]))
+        rows = np.stack([ends, ends[::-1], np.full_like(ends, info.max), np.full_like(ends, info.min)])
+        tr, tv = tt(rows.shape, dt), tt((rows.shape[0],), dt)
+        for red, init in (("add", "0"), ("multiply", "1"), ("maximum", str(info.min)), ("minimum", str(info.max))):
+            if dt == "ui64" and red in ("maximum", "minimum"):
+                continue  # refused by the lowering (64-bit unsigned order)
+            body = (f"    %c = stablehlo.constant dense<{init}> : tensor<{dt}>\n"
+                    f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.{red} across dimensions = [1] : ({tr}, tensor<{dt}>) -> {tv}")
+            out.append((f"special_reduce_{red}_{dt}", func([tr], [tv], body, "%0"), [rows]))
+    # tensors with no elements, scalars, and rank 6
+    rng = np.random.default_rng(4242)
+    e0, e1 = tt((0, 5), "f32"), tt((3, 0), "f32")
+    out.append(("empty_add", func([e0, e0], [e0], f"    %0 = stablehlo.add %arg0, %arg1 : {e0}", "%0"), [np.zeros((0, 5), np.float32)] * 2))
+    out.append(("empty_reduce_to_init", func([e1], [tt((3,), "f32")],
+                                             f"    %c = stablehlo.constant dense<7.0> : tensor<f32>\n"
+                                             f"    %0 = stablehlo.reduce(%arg0 init: %c) applies stablehlo.add across dimensions = [1] : ({e1}, tensor<f32>) -> {tt((3,), 'f32')}", "%0"),
+                [np.zeros((3, 0), np.float32)]))
+    out.append(("empty_contraction", func([tt((4, 0), "f32"), tt((0, 6), "f32")], [tt((4, 6), "f32")],
+                                          f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [1] x [0] : ({tt((4, 0), 'f32')}, {tt((0, 6), 'f32')}) -> {tt((4, 6), 'f32')}", "%0"),
+                [np.zeros((4, 0), np.float32), np.zeros((0, 6), np.float32)]))
+    out.append(("empty_concatenate", func([e0, tt((2, 5), "f32")], [tt((2, 5), "f32")],
+                                          f"    %0 = stablehlo.concatenate %arg0, %arg1, dim = 0 : ({e0}, {tt((2, 5), 'f32')}) -> {tt((2, 5), 'f32')}", "%0"),
+                [np.zeros((0, 5), np.float32), rand(rng, (2, 5), "f32")]))
+    out.append(("empty_transpose_and_broadcast", func([e1], [tt((2, 0, 3), "f32")],
+                                                      f"    %0 = stablehlo.transpose %arg0, dims = [1, 0] : ({e1}) -> {tt((0, 3), 'f32')}\n"
+                                                      f"    %1 = stablehlo.broadcast_in_dim %0, dims = [1, 2] : ({tt((0, 3), 'f32')}) -> {tt((2, 0, 3), 'f32')}", "%1"),
+                [np.zeros((3, 0), np.float32)]))
+    s0 = tt((), "f32")
+    out.append(("scalar_chain", func([s0, s0], [s0, tt((), "i1")],
+                                     f"    %0 = stablehlo.multiply %arg0, %arg1 : {s0}\n    %1 = stablehlo.tanh %0 : {s0}\n"
+                                     f"    %2 = stablehlo.compare GT, %1, %arg1, FLOAT : ({s0}, {s0}) -> tensor<i1>", "%1, %2"),
+                [np.array(0.7, np.float32), np.array(-1.3, np.float32)]))
+    sh6 = (2, 3, 1, 4, 2, 5)
+    t6 = tt(sh6, "f32")
+    p6 = [5, 0, 3, 1, 4, 2]
+    o6 = tuple(sh6[i] for i in p6)
+    body = (f"    %0 = stablehlo.transpose %arg0, dims = {p6} : ({t6}) -> {tt(o6, 'f32')}\n"
+            f"    %c = stablehlo.constant dense<0.0> : tensor<f32>\n"
+            f"    %1 = stablehlo.reduce(%0 init: %c) applies stablehlo.add across dimensions = [1, 4] : ({tt(o6, 'f32')}, tensor<f32>) -> {tt((5, 4, 3, 1), 'f32')}\n"
+            f"    %2 = stablehlo.reverse %1, dims = [0, 2] : {tt((5, 4, 3, 1), 'f32')}")
+    out.append(("rank6_transpose_reduce_reverse", func([t6], [tt((5, 4, 3, 1), "f32")], body, "%2"), [rand(rng, sh6, "f32")]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1319,4 +1389,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases())
