@@ -1272,6 +1272,55 @@ def more_edge_cases():
     return out
 
 
+def fused_pattern_edge_cases():
+    """The fusable patterns on rows that stress their kernels: masked (-inf) and constant softmax rows, single-element rows,
+    constant and zero rows under the norms, activations far out on both sides."""
+    out = []
+    inf = np.inf
+    for dt in ("f32", "f16", "bf16"):
+        if dt not in NP:
+            continue
+        hid = 64
+        rows = np.zeros((8, hid), np.float32)
+        rng = np.random.default_rng(77)
+        rows[0] = rng.standard_normal(hid)
+        rows[1] = 3.25                                   # constant row: uniform probabilities, zero variance
+        rows[2] = rng.standard_normal(hid); rows[2, 10:] = -inf   # masked tail
+        rows[3] = -inf; rows[3, 5] = 0.0                 # one visible entry
+        rows[4] = rng.standard_normal(hid) * 30.0        # wide range: the maximum must be subtracted
+        rows[5] = 0.0
+        rows[6] = np.linspace(-60, 60, hid)
+        rows[7] = 1e4 if dt != "f16" else 6e4            # large constant
+        x = rows.astype(NP[dt])
+        shape = x.shape
+        t = tt(shape, dt)
+        body, res = softmax_text("%arg0", shape, dt, 1)
+        out.append((f"edge_softmax_rows_{dt}", func([t], [t], body.rstrip("\n"), res), [x]))
+        fin = np.where(np.isfinite(rows), rows, 0.0).astype(np.float32)
+        fin[7] = 100.0
+        if dt == "f16":  # the unfused program sums the squares in f16: keep a row's sum below 65504
+            fin[4] /= 3.0
+            fin[6] /= 3.0
+            fin[7] = 25.0
+        xf = fin.astype(NP[dt])
+        g = np.linspace(0.5, 1.5, hid).astype(np.float32).astype(NP[dt])
+        b = np.linspace(-0.2, 0.2, hid).astype(np.float32).astype(NP[dt])
+        tv = tt((hid,), dt)
+        body, res = layer_norm_text("%arg0", shape, dt, "%arg1", "%arg2")
+        out.append((f"edge_layer_norm_rows_{dt}", func([t, tv, tv], [t], body.rstrip("\n"), res), [xf, g, b]))
+        body, res = layer_norm_text("%arg0", shape, dt, "%arg1", None, eps=1e-6, rms=True)
+        out.append((f"edge_rms_norm_rows_{dt}", func([t, tv], [t], body.rstrip("\n"), res), [xf, g]))
+        far = np.array([[-100.0, -20.0, -9.0, -5.0, -1.0, -1e-3, 0.0, -0.0, 1e-3, 1.0, 5.0, 9.0, 20.0, 100.0, 3.0, -3.0]], np.float32).astype(NP[dt])
+        tf_ = tt(far.shape, dt)
+        body, res = gelu_text("%arg0", far.shape, dt)
+        out.append((f"edge_gelu_far_{dt}", func([tf_], [tf_], body.rstrip("\n"), res), [far]))
+        one = rng.standard_normal((5, 1)).astype(np.float32).astype(NP[dt])
+        t1 = tt((5, 1), dt)
+        body, res = softmax_text("%arg0", (5, 1), dt, 1)
+        out.append((f"edge_softmax_single_element_rows_{dt}", func([t1], [t1], body.rstrip("\n"), res), [one]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1389,4 +1438,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases())
