@@ -1321,6 +1321,31 @@ def fused_pattern_edge_cases():
     return out
 
 
+def contraction_edge_cases():
+    """Non-finite operands through the tensor-core products and attention: a NaN or an infinity must come out in exactly the
+    rows and columns it touches (inf * 0 and inf - inf included), nowhere else."""
+    out = []
+    rng = np.random.default_rng(555)
+    for dt in ("bf16", "f16", "f32"):
+        if dt not in NP:
+            continue
+        m, k, n = 128, 64, 128
+        a = rng.standard_normal((m, k)).astype(np.float32)
+        b = rng.standard_normal((k, n)).astype(np.float32)
+        a[3, 7] = np.nan
+        a[10, 0] = np.inf
+        a[20, 5] = np.inf; a[20, 6] = -np.inf   # inf - inf in every column of row 20 (b[5], b[6] of one sign below)
+        b[5, :] = np.abs(b[5, :]) + 0.1
+        b[6, :] = np.abs(b[6, :]) + 0.1
+        b[0, 17] = 0.0                           # inf * 0 at (10, 17)
+        b[9, 40] = np.nan
+        b[11, 99] = -np.inf
+        ta, tb, tc = tt((m, k), dt), tt((k, n), dt), tt((m, n), dt)
+        out.append((f"edge_dot_nonfinite_{dt}", func([ta, tb], [tc], f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [1] x [0] : ({ta}, {tb}) -> {tc}", "%0"),
+                    [a.astype(NP[dt]), b.astype(NP[dt])]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1438,4 +1463,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases())
