@@ -1346,6 +1346,35 @@ def contraction_edge_cases():
     return out
 
 
+def window_sort_edge_cases():
+    """Pooling windows that hold a NaN, an infinity or only padding; sorts of keys with ties, NaNs and signed zeros."""
+    out = []
+    rng = np.random.default_rng(8080)
+    for dt in ("f32", "bf16"):
+        if dt not in NP:
+            continue
+        x = rand(rng, (1, 6, 6, 8), dt).astype(np.float32)
+        x[0, 0, 0, :] = np.nan
+        x[0, 2, 3, 1] = np.inf
+        x[0, 4, 4, 2] = -np.inf
+        x[0, 5, :, 3] = 0.25   # ties along a window
+        x = x.astype(NP[dt])
+        out.append(reduce_window_case(f"edge_maxpool_nonfinite_{dt}", x, dt, "maximum", "-inf", (1, 3, 3, 1), (1, 3, 3, 8), strides=(1, 2, 2, 1),
+                                      padding=((0, 0), (1, 0), (1, 0), (0, 0))))
+        out.append(reduce_window_case(f"edge_minpool_nonfinite_{dt}", x, dt, "minimum", "inf", (1, 2, 2, 1), (1, 3, 3, 8), strides=(1, 2, 2, 1)))
+        out.append(reduce_window_case(f"edge_sumpool_nonfinite_{dt}", x, dt, "add", 0, (1, 2, 2, 1), (1, 5, 5, 8)))
+    # a window that lies in the padding alone gives the init value
+    out.append(reduce_window_case("edge_window_in_padding_only", rand(rng, (4, 4), "f32"), "f32", "maximum", "-inf", (2, 2), (4, 4),
+                                  strides=(2, 2), padding=((2, 2), (2, 2))))
+    keys = np.array([[3.0, np.nan, -0.0, 0.0, 3.0, -np.inf, np.inf, 1.0, -np.nan, 1.0, 0.0, -0.0]], dtype=np.float32)
+    pay = np.arange(keys.size, dtype=np.int32).reshape(keys.shape)
+    out.append(sort_case("edge_sort_ties_nan_zeros_asc", [keys, pay], ["f32", "i32"], 1))
+    out.append(sort_case("edge_sort_ties_nan_zeros_desc", [keys, pay], ["f32", "i32"], 1, direction="GT"))
+    ik = np.array([[5, -7, 5, 2147483647, -2147483648, 0, -7, 5]], dtype=np.int32)
+    out.append(sort_case("edge_sort_int_ties_stable", [ik, np.arange(8, dtype=np.int32).reshape(1, 8)], ["i32", "i32"], 1))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1463,4 +1492,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases() + window_sort_edge_cases())
