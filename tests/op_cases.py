@@ -1343,6 +1343,25 @@ def contraction_edge_cases():
         ta, tb, tc = tt((m, k), dt), tt((k, n), dt), tt((m, n), dt)
         out.append((f"edge_dot_nonfinite_{dt}", func([ta, tb], [tc], f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [1] x [0] : ({ta}, {tb}) -> {tc}", "%0"),
                     [a.astype(NP[dt]), b.astype(NP[dt])]))
+    # bias + GELU in the product's epilogue with pre-activations far out on both sides (the 16-bit epilogue evaluates the
+    # tanh form two values at a time in f16 arithmetic)
+    for dt in ("f16", "bf16"):
+        if dt not in NP:
+            continue
+        m, k, n = 128, 64, 128
+        x = np.zeros((m, k), np.float32)
+        x[:, 0] = np.linspace(-300, 300, m)
+        x[:, 1:] = 0.05 * rng.standard_normal((m, k - 1))
+        w = np.zeros((k, n), np.float32)
+        w[0, :] = np.linspace(0.01, 1.0, n)
+        w[1:, :] = 0.1 * rng.standard_normal((k - 1, n))
+        bias = np.linspace(-2, 2, n).astype(np.float32)
+        tx, tw, tb_, ty = tt((m, k), dt), tt((k, n), dt), tt((n,), dt), tt((m, n), dt)
+        gb, gres = gelu_text("%2", (m, n), dt)
+        body = (f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [1] x [0] : ({tx}, {tw}) -> {ty}\n"
+                f"    %1 = stablehlo.broadcast_in_dim %arg2, dims = [1] : ({tb_}) -> {ty}\n"
+                f"    %2 = stablehlo.add %0, %1 : {ty}\n" + gb)
+        out.append((f"edge_dense_gelu_far_{dt}", func([tx, tw, tb_], [ty], body.rstrip("\n"), gres), [x.astype(NP[dt]), w.astype(NP[dt]), bias.astype(NP[dt])]))
     return out
 
 
