@@ -59,10 +59,11 @@ def test_bshd_layout_is_read_and_written_in_place(causal):
     assert_close(to_np(got), reference(q, k, v, 0.125, causal, "BSHD"), 2e-2, "BSHD")
 
 
-def test_large_scores_trigger_rescaling():
+@pytest.mark.parametrize("d", [64, 128])
+def test_large_scores_trigger_rescaling(d):
     """Growing maxima along the key axis force the lazy rescale of the TMEM accumulator many times."""
     cuda = cuda_mod()
-    b, h, s, d = 1, 2, 512, 128
+    b, h, s = 1, 2, 512
     g = torch.Generator().manual_seed(3)
     q = torch.randn(b, h, s, d, generator=g)
     k = torch.randn(b, h, s, d, generator=g) * torch.linspace(0.2, 3.0, s).view(1, 1, s, 1)
@@ -73,16 +74,19 @@ def test_large_scores_trigger_rescaling():
     assert_close(to_np(got), reference(q, k, v, 0.5, False, "BHSD"), 2e-2, "rescale")
 
 
+@pytest.mark.parametrize("jump", [640, 704, 736])
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
-def test_scores_growing_past_the_carried_reference(dtype):
-    """After a tile's first key block the kernel exponentiates against the maximum carried over from earlier blocks and
-    falls back to a fresh maximum when a row sum reaches 2^15. Keys whose norm jumps by 40x half way force that fallback
-    (and, for f16, would overflow the probabilities without it)."""
+def test_scores_growing_past_the_carried_reference(dtype, d, jump):
+    """After a tile's first key block the kernel works against the maximum carried over from earlier blocks and moves it
+    when a block (head dim 128: by its row sums; head dim 64: a 64-key chunk by its own maximum) would leave the range of
+    the 16-bit probabilities. Keys whose norm jumps by 40x force that: at a block boundary (640), in the middle of a block
+    (704: the block's first chunk of probabilities, already written, has to be scaled down too) and inside a chunk (736)."""
     cuda = cuda_mod()
-    b, h, s, d = 1, 2, 1024, 128
+    b, h, s = 1, 2, 1024
     g = torch.Generator().manual_seed(5)
     q = torch.randn(b, h, s, d, generator=g)
-    gain = torch.where(torch.arange(s) < 640, 0.05, 2.0).view(1, 1, s, 1)
+    gain = torch.where(torch.arange(s) < jump, 0.05, 2.0).view(1, 1, s, 1)
     k = torch.randn(b, h, s, d, generator=g) * gain
     v = torch.randn(b, h, s, d, generator=g)
     q, k, v = (t.to(dtype) for t in (q, k, v))
