@@ -214,8 +214,8 @@ bool algebraic_simplify(Function& f, int max_iters) {
                         case MHLO_EW_SUB: v = a - b; break;
                         case MHLO_EW_MUL: v = a * b; break;
                         case MHLO_EW_DIV: v = a / b; break;
-                        case MHLO_EW_MAX: v = std::fmax(a, b); break;
-                        case MHLO_EW_MIN: v = std::fmin(a, b); break;
+                        case MHLO_EW_MAX: v = (a != a || b != b) ? std::nan("") : std::fmax(a, b); break;  // a NaN goes through, as in the kernels
+                        case MHLO_EW_MIN: v = (a != a || b != b) ? std::nan("") : std::fmin(a, b); break;
                         case MHLO_EW_NEG: v = -a; break;
                         case MHLO_EW_SQRT: v = std::sqrt(a); break;
                         case MHLO_EW_RSQRT: v = 1.0 / std::sqrt(a); break;

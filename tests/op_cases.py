@@ -1394,6 +1394,97 @@ def window_sort_edge_cases():
     return out
 
 
+def random_program_cases(count=60, seed=20260101, dt="f32"):
+    """Seeded random programs of 12 to 24 operations (elementwise chains, compares and selects, reductions broadcast back,
+    transposes, reshapes, slices, concatenations): what the optimisation levels do to a program nobody wrote by hand must not
+    change its result."""
+    rng = np.random.default_rng(seed)
+    out = []
+    integer = dt != "f32"
+    unary = ["abs", "negate", "not", "sign", "popcnt"] if integer else ["abs", "negate", "tanh", "logistic", "floor", "ceil", "sine", "cosine", "sign", "round_nearest_even"]
+    binary = ["add", "subtract", "multiply", "maximum", "minimum", "and", "or", "xor"] if integer else ["add", "subtract", "multiply", "maximum", "minimum"]
+    ctype = "SIGNED" if integer else "FLOAT"
+    info = np.iinfo(NP[dt]) if integer else None
+    for case in range(count):
+        shape = tuple(int(x) for x in rng.choice([2, 3, 4, 5, 6, 8], size=3))
+        n_in = int(rng.integers(1, 4))
+        vals = [(f"%arg{i}", shape) for i in range(n_in)]  # (name, shape), all f32
+        lines = []
+
+        def emit(text, shp):
+            name = f"%v{len(lines)}"
+            lines.append(f"    {name} = {text}")
+            vals.append((name, shp))
+            return name
+
+        def pick(shp=None):
+            cands = [v for v in vals if shp is None or v[1] == shp]
+            return cands[int(rng.integers(0, len(cands)))]
+
+        for _ in range(int(rng.integers(12, 25))):
+            kind = rng.choice(["unary", "binary", "binary", "select", "reduce", "transpose", "reshape", "slice", "concat", "safe"])
+            a, shp = pick()
+            t = tt(shp, dt)
+            if kind == "unary":
+                emit(f"stablehlo.{rng.choice(unary)} {a} : {t}", shp)
+            elif kind == "binary":
+                b, _ = pick(shp)
+                emit(f"stablehlo.{rng.choice(binary)} {a}, {b} : {t}", shp)
+            elif kind == "safe":  # divide / sqrt / log on arguments kept away from their singularities
+                b, _ = pick(shp)
+                one = emit(f"stablehlo.constant dense<{'3' if integer else '1.5'}> : {t}", shp)
+                den = emit(f"stablehlo.add {emit(f'stablehlo.abs {b} : {t}', shp)}, {one} : {t}", shp)
+                op = "divide" if integer else str(rng.choice(["divide", "sqrt", "log", "rsqrt"]))
+                if integer:  # |b| + 3 wraps to a negative number only for b near the ends: keep it positive with a mask
+                    den = emit(f"stablehlo.or {emit(f'stablehlo.and {den}, {emit(f"stablehlo.constant dense<1023> : {t}", shp)} : {t}', shp)}, {one} : {t}", shp)
+                emit(f"stablehlo.divide {a}, {den} : {t}" if op == "divide" else f"stablehlo.{op} {den} : {t}", shp)
+            elif kind == "select":
+                b, _ = pick(shp)
+                c, _ = pick(shp)
+                d = str(rng.choice(["LT", "GE", "EQ", "NE"]))
+                p = emit(f"stablehlo.compare {d}, {a}, {b}, {ctype} : ({t}, {t}) -> {tt(shp, 'i1')}", shp)
+                vals.pop()  # predicates are not operands of the float ops
+                emit(f"stablehlo.select {p}, {b}, {c} : {tt(shp, 'i1')}, {t}", shp)
+            elif kind == "reduce" and len(shp) >= 2:
+                ax = int(rng.integers(0, len(shp)))
+                red = str(rng.choice(["add", "maximum", "minimum"]))
+                init = {"add": "0", "maximum": str(info.min), "minimum": str(info.max)}[red] if integer else {"add": "0.0", "maximum": "0xFF800000", "minimum": "0x7F800000"}[red]
+                rs = tuple(d for i, d in enumerate(shp) if i != ax)
+                c0 = emit(f"stablehlo.constant dense<{init}> : tensor<{dt}>", ())
+                vals.pop()
+                r = emit(f"stablehlo.reduce({a} init: {c0}) applies stablehlo.{red} across dimensions = [{ax}] : ({t}, tensor<{dt}>) -> {tt(rs, dt)}", rs)
+                vals.pop()
+                dims = [i for i in range(len(shp)) if i != ax]
+                emit(f"stablehlo.broadcast_in_dim {r}, dims = {dims} : ({tt(rs, dt)}) -> {t}", shp)
+            elif kind == "transpose" and len(shp) >= 2:
+                perm = [int(x) for x in rng.permutation(len(shp))]
+                emit(f"stablehlo.transpose {a}, dims = {perm} : ({t}) -> {tt(tuple(shp[i] for i in perm), dt)}", tuple(shp[i] for i in perm))
+            elif kind == "reshape":
+                total = int(np.prod(shp))
+                facts = [d for d in (2, 3, 4, 5, 6, 8) if total % d == 0] or [1]
+                d0 = int(rng.choice(facts))
+                ns = (d0, total // d0)
+                emit(f"stablehlo.reshape {a} : ({t}) -> {tt(ns, dt)}", ns)
+            elif kind == "slice" and all(d >= 2 for d in shp):
+                lo = [int(rng.integers(0, d // 2)) for d in shp]
+                hi = [int(rng.integers(l + 1, d + 1)) for l, d in zip(lo, shp)]
+                st = [int(rng.integers(1, 3)) for _ in shp]
+                ns = tuple((h - l + s_ - 1) // s_ for l, h, s_ in zip(lo, hi, st))
+                spec = ", ".join(f"{l}:{h}:{s_}" for l, h, s_ in zip(lo, hi, st))
+                emit(f"stablehlo.slice {a} [{spec}] : ({t}) -> {tt(ns, dt)}", ns)
+            elif kind == "concat":
+                b, _ = pick(shp)
+                ax = int(rng.integers(0, len(shp)))
+                ns = tuple(d * 2 if i == ax else d for i, d in enumerate(shp))
+                emit(f"stablehlo.concatenate {a}, {b}, dim = {ax} : ({t}, {t}) -> {tt(ns, dt)}", ns)
+        if not lines:
+            continue
+        results = [vals[-1]] + ([vals[-3]] if len(vals) > n_in + 3 else [])
+        text = func([tt(shape, dt)] * n_in, [tt(r[1], dt) for r in results], "\n".join(lines), ", ".join(r[0] for r in results))
+        out.append((f"random_program_{dt}_{case:02d}", text, [rand(rng, shape, dt) for _ in range(n_in)]))
+    return out
+
+
 def quantize_cases():
     """uniform_quantize / uniform_dequantize in the reference's two-operand form (scale as a tensor operand)."""
     rng = np.random.default_rng(909)
@@ -1511,4 +1602,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases() + window_sort_edge_cases())
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases() + window_sort_edge_cases() + random_program_cases() + random_program_cases(count=40, seed=77, dt="i32"))
