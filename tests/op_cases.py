@@ -8,6 +8,7 @@ numpy oracle (oracle/interp.py); the CPU tests run the oracle and the host-side 
 from __future__ import annotations
 
 import math
+import re
 
 import numpy as np
 
@@ -1394,6 +1395,57 @@ def window_sort_edge_cases():
     return out
 
 
+def shared_intermediate_cases():
+    """The fusable patterns with a second reader on one of their inner values: the fusion has to leave that value alive
+    (or not fire), whatever the level."""
+    out = []
+    rng = np.random.default_rng(3131)
+    for dt in ("f32", "bf16"):
+        if dt not in NP:
+            continue
+        shape = (4, 24, 64)
+        t, red = tt(shape, dt), tt(shape[:-1], dt)
+        x = rand(rng, shape, dt)
+        g = (1 + 0.1 * rng.standard_normal(64)).astype(np.float32).astype(NP[dt])
+        b = (0.1 * rng.standard_normal(64)).astype(np.float32).astype(NP[dt])
+        tv = tt((64,), dt)
+        body, res = softmax_text("%arg0", shape, dt, 2)
+        for extra, et in (("%s3", t), ("%s0", red), ("%s4", red)):   # exp(x - max), the row maximum, the row sum
+            out.append((f"shared_softmax_{extra[1:]}_{dt}", func([t], [t, et], body.rstrip("\n"), f"{res}, {extra}"), [x]))
+        body, res = layer_norm_text("%arg0", shape, dt, "%arg1", "%arg2")
+        for extra, et in (("%n1", red), ("%n3", t), ("%n8", red), ("%n10", t)):   # mean, centred value, rsqrt, normalised value
+            out.append((f"shared_layer_norm_{extra[1:]}_{dt}", func([t, tv, tv], [t, et], body.rstrip("\n"), f"{res}, {extra}"), [x, g, b]))
+        body, res = gelu_text("%arg0", shape, dt)
+        for extra in ("%g5", "%g3"):   # tanh(...), the cubic
+            out.append((f"shared_gelu_{extra[1:]}_{dt}", func([t], [t, t], body.rstrip("\n"), f"{res}, {extra}"), [x]))
+        # dense + bias + gelu with the pre-activation read again; residual + norm with the sum and the variance read again
+        w = (rng.standard_normal((64, 128)) / 8).astype(np.float32).astype(NP[dt])
+        bias = (0.1 * rng.standard_normal(128)).astype(np.float32).astype(NP[dt])
+        ts, tw, tb_ = tt((4, 24, 128), dt), tt((64, 128), dt), tt((128,), dt)
+        gb, gres = gelu_text("%2", (4, 24, 128), dt)
+        body = (f"    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [2] x [0] : ({t}, {tw}) -> {ts}\n"
+                f"    %1 = stablehlo.broadcast_in_dim %arg2, dims = [2] : ({tb_}) -> {ts}\n"
+                f"    %2 = stablehlo.add %0, %1 : {ts}\n" + gb)
+        out.append((f"shared_dense_preactivation_{dt}", func([t, tw, tb_], [ts, ts, ts], body.rstrip("\n"), f"{gres}, %2, %0"), [x, w, bias]))
+        xr = rand(rng, shape, dt)
+        lb, lres = layer_norm_text("%s0", shape, dt, "%arg2", "%arg3")
+        body = f"    %s0 = stablehlo.add %arg0, %arg1 : {t}\n" + lb
+        out.append((f"shared_residual_norm_variance_{dt}", func([t, t, tv, tv], [t, t, red], body.rstrip("\n"), f"{lres}, %s0, %n6"), [x, xr, g, b]))
+    for dt in ("f32",):  # (16-bit attention outputs need the magnitude bound the pattern_attention cases get)
+        for causal in (False, True):
+            text, qshape = attention_text(2, 2, 32, 32, dt, causal, "BHSD")
+            # also return the scaled scores (%1): the fused attention never materialises them
+            q, k, v = (rand(rng, qshape, dt) for _ in range(3))
+            m = re.search(r"return (%\w+) : (tensor<[^>]*>)", text)
+            if not m:
+                continue
+            ts_ = tt((2, 2, 32, 32), dt)
+            text2 = text.replace(m.group(0), f"return {m.group(1)}, %1 : {m.group(2)}, {ts_}")
+            text2 = re.sub(r"-> \(?(tensor<[^>]*>)\)? \{", lambda mm: f"-> ({mm.group(1)}, {ts_}) {{", text2, count=1)
+            out.append((f"shared_attention_scores_{'causal_' if causal else ''}{dt}", text2, [q, k, v]))
+    return out
+
+
 def random_program_cases(count=60, seed=20260101, dt="f32"):
     """Seeded random programs of 12 to 24 operations (elementwise chains, compares and selects, reductions broadcast back,
     transposes, reshapes, slices, concatenations): what the optimisation levels do to a program nobody wrote by hand must not
@@ -1602,4 +1654,4 @@ def fft_cases():
 
 
 CASES = (build_cases() + widening_cases() + window_scatter_sort_cases() + convolution_cases() + linalg_cases() + custom_call_cases() + rng_cases()
-         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases() + window_sort_edge_cases() + random_program_cases() + random_program_cases(count=40, seed=77, dt="i32"))
+         + fft_cases() + quantize_cases() + saturating_convert_cases() + special_value_cases() + more_edge_cases() + fused_pattern_edge_cases() + contraction_edge_cases() + window_sort_edge_cases() + shared_intermediate_cases() + random_program_cases() + random_program_cases(count=40, seed=77, dt="i32"))
