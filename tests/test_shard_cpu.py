@@ -143,3 +143,25 @@ def test_batch_that_does_not_divide_and_bad_indices():
         capi.shard_text(text, 2, 2)
     assert capi.shard_text(text, 1, 0, n_inputs=1, n_outputs=1)[1:] == ([-1], [-1])  # one shard: nothing is split
     assert capi.shard_text(text, 3, 2, n_inputs=1, n_outputs=1)[1:] == ([0], [0])
+
+
+@pytest.mark.parametrize("dt", ["f32", "i32"])
+def test_random_programs_split_soundly_or_are_refused(dt):
+    """Seeded random programs (tests/op_cases.py): whenever the analysis accepts a split, the shards evaluated on their own
+    slices concatenate to the unsharded result; whatever it does not accept is refused with MHLO_ERROR_UNSUPPORTED_OP."""
+    import op_cases
+
+    accepted = refused = 0
+    for name, text, ins in op_cases.random_program_cases(count=80, seed=4321, dt=dt):
+        for count in (2, 3):
+            if ins[0].shape[0] % count:
+                continue
+            try:
+                capi.shard_text(text, count, 0, n_inputs=len(ins), n_outputs=4)
+            except capi.MetalHLOError as e:
+                assert e.status == 4, (name, str(e))
+                refused += 1
+                continue
+            check_shards(text, ins, count)
+            accepted += 1
+    assert accepted >= 5 and refused >= 10, (accepted, refused)
