@@ -1446,7 +1446,7 @@ def shared_intermediate_cases():
     return out
 
 
-def random_program_cases(count=60, seed=20260101, dt="f32"):
+def random_program_cases(count=60, seed=20260101, dt="f32", extents=(2, 3, 4, 5, 6, 8), more=False):
     """Seeded random programs of 12 to 24 operations (elementwise chains, compares and selects, reductions broadcast back,
     transposes, reshapes, slices, concatenations): what the optimisation levels do to a program nobody wrote by hand must not
     change its result."""
@@ -1458,7 +1458,7 @@ def random_program_cases(count=60, seed=20260101, dt="f32"):
     ctype = "SIGNED" if integer else "FLOAT"
     info = np.iinfo(NP[dt]) if integer else None
     for case in range(count):
-        shape = tuple(int(x) for x in rng.choice([2, 3, 4, 5, 6, 8], size=3))
+        shape = tuple(int(x) for x in rng.choice(list(extents), size=3))
         n_in = int(rng.integers(1, 4))
         vals = [(f"%arg{i}", shape) for i in range(n_in)]  # (name, shape), all f32
         lines = []
@@ -1474,7 +1474,8 @@ def random_program_cases(count=60, seed=20260101, dt="f32"):
             return cands[int(rng.integers(0, len(cands)))]
 
         for _ in range(int(rng.integers(12, 25))):
-            kind = rng.choice(["unary", "binary", "binary", "select", "reduce", "transpose", "reshape", "slice", "concat", "safe"])
+            kind = rng.choice(["unary", "binary", "binary", "select", "reduce", "transpose", "reshape", "slice", "concat", "safe"] +
+                              (["pad", "clamp", "iota", "dot", "reverse", "broadcast"] if more else []))
             a, shp = pick()
             t = tt(shp, dt)
             if kind == "unary":
@@ -1513,7 +1514,7 @@ def random_program_cases(count=60, seed=20260101, dt="f32"):
                 emit(f"stablehlo.transpose {a}, dims = {perm} : ({t}) -> {tt(tuple(shp[i] for i in perm), dt)}", tuple(shp[i] for i in perm))
             elif kind == "reshape":
                 total = int(np.prod(shp))
-                facts = [d for d in (2, 3, 4, 5, 6, 8) if total % d == 0] or [1]
+                facts = [d for d in tuple(extents) + (2, 3, 4) if total % d == 0] or [1]
                 d0 = int(rng.choice(facts))
                 ns = (d0, total // d0)
                 emit(f"stablehlo.reshape {a} : ({t}) -> {tt(ns, dt)}", ns)
@@ -1524,6 +1525,46 @@ def random_program_cases(count=60, seed=20260101, dt="f32"):
                 ns = tuple((h - l + s_ - 1) // s_ for l, h, s_ in zip(lo, hi, st))
                 spec = ", ".join(f"{l}:{h}:{s_}" for l, h, s_ in zip(lo, hi, st))
                 emit(f"stablehlo.slice {a} [{spec}] : ({t}) -> {tt(ns, dt)}", ns)
+            elif kind == "pad":
+                lo = [int(rng.integers(-1, 3)) for _ in shp]
+                hi = [int(rng.integers(-1, 3)) for _ in shp]
+                it_ = [int(rng.integers(0, 2)) for _ in shp]
+                ns = tuple(d + l + h + max(d - 1, 0) * i_ for d, l, h, i_ in zip(shp, lo, hi, it_))
+                if all(d >= 1 for d in ns) and len(shp) >= 1:
+                    c0 = emit(f"stablehlo.constant dense<{'7' if integer else '0.5'}> : tensor<{dt}>", ())
+                    vals.pop()
+                    emit(f"stablehlo.pad {a}, {c0}, low = {lo}, high = {hi}, interior = {it_} : ({t}, tensor<{dt}>) -> {tt(ns, dt)}", ns)
+            elif kind == "clamp":
+                b, _ = pick(shp)
+                c, _ = pick(shp)
+                lo_ = emit(f"stablehlo.minimum {b}, {c} : {t}", shp)
+                vals.pop()
+                hi_ = emit(f"stablehlo.maximum {b}, {c} : {t}", shp)
+                vals.pop()
+                emit(f"stablehlo.clamp {lo_}, {a}, {hi_} : {t}", shp)
+            elif kind == "iota" and len(shp) >= 1:
+                ax = int(rng.integers(0, len(shp)))
+                io = emit(f"stablehlo.iota dim = {ax} : {t}", shp)
+                vals.pop()
+                emit(f"stablehlo.{rng.choice(['add', 'multiply', 'maximum'])} {a}, {io} : {t}", shp)
+            elif kind == "reverse" and len(shp) >= 1:
+                ax = sorted(set(int(x) for x in rng.integers(0, len(shp), size=2)))
+                emit(f"stablehlo.reverse {a}, dims = {ax} : {t}", shp)
+            elif kind == "broadcast" and len(shp) >= 1 and len(shp) <= 3:
+                extra = int(rng.choice([1, 2, 3]))
+                pos = int(rng.integers(0, len(shp) + 1))
+                ns = shp[:pos] + (extra,) + shp[pos:]
+                dims = [i if i < pos else i + 1 for i in range(len(shp))]
+                emit(f"stablehlo.broadcast_in_dim {a}, dims = {dims} : ({t}) -> {tt(ns, dt)}", ns)
+            elif kind == "dot" and len(shp) >= 2:
+                b, bs = pick()
+                if len(bs) >= 2 and bs[-1] == shp[-1] and len(bs) == len(shp) and bs[:-2] == shp[:-2]:
+                    # a . b^T over the last axis, the leading axes as batch
+                    nb = len(shp) - 2
+                    batch = list(range(nb))
+                    ns = shp[:-1] + (bs[-2],)
+                    spec = (f"batching_dims = {batch} x {batch}, " if nb else "") + f"contracting_dims = [{len(shp) - 1}] x [{len(bs) - 1}]"
+                    emit(f"stablehlo.dot_general {a}, {b}, {spec} : ({t}, {tt(bs, dt)}) -> {tt(ns, dt)}", ns)
             elif kind == "concat":
                 b, _ = pick(shp)
                 ax = int(rng.integers(0, len(shp)))
