@@ -705,6 +705,13 @@ int mhlo_cuda_triangular_solve(int32_t dtype, const void* a_dev, const void* b_d
  * other length up to 14 000 the direct sum the reference uses for all lengths; half of either in f64. */
 int mhlo_cuda_fft_axis(int32_t dtype, int32_t kind, const void* in_dev, void* out_dev, int64_t outer, int64_t n, int64_t inner,
                        mhlo_cuda_stream_t stream);
+/* Lines longer than that, powers of two up to 2^24 points: the same passes, one launch each, between two scratch buffers
+ * in global memory. mhlo_cuda_fft_axis_scratch_bytes gives the scratch a call needs (0: the line fits shared memory, or its
+ * length is not a power of two); mhlo_cuda_fft_axis_long takes it and is mhlo_cuda_fft_axis where none is needed. In place
+ * (out_dev == in_dev) is allowed for kinds 0 and 1. */
+int64_t mhlo_cuda_fft_axis_scratch_bytes(int32_t dtype, int64_t outer, int64_t n, int64_t inner);
+int mhlo_cuda_fft_axis_long(int32_t dtype, int32_t kind, const void* in_dev, void* out_dev, void* scratch_dev, int64_t outer, int64_t n,
+                            int64_t inner, mhlo_cuda_stream_t stream);
 
 /* ---- dispatch plans ----------------------------------------------------------------------------------------------
  * The surface a host-side executor binds instead of MTLComputePipelineState / MTLBuffer / compute encoders

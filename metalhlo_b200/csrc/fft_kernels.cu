@@ -4,7 +4,8 @@
 // (n/2 butterflies per stage, two buffers, no bit reversal); every other length takes the direct O(n^2) sum with an exact
 // twiddle table, which is what the reference runs for every length (one thread per output and a loop over the line with
 // cos / sin per term, Sources/MetalHLOCore/Compiler/CodeGenerator.swift:2701-2830). Correctness kernels: lines are as long
-// as shared memory holds (8192 points in a power of two, 14 000 otherwise; half of that in f64).
+// as shared memory holds (8192 points in a power of two, 14 000 otherwise; half of that in f64); longer powers of two go
+// pass by pass through global scratch (fft_pass_kernel).
 #include "common.cuh"
 
 #include <type_traits>
@@ -103,6 +104,79 @@ __global__ void __launch_bounds__(256) fft_lines_kernel(const R* in, R* out,  //
     }
 }
 
+// Lines too long for shared memory (powers of two only): the same radix-2 Stockham passes, one launch per pass, between
+// two scratch buffers in global memory laid out [line][n]. The first pass reads the operand in its own layout (strided
+// complex lines, real lines, or half spectra completed by their conjugate mirror), the last one writes the result's.
+template <typename R>
+__global__ void __launch_bounds__(256) fft_pass_kernel(const R* src, R* dst, int64_t lines, int64_t inner, int n, int log_s, int kind, int first, int last) {
+    using C = typename PairOf<R>::type;
+    const bool inverse = kind == kInverse || kind == kComplexToReal;
+    const int half = n / 2 + 1;
+    const int64_t total = lines * (n / 2);
+    const C* csrc = reinterpret_cast<const C*>(src);
+    C* cdst = reinterpret_cast<C*>(dst);
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t line = g / (n / 2);
+        const int t = static_cast<int>(g - line * (n / 2));
+        const int64_t o = line / inner, i = line - o * inner;
+        const int s = 1 << log_s, m = n >> (log_s + 1);
+        const int p = t >> log_s, q = t & (s - 1);
+        auto load = [&](int e) -> C {
+            if (!first) return csrc[line * n + e];
+            if (kind == kRealToComplex) return C{src[line * n + e], R(0)};
+            if (kind == kComplexToReal) {
+                if (e < half) return csrc[line * half + e];
+                const C v = csrc[line * half + (n - e)];
+                return C{v.x, -v.y};
+            }
+            return csrc[(o * n + e) * inner + i];
+        };
+        const C u = load(q + s * p), v = load(q + s * (p + m));
+        double sn, cs;
+        sincospi(2.0 * static_cast<double>(static_cast<int64_t>(p) << log_s) / static_cast<double>(n), &sn, &cs);
+        const C w = C{static_cast<R>(cs), static_cast<R>(inverse ? sn : -sn)};
+        const C r0 = cadd(u, v), r1 = cmul(csub(u, v), w);
+        const R scale = inverse ? R(1) / static_cast<R>(n) : R(1);
+        auto store = [&](int e, C r) {
+            if (!last) { cdst[line * n + e] = r; return; }
+            if (kind == kComplexToReal) dst[line * n + e] = r.x * scale;
+            else if (kind == kRealToComplex) { if (e < half) cdst[line * half + e] = r; }
+            else cdst[(o * n + e) * inner + i] = C{r.x * scale, r.y * scale};
+        };
+        store(q + s * (2 * p), r0);
+        store(q + s * (2 * p + 1), r1);
+    }
+}
+
+template <typename R>
+int launch_fft_passes(int kind, const void* in, void* out, void* scratch, int64_t outer, int64_t n, int64_t inner, cudaStream_t stream) {
+    const int64_t lines = outer * inner;
+    if (lines == 0) return MHLO_CUDA_OK;
+    int stages = 0;
+    while ((int64_t{1} << stages) < n) ++stages;
+    R* buf[2] = {static_cast<R*>(scratch), static_cast<R*>(scratch) + 2 * lines * n};
+    const int64_t total = lines * (n / 2);
+    const int64_t grid = (total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32;
+    const R* src = static_cast<const R*>(in);
+    for (int st = 0; st < stages; ++st) {
+        const bool first = st == 0, last = st == stages - 1;
+        R* dst = last ? static_cast<R*>(out) : buf[st & 1];
+        fft_pass_kernel<R><<<static_cast<unsigned>(grid), 256, 0, stream>>>(src, dst, lines, inner, static_cast<int>(n), st, kind, first, last);
+        MHLO_CUDA_CHECK_LAUNCH("fft (pass)");
+        src = dst;
+    }
+    return MHLO_CUDA_OK;
+}
+
+// Whether a line of n points fits the one-launch kernel's shared memory.
+template <typename R>
+bool fft_line_fits(int64_t n) {
+    const bool pow2 = (n & (n - 1)) == 0;
+    const size_t pair = 2 * sizeof(R);
+    const size_t smem = pow2 ? pair * static_cast<size_t>(n) * 2 + pair * static_cast<size_t>(n / 2 ? n / 2 : 1) : pair * static_cast<size_t>(n) * 2;
+    return smem <= 227 * 1024;
+}
+
 template <typename R>
 int launch_fft(int kind, const void* in, void* out, int64_t outer, int64_t n, int64_t inner, cudaStream_t stream) {
     const bool pow2 = (n & (n - 1)) == 0;
@@ -125,6 +199,26 @@ int launch_fft(int kind, const void* in, void* out, int64_t outer, int64_t n, in
 
 }  // namespace
 }  // namespace mhlo
+
+extern "C" int64_t mhlo_cuda_fft_axis_scratch_bytes(int dtype, int64_t outer, int64_t n, int64_t inner) {
+    if (dtype != MHLO_DT_F32 && dtype != MHLO_DT_F64) return 0;
+    const bool fits = dtype == MHLO_DT_F32 ? mhlo::fft_line_fits<float>(n) : mhlo::fft_line_fits<double>(n);
+    if (fits || (n & (n - 1)) != 0 || outer <= 0 || inner <= 0) return 0;
+    return 2 * outer * inner * n * 2 * (dtype == MHLO_DT_F32 ? 4 : 8);  // two buffers of [lines][n] pairs
+}
+
+extern "C" int mhlo_cuda_fft_axis_long(int dtype, int kind, const void* in_dev, void* out_dev, void* scratch_dev, int64_t outer, int64_t n,
+                                       int64_t inner, mhlo_cuda_stream_t stream) {
+    const int64_t need = mhlo_cuda_fft_axis_scratch_bytes(dtype, outer, n, inner);
+    if (need == 0) return mhlo_cuda_fft_axis(dtype, kind, in_dev, out_dev, outer, n, inner, stream);
+    if (kind < 0 || kind > 3) return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "fft: kind %d", kind);
+    if (kind >= 2 && inner != 1) return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "fft: the real side of a half transform is the innermost axis (inner = %lld)", (long long)inner);
+    if (n > (1 << 24)) return mhlo::fail(MHLO_CUDA_UNSUPPORTED, "fft: lines of %lld points", (long long)n);
+    if (in_dev == nullptr || out_dev == nullptr || scratch_dev == nullptr) return mhlo::fail(MHLO_CUDA_INVALID_ARGUMENT, "fft: null pointer (a line of %lld points needs %lld bytes of scratch)", (long long)n, (long long)need);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == MHLO_DT_F32) return mhlo::launch_fft_passes<float>(kind, in_dev, out_dev, scratch_dev, outer, n, inner, s);
+    return mhlo::launch_fft_passes<double>(kind, in_dev, out_dev, scratch_dev, outer, n, inner, s);
+}
 
 extern "C" int mhlo_cuda_fft_axis(int dtype, int kind, const void* in_dev, void* out_dev, int64_t outer, int64_t n, int64_t inner,
                                   mhlo_cuda_stream_t stream) {

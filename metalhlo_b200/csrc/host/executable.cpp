@@ -1564,17 +1564,36 @@ class Lowering {
         }
         View tmp;
         if (scratch) tmp = dense_view(new_arena(it.bytes()), it);
-        DevView din = dev(in), dout = dev(out), dtmp;
+        // lines too long for the one-launch kernel's shared memory go pass by pass through two more buffers
+        int64_t long_bytes = 0;
+        int launches = 0;
+        for (const Pass& p : passes) {
+            const int64_t need = mhlo_cuda_fft_axis_scratch_bytes(dt, p.outer, p.n, p.inner);
+            long_bytes = std::max(long_bytes, need);
+            int stages = 0;
+            while ((int64_t{1} << stages) < p.n) ++stages;
+            launches += need > 0 ? stages : 1;
+        }
+        View lng;
+        if (long_bytes > 0) {
+            TensorType bytes_t;
+            bytes_t.dtype = DType::UI8;
+            bytes_t.shape = {long_bytes};
+            lng = dense_view(new_arena(long_bytes), bytes_t);
+        }
+        DevView din = dev(in), dout = dev(out), dtmp, dlng;
         keep_alive(in); keep_alive(out);
         if (scratch) { dtmp = dev(tmp); keep_alive(tmp); }
+        if (long_bytes > 0) { dlng = dev(lng); keep_alive(lng); }
         add_step("fft." + kind, [=](const Ctx& c) {
             const void* bufs[3] = {bind(din, c).base, bind(dout, c).base, scratch ? bind(dtmp, c).base : nullptr};
+            void* lp = long_bytes > 0 ? const_cast<void*>(bind(dlng, c).base) : nullptr;
             for (const Pass& p : passes) {
-                const int rc = mhlo_cuda_fft_axis(dt, p.kind, bufs[p.from], const_cast<void*>(bufs[p.to]), p.outer, p.n, p.inner, c.stream);
+                const int rc = mhlo_cuda_fft_axis_long(dt, p.kind, bufs[p.from], const_cast<void*>(bufs[p.to]), lp, p.outer, p.n, p.inner, c.stream);
                 if (rc != 0) return rc;
             }
             return 0;
-        }, static_cast<int>(passes.size()));
+        }, launches);
         set(op.results[0], out);
     }
 

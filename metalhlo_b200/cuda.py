@@ -110,6 +110,8 @@ _PROTOTYPES = {
     "mhlo_cuda_add_layer_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_add_rms_norm": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_fft_axis": (C.c_int, [C.c_int, C.c_int, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "mhlo_cuda_fft_axis_scratch_bytes": (_i64, [C.c_int, _i64, _i64, _i64]),
+    "mhlo_cuda_fft_axis_long": (C.c_int, [C.c_int, C.c_int, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mhlo_cuda_add_layer_norm_rows": (C.c_int, [C.c_int, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_add_rms_norm_rows": (C.c_int, [C.c_int, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, C.c_float, C.POINTER(RowTuning), _vp]),
     "mhlo_cuda_graph_capture_begin": (C.c_int, [_vp]),

@@ -1640,6 +1640,20 @@ def fft_cases():
             body, res, rts = parts("%0", hs, part)
             text = func([tt(shape, part)], rts, f"    %0 = stablehlo.fft %arg0, type = RFFT, length = [{n}] : ({tt(shape, part)}) -> {ct(hs, part)}\n" + body, res)
             out.append((f"fft_rfft_{part}_{n}", text, [rand(rng, shape, part)]))
+    # lines too long for shared memory: one launch per radix-2 pass through global scratch
+    for shape, lens, kinds in (((2, 16384), [16384], ("RFFT",)), ((1, 32768), [32768], ("RFFT",)), ((3, 16384), [16384], ("FFT", "IFFT"))):
+        for kind in kinds:
+            n = shape[-1]
+            if kind == "RFFT":
+                hs = shape[:-1] + (n // 2 + 1,)
+                t, c = tt(shape, "f32"), ct(hs)
+                text = func([t], [c, t], f"    %0 = stablehlo.fft %arg0, type = RFFT, length = {lens} : ({t}) -> {c}\n"
+                                         f"    %1 = stablehlo.fft %0, type = IRFFT, length = {lens} : ({c}) -> {t}", "%0, %1")
+                out.append((f"fft_long_rfft_irfft_{n}", text, [rand(rng, shape, "f32")]))
+            else:
+                c = ct(shape)
+                text = func([c], [c], f"    %0 = stablehlo.fft %arg0, type = {kind}, length = {lens} : ({c}) -> {c}", "%0")
+                out.append((f"fft_long_{kind.lower()}_{n}", text, [rand(rng, shape + (2,), "f32")]))
     # complex -> complex, forward and back, built from two real arguments
     for kind in ("FFT", "IFFT"):
         for shape, lens in (((3, 128), [128]), ((2, 8, 16), [8, 16]), ((2, 4, 6, 8), [4, 6, 8]), ((3, 5, 12), [12]), ((2, 9, 10), [9, 10])):
