@@ -1006,6 +1006,11 @@ def convolution_cases():
                              window="stride = [2, 2], pad = [[0, 1], [0, 1]]"))
         out.append(conv_case(f"conv_direct_stride2_1x1_{dt}", data((2, 37, 20, 64), dt), data((1, 1, 64, 64), dt, 0.15), dt, (2, 19, 10, 64),
                              window="stride = [2, 2]"))
+        out.append(conv_case(f"conv_direct_one_pixel_image_{dt}", data((3, 1, 1, 64), dt), data((3, 3, 64, 16), dt, 0.06), dt, (3, 1, 1, 16), window=same))
+        out.append(conv_case(f"conv_direct_padding_wider_than_the_filter_{dt}", data((1, 5, 4, 64), dt), data((3, 3, 64, 8), dt, 0.06), dt, (1, 15, 14, 8),
+                             window="pad = [[6, 6], [6, 6]]"))
+        out.append(conv_case(f"conv_direct_stride_past_the_filter_{dt}", data((2, 33, 21, 128), dt), data((1, 1, 128, 40), dt, 0.1), dt, (2, 9, 6, 40),
+                             window="stride = [4, 4]"))
         out.append(conv_case(f"conv_direct_stride_3_by_2_dilated_{dt}", data((1, 40, 45, 128), dt), data((3, 2, 128, 24), dt, 0.05), dt, (1, 13, 22, 24),
                              window="stride = [3, 2], pad = [[1, 1], [1, 0]], rhs_dilate = [2, 2]"))
     out.append(conv_case("conv_mixed_layouts_f32", data((6, 6, 2, 5), "f32"), data((3, 4, 3, 5), "f32", 0.3), "f32", (4, 2, 4, 4),
