@@ -1,5 +1,6 @@
 // Tuning database (JSON persistence) and the row-kernel auto-tuner. See tuning.h.
 #include "tuning.h"
+#include "numeric.h"
 
 #include <algorithm>
 #include <cmath>
@@ -10,6 +11,7 @@
 #include <ctime>
 #include <fstream>
 #include <sstream>
+#include <vector>
 
 #include "../../../include/mhlo_cuda.h"
 
@@ -595,6 +597,31 @@ TuningKey GemmCase::key(const std::string& device) const {
     return k;
 }
 
+namespace {
+// Fills a device buffer with 16-bit floats drawn once from (-1, 1) on the host (a 2 MB block, repeated).
+int fill_random_16(void* dev, size_t bytes, int dtype) {
+    static std::vector<uint16_t> block[2];
+    std::vector<uint16_t>& src = block[dtype == MHLO_DT_BF16 ? 1 : 0];
+    if (src.empty()) {
+        src.resize(1 << 20);
+        uint64_t state = 0x9E3779B97F4A7C15ull;
+        for (uint16_t& w : src) {
+            state = state * 6364136223846793005ull + 1442695040888963407ull;
+            const float v = static_cast<float>(static_cast<int32_t>(state >> 40) - (1 << 23)) / static_cast<float>(1 << 23);  // (-1, 1)
+            uint8_t raw[2];
+            encode_float(dtype == MHLO_DT_BF16 ? DType::BF16 : DType::F16, v, raw);
+            w = static_cast<uint16_t>(raw[0] | (raw[1] << 8));
+        }
+    }
+    const size_t chunk = src.size() * sizeof(uint16_t);
+    if (bytes == 0) return MHLO_CUDA_OK;
+    int st = mhlo_cuda_upload(dev, src.data(), std::min(chunk, bytes), nullptr);
+    for (size_t off = chunk; st == MHLO_CUDA_OK && off < bytes; off += chunk)
+        st = mhlo_cuda_copy(static_cast<uint8_t*>(dev) + off, dev, std::min(chunk, bytes - off), nullptr);
+    return st;
+}
+}  // namespace
+
 int tune_gemm(const GemmCase& c, int max_trials, TuningDatabase* db, TuningRecord* out, std::string* why) {
     if ((c.dtype != MHLO_DT_BF16 && c.dtype != MHLO_DT_F16) || c.batch < 1 || c.m < 1 || c.n < 1 || c.k < 1) {
         *why = "tune_gemm: bf16 / f16 operands and positive extents expected";
@@ -621,8 +648,9 @@ int tune_gemm(const GemmCase& c, int max_trials, TuningDatabase* db, TuningRecor
     if ((st = mhlo_cuda_alloc(a_bytes, &a)) || (st = mhlo_cuda_alloc(b_bytes, &b)) || (st = mhlo_cuda_alloc(c_bytes, &d)) ||
         (st = mhlo_cuda_event_create(&e0)) || (st = mhlo_cuda_event_create(&e1)))
         return failed(st);
-    // zero operands: the instruction stream and the traffic of the kernel do not depend on the values
-    if ((st = mhlo_cuda_memset(a, 0, a_bytes, nullptr)) || (st = mhlo_cuda_memset(b, 0, b_bytes, nullptr))) return failed(st);
+    // Random operands, not zeros: the instruction stream does not depend on the values, but the power the tensor cores
+    // draw does, and under the board's power cap the clocks (and with them the ranking of the candidates) follow it.
+    if ((st = fill_random_16(a, a_bytes, c.dtype)) || (st = fill_random_16(b, b_bytes, c.dtype))) return failed(st);
     const int64_t as[4] = {0, c.m * c.k, c.a_k_major ? c.k : 1, c.a_k_major ? 1 : c.m};
     const int64_t bs[4] = {0, c.k * c.n, c.b_k_major ? 1 : c.n, c.b_k_major ? c.k : 1};
     std::vector<TuningConfig> candidates = gemm_candidates(c.m, c.n, c.k);
@@ -692,7 +720,7 @@ int tune_attention(const AttentionCase& c, int max_trials, TuningDatabase* db, T
     if ((st = mhlo_cuda_alloc(q_bytes, &q)) || (st = mhlo_cuda_alloc(kv_bytes, &k)) || (st = mhlo_cuda_alloc(kv_bytes, &v)) ||
         (st = mhlo_cuda_alloc(q_bytes, &o)) || (st = mhlo_cuda_event_create(&e0)) || (st = mhlo_cuda_event_create(&e1)))
         return failed(st);
-    if ((st = mhlo_cuda_memset(q, 0, q_bytes, nullptr)) || (st = mhlo_cuda_memset(k, 0, kv_bytes, nullptr)) || (st = mhlo_cuda_memset(v, 0, kv_bytes, nullptr)))
+    if ((st = fill_random_16(q, q_bytes, c.dtype)) || (st = fill_random_16(k, kv_bytes, c.dtype)) || (st = fill_random_16(v, kv_bytes, c.dtype)))
         return failed(st);
     auto strides = [&](int64_t seq, int64_t* s) {
         if (c.bshd) { s[0] = seq * c.heads * c.head_dim; s[1] = c.head_dim; s[2] = c.heads * c.head_dim; }
